@@ -1,0 +1,244 @@
+#!/usr/bin/env python
+"""Headline benchmark: FTRL-proximal sparse logistic regression through the
+device parameter server (examples/s, whole job), plus push+pull keys/s.
+
+Workload (synthetic, random-init): 2^26 hashed uint64 keys, rows with 200 binary
+non-zeros (Zipf-like ids, s=1.05), 64k-row minibatch per worker, per-key fp32
+(z, sqrt_n, w) state sharded by key range over the GPUs, bounded delay tau=4,
+alpha 0.1, beta 1, l1 1, l2 0.1.
+
+    python bench.py --gpus N --steps K --warmup W          (N=1: plain python;
+    N>1: launched by torch.distributed.run, one rank per GPU)
+
+Rank 0 prints one JSON line. ``value`` is timed on the device (CUDA events, max
+over ranks) with the minibatches already resident in HBM; ``e2e`` runs the same
+steps through ``SparseLRWorker.submit`` from pinned host memory and reads each
+step's loss back to the host.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+PUBLISHED_FTRL_EXAMPLES_PER_S = 4.0e4   # online FTRL progress log of the reference (docker guide), derived
+
+
+def reference_arm():
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "reference is a Makefile C++ project (no setup.py/pyproject; pip install fails) and its "
+                       "build needs zeromq, protobuf+protoc, glog, gflags, snappy, Eigen3: none present offline",
+    }))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi during the timed region."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx = float(r[2])
+            except (ValueError, IndexError):
+                continue
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            for name, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl"])
+    ap.add_argument("--rows", type=int, default=65536)
+    ap.add_argument("--nnz-per-row", type=int, default=200)
+    ap.add_argument("--log2-keys", type=int, default=26)
+    ap.add_argument("--tau", type=int, default=4)
+    ap.add_argument("--pool", type=int, default=4, help="distinct minibatches cycled through")
+    ap.add_argument("--quant", default="none")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    import __graft_entry__ as ge
+    if rank == 0:
+        ge.build()
+    if world > 1:
+        dist.barrier()
+
+    from parameter_server_b200.models.sparse_lr import SparseLRConfig, SparseLRWorker
+    from parameter_server_b200.ops import _lib
+    from parameter_server_b200.parallel.dataplane import DataPlane, OptimizerConfig, PlaneConfig, heap_layout
+    from parameter_server_b200.parallel.fabric import Fabric
+    from parameter_server_b200.utils.synthetic import gen_batch
+
+    rows, z = args.rows, args.nnz_per_row
+    nnz = rows * z
+    n_feat = 1 << args.log2_keys
+    cap = 1
+    while cap < 2 * n_feat // world:
+        cap *= 2
+    inbox_cap = nnz if world == 1 else (nnz // world) * 5 // 4 + 4096
+    pc = PlaneConfig(table_capacity=cap, inbox_cap=inbox_cap, ring=args.tau + 2, quant=args.quant)
+    opt = OptimizerConfig(algo="ftrl", alpha=0.1, beta=1.0, l1=1.0, l2=0.1)
+    hb = heap_layout(pc, world).total()
+    fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
+    plane = DataPlane(fab, pc, opt)
+    worker = SparseLRWorker(plane, SparseLRConfig(max_rows=rows, max_nnz=nnz, tau=args.tau, hash_seed=0,
+                                                  pipeline=2))
+    # pool of distinct minibatches (per rank different data): on device and in pinned host memory
+    pool_d = [gen_batch(rows, z, n_feat, 1.05, seed=0, batch=rank * 100003 + i, device=dev)[:2]
+              for i in range(args.pool)]
+    pool_h = []
+    if not args.no_e2e:
+        for ids, y in pool_d:
+            pool_h.append((ids.cpu().pin_memory(), y.cpu().pin_memory()))
+    torch.cuda.synchronize()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def run(pool, n, log=None):
+        for i in range(n):
+            ids, y = pool[i % len(pool)]
+            worker.submit(ids, y, fixed_z=z)
+            if log is not None:
+                # D2H read of this step's running loss/accuracy counters (async, pinned)
+                with torch.cuda.stream(worker.main_stream):
+                    log[i].copy_(plane.pull_stats, non_blocking=True)
+        worker.wait()
+
+    # ---------------- device-timed arm
+    run(pool_d, args.warmup)
+    sync_all()
+    plane.check_status("warm-up")
+    uniq = [int(b.n_unique.item()) for b in worker.bufs]
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    l0 = _lib.LAUNCHES
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    run(pool_d, args.steps)
+    e1.record()
+    sync_all()
+    launches = _lib.LAUNCHES - l0
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    plane.check_status("timed region")
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    ex_per_s = world * rows * args.steps / (ms * 1e-3)
+
+    # ---------------- end-to-end arm (pinned host inputs, per-step D2H of the loss counters)
+    e2e = None
+    if not args.no_e2e:
+        log = torch.zeros((args.steps, 4), dtype=torch.float64).pin_memory()
+        run(pool_h, min(args.warmup, 3))
+        sync_all()
+        t0 = time.perf_counter()
+        run(pool_h, args.steps, log)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        sync_all()
+        plane.check_status("e2e region")
+        tt = torch.tensor([t1 - t0], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e = {"value": world * rows * args.steps / float(tt.item()), "unit": "examples/s",
+               "h2d_bytes_per_step": world * (nnz * 4 + rows * 4), "d2h_bytes_per_step": world * 32,
+               "loss_per_example_last": float((log[-1, 0] - log[-2, 0]) / max(1.0, float(log[-1, 2] - log[-2, 2])))
+               if args.steps > 1 else None}
+
+    prog = worker.read_progress()
+    if rank == 0:
+        u_mean = sum(uniq) / len(uniq)
+        out = {
+            "metric": "FTRL sparse-LR examples/sec (whole job); push+pull keys/sec in config",
+            "value": ex_per_s, "unit": "examples/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": ex_per_s / PUBLISHED_FTRL_EXAMPLES_PER_S,
+            "dtype": "fp32", "data": "synthetic (device generator, Zipf-like ids, random-init model)",
+            "impl": args.impl,
+            "config": {"model": "FTRL-proximal L1/L2 logistic regression", "global_batch": world * rows,
+                       "rows_per_worker": rows, "nnz_per_row": z, "keys": f"2^{args.log2_keys} hashed uint64",
+                       "seq_len": z, "parallelism": f"dp{world} x key-range shards{world}", "tau": args.tau,
+                       "alpha": 0.1, "beta": 1.0, "l1": 1.0, "l2": 0.1, "quant": args.quant,
+                       "unique_keys_per_step_per_worker": u_mean,
+                       "push_pull_keys_per_s": 2 * u_mean * world * args.steps / (ms * 1e-3),
+                       "l2_policy": f"inputs larger than L2: {args.pool} distinct minibatches of "
+                                    f"{nnz * 4 / 1e6:.0f} MB ids, >=300 MB sort working set per step"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "progress": {"loss_per_example": prog["loss_sum"] / max(1.0, prog["n_examples"])},
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        fab.close()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

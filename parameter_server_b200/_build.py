@@ -1,0 +1,129 @@
+"""In-tree native build: every CUDA kernel (sm_100a) and the C++ host runtime.
+
+Two shared objects are produced next to this file:
+
+* ``libpsb_cuda.so``  -- all hand-written sm_100a kernels behind a C ABI
+  (``extern "C"`` launchers taking raw device pointers and a stream); loaded
+  with ``ctypes`` by :mod:`parameter_server_b200.ops._lib`.
+* ``_core.<abi>.so``  -- the host control plane (ranges, messages, executor
+  DAG engine, van, postoffice, manager, CPU containers/filters/parsers) as a
+  pybind11 module.
+
+Objects are rebuilt only when a source or header is newer than the output.
+``nvcc`` cross-compiles without a GPU, so this also runs on CPU-only boxes.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+OBJ = PKG / "csrc" / "build"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-Xptxas", "-v",
+]
+# No --use_fast_math: it would change the exp/log/div numerics of the optimiser
+# and loss math, which is checked against an fp32 oracle.
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _newer(src_list, out: Path) -> bool:
+    if not out.exists():
+        return True
+    t = out.stat().st_mtime
+    return any(Path(s).stat().st_mtime > t for s in src_list)
+
+
+def _run(cmd, log: Path | None = None):
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if log is not None:
+        log.write_text(" ".join(map(str, cmd)) + "\n" + p.stdout)
+    if p.returncode != 0:
+        raise RuntimeError("build failed: %s\n%s" % (" ".join(map(str, cmd)), p.stdout))
+    return p.stdout
+
+
+def cuda_lib_path() -> Path:
+    return PKG / "libpsb_cuda.so"
+
+
+def core_lib_path() -> Path:
+    return PKG / ("_core" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_cuda(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every ``csrc/cuda/*.cu`` for sm_100a and link ``libpsb_cuda.so``."""
+    OBJ.mkdir(parents=True, exist_ok=True)
+    cu_dir = CSRC / "cuda"
+    headers = sorted(cu_dir.glob("*.cuh")) + sorted(cu_dir.glob("*.h"))
+    sources = sorted(cu_dir.glob("*.cu"))
+    nvcc = _nvcc()
+    objs, jobs = [], []
+    for src in sources:
+        obj = OBJ / (src.stem + ".o")
+        objs.append(obj)
+        if force or _newer([src] + headers, obj):
+            cmd = [nvcc, *NVCC_FLAGS, "-I", str(cu_dir), "-c", str(src), "-o", str(obj)]
+            jobs.append((cmd, OBJ / (src.stem + ".ptxas.log")))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            for out in ex.map(lambda j: _run(*j), jobs):
+                if verbose:
+                    print(out)
+    out = cuda_lib_path()
+    if force or jobs or _newer(objs, out):
+        _run([nvcc, "-shared", "-o", str(out), *map(str, objs), "-lcuda"])
+    return out
+
+
+def build_core(force: bool = False) -> Path:
+    """Compile the C++ host runtime (pybind11 module ``_core``)."""
+    import pybind11
+
+    OBJ.mkdir(parents=True, exist_ok=True)
+    core_dir = CSRC / "core"
+    headers = sorted(core_dir.glob("*.h"))
+    sources = sorted(core_dir.glob("*.cc"))
+    cxx = os.environ.get("CXX", "g++")
+    inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", str(core_dir)]
+    flags = ["-O2", "-g", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-pthread"]
+    objs, jobs = [], []
+    for src in sources:
+        obj = OBJ / ("core_" + src.stem + ".o")
+        objs.append(obj)
+        if force or _newer([src] + headers, obj):
+            jobs.append(([cxx, *flags, *inc, "-c", str(src), "-o", str(obj)], None))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            list(ex.map(lambda j: _run(*j), jobs))
+    out = core_lib_path()
+    if force or jobs or _newer(objs, out):
+        _run([cxx, "-shared", "-pthread", "-o", str(out), *map(str, objs), "-lz"])
+    return out
+
+
+def build_all(force: bool = False, verbose: bool = False):
+    a = build_cuda(force=force, verbose=verbose)
+    b = build_core(force=force)
+    return a, b
+
+
+if __name__ == "__main__":
+    paths = build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    for p in paths:
+        print(p)

@@ -1,0 +1,205 @@
+// Minibatch localisation on the device: from the sorted (key, position) pairs
+// produce the sorted unique key list, the CSC segment offsets, the CSR column
+// remap and the per-owner slice offsets.
+//
+// Reference behaviour: Localizer::CountUniqIndex + RemapIndex
+// (util/localizer.h:97-221) and the key-range slicing of
+// SliceKOFVMessage (system/message.h:107-147). Here the sort already groups
+// equal keys, so "unique + counts" is a head-flag scan, the remap is a scatter
+// of the unique index back to each nonzero's original position, and slicing
+// is S+1 binary searches over the unique keys.
+//
+// Kernels: k_uniq_count (heads per tile) -> k_uniq_scan (tile bases, U) ->
+// k_uniq_emit (everything else) -> k_owner_offsets.
+#include "psb_common.cuh"
+#include "psb_cuda.h"
+
+namespace psb {
+
+static constexpr int kLocThreads = 256;
+static constexpr int kLocItems = 16;
+static constexpr int kLocTile = kLocThreads * kLocItems;  // 4096 = 128 flag words
+
+__device__ __forceinline__ u32 head_ballot(const u64* __restrict__ keys, u32 n, u32 g, int lane,
+                                           u64* key_out) {
+  u64 k = g < n ? keys[g] : 0;
+  u64 prev = __shfl_up_sync(0xffffffffu, k, 1);
+  if (lane == 0) prev = (g == 0 || g >= n) ? ~k : keys[g - 1];
+  bool head = g < n && (g == 0 || k != prev);
+  *key_out = k;
+  return __ballot_sync(0xffffffffu, head);
+}
+
+__global__ void __launch_bounds__(kLocThreads) k_uniq_count(const u64* __restrict__ keys, u32 n,
+                                                            u32* __restrict__ tile_heads) {
+  __shared__ u32 s_w[8];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const u32 base = blockIdx.x * (u32)kLocTile + w * (32 * kLocItems);
+  u32 cnt = 0;
+#pragma unroll
+  for (int i = 0; i < kLocItems; ++i) {
+    u64 k;
+    cnt += __popc(head_ballot(keys, n, base + i * 32 + lane, lane, &k));
+  }
+  if (lane == 0) s_w[w] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    u32 t = 0;
+    for (int i = 0; i < 8; ++i) t += s_w[i];
+    tile_heads[blockIdx.x] = t;
+  }
+}
+
+// One block: exclusive scan of tile_heads in place; writes U.
+__global__ void __launch_bounds__(1024) k_uniq_scan(u32* __restrict__ tile_heads, u32 ntiles,
+                                                    u32* __restrict__ n_unique) {
+  __shared__ u32 s_warp[32];
+  __shared__ u32 s_carry;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  for (u32 base = 0; base < ntiles; base += 1024) {
+    u32 i = base + threadIdx.x;
+    u32 v = i < ntiles ? tile_heads[i] : 0;
+    u32 x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      u32 y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) s_warp[w] = x;
+    __syncthreads();
+    if (w == 0) {
+      u32 t = s_warp[lane];
+      u32 xs = t;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        u32 y = __shfl_up_sync(0xffffffffu, xs, o);
+        if (lane >= o) xs += y;
+      }
+      s_warp[lane] = xs - t;
+    }
+    __syncthreads();
+    u32 carry = s_carry;
+    if (i < ntiles) tile_heads[i] = carry + s_warp[w] + x - v;
+    __syncthreads();
+    if (threadIdx.x == 1023) s_carry = carry + s_warp[w] + x;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *n_unique = s_carry;
+}
+
+// Emits, for the sorted pairs (keys[i], pos[i]):
+//   ukeys[u], seg_off[u] at segment heads (seg_off[U] = n),
+//   csr_col[pos[i]] = u            (CSR remap to local column ids),
+//   pos[i] <- row of pos[i]        (in place: becomes the CSC row index),
+//   csc_val[i] = vals[pos[i]]      (only when vals != null),
+//   flagbits[i/32], wordbase[i/32] (head bitmap and heads before each word).
+// Row of a position: pos / fixed_z when row_ptr is null, else the row whose
+// [row_ptr[r], row_ptr[r+1]) contains it.
+__global__ void __launch_bounds__(kLocThreads) k_uniq_emit(
+    const u64* __restrict__ keys, u32* __restrict__ pos, u32 n, const u32* __restrict__ tile_base,
+    const u32* __restrict__ row_ptr, u32 n_rows, u32 fixed_z, const float* __restrict__ vals,
+    u64* __restrict__ ukeys, u32* __restrict__ seg_off, u32* __restrict__ csr_col,
+    float* __restrict__ csc_val, u32* __restrict__ flagbits, u32* __restrict__ wordbase) {
+  __shared__ u32 s_w[8];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const u32 base = blockIdx.x * (u32)kLocTile + w * (32 * kLocItems);
+  u64 key[kLocItems];
+  u32 bal[kLocItems];
+  u32 cnt = 0;
+#pragma unroll
+  for (int i = 0; i < kLocItems; ++i) {
+    bal[i] = head_ballot(keys, n, base + i * 32 + lane, lane, &key[i]);
+    cnt += __popc(bal[i]);
+  }
+  if (lane == 0) s_w[w] = cnt;
+  __syncthreads();
+  u32 run = tile_base[blockIdx.x];
+  for (int i = 0; i < w; ++i) run += s_w[i];
+  const u32 le = 0xffffffffu >> (31 - lane);
+#pragma unroll
+  for (int i = 0; i < kLocItems; ++i) {
+    u32 g = base + i * 32 + lane;
+    if (g - lane < n && lane == 0) {
+      flagbits[g >> 5] = bal[i];
+      wordbase[g >> 5] = run;
+    }
+    if (g < n) {
+      u32 u = run + __popc(bal[i] & le) - 1;
+      if ((bal[i] >> lane) & 1u) {
+        ukeys[u] = key[i];
+        seg_off[u] = g;
+      }
+      u32 p = pos[g];
+      csr_col[p] = u;
+      if (csc_val) csc_val[g] = vals[p];
+      u32 r;
+      if (row_ptr == nullptr) {
+        r = p / fixed_z;
+      } else {
+        u32 lo = 0, hi = n_rows;  // largest r with row_ptr[r] <= p
+        while (hi - lo > 1) {
+          u32 mid = (lo + hi) >> 1;
+          if (row_ptr[mid] <= p) lo = mid; else hi = mid;
+        }
+        r = lo;
+      }
+      pos[g] = r;
+    }
+    run += __popc(bal[i]);
+  }
+}
+
+// own_off[s] = lower_bound(ukeys[0..U), bounds[s]) for s in 0..S; own_off[S] = U.
+// Also closes the CSC offsets with seg_off[U] = n.
+__global__ void k_owner_offsets(const u64* __restrict__ ukeys, const u32* __restrict__ n_unique,
+                                const u64* __restrict__ bounds, int S, u32 n,
+                                u32* __restrict__ seg_off, u32* __restrict__ own_off) {
+  const u32 U = *n_unique;
+  int s = threadIdx.x;
+  if (s == 0) seg_off[U] = n;
+  if (s > S) return;
+  if (s == S) { own_off[S] = U; return; }
+  u64 b = bounds[s];
+  u32 lo = 0, hi = U;
+  while (lo < hi) {
+    u32 mid = (lo + hi) >> 1;
+    if (ukeys[mid] < b) lo = mid + 1; else hi = mid;
+  }
+  own_off[s] = lo;
+}
+
+}  // namespace psb
+
+using namespace psb;
+
+extern "C" size_t psb_localize_scratch_bytes(uint32_t n) {
+  size_t ntiles = (n + kLocTile - 1) / kLocTile;
+  return sizeof(u32) * (ntiles + 16);
+}
+
+extern "C" int psb_localize(const psb_u64* sorted_keys, uint32_t* sorted_pos, uint32_t n,
+                            const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z,
+                            const float* vals, const psb_u64* bounds, int S, psb_u64* ukeys,
+                            uint32_t* seg_off, uint32_t* csr_col, float* csc_val,
+                            uint32_t* flagbits, uint32_t* wordbase, uint32_t* n_unique,
+                            uint32_t* own_off, void* scratch, cudaStream_t stream) {
+  if (S < 1 || S > 64) return -(int)cudaErrorInvalidValue;
+  if (row_ptr == nullptr && fixed_z == 0) return -(int)cudaErrorInvalidValue;
+  u32 ntiles = (n + kLocTile - 1) / kLocTile;
+  u32* tile_heads = (u32*)scratch;
+  if (n == 0) {
+    cudaMemsetAsync(n_unique, 0, sizeof(u32), stream);
+    cudaMemsetAsync(own_off, 0, sizeof(u32) * (S + 1), stream);
+    cudaMemsetAsync(seg_off, 0, sizeof(u32), stream);
+    return -(int)cudaGetLastError();
+  }
+  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>(sorted_keys, n, tile_heads);
+  k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique);
+  k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>(sorted_keys, sorted_pos, n, tile_heads, row_ptr,
+                                                  n_rows, fixed_z, vals, ukeys, seg_off, csr_col,
+                                                  csc_val, flagbits, wordbase);
+  k_owner_offsets<<<1, 96, 0, stream>>>(ukeys, n_unique, bounds, S, n, seg_off, own_off);
+  return -(int)cudaGetLastError();
+}

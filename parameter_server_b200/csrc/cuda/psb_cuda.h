@@ -1,0 +1,170 @@
+// C ABI of libpsb_cuda.so: every hand-written sm_100a kernel of the library is
+// reached through one of these launchers. All pointers are device pointers
+// unless stated otherwise; launchers enqueue on `stream` and never allocate or
+// synchronise. Return value: 0 on success, otherwise minus the cudaError (a few
+// launchers document a non-negative payload instead).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PSB_MAX_SHARDS 16
+typedef unsigned long long psb_u64;  // 64-bit keys (same ABI as uint64_t)
+
+// ---------------------------------------------------------------- sort / localise
+size_t psb_sort_scratch_bytes(uint32_t n, int begin_bit, int end_bit);
+int psb_sort_pairs(const void* in, int in_kind, psb_u64 seed, psb_u64* keys_a, uint32_t* vals_a,
+                   int vals_given, psb_u64* keys_b, uint32_t* vals_b, uint32_t n, int begin_bit,
+                   int end_bit, void* scratch, uint32_t* status, cudaStream_t stream);
+size_t psb_localize_scratch_bytes(uint32_t n);
+int psb_localize(const psb_u64* sorted_keys, uint32_t* sorted_pos, uint32_t n,
+                 const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z, const float* vals,
+                 const psb_u64* bounds, int S, psb_u64* ukeys, uint32_t* seg_off,
+                 uint32_t* csr_col, float* csc_val, uint32_t* flagbits, uint32_t* wordbase,
+                 uint32_t* n_unique, uint32_t* own_off, void* scratch, cudaStream_t stream);
+
+// ---------------------------------------------------------------- server shard table
+// Optimiser selection for the scalar-value table.
+enum { PSB_ALGO_FTRL = 0, PSB_ALGO_ADAGRAD = 1, PSB_ALGO_SGD = 2, PSB_ALGO_SUM = 3 };
+enum { PSB_LR_CONSTANT = 0, PSB_LR_DECAY = 1 };
+enum { PSB_LOSS_LOGIT = 0, PSB_LOSS_SQUARE_HINGE = 1 };
+enum { PSB_QUANT_NONE = 0, PSB_QUANT_INT8 = 1, PSB_QUANT_FP16 = 2 };
+
+typedef struct {
+  int algo;      // PSB_ALGO_*
+  int lr_type;   // PSB_LR_*
+  float alpha, beta;
+  float l1, l2;  // elastic-net penalty
+} PsbOptimizer;
+
+// What a worker needs to pull from S shards and compute margins (kernel F2).
+typedef struct {
+  int S;
+  int insert;                 // insert absent keys on pull (KVMap first-touch semantics)
+  void* table[PSB_MAX_SHARDS];            // Entry* of shard s (local or peer-mapped)
+  psb_u64 mask[PSB_MAX_SHARDS];          // capacity-1 of shard s
+  const uint32_t* applied[PSB_MAX_SHARDS];  // shard s's "applied" counter (may be peer-mapped)
+  uint32_t need_applied;      // bounded delay: wait until applied[s] >= need_applied
+  const psb_u64* ukeys;
+  const uint32_t* n_unique;
+  const uint32_t* own_off;
+  float* w_local;             // out: weight per unique key
+  int32_t* slot_local;        // out (nullable): slot of each key in its owner's table, -1 if absent
+  float* grad_zero;           // nullable: zeroed per unique key (prepares the push)
+  // margins (skipped when n_rows == 0)
+  const uint32_t* row_ptr;    // nullable -> fixed_z nonzeros per row
+  uint32_t n_rows, fixed_z;
+  const uint32_t* csr_col;
+  const float* csr_val;       // nullable -> binary features
+  const float* y;             // labels in {-1,+1}
+  int loss;                   // PSB_LOSS_*
+  float* gcoef;               // out: d loss / d margin per row
+  float* margin;              // out (nullable)
+  double* stats;              // += {loss_sum, n_correct, n_rows}
+  uint32_t* auc_hist;         // nullable: [2][4096] histogram of sigmoid(margin) by label
+  uint32_t* bar;              // 2 words, grid barrier
+  uint32_t* status;
+} PsbPullParams;
+
+// Worker half of a push (kernel F1a): X^T g over CSC segments, range partition,
+// optional block-scaled quantisation, peer stores into the owners' inboxes, signal.
+typedef struct {
+  int S;
+  uint32_t ts1;               // timestamp+1 published in the ready flags
+  uint32_t inbox_cap;         // records per (owner, source) inbox
+  int quant;                  // PSB_QUANT_*
+  int send_keys;              // 0 on a key-cache hit: values only
+  psb_u64* inbox_keys[PSB_MAX_SHARDS];   // owner s's inbox for this source and ring slot
+  void* inbox_vals[PSB_MAX_SHARDS];
+  uint32_t* ready[PSB_MAX_SHARDS];        // owner s's ready flag for this source and ring slot
+  uint32_t* count[PSB_MAX_SHARDS];        // owner s's record count word
+  const uint32_t* applied[PSB_MAX_SHARDS];  // owner s's applied counter (ring reuse gate)
+  uint32_t need_applied;
+  const psb_u64* ukeys;
+  const uint32_t* n_unique;
+  const uint32_t* own_off;
+  // gradient phase (skipped when nnz == 0: `grad` then holds user values)
+  uint32_t nnz;
+  const uint32_t* csc_row;
+  const float* csc_val;       // nullable -> binary
+  const uint32_t* flagbits;
+  const uint32_t* wordbase;
+  const float* gcoef;
+  float* grad;                // per unique key; must be zero on entry when nnz > 0
+  uint32_t* bar;              // 2 words
+  uint32_t* done;             // 1 word, zero on entry, left zero
+  uint32_t* status;
+} PsbPushParams;
+
+// Server half of a push (kernel F1b): wait for the sources' flags, reduce
+// duplicate keys across sources, run the optimiser once per touched key.
+typedef struct {
+  int S;
+  uint32_t ts1;
+  uint32_t inbox_cap;
+  int quant;
+  void* table;
+  psb_u64 mask;
+  const psb_u64* inbox_keys[PSB_MAX_SHARDS];
+  const void* inbox_vals[PSB_MAX_SHARDS];
+  const uint32_t* ready[PSB_MAX_SHARDS];
+  const uint32_t* count[PSB_MAX_SHARDS];
+  uint8_t alive[PSB_MAX_SHARDS];          // dead sources are skipped (their waits complete)
+  uint8_t cached[PSB_MAX_SHARDS];         // key-cache hit: reuse slot_cache[r], no keys sent
+  uint32_t* slot_cache[PSB_MAX_SHARDS];   // per source: slot of each record (scratch + key cache)
+  PsbOptimizer opt;
+  double* stats;              // += {d_nnz, sum w^2, sum dw^2, n_updates}
+  uint32_t* applied;          // set to ts1 when done
+  uint32_t wait_iters;        // bounded wait budget for the ready flags (0 = default)
+  uint32_t* bar;
+  uint32_t* done;
+  uint32_t* status;
+} PsbApplyParams;
+
+int psb_table_init(void* table, psb_u64 capacity, cudaStream_t stream);
+int psb_pull_margin(const PsbPullParams* p, cudaStream_t stream);
+int psb_push(const PsbPushParams* p, cudaStream_t stream);
+int psb_apply(const PsbApplyParams* p, cudaStream_t stream);
+// Compacts (key, w) of every entry with w != 0 into out_keys/out_w; *out_n gets the count.
+int psb_table_dump(const void* table, psb_u64 capacity, psb_u64* out_keys, float* out_w,
+                   psb_u64 out_cap, unsigned long long* out_n, cudaStream_t stream);
+// Bulk load (key, s0, s1, w) tuples into a table (checkpoint restore / model_input).
+int psb_table_load(void* table, psb_u64 mask, const psb_u64* keys, const float* s0,
+                   const float* s1, const float* w, psb_u64 n, uint32_t* status,
+                   cudaStream_t stream);
+// Full state dump for checkpoints: every occupied slot.
+int psb_table_export(const void* table, psb_u64 capacity, psb_u64* out_keys, float* out_s0,
+                     float* out_s1, float* out_w, psb_u64 out_cap, unsigned long long* out_n,
+                     cudaStream_t stream);
+
+// number of CTAs a cooperative launch of the three fused kernels uses
+int psb_coop_grid(int which);
+int psb_struct_size(int which);
+
+// ---------------------------------------------------------------- data / misc
+int psb_gen_batch(uint32_t* ids32, psb_u64* ids64, float* vals, float* y, uint32_t n_rows,
+                  uint32_t z, psb_u64 n_feat, double zipf_s, psb_u64 seed, psb_u64 batch,
+                  int real_values, cudaStream_t stream);
+int psb_hash_ids(const uint32_t* ids32, const psb_u64* ids64, psb_u64* keys, psb_u64 n,
+                 psb_u64 seed, cudaStream_t stream);
+int psb_flush_l2(uint32_t* buf, psb_u64 n_words, uint32_t v, cudaStream_t stream);
+int psb_device_sm_count(void);
+
+// ---------------------------------------------------------------- symmetric heap (CUDA IPC)
+int psb_heap_alloc(void** ptr, size_t bytes);
+int psb_heap_free(void* ptr);
+int psb_ipc_export(void* ptr, void* handle_out /*64 host bytes*/);
+int psb_ipc_open(const void* handle, void** ptr);
+int psb_ipc_close(void* ptr);
+int psb_ipc_handle_bytes(void);
+int psb_set_device(int dev);
+int psb_can_access_peer(int dev, int peer);
+const char* psb_error_string(int neg_code);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,261 @@
+// Single-pass-per-digit LSD radix sort of (uint64 key, uint32 payload) pairs.
+//
+// This is the device replacement for the recursive thread merge sort that the
+// reference uses to localise a minibatch (util/parallel_sort.h:14-41, called
+// from util/localizer.h:97-160). Design (B200: 148 SMs, 126 MB L2, 6.5 TB/s):
+//
+//   * one up-front kernel reads the keys once and builds the histograms of all
+//     digits (and can hash raw feature ids to uint64 keys on the way in);
+//   * each 8-bit digit pass is ONE kernel: a tile of 256 threads x 16 keys is
+//     ranked with warp match-any, tile totals are chained with a decoupled
+//     look-back over per-tile status words, and the tile is scattered through
+//     shared memory so that global stores go out in digit runs;
+//   * tiles take their index from an atomic ticket, so a predecessor tile is
+//     always scheduled before its successor looks back at it; the look-back
+//     spin is bounded and reports through the status word.
+//
+// Traffic per pass is one read and one write of the pairs (24 B per element).
+#include "psb_common.cuh"
+#include "psb_cuda.h"
+
+namespace psb {
+
+static constexpr int kSortThreads = 256;
+static constexpr int kSortItems = 16;
+static constexpr int kSortTile = kSortThreads * kSortItems;  // 4096
+static constexpr int kRadixBits = 8;
+static constexpr int kRadix = 1 << kRadixBits;
+static constexpr u32 kFlagAgg = 1u << 30;
+static constexpr u32 kFlagIncl = 2u << 30;
+static constexpr u32 kValMask = (1u << 30) - 1;
+
+__device__ __forceinline__ u32 digit_of(u64 k, int shift, u32 dmask) {
+  return (u32)(k >> shift) & dmask;
+}
+
+// in_kind: 0 = uint64 keys (used as is), 1 = uint32 ids, 2 = uint64 ids; for
+// 1 and 2 the key is hash_id_to_key(id, seed) and is written to keys_out.
+__global__ void __launch_bounds__(256) k_sort_histogram(
+    const void* __restrict__ in, int in_kind, u64 seed, u64* __restrict__ keys_out, u32 n,
+    int begin_bit, int end_bit, u32* __restrict__ ghist) {
+  __shared__ u32 sh[8 * kRadix];
+  const int npass = (end_bit - begin_bit + kRadixBits - 1) / kRadixBits;
+  for (int i = threadIdx.x; i < npass * kRadix; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  for (u32 i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    u64 k;
+    if (in_kind == 0) {
+      k = ((const u64*)in)[i];
+    } else {
+      u64 id = in_kind == 1 ? (u64)((const u32*)in)[i] : ((const u64*)in)[i];
+      k = hash_id_to_key(id, seed);
+      keys_out[i] = k;
+    }
+    for (int p = 0; p < npass; ++p) {
+      int shift = begin_bit + p * kRadixBits;
+      int bits = min(kRadixBits, end_bit - shift);
+      atomicAdd(&sh[p * kRadix + digit_of(k, shift, (1u << bits) - 1)], 1u);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < npass * kRadix; i += blockDim.x)
+    if (sh[i]) atomicAdd(&ghist[i], sh[i]);
+}
+
+// Exclusive scan of one value per thread across a 256-thread block.
+__device__ __forceinline__ u32 block_excl_scan_256(u32 v, u32* s_warp /*8 words*/, u32* total) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  u32 x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    u32 y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  if (lane == 31) s_warp[w] = x;
+  __syncthreads();
+  u32 base = 0, tot = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    u32 t = s_warp[i];
+    if (i < w) base += t;
+    tot += t;
+  }
+  if (total) *total = tot;
+  __syncthreads();
+  return base + x - v;
+}
+
+// One digit pass. `status` holds ntiles*256 zeroed words for this pass.
+__global__ void __launch_bounds__(kSortThreads) k_sort_onesweep(
+    const u64* __restrict__ keys_in, const u32* __restrict__ vals_in, u64* __restrict__ keys_out,
+    u32* __restrict__ vals_out, u32 n, int shift, u32 dmask, const u32* __restrict__ ghist,
+    u32* __restrict__ ticket, u32* __restrict__ status, u32* __restrict__ err) {
+  __shared__ u64 s_keys[kSortTile];            // 32 KB, reused for payloads
+  __shared__ u32 s_cnt[8 * kRadix];            // per-warp digit counters, 8 KB
+  __shared__ u32 s_dstart[kRadix];             // tile-local start of each digit
+  __shared__ u32 s_gbase[kRadix];              // global dst = s_gbase[d] + p
+  __shared__ u32 s_warp[8];
+  __shared__ u32 s_tile;
+
+  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+  if (t == 0) s_tile = atomicAdd(ticket, 1u);
+  for (int i = t; i < 8 * kRadix; i += kSortThreads) s_cnt[i] = 0;
+  __syncthreads();
+  const u32 tile = s_tile;
+  const u32 tile_base = tile * (u32)kSortTile;
+  const u32 nvalid = min((u32)kSortTile, n - tile_base);
+
+  // ---- load (warp-striped: consecutive lanes read consecutive elements) ----
+  u64 key[kSortItems];
+  u32 off[kSortItems];
+  const u32 wbase = w * (32 * kSortItems);
+#pragma unroll
+  for (int i = 0; i < kSortItems; ++i) {
+    u32 idx = wbase + i * 32 + lane;
+    key[i] = idx < nvalid ? keys_in[tile_base + idx] : kEmptyKey;
+  }
+  // ---- rank inside the warp, in (item, lane) order ----
+  const u32 lt = (1u << lane) - 1;
+#pragma unroll
+  for (int i = 0; i < kSortItems; ++i) {
+    u32 d = digit_of(key[i], shift, dmask);
+    u32 m = __match_any_sync(0xffffffffu, d);
+    int leader = __ffs(m) - 1;
+    u32 old = 0;
+    if (lane == leader) {
+      old = s_cnt[w * kRadix + d];
+      s_cnt[w * kRadix + d] = old + __popc(m);
+    }
+    old = __shfl_sync(0xffffffffu, old, leader);
+    off[i] = old + __popc(m & lt);
+    __syncwarp();
+  }
+  __syncthreads();
+  // ---- per digit (thread t owns digit t): prefix over warps, tile total ----
+  u32 total = 0;
+#pragma unroll
+  for (int ww = 0; ww < 8; ++ww) {
+    u32 c = s_cnt[ww * kRadix + t];
+    s_cnt[ww * kRadix + t] = total;
+    total += c;
+  }
+  // publish the tile aggregate early so successors can move on
+  u32* my_status = status + (size_t)tile * kRadix;
+  if (tile == 0) st_release_gpu(&my_status[t], kFlagIncl | total);
+  else st_release_gpu(&my_status[t], kFlagAgg | total);
+
+  u32 dstart = block_excl_scan_256(total, s_warp, nullptr);
+  s_dstart[t] = dstart;
+  // global exclusive base of digit t
+  u32 gh = ghist[t];
+  u32 gex = block_excl_scan_256(gh, s_warp, nullptr);
+
+  // ---- decoupled look-back for digit t ----
+  u32 ex = 0;
+  if (tile > 0) {
+    long long p = (long long)tile - 1;
+    u32 spins = 0;
+    while (p >= 0) {
+      u32 s = ld_acquire_gpu(status + (size_t)p * kRadix + t);
+      u32 f = s & ~kValMask;
+      if (f == 0) {
+        if (++spins > kGridWaitIters) { set_status(err, kLookbackTimeout); break; }
+        __nanosleep(20);
+        continue;
+      }
+      ex += s & kValMask;
+      if (f == kFlagIncl) break;
+      --p;
+    }
+    st_release_gpu(&my_status[t], kFlagIncl | ((ex + total) & kValMask));
+  }
+  s_gbase[t] = gex + ex - dstart;
+  __syncthreads();
+
+  // ---- scatter keys into shared memory in digit order ----
+#pragma unroll
+  for (int i = 0; i < kSortItems; ++i) {
+    u32 d = digit_of(key[i], shift, dmask);
+    u32 p = s_dstart[d] + s_cnt[w * kRadix + d] + off[i];
+    off[i] = p;
+    s_keys[p] = key[i];
+  }
+  __syncthreads();
+  u32 dst[kSortItems];
+#pragma unroll
+  for (int j = 0; j < kSortItems; ++j) {
+    u32 p = t + j * kSortThreads;
+    u64 k = s_keys[p];
+    u32 d = digit_of(k, shift, dmask);
+    dst[j] = s_gbase[d] + p;
+    if (p < nvalid) keys_out[dst[j]] = k;
+  }
+  if (vals_out == nullptr) return;
+  __syncthreads();
+  // ---- payloads through the same staging buffer ----
+  u32* s_vals = reinterpret_cast<u32*>(s_keys);
+#pragma unroll
+  for (int i = 0; i < kSortItems; ++i) {
+    u32 idx = wbase + i * 32 + lane;
+    u32 v = 0;
+    if (idx < nvalid) v = vals_in ? vals_in[tile_base + idx] : tile_base + idx;
+    s_vals[off[i]] = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kSortItems; ++j) {
+    u32 p = t + j * kSortThreads;
+    if (p < nvalid) vals_out[dst[j]] = s_vals[p];
+  }
+}
+
+}  // namespace psb
+
+using namespace psb;
+
+extern "C" size_t psb_sort_scratch_bytes(uint32_t n, int begin_bit, int end_bit) {
+  int npass = (end_bit - begin_bit + kRadixBits - 1) / kRadixBits;
+  size_t ntiles = (n + kSortTile - 1) / kSortTile;
+  if (ntiles == 0) ntiles = 1;
+  // ghist | tickets | err(+pad) | status
+  return sizeof(u32) * ((size_t)npass * kRadix + 16 + (size_t)npass * ntiles * kRadix);
+}
+
+// Sorts n pairs by key bits [begin_bit, end_bit). Buffers A (keys_a, vals_a) and
+// B (keys_b, vals_b) are ping-ponged; the input is `in` (see k_sort_histogram
+// for in_kind; for in_kind 0 `in` may equal keys_a). vals_a may be null on
+// entry, meaning payload = element index. Returns 0 if the result is in A and
+// 1 if it is in B, or a negative cudaError.
+extern "C" int psb_sort_pairs(const void* in, int in_kind, psb_u64 seed, psb_u64* keys_a,
+                              uint32_t* vals_a, int vals_given, psb_u64* keys_b, uint32_t* vals_b,
+                              uint32_t n, int begin_bit, int end_bit, void* scratch,
+                              uint32_t* status, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (end_bit <= begin_bit || end_bit > 64 || begin_bit < 0) return -(int)cudaErrorInvalidValue;
+  const int npass = (end_bit - begin_bit + kRadixBits - 1) / kRadixBits;
+  const u32 ntiles = (n + kSortTile - 1) / kSortTile;
+  u32* ghist = (u32*)scratch;
+  u32* tickets = ghist + (size_t)npass * kRadix;
+  u32* st = tickets + 16;
+  cudaMemsetAsync(scratch, 0, psb_sort_scratch_bytes(n, begin_bit, end_bit), stream);
+  int hb = (int)min((u32)(148 * 8), (n + 255) / 256);
+  k_sort_histogram<<<hb, 256, 0, stream>>>(in, in_kind, seed, keys_a, n, begin_bit, end_bit, ghist);
+  const u64* kin = in_kind == 0 ? (const u64*)in : keys_a;
+  const u32* vin = vals_given ? vals_a : nullptr;
+  int where = 0;  // where the *next output* goes: first pass reads A (or `in`), writes B
+  for (int p = 0; p < npass; ++p) {
+    int shift = begin_bit + p * kRadixBits;
+    int bits = min(kRadixBits, end_bit - shift);
+    u64* kout = where == 0 ? keys_b : keys_a;
+    u32* vout = where == 0 ? vals_b : vals_a;
+    k_sort_onesweep<<<ntiles, kSortThreads, 0, stream>>>(
+        kin, vin, kout, vout, n, shift, (1u << bits) - 1, ghist + (size_t)p * kRadix, tickets + p,
+        st + (size_t)p * ntiles * kRadix, status);
+    kin = kout;
+    vin = vout;
+    where ^= 1;
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return -(int)e;
+  return where;  // after an odd number of passes the data is in B (where==1)
+}

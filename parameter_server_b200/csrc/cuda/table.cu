@@ -1,0 +1,536 @@
+// Server-shard table and the three fused push/pull kernels for scalar values.
+//
+//   k_pull_margin  (F2)  worker: gather w for each unique key straight out of
+//                        the owning shard's table through (peer) pointers,
+//                        then X.w margins, loss, d loss/d margin and metrics.
+//                        Replaces KVMap::GetValue (parameter/kv_map.h:69-77),
+//                        the pull round trip (parameter/parameter.cc:5-49) and
+//                        the worker SpMV + loss (app/linear_method/
+//                        async_sgd.h:264-296, loss.h:81-93).
+//   k_push         (F1a) worker: X^T g as a segmented reduction over the CSC
+//                        order the sort produced, range partition, optional
+//                        block-scaled quantisation (fixed-point filter), peer
+//                        stores into the owners' inboxes, release flags.
+//                        Replaces loss.h:91-92, SliceKOFVMessage
+//                        (system/message.h:107-147) and the Van send path.
+//   k_apply        (F1b) server: bounded wait on the sources' flags, duplicate
+//                        key reduce across sources, one optimiser step per
+//                        touched key (FTRLEntry::Set / AdaGradEntry::Set,
+//                        app/linear_method/async_sgd.h:132-176), progress
+//                        stats (SGDState::UpdateWeight, :104-114).
+//
+// All three are persistent kernels launched cooperatively (one wave, grid
+// barrier between phases). Nothing here uses TMA or cluster multicast: remote
+// data moves with plain loads/stores through peer-mapped pointers.
+#include <cuda_fp16.h>
+#include "psb_common.cuh"
+#include "psb_cuda.h"
+
+namespace psb {
+
+static constexpr int kThreads = 256;
+static constexpr u32 kMaxProbe = 1u << 16;
+
+// ------------------------------------------------------------------ optimiser
+__device__ __forceinline__ float lr_eval(const PsbOptimizer& o, float x) {
+  return o.lr_type == PSB_LR_CONSTANT ? o.alpha : o.alpha / (x + o.beta);
+}
+__device__ __forceinline__ float prox(const PsbOptimizer& o, float z, float eta) {
+  float leta = o.l1 * eta;
+  if (z <= leta && z >= -leta) return 0.f;
+  return z > 0 ? (z - leta) / (1.f + o.l2 * eta) : (z + leta) / (1.f + o.l2 * eta);
+}
+
+// One optimiser step on (w, s0, s1) with gradient g; returns the new weight.
+__device__ __forceinline__ float opt_step(const PsbOptimizer& o, float g, float& w, float& s0,
+                                          float& s1) {
+  if (o.algo == PSB_ALGO_FTRL) {
+    // s0 = z, s1 = sqrt(n)
+    float sn = sqrtf(s1 * s1 + g * g);
+    float sigma = (sn - s1) / o.alpha;
+    s0 += g - sigma * w;
+    s1 = sn;
+    float eta = lr_eval(o, sn);
+    w = prox(o, -s0 * eta, eta);
+  } else if (o.algo == PSB_ALGO_ADAGRAD) {
+    s0 += g * g;  // sum of squared gradients
+    float eta = lr_eval(o, sqrtf(s0));
+    w = prox(o, w - eta * g, eta);
+  } else if (o.algo == PSB_ALGO_SGD) {
+    s0 += 1.f;    // number of updates of this key
+    float eta = lr_eval(o, sqrtf(s0));
+    w = prox(o, w - eta * g, eta);
+  } else {        // PSB_ALGO_SUM: plain accumulate (KVVector PLUS / custom "+=" entries)
+    w += g;
+  }
+  return w;
+}
+
+struct StatAcc {
+  double d_nnz = 0, w2 = 0, dw2 = 0, n = 0;
+  __device__ __forceinline__ void add(float w_new, float w_old) {
+    if (w_new == 0.f && w_old != 0.f) d_nnz -= 1;
+    else if (w_new != 0.f && w_old == 0.f) d_nnz += 1;
+    w2 += (double)w_new * w_new;
+    double d = (double)w_new - w_old;
+    dw2 += d * d;
+    n += 1;
+  }
+};
+
+__device__ __forceinline__ void block_add4(double a, double b, double c, double d, double* out) {
+  __shared__ double s_acc[4];
+  if (threadIdx.x < 4) s_acc[threadIdx.x] = 0;
+  __syncthreads();
+  a = warp_sum_d(a); b = warp_sum_d(b); c = warp_sum_d(c); d = warp_sum_d(d);
+  if ((threadIdx.x & 31) == 0) {
+    atomicAdd(&s_acc[0], a); atomicAdd(&s_acc[1], b);
+    atomicAdd(&s_acc[2], c); atomicAdd(&s_acc[3], d);
+  }
+  __syncthreads();
+  if (threadIdx.x < 4 && out && s_acc[threadIdx.x] != 0) atomicAdd(&out[threadIdx.x], s_acc[threadIdx.x]);
+}
+
+// ------------------------------------------------------------------ table init / io
+__global__ void k_table_init(Entry* tab, u64 cap) {
+  for (u64 i = blockIdx.x * (u64)blockDim.x + threadIdx.x; i < cap; i += (u64)gridDim.x * blockDim.x) {
+    uint4* p = reinterpret_cast<uint4*>(&tab[i]);
+    p[0] = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0u, 0u);
+    p[1] = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+template <bool kAll>
+__global__ void k_table_dump(const Entry* tab, u64 cap, u64* out_keys, float* out_s0, float* out_s1,
+                             float* out_w, u64 out_cap, unsigned long long* out_n) {
+  const int lane = threadIdx.x & 31;
+  for (u64 base = (blockIdx.x * (u64)blockDim.x + threadIdx.x) - lane; base < cap;
+       base += (u64)gridDim.x * blockDim.x) {
+    u64 i = base + lane;
+    bool take = false;
+    Entry e;
+    if (i < cap) {
+      e = tab[i];
+      take = e.key != kEmptyKey && (kAll || (e.w != 0.f && e.w == e.w));
+    }
+    u32 m = __ballot_sync(0xffffffffu, take);
+    if (m == 0) continue;
+    unsigned long long at = 0;
+    if (lane == 0) at = atomicAdd(out_n, (unsigned long long)__popc(m));
+    at = __shfl_sync(0xffffffffu, at, 0);
+    if (take) {
+      u64 o = at + __popc(m & ((1u << lane) - 1));
+      if (o < out_cap) {
+        out_keys[o] = e.key;
+        out_w[o] = e.w;
+        if (kAll) { out_s0[o] = e.s0; out_s1[o] = e.s1; }
+      }
+    }
+  }
+}
+
+__global__ void k_table_load(Entry* tab, u64 mask, const u64* keys, const float* s0, const float* s1,
+                             const float* w, u64 n, u32* status) {
+  for (u64 i = blockIdx.x * (u64)blockDim.x + threadIdx.x; i < n; i += (u64)gridDim.x * blockDim.x) {
+    long long slot = table_find<true>(tab, mask, keys[i], kMaxProbe);
+    if (slot < 0) { set_status(status, kTableFull); continue; }
+    tab[slot].w = w ? w[i] : 0.f;
+    tab[slot].s0 = s0 ? s0[i] : 0.f;
+    tab[slot].s1 = s1 ? s1[i] : 0.f;
+  }
+}
+
+// ------------------------------------------------------------------ F2: pull + margins
+__global__ void __launch_bounds__(kThreads) k_pull_margin(const PsbPullParams p) {
+  __shared__ u32 s_off[PSB_MAX_SHARDS + 1];
+  const int S = p.S;
+  const u32 U = *p.n_unique;
+  if (threadIdx.x <= S) s_off[threadIdx.x] = p.own_off[threadIdx.x];
+  if (threadIdx.x == 0 && p.need_applied > 0) {
+    for (int s = 0; s < S; ++s)
+      if (!wait_flag_ge_sys(p.applied[s], p.need_applied, kPeerWaitIters))
+        set_status(p.status, kWaitTimeout);
+  }
+  __syncthreads();
+  const u32 gsize = gridDim.x * blockDim.x;
+  const u32 gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  // phase 1: gather one weight per unique key from its owner's table
+  for (u32 u = gtid; u < U; u += gsize) {
+    int s = owner_of(s_off, S, u);
+    u64 key = p.ukeys[u];
+    float w;
+    long long slot;
+    if (p.insert) {
+      slot = table_find<true>((Entry*)p.table[s], p.mask[s], key, kMaxProbe);
+      w = 0.f;
+      if (slot >= 0) {
+        asm volatile("ld.relaxed.sys.global.f32 %0, [%1];"
+                     : "=f"(w) : "l"(&((Entry*)p.table[s])[slot].w) : "memory");
+      } else {
+        set_status(p.status, kTableFull);
+      }
+    } else {
+      slot = table_lookup_w((const Entry*)p.table[s], p.mask[s], key, kMaxProbe, &w);
+    }
+    p.w_local[u] = w;
+    if (p.slot_local) p.slot_local[u] = (int32_t)slot;
+    if (p.grad_zero) p.grad_zero[u] = 0.f;
+  }
+  if (p.n_rows == 0) return;
+  if (!grid_barrier(p.bar, p.status)) return;
+  // phase 2: one warp per row
+  const int lane = threadIdx.x & 31;
+  const u32 gwarp = gtid >> 5, nwarps = gsize >> 5;
+  double loss_sum = 0, n_correct = 0, n_seen = 0;
+  for (u32 r = gwarp; r < p.n_rows; r += nwarps) {
+    u32 b, e;
+    if (p.row_ptr) { b = p.row_ptr[r]; e = p.row_ptr[r + 1]; }
+    else { b = r * p.fixed_z; e = b + p.fixed_z; }
+    float acc = 0.f;
+    for (u32 j = b + lane; j < e; j += 32) {
+      float w = __ldcg(&p.w_local[p.csr_col[j]]);
+      acc += p.csr_val ? w * p.csr_val[j] : w;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      float y = p.y[r];
+      float ym = y * acc;
+      float g, l;
+      if (p.loss == PSB_LOSS_LOGIT) {
+        // tau = 1/(1+exp(y m)); loss = log(1+exp(-y m)), both evaluated stably
+        float en = expf(-fabsf(ym));
+        float tau = ym > 0 ? en / (1.f + en) : 1.f / (1.f + en);
+        g = -y * tau;
+        l = log1pf(en) + fmaxf(-ym, 0.f);
+      } else {
+        float h = fmaxf(1.f - ym, 0.f);
+        g = -2.f * y * h;
+        l = h * h;
+      }
+      p.gcoef[r] = g;
+      if (p.margin) p.margin[r] = acc;
+      loss_sum += l;
+      n_correct += (ym > 0.f) ? 1.0 : 0.0;
+      n_seen += 1.0;
+      if (p.auc_hist) {
+        float pr = 1.f / (1.f + expf(-acc));
+        int bin = min(4095, max(0, (int)(pr * 4096.f)));
+        atomicAdd(&p.auc_hist[(y > 0 ? 4096 : 0) + bin], 1u);
+      }
+    }
+  }
+  block_add4(loss_sum, n_correct, n_seen, 0.0, p.stats);
+}
+
+// ------------------------------------------------------------------ F1a: worker push
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Value region of one inbox, by quantisation mode (cap = records per inbox):
+//   NONE : float v[cap]
+//   INT8 : float scale[ceil(cap/32)] followed by int8 code[cap]
+//   FP16 : float scale[ceil(cap/32)] followed by half  code[cap]
+__device__ __forceinline__ u32 scale_words(u32 cap) { return (cap + 31) / 32; }
+
+__global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
+  __shared__ u32 s_off[PSB_MAX_SHARDS + 1];
+  __shared__ u32 s_gp[PSB_MAX_SHARDS + 1];  // group prefix per owner
+  __shared__ u32 s_last;
+  const int S = p.S;
+  if (threadIdx.x <= S) s_off[threadIdx.x] = p.own_off[threadIdx.x];
+  if (threadIdx.x == 0 && p.need_applied > 0) {
+    for (int s = 0; s < S; ++s)
+      if (!wait_flag_ge_sys(p.applied[s], p.need_applied, kPeerWaitIters))
+        set_status(p.status, kWaitTimeout);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    u32 acc = 0;
+    for (int s = 0; s < S; ++s) {
+      s_gp[s] = acc;
+      u32 c = s_off[s + 1] - s_off[s];
+      if (c > p.inbox_cap) { set_status(p.status, kInboxOverflow); c = p.inbox_cap; }
+      acc += (c + 31) / 32;
+    }
+    s_gp[S] = acc;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const u32 gsize = gridDim.x * blockDim.x;
+  const u32 gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const u32 gwarp = gtid >> 5, nwarps = gsize >> 5;
+  const u32 le = 0xffffffffu >> (31 - lane);
+
+  if (p.nnz > 0) {
+    // phase 1: segmented reduction of gcoef[row]*x over the key-sorted nonzeros
+    const u32 nwords = (p.nnz + 31) / 32;
+    for (u32 wi = gwarp; wi < nwords; wi += nwarps) {
+      u32 i = wi * 32 + lane;
+      u32 f = p.flagbits[wi];
+      u32 base = p.wordbase[wi];
+      float x = 0.f;
+      if (i < p.nnz) {
+        x = __ldg(&p.gcoef[p.csc_row[i]]);
+        if (p.csc_val) x *= p.csc_val[i];
+      }
+      u32 fle = f & le;
+      int start = fle ? 31 - __clz(fle) : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        float yv = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= start + o) x += yv;
+      }
+      bool tail = (lane == 31) || ((f >> (lane + 1)) & 1u) || (i == p.nnz - 1);
+      if (i < p.nnz && tail) atomicAdd(&p.grad[base + __popc(fle) - 1], x);
+    }
+    if (!grid_barrier(p.bar, p.status)) return;
+  }
+
+  // phase 2: range partition + (quantise) + peer stores, 32 records per warp step
+  const u32 G = s_gp[S];
+  for (u32 g = gwarp; g < G; g += nwarps) {
+    int s = 0;
+    while (s + 1 < S && g >= s_gp[s + 1]) ++s;
+    u32 cnt = min(s_off[s + 1] - s_off[s], p.inbox_cap);
+    u32 j0 = (g - s_gp[s]) * 32, j = j0 + lane;
+    bool valid = j < cnt;
+    u32 u = s_off[s] + j;
+    float v = valid ? __ldcg(&p.grad[u]) : 0.f;
+    if (p.send_keys && valid) p.inbox_keys[s][j] = p.ukeys[u];
+    if (p.quant == PSB_QUANT_NONE) {
+      if (valid) ((float*)p.inbox_vals[s])[j] = v;
+    } else {
+      float amax = warp_max(fabsf(v));
+      float* scales = (float*)p.inbox_vals[s];
+      if (p.quant == PSB_QUANT_INT8) {
+        float scale = amax / 127.f;
+        int code = amax > 0.f ? __float2int_rn(v / scale) : 0;
+        signed char* codes = (signed char*)(scales + scale_words(p.inbox_cap));
+        if (valid) codes[j] = (signed char)max(-127, min(127, code));
+        if (lane == 0) scales[j0 >> 5] = scale;
+      } else {
+        float scale = amax > 0.f ? amax : 1.f;
+        __half* codes = (__half*)(scales + scale_words(p.inbox_cap));
+        if (valid) codes[j] = __float2half_rn(v / scale);
+        if (lane == 0) scales[j0 >> 5] = scale;
+      }
+    }
+  }
+  // signal: all of this CTA's peer stores are ordered before its arrival, the
+  // last CTA to arrive publishes counts and the release flags
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    u32 arrived = atomicAdd(p.done, 1u) + 1;
+    s_last = (arrived == gridDim.x);
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x < S) {
+    int s = threadIdx.x;
+    __threadfence_system();
+    *p.count[s] = min(s_off[s + 1] - s_off[s], p.inbox_cap);
+    __threadfence_system();
+    st_release_sys(p.ready[s], p.ts1);
+    if (s == 0) atomicExch(p.done, 0u);
+  }
+}
+
+// ------------------------------------------------------------------ F1b: server apply
+__device__ __forceinline__ float inbox_value(const void* vals, int quant, u32 cap, u32 j) {
+  if (quant == PSB_QUANT_NONE) return ((const float*)vals)[j];
+  const float* scales = (const float*)vals;
+  float scale = scales[j >> 5];
+  if (quant == PSB_QUANT_INT8)
+    return scale * (float)((const signed char*)(scales + scale_words(cap)))[j];
+  return scale * __half2float(((const __half*)(scales + scale_words(cap)))[j]);
+}
+
+__global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
+  __shared__ u32 s_pre[PSB_MAX_SHARDS + 1];
+  __shared__ u32 s_last;
+  const int S = p.S;
+  Entry* tab = (Entry*)p.table;
+  if (threadIdx.x == 0) {
+    u32 acc = 0;
+    const u32 iters = p.wait_iters ? p.wait_iters : kPeerWaitIters;
+    for (int r = 0; r < S; ++r) {
+      s_pre[r] = acc;
+      if (!p.alive[r]) continue;
+      if (!wait_flag_ge_sys(p.ready[r], p.ts1, iters)) {
+        set_status(p.status, kWaitTimeout);
+        continue;
+      }
+      u32 c = *((volatile const u32*)p.count[r]);
+      acc += min(c, p.inbox_cap);
+    }
+    s_pre[S] = acc;
+  }
+  __syncthreads();
+  const u32 total = s_pre[S];
+  const u32 gsize = gridDim.x * blockDim.x;
+  const u32 gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  int n_src = 0;
+  for (int r = 0; r < S; ++r) n_src += p.alive[r] ? 1 : 0;
+  const bool single = n_src <= 1;
+  StatAcc st;
+
+  // phase A: locate the slot of every record; single source -> update in place,
+  // several sources -> accumulate into gacc and elect one leader per key
+  for (u32 i = gtid; i < total; i += gsize) {
+    int r = 0;
+    while (r + 1 < S && i >= s_pre[r + 1]) ++r;
+    u32 j = i - s_pre[r];
+    float g = inbox_value(p.inbox_vals[r], p.quant, p.inbox_cap, j);
+    long long slot;
+    if (p.cached[r]) {
+      slot = p.slot_cache[r][j] & 0x7fffffffu;
+    } else {
+      slot = table_find<true>(tab, p.mask, p.inbox_keys[r][j], kMaxProbe);
+      if (slot < 0) { set_status(p.status, kTableFull); if (p.slot_cache[r]) p.slot_cache[r][j] = 0x7fffffffu; continue; }
+    }
+    if (single) {
+      Entry* e = &tab[slot];
+      float w = e->w, s0 = e->s0, s1 = e->s1, w_old = w;
+      opt_step(p.opt, g, w, s0, s1);
+      e->w = w; e->s0 = s0; e->s1 = s1;
+      st.add(w, w_old);
+      if (p.slot_cache[r]) p.slot_cache[r][j] = (u32)slot;
+    } else {
+      u32 old = atomicExch(&tab[slot].epoch, p.ts1);
+      atomicAdd(&tab[slot].gacc, g);
+      p.slot_cache[r][j] = (u32)slot | (old != p.ts1 ? 0x80000000u : 0u);
+    }
+  }
+  if (!single) {
+    if (!grid_barrier(p.bar, p.status)) return;
+    // phase B: the leader of each touched key runs the optimiser on the summed gradient
+    for (u32 i = gtid; i < total; i += gsize) {
+      int r = 0;
+      while (r + 1 < S && i >= s_pre[r + 1]) ++r;
+      u32 sc = __ldcg(&p.slot_cache[r][i - s_pre[r]]);
+      if (!(sc & 0x80000000u) ) continue;
+      u32 slot = sc & 0x7fffffffu;
+      if (slot == 0x7fffffffu) continue;
+      Entry* e = &tab[slot];
+      float g = __ldcg(&e->gacc);
+      float w = __ldcg(&e->w), s0 = __ldcg(&e->s0), s1 = __ldcg(&e->s1), w_old = w;
+      opt_step(p.opt, g, w, s0, s1);
+      e->w = w; e->s0 = s0; e->s1 = s1; e->gacc = 0.f;
+      st.add(w, w_old);
+    }
+  }
+  block_add4(st.d_nnz, st.w2, st.dw2, st.n, p.stats);
+  // publish "applied" once every CTA is done
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    u32 arrived = atomicAdd(p.done, 1u) + 1;
+    s_last = (arrived == gridDim.x);
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x == 0) {
+    __threadfence_system();
+    st_release_sys(p.applied, p.ts1);
+    atomicExch(p.done, 0u);
+  }
+}
+
+static int coop_grid_for(const void* fn) {
+  int dev = 0, sms = 0, per = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per, fn, kThreads, 0);
+  if (per < 1) per = 1;
+  if (per > 4) per = 4;
+  return sms * per;
+}
+
+}  // namespace psb
+
+using namespace psb;
+
+extern "C" int psb_device_sm_count(void) {
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+
+extern "C" int psb_coop_grid(int which) {
+  static int g[3] = {0, 0, 0};
+  if (which < 0 || which > 2) return 0;
+  if (!g[which]) {
+    const void* fn = which == 0 ? (const void*)k_pull_margin
+                   : which == 1 ? (const void*)k_push : (const void*)k_apply;
+    g[which] = coop_grid_for(fn);
+  }
+  return g[which];
+}
+
+extern "C" int psb_table_init(void* table, psb_u64 capacity, cudaStream_t stream) {
+  k_table_init<<<148 * 8, 256, 0, stream>>>((Entry*)table, capacity);
+  return -(int)cudaGetLastError();
+}
+
+extern "C" int psb_table_dump(const void* table, psb_u64 capacity, psb_u64* out_keys,
+                              float* out_w, psb_u64 out_cap, unsigned long long* out_n,
+                              cudaStream_t stream) {
+  cudaMemsetAsync(out_n, 0, sizeof(unsigned long long), stream);
+  k_table_dump<false><<<148 * 8, 256, 0, stream>>>((const Entry*)table, capacity, (u64*)out_keys,
+                                                   nullptr, nullptr, out_w, out_cap, out_n);
+  return -(int)cudaGetLastError();
+}
+
+extern "C" int psb_table_export(const void* table, psb_u64 capacity, psb_u64* out_keys,
+                                float* out_s0, float* out_s1, float* out_w, psb_u64 out_cap,
+                                unsigned long long* out_n, cudaStream_t stream) {
+  cudaMemsetAsync(out_n, 0, sizeof(unsigned long long), stream);
+  k_table_dump<true><<<148 * 8, 256, 0, stream>>>((const Entry*)table, capacity, (u64*)out_keys,
+                                                  out_s0, out_s1, out_w, out_cap, out_n);
+  return -(int)cudaGetLastError();
+}
+
+extern "C" int psb_table_load(void* table, psb_u64 mask, const psb_u64* keys, const float* s0,
+                              const float* s1, const float* w, psb_u64 n, uint32_t* status,
+                              cudaStream_t stream) {
+  if (n == 0) return 0;
+  k_table_load<<<148 * 4, 256, 0, stream>>>((Entry*)table, mask, (const u64*)keys, s0, s1, w, n,
+                                            status);
+  return -(int)cudaGetLastError();
+}
+
+template <typename P>
+static int launch_coop(const void* fn, int which, const P* p, cudaStream_t stream) {
+  P local = *p;
+  void* args[] = {&local};
+  cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(psb_coop_grid(which)), dim3(kThreads), args,
+                                              0, stream);
+  return -(int)e;
+}
+
+extern "C" int psb_pull_margin(const PsbPullParams* p, cudaStream_t stream) {
+  if (p->S < 1 || p->S > PSB_MAX_SHARDS) return -(int)cudaErrorInvalidValue;
+  return launch_coop((const void*)k_pull_margin, 0, p, stream);
+}
+extern "C" int psb_push(const PsbPushParams* p, cudaStream_t stream) {
+  if (p->S < 1 || p->S > PSB_MAX_SHARDS) return -(int)cudaErrorInvalidValue;
+  return launch_coop((const void*)k_push, 1, p, stream);
+}
+extern "C" int psb_apply(const PsbApplyParams* p, cudaStream_t stream) {
+  if (p->S < 1 || p->S > PSB_MAX_SHARDS) return -(int)cudaErrorInvalidValue;
+  return launch_coop((const void*)k_apply, 2, p, stream);
+}
+
+// sizeof of the parameter blocks, so that a binding can verify its mirror structs
+extern "C" int psb_struct_size(int which) {
+  switch (which) {
+    case 0: return (int)sizeof(PsbPullParams);
+    case 1: return (int)sizeof(PsbPushParams);
+    case 2: return (int)sizeof(PsbApplyParams);
+    case 3: return (int)sizeof(PsbOptimizer);
+    default: return -1;
+  }
+}

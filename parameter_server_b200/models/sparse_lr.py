@@ -1,0 +1,156 @@
+"""Flagship model: sparse logistic regression trained through the device
+parameter server (async SGD family: FTRL-proximal / AdaGrad / SGD).
+
+One :class:`SparseLRWorker` per rank drives the per-minibatch pipeline
+
+    H2D copy -> sort/unique/remap (K1) -> pull + margins + loss (F2)
+             -> X^T g + scatter to owners (F1a) -> owner apply (F1b)
+
+which is the worker/server loop of the reference's ``AsyncSGDWorker`` and
+``AsyncSGDServer`` (``app/linear_method/async_sgd.h:42-310``) with the socket
+round trips replaced by peer loads/stores. Minibatch ``t`` may start its pull
+once every shard has applied round ``t - tau - 1`` (bounded delay).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from ..ops import _lib
+from ..ops.localize import LocalBatch
+from ..parallel.dataplane import DataPlane, OptimizerConfig, PlaneConfig
+from ..parallel.fabric import Fabric
+
+
+@dataclass
+class SparseLRConfig:
+    max_rows: int
+    max_nnz: int
+    tau: int = 0                       # bounded delay (minibatches)
+    hash_seed: Optional[int] = 0       # hash raw ids to uint64 keys on the device; None: ids are keys
+    key_bits: int = 64
+    loss: str = "logit"
+    real_values: bool = False
+    pipeline: int = 2                  # minibatches in flight on the worker (>=1)
+    auc: bool = False
+
+
+class SparseLRWorker:
+    def __init__(self, plane: DataPlane, cfg: SparseLRConfig):
+        self.plane, self.cfg = plane, cfg
+        dev = plane.device
+        assert plane.cfg.ring >= cfg.tau + 2 or plane.S == 1 and plane.cfg.ring >= 1
+        self.bufs: List[LocalBatch] = [
+            LocalBatch(cfg.max_rows, cfg.max_nnz, plane.S, dev, real_values=cfg.real_values)
+            for _ in range(max(1, cfg.pipeline))]
+        self.step_no = 0
+        self.loss_code = _lib.LOSS_LOGIT if cfg.loss == "logit" else _lib.LOSS_SQUARE_HINGE
+        self.auc_hist = torch.zeros(2 * 4096, dtype=torch.int32, device=dev) if cfg.auc else None
+        # streams: prep (copy + localise), main (pull/push), server (apply)
+        self.prep_stream = torch.cuda.Stream(device=dev)
+        self.main_stream = torch.cuda.Stream(device=dev)
+        self.server_stream = torch.cuda.Stream(device=dev)
+        self._prep_done = [torch.cuda.Event() for _ in self.bufs]
+        self._buf_free = [torch.cuda.Event() for _ in self.bufs]
+        self._push_done = torch.cuda.Event()
+        self._staged = [None] * len(self.bufs)
+
+    # ------------------------------------------------------------ pieces
+    def prepare(self, ids: torch.Tensor, y: torch.Tensor, *, fixed_z: int = 0, row_ptr=None, vals=None,
+                slot: Optional[int] = None, stream=None) -> LocalBatch:
+        """Localise a minibatch whose tensors already live on the device."""
+        slot = self.step_no % len(self.bufs) if slot is None else slot
+        b = self.bufs[slot]
+        b.localize(ids, y, self.plane.bounds, fixed_z=fixed_z, row_ptr=row_ptr, vals=vals,
+                   hash_seed=self.cfg.hash_seed, key_bits=self.cfg.key_bits, stream=stream)
+        return b
+
+    def train_prepared(self, b: LocalBatch, stream=None, server_stream=None):
+        """Pull + margins, push, apply for a localised batch (round = step number)."""
+        t = self.step_no
+        need = max(0, t - self.cfg.tau)
+        self.plane.pull_margin(b, need_applied=need, loss=self.loss_code, auc_hist=self.auc_hist, stream=stream)
+        self.plane.push(b, t, stream=stream)
+        self.plane.apply(t, stream=server_stream if server_stream is not None else stream)
+        self.step_no += 1
+
+    # ------------------------------------------------------------ simple synchronous step
+    def step(self, ids: torch.Tensor, y: torch.Tensor, *, fixed_z: int = 0, row_ptr=None, vals=None):
+        """One minibatch on the current stream (device tensors)."""
+        b = self.prepare(ids, y, fixed_z=fixed_z, row_ptr=row_ptr, vals=vals)
+        self.train_prepared(b)
+        return b
+
+    # ------------------------------------------------------------ pipelined public API
+    def submit(self, ids: torch.Tensor, y: torch.Tensor, *, fixed_z: int = 0, row_ptr=None, vals=None):
+        """Enqueue one minibatch. ``ids``/``y`` (and ``vals``/``row_ptr``) may be
+        pinned host tensors -- they are copied on the prep stream -- or device
+        tensors. Localisation runs on the prep stream and overlaps the previous
+        minibatch's pull/push/apply on the main and server streams."""
+        k = self.step_no % len(self.bufs)
+        b = self.bufs[k]
+        dev = self.plane.device
+        cur = torch.cuda.current_stream(dev)
+        self.prep_stream.wait_stream(cur)
+        self.prep_stream.wait_event(self._buf_free[k])
+        with torch.cuda.stream(self.prep_stream):
+            def to_dev(t, name):
+                if t is None or t.is_cuda:
+                    return t
+                st = self._staged[k] = self._staged[k] or {}
+                d = st.get(name)
+                if d is None or d.numel() < t.numel() or d.dtype != t.dtype:
+                    d = st[name] = torch.empty(t.numel(), dtype=t.dtype, device=dev)
+                v = d[:t.numel()]
+                v.copy_(t, non_blocking=True)
+                return v
+            ids_d, y_d = to_dev(ids, "ids"), to_dev(y, "y")
+            vals_d, rp_d = to_dev(vals, "vals"), to_dev(row_ptr, "row_ptr")
+            b.localize(ids_d, y_d, self.plane.bounds, fixed_z=fixed_z, row_ptr=rp_d, vals=vals_d,
+                       hash_seed=self.cfg.hash_seed, key_bits=self.cfg.key_bits, stream=self.prep_stream)
+            self._prep_done[k].record(self.prep_stream)
+        self.main_stream.wait_event(self._prep_done[k])
+        t = self.step_no
+        need = max(0, t - self.cfg.tau)
+        self.plane.pull_margin(b, need_applied=need, loss=self.loss_code, auc_hist=self.auc_hist,
+                               stream=self.main_stream)
+        self.plane.push(b, t, stream=self.main_stream)
+        self._buf_free[k].record(self.main_stream)
+        self._push_done.record(self.main_stream)
+        self.server_stream.wait_event(self._push_done)
+        self.plane.apply(t, stream=self.server_stream)
+        self.step_no += 1
+        return b
+
+    def wait(self):
+        """Make the current stream wait for everything submitted so far."""
+        cur = torch.cuda.current_stream(self.plane.device)
+        cur.wait_stream(self.main_stream)
+        cur.wait_stream(self.server_stream)
+        cur.wait_stream(self.prep_stream)
+
+    def read_progress(self, reset: bool = True):
+        """Device -> host read of the progress counters: dict with the summed
+        loss, accuracy count and examples seen since the last reset (worker side)
+        and nnz delta / sum w^2 / sum dw^2 / updates (server side)."""
+        self.wait()
+        p = self.plane
+        both = torch.cat([p.pull_stats, p.push_stats]).cpu()
+        if reset:
+            p.pull_stats.zero_()
+            p.push_stats.zero_()
+        loss, correct, rows, _, d_nnz, w2, dw2, n_upd = both.tolist()
+        return {"loss_sum": loss, "n_correct": correct, "n_examples": rows, "d_nnz": d_nnz,
+                "weight_sum": w2, "delta_sum": dw2, "n_updates": n_upd}
+
+
+def make_single_gpu(table_capacity: int, inbox_cap: int, opt: OptimizerConfig, cfg: SparseLRConfig,
+                    device=None, quant: str = "none") -> SparseLRWorker:
+    """Convenience: one GPU hosting one shard and one worker."""
+    ring = cfg.tau + 2
+    pc = PlaneConfig(table_capacity=table_capacity, inbox_cap=inbox_cap, ring=ring, quant=quant)
+    from ..parallel.dataplane import heap_layout
+    fab = Fabric.single(heap_layout(pc, 1).total(), device)
+    return SparseLRWorker(DataPlane(fab, pc, opt), cfg)

@@ -1,0 +1,134 @@
+"""Minibatch localisation on the GPU: radix sort + unique + remap (kernel K1/K2).
+
+:class:`LocalBatch` owns every per-minibatch device buffer of a worker, sized
+once for the largest minibatch, so a training step allocates nothing.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import check, ptr, stream_ptr
+
+
+def sort_pairs(keys: torch.Tensor, payload: Optional[torch.Tensor] = None, begin_bit: int = 0,
+               end_bit: int = 64, stream=None):
+    """Sort int64-viewed uint64 ``keys`` (and a uint32 payload, default = index).
+    Returns ``(sorted_keys, sorted_payload)`` as new tensors."""
+    n = keys.numel()
+    dev = keys.device
+    ka = keys.clone()
+    kb = torch.empty_like(ka)
+    va = payload.clone() if payload is not None else torch.empty(n, dtype=torch.int32, device=dev)
+    vb = torch.empty_like(va)
+    L = _lib.lib()
+    scratch = torch.empty(L.psb_sort_scratch_bytes(n, begin_bit, end_bit), dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    where = check(L.psb_sort_pairs(ptr(ka), 0, 0, ptr(ka), ptr(va), int(payload is not None), ptr(kb), ptr(vb),
+                                   n, begin_bit, end_bit, ptr(scratch), ptr(status), stream_ptr(stream)), "sort",
+                  kernels=1 + (end_bit - begin_bit + 7) // 8)
+    _lib.check_status(status, "radix sort")
+    return (kb, vb) if where == 1 else (ka, va)
+
+
+class LocalBatch:
+    """Device buffers of one in-flight minibatch of a worker."""
+
+    def __init__(self, max_rows: int, max_nnz: int, n_shards: int, device, real_values: bool = False):
+        dev = device
+        i32, i64, f32 = torch.int32, torch.int64, torch.float32
+        self.device, self.max_rows, self.max_nnz, self.S = dev, max_rows, max_nnz, n_shards
+        L = _lib.lib()
+        self.keys_a = torch.empty(max_nnz, dtype=i64, device=dev)
+        self.keys_b = torch.empty(max_nnz, dtype=i64, device=dev)
+        self.pos_a = torch.empty(max_nnz, dtype=i32, device=dev)
+        self.pos_b = torch.empty(max_nnz, dtype=i32, device=dev)
+        nb = max(L.psb_sort_scratch_bytes(max_nnz, 0, 64), L.psb_localize_scratch_bytes(max_nnz))
+        self.scratch = torch.empty(nb, dtype=torch.uint8, device=dev)
+        self.status = torch.zeros(1, dtype=i32, device=dev)
+        self.ukeys = torch.empty(max_nnz, dtype=i64, device=dev)
+        self.seg_off = torch.empty(max_nnz + 1, dtype=i32, device=dev)
+        self.csr_col = torch.empty(max_nnz, dtype=i32, device=dev)
+        self.flagbits = torch.empty((max_nnz + 31) // 32, dtype=i32, device=dev)
+        self.wordbase = torch.empty((max_nnz + 31) // 32, dtype=i32, device=dev)
+        self.n_unique = torch.zeros(1, dtype=i32, device=dev)
+        self.own_off = torch.zeros(n_shards + 1, dtype=i32, device=dev)
+        self.w_local = torch.empty(max_nnz, dtype=f32, device=dev)
+        self.grad = torch.zeros(max_nnz, dtype=f32, device=dev)
+        self.slot_local = None
+        self.gcoef = torch.empty(max_rows, dtype=f32, device=dev)
+        self.margin = torch.empty(max_rows, dtype=f32, device=dev)
+        self.csc_val_buf = torch.empty(max_nnz, dtype=f32, device=dev) if real_values else None
+        # set per batch
+        self.n_rows = 0
+        self.nnz = 0
+        self.fixed_z = 0
+        self.row_ptr = None
+        self.csr_val = None
+        self.csc_val = None
+        self.csc_row = None
+        self.y = None
+
+    def localize(self, ids: torch.Tensor, y: Optional[torch.Tensor], bounds: torch.Tensor, *,
+                 fixed_z: int = 0, row_ptr: Optional[torch.Tensor] = None,
+                 vals: Optional[torch.Tensor] = None, hash_seed: Optional[int] = None,
+                 key_bits: int = 64, stream=None):
+        """Sort + unique + remap one minibatch.
+
+        ``ids``: flat per-nonzero feature ids. ``int32`` (raw ids, hashed to uint64
+        keys on the device when ``hash_seed`` is given) or ``int64`` (already
+        uint64 keys viewed as int64, or raw ids to hash when ``hash_seed`` is given).
+        Rows are given by ``row_ptr`` (CSR offsets, int32) or a fixed ``fixed_z``
+        nonzeros per row.
+        """
+        L = _lib.lib()
+        n = ids.numel()
+        assert n <= self.max_nnz
+        self.nnz = n
+        if row_ptr is not None:
+            self.n_rows = row_ptr.numel() - 1
+            self.fixed_z = 0
+        else:
+            assert fixed_z > 0 and n % fixed_z == 0
+            self.n_rows = n // fixed_z
+            self.fixed_z = fixed_z
+        assert self.n_rows <= self.max_rows
+        self.row_ptr, self.csr_val, self.y = row_ptr, vals, y
+        sp = stream_ptr(stream)
+        if hash_seed is None:
+            assert ids.dtype == torch.int64
+            in_kind, seed = 0, 0
+        else:
+            in_kind, seed = (1 if ids.dtype == torch.int32 else 2), hash_seed
+        where = check(L.psb_sort_pairs(ptr(ids), in_kind, seed, ptr(self.keys_a), ptr(self.pos_a), 0,
+                                       ptr(self.keys_b), ptr(self.pos_b), n, 0, key_bits,
+                                       ptr(self.scratch), ptr(self.status), sp), "sort",
+                      kernels=1 + (key_bits + 7) // 8)
+        skeys, spos = (self.keys_b, self.pos_b) if where == 1 else (self.keys_a, self.pos_a)
+        self.csc_val = self.csc_val_buf if vals is not None else None
+        if vals is not None:
+            assert self.csc_val_buf is not None
+        check(L.psb_localize(ptr(skeys), ptr(spos), n, ptr(row_ptr), self.n_rows, self.fixed_z, ptr(vals),
+                             ptr(bounds), self.S, ptr(self.ukeys), ptr(self.seg_off), ptr(self.csr_col),
+                             ptr(self.csc_val), ptr(self.flagbits), ptr(self.wordbase), ptr(self.n_unique),
+                             ptr(self.own_off), ptr(self.scratch), sp), "localize", kernels=4)
+        self.csc_row = spos
+        self.sorted_keys = skeys
+        return self
+
+    def set_keys(self, ukeys_sorted: torch.Tensor, bounds_host):
+        """Use an already sorted unique key list (generic Push/Pull API path)."""
+        import numpy as np
+        n = ukeys_sorted.numel()
+        assert n <= self.max_nnz
+        self.ukeys[:n].copy_(ukeys_sorted)
+        self.n_unique.fill_(n)
+        ku = ukeys_sorted.cpu().numpy().view("uint64")
+        offs = [int(np.searchsorted(ku, np.uint64(b), side="left")) if b < (1 << 64) - 1 or True else n
+                for b in bounds_host[:-1]] + [n]
+        self.own_off.copy_(torch.tensor(offs, dtype=torch.int32))
+        self.n_rows = 0
+        self.nnz = 0
+        return self

@@ -1,0 +1,254 @@
+"""Device data plane: one server shard plus one worker endpoint per GPU.
+
+The heap of every rank holds, at identical offsets,
+
+* ``ctrl``   -- flag words: ``applied`` (timestamp+1 of the last applied push
+  round), and per (ring slot, source) a ``ready`` flag and a record ``count``;
+* ``table``  -- the shard's open-addressing table (32-byte entries: key, w,
+  optimiser state, per-round gradient accumulator, epoch tag);
+* ``inbox``  -- per (ring slot, source) a key array and a value array that the
+  source's push kernel fills with peer stores.
+
+A push of timestamp ``t`` uses ring slot ``t % ring``; a worker may reuse a slot
+once the owner has applied round ``t - ring``. A pull at step ``t`` with bounded
+delay ``tau`` waits until every owner has applied round ``t - tau - 1``. Both are
+waits on the owners' ``applied`` counters, i.e. the device form of the
+reference's per-sender timestamp trackers and ``wait_time`` dependencies
+(``system/remote_node.h:13-32``, ``system/executor.cc:169-230``).
+
+Push rounds are aggregated per timestamp at the owner: gradients of the same key
+from different workers are summed and the optimiser runs once on the sum (the
+buffered-aggregation semantics of ``parameter/kv_vector.h:182-207``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import torch
+
+from ..ops import _lib
+from ..ops._lib import (ApplyParams, Optimizer, PullParams, PushParams, check, ptr, stream_ptr)
+from ..utils.range import Range, shard_bounds
+from .fabric import Fabric, HeapLayout
+
+CTRL_WORDS = 1024
+
+
+@dataclass
+class OptimizerConfig:
+    algo: str = "ftrl"            # ftrl | adagrad | sgd | sum
+    alpha: float = 0.1
+    beta: float = 1.0
+    l1: float = 1.0
+    l2: float = 0.1
+    lr_type: str = "decay"        # decay: alpha/(x+beta) ; constant: alpha
+
+    def to_c(self) -> Optimizer:
+        algo = {"ftrl": _lib.ALGO_FTRL, "adagrad": _lib.ALGO_ADAGRAD, "sgd": _lib.ALGO_SGD,
+                "sum": _lib.ALGO_SUM}[self.algo]
+        lr = _lib.LR_CONSTANT if self.lr_type == "constant" else _lib.LR_DECAY
+        return Optimizer(algo, lr, self.alpha, self.beta, self.l1, self.l2)
+
+
+@dataclass
+class PlaneConfig:
+    table_capacity: int                     # slots per shard, power of two
+    inbox_cap: int                          # records per (owner, source) inbox
+    ring: int = 2                           # inbox ring slots (bounded delay tau => tau+2)
+    key_range: Range = field(default_factory=Range.all)
+    quant: str = "none"                     # none | int8 | fp16 (fixed-point filter on pushes)
+
+    def quant_code(self) -> int:
+        return {"none": _lib.QUANT_NONE, "int8": _lib.QUANT_INT8, "fp16": _lib.QUANT_FP16}[self.quant]
+
+
+def heap_layout(cfg: PlaneConfig, world: int) -> HeapLayout:
+    assert cfg.table_capacity & (cfg.table_capacity - 1) == 0, "table capacity must be a power of two"
+    assert cfg.table_capacity < (1 << 31)
+    assert 8 + 2 * cfg.ring * world <= CTRL_WORDS
+    lay = HeapLayout()
+    lay.add("ctrl", CTRL_WORDS * 4)
+    lay.add("table", cfg.table_capacity * 32)
+    lay.add("inbox_keys", cfg.ring * world * cfg.inbox_cap * 8)
+    lay.add("inbox_vals", cfg.ring * world * cfg.inbox_cap * 4 + 256)
+    return lay
+
+
+class DataPlane:
+    """Server shard + worker endpoint of one rank."""
+
+    def __init__(self, fabric: Fabric, cfg: PlaneConfig, opt: OptimizerConfig):
+        self.fabric, self.cfg, self.opt = fabric, cfg, opt
+        self.rank, self.S = fabric.rank, fabric.world
+        assert self.S <= _lib.MAX_SHARDS
+        self.layout = heap_layout(cfg, self.S)
+        assert self.layout.total() <= fabric.heap_bytes, "heap too small for this configuration"
+        dev = fabric.device
+        self.device = dev
+        self.bounds_host = shard_bounds(cfg.key_range, self.S)
+        self.bounds = torch.tensor([b if b < (1 << 63) else b - (1 << 64) for b in self.bounds_host],
+                                   dtype=torch.int64, device=dev)
+        # local scratch (zero-initialised); one word group per kernel kind
+        self.sync_words = torch.zeros(64, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.slot_cache = torch.zeros((self.S, cfg.inbox_cap), dtype=torch.int32, device=dev)
+        self.push_stats = torch.zeros(4, dtype=torch.float64, device=dev)   # d_nnz, w2, dw2, n
+        self.pull_stats = torch.zeros(4, dtype=torch.float64, device=dev)   # loss, correct, rows
+        self.alive = [True] * self.S
+        self.applied_ts1 = 0
+        self.ctrl = fabric.view(self.layout["ctrl"], (CTRL_WORDS,), torch.int32)
+        check(_lib.lib().psb_table_init(fabric.ptr(self.rank, self.layout["table"]),
+                                        cfg.table_capacity, stream_ptr()), "table init")
+
+    # ---------------------------------------------------------------- addresses
+    def _ctrl(self, rank: int, word: int) -> int:
+        return self.fabric.ptr(rank, self.layout["ctrl"] + 4 * word)
+
+    def _ready(self, owner: int, q: int, src: int) -> int:
+        return self._ctrl(owner, 8 + q * self.S + src)
+
+    def _count(self, owner: int, q: int, src: int) -> int:
+        return self._ctrl(owner, 8 + self.cfg.ring * self.S + q * self.S + src)
+
+    def _inbox_keys(self, owner: int, q: int, src: int) -> int:
+        return self.fabric.ptr(owner, self.layout["inbox_keys"] + ((q * self.S + src) * self.cfg.inbox_cap) * 8)
+
+    def _inbox_vals(self, owner: int, q: int, src: int) -> int:
+        return self.fabric.ptr(owner, self.layout["inbox_vals"] + ((q * self.S + src) * self.cfg.inbox_cap) * 4)
+
+    def _bar(self, kind: int) -> int:
+        return self.sync_words.data_ptr() + 16 * kind
+
+    def _done(self, kind: int) -> int:
+        return self.sync_words.data_ptr() + 16 * kind + 8
+
+    def table_ptr(self, rank: Optional[int] = None) -> int:
+        return self.fabric.ptr(self.rank if rank is None else rank, self.layout["table"])
+
+    # ---------------------------------------------------------------- worker: pull (+ margins)
+    def pull_margin(self, b, *, need_applied: int = 0, with_margins: bool = True, loss: int = 0,
+                    insert: bool = False, auc_hist: Optional[torch.Tensor] = None, stream=None):
+        """F2 on a localised batch ``b`` (see :class:`~parameter_server_b200.ops.localize.LocalBatch`)."""
+        p = PullParams()
+        p.S, p.insert = self.S, int(insert)
+        for s in range(self.S):
+            p.table[s] = self.table_ptr(s)
+            p.mask[s] = self.cfg.table_capacity - 1
+            p.applied[s] = self._ctrl(s, 0)
+        p.need_applied = need_applied
+        p.ukeys, p.n_unique, p.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
+        p.w_local, p.slot_local, p.grad_zero = ptr(b.w_local), ptr(b.slot_local), ptr(b.grad)
+        if with_margins:
+            p.row_ptr, p.n_rows, p.fixed_z = ptr(b.row_ptr), b.n_rows, b.fixed_z
+            p.csr_col, p.csr_val, p.y = ptr(b.csr_col), ptr(b.csr_val), ptr(b.y)
+            p.gcoef, p.margin = ptr(b.gcoef), ptr(b.margin)
+        else:
+            p.n_rows = 0
+        p.loss = loss
+        p.stats, p.auc_hist = ptr(self.pull_stats), ptr(auc_hist)
+        p.bar, p.status = self._bar(0), ptr(self.status)
+        check(_lib.lib().psb_pull_margin(C.byref(p), stream_ptr(stream)), "pull_margin")
+
+    # ---------------------------------------------------------------- worker: push
+    def push(self, b, ts: int, *, with_gradient: bool = True, send_keys: bool = True, stream=None):
+        """F1a: push round ``ts`` of batch ``b``. With ``with_gradient`` the values
+        are X^T gcoef computed in the kernel; otherwise ``b.grad`` is sent as is."""
+        cfg = self.cfg
+        q = ts % cfg.ring
+        p = PushParams()
+        p.S, p.ts1, p.inbox_cap = self.S, ts + 1, cfg.inbox_cap
+        p.quant, p.send_keys = cfg.quant_code(), int(send_keys)
+        for s in range(self.S):
+            p.inbox_keys[s] = self._inbox_keys(s, q, self.rank)
+            p.inbox_vals[s] = self._inbox_vals(s, q, self.rank)
+            p.ready[s] = self._ready(s, q, self.rank)
+            p.count[s] = self._count(s, q, self.rank)
+            p.applied[s] = self._ctrl(s, 0)
+        p.need_applied = max(0, ts + 1 - cfg.ring)
+        p.ukeys, p.n_unique, p.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
+        if with_gradient:
+            p.nnz = b.nnz
+            p.csc_row, p.csc_val = ptr(b.csc_row), ptr(b.csc_val)
+            p.flagbits, p.wordbase, p.gcoef = ptr(b.flagbits), ptr(b.wordbase), ptr(b.gcoef)
+        else:
+            p.nnz = 0
+        p.grad = ptr(b.grad)
+        p.bar, p.done, p.status = self._bar(1), self._done(1), ptr(self.status)
+        check(_lib.lib().psb_push(C.byref(p), stream_ptr(stream)), "push")
+
+    # ---------------------------------------------------------------- server: apply
+    def apply(self, ts: int, *, cached=None, wait_iters: int = 0, stream=None):
+        """F1b: apply push round ``ts`` from every alive source."""
+        cfg = self.cfg
+        q = ts % cfg.ring
+        p = ApplyParams()
+        p.S, p.ts1, p.inbox_cap, p.quant = self.S, ts + 1, cfg.inbox_cap, cfg.quant_code()
+        p.table, p.mask = self.table_ptr(), cfg.table_capacity - 1
+        for r in range(self.S):
+            p.inbox_keys[r] = self._inbox_keys(self.rank, q, r)
+            p.inbox_vals[r] = self._inbox_vals(self.rank, q, r)
+            p.ready[r] = self._ready(self.rank, q, r)
+            p.count[r] = self._count(self.rank, q, r)
+            p.alive[r] = 1 if self.alive[r] else 0
+            p.cached[r] = 1 if (cached is not None and cached[r]) else 0
+            p.slot_cache[r] = self.slot_cache.data_ptr() + r * cfg.inbox_cap * 4
+        p.opt = self.opt.to_c()
+        p.stats, p.applied = ptr(self.push_stats), self._ctrl(self.rank, 0)
+        p.wait_iters = wait_iters
+        p.bar, p.done, p.status = self._bar(2), self._done(2), ptr(self.status)
+        check(_lib.lib().psb_apply(C.byref(p), stream_ptr(stream)), "apply")
+        self.applied_ts1 = ts + 1
+
+    # ---------------------------------------------------------------- membership
+    def set_alive(self, rank: int, alive: bool):
+        """Host-side membership: a dead source is skipped by ``apply`` (its wait
+        completes immediately), as with ``alive=false`` in the reference's
+        ``Executor::RemoveNode`` (``system/executor.cc:303-313``)."""
+        self.alive[rank] = alive
+
+    def check_status(self, what: str = "data plane"):
+        _lib.check_status(self.status, what)
+
+    # ---------------------------------------------------------------- model io
+    def dump_nonzero(self):
+        """(keys, w) of every entry with a non-zero weight, as CPU tensors sorted by key."""
+        cap = self.cfg.table_capacity
+        n = torch.zeros(1, dtype=torch.int64, device=self.device)
+        # two passes: count, then fill
+        L = _lib.lib()
+        k0 = torch.empty(1, dtype=torch.int64, device=self.device)
+        w0 = torch.empty(1, dtype=torch.float32, device=self.device)
+        check(L.psb_table_dump(self.table_ptr(), cap, ptr(k0), ptr(w0), 0, ptr(n), stream_ptr()), "dump")
+        cnt = int(n.item())
+        keys = torch.empty(max(cnt, 1), dtype=torch.int64, device=self.device)
+        w = torch.empty(max(cnt, 1), dtype=torch.float32, device=self.device)
+        check(L.psb_table_dump(self.table_ptr(), cap, ptr(keys), ptr(w), cnt, ptr(n), stream_ptr()), "dump")
+        keys, w = keys[:cnt].cpu(), w[:cnt].cpu()
+        ukeys = keys.numpy().view("uint64")
+        order = ukeys.argsort(kind="stable")
+        return torch.from_numpy(ukeys[order].copy()), w[torch.from_numpy(order)]
+
+    def export_state(self):
+        """Every occupied slot: (keys uint64 numpy, s0, s1, w) for checkpoints."""
+        cap = self.cfg.table_capacity
+        L = _lib.lib()
+        n = torch.zeros(1, dtype=torch.int64, device=self.device)
+        d = torch.empty(1, dtype=torch.float32, device=self.device)
+        k0 = torch.empty(1, dtype=torch.int64, device=self.device)
+        check(L.psb_table_export(self.table_ptr(), cap, ptr(k0), ptr(d), ptr(d), ptr(d), 0, ptr(n), stream_ptr()), "export")
+        cnt = int(n.item())
+        keys = torch.empty(max(cnt, 1), dtype=torch.int64, device=self.device)
+        s0, s1, w = (torch.empty(max(cnt, 1), dtype=torch.float32, device=self.device) for _ in range(3))
+        check(L.psb_table_export(self.table_ptr(), cap, ptr(keys), ptr(s0), ptr(s1), ptr(w), cnt, ptr(n), stream_ptr()), "export")
+        return keys[:cnt].cpu().numpy().view("uint64"), s0[:cnt].cpu(), s1[:cnt].cpu(), w[:cnt].cpu()
+
+    def load_state(self, keys_u64, s0=None, s1=None, w=None):
+        import numpy as np
+        k = torch.from_numpy(np.ascontiguousarray(keys_u64).view("int64")).to(self.device)
+        f = lambda t: None if t is None else t.to(self.device, torch.float32).contiguous()
+        s0, s1, w = f(s0), f(s1), f(w)
+        check(_lib.lib().psb_table_load(self.table_ptr(), self.cfg.table_capacity - 1, ptr(k), ptr(s0), ptr(s1),
+                                        ptr(w), k.numel(), ptr(self.status), stream_ptr()), "load")
+        torch.cuda.current_stream().synchronize()

@@ -1,0 +1,152 @@
+"""CPU oracle: plain NumPy fp32 restatements of the math every kernel is checked
+against. Same formulas as the reference: FTRL / AdaGrad entries
+(``app/linear_method/async_sgd.h:132-176``), elastic-net proximal operator
+(``app/linear_method/penalty.h:48-56``), learning rate
+(``app/linear_method/learning_rate.h:15-22``), logistic loss and its gradient
+(``app/linear_method/loss.h:81-93``).
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import numpy as np
+
+f32 = np.float32
+
+_M1 = np.uint64(0xff51afd7ed558ccd)
+_M2 = np.uint64(0xc4ceb9fe1a85ec53)
+
+
+def fmix64(k):
+    k = np.asarray(k, dtype=np.uint64).copy()
+    with np.errstate(over="ignore"):
+        k ^= k >> np.uint64(33)
+        k *= _M1
+        k ^= k >> np.uint64(33)
+        k *= _M2
+        k ^= k >> np.uint64(33)
+    return k
+
+
+def hash_id_to_key(ids, seed: int):
+    ids = np.asarray(ids).astype(np.uint64)
+    with np.errstate(over="ignore"):
+        k = fmix64(ids + np.uint64(seed) * np.uint64(0x9E3779B97F4A7C15) + np.uint64(0x632BE59BD9B4E019))
+    k[k == np.uint64(0xFFFFFFFFFFFFFFFF)] = np.uint64(0xFFFFFFFFFFFFFFFE)
+    return k
+
+
+def lr_eval(opt, x):
+    if opt.lr_type == "constant":
+        return np.full_like(x, f32(opt.alpha), dtype=f32)
+    return (f32(opt.alpha) / (x + f32(opt.beta))).astype(f32)
+
+
+def prox(opt, z, eta):
+    z, eta = z.astype(f32), eta.astype(f32)
+    leta = f32(opt.l1) * eta
+    den = f32(1) + f32(opt.l2) * eta
+    out = np.where(z > 0, (z - leta) / den, (z + leta) / den).astype(f32)
+    out[(z <= leta) & (z >= -leta)] = 0
+    return out
+
+
+def opt_step(opt, g, w, s0, s1):
+    """Vectorised single optimiser step; returns new (w, s0, s1) as float32."""
+    g, w, s0, s1 = (np.asarray(a, dtype=f32) for a in (g, w, s0, s1))
+    if opt.algo == "ftrl":
+        sn = np.sqrt(s1 * s1 + g * g).astype(f32)
+        sigma = ((sn - s1) / f32(opt.alpha)).astype(f32)
+        z = (s0 + (g - sigma * w)).astype(f32)
+        eta = lr_eval(opt, sn)
+        return prox(opt, -z * eta, eta), z, sn
+    if opt.algo == "adagrad":
+        s = (s0 + g * g).astype(f32)
+        eta = lr_eval(opt, np.sqrt(s).astype(f32))
+        return prox(opt, w - eta * g, eta), s, s1
+    if opt.algo == "sgd":
+        c = (s0 + f32(1)).astype(f32)
+        eta = lr_eval(opt, np.sqrt(c).astype(f32))
+        return prox(opt, w - eta * g, eta), c, s1
+    return (w + g).astype(f32), s0, s1
+
+
+def logit_loss_and_gcoef(y, margin):
+    ym = (y * margin).astype(f32)
+    en = np.exp(-np.abs(ym)).astype(f32)
+    tau = np.where(ym > 0, en / (1 + en), 1 / (1 + en)).astype(f32)
+    loss = (np.log1p(en) + np.maximum(-ym, 0)).astype(f32)
+    return loss, (-y * tau).astype(f32)
+
+
+class OracleTable:
+    """Dictionary-backed server state keyed by uint64."""
+
+    def __init__(self, opt):
+        self.opt = opt
+        self.idx: Dict[int, int] = {}
+        self.w, self.s0, self.s1 = [], [], []
+
+    def _slots(self, keys, insert=True):
+        out = np.empty(len(keys), dtype=np.int64)
+        for i, k in enumerate(keys.tolist()):
+            j = self.idx.get(k, -1)
+            if j < 0 and insert:
+                j = len(self.w)
+                self.idx[k] = j
+                self.w.append(f32(0)); self.s0.append(f32(0)); self.s1.append(f32(0))
+            out[i] = j
+        return out
+
+    def pull(self, keys):
+        sl = self._slots(keys, insert=False)
+        w = np.asarray(self.w + [f32(0)], dtype=f32)
+        return w[sl]  # -1 -> appended zero
+
+    def push(self, keys, grads):
+        """keys unique; one optimiser step per key."""
+        sl = self._slots(keys)
+        w, s0, s1 = (np.asarray(a, dtype=f32) for a in (self.w, self.s0, self.s1))
+        nw, n0, n1 = opt_step(self.opt, grads, w[sl], s0[sl], s1[sl])
+        w[sl], s0[sl], s1[sl] = nw, n0, n1
+        self.w, self.s0, self.s1 = list(w), list(s0), list(s1)
+
+    def nonzero(self):
+        items = sorted((k, self.w[j]) for k, j in self.idx.items() if self.w[j] != 0)
+        return (np.array([k for k, _ in items], dtype=np.uint64),
+                np.array([v for _, v in items], dtype=f32))
+
+
+def localize(keys_flat):
+    """(unique sorted keys, inverse column ids, counts)."""
+    u, inv, cnt = np.unique(keys_flat, return_inverse=True, return_counts=True)
+    return u, inv.astype(np.int64), cnt
+
+
+def sparse_lr_step(table: OracleTable, keys_flat, row_ptr, y, vals=None):
+    """One minibatch of sparse logistic regression against ``table``: pull,
+    margins, loss, X^T g (minibatch sum, as ``async_sgd.h:286-292``), push."""
+    u, col, _ = localize(keys_flat)
+    w = table.pull(u)
+    x = np.ones(len(keys_flat), dtype=f32) if vals is None else vals.astype(f32)
+    contrib = (w[col] * x).astype(np.float64)
+    margin = np.add.reduceat(contrib, row_ptr[:-1]).astype(f32) if len(keys_flat) else np.zeros(len(y), f32)
+    loss, gc = logit_loss_and_gcoef(y.astype(f32), margin)
+    rows = np.repeat(np.arange(len(y)), np.diff(row_ptr))
+    grad = np.zeros(len(u), dtype=np.float64)
+    np.add.at(grad, col, gc[rows].astype(np.float64) * x)
+    table.push(u, grad.astype(f32))
+    return float(loss.sum()), margin, u, grad.astype(f32)
+
+
+def auc(y, score):
+    """Exact AUC by rank-sum (``util/evaluation.h:24-45``)."""
+    y = np.asarray(y) > 0
+    order = np.argsort(score, kind="stable")
+    ranks = np.empty(len(score), dtype=np.float64)
+    ranks[order] = np.arange(1, len(score) + 1)
+    npos, nneg = y.sum(), (~y).sum()
+    if npos == 0 or nneg == 0:
+        return 0.5
+    a = (ranks[y].sum() - npos * (npos + 1) / 2) / (npos * nneg)
+    return float(a)

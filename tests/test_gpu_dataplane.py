@@ -1,0 +1,166 @@
+"""Fused pull / push / apply kernels against the NumPy oracle, on one GPU and on
+several emulated shards of one GPU (kernels of different virtual ranks run one
+after another on one stream)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(S, opt, cap=1 << 14, inbox=1 << 13, ring=3, quant="none"):
+    from parameter_server_b200.parallel.dataplane import DataPlane, PlaneConfig, heap_layout
+    from parameter_server_b200.parallel.fabric import Fabric
+    pc = PlaneConfig(table_capacity=cap, inbox_cap=inbox, ring=ring, quant=quant)
+    fabs = Fabric.emulated(S, heap_layout(pc, S).total())
+    return [DataPlane(f, pc, opt) for f in fabs]
+
+
+def _batch(rng, rows, z, n_feat, seed=1):
+    from parameter_server_b200.utils.oracle import hash_id_to_key
+    ids = np.minimum((rng.pareto(1.05, rows * z) * 2).astype(np.int64), n_feat - 1).astype(np.int32)
+    y = np.where(rng.random(rows) < 0.5, 1.0, -1.0).astype(np.float32)
+    return ids, y, hash_id_to_key(ids, seed)
+
+
+@pytest.mark.parametrize("algo", ["ftrl", "adagrad", "sgd"])
+def test_single_shard_training_matches_oracle(cuda_lib, algo):
+    from parameter_server_b200.models.sparse_lr import SparseLRConfig, SparseLRWorker
+    from parameter_server_b200.parallel.dataplane import OptimizerConfig
+    from parameter_server_b200.utils import oracle
+    opt = OptimizerConfig(algo=algo, alpha=0.1, beta=1.0, l1=0.01, l2=0.1)
+    plane = _mk(1, opt)[0]
+    rows, z = 256, 24
+    w = SparseLRWorker(plane, SparseLRConfig(max_rows=rows, max_nnz=rows * z, tau=0, hash_seed=1, pipeline=1))
+    ot = oracle.OracleTable(opt)
+    rng = np.random.default_rng(0)
+    row_ptr = np.arange(rows + 1) * z
+    tot = 0.0
+    for step in range(6):
+        ids, y, keys = _batch(rng, rows, z, 3000)
+        b = w.step(torch.from_numpy(ids).cuda(), torch.from_numpy(y).cuda(), fixed_z=z)
+        loss, margin, u, grad = oracle.sparse_lr_step(ot, keys, row_ptr, y)
+        tot += loss
+        torch.cuda.synchronize()
+        plane.check_status()
+        assert np.allclose(b.margin[:rows].cpu().numpy(), margin, rtol=1e-4, atol=1e-5), step
+        U = int(b.n_unique.item())
+        assert np.allclose(b.grad[:U].cpu().numpy(), grad, rtol=1e-4, atol=1e-5)
+    prog = w.read_progress()
+    assert prog["n_examples"] == 6 * rows
+    assert abs(prog["loss_sum"] - tot) < 1e-3 * tot
+    k, wv = plane.dump_nonzero()
+    ok, ow = ot.nonzero()
+    assert np.array_equal(k.numpy(), ok)
+    assert np.allclose(wv.numpy(), ow, rtol=2e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("S", [2, 4])
+@pytest.mark.parametrize("quant", ["none", "int8", "fp16"])
+def test_emulated_shards_aggregate_pushes(cuda_lib, S, quant):
+    """S workers push the same round; every owner sums duplicate keys across
+    sources and runs FTRL once on the sum."""
+    from parameter_server_b200.ops.localize import LocalBatch
+    from parameter_server_b200.parallel.dataplane import OptimizerConfig
+    from parameter_server_b200.utils import oracle
+    opt = OptimizerConfig(algo="ftrl", alpha=0.1, beta=1.0, l1=0.001, l2=0.1)
+    planes = _mk(S, opt, quant=quant)
+    rows, z = 128, 16
+    rng = np.random.default_rng(S)
+    ot = oracle.OracleTable(opt)
+    bufs = [LocalBatch(rows, rows * z, S, "cuda") for _ in range(S)]
+    row_ptr = np.arange(rows + 1) * z
+    for t in range(4):
+        data = [_batch(rng, rows, z, 2000) for _ in range(S)]
+        # oracle: pull (same weights for all), per-worker gradients, summed per key, one step
+        gsum = {}
+        for ids, y, keys in data:
+            u, col, _ = oracle.localize(keys)
+            wv = ot.pull(u)
+            margin = np.add.reduceat(wv[col].astype(np.float64), row_ptr[:-1]).astype(np.float32)
+            _, gc = oracle.logit_loss_and_gcoef(y, margin)
+            g = np.zeros(len(u)); np.add.at(g, col, gc[np.repeat(np.arange(rows), z)])
+            if quant != "none":
+                pass
+            for k, v in zip(u.tolist(), g.tolist()):
+                gsum[k] = gsum.get(k, 0.0) + v
+        ks = np.array(sorted(gsum), dtype=np.uint64)
+        ot.push(ks, np.array([gsum[k] for k in ks.tolist()], dtype=np.float32))
+        for r in range(S):
+            ids, y, _ = data[r]
+            bufs[r].localize(torch.from_numpy(ids).cuda(), torch.from_numpy(y).cuda(), planes[r].bounds,
+                             fixed_z=z, hash_seed=1)
+            planes[r].pull_margin(bufs[r], need_applied=t)
+        for r in range(S):
+            planes[r].push(bufs[r], t)
+        for r in range(S):
+            planes[r].apply(t)
+        torch.cuda.synchronize()
+        for p in planes:
+            p.check_status()
+    got = {}
+    for p in planes:
+        k, wv = p.dump_nonzero()
+        lo, hi = p.bounds_host[p.rank], p.bounds_host[p.rank + 1]
+        assert all(lo <= int(x) < hi for x in k.numpy().tolist())
+        got.update(zip(k.numpy().tolist(), wv.numpy().tolist()))
+    ok, ow = ot.nonzero()
+    tol = dict(none=(2e-4, 1e-6), int8=(0.2, 0.02), fp16=(2e-2, 2e-3))[quant]
+    if quant == "none":
+        assert sorted(got) == ok.tolist()
+    exp = dict(zip(ok.tolist(), ow.tolist()))
+    common = [k for k in exp if k in got]
+    assert len(common) > 0.9 * len(exp)
+    a = np.array([got[k] for k in common]); b_ = np.array([exp[k] for k in common])
+    assert np.allclose(a, b_, rtol=tol[0], atol=tol[1])
+
+
+def test_dead_source_is_skipped_and_wait_times_out_cleanly(cuda_lib):
+    """A source that never pushes: with alive=False the apply completes; with
+    alive=True the bounded wait runs out and reports status 3 (no hang)."""
+    from parameter_server_b200.ops.localize import LocalBatch
+    from parameter_server_b200.ops._lib import PsbCudaError
+    from parameter_server_b200.parallel.dataplane import OptimizerConfig
+    opt = OptimizerConfig(algo="sum")
+    planes = _mk(2, opt)
+    b = LocalBatch(8, 64, 2, "cuda")
+    keys = np.array([5, 1 << 63, (1 << 63) + 9], dtype=np.uint64)
+    b.set_keys(torch.from_numpy(keys.view(np.int64)).cuda(), planes[0].bounds_host)
+    b.grad[:3] = torch.tensor([1.0, 2.0, 3.0]).cuda()
+    planes[0].push(b, 0, with_gradient=False)       # rank 1 never pushes
+    planes[1].set_alive(1, False)
+    planes[1].apply(0)
+    torch.cuda.synchronize()
+    planes[1].check_status()
+    k, w = planes[1].dump_nonzero()
+    assert k.numpy().tolist() == [1 << 63, (1 << 63) + 9] and w.tolist() == [2.0, 3.0]
+    planes[0].apply(0, wait_iters=2000)              # waits for rank 1's flag: bounded
+    torch.cuda.synchronize()
+    with pytest.raises(PsbCudaError, match="timed out"):
+        planes[0].check_status()
+    # the context is still usable
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0
+
+
+def test_pipelined_submit_matches_synchronous(cuda_lib):
+    from parameter_server_b200.models.sparse_lr import SparseLRConfig, SparseLRWorker
+    from parameter_server_b200.parallel.dataplane import OptimizerConfig
+    opt = OptimizerConfig(algo="ftrl", l1=0.01)
+    rows, z = 512, 20
+    rng = np.random.default_rng(2)
+    batches = [_batch(rng, rows, z, 5000) for _ in range(5)]
+    outs = []
+    for mode in ("sync", "pipe"):
+        plane = _mk(1, opt, ring=2)[0]
+        w = SparseLRWorker(plane, SparseLRConfig(max_rows=rows, max_nnz=rows * z, tau=0, hash_seed=1, pipeline=2))
+        for ids, y, _ in batches:
+            if mode == "sync":
+                w.step(torch.from_numpy(ids).cuda(), torch.from_numpy(y).cuda(), fixed_z=z)
+            else:
+                w.submit(torch.from_numpy(ids).pin_memory(), torch.from_numpy(y).pin_memory(), fixed_z=z)
+        w.wait()
+        torch.cuda.synchronize()
+        plane.check_status()
+        outs.append(plane.dump_nonzero())
+    assert np.array_equal(outs[0][0].numpy(), outs[1][0].numpy())
+    assert np.allclose(outs[0][1].numpy(), outs[1][1].numpy(), rtol=1e-5, atol=1e-7)

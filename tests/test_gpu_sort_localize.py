@@ -1,0 +1,102 @@
+"""Radix sort and minibatch localisation against NumPy."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand_keys(n, rng, skew=False, bits=64):
+    if skew:
+        ids = (rng.pareto(1.05, n) * 3).astype(np.uint64) % np.uint64(1 << 20)
+        from parameter_server_b200.utils.oracle import hash_id_to_key
+        k = hash_id_to_key(ids, 7)
+    else:
+        k = rng.integers(0, 1 << 63, n, dtype=np.uint64) * np.uint64(2) + rng.integers(0, 2, n, dtype=np.uint64)
+    if bits < 64:
+        k = k >> np.uint64(64 - bits)
+    return k
+
+
+@pytest.mark.parametrize("n", [1, 31, 4096, 4097, 100_003, 1_500_000])
+@pytest.mark.parametrize("skew", [False, True])
+def test_sort_pairs_matches_numpy(cuda_lib, n, skew):
+    from parameter_server_b200.ops.localize import sort_pairs
+    rng = np.random.default_rng(n + skew)
+    k = _rand_keys(n, rng, skew)
+    kt = torch.from_numpy(k.view(np.int64)).cuda()
+    sk, sv = sort_pairs(kt)
+    torch.cuda.synchronize()
+    order = np.argsort(k, kind="stable")
+    assert np.array_equal(sk.cpu().numpy().view(np.uint64), k[order])
+    assert np.array_equal(sv.cpu().numpy().astype(np.int64), order)  # stable => identical permutation
+
+
+def test_sort_partial_bits_and_payload(cuda_lib):
+    from parameter_server_b200.ops.localize import sort_pairs
+    rng = np.random.default_rng(3)
+    n = 50_000
+    k = _rand_keys(n, rng, bits=26)
+    pay = rng.integers(0, 1 << 31, n, dtype=np.int64).astype(np.int32)
+    sk, sv = sort_pairs(torch.from_numpy(k.view(np.int64)).cuda(), torch.from_numpy(pay).cuda(), 0, 26)
+    order = np.argsort(k, kind="stable")
+    assert np.array_equal(sk.cpu().numpy().view(np.uint64), k[order])
+    assert np.array_equal(sv.cpu().numpy(), pay[order])
+
+
+@pytest.mark.parametrize("S", [1, 2, 8])
+@pytest.mark.parametrize("fixed", [True, False])
+def test_localize_matches_numpy(cuda_lib, S, fixed):
+    from parameter_server_b200.ops.localize import LocalBatch
+    from parameter_server_b200.utils.range import Range, shard_bounds
+    rng = np.random.default_rng(11 + S)
+    rows, z = 700, 37
+    if fixed:
+        row_ptr = np.arange(rows + 1) * z
+    else:
+        lens = rng.integers(0, 2 * z, rows)
+        row_ptr = np.concatenate([[0], np.cumsum(lens)])
+    nnz = int(row_ptr[-1])
+    keys = _rand_keys(nnz, rng, skew=True)
+    vals = rng.random(nnz, dtype=np.float32)
+    b = LocalBatch(rows, nnz, S, "cuda", real_values=True)
+    bounds_h = shard_bounds(Range.all(), S)
+    bounds = torch.tensor([x if x < (1 << 63) else x - (1 << 64) for x in bounds_h], dtype=torch.int64).cuda()
+    ids = torch.from_numpy(keys.view(np.int64)).cuda()
+    kw = dict(fixed_z=z) if fixed else dict(row_ptr=torch.from_numpy(row_ptr.astype(np.int32)).cuda())
+    b.localize(ids, None, bounds, vals=torch.from_numpy(vals).cuda(), hash_seed=None, **kw)
+    torch.cuda.synchronize()
+    u, inv, cnt = np.unique(keys, return_inverse=True, return_counts=True)
+    U = int(b.n_unique.item())
+    assert U == len(u)
+    assert np.array_equal(b.ukeys[:U].cpu().numpy().view(np.uint64), u)
+    assert np.array_equal(b.csr_col[:nnz].cpu().numpy(), inv)
+    seg = b.seg_off[:U + 1].cpu().numpy()
+    assert np.array_equal(np.diff(seg), cnt)
+    # CSC rows/values: each segment lists the rows containing that key, in position order
+    rows_of = np.repeat(np.arange(rows), np.diff(row_ptr))
+    order = np.argsort(keys, kind="stable")
+    assert np.array_equal(b.csc_row[:nnz].cpu().numpy(), rows_of[order])
+    assert np.allclose(b.csc_val[:nnz].cpu().numpy(), vals[order])
+    own = b.own_off.cpu().numpy()
+    exp = [int(np.searchsorted(u, np.uint64(x))) for x in bounds_h[:-1]] + [U]
+    assert list(own) == exp
+    # head bitmap consistent with segment offsets
+    fb = b.flagbits[:(nnz + 31) // 32].cpu().numpy().view(np.uint32)
+    heads = np.zeros(nnz, dtype=bool); heads[seg[:-1]] = True
+    bits = np.unpackbits(fb.view(np.uint8), bitorder="little")[:nnz].astype(bool)
+    assert np.array_equal(bits, heads)
+    wb = b.wordbase[:(nnz + 31) // 32].cpu().numpy()
+    assert np.array_equal(wb, np.concatenate([[0], np.cumsum(heads)])[0:nnz:32])
+
+
+def test_hash_on_device_matches_oracle(cuda_lib):
+    from parameter_server_b200.ops.localize import LocalBatch
+    from parameter_server_b200.utils.oracle import hash_id_to_key
+    rng = np.random.default_rng(5)
+    ids = rng.integers(0, 1 << 26, 64 * 50, dtype=np.int64).astype(np.int32)
+    b = LocalBatch(64, ids.size, 1, "cuda")
+    bounds = torch.tensor([0, -1], dtype=torch.int64).cuda()
+    b.localize(torch.from_numpy(ids).cuda(), None, bounds, fixed_z=50, hash_seed=9)
+    U = int(b.n_unique.item())
+    assert np.array_equal(b.ukeys[:U].cpu().numpy().view(np.uint64), np.unique(hash_id_to_key(ids, 9)))
