@@ -98,6 +98,8 @@ def main():
     ap.add_argument("--pool", type=int, default=4, help="distinct minibatches cycled through")
     ap.add_argument("--quant", default="none")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--hashed-slots", action="store_true",
+                    help="re-hash keys into table slots instead of the order-preserving slot map")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -134,7 +136,8 @@ def main():
     while cap < 2 * n_feat // world:
         cap *= 2
     inbox_cap = nnz if world == 1 else (nnz // world) * 5 // 4 + 4096
-    pc = PlaneConfig(table_capacity=cap, inbox_cap=inbox_cap, ring=args.tau + 2, quant=args.quant)
+    pc = PlaneConfig(table_capacity=cap, inbox_cap=inbox_cap, ring=args.tau + 2, quant=args.quant,
+                     ordered_slots=not args.hashed_slots)
     opt = OptimizerConfig(algo="ftrl", alpha=0.1, beta=1.0, l1=1.0, l2=0.1)
     hb = heap_layout(pc, world).total()
     fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
@@ -224,7 +227,7 @@ def main():
             "config": {"model": "FTRL-proximal L1/L2 logistic regression", "global_batch": world * rows,
                        "rows_per_worker": rows, "nnz_per_row": z, "keys": f"2^{args.log2_keys} hashed uint64",
                        "seq_len": z, "parallelism": f"dp{world} x key-range shards{world}", "tau": args.tau,
-                       "alpha": 0.1, "beta": 1.0, "l1": 1.0, "l2": 0.1, "quant": args.quant,
+                       "alpha": 0.1, "beta": 1.0, "l1": 1.0, "l2": 0.1, "quant": args.quant, "ordered_slots": not args.hashed_slots,
                        "unique_keys_per_step_per_worker": u_mean,
                        "push_pull_keys_per_s": 2 * u_mean * world * args.steps / (ms * 1e-3),
                        "l2_policy": f"inputs larger than L2: {args.pool} distinct minibatches of "

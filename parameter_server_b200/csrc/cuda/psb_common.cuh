@@ -87,6 +87,14 @@ __device__ __forceinline__ u32 ld_acquire_gpu(const u32* p) {
 __device__ __forceinline__ void st_release_gpu(u32* p, u32 v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ u32 ld_relaxed_gpu(const u32* p) {
+  u32 v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_gpu(u32* p, u32 v) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ u64 ld_relaxed_sys_u64(const u64* p) {
   u64 v;
   asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -138,13 +146,31 @@ __device__ __forceinline__ bool grid_barrier(u32* bar, u32* status) {
   return s_ok != 0;
 }
 
+// How a key is mapped to its first probe slot. mult == 0: slot = fmix64(key) &
+// mask (any key distribution). mult != 0: order-preserving map for keys that are
+// already uniformly spread over the shard's range (hashed keys):
+//   slot = floor((key - begin) * capacity / range_size) = umulhi(key - begin, mult),
+// so that a sorted key list walks the table in address order (TLB- and
+// DRAM-page-friendly for the pull and apply kernels, which see sorted keys).
+struct SlotMap {
+  u64 mask;
+  u64 begin;
+  u64 mult;
+};
+__device__ __forceinline__ u64 first_slot(const SlotMap& m, u64 key) {
+  if (m.mult == 0) return fmix64(key) & m.mask;
+  u64 s = __umul64hi(key - m.begin, m.mult);
+  return s > m.mask ? m.mask : s;
+}
+
 // ---- open-addressing table probe (linear probing, power-of-two capacity) ----
 // Returns the slot index of `key`, or -1 if absent (insert=false) / table full.
 // `tab` may be a peer-mapped pointer: all accesses are plain loads plus one
 // 64-bit CAS on insert, which NVLink carries natively.
 template <bool kInsert>
-__device__ __forceinline__ long long table_find(Entry* tab, u64 mask, u64 key, u32 max_probe) {
-  u64 slot = fmix64(key) & mask;
+__device__ __forceinline__ long long table_find(Entry* tab, const SlotMap& sm, u64 key, u32 max_probe) {
+  const u64 mask = sm.mask;
+  u64 slot = first_slot(sm, key);
   for (u32 p = 0; p < max_probe; ++p) {
     u64 k = ld_relaxed_sys_u64(&tab[slot].key);
     if (k == key) return (long long)slot;
@@ -160,9 +186,10 @@ __device__ __forceinline__ long long table_find(Entry* tab, u64 mask, u64 key, u
 
 // Pull-side probe: one 16-byte load per probed slot returns key and weight.
 // Returns the slot (or -1) and writes the weight (0 when absent).
-__device__ __forceinline__ long long table_lookup_w(const Entry* tab, u64 mask, u64 key,
+__device__ __forceinline__ long long table_lookup_w(const Entry* tab, const SlotMap& sm, u64 key,
                                                     u32 max_probe, float* w_out) {
-  u64 slot = fmix64(key) & mask;
+  const u64 mask = sm.mask;
+  u64 slot = first_slot(sm, key);
   for (u32 p = 0; p < max_probe; ++p) {
     u64 k, hi;
     asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];"

@@ -47,6 +47,8 @@ typedef struct {
   int insert;                 // insert absent keys on pull (KVMap first-touch semantics)
   void* table[PSB_MAX_SHARDS];            // Entry* of shard s (local or peer-mapped)
   psb_u64 mask[PSB_MAX_SHARDS];          // capacity-1 of shard s
+  psb_u64 key_begin[PSB_MAX_SHARDS];     // first key of shard s's range
+  psb_u64 slot_mult[PSB_MAX_SHARDS];     // 0: hashed slots; else order-preserving multiplier
   const uint32_t* applied[PSB_MAX_SHARDS];  // shard s's "applied" counter (may be peer-mapped)
   uint32_t need_applied;      // bounded delay: wait until applied[s] >= need_applied
   const psb_u64* ukeys;
@@ -109,6 +111,8 @@ typedef struct {
   int quant;
   void* table;
   psb_u64 mask;
+  psb_u64 key_begin;
+  psb_u64 slot_mult;
   const psb_u64* inbox_keys[PSB_MAX_SHARDS];
   const void* inbox_vals[PSB_MAX_SHARDS];
   const uint32_t* ready[PSB_MAX_SHARDS];
@@ -133,7 +137,7 @@ int psb_apply(const PsbApplyParams* p, cudaStream_t stream);
 int psb_table_dump(const void* table, psb_u64 capacity, psb_u64* out_keys, float* out_w,
                    psb_u64 out_cap, unsigned long long* out_n, cudaStream_t stream);
 // Bulk load (key, s0, s1, w) tuples into a table (checkpoint restore / model_input).
-int psb_table_load(void* table, psb_u64 mask, const psb_u64* keys, const float* s0,
+int psb_table_load(void* table, psb_u64 mask, psb_u64 key_begin, psb_u64 slot_mult, const psb_u64* keys, const float* s0,
                    const float* s1, const float* w, psb_u64 n, uint32_t* status,
                    cudaStream_t stream);
 // Full state dump for checkpoints: every occupied slot.

@@ -139,10 +139,10 @@ __global__ void __launch_bounds__(kSortThreads) k_sort_onesweep(
     s_cnt[ww * kRadix + t] = total;
     total += c;
   }
-  // publish the tile aggregate early so successors can move on
+  // publish the tile aggregate early so successors can move on. The status word
+  // itself is the only datum exchanged, so relaxed gpu-scope accesses suffice.
   u32* my_status = status + (size_t)tile * kRadix;
-  if (tile == 0) st_release_gpu(&my_status[t], kFlagIncl | total);
-  else st_release_gpu(&my_status[t], kFlagAgg | total);
+  st_relaxed_gpu(&my_status[t], (tile == 0 ? kFlagIncl : kFlagAgg) | total);
 
   u32 dstart = block_excl_scan_256(total, s_warp, nullptr);
   s_dstart[t] = dstart;
@@ -150,24 +150,38 @@ __global__ void __launch_bounds__(kSortThreads) k_sort_onesweep(
   u32 gh = ghist[t];
   u32 gex = block_excl_scan_256(gh, s_warp, nullptr);
 
-  // ---- decoupled look-back for digit t ----
+  // ---- decoupled look-back for digit t, kLookBatch predecessors per round trip ----
+  // All tiles of the first wave start together, so a tile may have to walk over
+  // many predecessors that have only published aggregates; fetching them in
+  // batches of independent loads hides the L2 latency of that walk.
   u32 ex = 0;
   if (tile > 0) {
+    constexpr int kLookBatch = 8;
     long long p = (long long)tile - 1;
     u32 spins = 0;
-    while (p >= 0) {
-      u32 s = ld_acquire_gpu(status + (size_t)p * kRadix + t);
-      u32 f = s & ~kValMask;
-      if (f == 0) {
-        if (++spins > kGridWaitIters) { set_status(err, kLookbackTimeout); break; }
-        __nanosleep(20);
-        continue;
+    bool done = false;
+    while (!done && p >= 0) {
+      u32 sv[kLookBatch];
+#pragma unroll
+      for (int k = 0; k < kLookBatch; ++k)
+        sv[k] = (p - k >= 0) ? ld_relaxed_gpu(status + (size_t)(p - k) * kRadix + t) : kFlagIncl;
+      int used = 0;
+#pragma unroll
+      for (int k = 0; k < kLookBatch; ++k) {
+        if (done || used < k) continue;
+        u32 f = sv[k] & ~kValMask;
+        if (f == 0) continue;          // not published yet: stop consuming, re-poll from here
+        ex += sv[k] & kValMask;
+        used = k + 1;
+        if (f == kFlagIncl) done = true;
       }
-      ex += s & kValMask;
-      if (f == kFlagIncl) break;
-      --p;
+      p -= used;
+      if (!done && used < kLookBatch) {
+        if (++spins > kGridWaitIters) { set_status(err, kLookbackTimeout); break; }
+        if (used == 0) __nanosleep(20);
+      }
     }
-    st_release_gpu(&my_status[t], kFlagIncl | ((ex + total) & kValMask));
+    st_relaxed_gpu(&my_status[t], kFlagIncl | ((ex + total) & kValMask));
   }
   s_gbase[t] = gex + ex - dstart;
   __syncthreads();

@@ -129,10 +129,10 @@ __global__ void k_table_dump(const Entry* tab, u64 cap, u64* out_keys, float* ou
   }
 }
 
-__global__ void k_table_load(Entry* tab, u64 mask, const u64* keys, const float* s0, const float* s1,
+__global__ void k_table_load(Entry* tab, SlotMap sm, const u64* keys, const float* s0, const float* s1,
                              const float* w, u64 n, u32* status) {
   for (u64 i = blockIdx.x * (u64)blockDim.x + threadIdx.x; i < n; i += (u64)gridDim.x * blockDim.x) {
-    long long slot = table_find<true>(tab, mask, keys[i], kMaxProbe);
+    long long slot = table_find<true>(tab, sm, keys[i], kMaxProbe);
     if (slot < 0) { set_status(status, kTableFull); continue; }
     tab[slot].w = w ? w[i] : 0.f;
     tab[slot].s0 = s0 ? s0[i] : 0.f;
@@ -160,8 +160,9 @@ __global__ void __launch_bounds__(kThreads) k_pull_margin(const PsbPullParams p)
     u64 key = p.ukeys[u];
     float w;
     long long slot;
+    const SlotMap sm{p.mask[s], p.key_begin[s], p.slot_mult[s]};
     if (p.insert) {
-      slot = table_find<true>((Entry*)p.table[s], p.mask[s], key, kMaxProbe);
+      slot = table_find<true>((Entry*)p.table[s], sm, key, kMaxProbe);
       w = 0.f;
       if (slot >= 0) {
         asm volatile("ld.relaxed.sys.global.f32 %0, [%1];"
@@ -170,7 +171,7 @@ __global__ void __launch_bounds__(kThreads) k_pull_margin(const PsbPullParams p)
         set_status(p.status, kTableFull);
       }
     } else {
-      slot = table_lookup_w((const Entry*)p.table[s], p.mask[s], key, kMaxProbe, &w);
+      slot = table_lookup_w((const Entry*)p.table[s], sm, key, kMaxProbe, &w);
     }
     p.w_local[u] = w;
     if (p.slot_local) p.slot_local[u] = (int32_t)slot;
@@ -375,6 +376,7 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
   int n_src = 0;
   for (int r = 0; r < S; ++r) n_src += p.alive[r] ? 1 : 0;
   const bool single = n_src <= 1;
+  const SlotMap sm{p.mask, p.key_begin, p.slot_mult};
   StatAcc st;
 
   // phase A: locate the slot of every record; single source -> update in place,
@@ -388,7 +390,7 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
     if (p.cached[r]) {
       slot = p.slot_cache[r][j] & 0x7fffffffu;
     } else {
-      slot = table_find<true>(tab, p.mask, p.inbox_keys[r][j], kMaxProbe);
+      slot = table_find<true>(tab, sm, p.inbox_keys[r][j], kMaxProbe);
       if (slot < 0) { set_status(p.status, kTableFull); if (p.slot_cache[r]) p.slot_cache[r][j] = 0x7fffffffu; continue; }
     }
     if (single) {
@@ -493,12 +495,12 @@ extern "C" int psb_table_export(const void* table, psb_u64 capacity, psb_u64* ou
   return -(int)cudaGetLastError();
 }
 
-extern "C" int psb_table_load(void* table, psb_u64 mask, const psb_u64* keys, const float* s0,
-                              const float* s1, const float* w, psb_u64 n, uint32_t* status,
-                              cudaStream_t stream) {
+extern "C" int psb_table_load(void* table, psb_u64 mask, psb_u64 key_begin, psb_u64 slot_mult,
+                              const psb_u64* keys, const float* s0, const float* s1, const float* w,
+                              psb_u64 n, uint32_t* status, cudaStream_t stream) {
   if (n == 0) return 0;
-  k_table_load<<<148 * 4, 256, 0, stream>>>((Entry*)table, mask, (const u64*)keys, s0, s1, w, n,
-                                            status);
+  k_table_load<<<148 * 4, 256, 0, stream>>>((Entry*)table, SlotMap{mask, key_begin, slot_mult},
+                                            (const u64*)keys, s0, s1, w, n, status);
   return -(int)cudaGetLastError();
 }
 

@@ -38,7 +38,8 @@ class Optimizer(C.Structure):
 class PullParams(C.Structure):
     _fields_ = [
         ("S", _i32), ("insert", _i32),
-        ("table", _vp * MAX_SHARDS), ("mask", _u64 * MAX_SHARDS), ("applied", _vp * MAX_SHARDS),
+        ("table", _vp * MAX_SHARDS), ("mask", _u64 * MAX_SHARDS),
+        ("key_begin", _u64 * MAX_SHARDS), ("slot_mult", _u64 * MAX_SHARDS), ("applied", _vp * MAX_SHARDS),
         ("need_applied", _u32),
         ("ukeys", _vp), ("n_unique", _vp), ("own_off", _vp),
         ("w_local", _vp), ("slot_local", _vp), ("grad_zero", _vp),
@@ -64,7 +65,7 @@ class PushParams(C.Structure):
 class ApplyParams(C.Structure):
     _fields_ = [
         ("S", _i32), ("ts1", _u32), ("inbox_cap", _u32), ("quant", _i32),
-        ("table", _vp), ("mask", _u64),
+        ("table", _vp), ("mask", _u64), ("key_begin", _u64), ("slot_mult", _u64),
         ("inbox_keys", _vp * MAX_SHARDS), ("inbox_vals", _vp * MAX_SHARDS),
         ("ready", _vp * MAX_SHARDS), ("count", _vp * MAX_SHARDS),
         ("alive", C.c_uint8 * MAX_SHARDS), ("cached", C.c_uint8 * MAX_SHARDS),
@@ -100,7 +101,7 @@ def _declare(lib):
     lib.psb_push.argtypes = [C.POINTER(PushParams), _vp]
     lib.psb_apply.argtypes = [C.POINTER(ApplyParams), _vp]
     lib.psb_table_dump.argtypes = [_vp, _u64, _vp, _vp, _u64, _vp, _vp]
-    lib.psb_table_load.argtypes = [_vp, _u64, _vp, _vp, _vp, _vp, _u64, _vp, _vp]
+    lib.psb_table_load.argtypes = [_vp, _u64, _u64, _u64, _vp, _vp, _vp, _vp, _u64, _vp, _vp]
     lib.psb_table_export.argtypes = [_vp, _u64, _vp, _vp, _vp, _vp, _u64, _vp, _vp]
     lib.psb_coop_grid.argtypes = [_i32]
     lib.psb_gen_batch.argtypes = [_vp, _vp, _vp, _vp, _u32, _u32, _u64, _f64, _u64, _u64, _i32, _vp]

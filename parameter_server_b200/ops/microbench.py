@@ -1,0 +1,158 @@
+"""Per-kernel micro-benchmarks with CUDA-event timing and roofline fractions.
+
+    python -m parameter_server_b200.ops.microbench sort  --n 13107200
+    python -m parameter_server_b200.ops.microbench step  --rows 65536 --z 200
+
+Each timed launch is preceded by an L2 flush (a write over a 256 MB buffer) and
+timed with CUDA events on the launching stream after warm-up. Fractions are
+"of measured": the denominators come from ``MEASURED_PEAKS.json`` at the
+repository root when present (copy bandwidth), else 6650 GB/s ("of fallback").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from pathlib import Path
+
+import torch
+
+
+def _peak_gbs():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        return json.loads(p.read_text())["hbm_gbs"], "of measured"
+    return 6650.0, "of fallback"
+
+
+def _time(fn, iters, flush):
+    from ..utils.synthetic import flush_l2
+    ts = []
+    for i in range(iters + 3):
+        flush_l2(flush, i)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def bench_sort(args):
+    from . import _lib
+    from .localize import LocalBatch
+    from ..utils.synthetic import gen_batch
+    n = args.n
+    dev = torch.device("cuda")
+    flush = torch.empty(64 << 20, dtype=torch.int32, device=dev)
+    ids, _, _ = gen_batch(n // 200, 200, 1 << 26, 1.05, 0, 0, device=dev)
+    n = ids.numel()
+    b = LocalBatch(n // 200, n, 1, dev)
+    bounds = torch.tensor([0, -1], dtype=torch.int64, device=dev)
+    peak, tag = _peak_gbs()
+
+    def run():
+        b.localize(ids, None, bounds, fixed_z=200, hash_seed=0, key_bits=args.bits)
+    med, best = _time(run, args.iters, flush)
+    _lib.check_status(b.status, "sort")
+    npass = (args.bits + 7) // 8
+    bytes_sort = n * (4 + 8 + 8) + npass * n * 24       # ids read + keys write + hist read; passes r+w
+    print(json.dumps({"kernel": "sort+localize", "n": n, "passes": npass, "ms_median": med, "ms_best": best,
+                      "sort_algorithmic_GB": bytes_sort / 1e9,
+                      "frac_of_copy_bw_if_all_sort": bytes_sort / 1e9 / (med * 1e-3) / peak, "peak": tag}))
+
+
+def bench_step(args):
+    from . import _lib
+    from ..models.sparse_lr import SparseLRConfig, make_single_gpu
+    from ..parallel.dataplane import OptimizerConfig
+    from ..utils.synthetic import gen_batch
+    dev = torch.device("cuda")
+    rows, z = args.rows, args.z
+    nnz = rows * z
+    cap = 1
+    while cap < 2 * (1 << args.log2_keys):
+        cap *= 2
+    w = make_single_gpu(cap, nnz, OptimizerConfig(), SparseLRConfig(max_rows=rows, max_nnz=nnz, pipeline=1),
+                        dev, ordered_slots=not args.hashed_slots)
+    flush = torch.empty(64 << 20, dtype=torch.int32, device=dev)
+    pool = [gen_batch(rows, z, 1 << args.log2_keys, 1.05, 0, i, device=dev)[:2] for i in range(3)]
+    peak, tag = _peak_gbs()
+    plane = w.plane
+    state = {"t": 0}
+    # warm the table so that pulls hit existing entries
+    for ids, y in pool:
+        w.step(ids, y, fixed_z=z)
+    torch.cuda.synchronize()
+    b = w.prepare(*pool[0], fixed_z=z, slot=0)
+    U = int(b.n_unique.item())
+    res = {"rows": rows, "z": z, "nnz": nnz, "unique": U, "peak": tag}
+
+    def t_prep():
+        w.prepare(*pool[0], fixed_z=z, slot=0)
+
+    def t_pull():
+        plane.pull_margin(b, need_applied=0)
+
+    def t_push():
+        plane.push(b, w.step_no)
+
+    def t_apply():
+        plane.apply(w.step_no)
+        w.step_no += 1
+    for name, fn, alg_bytes in (
+            ("localize(sort+unique+remap)", t_prep, nnz * 20 + 8 * nnz * 24 + nnz * 8 * 2 + nnz * 12),
+            ("pull_margin", t_pull, U * 32 + U * 16 + nnz * 8 + rows * 12),
+            ("push", t_push, nnz * 8 + U * 12 + U * 16),
+            ("apply", t_apply, U * 12 + U * 64)):
+        if name == "apply":
+            # every apply needs a fresh push of the same round
+            from ..utils.synthetic import flush_l2
+            ts = []
+            for i in range(args.iters + 2):
+                plane.push(b, w.step_no)
+                flush_l2(flush, i)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+                if i >= 2:
+                    ts.append(e0.elapsed_time(e1))
+            ts.sort(); med = ts[len(ts) // 2]
+        elif name == "push":
+            from ..utils.synthetic import flush_l2
+            ts = []
+            for i in range(args.iters + 2):
+                plane.pull_margin(b, need_applied=0)   # zeroes grad
+                flush_l2(flush, i)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+                plane.apply(w.step_no); w.step_no += 1
+                if i >= 2:
+                    ts.append(e0.elapsed_time(e1))
+            ts.sort(); med = ts[len(ts) // 2]
+        else:
+            med, _ = _time(fn, args.iters, flush)
+        res[name] = {"ms": med, "algorithmic_MB": alg_bytes / 1e6,
+                     "frac_of_copy_bw": alg_bytes / 1e9 / (med * 1e-3) / peak}
+    plane.check_status("microbench")
+    print(json.dumps(res))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    s = sub.add_parser("sort"); s.add_argument("--n", type=int, default=65536 * 200)
+    s.add_argument("--bits", type=int, default=64); s.add_argument("--iters", type=int, default=5)
+    s = sub.add_parser("step"); s.add_argument("--rows", type=int, default=65536); s.add_argument("--z", type=int, default=200)
+    s.add_argument("--log2-keys", type=int, default=26); s.add_argument("--iters", type=int, default=5)
+    s.add_argument("--hashed-slots", action="store_true")
+    args = ap.parse_args()
+    import sys
+    sys.path.insert(0, os.fspath(Path(__file__).resolve().parents[2]))
+    from .. import _build
+    _build.build_cuda()
+    {"sort": bench_sort, "step": bench_step}[args.cmd](args)
+
+
+if __name__ == "__main__":
+    main()

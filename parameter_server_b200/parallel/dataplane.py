@@ -59,6 +59,7 @@ class PlaneConfig:
     ring: int = 2                           # inbox ring slots (bounded delay tau => tau+2)
     key_range: Range = field(default_factory=Range.all)
     quant: str = "none"                     # none | int8 | fp16 (fixed-point filter on pushes)
+    ordered_slots: bool = False             # keys are uniformly hashed: order-preserving slot map
 
     def quant_code(self) -> int:
         return {"none": _lib.QUANT_NONE, "int8": _lib.QUANT_INT8, "fp16": _lib.QUANT_FP16}[self.quant]
@@ -97,6 +98,12 @@ class DataPlane:
         self.push_stats = torch.zeros(4, dtype=torch.float64, device=dev)   # d_nnz, w2, dw2, n
         self.pull_stats = torch.zeros(4, dtype=torch.float64, device=dev)   # loss, correct, rows
         self.alive = [True] * self.S
+        # order-preserving slot multiplier per shard: floor(capacity * 2^64 / range_size)
+        self.slot_mult = []
+        for s in range(self.S):
+            size = self.bounds_host[s + 1] - self.bounds_host[s]
+            m = (cfg.table_capacity << 64) // size if (cfg.ordered_slots and size > cfg.table_capacity) else 0
+            self.slot_mult.append(m if m < (1 << 64) else 0)
         self.applied_ts1 = 0
         self.ctrl = fabric.view(self.layout["ctrl"], (CTRL_WORDS,), torch.int32)
         check(_lib.lib().psb_table_init(fabric.ptr(self.rank, self.layout["table"]),
@@ -136,6 +143,8 @@ class DataPlane:
         for s in range(self.S):
             p.table[s] = self.table_ptr(s)
             p.mask[s] = self.cfg.table_capacity - 1
+            p.key_begin[s] = self.bounds_host[s]
+            p.slot_mult[s] = self.slot_mult[s]
             p.applied[s] = self._ctrl(s, 0)
         p.need_applied = need_applied
         p.ukeys, p.n_unique, p.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
@@ -186,6 +195,7 @@ class DataPlane:
         p = ApplyParams()
         p.S, p.ts1, p.inbox_cap, p.quant = self.S, ts + 1, cfg.inbox_cap, cfg.quant_code()
         p.table, p.mask = self.table_ptr(), cfg.table_capacity - 1
+        p.key_begin, p.slot_mult = self.bounds_host[self.rank], self.slot_mult[self.rank]
         for r in range(self.S):
             p.inbox_keys[r] = self._inbox_keys(self.rank, q, r)
             p.inbox_vals[r] = self._inbox_vals(self.rank, q, r)
@@ -249,6 +259,7 @@ class DataPlane:
         k = torch.from_numpy(np.ascontiguousarray(keys_u64).view("int64")).to(self.device)
         f = lambda t: None if t is None else t.to(self.device, torch.float32).contiguous()
         s0, s1, w = f(s0), f(s1), f(w)
-        check(_lib.lib().psb_table_load(self.table_ptr(), self.cfg.table_capacity - 1, ptr(k), ptr(s0), ptr(s1),
+        check(_lib.lib().psb_table_load(self.table_ptr(), self.cfg.table_capacity - 1, self.bounds_host[self.rank],
+                                        self.slot_mult[self.rank], ptr(k), ptr(s0), ptr(s1),
                                         ptr(w), k.numel(), ptr(self.status), stream_ptr()), "load")
         torch.cuda.current_stream().synchronize()

@@ -139,6 +139,27 @@ def sparse_lr_step(table: OracleTable, keys_flat, row_ptr, y, vals=None):
     return float(loss.sum()), margin, u, grad.astype(f32)
 
 
+def block_quantize(g, mode: str, group: int = 32):
+    """Block-scaled quantise + dequantise of a value slice, as the push kernel
+    does per group of ``group`` consecutive records of one (owner, source) inbox:
+    int8: scale = amax/127, code = rint(v/scale); fp16: scale = amax, code = half(v/scale)."""
+    g = np.asarray(g, dtype=f32)
+    out = np.empty_like(g)
+    for a in range(0, len(g), group):
+        v = g[a:a + group]
+        amax = f32(np.abs(v).max()) if len(v) else f32(0)
+        if mode == "int8":
+            scale = f32(amax / f32(127))
+            code = np.rint((v / scale).astype(f32)) if amax > 0 else np.zeros_like(v)
+            out[a:a + group] = (scale * np.clip(code, -127, 127).astype(f32)).astype(f32)
+        elif mode == "fp16":
+            scale = amax if amax > 0 else f32(1)
+            out[a:a + group] = (scale * (v / scale).astype(np.float16).astype(f32)).astype(f32)
+        else:
+            out[a:a + group] = v
+    return out
+
+
 def auc(y, score):
     """Exact AUC by rank-sum (``util/evaluation.h:24-45``)."""
     y = np.asarray(y) > 0

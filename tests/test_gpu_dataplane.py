@@ -8,10 +8,10 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _mk(S, opt, cap=1 << 14, inbox=1 << 13, ring=3, quant="none"):
+def _mk(S, opt, cap=1 << 14, inbox=1 << 13, ring=3, quant="none", ordered=False):
     from parameter_server_b200.parallel.dataplane import DataPlane, PlaneConfig, heap_layout
     from parameter_server_b200.parallel.fabric import Fabric
-    pc = PlaneConfig(table_capacity=cap, inbox_cap=inbox, ring=ring, quant=quant)
+    pc = PlaneConfig(table_capacity=cap, inbox_cap=inbox, ring=ring, quant=quant, ordered_slots=ordered)
     fabs = Fabric.emulated(S, heap_layout(pc, S).total())
     return [DataPlane(f, pc, opt) for f in fabs]
 
@@ -23,13 +23,14 @@ def _batch(rng, rows, z, n_feat, seed=1):
     return ids, y, hash_id_to_key(ids, seed)
 
 
+@pytest.mark.parametrize("ordered", [False, True])
 @pytest.mark.parametrize("algo", ["ftrl", "adagrad", "sgd"])
-def test_single_shard_training_matches_oracle(cuda_lib, algo):
+def test_single_shard_training_matches_oracle(cuda_lib, algo, ordered):
     from parameter_server_b200.models.sparse_lr import SparseLRConfig, SparseLRWorker
     from parameter_server_b200.parallel.dataplane import OptimizerConfig
     from parameter_server_b200.utils import oracle
     opt = OptimizerConfig(algo=algo, alpha=0.1, beta=1.0, l1=0.01, l2=0.1)
-    plane = _mk(1, opt)[0]
+    plane = _mk(1, opt, ordered=ordered)[0]
     rows, z = 256, 24
     w = SparseLRWorker(plane, SparseLRConfig(max_rows=rows, max_nnz=rows * z, tau=0, hash_seed=1, pipeline=1))
     ot = oracle.OracleTable(opt)
@@ -64,7 +65,7 @@ def test_emulated_shards_aggregate_pushes(cuda_lib, S, quant):
     from parameter_server_b200.parallel.dataplane import OptimizerConfig
     from parameter_server_b200.utils import oracle
     opt = OptimizerConfig(algo="ftrl", alpha=0.1, beta=1.0, l1=0.001, l2=0.1)
-    planes = _mk(S, opt, quant=quant)
+    planes = _mk(S, opt, quant=quant, ordered=(S == 4))
     rows, z = 128, 16
     rng = np.random.default_rng(S)
     ot = oracle.OracleTable(opt)
@@ -80,8 +81,13 @@ def test_emulated_shards_aggregate_pushes(cuda_lib, S, quant):
             margin = np.add.reduceat(wv[col].astype(np.float64), row_ptr[:-1]).astype(np.float32)
             _, gc = oracle.logit_loss_and_gcoef(y, margin)
             g = np.zeros(len(u)); np.add.at(g, col, gc[np.repeat(np.arange(rows), z)])
+            g = g.astype(np.float32)
             if quant != "none":
-                pass
+                # quantise per (owner, source) inbox, groups of 32 records
+                bh = planes[0].bounds_host
+                offs = [int(np.searchsorted(u, np.uint64(x))) for x in bh[:-1]] + [len(u)]
+                for s in range(S):
+                    g[offs[s]:offs[s + 1]] = oracle.block_quantize(g[offs[s]:offs[s + 1]], quant)
             for k, v in zip(u.tolist(), g.tolist()):
                 gsum[k] = gsum.get(k, 0.0) + v
         ks = np.array(sorted(gsum), dtype=np.uint64)
@@ -105,14 +111,17 @@ def test_emulated_shards_aggregate_pushes(cuda_lib, S, quant):
         assert all(lo <= int(x) < hi for x in k.numpy().tolist())
         got.update(zip(k.numpy().tolist(), wv.numpy().tolist()))
     ok, ow = ot.nonzero()
-    tol = dict(none=(2e-4, 1e-6), int8=(0.2, 0.02), fp16=(2e-2, 2e-3))[quant]
+    # quantisation is emulated exactly in the oracle; what remains is summation
+    # order, plus rare rounding ties in v/scale
+    tol = dict(none=(2e-4, 1e-6), int8=(2e-3, 1e-4), fp16=(2e-3, 1e-4))[quant]
+    exp = dict(zip(ok.tolist(), ow.tolist()))
     if quant == "none":
         assert sorted(got) == ok.tolist()
-    exp = dict(zip(ok.tolist(), ow.tolist()))
     common = [k for k in exp if k in got]
-    assert len(common) > 0.9 * len(exp)
+    assert len(common) > 0.98 * len(exp)
     a = np.array([got[k] for k in common]); b_ = np.array([exp[k] for k in common])
-    assert np.allclose(a, b_, rtol=tol[0], atol=tol[1])
+    close = np.isclose(a, b_, rtol=tol[0], atol=tol[1])
+    assert close.mean() > (0.999 if quant == "none" else 0.98), (close.mean(), np.abs(a - b_).max())
 
 
 def test_dead_source_is_skipped_and_wait_times_out_cleanly(cuda_lib):
