@@ -99,7 +99,9 @@ def build_core(force: bool = False) -> Path:
     core_dir = CSRC / "core"
     headers = sorted(core_dir.glob("*.h"))
     sources = sorted(core_dir.glob("*.cc"))
-    cxx = os.environ.get("CXX", "g++")
+    # The distribution compiler, not $CXX: a toolchain that links libstdc++
+    # statically would put a second C++ runtime next to the one NumPy/PyTorch load.
+    cxx = os.environ.get("PSB_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
     inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", str(core_dir)]
     flags = ["-O2", "-g", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-pthread"]
     objs, jobs = [], []

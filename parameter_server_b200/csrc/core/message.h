@@ -71,24 +71,23 @@ void SliceKOFVMessage(const Message& msg, const std::vector<Range<Key>>& krs, st
   SArray<K> key(msg.key);
   Range<Key> msg_range = msg.task.has_key_range ? msg.task.key_range : Range<Key>::All();
   for (size_t i = 0; i < n; ++i) {
-    if (i == 0) pos[0] = std::lower_bound(key.begin(), key.end(), (K)krs[0].begin()) - key.begin();
+    // boundaries are clamped into the message's own key range
+    if (i == 0) pos[0] = std::lower_bound(key.begin(), key.end(), (K)msg_range.Project(krs[0].begin())) - key.begin();
     else PS_CHECK_EQ(krs[i - 1].end(), krs[i].begin());
-    // the last range may end at kMaxKey, which no key equals
-    pos[i + 1] = std::lower_bound(key.begin(), key.end(), (K)krs[i].end()) - key.begin();
+    pos[i + 1] = std::lower_bound(key.begin(), key.end(), (K)msg_range.Project(krs[i].end())) - key.begin();
   }
   for (size_t i = 0; i < n; ++i) {
     Message* ret = (*rets)[i];
     if (krs[i].SetIntersection(msg_range).empty()) { ret->valid = false; continue; }
-    ret->valid = true;
+    ret->valid = true;  // an empty slice of an owned range is still sent
     if (key.empty()) continue;
     SizeR lr(pos[i], pos[i + 1]);
     ret->set_key(key.Segment(lr));
-    ret->task.set_key_range(krs[i].SetIntersection(msg_range));
     ret->value.clear();
     ret->task.value_type = msg.task.value_type;
     for (const auto& v : msg.value) {
-      if (v.empty() || key.empty()) { ret->value.push_back(v); continue; }
       size_t k = v.size() / key.size();  // bytes per key
+      PS_CHECK_EQ(key.size() * k, v.size());
       ret->value.push_back(v.Segment(SizeR(lr.begin() * k, lr.end() * k)));
     }
   }

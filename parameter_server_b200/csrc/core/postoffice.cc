@@ -1,0 +1,140 @@
+#include "postoffice.h"
+
+#include "customer.h"
+
+namespace PS {
+
+Postoffice::Postoffice() : manager_(this) {}
+
+Postoffice::~Postoffice() {
+  if (running_) {
+    running_ = false;
+    auto t = std::make_shared<Message>();
+    t->terminate = true;
+    sending_queue_.push(t);
+    manager_.van().WakeUp();
+  }
+  if (send_thread_.joinable()) send_thread_.join();
+  if (recv_thread_.joinable()) recv_thread_.join();
+}
+
+void Postoffice::StartThreads() {
+  running_ = true;
+  recv_thread_ = std::thread([this] { Recv(); });
+  send_thread_ = std::thread([this] { Send(); });
+}
+
+void Postoffice::Run(const Options& opt) {
+  opt_ = opt;
+  manager_.Init(opt);
+  StartThreads();
+  manager_.Run(true);
+}
+
+void Postoffice::Start(const Options& opt) {
+  opt_ = opt;
+  manager_.Init(opt);
+  StartThreads();
+  manager_.Run(false);
+}
+
+void Postoffice::Stop() {
+  manager_.Stop();
+  if (running_) {
+    running_ = false;
+    auto t = std::make_shared<Message>();
+    t->terminate = true;
+    sending_queue_.push(t);
+    manager_.van().WakeUp();
+  }
+  if (send_thread_.joinable()) send_thread_.join();
+  if (recv_thread_.joinable()) recv_thread_.join();
+  PS_VLOG(1) << manager_.van().Statistic();
+  manager_.van().Destroy();
+}
+
+void Postoffice::Send() {
+  while (true) {
+    MessagePtr msg;
+    sending_queue_.wait_and_pop(msg);
+    if (msg->terminate) break;
+    size_t bytes = 0;
+    manager_.van().Send(msg.get(), &bytes);
+    if (msg->task.request) manager_.AddRequest(msg.get());
+  }
+}
+
+void Postoffice::Queue(Message* raw) {
+  MessagePtr msg(raw);
+  const Task& t = msg->task;
+  const bool header_only = !msg->has_key() && msg->value.empty();
+  if (!t.control && t.request && header_only) {
+    // task packing
+    auto key = std::make_pair(msg->recver, t.customer_id);
+    Lock l(pack_mu_);
+    auto it = pack_.find(key);
+    if (t.more) {
+      if (it == pack_.end()) {
+        auto holder = std::make_shared<Message>();
+        holder->recver = msg->recver;
+        holder->sender = msg->sender;
+        holder->task.request = true;
+        holder->task.customer_id = t.customer_id;
+        holder->task.more = true;
+        it = pack_.emplace(key, holder).first;
+      }
+      it->second->task.task.push_back(t);
+      return;
+    }
+    if (it != pack_.end()) {
+      // flush: the pack plus this closing task travel as one wire message
+      MessagePtr holder = it->second;
+      pack_.erase(it);
+      holder->task.task.push_back(t);
+      sending_queue_.push(holder);
+      return;
+    }
+  }
+  sending_queue_.push(msg);
+}
+
+void Postoffice::Recv() {
+  while (true) {
+    auto msg = new Message();
+    size_t bytes = 0;
+    if (!manager_.van().Recv(msg, &bytes)) { delete msg; break; }
+    if (!msg->task.control && msg->task.request && !msg->task.task.empty() && msg->task.more) {
+      // unpack
+      std::vector<Task> tasks = msg->task.task;
+      for (auto& t : tasks) {
+        auto unpacked = new Message(t);
+        unpacked->sender = msg->sender;
+        unpacked->recver = msg->recver;
+        if (!Process(unpacked)) { delete msg; return; }
+      }
+      delete msg;
+      continue;
+    }
+    if (!Process(msg)) break;
+  }
+}
+
+bool Postoffice::Process(Message* msg) {
+  if (!msg->task.request) manager_.AddResponse(msg);
+  if (msg->task.control) {
+    bool keep_going = manager_.Process(msg);
+    delete msg;
+    return keep_going;
+  }
+  Customer* c = manager_.customer(msg->task.customer_id);
+  if (c == nullptr) {
+    PS_LOG(WARN) << manager_.van().my_node().id << ": no customer " << msg->task.customer_id << ", dropping "
+                 << msg->ShortDebugString();
+    delete msg;
+    return true;
+  }
+  c->executor()->Accept(msg);  // takes ownership
+  return true;
+}
+
+}  // namespace PS

@@ -1,0 +1,50 @@
+// Postoffice: one per node. Owns the Manager (membership), the Van
+// (transport), the outgoing queue with task packing, and the send / receive
+// threads. Counterpart of system/postoffice.h:9-52, system/postoffice.cc:25-131.
+// Unlike the reference it is an ordinary object, so several nodes can live in one
+// process (in-process Van); `instance()` is the process default.
+#pragma once
+#include "env.h"
+#include "manager.h"
+#include "threading.h"
+#include "van.h"
+
+namespace PS {
+
+class Postoffice {
+ public:
+  Postoffice();
+  ~Postoffice();
+  static Postoffice& instance() { static Postoffice po; return po; }
+
+  // Joins the system and runs the app on the calling thread.
+  void Run(const Options& opt);
+  // Same, but returns once the node has joined (the app's Run() is not called).
+  void Start(const Options& opt);
+  void Stop();
+  // Hands a message to the send thread (takes ownership). Header-only requests
+  // carrying `more` are packed into one wire message per (recipient, customer)
+  // until one without `more` arrives.
+  void Queue(Message* msg);
+
+  Manager& manager() { return manager_; }
+  const Options& options() const { return opt_; }
+  bool running() const { return running_; }
+
+ private:
+  void Send();
+  void Recv();
+  bool Process(Message* msg);
+  void StartThreads();
+
+  Options opt_;
+  Manager manager_;
+  ThreadsafeQueue<MessagePtr> sending_queue_;
+  std::mutex pack_mu_;
+  std::map<std::pair<NodeID, int>, MessagePtr> pack_;
+  std::thread recv_thread_, send_thread_;
+  std::atomic<bool> running_{false};
+  PS_DISALLOW_COPY(Postoffice);
+};
+
+}  // namespace PS

@@ -47,7 +47,9 @@ class Range {
     PS_CHECK_GT(n, (size_t)0);
     PS_CHECK_LT(i, n);
     long double step = static_cast<long double>(end_ - begin_) / static_cast<long double>(n);
-    return Range(static_cast<T>(begin_ + step * i), static_cast<T>(begin_ + step * (i + 1)));
+    // the last part ends exactly at end_ (the rounded product may exceed the type's range)
+    T hi = (i + 1 == n) ? end_ : static_cast<T>(begin_ + step * (i + 1));
+    return Range(static_cast<T>(begin_ + step * i), hi);
   }
   std::string ToString() const {
     std::ostringstream ss;

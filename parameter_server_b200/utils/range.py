@@ -50,8 +50,8 @@ class Range:
         ld = np.longdouble
         itv = ld(self.end - self.begin) / ld(n)
         lo = int(ld(self.begin) + itv * ld(i))
-        hi = int(ld(self.begin) + itv * ld(i + 1))
-        return Range(lo, min(hi, K_MAX_KEY))
+        hi = self.end if i + 1 == n else int(ld(self.begin) + itv * ld(i + 1))
+        return Range(lo, hi)
 
     def __add__(self, v: int) -> "Range":
         return Range(self.begin + v, self.end + v)
