@@ -114,8 +114,15 @@ def build_core(force: bool = False) -> Path:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(lambda j: _run(*j), jobs))
     out = core_lib_path()
-    if force or jobs or _newer(objs, out):
-        _run([cxx, "-shared", "-pthread", "-o", str(out), *map(str, objs), "-lz"])
+    lib_objs = [o for o in objs if not o.name.endswith("_main.o")]
+    if force or jobs or _newer(lib_objs, out):
+        _run([cxx, "-shared", "-pthread", "-o", str(out), *map(str, lib_objs), "-lz"])
+    # the stand-alone linear-method binary (every node of a CPU deployment runs it)
+    exe = PKG / "bin" / "psb_linear"
+    exe.parent.mkdir(exist_ok=True)
+    exe_objs = [o for o in objs if not o.name.startswith("core_bind") and o.name != "core_ps_main.o"]
+    if force or jobs or _newer(exe_objs, exe):
+        _run([cxx, "-pthread", "-o", str(exe), *map(str, exe_objs), "-lz"])
     return out
 
 

@@ -257,6 +257,7 @@ void BindSystem(py::module& m) {
 
   py::class_<App, Customer, PyApp> app(m, "App");
   app.def(py::init<Postoffice*, int>(), py::arg("po") = nullptr, py::arg("id") = 0, py::keep_alive<1, 2>());
+  app.def("run", [](App& a) { a.App::Run(); }, py::call_guard<py::gil_scoped_release>());
   m.def("set_app_factory", [](py::function f) {
     auto holder = std::make_shared<py::object>(f);
     App::external_ownership() = true;

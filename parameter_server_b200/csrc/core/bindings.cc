@@ -4,6 +4,7 @@
 namespace PS {
 void BindSystem(py::module& m);
 void BindUtil(py::module& m);
+void BindApp(py::module& m);
 }  // namespace PS
 
 PYBIND11_MODULE(_core, m) {
@@ -11,4 +12,5 @@ PYBIND11_MODULE(_core, m) {
   py::register_exception<PS::CheckError>(m, "CheckError");
   PS::BindSystem(m);
   PS::BindUtil(m);
+  PS::BindApp(m);
 }

@@ -206,7 +206,13 @@ void Executor::Run() {
       dag_cond_.wait(l, [this] { return done_ || PickActiveMsg(); });
       if (done_) break;
     }
-    ProcessActiveMsg();
+    try {
+      ProcessActiveMsg();
+    } catch (const std::exception& e) {
+      // an application error must not take the node's other customers down silently
+      PS_LOG(ERROR) << my_node_.id << " customer " << obj_.id() << ": " << e.what();
+      if (getenv("PSB_ABORT_ON_ERROR")) abort();
+    }
   }
 }
 

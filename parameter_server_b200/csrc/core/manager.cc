@@ -183,6 +183,7 @@ void Manager::AddNode(const Node& node) {
       ++num_active_nodes_;
     }
   }
+  if (node.id == my_node().id) van_.UpdateMyNode(node);
   van_.Connect(node);
   {
     Lock l(customer_mu_);

@@ -86,6 +86,8 @@ class KVVector : public Parameter {
     PS_CHECK_GT(k, 0);
   }
   virtual ~KVVector() {}
+  using Parameter::Push;
+  using Parameter::Pull;
 
   struct KVPairs {
     SArray<K> key;    // sorted, unique

@@ -39,6 +39,8 @@ class Van {
   void WakeUp();
 
   const Node& my_node() const { return my_node_; }
+  // the scheduler assigns rank and key range after registration
+  void UpdateMyNode(const Node& n) { my_node_.rank = n.rank; my_node_.key = n.key; }
   const Node& scheduler() const { return scheduler_; }
   void set_disconnect_handler(DisconnectHandler h) { on_disconnect_ = std::move(h); }
   // "sent x MB (y local), received ..." summary, as printed at exit

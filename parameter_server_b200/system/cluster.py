@@ -30,14 +30,21 @@ class LocalCluster:
     postoffice ``po`` (look at ``po.my_node().role``).
     """
 
-    def __init__(self, num_servers: int, num_workers: int, factory: Callable, conf: str = "",
-                 key_start: int = 0, key_end: Optional[int] = None):
+    def __init__(self, num_servers: int, num_workers: int, factory: Optional[Callable], conf: str = "",
+                 key_start: int = 0, key_end: Optional[int] = None, run: bool = False, num_threads: int = 2):
+        """``factory=None`` selects the C++ linear-method applications (from ``conf``).
+        With ``run=True`` every node also runs its app's ``Run()`` (the scheduler's
+        returns when the job is done); call :meth:`join` to wait for it."""
         from . import core
         self.core = core
+        self._run = run
         with _lock:
             _counter[0] += 1
             base = _counter[0] * 1000
-        core.set_app_factory(factory)
+        if factory is None:
+            core.use_linear_method_factory()
+        else:
+            core.set_app_factory(factory)
         sched = node_string("SCHEDULER", "inproc", base, "H")
         specs = [("H", sched)]
         specs += [(f"S{i}", node_string("SERVER", "inproc", base + 1 + i, f"S{i}")) for i in range(num_servers)]
@@ -51,11 +58,16 @@ class LocalCluster:
             opt.num_servers, opt.num_workers = num_servers, num_workers
             opt.my_node, opt.scheduler, opt.app_conf = spec, sched, conf
             opt.exit_on_scheduler_loss = False
+            opt.num_threads = num_threads
             if key_end is not None:
                 opt.key_start, opt.key_end = key_start, key_end
             self.nodes[nid] = po
             t = threading.Thread(target=self._start, args=(po, opt), name=f"ps-{nid}", daemon=True)
             self._threads.append(t)
+        if run:
+            for t in self._threads:
+                t.start()
+            return
         # the scheduler first: everybody connects to it
         self._threads[0].start()
         self._threads[0].join()
@@ -71,9 +83,19 @@ class LocalCluster:
 
     def _start(self, po, opt):
         try:
-            po.start(opt)
+            if self._run:
+                po.run(opt)
+            else:
+                po.start(opt)
         except BaseException as e:  # noqa: BLE001
             self._errors.append(e)
+
+    def join(self, timeout: Optional[float] = None):
+        """Wait until every node's ``Run()`` has returned (``run=True``)."""
+        for t in self._threads:
+            t.join(timeout)
+        if self._errors:
+            raise self._errors[0]
 
     def app(self, node_id: str):
         return self.nodes[node_id].app()
