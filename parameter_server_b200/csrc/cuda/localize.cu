@@ -203,3 +203,69 @@ extern "C" int psb_localize(const psb_u64* sorted_keys, uint32_t* sorted_pos, ui
   k_owner_offsets<<<1, 96, 0, stream>>>(ukeys, n_unique, bounds, S, n, seg_off, own_off);
   return -(int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant (declared in psb_noalloc.h; nothing like it exists in
+// the reference). The per-tile head counts, which psb_localize keeps in a
+// caller-provided scratch buffer, live in this fixed device array instead.
+#include <mutex>
+#include "psb_noalloc.h"
+
+static __device__ __align__(256) unsigned int g_localize_static_scratch[PSB_LOCALIZE_STATIC_SCRATCH_WORDS];
+
+namespace {
+// In host code the array's name is only a handle for the runtime, not an
+// address a kernel can use; the device address is looked up once per device,
+// with that device current.
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {nullptr};
+
+int localize_static_scratch(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return -(int)e;
+  if (dev < 0 || dev >= kMaxDevices) return -(int)cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_localize_static_scratch);
+    if (e != cudaSuccess) return -(int)e;
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int psb_localize_static(const psb_u64* sorted_keys, uint32_t* sorted_pos, uint32_t n,
+                                   const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z,
+                                   const float* vals, const psb_u64* bounds, int S, psb_u64* ukeys,
+                                   uint32_t* seg_off, uint32_t* csr_col, float* csc_val,
+                                   uint32_t* flagbits, uint32_t* wordbase, uint32_t* n_unique,
+                                   uint32_t* own_off, cudaStream_t stream) {
+  if (n > PSB_LOCALIZE_STATIC_MAX_N) return -(int)cudaErrorInvalidValue;  // beyond the built-in scratch
+  if (S < 1 || S > 64) return -(int)cudaErrorInvalidValue;
+  if (row_ptr == nullptr && fixed_z == 0) return -(int)cudaErrorInvalidValue;
+  void* scratch = nullptr;
+  int rc = localize_static_scratch(&scratch);
+  if (rc != 0) return rc;
+  u32* tile_heads = (u32*)scratch;
+  if (n == 0) {
+    cudaMemsetAsync(n_unique, 0, sizeof(u32), stream);
+    cudaMemsetAsync(own_off, 0, sizeof(u32) * (S + 1), stream);
+    cudaMemsetAsync(seg_off, 0, sizeof(u32), stream);
+    return -(int)cudaGetLastError();
+  }
+  const u32 ntiles = (n + kLocTile - 1) / kLocTile;
+  // every tile_heads word that the scan and the emit kernel read is written by
+  // k_uniq_count first, so the array needs no clearing between calls
+  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, n, tile_heads);
+  k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique);
+  k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, sorted_pos, n, tile_heads,
+                                                  row_ptr, n_rows, fixed_z, vals, (u64*)ukeys, seg_off,
+                                                  csr_col, csc_val, flagbits, wordbase);
+  k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off,
+                                        own_off);
+  return -(int)cudaGetLastError();
+}
