@@ -159,9 +159,25 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    nccl = None
+    if args.impl == "nccl":
+        assert world > 1, "--impl nccl needs at least two ranks"
+        from parameter_server_b200.parallel.nccl_baseline import NcclPushPull
+        nccl = NcclPushPull(plane, nnz)
+
     def run(pool, n, log=None):
         for i in range(n):
             ids, y = pool[i % len(pool)]
+            if nccl is not None:
+                # baseline arm: same kernels, NCCL all-to-all-v for everything that crosses GPUs
+                ids_d = ids if ids.is_cuda else ids.to(dev, non_blocking=True)
+                y_d = y if y.is_cuda else y.to(dev, non_blocking=True)
+                b = worker.prepare(ids_d, y_d, fixed_z=z)
+                nccl.step(b, worker.step_no)
+                worker.step_no += 1
+                if log is not None:
+                    log[i].copy_(plane.pull_stats, non_blocking=True)
+                continue
             worker.submit(ids, y, fixed_z=z)
             if log is not None:
                 # D2H read of this step's running loss/accuracy counters (async, pinned)

@@ -72,6 +72,9 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     cu_dir = CSRC / "cuda"
     headers = sorted(cu_dir.glob("*.cuh")) + sorted(cu_dir.glob("*.h"))
     sources = sorted(cu_dir.glob("*.cu"))
+    out = cuda_lib_path()
+    if not force and not _newer(sources + headers, out):
+        return out  # the shipped library is current (e.g. on a box that received only the .so)
     nvcc = _nvcc()
     objs, jobs = [], []
     for src in sources:
@@ -101,6 +104,10 @@ def build_core(force: bool = False) -> Path:
     sources = sorted(core_dir.glob("*.cc"))
     # The distribution compiler, not $CXX: a toolchain that links libstdc++
     # statically would put a second C++ runtime next to the one NumPy/PyTorch load.
+    out = core_lib_path()
+    exe = PKG / "bin" / "psb_linear"
+    if not force and not _newer(sources + headers, out) and exe.exists() and not _newer(sources + headers, exe):
+        return out
     cxx = os.environ.get("PSB_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
     inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", str(core_dir)]
     flags = ["-O2", "-g", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-pthread"]

@@ -44,7 +44,7 @@ typedef struct {
 // What a worker needs to pull from S shards and compute margins (kernel F2).
 typedef struct {
   int S;
-  int insert;                 // insert absent keys on pull (KVMap first-touch semantics)
+  int insert;                 // 1: insert absent keys on pull (KVMap first touch); 2: skip the gather (w_local given)
   void* table[PSB_MAX_SHARDS];            // Entry* of shard s (local or peer-mapped)
   psb_u64 mask[PSB_MAX_SHARDS];          // capacity-1 of shard s
   psb_u64 key_begin[PSB_MAX_SHARDS];     // first key of shard s's range

@@ -155,13 +155,17 @@ __global__ void __launch_bounds__(kThreads) k_pull_margin(const PsbPullParams p)
   const u32 gsize = gridDim.x * blockDim.x;
   const u32 gtid = blockIdx.x * blockDim.x + threadIdx.x;
   // phase 1: gather one weight per unique key from its owner's table
+  // (insert == 2: w_local was filled by someone else, e.g. a collective; only clear grad)
+  if (p.insert == 2) {
+    if (p.grad_zero) for (u32 u = gtid; u < U; u += gsize) p.grad_zero[u] = 0.f;
+  } else
   for (u32 u = gtid; u < U; u += gsize) {
     int s = owner_of(s_off, S, u);
     u64 key = p.ukeys[u];
     float w;
     long long slot;
     const SlotMap sm{p.mask[s], p.key_begin[s], p.slot_mult[s]};
-    if (p.insert) {
+    if (p.insert == 1) {
       slot = table_find<true>((Entry*)p.table[s], sm, key, kMaxProbe);
       w = 0.f;
       if (slot >= 0) {

@@ -1,0 +1,125 @@
+"""NCCL all-to-all-v push/pull: the baseline the fused kernels are measured against.
+
+Same minibatch pipeline and the same local kernels (sort/localise, table gather,
+margins, X^T g, optimiser), but every byte that crosses GPUs goes through
+``torch.distributed.all_to_all_single`` with split sizes, as a conventional
+implementation would do it:
+
+    counts exchange (+ host sync for the split sizes)
+    pull : keys -> owners | local table gather | values -> workers
+    push : values -> owners (keys are reused from the pull) | local apply
+
+This path is a baseline, not the product.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops._lib import ApplyParams, PullParams, PushParams, check, ptr, stream_ptr
+from .dataplane import DataPlane
+
+
+class NcclPushPull:
+    def __init__(self, plane: DataPlane, max_unique: int, group=None):
+        self.plane, self.group = plane, group
+        self.S, self.rank = plane.S, plane.rank
+        dev = plane.device
+        self.dev = dev
+        cap = max_unique * 2 + 1024
+        self.cap = cap
+        i32, i64, f32 = torch.int32, torch.int64, torch.float32
+        self.send_counts = torch.zeros(self.S, dtype=i64, device=dev)
+        self.recv_counts = torch.zeros(self.S, dtype=i64, device=dev)
+        self.rkeys = torch.empty(cap, dtype=i64, device=dev)      # keys received as an owner
+        self.rvals = torch.empty(cap, dtype=f32, device=dev)      # weights gathered for the requesters
+        self.rgrad = torch.empty(cap, dtype=f32, device=dev)      # gradients received as an owner
+        self.stage = torch.empty(max_unique, dtype=f32, device=dev)
+        self.stage_keys = torch.empty(max_unique, dtype=i64, device=dev)
+        self.counts32 = torch.zeros(self.S, dtype=i32, device=dev)
+        self.ready = torch.full((self.S,), 0x7FFFFFF0, dtype=i32, device=dev)
+        self.dummy = torch.zeros(4 * self.S + 8, dtype=i32, device=dev)
+        self.one_off = torch.zeros(2, dtype=i32, device=dev)
+        self.n_recv = torch.zeros(1, dtype=i32, device=dev)
+        self.slot_cache = torch.zeros(cap, dtype=i32, device=dev)
+        self.collectives = 0
+
+    def step(self, b, t: int, loss: int = 0):
+        """One minibatch (already localised into ``b``) through NCCL push/pull."""
+        p, S, L = self.plane, self.S, _lib.lib()
+        sp = stream_ptr()
+        # ---- split sizes (device -> host: the all-to-all-v needs them on the host)
+        self.send_counts.copy_((b.own_off[1:] - b.own_off[:-1]).to(torch.int64))
+        dist.all_to_all_single(self.recv_counts, self.send_counts, group=self.group)
+        sc = self.send_counts.tolist()
+        rc = self.recv_counts.tolist()
+        U, R = sum(sc), sum(rc)
+        assert R <= self.cap
+        # ---- pull: keys to the owners
+        dist.all_to_all_single(self.rkeys[:R], b.ukeys[:U], rc, sc, group=self.group)
+        # owner: gather from the local table
+        self.n_recv.fill_(R)
+        self.one_off.copy_(torch.tensor([0, R], dtype=torch.int32))
+        g = PullParams()
+        g.S, g.insert = 1, 0
+        g.table[0], g.mask[0] = p.table_ptr(), p.cfg.table_capacity - 1
+        g.key_begin[0], g.slot_mult[0] = p.bounds_host[self.rank], p.slot_mult[self.rank]
+        g.applied[0], g.need_applied = p._ctrl(self.rank, 0), 0
+        g.ukeys, g.n_unique, g.own_off = ptr(self.rkeys), ptr(self.n_recv), ptr(self.one_off)
+        g.w_local, g.n_rows = ptr(self.rvals), 0
+        g.stats, g.bar, g.status = ptr(p.pull_stats), p._bar(0), ptr(p.status)
+        check(L.psb_pull_margin(C.byref(g), sp), "gather")
+        # values back to the workers
+        dist.all_to_all_single(b.w_local[:U], self.rvals[:R], sc, rc, group=self.group)
+        # ---- margins + loss (gather skipped)
+        m = PullParams()
+        m.S, m.insert = S, 2
+        m.ukeys, m.n_unique, m.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
+        m.w_local, m.grad_zero = ptr(b.w_local), ptr(b.grad)
+        m.row_ptr, m.n_rows, m.fixed_z = ptr(b.row_ptr), b.n_rows, b.fixed_z
+        m.csr_col, m.csr_val, m.y, m.loss = ptr(b.csr_col), ptr(b.csr_val), ptr(b.y), loss
+        m.gcoef, m.margin = ptr(b.gcoef), ptr(b.margin)
+        m.stats, m.bar, m.status = ptr(p.pull_stats), p._bar(0), ptr(p.status)
+        check(L.psb_pull_margin(C.byref(m), sp), "margins")
+        # ---- X^T g into a contiguous staging buffer (same kernel, local destinations)
+        q = PushParams()
+        q.S, q.ts1, q.inbox_cap, q.quant, q.send_keys = S, t + 1, self.stage.numel(), 0, 0
+        off = 0
+        for s in range(S):
+            q.inbox_keys[s] = self.stage_keys.data_ptr() + off * 8
+            q.inbox_vals[s] = self.stage.data_ptr() + off * 4
+            q.ready[s] = self.dummy.data_ptr() + 4 * s
+            q.count[s] = self.dummy.data_ptr() + 4 * (S + s)
+            q.applied[s] = self.dummy.data_ptr()
+            off += sc[s]
+        q.need_applied = 0
+        q.ukeys, q.n_unique, q.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
+        q.nnz, q.csc_row, q.csc_val = b.nnz, ptr(b.csc_row), ptr(b.csc_val)
+        q.flagbits, q.wordbase, q.gcoef, q.grad = ptr(b.flagbits), ptr(b.wordbase), ptr(b.gcoef), ptr(b.grad)
+        q.bar, q.done, q.status = p._bar(1), p._done(1), ptr(p.status)
+        check(L.psb_push(C.byref(q), sp), "grad")
+        # ---- push: values to the owners (the owners still hold the keys of this round)
+        dist.all_to_all_single(self.rgrad[:R], self.stage[:U], rc, sc, group=self.group)
+        # ---- owner: duplicate-key reduce + optimiser on the received segments
+        self.counts32.copy_(self.recv_counts.to(torch.int32))
+        a = ApplyParams()
+        a.S, a.ts1, a.inbox_cap, a.quant = S, t + 1, self.cap, 0
+        a.table, a.mask = p.table_ptr(), p.cfg.table_capacity - 1
+        a.key_begin, a.slot_mult = p.bounds_host[self.rank], p.slot_mult[self.rank]
+        off = 0
+        for r in range(S):
+            a.inbox_keys[r] = self.rkeys.data_ptr() + off * 8
+            a.inbox_vals[r] = self.rgrad.data_ptr() + off * 4
+            a.ready[r] = self.ready.data_ptr() + 4 * r
+            a.count[r] = self.counts32.data_ptr() + 4 * r
+            a.alive[r], a.cached[r] = 1, 0
+            a.slot_cache[r] = self.slot_cache.data_ptr() + off * 4
+            off += rc[r]
+        a.opt = p.opt.to_c()
+        a.stats, a.applied = ptr(p.push_stats), p._ctrl(self.rank, 0)
+        a.bar, a.done, a.status = p._bar(2), p._done(2), ptr(p.status)
+        check(L.psb_apply(C.byref(a), sp), "apply")
+        self.collectives += 4
