@@ -98,6 +98,10 @@ def main():
     ap.add_argument("--pool", type=int, default=4, help="distinct minibatches cycled through")
     ap.add_argument("--quant", default="none")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="also time each stage (localise / pull+margins / push / apply) with CUDA events, "
+                         "stages run back to back on one stream")
+    ap.add_argument("--key-cache", action="store_true", help="enable the key-caching filter")
     ap.add_argument("--hashed-slots", action="store_true",
                     help="re-hash keys into table slots instead of the order-preserving slot map")
     args = ap.parse_args()
@@ -137,7 +141,7 @@ def main():
         cap *= 2
     inbox_cap = nnz if world == 1 else (nnz // world) * 5 // 4 + 4096
     pc = PlaneConfig(table_capacity=cap, inbox_cap=inbox_cap, ring=args.tau + 2, quant=args.quant,
-                     ordered_slots=not args.hashed_slots)
+                     ordered_slots=not args.hashed_slots, key_cache=args.key_cache)
     opt = OptimizerConfig(algo="ftrl", alpha=0.1, beta=1.0, l1=1.0, l2=0.1)
     hb = heap_layout(pc, world).total()
     fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
@@ -230,6 +234,37 @@ def main():
                "loss_per_example_last": float((log[-1, 0] - log[-2, 0]) / max(1.0, float(log[-1, 2] - log[-2, 2])))
                if args.steps > 1 else None}
 
+    breakdown = None
+    if args.breakdown and nccl is None:
+        names = ["localize", "pull_margin", "push", "apply"]
+        acc = {k: 0.0 for k in names}
+        reps = 6
+        for i in range(reps + 2):
+            ids, y = pool_d[i % len(pool_d)]
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+            sync_all()
+            ev[0].record()
+            b = worker.prepare(ids, y, fixed_z=z)
+            ev[1].record()
+            t_ = worker.step_no
+            plane.pull_margin(b, need_applied=max(0, t_ - args.tau))
+            ev[2].record()
+            plane.push(b, t_)
+            ev[3].record()
+            plane.apply(t_)
+            ev[4].record()
+            worker.step_no += 1
+            torch.cuda.synchronize()
+            if i >= 2:
+                for k, name in enumerate(names):
+                    acc[name] += ev[k].elapsed_time(ev[k + 1]) / reps
+        sync_all()
+        tb = torch.tensor([acc[k] for k in names], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tb, op=dist.ReduceOp.MAX)
+        breakdown = {k: float(v) for k, v in zip(names, tb.tolist())}
+        plane.check_status("breakdown")
+
     prog = worker.read_progress()
     if rank == 0:
         u_mean = sum(uniq) / len(uniq)
@@ -248,7 +283,7 @@ def main():
                        "push_pull_keys_per_s": 2 * u_mean * world * args.steps / (ms * 1e-3),
                        "l2_policy": f"inputs larger than L2: {args.pool} distinct minibatches of "
                                     f"{nnz * 4 / 1e6:.0f} MB ids, >=300 MB sort working set per step"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "stage_ms_max_over_ranks": breakdown,
             "progress": {"loss_per_example": prog["loss_sum"] / max(1.0, prog["n_examples"])},
         }
         print(json.dumps(out))

@@ -55,7 +55,8 @@ typedef struct {
   const uint32_t* n_unique;
   const uint32_t* own_off;
   float* w_local;             // out: weight per unique key
-  int32_t* slot_local;        // out (nullable): slot of each key in its owner's table, -1 if absent
+  int32_t* slot_local;        // in/out (nullable): slot of each key in its owner's table, -1 if absent
+  const uint32_t* key_hit;    // nullable device flag: 1 = same key list as last time, reuse slot_local
   float* grad_zero;           // nullable: zeroed per unique key (prepares the push)
   // margins (skipped when n_rows == 0)
   const uint32_t* row_ptr;    // nullable -> fixed_z nonzeros per row
@@ -79,7 +80,9 @@ typedef struct {
   uint32_t ts1;               // timestamp+1 published in the ready flags
   uint32_t inbox_cap;         // records per (owner, source) inbox
   int quant;                  // PSB_QUANT_*
-  int send_keys;              // 0 on a key-cache hit: values only
+  int send_keys;              // 0: values only (the owner reuses the slots of the previous push)
+  const uint32_t* key_hit;    // nullable device flag with the same meaning, decided on the device
+  uint32_t* mode[PSB_MAX_SHARDS];         // owner s's header word: 1 = keys omitted in this round
   psb_u64* inbox_keys[PSB_MAX_SHARDS];   // owner s's inbox for this source and ring slot
   void* inbox_vals[PSB_MAX_SHARDS];
   uint32_t* ready[PSB_MAX_SHARDS];        // owner s's ready flag for this source and ring slot
@@ -119,6 +122,7 @@ typedef struct {
   const uint32_t* count[PSB_MAX_SHARDS];
   uint8_t alive[PSB_MAX_SHARDS];          // dead sources are skipped (their waits complete)
   uint8_t cached[PSB_MAX_SHARDS];         // key-cache hit: reuse slot_cache[r], no keys sent
+  const uint32_t* mode[PSB_MAX_SHARDS];   // nullable: the source's header word (1 = keys omitted)
   uint32_t* slot_cache[PSB_MAX_SHARDS];   // per source: slot of each record (scratch + key cache)
   PsbOptimizer opt;
   double* stats;              // += {d_nnz, sum w^2, sum dw^2, n_updates}
@@ -148,6 +152,22 @@ int psb_table_export(const void* table, psb_u64 capacity, psb_u64* out_keys, flo
 // number of CTAs a cooperative launch of the three fused kernels uses
 int psb_coop_grid(int which);
 int psb_struct_size(int which);
+
+// ---------------------------------------------------------------- filters / sorted-key utilities
+int psb_key_signature(const psb_u64* keys, const uint32_t* n_ptr, uint32_t max_n, uint32_t* scratch,
+                      uint32_t* state, uint32_t* hit, uint32_t* sig_out, cudaStream_t stream);
+int psb_fixfloat_encode(const float* x, void* code, psb_u64 n, int nbytes, float lo, float hi, psb_u64 seed,
+                        cudaStream_t stream);
+int psb_fixfloat_decode(const void* code, float* x, psb_u64 n, int nbytes, float lo, float hi, cudaStream_t stream);
+int psb_minmax(const float* x, psb_u64 n, float* out, cudaStream_t stream);
+int psb_add_noise(float* x, psb_u64 n, float mean, float stdv, psb_u64 seed, cudaStream_t stream);
+int psb_countmin_insert(uint32_t* cells, uint32_t n_cells, int k, const psb_u64* keys, const unsigned char* counts,
+                        const uint32_t* n_ptr, uint32_t n, cudaStream_t stream);
+int psb_countmin_query(const uint32_t* cells, uint32_t n_cells, int k, const psb_u64* keys, unsigned char* out,
+                       const uint32_t* n_ptr, uint32_t n, cudaStream_t stream);
+int psb_ordered_match(const psb_u64* src_key, const float* src_val, uint32_t n_src, const psb_u64* dst_key,
+                      float* dst_val, uint32_t n_dst, int k, int op, unsigned long long* matched,
+                      cudaStream_t stream);
 
 // ---------------------------------------------------------------- data / misc
 int psb_gen_batch(uint32_t* ids32, psb_u64* ids64, float* vals, float* y, uint32_t n_rows,

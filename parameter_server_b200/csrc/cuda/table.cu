@@ -158,14 +158,20 @@ __global__ void __launch_bounds__(kThreads) k_pull_margin(const PsbPullParams p)
   // (insert == 2: w_local was filled by someone else, e.g. a collective; only clear grad)
   if (p.insert == 2) {
     if (p.grad_zero) for (u32 u = gtid; u < U; u += gsize) p.grad_zero[u] = 0.f;
-  } else
+  } else {
+  const bool reuse = p.key_hit && p.slot_local && *p.key_hit;
   for (u32 u = gtid; u < U; u += gsize) {
     int s = owner_of(s_off, S, u);
     u64 key = p.ukeys[u];
     float w;
     long long slot;
     const SlotMap sm{p.mask[s], p.key_begin[s], p.slot_mult[s]};
-    if (p.insert == 1) {
+    if (reuse && p.slot_local[u] >= 0) {
+      // key-cache hit: the slot found last time is still this key's slot
+      slot = p.slot_local[u];
+      asm volatile("ld.relaxed.sys.global.f32 %0, [%1];"
+                   : "=f"(w) : "l"(&((Entry*)p.table[s])[slot].w) : "memory");
+    } else if (p.insert == 1) {
       slot = table_find<true>((Entry*)p.table[s], sm, key, kMaxProbe);
       w = 0.f;
       if (slot >= 0) {
@@ -180,6 +186,7 @@ __global__ void __launch_bounds__(kThreads) k_pull_margin(const PsbPullParams p)
     p.w_local[u] = w;
     if (p.slot_local) p.slot_local[u] = (int32_t)slot;
     if (p.grad_zero) p.grad_zero[u] = 0.f;
+  }
   }
   if (p.n_rows == 0) return;
   if (!grid_barrier(p.bar, p.status)) return;
@@ -295,6 +302,7 @@ __global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
   }
 
   // phase 2: range partition + (quantise) + peer stores, 32 records per warp step
+  const bool omit_keys = !p.send_keys || (p.key_hit && *p.key_hit);
   const u32 G = s_gp[S];
   for (u32 g = gwarp; g < G; g += nwarps) {
     int s = 0;
@@ -304,7 +312,7 @@ __global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
     bool valid = j < cnt;
     u32 u = s_off[s] + j;
     float v = valid ? __ldcg(&p.grad[u]) : 0.f;
-    if (p.send_keys && valid) p.inbox_keys[s][j] = p.ukeys[u];
+    if (!omit_keys && valid) p.inbox_keys[s][j] = p.ukeys[u];
     if (p.quant == PSB_QUANT_NONE) {
       if (valid) ((float*)p.inbox_vals[s])[j] = v;
     } else {
@@ -337,6 +345,7 @@ __global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
     int s = threadIdx.x;
     __threadfence_system();
     *p.count[s] = min(s_off[s + 1] - s_off[s], p.inbox_cap);
+    if (p.mode[s]) *p.mode[s] = omit_keys ? 1u : 0u;
     __threadfence_system();
     st_release_sys(p.ready[s], p.ts1);
     if (s == 0) atomicExch(p.done, 0u);
@@ -355,6 +364,7 @@ __device__ __forceinline__ float inbox_value(const void* vals, int quant, u32 ca
 
 __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
   __shared__ u32 s_pre[PSB_MAX_SHARDS + 1];
+  __shared__ u32 s_cached[PSB_MAX_SHARDS];
   __shared__ u32 s_last;
   const int S = p.S;
   Entry* tab = (Entry*)p.table;
@@ -363,12 +373,14 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
     const u32 iters = p.wait_iters ? p.wait_iters : kPeerWaitIters;
     for (int r = 0; r < S; ++r) {
       s_pre[r] = acc;
+      s_cached[r] = p.cached[r];
       if (!p.alive[r]) continue;
       if (!wait_flag_ge_sys(p.ready[r], p.ts1, iters)) {
         set_status(p.status, kWaitTimeout);
         continue;
       }
       u32 c = *((volatile const u32*)p.count[r]);
+      if (p.mode[r] && *((volatile const u32*)p.mode[r])) s_cached[r] = 1;
       acc += min(c, p.inbox_cap);
     }
     s_pre[S] = acc;
@@ -391,8 +403,9 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
     u32 j = i - s_pre[r];
     float g = inbox_value(p.inbox_vals[r], p.quant, p.inbox_cap, j);
     long long slot;
-    if (p.cached[r]) {
+    if (s_cached[r]) {
       slot = p.slot_cache[r][j] & 0x7fffffffu;
+      if (slot == 0x7fffffffu) continue;
     } else {
       slot = table_find<true>(tab, sm, p.inbox_keys[r][j], kMaxProbe);
       if (slot < 0) { set_status(p.status, kTableFull); if (p.slot_cache[r]) p.slot_cache[r][j] = 0x7fffffffu; continue; }

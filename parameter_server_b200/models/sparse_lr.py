@@ -71,6 +71,8 @@ class SparseLRWorker:
         """Pull + margins, push, apply for a localised batch (round = step number)."""
         t = self.step_no
         need = max(0, t - self.cfg.tau)
+        if self.plane.cfg.key_cache:
+            self.plane.key_signature(b, stream=stream)
         self.plane.pull_margin(b, need_applied=need, loss=self.loss_code, auc_hist=self.auc_hist, stream=stream)
         self.plane.push(b, t, stream=stream)
         self.plane.apply(t, stream=server_stream if server_stream is not None else stream)
@@ -114,6 +116,8 @@ class SparseLRWorker:
         self.main_stream.wait_event(self._prep_done[k])
         t = self.step_no
         need = max(0, t - self.cfg.tau)
+        if self.plane.cfg.key_cache:
+            self.plane.key_signature(b, stream=self.main_stream)
         self.plane.pull_margin(b, need_applied=need, loss=self.loss_code, auc_hist=self.auc_hist,
                                stream=self.main_stream)
         self.plane.push(b, t, stream=self.main_stream)

@@ -42,7 +42,7 @@ class PullParams(C.Structure):
         ("key_begin", _u64 * MAX_SHARDS), ("slot_mult", _u64 * MAX_SHARDS), ("applied", _vp * MAX_SHARDS),
         ("need_applied", _u32),
         ("ukeys", _vp), ("n_unique", _vp), ("own_off", _vp),
-        ("w_local", _vp), ("slot_local", _vp), ("grad_zero", _vp),
+        ("w_local", _vp), ("slot_local", _vp), ("key_hit", _vp), ("grad_zero", _vp),
         ("row_ptr", _vp), ("n_rows", _u32), ("fixed_z", _u32),
         ("csr_col", _vp), ("csr_val", _vp), ("y", _vp), ("loss", _i32),
         ("gcoef", _vp), ("margin", _vp), ("stats", _vp), ("auc_hist", _vp),
@@ -53,6 +53,7 @@ class PullParams(C.Structure):
 class PushParams(C.Structure):
     _fields_ = [
         ("S", _i32), ("ts1", _u32), ("inbox_cap", _u32), ("quant", _i32), ("send_keys", _i32),
+        ("key_hit", _vp), ("mode", _vp * MAX_SHARDS),
         ("inbox_keys", _vp * MAX_SHARDS), ("inbox_vals", _vp * MAX_SHARDS),
         ("ready", _vp * MAX_SHARDS), ("count", _vp * MAX_SHARDS), ("applied", _vp * MAX_SHARDS),
         ("need_applied", _u32),
@@ -69,6 +70,7 @@ class ApplyParams(C.Structure):
         ("inbox_keys", _vp * MAX_SHARDS), ("inbox_vals", _vp * MAX_SHARDS),
         ("ready", _vp * MAX_SHARDS), ("count", _vp * MAX_SHARDS),
         ("alive", C.c_uint8 * MAX_SHARDS), ("cached", C.c_uint8 * MAX_SHARDS),
+        ("mode", _vp * MAX_SHARDS),
         ("slot_cache", _vp * MAX_SHARDS),
         ("opt", Optimizer), ("stats", _vp), ("applied", _vp), ("wait_iters", _u32),
         ("bar", _vp), ("done", _vp), ("status", _vp),
@@ -104,6 +106,14 @@ def _declare(lib):
     lib.psb_table_load.argtypes = [_vp, _u64, _u64, _u64, _vp, _vp, _vp, _vp, _u64, _vp, _vp]
     lib.psb_table_export.argtypes = [_vp, _u64, _vp, _vp, _vp, _vp, _u64, _vp, _vp]
     lib.psb_coop_grid.argtypes = [_i32]
+    lib.psb_key_signature.argtypes = [_vp, _vp, _u32, _vp, _vp, _vp, _vp, _vp]
+    lib.psb_fixfloat_encode.argtypes = [_vp, _vp, _u64, _i32, _f32, _f32, _u64, _vp]
+    lib.psb_fixfloat_decode.argtypes = [_vp, _vp, _u64, _i32, _f32, _f32, _vp]
+    lib.psb_minmax.argtypes = [_vp, _u64, _vp, _vp]
+    lib.psb_add_noise.argtypes = [_vp, _u64, _f32, _f32, _u64, _vp]
+    lib.psb_countmin_insert.argtypes = [_vp, _u32, _i32, _vp, _vp, _vp, _u32, _vp]
+    lib.psb_countmin_query.argtypes = [_vp, _u32, _i32, _vp, _vp, _vp, _u32, _vp]
+    lib.psb_ordered_match.argtypes = [_vp, _vp, _u32, _vp, _vp, _u32, _i32, _i32, _vp, _vp]
     lib.psb_gen_batch.argtypes = [_vp, _vp, _vp, _vp, _u32, _u32, _u64, _f64, _u64, _u64, _i32, _vp]
     lib.psb_hash_ids.argtypes = [_vp, _vp, _vp, _u64, _u64, _vp]
     lib.psb_flush_l2.argtypes = [_vp, _u64, _u32, _vp]

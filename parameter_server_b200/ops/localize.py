@@ -58,6 +58,8 @@ class LocalBatch:
         self.w_local = torch.empty(max_nnz, dtype=f32, device=dev)
         self.grad = torch.zeros(max_nnz, dtype=f32, device=dev)
         self.slot_local = None
+        self.key_hit = torch.zeros(1, dtype=i32, device=dev)     # key-caching filter: 1 = same list as last time
+        self.key_sig = torch.zeros(4, dtype=i32, device=dev)
         self.gcoef = torch.empty(max_rows, dtype=f32, device=dev)
         self.margin = torch.empty(max_rows, dtype=f32, device=dev)
         self.csc_val_buf = torch.empty(max_nnz, dtype=f32, device=dev) if real_values else None

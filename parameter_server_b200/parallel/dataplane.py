@@ -60,6 +60,7 @@ class PlaneConfig:
     key_range: Range = field(default_factory=Range.all)
     quant: str = "none"                     # none | int8 | fp16 (fixed-point filter on pushes)
     ordered_slots: bool = False             # keys are uniformly hashed: order-preserving slot map
+    key_cache: bool = False                 # key-caching filter: skip keys (push) and probes (pull) on a repeated key list
 
     def quant_code(self) -> int:
         return {"none": _lib.QUANT_NONE, "int8": _lib.QUANT_INT8, "fp16": _lib.QUANT_FP16}[self.quant]
@@ -68,7 +69,7 @@ class PlaneConfig:
 def heap_layout(cfg: PlaneConfig, world: int) -> HeapLayout:
     assert cfg.table_capacity & (cfg.table_capacity - 1) == 0, "table capacity must be a power of two"
     assert cfg.table_capacity < (1 << 31)
-    assert 8 + 2 * cfg.ring * world <= CTRL_WORDS
+    assert 8 + 3 * cfg.ring * world <= CTRL_WORDS
     lay = HeapLayout()
     lay.add("ctrl", CTRL_WORDS * 4)
     lay.add("table", cfg.table_capacity * 32)
@@ -98,6 +99,10 @@ class DataPlane:
         self.push_stats = torch.zeros(4, dtype=torch.float64, device=dev)   # d_nnz, w2, dw2, n
         self.pull_stats = torch.zeros(4, dtype=torch.float64, device=dev)   # loss, correct, rows
         self.alive = [True] * self.S
+        # key-caching filter state: signature of the previous key list, and the slots found for it
+        self.sig_state = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.sig_scratch = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.pull_slot_cache = None
         # order-preserving slot multiplier per shard: floor(capacity * 2^64 / range_size)
         self.slot_mult = []
         for s in range(self.S):
@@ -119,6 +124,9 @@ class DataPlane:
     def _count(self, owner: int, q: int, src: int) -> int:
         return self._ctrl(owner, 8 + self.cfg.ring * self.S + q * self.S + src)
 
+    def _mode(self, owner: int, q: int, src: int) -> int:
+        return self._ctrl(owner, 8 + 2 * self.cfg.ring * self.S + q * self.S + src)
+
     def _inbox_keys(self, owner: int, q: int, src: int) -> int:
         return self.fabric.ptr(owner, self.layout["inbox_keys"] + ((q * self.S + src) * self.cfg.inbox_cap) * 8)
 
@@ -133,6 +141,17 @@ class DataPlane:
 
     def table_ptr(self, rank: Optional[int] = None) -> int:
         return self.fabric.ptr(self.rank if rank is None else rank, self.layout["table"])
+
+    # ---------------------------------------------------------------- key-caching filter
+    def key_signature(self, b, stream=None):
+        """Signature of ``b``'s key list (crc32c of its head + a fingerprint of
+        the whole list) compared on the device with the previous list's; leaves
+        the hit flag in ``b.key_hit``. Call once per minibatch, before the pull."""
+        check(_lib.lib().psb_key_signature(ptr(b.ukeys), ptr(b.n_unique), b.max_nnz, ptr(self.sig_scratch),
+                                           ptr(self.sig_state), ptr(b.key_hit), ptr(b.key_sig), stream_ptr(stream)),
+              "key_signature")
+        if self.pull_slot_cache is None or self.pull_slot_cache.numel() < b.max_nnz:
+            self.pull_slot_cache = torch.full((b.max_nnz,), -1, dtype=torch.int32, device=self.device)
 
     # ---------------------------------------------------------------- worker: pull (+ margins)
     def pull_margin(self, b, *, need_applied: int = 0, with_margins: bool = True, loss: int = 0,
@@ -149,6 +168,8 @@ class DataPlane:
         p.need_applied = need_applied
         p.ukeys, p.n_unique, p.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
         p.w_local, p.slot_local, p.grad_zero = ptr(b.w_local), ptr(b.slot_local), ptr(b.grad)
+        if self.cfg.key_cache and self.pull_slot_cache is not None:
+            p.slot_local, p.key_hit = ptr(self.pull_slot_cache), ptr(b.key_hit)
         if with_margins:
             p.row_ptr, p.n_rows, p.fixed_z = ptr(b.row_ptr), b.n_rows, b.fixed_z
             p.csr_col, p.csr_val, p.y = ptr(b.csr_col), ptr(b.csr_val), ptr(b.y)
@@ -174,7 +195,10 @@ class DataPlane:
             p.inbox_vals[s] = self._inbox_vals(s, q, self.rank)
             p.ready[s] = self._ready(s, q, self.rank)
             p.count[s] = self._count(s, q, self.rank)
+            p.mode[s] = self._mode(s, q, self.rank)
             p.applied[s] = self._ctrl(s, 0)
+        if cfg.key_cache:
+            p.key_hit = ptr(b.key_hit)
         p.need_applied = max(0, ts + 1 - cfg.ring)
         p.ukeys, p.n_unique, p.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
         if with_gradient:
@@ -201,6 +225,7 @@ class DataPlane:
             p.inbox_vals[r] = self._inbox_vals(self.rank, q, r)
             p.ready[r] = self._ready(self.rank, q, r)
             p.count[r] = self._count(self.rank, q, r)
+            p.mode[r] = self._mode(self.rank, q, r)
             p.alive[r] = 1 if self.alive[r] else 0
             p.cached[r] = 1 if (cached is not None and cached[r]) else 0
             p.slot_cache[r] = self.slot_cache.data_ptr() + r * cfg.inbox_cap * 4
