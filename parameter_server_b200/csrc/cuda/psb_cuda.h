@@ -151,7 +151,7 @@ int psb_table_export(const void* table, psb_u64 capacity, psb_u64* out_keys, flo
 
 // number of CTAs a cooperative launch of the three fused kernels uses
 int psb_coop_grid(int which);
-int psb_struct_size(int which);
+int psb_struct_size(int which);   // 0 pull, 1 push, 2 apply, 3 optimizer, 4/5/6 darlin grad/update/dual
 
 // ---------------------------------------------------------------- filters / sorted-key utilities
 int psb_key_signature(const psb_u64* keys, const uint32_t* n_ptr, uint32_t max_n, uint32_t* scratch,
@@ -168,6 +168,86 @@ int psb_countmin_query(const uint32_t* cells, uint32_t n_cells, int k, const psb
 int psb_ordered_match(const psb_u64* src_key, const float* src_val, uint32_t n_src, const psb_u64* dst_key,
                       float* dst_val, uint32_t n_dst, int k, int op, unsigned long long* matched,
                       cudaStream_t stream);
+
+// ---------------------------------------------------------------- Darlin block coordinate descent (F3)
+// The model lives in a dense global column space (sorted union of all keys); shard s
+// owns columns [shard_col[s], shard_col[s+1]). A worker's data is its rows in CSC
+// order over its own unique keys (the output of sort + localise over the whole
+// local data set); gcol maps a local unique key to its global column.
+typedef struct {
+  int S;
+  uint32_t ts1;                 // block stamp + 1 (monotone)
+  uint32_t c0, c1;              // global column range of the block
+  uint32_t u0, u1;              // local unique-key range falling in the block
+  uint32_t block_cap;           // capacity (columns) of the per-block exchange areas
+  uint32_t shard_col[PSB_MAX_SHARDS + 1];
+  // worker data
+  const uint32_t* seg_off;      // CSC offsets over local unique keys
+  const uint32_t* csc_row;
+  const float* csc_val;         // nullable -> binary
+  const uint32_t* flagbits;
+  const uint32_t* wordbase;
+  const uint32_t* gcol;         // local unique key -> global column
+  const float* y;
+  float* margin;                // X w per local row (the log-domain dual)
+  const unsigned char* active;  // per global column (worker copy)
+  const float* delta;           // trust region per global column (worker copy)
+  float* stage;                 // [2][block_cap] local staging for (G, U)
+  float* gu_inbox[PSB_MAX_SHARDS];   // owner s: [2][block_cap] area of this source
+  uint32_t* ready[PSB_MAX_SHARDS];   // owner s: flag of this source
+  uint32_t* bar; uint32_t* done; uint32_t* status;
+} PsbDarlinGrad;
+
+typedef struct {
+  int S;
+  uint32_t ts1;
+  uint32_t c0, c1;              // block
+  uint32_t my0, my1;            // my columns of the block (may be empty)
+  uint32_t block_cap;
+  const float* gu_inbox[PSB_MAX_SHARDS];   // my inbox areas, one per source
+  const uint32_t* ready[PSB_MAX_SHARDS];
+  uint8_t alive[PSB_MAX_SHARDS];
+  float* w;                     // owner state per global column (only my range is used)
+  float* delta;
+  unsigned char* active;
+  float eta, lambda, delta_max, kkt_threshold;
+  float* wnew_inbox[PSB_MAX_SHARDS];       // dest r: [block_cap] new weights (NaN = deactivated)
+  uint32_t* wnew_ready[PSB_MAX_SHARDS];    // dest r: flag of this owner
+  float* violation;             // max |violation| (float as ordered int)
+  uint32_t wait_iters;
+  uint32_t* done; uint32_t* status;
+} PsbDarlinUpdate;
+
+typedef struct {
+  int S;
+  uint32_t ts1;
+  uint32_t c0, c1, u0, u1;
+  uint32_t block_cap;
+  uint32_t shard_col[PSB_MAX_SHARDS + 1];
+  const uint32_t* seg_off;
+  const uint32_t* csc_row;
+  const float* csc_val;
+  const uint32_t* flagbits;
+  const uint32_t* wordbase;
+  const uint32_t* gcol;
+  float* margin;
+  float* w_cur;                 // worker copy of the weights per global column
+  float* delta;
+  unsigned char* active;
+  float delta_max;
+  const float* wnew;            // my wnew inbox [block_cap]
+  const uint32_t* wnew_ready[PSB_MAX_SHARDS];  // flags of the owners
+  uint8_t alive[PSB_MAX_SHARDS];
+  uint32_t wait_iters;
+  uint32_t* bar; uint32_t* status;
+} PsbDarlinDual;
+
+int psb_darlin_grad(const PsbDarlinGrad* p, cudaStream_t stream);
+int psb_darlin_update(const PsbDarlinUpdate* p, cudaStream_t stream);
+int psb_darlin_dual(const PsbDarlinDual* p, cudaStream_t stream);
+// out[0] += sum_rows log(1+exp(-y m)) ; out[1] += lambda*sum|w| over [c0,c1) ; out[2] += nnz(w) ; out[3] += #active
+int psb_darlin_eval(const float* y, const float* margin, uint32_t n_rows, const float* w, const unsigned char* active,
+                    uint32_t c0, uint32_t c1, float lambda, double* out, cudaStream_t stream);
 
 // ---------------------------------------------------------------- data / misc
 int psb_gen_batch(uint32_t* ids32, psb_u64* ids64, float* vals, float* y, uint32_t n_rows,

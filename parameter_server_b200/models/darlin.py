@@ -1,0 +1,269 @@
+"""Darlin on the GPUs: delayed block proximal gradient (block coordinate descent)
+for L1-regularised logistic regression.
+
+Every rank is a worker (its rows, CSC over its unique keys) and an owner (a
+contiguous range of the global column space = the sorted union of all keys,
+cut at the shards' key-range boundaries). Per feature block three fused kernels
+run on every rank (``csrc/cuda/darlin.cu``): gradient + reduce-to-owner,
+owner update + broadcast, margin update. Blocks are pipelined with bounded
+delay ``tau``: the gradients of block ``t + tau`` are computed before the
+weights of block ``t`` have been applied, which is the device form of the
+scheduler's ``wait_time`` window (``app/linear_method/darlin.h:157-164``).
+
+The pass structure, KKT-filter threshold rule and stopping test follow
+``DarlinScheduler::Run`` (``app/linear_method/darlin.h:21-132``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..ops import _lib
+from ..ops._lib import DarlinDual, DarlinGrad, DarlinUpdate, check, ptr, stream_ptr
+from ..ops.localize import LocalBatch
+from ..parallel.fabric import Fabric, HeapLayout
+from ..utils.range import Range, shard_bounds
+
+
+@dataclass
+class DarlinConfig:
+    lambda_l1: float = 1.0
+    eta: float = 0.9                 # learning_rate.alpha
+    delta_init: float = 1.0
+    delta_max: float = 5.0
+    kkt_ratio: float = 10.0
+    max_pass: int = 10
+    epsilon: float = 1e-4
+    block_cols: int = 1 << 16        # columns per feature block
+    tau: int = 0                     # max_block_delay
+    random_block_order: bool = True
+    key_range: Range = Range.all()
+
+
+def darlin_heap_bytes(cfg: DarlinConfig, world: int) -> int:
+    return _layout(cfg, world).total()
+
+
+def _layout(cfg: DarlinConfig, world: int) -> HeapLayout:
+    R = cfg.tau + 2
+    lay = HeapLayout()
+    lay.add("flags", 4 * 2 * R * world + 64)                 # gu_ready[R][src], wnew_ready[R][owner]
+    lay.add("gu_inbox", R * world * 2 * cfg.block_cols * 4)   # [R][src][2][block]
+    lay.add("wnew", R * cfg.block_cols * 4)                   # [R][block]
+    return lay
+
+
+class DarlinRank:
+    """Worker + owner state of one rank."""
+
+    def __init__(self, fabric: Fabric, cfg: DarlinConfig, keys: torch.Tensor, y: torch.Tensor, *, fixed_z: int = 0,
+                 row_ptr: Optional[torch.Tensor] = None, vals: Optional[torch.Tensor] = None,
+                 global_keys: Optional[torch.Tensor] = None):
+        """``keys``: per-nonzero uint64 keys (int64 view) of this rank's rows in CSR
+        order; ``global_keys``: sorted union of every rank's unique keys (if None,
+        this rank's own unique keys -- single-rank use)."""
+        self.fabric, self.cfg = fabric, cfg
+        self.rank, self.S = fabric.rank, fabric.world
+        dev = fabric.device
+        self.dev = dev
+        self.lay = _layout(cfg, self.S)
+        assert self.lay.total() <= fabric.heap_bytes
+        self.R = cfg.tau + 2
+        nnz = keys.numel()
+        self.n_rows = y.numel()
+        self.y = y.contiguous().float()
+        # CSC of the local rows: the same sort + localise as a minibatch, once
+        self.b = LocalBatch(self.n_rows, nnz, 1, dev, real_values=vals is not None)
+        bounds1 = torch.tensor([0, -1], dtype=torch.int64, device=dev)
+        self.b.localize(keys, self.y, bounds1, fixed_z=fixed_z, row_ptr=row_ptr, vals=vals, hash_seed=None)
+        torch.cuda.synchronize(dev)
+        self.U = int(self.b.n_unique.item())
+        self.local_keys = self.b.ukeys[:self.U]
+        self.set_global_keys(self.local_keys if global_keys is None else global_keys)
+        self.margin = torch.zeros(self.n_rows, dtype=torch.float32, device=dev)
+        self.sync = torch.zeros(16, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.violation = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.stage = torch.zeros(2 * cfg.block_cols, dtype=torch.float32, device=dev)
+        self.kkt_threshold = 1e20
+        self.step = 0
+
+    def set_global_keys(self, global_keys: torch.Tensor):
+        cfg, dev = self.cfg, self.dev
+        self.global_keys = global_keys
+        self.n_cols = global_keys.numel()
+        gk = global_keys.cpu().numpy().view(np.uint64)
+        lk = self.local_keys.cpu().numpy().view(np.uint64)
+        self.gcol = torch.from_numpy(np.searchsorted(gk, lk).astype(np.int32)).to(dev)
+        self.gcol_host = np.searchsorted(gk, lk)
+        bh = shard_bounds(cfg.key_range, self.S)
+        self.shard_col = [int(np.searchsorted(gk, np.uint64(min(b, (1 << 64) - 1)))) for b in bh[:-1]] + [self.n_cols]
+        f32 = torch.float32
+        n = max(1, self.n_cols)
+        # owner state (only my column range is touched) and worker copies
+        self.w_own = torch.zeros(n, dtype=f32, device=dev)
+        self.delta_own = torch.full((n,), cfg.delta_init, dtype=f32, device=dev)
+        self.active_own = torch.ones(n, dtype=torch.uint8, device=dev)
+        self.w_cur = torch.zeros(n, dtype=f32, device=dev)
+        self.delta_w = torch.full((n,), cfg.delta_init, dtype=f32, device=dev)
+        self.active_w = torch.ones(n, dtype=torch.uint8, device=dev)
+        nb = (self.n_cols + cfg.block_cols - 1) // cfg.block_cols
+        self.blocks = [(i * cfg.block_cols, min(self.n_cols, (i + 1) * cfg.block_cols)) for i in range(nb)]
+
+    # ---- addresses in a rank's heap
+    def _flag(self, rank: int, kind: int, q: int, idx: int) -> int:
+        return self.fabric.ptr(rank, self.lay["flags"] + 4 * ((kind * self.R + q) * self.S + idx))
+
+    def _gu(self, owner: int, q: int, src: int) -> int:
+        return self.fabric.ptr(owner, self.lay["gu_inbox"] + ((q * self.S + src) * 2 * self.cfg.block_cols) * 4)
+
+    def _wnew(self, rank: int, q: int) -> int:
+        return self.fabric.ptr(rank, self.lay["wnew"] + q * self.cfg.block_cols * 4)
+
+    def _block_u(self, c0: int, c1: int):
+        return int(np.searchsorted(self.gcol_host, c0)), int(np.searchsorted(self.gcol_host, c1))
+
+    # ---- the three kernels of a block
+    def grad(self, blk: int, ts: int, stream=None):
+        c0, c1 = self.blocks[blk]
+        u0, u1 = self._block_u(c0, c1)
+        q = ts % self.R
+        p = DarlinGrad()
+        p.S, p.ts1, p.c0, p.c1, p.u0, p.u1, p.block_cap = self.S, ts + 1, c0, c1, u0, u1, self.cfg.block_cols
+        for s in range(self.S + 1):
+            p.shard_col[s] = self.shard_col[s]
+        b = self.b
+        p.seg_off, p.csc_row, p.csc_val = ptr(b.seg_off), ptr(b.csc_row), ptr(b.csc_val)
+        p.flagbits, p.wordbase, p.gcol = ptr(b.flagbits), ptr(b.wordbase), ptr(self.gcol)
+        p.y, p.margin, p.active, p.delta, p.stage = ptr(self.y), ptr(self.margin), ptr(self.active_w), ptr(self.delta_w), ptr(self.stage)
+        for s in range(self.S):
+            p.gu_inbox[s] = self._gu(s, q, self.rank)
+            p.ready[s] = self._flag(s, 0, q, self.rank)
+        p.bar, p.done, p.status = self.sync.data_ptr(), self.sync.data_ptr() + 8, ptr(self.status)
+        check(_lib.lib().psb_darlin_grad(C.byref(p), stream_ptr(stream)), "darlin_grad")
+
+    def update(self, blk: int, ts: int, wait_iters: int = 0, stream=None):
+        c0, c1 = self.blocks[blk]
+        q = ts % self.R
+        p = DarlinUpdate()
+        my0, my1 = max(c0, self.shard_col[self.rank]), min(c1, self.shard_col[self.rank + 1])
+        if my1 <= my0:
+            return                                    # no column of this block is mine
+        p.S, p.ts1, p.c0, p.c1, p.my0, p.my1, p.block_cap = self.S, ts + 1, c0, c1, my0, my1, self.cfg.block_cols
+        for r in range(self.S):
+            p.gu_inbox[r] = self._gu(self.rank, q, r)
+            p.ready[r] = self._flag(self.rank, 0, q, r)
+            p.alive[r] = 1
+            p.wnew_inbox[r] = self._wnew(r, q)
+            p.wnew_ready[r] = self._flag(r, 1, q, self.rank)
+        p.w, p.delta, p.active = ptr(self.w_own), ptr(self.delta_own), ptr(self.active_own)
+        cfg = self.cfg
+        p.eta, p.lam, p.delta_max, p.kkt_threshold = cfg.eta, cfg.lambda_l1, cfg.delta_max, self.kkt_threshold
+        p.violation, p.wait_iters = ptr(self.violation), wait_iters
+        p.done, p.status = self.sync.data_ptr() + 24, ptr(self.status)
+        check(_lib.lib().psb_darlin_update(C.byref(p), stream_ptr(stream)), "darlin_update")
+
+    def dual(self, blk: int, ts: int, wait_iters: int = 0, stream=None):
+        c0, c1 = self.blocks[blk]
+        u0, u1 = self._block_u(c0, c1)
+        q = ts % self.R
+        p = DarlinDual()
+        p.S, p.ts1, p.c0, p.c1, p.u0, p.u1, p.block_cap = self.S, ts + 1, c0, c1, u0, u1, self.cfg.block_cols
+        for s in range(self.S + 1):
+            p.shard_col[s] = self.shard_col[s]
+        b = self.b
+        p.seg_off, p.csc_row, p.csc_val = ptr(b.seg_off), ptr(b.csc_row), ptr(b.csc_val)
+        p.flagbits, p.wordbase, p.gcol = ptr(b.flagbits), ptr(b.wordbase), ptr(self.gcol)
+        p.margin, p.w_cur, p.delta, p.active = ptr(self.margin), ptr(self.w_cur), ptr(self.delta_w), ptr(self.active_w)
+        p.delta_max, p.wnew = self.cfg.delta_max, self._wnew(self.rank, q)
+        for s in range(self.S):
+            p.wnew_ready[s] = self._flag(self.rank, 1, q, s)
+            p.alive[s] = 1
+        p.wait_iters = wait_iters
+        p.bar, p.status = self.sync.data_ptr() + 32, ptr(self.status)
+        check(_lib.lib().psb_darlin_dual(C.byref(p), stream_ptr(stream)), "darlin_dual")
+
+    def reset_kkt_filter(self):
+        self.active_own.fill_(1)
+        self.active_w.fill_(1)
+
+    def evaluate(self):
+        """(loss over my rows, lambda*|w|_1 / nnz / active over my columns, max violation)."""
+        out = torch.zeros(4, dtype=torch.float64, device=self.dev)
+        c0, c1 = self.shard_col[self.rank], self.shard_col[self.rank + 1]
+        check(_lib.lib().psb_darlin_eval(ptr(self.y), ptr(self.margin), self.n_rows, ptr(self.w_own), ptr(self.active_own),
+                                         c0, c1, self.cfg.lambda_l1, ptr(out), stream_ptr()), "darlin_eval")
+        vals = out.tolist() + [float(self.violation.item())]
+        self.violation.zero_()
+        return vals
+
+    def my_model(self):
+        """(keys uint64, w) of my non-zero weights."""
+        c0, c1 = self.shard_col[self.rank], self.shard_col[self.rank + 1]
+        w = self.w_own[c0:c1]
+        nz = torch.nonzero((w != 0) & (w == w)).flatten()
+        return self.global_keys[c0:c1][nz].cpu().numpy().view(np.uint64), w[nz].cpu().numpy()
+
+    def check_status(self, what="darlin"):
+        _lib.check_status(self.status, what)
+
+
+def run_darlin(ranks: Sequence[DarlinRank], *, all_reduce=None, verbose: bool = False, num_examples: Optional[int] = None):
+    """Drive passes over the blocks. ``ranks``: every rank of an emulated fabric
+    (kernels of the ranks run one after another), or the single local rank of a
+    multi-process run, with ``all_reduce(values, op)`` combining the per-pass
+    scalars across processes."""
+    cfg = ranks[0].cfg
+    tau = cfg.tau if len(ranks) == 1 or all_reduce is not None else 0   # emulated ranks share a stream: no delay
+    nb = len(ranks[0].blocks)
+    history = []
+    ts = 0
+    reset_kkt = False
+    n_ex = num_examples or sum(r.n_rows for r in ranks)
+    for it in range(cfg.max_pass):
+        order = list(range(nb))
+        if cfg.random_block_order:
+            np.random.default_rng(1000 + it).shuffle(order)
+        if reset_kkt:
+            for r in ranks:
+                r.reset_kkt_filter()
+        # software pipeline: gradients run `tau` blocks ahead of the weight application
+        for i in range(len(order) + tau):
+            if i < len(order):
+                for r in ranks:
+                    r.grad(order[i], ts + i)
+            j = i - tau
+            if j >= 0:
+                for r in ranks:
+                    r.update(order[j], ts + j)
+                for r in ranks:
+                    r.dual(order[j], ts + j)
+        ts += len(order)
+        loss = l1 = nnz = act = vio = 0.0
+        for r in ranks:
+            a = r.evaluate()
+            loss += a[0]; l1 += a[1]; nnz += a[2]; act += a[3]; vio = max(vio, a[4])
+            r.check_status()
+        if all_reduce is not None:
+            loss, l1, nnz, act = all_reduce([loss, l1, nnz, act], "sum")
+            vio = all_reduce([vio], "max")[0]
+        obj = loss + l1
+        rel = (history[-1]["objective"] - obj) / history[-1]["objective"] if history else 1.0
+        history.append(dict(iter=it, objective=obj, relative=rel, nnz_w=int(nnz), violation=vio, active=int(act)))
+        if verbose:
+            print(f" {it:5d} | {obj:.5e}  {rel:.3e}  {int(nnz):8d} | {vio:.3e}  {int(act):9d}")
+        thr = vio / max(1, n_ex) * cfg.kkt_ratio
+        for r in ranks:
+            r.kkt_threshold = thr
+        if 0 < rel <= cfg.epsilon:
+            if reset_kkt:
+                break
+            reset_kkt = True
+        else:
+            reset_kkt = False
+    return history

@@ -77,6 +77,39 @@ class ApplyParams(C.Structure):
     ]
 
 
+class DarlinGrad(C.Structure):
+    _fields_ = [
+        ("S", _i32), ("ts1", _u32), ("c0", _u32), ("c1", _u32), ("u0", _u32), ("u1", _u32), ("block_cap", _u32),
+        ("shard_col", _u32 * (MAX_SHARDS + 1)),
+        ("seg_off", _vp), ("csc_row", _vp), ("csc_val", _vp), ("flagbits", _vp), ("wordbase", _vp), ("gcol", _vp),
+        ("y", _vp), ("margin", _vp), ("active", _vp), ("delta", _vp), ("stage", _vp),
+        ("gu_inbox", _vp * MAX_SHARDS), ("ready", _vp * MAX_SHARDS),
+        ("bar", _vp), ("done", _vp), ("status", _vp),
+    ]
+
+
+class DarlinUpdate(C.Structure):
+    _fields_ = [
+        ("S", _i32), ("ts1", _u32), ("c0", _u32), ("c1", _u32), ("my0", _u32), ("my1", _u32), ("block_cap", _u32),
+        ("gu_inbox", _vp * MAX_SHARDS), ("ready", _vp * MAX_SHARDS), ("alive", C.c_uint8 * MAX_SHARDS),
+        ("w", _vp), ("delta", _vp), ("active", _vp),
+        ("eta", _f32), ("lam", _f32), ("delta_max", _f32), ("kkt_threshold", _f32),
+        ("wnew_inbox", _vp * MAX_SHARDS), ("wnew_ready", _vp * MAX_SHARDS),
+        ("violation", _vp), ("wait_iters", _u32), ("done", _vp), ("status", _vp),
+    ]
+
+
+class DarlinDual(C.Structure):
+    _fields_ = [
+        ("S", _i32), ("ts1", _u32), ("c0", _u32), ("c1", _u32), ("u0", _u32), ("u1", _u32), ("block_cap", _u32),
+        ("shard_col", _u32 * (MAX_SHARDS + 1)),
+        ("seg_off", _vp), ("csc_row", _vp), ("csc_val", _vp), ("flagbits", _vp), ("wordbase", _vp), ("gcol", _vp),
+        ("margin", _vp), ("w_cur", _vp), ("delta", _vp), ("active", _vp), ("delta_max", _f32),
+        ("wnew", _vp), ("wnew_ready", _vp * MAX_SHARDS), ("alive", C.c_uint8 * MAX_SHARDS),
+        ("wait_iters", _u32), ("bar", _vp), ("status", _vp),
+    ]
+
+
 _LIB = None
 LAUNCHES = 0
 
@@ -106,6 +139,11 @@ def _declare(lib):
     lib.psb_table_load.argtypes = [_vp, _u64, _u64, _u64, _vp, _vp, _vp, _vp, _u64, _vp, _vp]
     lib.psb_table_export.argtypes = [_vp, _u64, _vp, _vp, _vp, _vp, _u64, _vp, _vp]
     lib.psb_coop_grid.argtypes = [_i32]
+    lib.psb_darlin_grad.argtypes = [C.POINTER(DarlinGrad), _vp]
+    lib.psb_darlin_update.argtypes = [C.POINTER(DarlinUpdate), _vp]
+    lib.psb_darlin_dual.argtypes = [C.POINTER(DarlinDual), _vp]
+    lib.psb_darlin_eval.argtypes = [_vp, _vp, _u32, _vp, _vp, _u32, _u32, _f32, _vp, _vp]
+    lib.psb_darlin_struct_size.argtypes = [_i32]
     lib.psb_key_signature.argtypes = [_vp, _vp, _u32, _vp, _vp, _vp, _vp, _vp]
     lib.psb_fixfloat_encode.argtypes = [_vp, _vp, _u64, _i32, _f32, _f32, _u64, _vp]
     lib.psb_fixfloat_decode.argtypes = [_vp, _vp, _u64, _i32, _f32, _f32, _vp]
@@ -159,6 +197,10 @@ def lib():
             if _LIB.psb_struct_size(which) != C.sizeof(st):
                 raise RuntimeError(f"{st.__name__}: binding struct is {C.sizeof(st)} bytes, "
                                    f"library expects {_LIB.psb_struct_size(which)}")
+        for which, st in enumerate((DarlinGrad, DarlinUpdate, DarlinDual)):
+            if _LIB.psb_darlin_struct_size(which) != C.sizeof(st):
+                raise RuntimeError(f"{st.__name__}: binding struct is {C.sizeof(st)} bytes, "
+                                   f"library expects {_LIB.psb_darlin_struct_size(which)}")
     return _LIB
 
 

@@ -171,3 +171,64 @@ def auc(y, score):
         return 0.5
     a = (ranks[y].sum() - npos * (npos + 1) / 2) / (npos * nneg)
     return float(a)
+
+
+def darlin_oracle(parts, global_keys, lam, eta, delta_init, delta_max, blocks_per_pass, n_pass, kkt_ratio=10.0):
+    """NumPy restatement of Darlin with BSP blocks (no delay). ``parts``: list of
+    (keys_flat uint64, row_ptr, y, vals or None) per worker; ``blocks_per_pass``:
+    list (per pass) of lists of (c0, c1) column ranges in processing order.
+    Returns (w per global column, history of objectives)."""
+    ncol = len(global_keys)
+    w = np.zeros(ncol, f32); delta = np.full(ncol, delta_init, f32); active = np.ones(ncol, bool)
+    data = []
+    for keys, row_ptr, y, vals in parts:
+        col = np.searchsorted(global_keys, keys)
+        rows = np.repeat(np.arange(len(y)), np.diff(row_ptr))
+        x = np.ones(len(keys), f32) if vals is None else vals.astype(f32)
+        data.append(dict(col=col, rows=rows, x=x, y=y.astype(f32), m=np.zeros(len(y), f32), binary=vals is None))
+    n_ex = sum(len(d["y"]) for d in data)
+    thr = 1e20
+    hist = []
+    for it in range(n_pass):
+        vio_max = 0.0
+        for (c0, c1) in blocks_per_pass[it]:
+            G = np.zeros(c1 - c0, np.float64); U = np.zeros(c1 - c0, np.float64)
+            for d in data:
+                sel = (d["col"] >= c0) & (d["col"] < c1) & active[d["col"]]
+                c, r, x = d["col"][sel], d["rows"][sel], d["x"][sel]
+                ym = d["y"][r] * d["m"][r]
+                en = np.exp(-np.abs(ym)); tau = np.where(ym > 0, en / (1 + en), 1 / (1 + en))
+                dl = delta[c]
+                if d["binary"]:
+                    g = -d["y"][r] * tau; h = np.minimum(tau * (1 - tau) * np.exp(dl), 0.25)
+                else:
+                    g = -d["y"][r] * tau * x; h = np.minimum(tau * (1 - tau) * np.exp(np.abs(x) * dl), 0.25) * x * x
+                np.add.at(G, c - c0, g); np.add.at(U, c - c0, h)
+            new_w = w[c0:c1].copy()
+            for j in range(c1 - c0):
+                k = c0 + j
+                if not active[k]:
+                    continue
+                g, u = f32(G[j]), f32(U[j]) / f32(eta) + f32(1e-10)
+                gp, gn = g + f32(lam), g - f32(lam)
+                wk = w[k]; dd = -wk; vio = 0.0
+                if wk == 0:
+                    if gp < 0: vio = -gp
+                    elif gn > 0: vio = gn
+                    elif gp > thr and gn < -thr:
+                        active[k] = False; continue
+                vio_max = max(vio_max, float(vio))
+                if gp <= u * wk: dd = -gp / u
+                elif gn >= u * wk: dd = -gn / u
+                dd = min(delta[k], max(-delta[k], dd))
+                delta[k] = min(delta_max, 2 * abs(dd) + 0.1)
+                new_w[j] = wk + dd
+            dw = new_w - w[c0:c1]
+            for d in data:
+                sel = (d["col"] >= c0) & (d["col"] < c1) & active[d["col"]]
+                np.add.at(d["m"], d["rows"][sel], dw[d["col"][sel] - c0] * d["x"][sel])
+            w[c0:c1] = new_w
+        loss = sum(float(np.sum(np.log1p(np.exp(-np.abs(d["y"] * d["m"]))) + np.maximum(-d["y"] * d["m"], 0))) for d in data)
+        hist.append(loss + lam * float(np.abs(w).sum()))
+        thr = vio_max / n_ex * kkt_ratio
+    return w, hist
