@@ -1,0 +1,514 @@
+// Wide-value path (kernel family F4): tables whose values are 64-wide bf16
+// vectors with fp32 AdaGrad accumulators on the server side.
+//
+//   k_wide_pull_gemm  worker: for a tile of 128 unique keys, locate each key in
+//                     its owner's key table and fetch its 128-byte value row
+//                     (plain loads; the owner may be a peer GPU) straight into
+//                     shared memory in the 128-byte-swizzled K-major layout that
+//                     the tensor core expects, then multiply the [128 x 64] tile
+//                     by the batch's [64 x N] context matrix with tcgen05.mma
+//                     (accumulator in TMEM), read the result back with tcgen05.ld
+//                     and store P[U x N]. The context matrix is brought in once
+//                     per CTA by a TMA tiled load (cp.async.bulk.tensor.2d, no
+//                     multicast) with the same swizzle.
+//   k_wide_rowsum     worker: prediction per row = sum over its keys of
+//                     P[key, context(row)], logistic loss and d loss / d margin.
+//   k_wide_push       worker: gradient of every unique key,
+//                     G[u,:] = sum_{rows containing u} gcoef[row] * C[:, ctx(row)],
+//                     one warp per key over the CSC segment, written as bf16
+//                     records into the owner's inbox by peer stores + release flag.
+//   k_wide_apply      owner: bounded wait per source, then AdaGrad on the fp32
+//                     accumulators and bf16 weights, sources applied in rank order
+//                     (grid barrier between sources).
+//
+// Only loads/stores through peer pointers cross GPUs; the TMA load reads local
+// memory and carries no multicast qualifier.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include "psb_common.cuh"
+#include "psb_cuda.h"
+
+namespace psb {
+
+static constexpr int kWide = 64;                 // values per key
+static constexpr int kTileM = 128;               // keys per MMA tile
+static constexpr u32 kWideProbe = 1u << 16;
+
+// ---------------------------------------------------------------- small PTX wrappers
+__device__ __forceinline__ u32 smem_u32(const void* p) { return (u32)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(u64* bar, u32 count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(u64* bar, u32 bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// bounded wait on a phase parity; false if the budget ran out
+__device__ __forceinline__ bool mbar_wait(u64* bar, u32 parity, u32 max_iters) {
+  const u32 addr = smem_u32(bar);
+  for (u32 it = 0; it < max_iters; ++it) {
+    u32 ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, u64* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(u32* smem_out, u32 ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_out)), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(u32 taddr, u32 ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle:
+// 8-row groups are 1024 bytes apart (SBO); LBO is unused for this layout.
+__device__ __forceinline__ u64 make_smem_desc(u32 smem_addr) {
+  u64 d = 0;
+  d |= (u64)((smem_addr & 0x3FFFF) >> 4);         // start address
+  d |= (u64)(16 >> 4) << 16;                      // leading byte offset (ignored)
+  d |= (u64)(1024 >> 4) << 32;                    // stride byte offset between 8-row groups
+  d |= 1ull << 46;                                // descriptor version of this architecture
+  d |= 2ull << 61;                                // 128-byte swizzle
+  return d;
+}
+// kind::f16, bf16 x bf16 -> fp32, both operands K-major, M x N tile
+__device__ __forceinline__ u32 make_idesc(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((u32)(N >> 3) << 17) | ((u32)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(u32 tmem_d, u64 desc_a, u64 desc_b, u32 idesc, u32 accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(u64* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 lanes x 32 columns of 32-bit: thread i of the warp gets row (lane base + i)
+__device__ __forceinline__ void tmem_ld_32x32(u32 taddr, u32* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- key table of a wide shard
+// keys[slot] (u64, kEmptyKey = free); values at vals + slot*64 (bf16), accumulators at acc + slot*64 (fp32)
+template <bool kInsert>
+__device__ __forceinline__ long long wide_find(u64* keys, const SlotMap& sm, u64 key) {
+  u64 slot = first_slot(sm, key);
+  for (u32 p = 0; p < kWideProbe; ++p) {
+    u64 k = ld_relaxed_sys_u64(&keys[slot]);
+    if (k == key) return (long long)slot;
+    if (k == kEmptyKey) {
+      if (!kInsert) return -1;
+      u64 old = atomicCAS_system(&keys[slot], kEmptyKey, key);
+      if (old == kEmptyKey || old == key) return (long long)slot;
+    }
+    slot = (slot + 1) & sm.mask;
+  }
+  return -1;
+}
+
+// ---------------------------------------------------------------- F4: pull + GEMM
+struct WidePullArgs {
+  int S;
+  int N;                                  // contexts (columns of the result): 64 or 128
+  psb_u64* keys[PSB_MAX_SHARDS];
+  const __nv_bfloat16* vals[PSB_MAX_SHARDS];
+  psb_u64 mask[PSB_MAX_SHARDS], key_begin[PSB_MAX_SHARDS], slot_mult[PSB_MAX_SHARDS];
+  const psb_u64* ukeys;
+  const uint32_t* n_unique;
+  const uint32_t* own_off;
+  float* P;                               // [U x N] fp32
+  __nv_bfloat16* v_local;                 // nullable: gathered rows [U x 64]
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(128) k_wide_pull_gemm(const __grid_constant__ CUtensorMap ctx_map, const WidePullArgs p) {
+  // operand tiles: 1024-byte aligned because of the 128-byte swizzle
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* sA = smem;                      // [128 rows x 128 B]
+  unsigned char* sB = smem + kTileM * 128;       // [N rows x 128 B]
+  __shared__ u64 s_bar[2];                       // 0: TMA, 1: MMA
+  __shared__ u32 s_tmem;
+  __shared__ u32 s_off[PSB_MAX_SHARDS + 1];
+  __shared__ u32 s_fail;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int N = p.N;
+  const u32 U = *p.n_unique;
+  if (tid <= p.S) s_off[tid] = p.own_off[tid];
+  if (tid == 0) {
+    s_fail = 0;
+    mbar_init(&s_bar[0], 1);
+    mbar_init(&s_bar[1], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tmem_alloc(&s_tmem, (u32)N);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const u32 tmem_base = s_tmem;
+  // context matrix, once per CTA
+  if (tid == 0) {
+    mbar_expect_tx(&s_bar[0], (u32)N * 128u);
+    tma_load_2d(sB, &ctx_map, 0, 0, &s_bar[0]);
+  }
+  if (!mbar_wait(&s_bar[0], 0, 1u << 22)) { if (tid == 0) { s_fail = 1; set_status(p.status, kWaitTimeout); } }
+  __syncthreads();
+  const u32 idesc = make_idesc(kTileM, N);
+  const u32 ntiles = (U + kTileM - 1) / kTileM;
+  u32 phase = 0;
+  for (u32 t = blockIdx.x; t < ntiles && !s_fail; t += gridDim.x) {
+    // ---- gather: thread = one key = one 128-byte row
+    const u32 u = t * kTileM + tid;
+    uint4 row[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) row[c] = make_uint4(0, 0, 0, 0);
+    if (u < U) {
+      int s = owner_of(s_off, p.S, u);
+      const SlotMap sm{p.mask[s], p.key_begin[s], p.slot_mult[s]};
+      long long slot = wide_find<false>((u64*)p.keys[s], sm, p.ukeys[u]);
+      if (slot >= 0) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.vals[s] + (size_t)slot * kWide);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) row[c] = src[c];
+      }
+      if (p.v_local) {
+        uint4* dst = reinterpret_cast<uint4*>(p.v_local + (size_t)u * kWide);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) dst[c] = row[c];
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c)   // 16-byte chunk c of row r lands at chunk (c ^ (r & 7))
+      *reinterpret_cast<uint4*>(sA + tid * 128 + ((c ^ (tid & 7)) << 4)) = row[c];
+    fence_async_smem();
+    __syncthreads();
+    // ---- MMA: one thread issues K = 64 as four K = 16 steps
+    if (tid == 0) {
+      tc_fence_after();
+      const u64 da = make_smem_desc(smem_u32(sA)), db = make_smem_desc(smem_u32(sB));
+#pragma unroll
+      for (int k = 0; k < 4; ++k) umma_bf16(tmem_base, da + (u64)(2 * k), db + (u64)(2 * k), idesc, k > 0 ? 1u : 0u);
+      umma_commit(&s_bar[1]);
+    }
+    if (!mbar_wait(&s_bar[1], phase, 1u << 22)) { if (tid == 0) { s_fail = 1; set_status(p.status, kWaitTimeout); } }
+    phase ^= 1;
+    tc_fence_after();
+    __syncthreads();
+    if (s_fail) break;
+    // ---- epilogue: warp w owns TMEM lanes [32w, 32w+32) = rows of the tile
+    for (int c0 = 0; c0 < N; c0 += 32) {
+      u32 r[32];
+      tmem_ld_32x32(tmem_base + ((u32)(warp * 32) << 16) + (u32)c0, r);
+      if (u < U) {
+        float4* dst = reinterpret_cast<float4*>(p.P + (size_t)u * N + c0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                               __uint_as_float(r[4 * j + 3]));
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, (u32)N);
+  (void)lane;
+}
+
+// ---------------------------------------------------------------- rows: prediction, loss, gcoef
+__global__ void __launch_bounds__(256) k_wide_rowsum(const float* __restrict__ P, int N, const u32* __restrict__ row_ptr,
+                                                     u32 n_rows, u32 fixed_z, const u32* __restrict__ csr_col,
+                                                     const u32* __restrict__ row_ctx, const float* __restrict__ y,
+                                                     float* __restrict__ gcoef, float* __restrict__ margin,
+                                                     double* __restrict__ stats) {
+  const int lane = threadIdx.x & 31;
+  const u32 gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+  double loss = 0, correct = 0, seen = 0;
+  for (u32 r = gwarp; r < n_rows; r += nwarps) {
+    u32 b = row_ptr ? row_ptr[r] : r * fixed_z, e = row_ptr ? row_ptr[r + 1] : b + fixed_z;
+    u32 ctx = row_ctx ? row_ctx[r] : r % (u32)N;
+    float acc = 0.f;
+    for (u32 j = b + lane; j < e; j += 32) acc += P[(size_t)csr_col[j] * N + ctx];
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      float yy = y[r], ym = yy * acc;
+      float en = expf(-fabsf(ym));
+      float tau = ym > 0 ? en / (1.f + en) : 1.f / (1.f + en);
+      gcoef[r] = -yy * tau;
+      if (margin) margin[r] = acc;
+      loss += log1pf(en) + fmaxf(-ym, 0.f);
+      correct += ym > 0 ? 1 : 0;
+      seen += 1;
+    }
+  }
+  loss = warp_sum_d(loss); correct = warp_sum_d(correct); seen = warp_sum_d(seen);
+  if (lane == 0 && stats && seen > 0) { atomicAdd(&stats[0], loss); atomicAdd(&stats[1], correct); atomicAdd(&stats[2], seen); }
+}
+
+// ---------------------------------------------------------------- push: per-key gradient rows to the owners
+struct WidePushArgs {
+  int S;
+  int N;
+  uint32_t ts1, inbox_cap;
+  psb_u64* inbox_keys[PSB_MAX_SHARDS];
+  __nv_bfloat16* inbox_vals[PSB_MAX_SHARDS];   // [cap x 64]
+  uint32_t* ready[PSB_MAX_SHARDS];
+  uint32_t* count[PSB_MAX_SHARDS];
+  const psb_u64* ukeys;
+  const uint32_t* n_unique;
+  const uint32_t* own_off;
+  const uint32_t* seg_off;
+  const uint32_t* csc_row;
+  const float* gcoef;
+  const uint32_t* row_ctx;                     // nullable -> row % N
+  const __nv_bfloat16* ctx;                    // [N x 64] (context n in row n)
+  uint32_t* done;
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(256) k_wide_push(const WidePushArgs p) {
+  __shared__ u32 s_off[PSB_MAX_SHARDS + 1];
+  __shared__ u32 s_last;
+  if (threadIdx.x <= p.S) s_off[threadIdx.x] = p.own_off[threadIdx.x];
+  __syncthreads();
+  const u32 U = *p.n_unique;
+  const int lane = threadIdx.x & 31;
+  const u32 gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (u32 u = gwarp; u < U; u += nwarps) {
+    // lane handles dimensions 2*lane, 2*lane+1
+    float g0 = 0.f, g1 = 0.f;
+    for (u32 i = p.seg_off[u]; i < p.seg_off[u + 1]; ++i) {
+      u32 r = p.csc_row[i];
+      float gc = __ldg(&p.gcoef[r]);
+      u32 n = p.row_ctx ? p.row_ctx[r] : r % (u32)p.N;
+      __nv_bfloat162 c2 = reinterpret_cast<const __nv_bfloat162*>(p.ctx + (size_t)n * kWide)[lane];
+      g0 += gc * __bfloat162float(c2.x);
+      g1 += gc * __bfloat162float(c2.y);
+    }
+    int s = owner_of(s_off, p.S, u);
+    u32 j = u - s_off[s];
+    if (j >= p.inbox_cap) { if (lane == 0) set_status(p.status, kInboxOverflow); continue; }
+    reinterpret_cast<__nv_bfloat162*>(p.inbox_vals[s] + (size_t)j * kWide)[lane] = __floats2bfloat162_rn(g0, g1);
+    if (lane == 0) p.inbox_keys[s][j] = p.ukeys[u];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(p.done, 1u) + 1 == gridDim.x;
+  __syncthreads();
+  if (s_last && threadIdx.x < p.S) {
+    int s = threadIdx.x;
+    __threadfence_system();
+    *p.count[s] = min(s_off[s + 1] - s_off[s], p.inbox_cap);
+    __threadfence_system();
+    st_release_sys(p.ready[s], p.ts1);
+    if (s == 0) atomicExch(p.done, 0u);
+  }
+}
+
+// ---------------------------------------------------------------- apply: AdaGrad per source, in rank order
+struct WideApplyArgs {
+  int S;
+  uint32_t ts1, inbox_cap;
+  psb_u64* keys;
+  __nv_bfloat16* vals;
+  float* acc;
+  psb_u64 mask, key_begin, slot_mult;
+  const psb_u64* inbox_keys[PSB_MAX_SHARDS];
+  const __nv_bfloat16* inbox_vals[PSB_MAX_SHARDS];
+  const uint32_t* ready[PSB_MAX_SHARDS];
+  const uint32_t* count[PSB_MAX_SHARDS];
+  uint8_t alive[PSB_MAX_SHARDS];
+  float alpha, beta;
+  uint32_t wait_iters;
+  uint32_t* applied;
+  uint32_t* bar;
+  uint32_t* done;
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(256) k_wide_apply(const WideApplyArgs p) {
+  __shared__ u32 s_cnt[PSB_MAX_SHARDS];
+  __shared__ u32 s_last;
+  if (threadIdx.x == 0) {
+    const u32 iters = p.wait_iters ? p.wait_iters : kPeerWaitIters;
+    for (int r = 0; r < p.S; ++r) {
+      s_cnt[r] = 0;
+      if (!p.alive[r]) continue;
+      if (!wait_flag_ge_sys(p.ready[r], p.ts1, iters)) { set_status(p.status, kWaitTimeout); continue; }
+      s_cnt[r] = min(*((volatile const u32*)p.count[r]), p.inbox_cap);
+    }
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const u32 gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+  const SlotMap sm{p.mask, p.key_begin, p.slot_mult};
+  int applied_sources = 0;
+  for (int r = 0; r < p.S; ++r) {
+    if (!p.alive[r]) continue;
+    // a key pushed by two sources is updated twice, once per source: keep the passes apart
+    if (applied_sources++ > 0) { if (!grid_barrier(p.bar, p.status)) return; }
+    for (u32 j = gwarp; j < s_cnt[r]; j += nwarps) {
+      long long slot = 0;
+      if (lane == 0) slot = wide_find<true>((u64*)p.keys, sm, p.inbox_keys[r][j]);
+      slot = __shfl_sync(0xffffffffu, slot, 0);
+      if (slot < 0) { if (lane == 0) set_status(p.status, kTableFull); continue; }
+      __nv_bfloat162 g2 = reinterpret_cast<const __nv_bfloat162*>(p.inbox_vals[r] + (size_t)j * kWide)[lane];
+      float g0 = __bfloat162float(g2.x), g1 = __bfloat162float(g2.y);
+      float2* ap = reinterpret_cast<float2*>(p.acc + (size_t)slot * kWide) + lane;
+      __nv_bfloat162* wp = reinterpret_cast<__nv_bfloat162*>(p.vals + (size_t)slot * kWide) + lane;
+      float2 a = *ap;
+      __nv_bfloat162 w2 = *wp;
+      a.x += g0 * g0; a.y += g1 * g1;
+      float w0 = __bfloat162float(w2.x) - p.alpha / (sqrtf(a.x) + p.beta) * g0;
+      float w1 = __bfloat162float(w2.y) - p.alpha / (sqrtf(a.y) + p.beta) * g1;
+      *ap = a;
+      *wp = __floats2bfloat162_rn(w0, w1);
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(p.done, 1u) + 1 == gridDim.x;
+  __syncthreads();
+  if (s_last && threadIdx.x == 0) {
+    __threadfence_system();
+    st_release_sys(p.applied, p.ts1);
+    atomicExch(p.done, 0u);
+  }
+}
+
+__global__ void k_wide_init(u64* keys, __nv_bfloat16* vals, float* acc, u64 cap, u64 seed, float scale) {
+  for (u64 i = blockIdx.x * (u64)blockDim.x + threadIdx.x; i < cap * kWide; i += (u64)gridDim.x * blockDim.x) {
+    if (i < cap) keys[i] = kEmptyKey;
+    vals[i] = __float2bfloat16(0.f);
+    acc[i] = 0.f;
+  }
+  (void)seed; (void)scale;
+}
+
+// bulk load of (key, 64 values) rows: table initialisation / checkpoint restore
+__global__ void k_wide_load(u64* keys, __nv_bfloat16* vals, SlotMap sm, const u64* in_keys, const __nv_bfloat16* in_vals,
+                            u32 n, u32* status) {
+  const int lane = threadIdx.x & 31;
+  const u32 gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (u32 i = gwarp; i < n; i += nwarps) {
+    long long slot = 0;
+    if (lane == 0) slot = wide_find<true>(keys, sm, in_keys[i]);
+    slot = __shfl_sync(0xffffffffu, slot, 0);
+    if (slot < 0) { if (lane == 0) set_status(status, kTableFull); continue; }
+    reinterpret_cast<__nv_bfloat162*>(vals + (size_t)slot * kWide)[lane] =
+        reinterpret_cast<const __nv_bfloat162*>(in_vals + (size_t)i * kWide)[lane];
+  }
+}
+
+}  // namespace psb
+using namespace psb;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+extern "C" int psb_wide_init(psb_u64* keys, void* vals, float* acc, psb_u64 cap, cudaStream_t stream) {
+  k_wide_init<<<148 * 8, 256, 0, stream>>>((u64*)keys, (__nv_bfloat16*)vals, acc, cap, 0, 0.f);
+  return -(int)cudaGetLastError();
+}
+extern "C" int psb_wide_load(psb_u64* keys, void* vals, psb_u64 mask, psb_u64 key_begin, psb_u64 slot_mult,
+                             const psb_u64* in_keys, const void* in_vals, uint32_t n, uint32_t* status,
+                             cudaStream_t stream) {
+  if (n == 0) return 0;
+  k_wide_load<<<148 * 4, 256, 0, stream>>>((u64*)keys, (__nv_bfloat16*)vals, SlotMap{mask, key_begin, slot_mult},
+                                           (const u64*)in_keys, (const __nv_bfloat16*)in_vals, n, status);
+  return -(int)cudaGetLastError();
+}
+
+// args: a WidePullArgs block (see psb_wide_args_size); ctx: [N x 64] bf16, 16-byte aligned, local memory
+extern "C" int psb_wide_pull_gemm(const void* args, const void* ctx, uint32_t max_unique, cudaStream_t stream) {
+  WidePullArgs a = *reinterpret_cast<const WidePullArgs*>(args);
+  if (a.N != 64 && a.N != 128) return -(int)cudaErrorInvalidValue;
+  if (a.S < 1 || a.S > PSB_MAX_SHARDS) return -(int)cudaErrorInvalidValue;
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return -(int)cudaErrorNotSupported;
+  CUtensorMap map;
+  cuuint64_t dims[2] = {(cuuint64_t)kWide, (cuuint64_t)a.N};
+  cuuint64_t strides[1] = {(cuuint64_t)kWide * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kWide, (cuuint32_t)a.N};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ctx), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -(int)cudaErrorInvalidValue;
+  size_t smem = (size_t)kTileM * 128 + (size_t)a.N * 128 + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute((const void*)k_wide_pull_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    attr_set = true;
+  }
+  int tiles = (int)((max_unique + kTileM - 1) / kTileM);
+  int grid = tiles < 1 ? 1 : (tiles > 148 * 3 ? 148 * 3 : tiles);
+  k_wide_pull_gemm<<<grid, 128, smem, stream>>>(map, a);
+  return -(int)cudaGetLastError();
+}
+
+extern "C" int psb_wide_rowsum(const float* P, int N, const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z,
+                               const uint32_t* csr_col, const uint32_t* row_ctx, const float* y, float* gcoef,
+                               float* margin, double* stats, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  k_wide_rowsum<<<148 * 4, 256, 0, stream>>>(P, N, row_ptr, n_rows, fixed_z, csr_col, row_ctx, y, gcoef, margin, stats);
+  return -(int)cudaGetLastError();
+}
+extern "C" int psb_wide_push(const void* args, cudaStream_t stream) {
+  WidePushArgs a = *reinterpret_cast<const WidePushArgs*>(args);
+  if (a.S < 1 || a.S > PSB_MAX_SHARDS) return -(int)cudaErrorInvalidValue;
+  k_wide_push<<<148 * 4, 256, 0, stream>>>(a);
+  return -(int)cudaGetLastError();
+}
+extern "C" int psb_wide_apply(const void* args, cudaStream_t stream) {
+  WideApplyArgs a = *reinterpret_cast<const WideApplyArgs*>(args);
+  if (a.S < 1 || a.S > PSB_MAX_SHARDS) return -(int)cudaErrorInvalidValue;
+  static int grid = 0;
+  if (!grid) {
+    int dev = 0, sms = 0, per = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per, (const void*)k_wide_apply, 256, 0);
+    grid = sms * (per < 1 ? 1 : (per > 4 ? 4 : per));
+  }
+  void* params[] = {&a};
+  return -(int)cudaLaunchCooperativeKernel((const void*)k_wide_apply, dim3(grid), dim3(256), params, 0, stream);
+}
+extern "C" int psb_wide_args_size(int which) {
+  return which == 0 ? (int)sizeof(WidePullArgs) : which == 1 ? (int)sizeof(WidePushArgs) : (int)sizeof(WideApplyArgs);
+}

@@ -1,0 +1,195 @@
+"""Wide-value shards: 64-wide bf16 vectors per key with fp32 AdaGrad accumulators.
+
+The data plane mirrors :mod:`dataplane` (symmetric heap, per-(ring slot, source)
+inboxes, release/acquire flags), with 128-byte value rows instead of scalars. The
+pull is fused with the tensor-core product against the batch's context matrix
+(``k_wide_pull_gemm``: tcgen05.mma, accumulator in TMEM, context matrix by TMA).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..ops import _lib
+from ..ops._lib import MAX_SHARDS, check, ptr, stream_ptr
+from ..utils.range import Range, shard_bounds
+from .fabric import Fabric, HeapLayout
+
+_vp, _u32, _u64, _i32, _f32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int, C.c_float
+WIDTH = 64
+
+
+class _PullArgs(C.Structure):
+    _fields_ = [("S", _i32), ("N", _i32), ("keys", _vp * MAX_SHARDS), ("vals", _vp * MAX_SHARDS),
+                ("mask", _u64 * MAX_SHARDS), ("key_begin", _u64 * MAX_SHARDS), ("slot_mult", _u64 * MAX_SHARDS),
+                ("ukeys", _vp), ("n_unique", _vp), ("own_off", _vp), ("P", _vp), ("v_local", _vp), ("status", _vp)]
+
+
+class _PushArgs(C.Structure):
+    _fields_ = [("S", _i32), ("N", _i32), ("ts1", _u32), ("inbox_cap", _u32),
+                ("inbox_keys", _vp * MAX_SHARDS), ("inbox_vals", _vp * MAX_SHARDS),
+                ("ready", _vp * MAX_SHARDS), ("count", _vp * MAX_SHARDS),
+                ("ukeys", _vp), ("n_unique", _vp), ("own_off", _vp), ("seg_off", _vp), ("csc_row", _vp),
+                ("gcoef", _vp), ("row_ctx", _vp), ("ctx", _vp), ("done", _vp), ("status", _vp)]
+
+
+class _ApplyArgs(C.Structure):
+    _fields_ = [("S", _i32), ("ts1", _u32), ("inbox_cap", _u32), ("keys", _vp), ("vals", _vp), ("acc", _vp),
+                ("mask", _u64), ("key_begin", _u64), ("slot_mult", _u64),
+                ("inbox_keys", _vp * MAX_SHARDS), ("inbox_vals", _vp * MAX_SHARDS),
+                ("ready", _vp * MAX_SHARDS), ("count", _vp * MAX_SHARDS), ("alive", C.c_uint8 * MAX_SHARDS),
+                ("alpha", _f32), ("beta", _f32), ("wait_iters", _u32),
+                ("applied", _vp), ("bar", _vp), ("done", _vp), ("status", _vp)]
+
+
+def _declare():
+    L = _lib.lib()
+    if getattr(L, "_wide_declared", False):
+        return L
+    L.psb_wide_init.argtypes = [_vp, _vp, _vp, _u64, _vp]
+    L.psb_wide_load.argtypes = [_vp, _vp, _u64, _u64, _u64, _vp, _vp, _u32, _vp, _vp]
+    L.psb_wide_pull_gemm.argtypes = [_vp, _vp, _u32, _vp]
+    L.psb_wide_rowsum.argtypes = [_vp, _i32, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]
+    L.psb_wide_push.argtypes = [_vp, _vp]
+    L.psb_wide_apply.argtypes = [_vp, _vp]
+    L.psb_wide_args_size.argtypes = [_i32]
+    for i, st in enumerate((_PullArgs, _PushArgs, _ApplyArgs)):
+        if L.psb_wide_args_size(i) != C.sizeof(st):
+            raise RuntimeError(f"{st.__name__}: binding is {C.sizeof(st)} bytes, library expects {L.psb_wide_args_size(i)}")
+    L._wide_declared = True
+    return L
+
+
+@dataclass
+class WideConfig:
+    table_capacity: int              # slots per shard (power of two)
+    inbox_cap: int                   # records per (owner, source) inbox
+    ring: int = 2
+    alpha: float = 0.05              # AdaGrad: eta = alpha / (sqrt(sum g^2) + beta)
+    beta: float = 1.0
+    key_range: Range = field(default_factory=Range.all)
+    ordered_slots: bool = True
+
+
+def wide_layout(cfg: WideConfig, world: int) -> HeapLayout:
+    assert cfg.table_capacity & (cfg.table_capacity - 1) == 0
+    lay = HeapLayout(align=1024)
+    lay.add("ctrl", 4096)
+    lay.add("keys", cfg.table_capacity * 8)
+    lay.add("vals", cfg.table_capacity * WIDTH * 2)
+    lay.add("acc", cfg.table_capacity * WIDTH * 4)
+    lay.add("inbox_keys", cfg.ring * world * cfg.inbox_cap * 8)
+    lay.add("inbox_vals", cfg.ring * world * cfg.inbox_cap * WIDTH * 2)
+    return lay
+
+
+class WidePlane:
+    """One wide shard + worker endpoint."""
+
+    def __init__(self, fabric: Fabric, cfg: WideConfig):
+        self.L = _declare()
+        self.fabric, self.cfg = fabric, cfg
+        self.rank, self.S = fabric.rank, fabric.world
+        self.lay = wide_layout(cfg, self.S)
+        assert self.lay.total() <= fabric.heap_bytes
+        dev = fabric.device
+        self.device = dev
+        self.bounds_host = shard_bounds(cfg.key_range, self.S)
+        self.bounds = torch.tensor([b if b < (1 << 63) else b - (1 << 64) for b in self.bounds_host], dtype=torch.int64, device=dev)
+        self.slot_mult = []
+        for s in range(self.S):
+            size = self.bounds_host[s + 1] - self.bounds_host[s]
+            m = (cfg.table_capacity << 64) // size if (cfg.ordered_slots and size > cfg.table_capacity) else 0
+            self.slot_mult.append(m if m < (1 << 64) else 0)
+        self.sync = torch.zeros(16, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.stats = torch.zeros(4, dtype=torch.float64, device=dev)
+        check(self.L.psb_wide_init(self._p("keys"), self._p("vals"), self._p("acc"), cfg.table_capacity, stream_ptr()), "wide_init")
+
+    def _p(self, name, rank=None, off=0):
+        return self.fabric.ptr(self.rank if rank is None else rank, self.lay[name] + off)
+
+    def _ctrl(self, rank, word):
+        return self._p("ctrl", rank, 4 * word)
+
+    def _ready(self, owner, q, src):
+        return self._ctrl(owner, 8 + q * self.S + src)
+
+    def _count(self, owner, q, src):
+        return self._ctrl(owner, 8 + self.cfg.ring * self.S + q * self.S + src)
+
+    def _ik(self, owner, q, src):
+        return self._p("inbox_keys", owner, ((q * self.S + src) * self.cfg.inbox_cap) * 8)
+
+    def _iv(self, owner, q, src):
+        return self._p("inbox_vals", owner, ((q * self.S + src) * self.cfg.inbox_cap) * WIDTH * 2)
+
+    def load(self, keys_u64: np.ndarray, rows: torch.Tensor):
+        """Insert (key, 64-value row) pairs that belong to this shard."""
+        k = torch.from_numpy(np.ascontiguousarray(keys_u64).view(np.int64)).to(self.device)
+        v = rows.to(self.device, torch.bfloat16).contiguous()
+        check(self.L.psb_wide_load(self._p("keys"), self._p("vals"), self.cfg.table_capacity - 1, self.bounds_host[self.rank],
+                                   self.slot_mult[self.rank], ptr(k), ptr(v), k.numel(), ptr(self.status), stream_ptr()), "wide_load")
+        torch.cuda.current_stream().synchronize()
+
+    def pull_gemm(self, b, ctx: torch.Tensor, P: torch.Tensor, v_local: Optional[torch.Tensor] = None, stream=None):
+        """``P[u, n] = <value row of unique key u, ctx[n]>`` for the batch ``b``.
+        ``ctx``: [N, 64] bf16 with N in (64, 128)."""
+        a = _PullArgs()
+        a.S, a.N = self.S, ctx.shape[0]
+        for s in range(self.S):
+            a.keys[s], a.vals[s] = self._p("keys", s), self._p("vals", s)
+            a.mask[s], a.key_begin[s], a.slot_mult[s] = self.cfg.table_capacity - 1, self.bounds_host[s], self.slot_mult[s]
+        a.ukeys, a.n_unique, a.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
+        a.P, a.v_local, a.status = ptr(P), ptr(v_local), ptr(self.status)
+        assert ctx.dtype == torch.bfloat16 and ctx.is_contiguous() and ctx.shape[1] == WIDTH
+        check(self.L.psb_wide_pull_gemm(C.byref(a), ptr(ctx), b.max_nnz, stream_ptr(stream)), "wide_pull_gemm")
+
+    def rowsum(self, b, P: torch.Tensor, N: int, row_ctx: Optional[torch.Tensor] = None, stream=None):
+        check(self.L.psb_wide_rowsum(ptr(P), N, ptr(b.row_ptr), b.n_rows, b.fixed_z, ptr(b.csr_col), ptr(row_ctx), ptr(b.y),
+                                     ptr(b.gcoef), ptr(b.margin), ptr(self.stats), stream_ptr(stream)), "wide_rowsum")
+
+    def push(self, b, ctx: torch.Tensor, ts: int, row_ctx: Optional[torch.Tensor] = None, stream=None):
+        q = ts % self.cfg.ring
+        a = _PushArgs()
+        a.S, a.N, a.ts1, a.inbox_cap = self.S, ctx.shape[0], ts + 1, self.cfg.inbox_cap
+        for s in range(self.S):
+            a.inbox_keys[s], a.inbox_vals[s] = self._ik(s, q, self.rank), self._iv(s, q, self.rank)
+            a.ready[s], a.count[s] = self._ready(s, q, self.rank), self._count(s, q, self.rank)
+        a.ukeys, a.n_unique, a.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
+        a.seg_off, a.csc_row, a.gcoef, a.row_ctx, a.ctx = ptr(b.seg_off), ptr(b.csc_row), ptr(b.gcoef), ptr(row_ctx), ptr(ctx)
+        a.done, a.status = self.sync.data_ptr() + 8, ptr(self.status)
+        check(self.L.psb_wide_push(C.byref(a), stream_ptr(stream)), "wide_push")
+
+    def apply(self, ts: int, wait_iters: int = 0, stream=None):
+        q = ts % self.cfg.ring
+        a = _ApplyArgs()
+        a.S, a.ts1, a.inbox_cap = self.S, ts + 1, self.cfg.inbox_cap
+        a.keys, a.vals, a.acc = self._p("keys"), self._p("vals"), self._p("acc")
+        a.mask, a.key_begin, a.slot_mult = self.cfg.table_capacity - 1, self.bounds_host[self.rank], self.slot_mult[self.rank]
+        for r in range(self.S):
+            a.inbox_keys[r], a.inbox_vals[r] = self._ik(self.rank, q, r), self._iv(self.rank, q, r)
+            a.ready[r], a.count[r], a.alive[r] = self._ready(self.rank, q, r), self._count(self.rank, q, r), 1
+        a.alpha, a.beta, a.wait_iters = self.cfg.alpha, self.cfg.beta, wait_iters
+        a.applied, a.bar, a.done, a.status = self._ctrl(self.rank, 0), self.sync.data_ptr() + 16, self.sync.data_ptr() + 24, ptr(self.status)
+        check(self.L.psb_wide_apply(C.byref(a), stream_ptr(stream)), "wide_apply")
+
+    def lookup(self, keys_u64: np.ndarray) -> torch.Tensor:
+        """Rows of ``keys`` owned by this shard (zeros if absent), for tests and dumps."""
+        cap = self.cfg.table_capacity
+        tk = self.fabric.view(self.lay["keys"], (cap,), torch.int64).cpu().numpy().view(np.uint64)
+        tv = self.fabric.view(self.lay["vals"], (cap, WIDTH), torch.bfloat16).cpu()
+        pos = {int(k): i for i, k in enumerate(tk.tolist()) if k != (1 << 64) - 1}
+        out = torch.zeros(len(keys_u64), WIDTH, dtype=torch.bfloat16)
+        for i, k in enumerate(keys_u64.tolist()):
+            j = pos.get(int(k))
+            if j is not None:
+                out[i] = tv[j]
+        return out
+
+    def check_status(self, what="wide plane"):
+        _lib.check_status(self.status, what)

@@ -1,0 +1,97 @@
+"""Wide-value path: tcgen05 pull+GEMM, row sums, push and AdaGrad apply against PyTorch fp32."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(S, N, rows=300, z=12, n_feat=2500, seed=0):
+    from parameter_server_b200.ops.localize import LocalBatch
+    from parameter_server_b200.parallel.fabric import Fabric
+    from parameter_server_b200.parallel.wide import WideConfig, WidePlane, wide_layout
+    from parameter_server_b200.utils.oracle import hash_id_to_key
+    rng = np.random.default_rng(seed)
+    cfg = WideConfig(table_capacity=1 << 13, inbox_cap=rows * z, ring=2, alpha=0.1, beta=1.0)
+    fabs = Fabric.emulated(S, wide_layout(cfg, S).total())
+    planes = [WidePlane(f, cfg) for f in fabs]
+    all_ids = np.arange(n_feat)
+    all_keys = hash_id_to_key(all_ids, 11)
+    table = (torch.randn(n_feat, 64) * 0.5).to(torch.bfloat16)
+    known = rng.random(n_feat) < 0.8                  # 20 % of the keys are not in the table yet
+    for p in planes:
+        lo, hi = p.bounds_host[p.rank], p.bounds_host[p.rank + 1]
+        sel = known & (all_keys >= np.uint64(lo)) & (all_keys < np.uint64(min(hi, (1 << 64) - 1)))
+        p.load(all_keys[sel], table[torch.from_numpy(sel)])
+    ids = np.minimum((rng.pareto(1.2, rows * z) * 3).astype(np.int64), n_feat - 1).astype(np.int32)
+    y = np.where(rng.random(rows) < 0.5, 1.0, -1.0).astype(np.float32)
+    b = LocalBatch(rows, rows * z, S, "cuda")
+    b.localize(torch.from_numpy(ids).cuda(), torch.from_numpy(y).cuda(), planes[0].bounds, fixed_z=z, hash_seed=11)
+    ctx = (torch.randn(N, 64) * 0.3).to(torch.bfloat16).cuda()
+    torch.cuda.synchronize()
+    return planes, b, ctx, table, known, all_keys, ids, y, rows, z
+
+
+@pytest.mark.parametrize("S,N", [(1, 64), (2, 128), (1, 128)])
+def test_wide_pull_gemm_matches_fp32_matmul(cuda_lib, S, N):
+    planes, b, ctx, table, known, all_keys, ids, y, rows, z = _setup(S, N)
+    U = int(b.n_unique.item())
+    P = torch.zeros(b.max_nnz, N, device="cuda")
+    V = torch.zeros(b.max_nnz, 64, dtype=torch.bfloat16, device="cuda")
+    planes[0].pull_gemm(b, ctx, P, V)
+    torch.cuda.synchronize()
+    planes[0].check_status()
+    uk = b.ukeys[:U].cpu().numpy().view(np.uint64)
+    idx = {int(k): i for i, k in enumerate(all_keys.tolist())}
+    rows_ref = torch.stack([table[idx[int(k)]] if known[idx[int(k)]] else torch.zeros(64, dtype=torch.bfloat16) for k in uk.tolist()])
+    assert torch.equal(V[:U].cpu(), rows_ref)                                  # the gather is exact
+    ref = rows_ref.float() @ ctx.cpu().float().T
+    assert torch.allclose(P[:U].cpu(), ref, rtol=1e-3, atol=1e-3), float((P[:U].cpu() - ref).abs().max())
+
+
+def test_wide_training_step_matches_reference(cuda_lib):
+    S, N = 2, 64
+    planes, b, ctx, table, known, all_keys, ids, y, rows, z = _setup(S, N, seed=4)
+    U = int(b.n_unique.item())
+    w = planes[0]
+    P = torch.zeros(b.max_nnz, N, device="cuda")
+    w.pull_gemm(b, ctx, P)
+    w.rowsum(b, P, N)
+    w.push(b, ctx, 0)
+    # the other (virtual) worker pushes nothing: publish an empty round for it
+    from parameter_server_b200.ops.localize import LocalBatch
+    empty = LocalBatch(4, 16, S, "cuda")
+    empty.n_unique.zero_(); empty.own_off.zero_(); empty.seg_off.zero_()
+    planes[1].push(empty, ctx, 0)
+    for p in planes:
+        p.apply(0)
+    torch.cuda.synchronize()
+    for p in planes:
+        p.check_status()
+    # reference in fp32
+    idx = {int(k): i for i, k in enumerate(all_keys.tolist())}
+    uk = b.ukeys[:U].cpu().numpy().view(np.uint64)
+    col = b.csr_col[:rows * z].cpu().numpy().reshape(rows, z)
+    Vref = torch.stack([table[idx[int(k)]].float() if known[idx[int(k)]] else torch.zeros(64) for k in uk.tolist()])
+    Pref = Vref @ ctx.cpu().float().T
+    n_of_row = np.arange(rows) % N
+    margin = Pref[torch.from_numpy(col), torch.from_numpy(n_of_row)[:, None]].sum(1)
+    assert torch.allclose(b.margin[:rows].cpu(), margin, rtol=2e-3, atol=2e-3)
+    ym = torch.from_numpy(y) * margin
+    gcoef = -torch.from_numpy(y) * torch.sigmoid(-ym)
+    assert torch.allclose(b.gcoef[:rows].cpu(), gcoef, rtol=2e-3, atol=2e-3)
+    G = torch.zeros(U, 64)
+    C = ctx.cpu().float()
+    for r in range(rows):
+        for j in range(z):
+            G[col[r, j]] += gcoef[r] * C[n_of_row[r]]
+    Gb = G.to(torch.bfloat16).float()                        # gradients travel as bf16
+    acc = Gb * Gb
+    Wref = (Vref - 0.1 / (acc.sqrt() + 1.0) * Gb).to(torch.bfloat16)
+    got = torch.zeros(U, 64, dtype=torch.bfloat16)
+    for p in planes:
+        lo, hi = p.bounds_host[p.rank], p.bounds_host[p.rank + 1]
+        sel = (uk >= np.uint64(lo)) & (uk < np.uint64(min(hi, (1 << 64) - 1)))
+        got[torch.from_numpy(sel)] = p.lookup(uk[sel])
+    diff = (got.float() - Wref.float()).abs()
+    assert float(diff.max()) < 0.02 and float((diff > 0.004).float().mean()) < 0.02
