@@ -110,7 +110,7 @@ def build_core(force: bool = False) -> Path:
         return out
     cxx = os.environ.get("PSB_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
     inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", str(core_dir)]
-    flags = ["-O2", "-g", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-pthread"]
+    flags = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-pthread"]
     objs, jobs = [], []
     for src in sources:
         obj = OBJ / ("core_" + src.stem + ".o")

@@ -115,6 +115,8 @@ class Fabric:
         device may be viewed (the local heap, or any heap of an emulated fabric);
         peer heaps are reached from kernels through :meth:`ptr`."""
         rank = self.rank if rank is None else rank
+        if dtype == torch.bfloat16:     # no array-interface code for bf16: alias as int16 and reinterpret
+            return self.view(offset, shape, torch.int16, rank).view(torch.bfloat16)
         n = int(np.prod(shape)) if len(shape) else 1
         assert offset + n * torch.empty((), dtype=dtype).element_size() <= self.heap_bytes
         raw = _RawCuda(self.bases[rank] + offset, shape, _TORCH2NP[dtype], self)
