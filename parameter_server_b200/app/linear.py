@@ -1,0 +1,342 @@
+"""Linear methods on the GPUs, configured by the reference's text format.
+
+    python -m parameter_server_b200.app.linear -app_file online_l1lr.conf            # one GPU
+    python -m torch.distributed.run --nproc-per-node 8 -m parameter_server_b200.app.linear -app_file x.conf
+
+Accepts the ``PS.LM.Config`` text format (``app/linear_method/proto/linear.proto:7-101``):
+``async_sgd { ... }`` trains FTRL-proximal / AdaGrad / SGD through the device
+parameter server (one shard + one worker per GPU), ``darlin { ... }`` runs block
+coordinate descent, and a configuration with only ``validation_data`` +
+``model_input`` evaluates a saved model. The model is written as one text file
+per shard, ``<model_output.file>_S<rank>``, one ``key<TAB>weight`` line per
+non-zero weight, which is what the reference's servers write
+(``parameter/kv_map.h:100-117``) and what its evaluator reads back.
+"""
+from __future__ import annotations
+
+import argparse
+import glob
+import os
+import sys
+import time
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from ..system import core
+
+
+def _files(conf_data) -> List[str]:
+    pats = conf_data.get("file", [])
+    pats = pats if isinstance(pats, list) else [pats]
+    return list(core.search_files(pats))
+
+
+def _penalty(conf):
+    p = conf.get("penalty", {})
+    lam = p.get("lambda", ["0"])
+    lam = lam if isinstance(lam, list) else [lam]
+    lam = [float(x) for x in lam]
+    if p.get("type", "L1") == "L2":
+        return 0.0, lam[0]
+    return lam[0], (lam[1] if len(lam) > 1 else 0.0)
+
+
+def _dist():
+    import torch.distributed as dist
+    if "RANK" in os.environ and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        if not dist.is_initialized():
+            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+            dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+        return dist, dist.get_rank(), dist.get_world_size()
+    return None, 0, 1
+
+
+def format_weight(v: float) -> str:
+    """Default iostream formatting of a float: 6 significant digits."""
+    return "%g" % v
+
+
+def write_model(path: str, keys, weights):
+    with open(path, "w") as out:
+        for k, v in zip(keys.tolist(), weights.tolist()):
+            out.write(f"{k}\t{format_weight(v)}\n")
+
+
+class ProgressPrinter:
+    HEADER = " sec  examples    loss      auc   accuracy   |w|_0  updt ratio"
+
+    def __init__(self):
+        self.t0 = time.time()
+        self.total = 0
+        self.nnz = 0
+        self.printed = False
+
+    def line(self, p) -> str:
+        self.total += int(p["n_examples"])
+        self.nnz += int(p["d_nnz"])
+        n = max(1.0, p["n_examples"])
+        ratio = (p["delta_sum"] ** 0.5) / (p["weight_sum"] ** 0.5) if p["weight_sum"] > 0 else 0.0
+        if not self.printed:
+            print(self.HEADER, flush=True)
+            self.printed = True
+        return (f"{int(time.time() - self.t0):4d}  {self.total:.2e}  {p['loss_sum'] / n:.3e}  {p.get('auc', 0.0):.4f}  "
+                f"{p['n_correct'] / n:.4f}  {self.nnz:.2e}  {ratio:.2e}")
+
+
+def run_async_sgd(conf, verbose=True):
+    from ..models.sparse_lr import SparseLRConfig, SparseLRWorker
+    from ..parallel.dataplane import DataPlane, OptimizerConfig, PlaneConfig, heap_layout
+    from ..parallel.fabric import Fabric
+
+    dist, rank, world = _dist()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    sgd = conf["async_sgd"]
+    l1, l2 = _penalty(conf)
+    lr = conf.get("learning_rate", {})
+    algo = "ftrl" if sgd.get("algo", "FTRL") == "FTRL" else ("adagrad" if sgd.get("ada_grad", "true") == "true" else "sgd")
+    opt = OptimizerConfig(algo=algo, alpha=float(lr.get("alpha", 1)), beta=float(lr.get("beta", 1)), l1=l1, l2=l2,
+                          lr_type="constant" if lr.get("type", "DECAY") == "CONSTANT" else "decay")
+    minibatch = int(sgd.get("minibatch", 1000))
+    tau = int(sgd.get("max_delay", 0))
+    passes = int(sgd.get("num_data_pass", 1))
+    filters = sgd.get("push_filter", [])
+    filters = filters if isinstance(filters, list) else [filters]
+    quant = "none"
+    key_cache = False
+    for f in filters:
+        if f.get("type") == "FIXING_FLOAT":
+            quant = "int8" if int(f.get("num_bytes", 3)) <= 1 else "fp16"
+        if f.get("type") == "KEY_CACHING":
+            key_cache = True
+    data = conf["training_data"]
+    files = _files(data)
+    my_files = files[rank::world]
+    text = data.get("text", "LIBSVM")
+    max_nnz = int(os.environ.get("PSB_MAX_NNZ_PER_ROW", "512")) * minibatch
+    table_cap = 1 << int(os.environ.get("PSB_LOG2_TABLE", "22"))
+    pc = PlaneConfig(table_capacity=table_cap, inbox_cap=max_nnz, ring=tau + 2, quant=quant, key_cache=key_cache,
+                     ordered_slots=os.environ.get("PSB_ORDERED_SLOTS", "0") == "1")
+    hb = heap_layout(pc, world).total()
+    fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
+    plane = DataPlane(fab, pc, opt)
+    worker = SparseLRWorker(plane, SparseLRConfig(max_rows=minibatch, max_nnz=max_nnz, tau=tau, hash_seed=None,
+                                                  pipeline=2, auc=True, real_values=text not in ("SPARSE_BINARY", "ADFEA", "TERAFEA", "CRITEO")))
+    printer = ProgressPrinter()
+    last = time.time()
+    steps = 0
+    for _ in range(passes):
+        # every rank must submit the same number of rounds: ranks that run out of data push empty rounds
+        reader = core.StreamReader(my_files, data.get("format", "TEXT"), text, True)
+        while True:
+            got = reader.read_matrices(minibatch) if my_files else None
+            flag = torch.tensor([0 if got is None else 1], device=dev)
+            if dist is not None:
+                dist.all_reduce(flag)
+            if int(flag.item()) == 0:
+                break
+            if got is None or not got[1]:
+                ids = torch.zeros(0, dtype=torch.int64)
+                y = torch.zeros(0, dtype=torch.float32)
+                rp = torch.zeros(1, dtype=torch.int32)
+                vals = None
+            else:
+                yv, mats = got
+                m = mats[0]
+                ids = torch.from_numpy(m["index"].view(np.int64))
+                rp = torch.from_numpy(m["offset"].astype(np.int32))
+                y = torch.from_numpy(np.where(yv > 0, 1.0, -1.0).astype(np.float32))
+                vals = None if m["binary"] else torch.from_numpy(m["value"])
+            worker.submit(ids.pin_memory(), y.pin_memory(), row_ptr=rp.pin_memory(),
+                          vals=None if vals is None else vals.pin_memory())
+            steps += 1
+            if verbose and time.time() - last >= float(sgd.get("report_interval", 1)):
+                last = time.time()
+                p = _merged_progress(worker, dist, dev)
+                if rank == 0:
+                    print(printer.line(p), flush=True)
+    worker.wait()
+    torch.cuda.synchronize()
+    plane.check_status("async sgd")
+    p = _merged_progress(worker, dist, dev)
+    if rank == 0 and verbose:
+        print(printer.line(p), flush=True)
+    out = conf.get("model_output", {}).get("file")
+    if out:
+        out = out if isinstance(out, str) else out[0]
+        keys, w = plane.dump_nonzero()
+        os.makedirs(os.path.dirname(out) or ".", exist_ok=True)
+        write_model(f"{out}_S{rank}", keys.numpy(), w.numpy())
+    if dist is not None:
+        dist.barrier()
+        fab.close()
+    return dict(steps=steps, examples=printer.total)
+
+
+def _merged_progress(worker, dist, dev):
+    p = worker.read_progress()
+    if worker.auc_hist is not None:
+        h = worker.auc_hist.clone()
+        worker.auc_hist.zero_()
+    else:
+        h = None
+    keys = ["loss_sum", "n_correct", "n_examples", "d_nnz", "weight_sum", "delta_sum", "n_updates"]
+    t = torch.tensor([p[k] for k in keys], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t)
+        if h is not None:
+            dist.all_reduce(h)
+    out = dict(zip(keys, t.tolist()))
+    if h is not None:
+        out["auc"] = auc_from_histogram(h.cpu().numpy())
+    return out
+
+
+def auc_from_histogram(h: np.ndarray) -> float:
+    """AUC from the [2][4096] histogram of sigmoid(margin) by label."""
+    neg, pos = h[:4096].astype(np.float64), h[4096:].astype(np.float64)
+    if pos.sum() == 0 or neg.sum() == 0:
+        return 0.5
+    cum_neg = np.concatenate([[0], np.cumsum(neg)[:-1]])
+    return float((pos * (cum_neg + neg / 2)).sum() / (pos.sum() * neg.sum()))
+
+
+def run_evaluation(conf, verbose=True):
+    """Model evaluation on one GPU (``app/linear_method/model_evaluation.h:27-107``):
+    load ``key value`` files into a device table, stream the validation data,
+    margins by table lookup, AUC / accuracy / logloss."""
+    from ..models.sparse_lr import SparseLRConfig, SparseLRWorker
+    from ..parallel.dataplane import DataPlane, OptimizerConfig, PlaneConfig, heap_layout
+    from ..parallel.fabric import Fabric
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    model_files = _files(conf["model_input"])
+    ks, ws = [], []
+    for f in model_files:
+        for line in open(f):
+            a = line.split()
+            if len(a) == 2:
+                ks.append(int(a[0])); ws.append(float(a[1]))
+    keys = np.array(ks, dtype=np.uint64)
+    cap = 1 << max(12, int(np.ceil(np.log2(max(2, 2 * len(keys))))))
+    chunk = 100000
+    max_nnz = int(os.environ.get("PSB_MAX_NNZ_PER_ROW", "512")) * chunk
+    pc = PlaneConfig(table_capacity=cap, inbox_cap=16, ring=2)
+    fab = Fabric.single(heap_layout(pc, 1).total(), dev)
+    plane = DataPlane(fab, pc, OptimizerConfig())
+    plane.load_state(keys, w=torch.tensor(ws, dtype=torch.float32))
+    worker = SparseLRWorker(plane, SparseLRConfig(max_rows=chunk, max_nnz=max_nnz, hash_seed=None, pipeline=1, real_values=True))
+    data = conf["validation_data"]
+    reader = core.StreamReader(_files(data), data.get("format", "TEXT"), data.get("text", "LIBSVM"), True)
+    ys, ms = [], []
+    while True:
+        got = reader.read_matrices(chunk)
+        if got is None:
+            break
+        yv, mats = got
+        if not mats:
+            continue
+        m = mats[0]
+        b = worker.prepare(torch.from_numpy(m["index"].view(np.int64)).to(dev),
+                           torch.from_numpy(np.where(yv > 0, 1.0, -1.0).astype(np.float32)).to(dev),
+                           row_ptr=torch.from_numpy(m["offset"].astype(np.int32)).to(dev),
+                           vals=None if m["binary"] else torch.from_numpy(m["value"]).to(dev))
+        plane.pull_margin(b)
+        torch.cuda.synchronize()
+        ys.append(yv); ms.append(b.margin[:len(yv)].cpu().numpy())
+    y, margin = np.concatenate(ys), np.concatenate(ms)
+    ev = core.evaluate(y.astype(np.float32), margin.astype(np.float32))
+    if verbose:
+        print(f"load {len(keys)} model entries\nload {len(y)} examples")
+        print(f"auc: {ev['auc']:.6f}\naccuracy: {ev['accuracy']:.6f}\nlogloss: {ev['logloss']:.6f}")
+    return ev
+
+
+def run_darlin(conf, verbose=True):
+    from ..models.darlin import DarlinConfig, DarlinRank, darlin_heap_bytes, run_darlin as drive
+    from ..parallel.fabric import Fabric
+
+    dist, rank, world = _dist()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    d = conf["darlin"]
+    l1, _ = _penalty(conf)
+    data = conf["training_data"]
+    files = _files(data)[rank::world]
+    reader = core.StreamReader(files, data.get("format", "TEXT"), data.get("text", "LIBSVM"), True)
+    idx, off, ys, vs, binary = [], [np.zeros(1, np.int64)], [], [], True
+    while True:
+        got = reader.read_matrices(100000) if files else None
+        if got is None:
+            break
+        yv, mats = got
+        if not mats:
+            continue
+        m = mats[0]
+        idx.append(m["index"]); off.append(m["offset"][1:].astype(np.int64) + off[-1][-1]); ys.append(yv)
+        if not m["binary"]:
+            binary = False; vs.append(m["value"])
+    keys = np.concatenate(idx) if idx else np.zeros(0, np.uint64)
+    row_ptr = np.concatenate(off).astype(np.int32)
+    y = np.where(np.concatenate(ys) > 0, 1.0, -1.0).astype(np.float32) if ys else np.zeros(0, np.float32)
+    cfg = DarlinConfig(lambda_l1=l1, eta=float(conf.get("learning_rate", {}).get("alpha", 1.0)),
+                       delta_init=float(d.get("delta_init_value", 1)), delta_max=float(d.get("delta_max_value", 5)),
+                       kkt_ratio=float(d.get("kkt_filter_threshold_ratio", 10)), max_pass=int(d.get("max_pass_of_data", 10)),
+                       epsilon=float(d.get("epsilon", 1e-4)), tau=int(d.get("max_block_delay", 0)),
+                       block_cols=int(os.environ.get("PSB_DARLIN_BLOCK", str(1 << 16))),
+                       random_block_order=d.get("random_feature_block_order", "true") == "true")
+    hb = darlin_heap_bytes(cfg, world)
+    fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
+    uniq = np.unique(keys)
+    if dist is not None:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, uniq)
+        uniq = np.unique(np.concatenate(gathered))
+    r = DarlinRank(fab, cfg, torch.from_numpy(keys.view(np.int64)).to(dev), torch.from_numpy(y).to(dev),
+                   row_ptr=torch.from_numpy(row_ptr).to(dev),
+                   vals=None if binary else torch.from_numpy(np.concatenate(vs)).to(dev),
+                   global_keys=torch.from_numpy(uniq.view(np.int64)).to(dev))
+
+    def all_reduce(vals, op):
+        if dist is None:
+            return vals
+        t = torch.tensor(vals, dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM if op == "sum" else dist.ReduceOp.MAX)
+        return t.tolist()
+
+    n_ex = int(all_reduce([float(len(y))], "sum")[0])
+    if rank == 0 and verbose:
+        print("  iter |  objective    relative   |w|_0   | violation  active set")
+    hist = drive([r], all_reduce=all_reduce if dist is not None else None, verbose=verbose and rank == 0, num_examples=n_ex)
+    out = conf.get("model_output", {}).get("file")
+    if out:
+        out = out if isinstance(out, str) else out[0]
+        k, w = r.my_model()
+        os.makedirs(os.path.dirname(out) or ".", exist_ok=True)
+        write_model(f"{out}_S{rank}", k, w)
+    if dist is not None:
+        dist.barrier()
+        fab.close()
+    return hist
+
+
+def main(argv: Optional[List[str]] = None):
+    ap = argparse.ArgumentParser(prefix_chars="-")
+    ap.add_argument("-app_file", "--app_file", default="")
+    ap.add_argument("-app_conf", "--app_conf", default="")
+    args, _ = ap.parse_known_args(argv)
+    text = (open(args.app_file).read() if args.app_file else "") + args.app_conf
+    conf = core.parse_text_proto(text)
+    from .. import _build
+    _build.build_cuda()
+    if "darlin" in conf:
+        return run_darlin(conf)
+    if "async_sgd" in conf:
+        return run_async_sgd(conf)
+    if "validation_data" in conf:
+        return run_evaluation(conf)
+    raise SystemExit("the configuration selects no application (async_sgd, darlin or validation_data)")
+
+
+if __name__ == "__main__":
+    main()
