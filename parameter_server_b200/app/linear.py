@@ -73,12 +73,12 @@ class ProgressPrinter:
         self.nnz = 0
         self.printed = False
 
-    def line(self, p) -> str:
+    def line(self, p, header: bool = True) -> str:
         self.total += int(p["n_examples"])
         self.nnz += int(p["d_nnz"])
         n = max(1.0, p["n_examples"])
         ratio = (p["delta_sum"] ** 0.5) / (p["weight_sum"] ** 0.5) if p["weight_sum"] > 0 else 0.0
-        if not self.printed:
+        if header and not self.printed:
             print(self.HEADER, flush=True)
             self.printed = True
         return (f"{int(time.time() - self.t0):4d}  {self.total:.2e}  {p['loss_sum'] / n:.3e}  {p.get('auc', 0.0):.4f}  "
@@ -151,17 +151,17 @@ def run_async_sgd(conf, verbose=True):
             worker.submit(ids.pin_memory(), y.pin_memory(), row_ptr=rp.pin_memory(),
                           vals=None if vals is None else vals.pin_memory())
             steps += 1
-            if verbose and time.time() - last >= float(sgd.get("report_interval", 1)):
+            if time.time() - last >= float(sgd.get("report_interval", 1)):
                 last = time.time()
-                p = _merged_progress(worker, dist, dev)
-                if rank == 0:
-                    print(printer.line(p), flush=True)
+                line = printer.line(_merged_progress(worker, dist, dev), header=verbose and rank == 0)
+                if rank == 0 and verbose:
+                    print(line, flush=True)
     worker.wait()
     torch.cuda.synchronize()
     plane.check_status("async sgd")
-    p = _merged_progress(worker, dist, dev)
+    line = printer.line(_merged_progress(worker, dist, dev), header=verbose and rank == 0)
     if rank == 0 and verbose:
-        print(printer.line(p), flush=True)
+        print(line, flush=True)
     out = conf.get("model_output", {}).get("file")
     if out:
         out = out if isinstance(out, str) else out[0]

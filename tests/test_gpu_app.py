@@ -20,7 +20,7 @@ training_data {{ format: TEXT text: SPARSE_BINARY file: "{train}/part.*" }}
 model_output {{ format: TEXT file: "{out}/darlin" }}
 penalty {{ type: L1 lambda: 2 }}
 learning_rate {{ type: CONSTANT alpha: 0.5 }}
-darlin {{ max_pass_of_data: 8 epsilon: 1e-5 max_block_delay: 1 }}
+darlin {{ max_pass_of_data: 8 epsilon: 1e-5 max_block_delay: 0 }}
 """
 CONF_EVAL = """
 validation_data {{ format: TEXT text: SPARSE_BINARY file: "{train}/part.*" }}
