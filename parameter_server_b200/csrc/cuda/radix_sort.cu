@@ -20,8 +20,12 @@
 
 namespace psb {
 
-static constexpr int kSortThreads = 256;
-static constexpr int kSortItems = 16;
+// 512 threads x 8 keys: the same 4096-key tile as 256 x 16, but half the
+// registers per thread (two resident CTAs = 32 warps per SM) and a ranking chain
+// of 8 dependent steps instead of 16.
+static constexpr int kSortThreads = 512;
+static constexpr int kSortWarps = kSortThreads / 32;
+static constexpr int kSortItems = 8;
 static constexpr int kSortTile = kSortThreads * kSortItems;  // 4096
 static constexpr int kRadixBits = 8;
 static constexpr int kRadix = 1 << kRadixBits;
@@ -62,8 +66,8 @@ __global__ void __launch_bounds__(256) k_sort_histogram(
     if (sh[i]) atomicAdd(&ghist[i], sh[i]);
 }
 
-// Exclusive scan of one value per thread across a 256-thread block.
-__device__ __forceinline__ u32 block_excl_scan_256(u32 v, u32* s_warp /*8 words*/, u32* total) {
+// Exclusive scan of one value per thread across the block (kSortWarps warps).
+__device__ __forceinline__ u32 block_excl_scan_256(u32 v, u32* s_warp /*kSortWarps words*/, u32* total) {
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   u32 x = v;
 #pragma unroll
@@ -75,7 +79,7 @@ __device__ __forceinline__ u32 block_excl_scan_256(u32 v, u32* s_warp /*8 words*
   __syncthreads();
   u32 base = 0, tot = 0;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < kSortWarps; ++i) {
     u32 t = s_warp[i];
     if (i < w) base += t;
     tot += t;
@@ -86,20 +90,20 @@ __device__ __forceinline__ u32 block_excl_scan_256(u32 v, u32* s_warp /*8 words*
 }
 
 // One digit pass. `status` holds ntiles*256 zeroed words for this pass.
-__global__ void __launch_bounds__(kSortThreads) k_sort_onesweep(
+__global__ void __launch_bounds__(kSortThreads, 2) k_sort_onesweep(
     const u64* __restrict__ keys_in, const u32* __restrict__ vals_in, u64* __restrict__ keys_out,
     u32* __restrict__ vals_out, u32 n, int shift, u32 dmask, const u32* __restrict__ ghist,
     u32* __restrict__ ticket, u32* __restrict__ status, u32* __restrict__ err) {
   __shared__ u64 s_keys[kSortTile];            // 32 KB, reused for payloads
-  __shared__ u32 s_cnt[8 * kRadix];            // per-warp digit counters, 8 KB
+  __shared__ unsigned short s_cnt[kSortWarps * kRadix];  // per-warp digit counters (<= 256 each), 8 KB
   __shared__ u32 s_dstart[kRadix];             // tile-local start of each digit
   __shared__ u32 s_gbase[kRadix];              // global dst = s_gbase[d] + p
-  __shared__ u32 s_warp[8];
+  __shared__ u32 s_warp[kSortWarps];
   __shared__ u32 s_tile;
 
   const int t = threadIdx.x, lane = t & 31, w = t >> 5;
   if (t == 0) s_tile = atomicAdd(ticket, 1u);
-  for (int i = t; i < 8 * kRadix; i += kSortThreads) s_cnt[i] = 0;
+  for (int i = t; i < kSortWarps * kRadix; i += kSortThreads) s_cnt[i] = 0;
   __syncthreads();
   const u32 tile = s_tile;
   const u32 tile_base = tile * (u32)kSortTile;
@@ -124,30 +128,33 @@ __global__ void __launch_bounds__(kSortThreads) k_sort_onesweep(
     u32 old = 0;
     if (lane == leader) {
       old = s_cnt[w * kRadix + d];
-      s_cnt[w * kRadix + d] = old + __popc(m);
+      s_cnt[w * kRadix + d] = (unsigned short)(old + __popc(m));
     }
     old = __shfl_sync(0xffffffffu, old, leader);
     off[i] = old + __popc(m & lt);
     __syncwarp();
   }
   __syncthreads();
-  // ---- per digit (thread t owns digit t): prefix over warps, tile total ----
+  // ---- per digit (thread t < 256 owns digit t): prefix over warps, tile total ----
+  const bool owner = t < kRadix;
   u32 total = 0;
-#pragma unroll
-  for (int ww = 0; ww < 8; ++ww) {
-    u32 c = s_cnt[ww * kRadix + t];
-    s_cnt[ww * kRadix + t] = total;
-    total += c;
-  }
-  // publish the tile aggregate early so successors can move on. The status word
-  // itself is the only datum exchanged, so relaxed gpu-scope accesses suffice.
   u32* my_status = status + (size_t)tile * kRadix;
-  st_relaxed_gpu(&my_status[t], (tile == 0 ? kFlagIncl : kFlagAgg) | total);
+  if (owner) {
+#pragma unroll
+    for (int ww = 0; ww < kSortWarps; ++ww) {
+      u32 c = s_cnt[ww * kRadix + t];
+      s_cnt[ww * kRadix + t] = (unsigned short)total;
+      total += c;
+    }
+    // publish the tile aggregate early so successors can move on. The status word
+    // itself is the only datum exchanged, so relaxed gpu-scope accesses suffice.
+    st_relaxed_gpu(&my_status[t], (tile == 0 ? kFlagIncl : kFlagAgg) | total);
+  }
 
   u32 dstart = block_excl_scan_256(total, s_warp, nullptr);
-  s_dstart[t] = dstart;
+  if (owner) s_dstart[t] = dstart;
   // global exclusive base of digit t
-  u32 gh = ghist[t];
+  u32 gh = owner ? ghist[t] : 0u;
   u32 gex = block_excl_scan_256(gh, s_warp, nullptr);
 
   // ---- decoupled look-back for digit t, kLookBatch predecessors per round trip ----
@@ -155,7 +162,7 @@ __global__ void __launch_bounds__(kSortThreads) k_sort_onesweep(
   // many predecessors that have only published aggregates; fetching them in
   // batches of independent loads hides the L2 latency of that walk.
   u32 ex = 0;
-  if (tile > 0) {
+  if (tile > 0 && owner) {
     constexpr int kLookBatch = 8;
     long long p = (long long)tile - 1;
     u32 spins = 0;
@@ -183,7 +190,7 @@ __global__ void __launch_bounds__(kSortThreads) k_sort_onesweep(
     }
     st_relaxed_gpu(&my_status[t], kFlagIncl | ((ex + total) & kValMask));
   }
-  s_gbase[t] = gex + ex - dstart;
+  if (owner) s_gbase[t] = gex + ex - dstart;
   __syncthreads();
 
   // ---- scatter keys into shared memory in digit order ----
