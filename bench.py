@@ -102,6 +102,8 @@ def main():
                     help="also time each stage (localise / pull+margins / push / apply) with CUDA events, "
                          "stages run back to back on one stream")
     ap.add_argument("--key-cache", action="store_true", help="enable the key-caching filter")
+    ap.add_argument("--pull", default="exchange", choices=["exchange", "one-sided"],
+                    help="exchange: keys to owners + weights back as bulk peer stores; one-sided: remote table probes")
     ap.add_argument("--hashed-slots", action="store_true",
                     help="re-hash keys into table slots instead of the order-preserving slot map")
     args = ap.parse_args()
@@ -141,7 +143,8 @@ def main():
         cap *= 2
     inbox_cap = nnz if world == 1 else (nnz // world) * 5 // 4 + 4096
     pc = PlaneConfig(table_capacity=cap, inbox_cap=inbox_cap, ring=args.tau + 2, quant=args.quant,
-                     ordered_slots=not args.hashed_slots, key_cache=args.key_cache)
+                     ordered_slots=not args.hashed_slots, key_cache=args.key_cache,
+                     pull_cap=nnz if (args.pull == "exchange" and args.impl == "ours") else 0)
     opt = OptimizerConfig(algo="ftrl", alpha=0.1, beta=1.0, l1=1.0, l2=0.1)
     hb = heap_layout(pc, world).total()
     fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
@@ -247,9 +250,12 @@ def main():
             b = worker.prepare(ids, y, fixed_z=z)
             ev[1].record()
             t_ = worker.step_no
-            plane.pull_margin(b, need_applied=max(0, t_ - args.tau))
+            if pc.pull_cap:
+                plane.pull_exchange(b, t_, need_applied=max(0, t_ - args.tau))
+            else:
+                plane.pull_margin(b, need_applied=max(0, t_ - args.tau))
             ev[2].record()
-            plane.push(b, t_)
+            plane.push(b, t_, send_keys=not pc.pull_cap)
             ev[3].record()
             plane.apply(t_)
             ev[4].record()
@@ -278,7 +284,7 @@ def main():
             "config": {"model": "FTRL-proximal L1/L2 logistic regression", "global_batch": world * rows,
                        "rows_per_worker": rows, "nnz_per_row": z, "keys": f"2^{args.log2_keys} hashed uint64",
                        "seq_len": z, "parallelism": f"dp{world} x key-range shards{world}", "tau": args.tau,
-                       "alpha": 0.1, "beta": 1.0, "l1": 1.0, "l2": 0.1, "quant": args.quant, "ordered_slots": not args.hashed_slots,
+                       "alpha": 0.1, "beta": 1.0, "l1": 1.0, "l2": 0.1, "quant": args.quant, "ordered_slots": not args.hashed_slots, "pull": args.pull,
                        "unique_keys_per_step_per_worker": u_mean,
                        "push_pull_keys_per_s": 2 * u_mean * world * args.steps / (ms * 1e-3),
                        "l2_policy": f"inputs larger than L2: {args.pool} distinct minibatches of "

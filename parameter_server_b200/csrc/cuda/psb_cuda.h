@@ -133,6 +133,61 @@ typedef struct {
   uint32_t* status;
 } PsbApplyParams;
 
+// Two-sided pull fused with the margins (kernel F2, exchange form). One launch on
+// every rank does three things: (a) store this worker's keys into the owners'
+// request areas (coalesced peer stores, release flags); (b) as an owner, wait for
+// each source's request, locate / insert the keys in the local table, remember
+// the slots for the push of the same round, and store the weights straight into
+// the requester's response buffer (coalesced peer stores, release flags); (c) as a
+// worker again, wait for the owners' responses and compute margins, loss and
+// d loss / d margin. Only bulk, coalesced traffic crosses NVLink.
+typedef struct {
+  int S;
+  int me;
+  uint32_t ts1;
+  uint32_t need_applied;      // owner role: serve only after my shard applied this many rounds
+  uint32_t req_cap;           // keys per (owner, source) request area
+  uint32_t wait_iters;        // 0 = default budget
+  int phases;                 // bit 0: (a), bit 1: (b), bit 2: (c); 7 = all in one launch. Separate
+                              // launches exist for single-GPU emulation of several ranks, where a
+                              // launch must never wait for a later launch.
+  // (a) worker -> owners
+  psb_u64* req_keys[PSB_MAX_SHARDS];     // owner s: request area of this source
+  uint32_t* req_hdr[PSB_MAX_SHARDS];     // owner s: {count, base offset in my response buffer}
+  uint32_t* req_ready[PSB_MAX_SHARDS];   // owner s: flag of this source
+  // (b) owner role
+  const psb_u64* my_req_keys[PSB_MAX_SHARDS];   // my request areas, one per source
+  const uint32_t* my_req_hdr[PSB_MAX_SHARDS];
+  const uint32_t* my_req_ready[PSB_MAX_SHARDS];
+  float* resp_w[PSB_MAX_SHARDS];         // requester r: its response buffer
+  uint32_t* resp_ready[PSB_MAX_SHARDS];  // requester r: flag of this owner
+  uint32_t* slot_cache[PSB_MAX_SHARDS];  // per source: slot of every requested key (reused by the apply)
+  uint8_t alive[PSB_MAX_SHARDS];
+  void* table;
+  psb_u64 mask, key_begin, slot_mult;
+  const uint32_t* applied;               // my applied counter
+  // (c) worker
+  const float* my_resp_w;                // my response buffer (weights per unique key)
+  const uint32_t* my_resp_ready[PSB_MAX_SHARDS];
+  const psb_u64* ukeys;
+  const uint32_t* n_unique;
+  const uint32_t* own_off;
+  float* grad_zero;
+  const uint32_t* row_ptr;
+  uint32_t n_rows, fixed_z;
+  const uint32_t* csr_col;
+  const float* csr_val;
+  const float* y;
+  int loss;
+  float* gcoef;
+  float* margin;
+  double* stats;
+  uint32_t* auc_hist;
+  uint32_t* done;                        // 2 zeroed words
+  uint32_t* status;
+} PsbPullExchangeParams;
+
+int psb_pull_exchange(const PsbPullExchangeParams* p, cudaStream_t stream);
 int psb_table_init(void* table, psb_u64 capacity, cudaStream_t stream);
 int psb_pull_margin(const PsbPullParams* p, cudaStream_t stream);
 int psb_push(const PsbPushParams* p, cudaStream_t stream);
@@ -151,7 +206,7 @@ int psb_table_export(const void* table, psb_u64 capacity, psb_u64* out_keys, flo
 
 // number of CTAs a cooperative launch of the three fused kernels uses
 int psb_coop_grid(int which);
-int psb_struct_size(int which);   // 0 pull, 1 push, 2 apply, 3 optimizer, 4/5/6 darlin grad/update/dual
+int psb_struct_size(int which);   // 0 pull, 1 push, 2 apply, 3 optimizer, 4 pull exchange
 
 // ---------------------------------------------------------------- filters / sorted-key utilities
 int psb_key_signature(const psb_u64* keys, const uint32_t* n_ptr, uint32_t max_n, uint32_t* scratch,

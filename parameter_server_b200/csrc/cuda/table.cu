@@ -234,6 +234,135 @@ __global__ void __launch_bounds__(kThreads) k_pull_margin(const PsbPullParams p)
   block_add4(loss_sum, n_correct, n_seen, 0.0, p.stats);
 }
 
+// ------------------------------------------------------------------ F2 (exchange form)
+__global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchangeParams p) {
+  __shared__ u32 s_off[PSB_MAX_SHARDS + 1];
+  __shared__ u32 s_last;
+  __shared__ u32 s_n, s_base;
+  const int S = p.S;
+  const u32 U = *p.n_unique;
+  const u32 iters = p.wait_iters ? p.wait_iters : kPeerWaitIters;
+  if (threadIdx.x <= S) s_off[threadIdx.x] = p.own_off[threadIdx.x];
+  __syncthreads();
+  const u32 gsize = gridDim.x * blockDim.x;
+  const u32 gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  // ---- (a) my keys to their owners
+  if (p.phases & 1) {
+  for (u32 u = gtid; u < U; u += gsize) {
+    int s = owner_of(s_off, S, u);
+    u32 j = u - s_off[s];
+    if (j < p.req_cap) p.req_keys[s][j] = p.ukeys[u];
+    if (p.grad_zero) p.grad_zero[u] = 0.f;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&p.done[0], 1u) + 1 == gridDim.x;
+  __syncthreads();
+  if (s_last && threadIdx.x < S) {
+    int s = threadIdx.x;
+    u32 c = s_off[s + 1] - s_off[s];
+    if (c > p.req_cap) { set_status(p.status, kInboxOverflow); c = p.req_cap; }
+    __threadfence_system();
+    p.req_hdr[s][0] = c;
+    p.req_hdr[s][1] = s_off[s];
+    __threadfence_system();
+    st_release_sys(p.req_ready[s], p.ts1);
+    if (s == 0) atomicExch(&p.done[0], 0u);
+  }
+  }
+  // ---- (b) owner role: serve every source
+  if (p.phases & 2) {
+  if (threadIdx.x == 0 && p.need_applied > 0 && !wait_flag_ge_sys(p.applied, p.need_applied, iters))
+    set_status(p.status, kWaitTimeout);
+  Entry* tab = (Entry*)p.table;
+  const SlotMap sm{p.mask, p.key_begin, p.slot_mult};
+  for (int r = 0; r < S; ++r) {
+    if (!p.alive[r]) continue;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      u32 n = 0, base = 0;
+      if (wait_flag_ge_sys(p.my_req_ready[r], p.ts1, iters)) {
+        n = *((volatile const u32*)&p.my_req_hdr[r][0]);
+        base = *((volatile const u32*)&p.my_req_hdr[r][1]);
+      } else {
+        set_status(p.status, kWaitTimeout);
+      }
+      s_n = min(n, p.req_cap);
+      s_base = base;
+    }
+    __syncthreads();
+    const u32 n = s_n, base = s_base;
+    for (u32 j = gtid; j < n; j += gsize) {
+      u64 key = p.my_req_keys[r][j];
+      long long slot = table_find<true>(tab, sm, key, kMaxProbe);
+      float w = 0.f;
+      u32 sc = 0x7fffffffu;
+      if (slot >= 0) { w = __ldcg(&tab[slot].w); sc = (u32)slot; }
+      else set_status(p.status, kTableFull);
+      p.slot_cache[r][j] = sc;
+      p.resp_w[r][base + j] = w;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&p.done[1], 1u) + 1 == gridDim.x;
+  __syncthreads();
+  if (s_last && threadIdx.x < S && p.alive[threadIdx.x]) {
+    __threadfence_system();
+    st_release_sys(p.resp_ready[threadIdx.x], p.ts1);
+  }
+  if (s_last && threadIdx.x == 0) atomicExch(&p.done[1], 0u);
+  }
+  if (p.n_rows == 0 || !(p.phases & 4)) return;
+  // ---- (c) worker: all owners have answered -> margins
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s)
+      if (p.alive[s] && !wait_flag_ge_sys(p.my_resp_ready[s], p.ts1, iters)) set_status(p.status, kWaitTimeout);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const u32 gwarp = gtid >> 5, nwarps = gsize >> 5;
+  double loss_sum = 0, n_correct = 0, n_seen = 0;
+  for (u32 r = gwarp; r < p.n_rows; r += nwarps) {
+    u32 b, e;
+    if (p.row_ptr) { b = p.row_ptr[r]; e = p.row_ptr[r + 1]; }
+    else { b = r * p.fixed_z; e = b + p.fixed_z; }
+    float acc = 0.f;
+    for (u32 j = b + lane; j < e; j += 32) {
+      float w = __ldcg(&p.my_resp_w[p.csr_col[j]]);
+      acc += p.csr_val ? w * p.csr_val[j] : w;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      float y = p.y[r];
+      float ym = y * acc;
+      float g, l;
+      if (p.loss == PSB_LOSS_LOGIT) {
+        float en = expf(-fabsf(ym));
+        float tau = ym > 0 ? en / (1.f + en) : 1.f / (1.f + en);
+        g = -y * tau;
+        l = log1pf(en) + fmaxf(-ym, 0.f);
+      } else {
+        float h = fmaxf(1.f - ym, 0.f);
+        g = -2.f * y * h;
+        l = h * h;
+      }
+      p.gcoef[r] = g;
+      if (p.margin) p.margin[r] = acc;
+      loss_sum += l;
+      n_correct += (ym > 0.f) ? 1.0 : 0.0;
+      n_seen += 1.0;
+      if (p.auc_hist) {
+        float pr = 1.f / (1.f + expf(-acc));
+        int bin = min(4095, max(0, (int)(pr * 4096.f)));
+        atomicAdd(&p.auc_hist[(y > 0 ? 4096 : 0) + bin], 1u);
+      }
+    }
+  }
+  block_add4(loss_sum, n_correct, n_seen, 0.0, p.stats);
+}
+
 // ------------------------------------------------------------------ F1a: worker push
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -479,11 +608,12 @@ extern "C" int psb_device_sm_count(void) {
 }
 
 extern "C" int psb_coop_grid(int which) {
-  static int g[3] = {0, 0, 0};
-  if (which < 0 || which > 2) return 0;
+  static int g[4] = {0, 0, 0, 0};
+  if (which < 0 || which > 3) return 0;
   if (!g[which]) {
     const void* fn = which == 0 ? (const void*)k_pull_margin
-                   : which == 1 ? (const void*)k_push : (const void*)k_apply;
+                   : which == 1 ? (const void*)k_push
+                   : which == 2 ? (const void*)k_apply : (const void*)k_pull_exchange;
     g[which] = coop_grid_for(fn);
   }
   return g[which];
@@ -534,6 +664,10 @@ extern "C" int psb_pull_margin(const PsbPullParams* p, cudaStream_t stream) {
   if (p->S < 1 || p->S > PSB_MAX_SHARDS) return -(int)cudaErrorInvalidValue;
   return launch_coop((const void*)k_pull_margin, 0, p, stream);
 }
+extern "C" int psb_pull_exchange(const PsbPullExchangeParams* p, cudaStream_t stream) {
+  if (p->S < 1 || p->S > PSB_MAX_SHARDS) return -(int)cudaErrorInvalidValue;
+  return launch_coop((const void*)k_pull_exchange, 3, p, stream);
+}
 extern "C" int psb_push(const PsbPushParams* p, cudaStream_t stream) {
   if (p->S < 1 || p->S > PSB_MAX_SHARDS) return -(int)cudaErrorInvalidValue;
   return launch_coop((const void*)k_push, 1, p, stream);
@@ -550,6 +684,7 @@ extern "C" int psb_struct_size(int which) {
     case 1: return (int)sizeof(PsbPushParams);
     case 2: return (int)sizeof(PsbApplyParams);
     case 3: return (int)sizeof(PsbOptimizer);
+    case 4: return (int)sizeof(PsbPullExchangeParams);
     default: return -1;
   }
 }

@@ -71,10 +71,14 @@ class SparseLRWorker:
         """Pull + margins, push, apply for a localised batch (round = step number)."""
         t = self.step_no
         need = max(0, t - self.cfg.tau)
-        if self.plane.cfg.key_cache:
-            self.plane.key_signature(b, stream=stream)
-        self.plane.pull_margin(b, need_applied=need, loss=self.loss_code, auc_hist=self.auc_hist, stream=stream)
-        self.plane.push(b, t, stream=stream)
+        if self.plane.cfg.pull_cap:
+            self.plane.pull_exchange(b, t, need_applied=need, loss=self.loss_code, auc_hist=self.auc_hist, stream=stream)
+            self.plane.push(b, t, send_keys=False, stream=stream)
+        else:
+            if self.plane.cfg.key_cache:
+                self.plane.key_signature(b, stream=stream)
+            self.plane.pull_margin(b, need_applied=need, loss=self.loss_code, auc_hist=self.auc_hist, stream=stream)
+            self.plane.push(b, t, stream=stream)
         self.plane.apply(t, stream=server_stream if server_stream is not None else stream)
         self.step_no += 1
 
@@ -116,11 +120,17 @@ class SparseLRWorker:
         self.main_stream.wait_event(self._prep_done[k])
         t = self.step_no
         need = max(0, t - self.cfg.tau)
-        if self.plane.cfg.key_cache:
-            self.plane.key_signature(b, stream=self.main_stream)
-        self.plane.pull_margin(b, need_applied=need, loss=self.loss_code, auc_hist=self.auc_hist,
-                               stream=self.main_stream)
-        self.plane.push(b, t, stream=self.main_stream)
+        if self.plane.cfg.pull_cap:
+            # two-sided exchange: bulk traffic only, and the push of this round is values-only
+            self.plane.pull_exchange(b, t, need_applied=need, loss=self.loss_code, auc_hist=self.auc_hist,
+                                     stream=self.main_stream)
+            self.plane.push(b, t, send_keys=False, stream=self.main_stream)
+        else:
+            if self.plane.cfg.key_cache:
+                self.plane.key_signature(b, stream=self.main_stream)
+            self.plane.pull_margin(b, need_applied=need, loss=self.loss_code, auc_hist=self.auc_hist,
+                                   stream=self.main_stream)
+            self.plane.push(b, t, stream=self.main_stream)
         self._buf_free[k].record(self.main_stream)
         self._push_done.record(self.main_stream)
         self.server_stream.wait_event(self._push_done)

@@ -50,6 +50,23 @@ class PullParams(C.Structure):
     ]
 
 
+class PullExchangeParams(C.Structure):
+    _fields_ = [
+        ("S", _i32), ("me", _i32), ("ts1", _u32), ("need_applied", _u32), ("req_cap", _u32), ("wait_iters", _u32),
+        ("phases", _i32),
+        ("req_keys", _vp * MAX_SHARDS), ("req_hdr", _vp * MAX_SHARDS), ("req_ready", _vp * MAX_SHARDS),
+        ("my_req_keys", _vp * MAX_SHARDS), ("my_req_hdr", _vp * MAX_SHARDS), ("my_req_ready", _vp * MAX_SHARDS),
+        ("resp_w", _vp * MAX_SHARDS), ("resp_ready", _vp * MAX_SHARDS), ("slot_cache", _vp * MAX_SHARDS),
+        ("alive", C.c_uint8 * MAX_SHARDS),
+        ("table", _vp), ("mask", _u64), ("key_begin", _u64), ("slot_mult", _u64), ("applied", _vp),
+        ("my_resp_w", _vp), ("my_resp_ready", _vp * MAX_SHARDS),
+        ("ukeys", _vp), ("n_unique", _vp), ("own_off", _vp), ("grad_zero", _vp),
+        ("row_ptr", _vp), ("n_rows", _u32), ("fixed_z", _u32), ("csr_col", _vp), ("csr_val", _vp), ("y", _vp),
+        ("loss", _i32), ("gcoef", _vp), ("margin", _vp), ("stats", _vp), ("auc_hist", _vp),
+        ("done", _vp), ("status", _vp),
+    ]
+
+
 class PushParams(C.Structure):
     _fields_ = [
         ("S", _i32), ("ts1", _u32), ("inbox_cap", _u32), ("quant", _i32), ("send_keys", _i32),
@@ -134,6 +151,7 @@ def _declare(lib):
     lib.psb_table_init.argtypes = [_vp, _u64, _vp]
     lib.psb_pull_margin.argtypes = [C.POINTER(PullParams), _vp]
     lib.psb_push.argtypes = [C.POINTER(PushParams), _vp]
+    lib.psb_pull_exchange.argtypes = [C.POINTER(PullExchangeParams), _vp]
     lib.psb_apply.argtypes = [C.POINTER(ApplyParams), _vp]
     lib.psb_table_dump.argtypes = [_vp, _u64, _vp, _vp, _u64, _vp, _vp]
     lib.psb_table_load.argtypes = [_vp, _u64, _u64, _u64, _vp, _vp, _vp, _vp, _u64, _vp, _vp]
@@ -193,7 +211,7 @@ def lib():
                 "(or __graft_entry__.build()) first")
         _LIB = C.CDLL(os.fspath(path), mode=C.RTLD_GLOBAL)
         _declare(_LIB)
-        for which, st in enumerate((PullParams, PushParams, ApplyParams, Optimizer)):
+        for which, st in enumerate((PullParams, PushParams, ApplyParams, Optimizer, PullExchangeParams)):
             if _LIB.psb_struct_size(which) != C.sizeof(st):
                 raise RuntimeError(f"{st.__name__}: binding struct is {C.sizeof(st)} bytes, "
                                    f"library expects {_LIB.psb_struct_size(which)}")

@@ -61,6 +61,7 @@ class PlaneConfig:
     quant: str = "none"                     # none | int8 | fp16 (fixed-point filter on pushes)
     ordered_slots: bool = False             # keys are uniformly hashed: order-preserving slot map
     key_cache: bool = False                 # key-caching filter: skip keys (push) and probes (pull) on a repeated key list
+    pull_cap: int = 0                       # unique keys per worker minibatch for the two-sided pull (0: off)
 
     def quant_code(self) -> int:
         return {"none": _lib.QUANT_NONE, "int8": _lib.QUANT_INT8, "fp16": _lib.QUANT_FP16}[self.quant]
@@ -75,6 +76,11 @@ def heap_layout(cfg: PlaneConfig, world: int) -> HeapLayout:
     lay.add("table", cfg.table_capacity * 32)
     lay.add("inbox_keys", cfg.ring * world * cfg.inbox_cap * 8)
     lay.add("inbox_vals", cfg.ring * world * cfg.inbox_cap * 4 + 256)
+    if cfg.pull_cap:
+        # two-sided pull: request areas per (parity, source), response buffer per parity, flags
+        lay.add("xflags", 4 * (16 * world + 16))
+        lay.add("req_keys", 2 * world * cfg.inbox_cap * 8)
+        lay.add("resp_w", 2 * cfg.pull_cap * 4)
     return lay
 
 
@@ -180,6 +186,55 @@ class DataPlane:
         p.stats, p.auc_hist = ptr(self.pull_stats), ptr(auc_hist)
         p.bar, p.status = self._bar(0), ptr(self.status)
         check(_lib.lib().psb_pull_margin(C.byref(p), stream_ptr(stream)), "pull_margin")
+
+    # ---------------------------------------------------------------- two-sided pull (+ margins)
+    def _xflag(self, rank: int, kind: int, par: int, idx: int) -> int:
+        """kind 0: req_ready, 1: resp_ready, 2/3: the two request header words."""
+        return self.fabric.ptr(rank, self.layout["xflags"] + 4 * (((kind * 2) + par) * self.S + idx))
+
+    def pull_exchange(self, b, ts: int, *, need_applied: int = 0, with_margins: bool = True, loss: int = 0,
+                      auc_hist: Optional[torch.Tensor] = None, phases: int = 7, wait_iters: int = 0, stream=None):
+        """Exchange form of F2 for round ``ts``: keys go to the owners in bulk, the
+        owners look them up (inserting absent keys), remember the slots for the push
+        of the same round and store the weights into this worker's response buffer.
+        After it, ``push(..., send_keys=False)`` + ``apply`` reuse those slots."""
+        from ..ops._lib import PullExchangeParams
+        cfg = self.cfg
+        assert cfg.pull_cap >= b.max_nnz, "pull_cap must cover the largest minibatch's unique keys"
+        par = ts & 1
+        p = PullExchangeParams()
+        p.S, p.me, p.ts1, p.need_applied, p.req_cap, p.wait_iters, p.phases = \
+            self.S, self.rank, ts + 1, need_applied, cfg.inbox_cap, wait_iters, phases
+        req_bytes = cfg.inbox_cap * 8
+        for s in range(self.S):
+            p.req_keys[s] = self.fabric.ptr(s, self.layout["req_keys"] + (par * self.S + self.rank) * req_bytes)
+            p.req_ready[s] = self._xflag(s, 0, par, self.rank)
+            p.my_req_keys[s] = self.fabric.ptr(self.rank, self.layout["req_keys"] + (par * self.S + s) * req_bytes)
+            p.my_req_ready[s] = self._xflag(self.rank, 0, par, s)
+            p.resp_w[s] = self.fabric.ptr(s, self.layout["resp_w"] + par * cfg.pull_cap * 4)
+            p.resp_ready[s] = self._xflag(s, 1, par, self.rank)
+            p.my_resp_ready[s] = self._xflag(self.rank, 1, par, s)
+            p.slot_cache[s] = self.slot_cache.data_ptr() + s * cfg.inbox_cap * 4
+            p.alive[s] = 1 if self.alive[s] else 0
+            # header = two consecutive words {count, base} per (parity, source)
+            p.req_hdr[s] = self.fabric.ptr(s, self.layout["xflags"] + 4 * (8 * self.S + (par * self.S + self.rank) * 2))
+            p.my_req_hdr[s] = self.fabric.ptr(self.rank, self.layout["xflags"] + 4 * (8 * self.S + (par * self.S + s) * 2))
+        p.table, p.mask = self.table_ptr(), cfg.table_capacity - 1
+        p.key_begin, p.slot_mult = self.bounds_host[self.rank], self.slot_mult[self.rank]
+        p.applied = self._ctrl(self.rank, 0)
+        p.my_resp_w = self.fabric.ptr(self.rank, self.layout["resp_w"] + par * cfg.pull_cap * 4)
+        p.ukeys, p.n_unique, p.own_off, p.grad_zero = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off), ptr(b.grad)
+        if with_margins:
+            p.row_ptr, p.n_rows, p.fixed_z = ptr(b.row_ptr), b.n_rows, b.fixed_z
+            p.csr_col, p.csr_val, p.y = ptr(b.csr_col), ptr(b.csr_val), ptr(b.y)
+            p.gcoef, p.margin = ptr(b.gcoef), ptr(b.margin)
+        p.loss, p.stats, p.auc_hist = loss, ptr(self.pull_stats), ptr(auc_hist)
+        p.done, p.status = self.sync_words.data_ptr() + 48, ptr(self.status)
+        check(_lib.lib().psb_pull_exchange(C.byref(p), stream_ptr(stream)), "pull_exchange")
+
+    def response_weights(self, ts: int, n: int) -> torch.Tensor:
+        """The weights this worker received in the exchange of round ``ts``."""
+        return self.fabric.view(self.layout["resp_w"] + (ts & 1) * self.cfg.pull_cap * 4, (n,), torch.float32)
 
     # ---------------------------------------------------------------- worker: push
     def push(self, b, ts: int, *, with_gradient: bool = True, send_keys: bool = True, stream=None):

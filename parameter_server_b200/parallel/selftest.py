@@ -22,6 +22,7 @@ def main():
     ap.add_argument("--quant", default="none")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--tau", type=int, default=1)
+    ap.add_argument("--pull", default="exchange", choices=["exchange", "one-sided"])
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -36,7 +37,7 @@ def main():
     rows, z, n_feat = 512, 24, 6000
     opt = OptimizerConfig(algo="ftrl", alpha=0.1, beta=1.0, l1=0.01, l2=0.1)
     pc = PlaneConfig(table_capacity=1 << 15, inbox_cap=rows * z, ring=args.tau + 2, quant=args.quant,
-                     ordered_slots=True)
+                     ordered_slots=True, pull_cap=rows * z if args.pull == "exchange" else 0)
     fab = Fabric.from_process_group(heap_layout(pc, world).total())
     plane = DataPlane(fab, pc, opt)
     w = SparseLRWorker(plane, SparseLRConfig(max_rows=rows, max_nnz=rows * z, tau=args.tau, hash_seed=3, pipeline=2))

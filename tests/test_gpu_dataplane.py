@@ -8,10 +8,11 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _mk(S, opt, cap=1 << 14, inbox=1 << 13, ring=3, quant="none", ordered=False):
+def _mk(S, opt, cap=1 << 14, inbox=1 << 13, ring=3, quant="none", ordered=False, pull_cap=0):
     from parameter_server_b200.parallel.dataplane import DataPlane, PlaneConfig, heap_layout
     from parameter_server_b200.parallel.fabric import Fabric
-    pc = PlaneConfig(table_capacity=cap, inbox_cap=inbox, ring=ring, quant=quant, ordered_slots=ordered)
+    pc = PlaneConfig(table_capacity=cap, inbox_cap=inbox, ring=ring, quant=quant, ordered_slots=ordered,
+                     pull_cap=pull_cap)
     fabs = Fabric.emulated(S, heap_layout(pc, S).total())
     return [DataPlane(f, pc, opt) for f in fabs]
 
@@ -173,3 +174,49 @@ def test_pipelined_submit_matches_synchronous(cuda_lib):
         outs.append(plane.dump_nonzero())
     assert np.array_equal(outs[0][0].numpy(), outs[1][0].numpy())
     assert np.allclose(outs[0][1].numpy(), outs[1][1].numpy(), rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("S", [1, 3])
+def test_pull_exchange_equals_one_sided_path(cuda_lib, S):
+    """Two-sided pull (keys to owners, weights back, slots reused by a values-only
+    push) gives the same margins and the same model as the one-sided path. The
+    three phases run as separate launches here because the emulated ranks share
+    one GPU and one stream."""
+    from parameter_server_b200.ops.localize import LocalBatch
+    from parameter_server_b200.parallel.dataplane import OptimizerConfig
+    opt = OptimizerConfig(algo="ftrl", alpha=0.1, beta=1.0, l1=0.01, l2=0.1)
+    rows, z = 128, 16
+    rng = np.random.default_rng(40 + S)
+    rounds = [[_batch(rng, rows, z, 2000) for _ in range(S)] for _ in range(4)]
+    results = []
+    for mode in ("one_sided", "exchange"):
+        planes = _mk(S, opt, pull_cap=rows * z if mode == "exchange" else 0, ordered=True, inbox=rows * z)
+        bufs = [LocalBatch(rows, rows * z, S, "cuda") for _ in range(S)]
+        margins = []
+        for t, data in enumerate(rounds):
+            for r in range(S):
+                ids, y, _ = data[r]
+                bufs[r].localize(torch.from_numpy(ids).cuda(), torch.from_numpy(y).cuda(), planes[r].bounds, fixed_z=z, hash_seed=1)
+            if mode == "one_sided":
+                for r in range(S):
+                    planes[r].pull_margin(bufs[r], need_applied=t)
+                for r in range(S):
+                    planes[r].push(bufs[r], t)
+            else:
+                for ph in (1, 2, 4):
+                    for r in range(S):
+                        planes[r].pull_exchange(bufs[r], t, need_applied=t, phases=ph)
+                for r in range(S):
+                    planes[r].push(bufs[r], t, send_keys=False)
+            for r in range(S):
+                planes[r].apply(t)
+            torch.cuda.synchronize()
+            for p in planes:
+                p.check_status()
+            margins.append(torch.stack([b.margin[:rows].clone() for b in bufs]).cpu())
+        results.append((margins, [p.dump_nonzero() for p in planes]))
+    for a, b in zip(results[0][0], results[1][0]):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
+    for (k0, w0), (k1, w1) in zip(results[0][1], results[1][1]):
+        assert np.array_equal(k0.numpy(), k1.numpy())
+        assert np.allclose(w0.numpy(), w1.numpy(), rtol=1e-4, atol=1e-6)

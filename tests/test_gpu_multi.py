@@ -14,8 +14,8 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("quant", ["none", "int8"])
-def test_two_rank_training_matches_oracle(cuda_lib, quant):
+@pytest.mark.parametrize("quant,pull", [("none", "exchange"), ("int8", "exchange"), ("none", "one-sided")])
+def test_two_rank_training_matches_oracle(cuda_lib, quant, pull):
     n = min(torch.cuda.device_count(), 4)
     if n < 2:
         pytest.skip("needs at least two GPUs")
@@ -23,7 +23,7 @@ def test_two_rank_training_matches_oracle(cuda_lib, quant):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=root)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", "29731", "-m",
-           "parameter_server_b200.parallel.selftest", "--quant", quant]
+           "parameter_server_b200.parallel.selftest", "--quant", quant, "--pull", pull]
     r = subprocess.run(cmd, env=env, cwd=root, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "SELFTEST OK" in r.stdout
