@@ -109,6 +109,9 @@ def main():
                     help="also time each stage (localise / pull+margins / push / apply) with CUDA events, "
                          "stages run back to back on one stream")
     ap.add_argument("--key-cache", action="store_true", help="enable the key-caching filter")
+    ap.add_argument("--key-bits", type=int, default=40,
+                    help="significant bits of the hashed uint64 keys (top bits); 64 = full-width keys. The radix "
+                         "sort skips digit positions that are constant across the batch")
     ap.add_argument("--pull", default="exchange", choices=["exchange", "one-sided"],
                     help="exchange: keys to owners + weights back as bulk peer stores; one-sided: remote table probes")
     ap.add_argument("--hashed-slots", action="store_true",
@@ -157,7 +160,7 @@ def main():
     fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
     plane = DataPlane(fab, pc, opt)
     worker = SparseLRWorker(plane, SparseLRConfig(max_rows=rows, max_nnz=nnz, tau=args.tau, hash_seed=0,
-                                                  pipeline=2))
+                                                  hash_bits=args.key_bits % 64, pipeline=2))
     # pool of distinct minibatches (per rank different data): on device and in pinned host memory
     pool_d = [gen_batch(rows, z, n_feat, 1.05, seed=0, batch=rank * 100003 + i, device=dev)[:2]
               for i in range(args.pool)]
@@ -289,7 +292,8 @@ def main():
             "dtype": "fp32", "data": "synthetic (device generator, Zipf-like ids, random-init model)",
             "impl": args.impl,
             "config": {"model": "FTRL-proximal L1/L2 logistic regression", "global_batch": world * rows,
-                       "rows_per_worker": rows, "nnz_per_row": z, "keys": f"2^{args.log2_keys} hashed uint64",
+                       "rows_per_worker": rows, "nnz_per_row": z, "keys": f"2^{args.log2_keys} ids hashed on the device to uint64 keys "
+                                                        f"({args.key_bits} significant bits, in the top bits)",
                        "seq_len": z, "parallelism": f"dp{world} x key-range shards{world}", "tau": args.tau,
                        "alpha": 0.1, "beta": 1.0, "l1": 1.0, "l2": 0.1, "quant": args.quant, "ordered_slots": not args.hashed_slots, "pull": args.pull,
                        "unique_keys_per_step_per_worker": u_mean,

@@ -30,9 +30,12 @@ __device__ __forceinline__ u32 head_ballot(const u64* __restrict__ keys, u32 n, 
   return __ballot_sync(0xffffffffu, head);
 }
 
-__global__ void __launch_bounds__(kLocThreads) k_uniq_count(const u64* __restrict__ keys, u32 n,
+__global__ void __launch_bounds__(kLocThreads) k_uniq_count(const u64* __restrict__ keys_a,
+                                                            const u64* __restrict__ keys_b,
+                                                            const u32* __restrict__ where, u32 n,
                                                             u32* __restrict__ tile_heads) {
   __shared__ u32 s_w[8];
+  const u64* __restrict__ keys = (where && *where) ? keys_b : keys_a;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const u32 base = blockIdx.x * (u32)kLocTile + w * (32 * kLocItems);
   u32 cnt = 0;
@@ -89,20 +92,25 @@ __global__ void __launch_bounds__(1024) k_uniq_scan(u32* __restrict__ tile_heads
   if (threadIdx.x == 0) *n_unique = s_carry;
 }
 
-// Emits, for the sorted pairs (keys[i], pos[i]):
+// Emits, for the sorted pairs (keys[i], pos[i]) held in buffer A or B (*where):
 //   ukeys[u], seg_off[u] at segment heads (seg_off[U] = n),
 //   csr_col[pos[i]] = u            (CSR remap to local column ids),
-//   pos[i] <- row of pos[i]        (in place: becomes the CSC row index),
+//   csc_row[i] = row of pos[i]     (the CSC row index),
 //   csc_val[i] = vals[pos[i]]      (only when vals != null),
 //   flagbits[i/32], wordbase[i/32] (head bitmap and heads before each word).
 // Row of a position: pos / fixed_z when row_ptr is null, else the row whose
 // [row_ptr[r], row_ptr[r+1]) contains it.
 __global__ void __launch_bounds__(kLocThreads) k_uniq_emit(
-    const u64* __restrict__ keys, u32* __restrict__ pos, u32 n, const u32* __restrict__ tile_base,
+    const u64* __restrict__ keys_a, const u64* __restrict__ keys_b, const u32* pos_a,
+    const u32* pos_b, const u32* __restrict__ where, u32* csc_row /* may alias pos */, u32 n,
+    const u32* __restrict__ tile_base,
     const u32* __restrict__ row_ptr, u32 n_rows, u32 fixed_z, const float* __restrict__ vals,
     u64* __restrict__ ukeys, u32* __restrict__ seg_off, u32* __restrict__ csr_col,
     float* __restrict__ csc_val, u32* __restrict__ flagbits, u32* __restrict__ wordbase) {
   __shared__ u32 s_w[8];
+  const bool in_b = where && *where;
+  const u64* __restrict__ keys = in_b ? keys_b : keys_a;
+  const u32* pos = in_b ? pos_b : pos_a;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const u32 base = blockIdx.x * (u32)kLocTile + w * (32 * kLocItems);
   u64 key[kLocItems];
@@ -145,7 +153,7 @@ __global__ void __launch_bounds__(kLocThreads) k_uniq_emit(
         }
         r = lo;
       }
-      pos[g] = r;
+      csc_row[g] = r;
     }
     run += __popc(bal[i]);
   }
@@ -179,6 +187,35 @@ extern "C" size_t psb_localize_scratch_bytes(uint32_t n) {
   return sizeof(u32) * (ntiles + 16);
 }
 
+// The sorted pairs are in (keys_a, pos_a) when *where == 0 (or where is null) and
+// in (keys_b, pos_b) otherwise. csc_row may alias the selected pos buffer.
+extern "C" int psb_localize2(const psb_u64* keys_a, const psb_u64* keys_b, const uint32_t* pos_a,
+                             const uint32_t* pos_b, const uint32_t* where, uint32_t* csc_row, uint32_t n,
+                             const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z,
+                             const float* vals, const psb_u64* bounds, int S, psb_u64* ukeys,
+                             uint32_t* seg_off, uint32_t* csr_col, float* csc_val,
+                             uint32_t* flagbits, uint32_t* wordbase, uint32_t* n_unique,
+                             uint32_t* own_off, void* scratch, cudaStream_t stream) {
+  if (S < 1 || S > 64) return -(int)cudaErrorInvalidValue;
+  if (row_ptr == nullptr && fixed_z == 0) return -(int)cudaErrorInvalidValue;
+  u32 ntiles = (n + kLocTile - 1) / kLocTile;
+  u32* tile_heads = (u32*)scratch;
+  if (n == 0) {
+    cudaMemsetAsync(n_unique, 0, sizeof(u32), stream);
+    cudaMemsetAsync(own_off, 0, sizeof(u32) * (S + 1), stream);
+    cudaMemsetAsync(seg_off, 0, sizeof(u32), stream);
+    return -(int)cudaGetLastError();
+  }
+  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)keys_a, (const u64*)keys_b, where, n, tile_heads);
+  k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique);
+  k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>((const u64*)keys_a, (const u64*)keys_b, pos_a, pos_b, where, csc_row,
+                                                  n, tile_heads, row_ptr, n_rows, fixed_z, vals, (u64*)ukeys, seg_off,
+                                                  csr_col, csc_val, flagbits, wordbase);
+  k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off, own_off);
+  return -(int)cudaGetLastError();
+}
+
+// Sorted pairs in one buffer; sorted_pos is rewritten in place with the CSC row index.
 extern "C" int psb_localize(const psb_u64* sorted_keys, uint32_t* sorted_pos, uint32_t n,
                             const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z,
                             const float* vals, const psb_u64* bounds, int S, psb_u64* ukeys,
@@ -195,12 +232,12 @@ extern "C" int psb_localize(const psb_u64* sorted_keys, uint32_t* sorted_pos, ui
     cudaMemsetAsync(seg_off, 0, sizeof(u32), stream);
     return -(int)cudaGetLastError();
   }
-  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>(sorted_keys, n, tile_heads);
+  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, nullptr, n, tile_heads);
   k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique);
-  k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>(sorted_keys, sorted_pos, n, tile_heads, row_ptr,
-                                                  n_rows, fixed_z, vals, ukeys, seg_off, csr_col,
-                                                  csc_val, flagbits, wordbase);
-  k_owner_offsets<<<1, 96, 0, stream>>>(ukeys, n_unique, bounds, S, n, seg_off, own_off);
+  k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, sorted_pos, nullptr, nullptr,
+                                                  sorted_pos, n, tile_heads, row_ptr, n_rows, fixed_z, vals,
+                                                  (u64*)ukeys, seg_off, csr_col, csc_val, flagbits, wordbase);
+  k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off, own_off);
   return -(int)cudaGetLastError();
 }
 
@@ -260,11 +297,11 @@ extern "C" int psb_localize_static(const psb_u64* sorted_keys, uint32_t* sorted_
   const u32 ntiles = (n + kLocTile - 1) / kLocTile;
   // every tile_heads word that the scan and the emit kernel read is written by
   // k_uniq_count first, so the array needs no clearing between calls
-  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, n, tile_heads);
+  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, nullptr, n, tile_heads);
   k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique);
-  k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, sorted_pos, n, tile_heads,
-                                                  row_ptr, n_rows, fixed_z, vals, (u64*)ukeys, seg_off,
-                                                  csr_col, csc_val, flagbits, wordbase);
+  k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, sorted_pos, nullptr, nullptr,
+                                                  sorted_pos, n, tile_heads, row_ptr, n_rows, fixed_z, vals,
+                                                  (u64*)ukeys, seg_off, csr_col, csc_val, flagbits, wordbase);
   k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off,
                                         own_off);
   return -(int)cudaGetLastError();

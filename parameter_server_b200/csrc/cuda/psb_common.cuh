@@ -43,11 +43,29 @@ __host__ __device__ __forceinline__ u64 fmix64(u64 k) {
   return k;
 }
 
-// Feature id -> uint64 key (bijective for a fixed seed, never kEmptyKey-prone
-// in practice; the all-ones output is remapped).
-__host__ __device__ __forceinline__ u64 hash_id_to_key(u64 id, u64 seed) {
-  u64 k = fmix64(id + seed * 0x9E3779B97F4A7C15ull + 0x632BE59BD9B4E019ull);
-  return k == kEmptyKey ? (kEmptyKey - 1) : k;
+// Feature id -> uint64 key. The low 56 bits of `seed_bits` are the seed, the top
+// byte is the number of significant key bits B (0 means 64). For B = 64 the key is
+// a 64-bit mix of the id (a bijection; the all-ones output is remapped). For
+// B < 64 the id (which must be < 2^B) goes through a bijection of B-bit values
+// (odd multiplications and right xor-shifts modulo 2^B) and the result is placed
+// in the TOP B bits of the key: keys stay uniformly spread over the key space for
+// range sharding, and a radix sort of them only needs ceil(B/8) digit passes.
+__host__ __device__ __forceinline__ u64 hash_id_to_key(u64 id, u64 seed_bits) {
+  const u64 seed = seed_bits & 0x00FFFFFFFFFFFFFFull;
+  const int bits = (int)(seed_bits >> 56);
+  if (bits == 0 || bits >= 64) {
+    u64 k = fmix64(id + seed * 0x9E3779B97F4A7C15ull + 0x632BE59BD9B4E019ull);
+    return k == kEmptyKey ? (kEmptyKey - 1) : k;
+  }
+  const u64 m = (1ull << bits) - 1;
+  u64 h = (id + seed * 0x9E3779B97F4A7C15ull) & m;
+  h = (h * 0xff51afd7ed558ccdull) & m;
+  h ^= h >> (bits / 2);
+  h = (h * 0xc4ceb9fe1a85ec53ull) & m;
+  h ^= h >> (bits / 2 + 1);
+  h = (h * 0x9E3779B97F4A7C15ull) & m;
+  h ^= h >> (bits / 2);
+  return h << (64 - bits);
 }
 
 // One slot of a server shard's open-addressing table for scalar (k=1) values.

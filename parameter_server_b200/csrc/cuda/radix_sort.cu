@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(256) k_sort_histogram(
     u64 k;
     if (in_kind == 0) {
       k = ((const u64*)in)[i];
+      if (keys_out && keys_out != (const u64*)in) keys_out[i] = k;   // passes ping-pong between A and B
     } else {
       u64 id = in_kind == 1 ? (u64)((const u32*)in)[i] : ((const u64*)in)[i];
       k = hash_id_to_key(id, seed);
@@ -64,6 +65,38 @@ __global__ void __launch_bounds__(256) k_sort_histogram(
   __syncthreads();
   for (int i = threadIdx.x; i < npass * kRadix; i += blockDim.x)
     if (sh[i]) atomicAdd(&ghist[i], sh[i]);
+}
+
+// Pass plan. A digit position whose histogram has a single non-empty bin does
+// not change the order, so its pass is skipped (keys with fewer significant bits
+// than the sorted range, e.g. hashed 40-bit keys, cost proportionally less).
+// plan[p]: bit 0 = skip, bit 1 = source buffer (0 = A, 1 = B), bit 2 = first
+// executed pass (payload defaults to the element index); plan[16] = buffer that
+// holds the result.
+__global__ void k_sort_plan(const u32* __restrict__ ghist, int npass, u32 n, u32* __restrict__ plan) {
+  __shared__ u32 s_skip[8];
+  if (threadIdx.x < 8) s_skip[threadIdx.x] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < npass * kRadix; i += blockDim.x)
+    if (ghist[i] == n) s_skip[i / kRadix] = 1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    u32 cur = 0, first = 1;
+    for (int p = 0; p < npass; ++p) {
+      u32 w = s_skip[p] | (cur << 1) | ((first && !s_skip[p]) ? 4u : 0u);
+      plan[p] = w;
+      if (!s_skip[p]) { cur ^= 1; first = 0; }
+    }
+    plan[16] = cur;
+    plan[17] = first;   // 1: every pass was skipped (the input order is already sorted)
+  }
+}
+
+// When every pass is skipped (the input is already in order) and no payload was
+// given, the payload still has to become the element index.
+__global__ void k_sort_identity_payload(const u32* __restrict__ plan, u32* __restrict__ vals_a, u32 n) {
+  if (plan[17] == 0) return;
+  for (u32 i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) vals_a[i] = i;
 }
 
 // Exclusive scan of one value per thread across the block (kSortWarps warps).
@@ -91,9 +124,17 @@ __device__ __forceinline__ u32 block_excl_scan_256(u32 v, u32* s_warp /*kSortWar
 
 // One digit pass. `status` holds ntiles*256 zeroed words for this pass.
 __global__ void __launch_bounds__(kSortThreads, 2) k_sort_onesweep(
-    const u64* __restrict__ keys_in, const u32* __restrict__ vals_in, u64* __restrict__ keys_out,
-    u32* __restrict__ vals_out, u32 n, int shift, u32 dmask, const u32* __restrict__ ghist,
-    u32* __restrict__ ticket, u32* __restrict__ status, u32* __restrict__ err) {
+    u64* __restrict__ keys_a, u32* __restrict__ vals_a, u64* __restrict__ keys_b, u32* __restrict__ vals_b,
+    int vals_given, u32 n, int shift, u32 dmask, const u32* __restrict__ ghist, u32* __restrict__ ticket,
+    u32* __restrict__ status, u32* __restrict__ err, const u32* __restrict__ plan, int pass) {
+  const u32 pl = plan[pass];
+  if (pl & 1u) return;                                   // constant digit: nothing to do
+  const bool from_b = (pl >> 1) & 1u;
+  const u64* __restrict__ keys_in = from_b ? keys_b : keys_a;
+  u64* __restrict__ keys_out = from_b ? keys_a : keys_b;
+  const u32* __restrict__ vals_in = from_b ? vals_b : vals_a;
+  u32* __restrict__ vals_out = from_b ? vals_a : vals_b;
+  if ((pl & 4u) && !vals_given) vals_in = nullptr;       // first executed pass: payload = index
   __shared__ u64 s_keys[kSortTile];            // 32 KB, reused for payloads
   __shared__ unsigned short s_cnt[kSortWarps * kRadix];  // per-warp digit counters (<= 256 each), 8 KB
   __shared__ u32 s_dstart[kRadix];             // tile-local start of each digit
@@ -238,45 +279,40 @@ extern "C" size_t psb_sort_scratch_bytes(uint32_t n, int begin_bit, int end_bit)
   int npass = (end_bit - begin_bit + kRadixBits - 1) / kRadixBits;
   size_t ntiles = (n + kSortTile - 1) / kSortTile;
   if (ntiles == 0) ntiles = 1;
-  // ghist | tickets | err(+pad) | status
-  return sizeof(u32) * ((size_t)npass * kRadix + 16 + (size_t)npass * ntiles * kRadix);
+  // ghist | tickets (16) | plan (32) | status
+  return sizeof(u32) * ((size_t)npass * kRadix + 48 + (size_t)npass * ntiles * kRadix);
 }
 
-// Sorts n pairs by key bits [begin_bit, end_bit). Buffers A (keys_a, vals_a) and
-// B (keys_b, vals_b) are ping-ponged; the input is `in` (see k_sort_histogram
-// for in_kind; for in_kind 0 `in` may equal keys_a). vals_a may be null on
-// entry, meaning payload = element index. Returns 0 if the result is in A and
-// 1 if it is in B, or a negative cudaError.
+// Sorts n pairs by key bits [begin_bit, end_bit), ping-ponging between buffers A
+// (keys_a, vals_a) and B (keys_b, vals_b). The input is `in` (see k_sort_histogram
+// for in_kind); plain keys (in_kind 0) that are not already in A are copied there.
+// vals_given = 0 means payload = element index. Passes over digit positions that
+// are constant across the batch are skipped, so which buffer holds the result is
+// only known on the device: *where_out (device word) is 0 for A, 1 for B.
 extern "C" int psb_sort_pairs(const void* in, int in_kind, psb_u64 seed, psb_u64* keys_a,
                               uint32_t* vals_a, int vals_given, psb_u64* keys_b, uint32_t* vals_b,
                               uint32_t n, int begin_bit, int end_bit, void* scratch,
-                              uint32_t* status, cudaStream_t stream) {
-  if (n == 0) return 0;
+                              uint32_t* status, uint32_t* where_out, cudaStream_t stream) {
   if (end_bit <= begin_bit || end_bit > 64 || begin_bit < 0) return -(int)cudaErrorInvalidValue;
+  if (n == 0) { cudaMemsetAsync(where_out, 0, sizeof(u32), stream); return -(int)cudaGetLastError(); }
   const int npass = (end_bit - begin_bit + kRadixBits - 1) / kRadixBits;
   const u32 ntiles = (n + kSortTile - 1) / kSortTile;
   u32* ghist = (u32*)scratch;
   u32* tickets = ghist + (size_t)npass * kRadix;
-  u32* st = tickets + 16;
+  u32* plan = tickets + 16;
+  u32* st = plan + 32;
   cudaMemsetAsync(scratch, 0, psb_sort_scratch_bytes(n, begin_bit, end_bit), stream);
   int hb = (int)min((u32)(148 * 8), (n + 255) / 256);
-  k_sort_histogram<<<hb, 256, 0, stream>>>(in, in_kind, seed, keys_a, n, begin_bit, end_bit, ghist);
-  const u64* kin = in_kind == 0 ? (const u64*)in : keys_a;
-  const u32* vin = vals_given ? vals_a : nullptr;
-  int where = 0;  // where the *next output* goes: first pass reads A (or `in`), writes B
+  k_sort_histogram<<<hb, 256, 0, stream>>>(in, in_kind, seed, (u64*)keys_a, n, begin_bit, end_bit, ghist);
+  k_sort_plan<<<1, 256, 0, stream>>>(ghist, npass, n, plan);
   for (int p = 0; p < npass; ++p) {
     int shift = begin_bit + p * kRadixBits;
     int bits = min(kRadixBits, end_bit - shift);
-    u64* kout = where == 0 ? keys_b : keys_a;
-    u32* vout = where == 0 ? vals_b : vals_a;
     k_sort_onesweep<<<ntiles, kSortThreads, 0, stream>>>(
-        kin, vin, kout, vout, n, shift, (1u << bits) - 1, ghist + (size_t)p * kRadix, tickets + p,
-        st + (size_t)p * ntiles * kRadix, status);
-    kin = kout;
-    vin = vout;
-    where ^= 1;
+        (u64*)keys_a, vals_a, (u64*)keys_b, vals_b, vals_given, n, shift, (1u << bits) - 1,
+        ghist + (size_t)p * kRadix, tickets + p, st + (size_t)p * ntiles * kRadix, status, plan, p);
   }
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return -(int)e;
-  return where;  // after an odd number of passes the data is in B (where==1)
+  if (!vals_given && vals_a) k_sort_identity_payload<<<hb, 256, 0, stream>>>(plan, vals_a, n);
+  cudaMemcpyAsync(where_out, plan + 16, sizeof(u32), cudaMemcpyDeviceToDevice, stream);
+  return -(int)cudaGetLastError();
 }

@@ -30,7 +30,8 @@ class SparseLRConfig:
     max_nnz: int
     tau: int = 0                       # bounded delay (minibatches)
     hash_seed: Optional[int] = 0       # hash raw ids to uint64 keys on the device; None: ids are keys
-    key_bits: int = 64
+    key_bits: int = 64                 # sorted key bit range: int or (begin, end)
+    hash_bits: int = 0                 # significant bits of device-hashed keys (0 = 64), placed in the top bits
     loss: str = "logit"
     real_values: bool = False
     pipeline: int = 2                  # minibatches in flight on the worker (>=1)
@@ -64,7 +65,7 @@ class SparseLRWorker:
         slot = self.step_no % len(self.bufs) if slot is None else slot
         b = self.bufs[slot]
         b.localize(ids, y, self.plane.bounds, fixed_z=fixed_z, row_ptr=row_ptr, vals=vals,
-                   hash_seed=self.cfg.hash_seed, key_bits=self.cfg.key_bits, stream=stream)
+                   hash_seed=self.cfg.hash_seed, key_bits=self.cfg.key_bits, hash_bits=self.cfg.hash_bits, stream=stream)
         return b
 
     def train_prepared(self, b: LocalBatch, stream=None, server_stream=None):
@@ -115,7 +116,8 @@ class SparseLRWorker:
             ids_d, y_d = to_dev(ids, "ids"), to_dev(y, "y")
             vals_d, rp_d = to_dev(vals, "vals"), to_dev(row_ptr, "row_ptr")
             b.localize(ids_d, y_d, self.plane.bounds, fixed_z=fixed_z, row_ptr=rp_d, vals=vals_d,
-                       hash_seed=self.cfg.hash_seed, key_bits=self.cfg.key_bits, stream=self.prep_stream)
+                       hash_seed=self.cfg.hash_seed, key_bits=self.cfg.key_bits, hash_bits=self.cfg.hash_bits,
+                       stream=self.prep_stream)
             self._prep_done[k].record(self.prep_stream)
         self.main_stream.wait_event(self._prep_done[k])
         t = self.step_no

@@ -26,11 +26,13 @@ def sort_pairs(keys: torch.Tensor, payload: Optional[torch.Tensor] = None, begin
     L = _lib.lib()
     scratch = torch.empty(L.psb_sort_scratch_bytes(n, begin_bit, end_bit), dtype=torch.uint8, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    where = check(L.psb_sort_pairs(ptr(ka), 0, 0, ptr(ka), ptr(va), int(payload is not None), ptr(kb), ptr(vb),
-                                   n, begin_bit, end_bit, ptr(scratch), ptr(status), stream_ptr(stream)), "sort",
-                  kernels=1 + (end_bit - begin_bit + 7) // 8)
+    where = torch.zeros(1, dtype=torch.int32, device=dev)
+    check(L.psb_sort_pairs(ptr(ka), 0, 0, ptr(ka), ptr(va), int(payload is not None), ptr(kb), ptr(vb),
+                           n, begin_bit, end_bit, ptr(scratch), ptr(status), ptr(where), stream_ptr(stream)), "sort",
+          kernels=3 + (end_bit - begin_bit + 7) // 8)
     _lib.check_status(status, "radix sort")
-    return (kb, vb) if where == 1 else (ka, va)
+    in_b = int(where.item()) == 1
+    return (kb, vb) if in_b else (ka, va)
 
 
 class LocalBatch:
@@ -45,6 +47,8 @@ class LocalBatch:
         self.keys_b = torch.empty(max_nnz, dtype=i64, device=dev)
         self.pos_a = torch.empty(max_nnz, dtype=i32, device=dev)
         self.pos_b = torch.empty(max_nnz, dtype=i32, device=dev)
+        self.csc_row_buf = torch.empty(max_nnz, dtype=i32, device=dev)
+        self.where = torch.zeros(1, dtype=i32, device=dev)   # which ping-pong buffer holds the sorted pairs
         nb = max(L.psb_sort_scratch_bytes(max_nnz, 0, 64), L.psb_localize_scratch_bytes(max_nnz))
         self.scratch = torch.empty(nb, dtype=torch.uint8, device=dev)
         self.status = torch.zeros(1, dtype=i32, device=dev)
@@ -76,14 +80,17 @@ class LocalBatch:
     def localize(self, ids: torch.Tensor, y: Optional[torch.Tensor], bounds: torch.Tensor, *,
                  fixed_z: int = 0, row_ptr: Optional[torch.Tensor] = None,
                  vals: Optional[torch.Tensor] = None, hash_seed: Optional[int] = None,
-                 key_bits: int = 64, stream=None):
+                 key_bits=64, hash_bits: int = 0, stream=None):
         """Sort + unique + remap one minibatch.
 
         ``ids``: flat per-nonzero feature ids. ``int32`` (raw ids, hashed to uint64
         keys on the device when ``hash_seed`` is given) or ``int64`` (already
         uint64 keys viewed as int64, or raw ids to hash when ``hash_seed`` is given).
         Rows are given by ``row_ptr`` (CSR offsets, int32) or a fixed ``fixed_z``
-        nonzeros per row.
+        nonzeros per row. ``hash_bits`` (0 = 64) is the number of significant bits
+        of the hashed keys, which sit in the top bits; ``key_bits`` is the sorted
+        bit range, an int (``[0, key_bits)``) or a ``(begin, end)`` pair. Digit
+        positions that turn out constant across the batch are skipped anyway.
         """
         L = _lib.lib()
         n = ids.numel()
@@ -103,21 +110,21 @@ class LocalBatch:
             assert ids.dtype == torch.int64
             in_kind, seed = 0, 0
         else:
-            in_kind, seed = (1 if ids.dtype == torch.int32 else 2), hash_seed
-        where = check(L.psb_sort_pairs(ptr(ids), in_kind, seed, ptr(self.keys_a), ptr(self.pos_a), 0,
-                                       ptr(self.keys_b), ptr(self.pos_b), n, 0, key_bits,
-                                       ptr(self.scratch), ptr(self.status), sp), "sort",
-                      kernels=1 + (key_bits + 7) // 8)
-        skeys, spos = (self.keys_b, self.pos_b) if where == 1 else (self.keys_a, self.pos_a)
+            in_kind, seed = (1 if ids.dtype == torch.int32 else 2), hash_seed | (hash_bits << 56)
+        lo_bit, hi_bit = key_bits if isinstance(key_bits, tuple) else (0, key_bits)
+        check(L.psb_sort_pairs(ptr(ids), in_kind, seed, ptr(self.keys_a), ptr(self.pos_a), 0,
+                               ptr(self.keys_b), ptr(self.pos_b), n, lo_bit, hi_bit,
+                               ptr(self.scratch), ptr(self.status), ptr(self.where), sp), "sort",
+              kernels=3 + (hi_bit - lo_bit + 7) // 8)
         self.csc_val = self.csc_val_buf if vals is not None else None
         if vals is not None:
             assert self.csc_val_buf is not None
-        check(L.psb_localize(ptr(skeys), ptr(spos), n, ptr(row_ptr), self.n_rows, self.fixed_z, ptr(vals),
-                             ptr(bounds), self.S, ptr(self.ukeys), ptr(self.seg_off), ptr(self.csr_col),
-                             ptr(self.csc_val), ptr(self.flagbits), ptr(self.wordbase), ptr(self.n_unique),
-                             ptr(self.own_off), ptr(self.scratch), sp), "localize", kernels=4)
-        self.csc_row = spos
-        self.sorted_keys = skeys
+        check(L.psb_localize2(ptr(self.keys_a), ptr(self.keys_b), ptr(self.pos_a), ptr(self.pos_b), ptr(self.where),
+                              ptr(self.csc_row_buf), n, ptr(row_ptr), self.n_rows, self.fixed_z, ptr(vals),
+                              ptr(bounds), self.S, ptr(self.ukeys), ptr(self.seg_off), ptr(self.csr_col),
+                              ptr(self.csc_val), ptr(self.flagbits), ptr(self.wordbase), ptr(self.n_unique),
+                              ptr(self.own_off), ptr(self.scratch), sp), "localize", kernels=4)
+        self.csc_row = self.csc_row_buf
         return self
 
     def set_keys(self, ukeys_sorted: torch.Tensor, bounds_host):

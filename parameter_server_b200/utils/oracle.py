@@ -28,12 +28,24 @@ def fmix64(k):
     return k
 
 
-def hash_id_to_key(ids, seed: int):
+def hash_id_to_key(ids, seed: int, bits: int = 64):
+    """Same map as the device ``hash_id_to_key`` (``bits`` significant key bits, in the top bits)."""
     ids = np.asarray(ids).astype(np.uint64)
+    G = np.uint64(0x9E3779B97F4A7C15)
     with np.errstate(over="ignore"):
-        k = fmix64(ids + np.uint64(seed) * np.uint64(0x9E3779B97F4A7C15) + np.uint64(0x632BE59BD9B4E019))
-    k[k == np.uint64(0xFFFFFFFFFFFFFFFF)] = np.uint64(0xFFFFFFFFFFFFFFFE)
-    return k
+        if bits == 0 or bits >= 64:
+            k = fmix64(ids + np.uint64(seed) * G + np.uint64(0x632BE59BD9B4E019))
+            k[k == np.uint64(0xFFFFFFFFFFFFFFFF)] = np.uint64(0xFFFFFFFFFFFFFFFE)
+            return k
+        m = np.uint64((1 << bits) - 1)
+        h = (ids + np.uint64(seed) * G) & m
+        h = (h * _M1) & m
+        h ^= h >> np.uint64(bits // 2)
+        h = (h * _M2) & m
+        h ^= h >> np.uint64(bits // 2 + 1)
+        h = (h * G) & m
+        h ^= h >> np.uint64(bits // 2)
+        return h << np.uint64(64 - bits)
 
 
 def lr_eval(opt, x):

@@ -100,3 +100,31 @@ def test_hash_on_device_matches_oracle(cuda_lib):
     b.localize(torch.from_numpy(ids).cuda(), None, bounds, fixed_z=50, hash_seed=9)
     U = int(b.n_unique.item())
     assert np.array_equal(b.ukeys[:U].cpu().numpy().view(np.uint64), np.unique(hash_id_to_key(ids, 9)))
+
+
+def test_sort_skips_constant_digits_and_narrow_hash(cuda_lib):
+    """Keys with 40 significant bits (top bits): the three low digit passes are
+    skipped on the device, the result is still the stable sorted order; and the
+    device hash with 40 bits matches the NumPy restatement."""
+    from parameter_server_b200.ops.localize import LocalBatch, sort_pairs
+    from parameter_server_b200.utils.oracle import hash_id_to_key
+    rng = np.random.default_rng(8)
+    ids = rng.integers(0, 1 << 26, 64 * 300, dtype=np.int64).astype(np.int32)
+    k = hash_id_to_key(ids, 0, 40)
+    sk, sv = sort_pairs(torch.from_numpy(k.view(np.int64)).cuda())
+    order = np.argsort(k, kind="stable")
+    assert np.array_equal(sk.cpu().numpy().view(np.uint64), k[order])
+    assert np.array_equal(sv.cpu().numpy().astype(np.int64), order)
+    # already sorted input with identical keys: every pass is skipped, payload = index
+    same = torch.full((5000,), 77, dtype=torch.int64, device="cuda")
+    sk2, sv2 = sort_pairs(same)
+    assert torch.equal(sv2.cpu(), torch.arange(5000, dtype=torch.int32)) and torch.equal(sk2, same)
+    b = LocalBatch(64, ids.size, 2, "cuda")
+    bounds = torch.tensor([0, -(1 << 63), -1], dtype=torch.int64).cuda()
+    b.localize(torch.from_numpy(ids).cuda(), None, bounds, fixed_z=300, hash_seed=0, hash_bits=40)
+    U = int(b.n_unique.item())
+    u = np.unique(k)
+    assert np.array_equal(b.ukeys[:U].cpu().numpy().view(np.uint64), u)
+    assert b.own_off.cpu().tolist() == [0, int(np.searchsorted(u, np.uint64(1 << 63))), U]
+    rows_of = np.repeat(np.arange(64), 300)
+    assert np.array_equal(b.csc_row[:ids.size].cpu().numpy(), rows_of[order])
