@@ -61,7 +61,7 @@ def test_darlin_bounded_delay_single_rank_converges(cuda_lib):
     keys, y, _ = _data(rng, 4000, 12, 2000, False)
     objs = {}
     for tau in (0, 2):
-        cfg = DarlinConfig(lambda_l1=1.0, eta=0.5, block_cols=128, max_pass=8, epsilon=1e-5, tau=tau)
+        cfg = DarlinConfig(lambda_l1=1.0, eta=0.3, block_cols=8, max_pass=8, epsilon=1e-5, tau=tau)
         fab = Fabric.single(darlin_heap_bytes(cfg, 1))
         r = DarlinRank(fab, cfg, torch.from_numpy(keys.view(np.int64)).cuda(), torch.from_numpy(y).cuda(), fixed_z=12)
         hist = run_darlin([r])
