@@ -160,7 +160,7 @@ def main():
     fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
     plane = DataPlane(fab, pc, opt)
     worker = SparseLRWorker(plane, SparseLRConfig(max_rows=rows, max_nnz=nnz, tau=args.tau, hash_seed=0,
-                                                  hash_bits=args.key_bits % 64, pipeline=2))
+                                                  hash_bits=args.key_bits % 64, pipeline=3))
     # pool of distinct minibatches (per rank different data): on device and in pinned host memory
     pool_d = [gen_batch(rows, z, n_feat, 1.05, seed=0, batch=rank * 100003 + i, device=dev)[:2]
               for i in range(args.pool)]

@@ -34,7 +34,7 @@ class SparseLRConfig:
     hash_bits: int = 0                 # significant bits of device-hashed keys (0 = 64), placed in the top bits
     loss: str = "logit"
     real_values: bool = False
-    pipeline: int = 2                  # minibatches in flight on the worker (>=1)
+    pipeline: int = 3                  # minibatches in flight on the worker: copy | localise | pull+push
     auc: bool = False
 
 
@@ -49,11 +49,13 @@ class SparseLRWorker:
         self.step_no = 0
         self.loss_code = _lib.LOSS_LOGIT if cfg.loss == "logit" else _lib.LOSS_SQUARE_HINGE
         self.auc_hist = torch.zeros(2 * 4096, dtype=torch.int32, device=dev) if cfg.auc else None
-        # streams: prep (copy + localise), main (pull/push), server (apply)
+        # streams: copy (H2D), prep (localise), main (pull/push), server (apply)
+        self.copy_stream = torch.cuda.Stream(device=dev)
         self.prep_stream = torch.cuda.Stream(device=dev)
         self.main_stream = torch.cuda.Stream(device=dev)
         self.server_stream = torch.cuda.Stream(device=dev)
         self._prep_done = [torch.cuda.Event() for _ in self.bufs]
+        self._copy_done = [torch.cuda.Event() for _ in self.bufs]
         self._buf_free = [torch.cuda.Event() for _ in self.bufs]
         self._push_done = torch.cuda.Event()
         self._staged = [None] * len(self.bufs)
@@ -93,16 +95,19 @@ class SparseLRWorker:
     # ------------------------------------------------------------ pipelined public API
     def submit(self, ids: torch.Tensor, y: torch.Tensor, *, fixed_z: int = 0, row_ptr=None, vals=None):
         """Enqueue one minibatch. ``ids``/``y`` (and ``vals``/``row_ptr``) may be
-        pinned host tensors -- they are copied on the prep stream -- or device
-        tensors. Localisation runs on the prep stream and overlaps the previous
-        minibatch's pull/push/apply on the main and server streams."""
+        pinned host tensors -- they are copied on the copy stream -- or device
+        tensors. Three minibatches are in flight: the copy of t+2, the localisation
+        of t+1 (prep stream) and the pull/push/apply of t (main and server streams)."""
         k = self.step_no % len(self.bufs)
         b = self.bufs[k]
         dev = self.plane.device
         cur = torch.cuda.current_stream(dev)
-        self.prep_stream.wait_stream(cur)
-        self.prep_stream.wait_event(self._buf_free[k])
-        with torch.cuda.stream(self.prep_stream):
+        # stage 1, copy stream: host -> device into this buffer's staging area (reusable once the
+        # localise that last read it has finished)
+        self.copy_stream.wait_stream(cur)
+        self.copy_stream.wait_event(self._prep_done[k])
+        self.copy_stream.wait_event(self._buf_free[k])   # labels / row offsets / values are read until the push
+        with torch.cuda.stream(self.copy_stream):
             def to_dev(t, name):
                 if t is None or t.is_cuda:
                     return t
@@ -115,6 +120,11 @@ class SparseLRWorker:
                 return v
             ids_d, y_d = to_dev(ids, "ids"), to_dev(y, "y")
             vals_d, rp_d = to_dev(vals, "vals"), to_dev(row_ptr, "row_ptr")
+            self._copy_done[k].record(self.copy_stream)
+        # stage 2, prep stream: sort + unique + remap (the buffer is free once its push has read it)
+        self.prep_stream.wait_event(self._copy_done[k])
+        self.prep_stream.wait_event(self._buf_free[k])
+        with torch.cuda.stream(self.prep_stream):
             b.localize(ids_d, y_d, self.plane.bounds, fixed_z=fixed_z, row_ptr=rp_d, vals=vals_d,
                        hash_seed=self.cfg.hash_seed, key_bits=self.cfg.key_bits, hash_bits=self.cfg.hash_bits,
                        stream=self.prep_stream)
@@ -146,6 +156,7 @@ class SparseLRWorker:
         cur.wait_stream(self.main_stream)
         cur.wait_stream(self.server_stream)
         cur.wait_stream(self.prep_stream)
+        cur.wait_stream(self.copy_stream)
 
     def read_progress(self, reset: bool = True):
         """Device -> host read of the progress counters: dict with the summed
