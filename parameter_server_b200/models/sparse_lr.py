@@ -174,11 +174,11 @@ class SparseLRWorker:
 
 
 def make_single_gpu(table_capacity: int, inbox_cap: int, opt: OptimizerConfig, cfg: SparseLRConfig,
-                    device=None, quant: str = "none", ordered_slots: bool = False) -> SparseLRWorker:
+                    device=None, quant: str = "none", ordered_slots: bool = False, pull_cap: int = 0) -> SparseLRWorker:
     """Convenience: one GPU hosting one shard and one worker."""
     ring = cfg.tau + 2
     pc = PlaneConfig(table_capacity=table_capacity, inbox_cap=inbox_cap, ring=ring, quant=quant,
-                     ordered_slots=ordered_slots)
+                     ordered_slots=ordered_slots, pull_cap=pull_cap)
     from ..parallel.dataplane import heap_layout
     fab = Fabric.single(heap_layout(pc, 1).total(), device)
     return SparseLRWorker(DataPlane(fab, pc, opt), cfg)

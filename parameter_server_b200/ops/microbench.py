@@ -53,10 +53,10 @@ def bench_sort(args):
     peak, tag = _peak_gbs()
 
     def run():
-        b.localize(ids, None, bounds, fixed_z=200, hash_seed=0, key_bits=args.bits)
+        b.localize(ids, None, bounds, fixed_z=200, hash_seed=0, hash_bits=args.bits % 64)
     med, best = _time(run, args.iters, flush)
     _lib.check_status(b.status, "sort")
-    npass = (args.bits + 7) // 8
+    npass = (args.bits + 7) // 8     # digit passes that are not skipped
     bytes_sort = n * (4 + 8 + 8) + npass * n * 24       # ids read + keys write + hist read; passes r+w
     print(json.dumps({"kernel": "sort+localize", "n": n, "passes": npass, "ms_median": med, "ms_best": best,
                       "sort_algorithmic_GB": bytes_sort / 1e9,
@@ -74,8 +74,8 @@ def bench_step(args):
     cap = 1
     while cap < 2 * (1 << args.log2_keys):
         cap *= 2
-    w = make_single_gpu(cap, nnz, OptimizerConfig(), SparseLRConfig(max_rows=rows, max_nnz=nnz, pipeline=1),
-                        dev, ordered_slots=not args.hashed_slots)
+    w = make_single_gpu(cap, nnz, OptimizerConfig(), SparseLRConfig(max_rows=rows, max_nnz=nnz, pipeline=1, hash_bits=40),
+                        dev, ordered_slots=not args.hashed_slots, pull_cap=nnz)
     flush = torch.empty(64 << 20, dtype=torch.int32, device=dev)
     pool = [gen_batch(rows, z, 1 << args.log2_keys, 1.05, 0, i, device=dev)[:2] for i in range(3)]
     peak, tag = _peak_gbs()
@@ -93,25 +93,26 @@ def bench_step(args):
         w.prepare(*pool[0], fixed_z=z, slot=0)
 
     def t_pull():
-        plane.pull_margin(b, need_applied=0)
+        plane.pull_exchange(b, w.step_no, need_applied=0)
 
     def t_push():
-        plane.push(b, w.step_no)
+        plane.push(b, w.step_no, send_keys=False)
 
     def t_apply():
         plane.apply(w.step_no)
         w.step_no += 1
     for name, fn, alg_bytes in (
             ("localize(sort+unique+remap)", t_prep, nnz * 20 + 8 * nnz * 24 + nnz * 8 * 2 + nnz * 12),
-            ("pull_margin", t_pull, U * 32 + U * 16 + nnz * 8 + rows * 12),
-            ("push", t_push, nnz * 8 + U * 12 + U * 16),
-            ("apply", t_apply, U * 12 + U * 64)):
+            ("pull_exchange", t_pull, U * (8 + 8 + 8 + 32 + 4 + 4 + 4) + nnz * 8 + rows * 12),
+            ("push", t_push, nnz * 8 + U * (4 + 4 + 4)),
+            ("apply", t_apply, U * (4 + 4 + 64))):
         if name == "apply":
             # every apply needs a fresh push of the same round
             from ..utils.synthetic import flush_l2
             ts = []
             for i in range(args.iters + 2):
-                plane.push(b, w.step_no)
+                plane.pull_exchange(b, w.step_no, need_applied=0)
+                plane.push(b, w.step_no, send_keys=False)
                 flush_l2(flush, i)
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(); fn(); e1.record(); torch.cuda.synchronize()
@@ -122,7 +123,7 @@ def bench_step(args):
             from ..utils.synthetic import flush_l2
             ts = []
             for i in range(args.iters + 2):
-                plane.pull_margin(b, need_applied=0)   # zeroes grad
+                plane.pull_exchange(b, w.step_no, need_applied=0)   # zeroes grad, fills the slot cache
                 flush_l2(flush, i)
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(); fn(); e1.record(); torch.cuda.synchronize()
@@ -138,6 +139,71 @@ def bench_step(args):
     print(json.dumps(res))
 
 
+def bench_wide(args):
+    """Wide-value pull fused with the tcgen05 GEMM against the context matrix."""
+    from . import _lib
+    from .localize import LocalBatch
+    from ..parallel.fabric import Fabric
+    from ..parallel.wide import WideConfig, WidePlane, wide_layout
+    from ..utils.synthetic import gen_batch
+    import numpy as np
+    dev = torch.device("cuda")
+    rows, z, N = args.rows, args.z, args.n_ctx
+    cap = 1
+    while cap < 2 * (1 << args.log2_keys):
+        cap *= 2
+    cfg = WideConfig(table_capacity=cap, inbox_cap=rows * z, ring=2)
+    fab = Fabric.single(wide_layout(cfg, 1).total())
+    plane = WidePlane(fab, cfg)
+    ids, y, _ = gen_batch(rows, z, 1 << args.log2_keys, 1.2, 0, 0, device=dev)
+    b = LocalBatch(rows, rows * z, 1, dev)
+    b.localize(ids, y, plane.bounds, fixed_z=z, hash_seed=0, hash_bits=40)
+    torch.cuda.synchronize()
+    U = int(b.n_unique.item())
+    # put every key of the batch into the table with random rows
+    plane.load(b.ukeys[:U].cpu().numpy().view(np.uint64), torch.randn(U, 64) * 0.1)
+    ctx = (torch.randn(N, 64) * 0.3).to(torch.bfloat16).to(dev)
+    P = torch.zeros(rows * z, N, device=dev)
+    flush = torch.empty(64 << 20, dtype=torch.int32, device=dev)
+    peak, tag = _peak_gbs()
+    med, best = _time(lambda: plane.pull_gemm(b, ctx, P), args.iters, flush)
+    plane.check_status("wide")
+    # bytes: key list + key-table probes (8 B) + value rows (128 B) + result (N*4 B)
+    alg = U * (8 + 8 + 128 + N * 4)
+    print(json.dumps({"kernel": "wide_pull_gemm", "unique_keys": U, "N": N, "ms_median": med, "ms_best": best,
+                      "algorithmic_MB": alg / 1e6, "frac_of_copy_bw": alg / 1e9 / (med * 1e-3) / peak,
+                      "tflops": 2.0 * U * 64 * N / (med * 1e-3) / 1e12, "peak": tag}))
+
+
+def bench_kv(args):
+    """Push + pull of K sorted unique keys with scalar values through the device
+    KV containers (one rank): keys/s for the pair push-then-pull."""
+    import numpy as np
+    from ..parallel.dataplane import OptimizerConfig
+    from ..parameter.kv import DeviceKVVector
+    out = []
+    for K in args.sizes:
+        kv = DeviceKVVector.create(table_capacity=1 << max(12, int(np.ceil(np.log2(4 * K)))), max_keys=K,
+                                   opt=OptimizerConfig(algo="sum"))
+        rng = np.random.default_rng(K)
+        keys = np.unique(rng.integers(0, 1 << 40, int(K * 1.2), dtype=np.uint64))[:K]
+        kt = torch.from_numpy(keys.view(np.int64)).cuda()
+        vals = torch.randn(len(keys), device="cuda")
+        for _ in range(3):
+            kv.wait(kv.pull(kt, wait=[kv.push(kt, vals)]))
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = args.iters
+        e0.record()
+        for _ in range(reps):
+            t = kv.pull(kt, wait=[kv.push(kt, vals)])
+        kv.wait(t)
+        e1.record(); torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        out.append({"K": len(keys), "ms_push_pull": ms, "keys_per_s": 2 * len(keys) / (ms * 1e-3)})
+    print(json.dumps({"kernel": "kv push+pull (width 1, 1 rank)", "results": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -146,12 +212,17 @@ def main():
     s = sub.add_parser("step"); s.add_argument("--rows", type=int, default=65536); s.add_argument("--z", type=int, default=200)
     s.add_argument("--log2-keys", type=int, default=26); s.add_argument("--iters", type=int, default=5)
     s.add_argument("--hashed-slots", action="store_true")
+    s = sub.add_parser("wide"); s.add_argument("--rows", type=int, default=32768); s.add_argument("--z", type=int, default=40)
+    s.add_argument("--log2-keys", type=int, default=22); s.add_argument("--n-ctx", type=int, default=128)
+    s.add_argument("--iters", type=int, default=5)
+    s = sub.add_parser("kv"); s.add_argument("--sizes", type=int, nargs="+", default=[1000, 100000, 1000000, 16000000])
+    s.add_argument("--iters", type=int, default=5)
     args = ap.parse_args()
     import sys
     sys.path.insert(0, os.fspath(Path(__file__).resolve().parents[2]))
     from .. import _build
     _build.build_cuda()
-    {"sort": bench_sort, "step": bench_step}[args.cmd](args)
+    {"sort": bench_sort, "step": bench_step, "wide": bench_wide, "kv": bench_kv}[args.cmd](args)
 
 
 if __name__ == "__main__":
