@@ -330,8 +330,8 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
     else { b = r * p.fixed_z; e = b + p.fixed_z; }
     float acc = 0.f;
     for (u32 j = b + lane; j < e; j += 32) {
-      float w = __ldcg(&p.my_resp_w[p.csr_col[j]]);
-      acc += p.csr_val ? w * p.csr_val[j] : w;
+      float w = __ldcg(&p.my_resp_w[__ldcs(&p.csr_col[j])]);   // column ids are streamed, the weights stay in L2
+      acc += p.csr_val ? w * __ldcs(&p.csr_val[j]) : w;
     }
     acc = warp_sum(acc);
     if (lane == 0) {
@@ -414,8 +414,8 @@ __global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
       u32 base = p.wordbase[wi];
       float x = 0.f;
       if (i < p.nnz) {
-        x = __ldg(&p.gcoef[p.csc_row[i]]);
-        if (p.csc_val) x *= p.csc_val[i];
+        x = __ldg(&p.gcoef[__ldcs(&p.csc_row[i])]);
+        if (p.csc_val) x *= __ldcs(&p.csc_val[i]);
       }
       u32 fle = f & le;
       int start = fle ? 31 - __clz(fle) : 0;

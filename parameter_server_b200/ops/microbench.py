@@ -204,6 +204,60 @@ def bench_kv(args):
     print(json.dumps({"kernel": "kv push+pull (width 1, 1 rank)", "results": out}))
 
 
+def bench_darlin(args):
+    """Darlin passes on synthetic data (rows x 100 real-valued nonzeros, Zipf ids s=1.1,
+    values |N(0,1)| normalised per row). One rank per GPU; with torch.distributed.run the
+    (G, U) slices and the new weights travel over peer memory."""
+    import time
+    import numpy as np
+    import torch.distributed as dist
+    from ..models.darlin import DarlinConfig, DarlinRank, darlin_heap_bytes, run_darlin
+    from ..parallel.fabric import Fabric
+    from ..utils.synthetic import gen_batch
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rows, z, nf = args.rows, args.z, 1 << args.log2_keys
+    ids, y, vals = gen_batch(rows, z, nf, 1.1, seed=0, batch=rank, device=dev, ids64=True, real_values=True)
+    from . import _lib as L
+    keys = torch.empty_like(ids)
+    L.check(L.lib().psb_hash_ids(0, L.ptr(ids), L.ptr(keys), ids.numel(), 40 << 56, L.stream_ptr()), "hash")
+    cfg = DarlinConfig(lambda_l1=1.0, eta=0.9, block_cols=1 << 16, max_pass=args.passes, epsilon=0.0, tau=args.tau)
+    hb = darlin_heap_bytes(cfg, world)
+    fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
+    # global dictionary: all feature ids hashed (every rank can compute it without communication)
+    allk = torch.empty(nf, dtype=torch.int64, device=dev)
+    L.check(L.lib().psb_hash_ids(0, L.ptr(torch.arange(nf, dtype=torch.int64, device=dev)), L.ptr(allk), nf, 40 << 56,
+                                 L.stream_ptr()), "hash")
+    gk = torch.from_numpy(np.sort(allk.cpu().numpy().view(np.uint64)).view(np.int64)).to(dev)
+    t0 = time.time()
+    r = DarlinRank(fab, cfg, keys, y, fixed_z=z, vals=vals, global_keys=gk)
+    torch.cuda.synchronize()
+    prep = time.time() - t0
+
+    def all_reduce(v, op):
+        t = torch.tensor(v, dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM if op == "sum" else dist.ReduceOp.MAX)
+        return t.tolist()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    hist = run_darlin([r], all_reduce=all_reduce if world > 1 else None, num_examples=rows * world)
+    torch.cuda.synchronize()
+    dt = time.time() - t0
+    if rank == 0:
+        print(json.dumps({"kernel": "darlin", "gpus": world, "rows_per_gpu": rows, "nnz_per_row": z, "features": nf,
+                          "blocks_per_pass": len(r.blocks), "tau": args.tau, "preprocess_s": prep,
+                          "s_per_pass": dt / len(hist), "examples_per_s_per_pass": rows * world * len(hist) / dt,
+                          "objective": [h["objective"] for h in hist], "nnz_w": hist[-1]["nnz_w"]}))
+    if world > 1:
+        dist.barrier(); fab.close(); dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -215,6 +269,9 @@ def main():
     s = sub.add_parser("wide"); s.add_argument("--rows", type=int, default=32768); s.add_argument("--z", type=int, default=40)
     s.add_argument("--log2-keys", type=int, default=22); s.add_argument("--n-ctx", type=int, default=128)
     s.add_argument("--iters", type=int, default=5)
+    s = sub.add_parser("darlin"); s.add_argument("--rows", type=int, default=1250000); s.add_argument("--z", type=int, default=100)
+    s.add_argument("--log2-keys", type=int, default=24); s.add_argument("--passes", type=int, default=3)
+    s.add_argument("--tau", type=int, default=2)
     s = sub.add_parser("kv"); s.add_argument("--sizes", type=int, nargs="+", default=[1000, 100000, 1000000, 16000000])
     s.add_argument("--iters", type=int, default=5)
     args = ap.parse_args()
@@ -222,7 +279,7 @@ def main():
     sys.path.insert(0, os.fspath(Path(__file__).resolve().parents[2]))
     from .. import _build
     _build.build_cuda()
-    {"sort": bench_sort, "step": bench_step, "wide": bench_wide, "kv": bench_kv}[args.cmd](args)
+    {"sort": bench_sort, "step": bench_step, "wide": bench_wide, "kv": bench_kv, "darlin": bench_darlin}[args.cmd](args)
 
 
 if __name__ == "__main__":
