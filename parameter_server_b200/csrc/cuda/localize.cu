@@ -20,12 +20,13 @@ static constexpr int kLocThreads = 256;
 static constexpr int kLocItems = 16;
 static constexpr int kLocTile = kLocThreads * kLocItems;  // 4096 = 128 flag words
 
+// kmask selects the key bits (all ones, or without the packed position bits)
 __device__ __forceinline__ u32 head_ballot(const u64* __restrict__ keys, u32 n, u32 g, int lane,
-                                           u64* key_out) {
+                                           u64* key_out, u64 kmask) {
   u64 k = g < n ? keys[g] : 0;
   u64 prev = __shfl_up_sync(0xffffffffu, k, 1);
   if (lane == 0) prev = (g == 0 || g >= n) ? ~k : keys[g - 1];
-  bool head = g < n && (g == 0 || k != prev);
+  bool head = g < n && (g == 0 || (k & kmask) != (prev & kmask));
   *key_out = k;
   return __ballot_sync(0xffffffffu, head);
 }
@@ -33,7 +34,7 @@ __device__ __forceinline__ u32 head_ballot(const u64* __restrict__ keys, u32 n, 
 __global__ void __launch_bounds__(kLocThreads) k_uniq_count(const u64* __restrict__ keys_a,
                                                             const u64* __restrict__ keys_b,
                                                             const u32* __restrict__ where, u32 n,
-                                                            u32* __restrict__ tile_heads) {
+                                                            u32* __restrict__ tile_heads, u64 kmask) {
   __shared__ u32 s_w[8];
   const u64* __restrict__ keys = (where && *where) ? keys_b : keys_a;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -42,7 +43,7 @@ __global__ void __launch_bounds__(kLocThreads) k_uniq_count(const u64* __restric
 #pragma unroll
   for (int i = 0; i < kLocItems; ++i) {
     u64 k;
-    cnt += __popc(head_ballot(keys, n, base + i * 32 + lane, lane, &k));
+    cnt += __popc(head_ballot(keys, n, base + i * 32 + lane, lane, &k, kmask));
   }
   if (lane == 0) s_w[w] = cnt;
   __syncthreads();
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(kLocThreads) k_uniq_emit(
     const u32* __restrict__ tile_base,
     const u32* __restrict__ row_ptr, u32 n_rows, u32 fixed_z, const float* __restrict__ vals,
     u64* __restrict__ ukeys, u32* __restrict__ seg_off, u32* __restrict__ csr_col,
-    float* __restrict__ csc_val, u32* __restrict__ flagbits, u32* __restrict__ wordbase) {
+    float* __restrict__ csc_val, u32* __restrict__ flagbits, u32* __restrict__ wordbase, u64 kmask) {
   __shared__ u32 s_w[8];
   const bool in_b = where && *where;
   const u64* __restrict__ keys = in_b ? keys_b : keys_a;
@@ -118,7 +119,7 @@ __global__ void __launch_bounds__(kLocThreads) k_uniq_emit(
   u32 cnt = 0;
 #pragma unroll
   for (int i = 0; i < kLocItems; ++i) {
-    bal[i] = head_ballot(keys, n, base + i * 32 + lane, lane, &key[i]);
+    bal[i] = head_ballot(keys, n, base + i * 32 + lane, lane, &key[i], kmask);
     cnt += __popc(bal[i]);
   }
   if (lane == 0) s_w[w] = cnt;
@@ -136,10 +137,10 @@ __global__ void __launch_bounds__(kLocThreads) k_uniq_emit(
     if (g < n) {
       u32 u = run + __popc(bal[i] & le) - 1;
       if ((bal[i] >> lane) & 1u) {
-        ukeys[u] = key[i];
+        ukeys[u] = key[i] & kmask;
         seg_off[u] = g;
       }
-      u32 p = pos[g];
+      u32 p = pos ? pos[g] : (u32)(key[i] & ~kmask);   // packed: the position rides in the key's low bits
       csr_col[p] = u;
       if (csc_val) csc_val[g] = vals[p];
       u32 r;
@@ -195,9 +196,12 @@ extern "C" int psb_localize2(const psb_u64* keys_a, const psb_u64* keys_b, const
                              const float* vals, const psb_u64* bounds, int S, psb_u64* ukeys,
                              uint32_t* seg_off, uint32_t* csr_col, float* csc_val,
                              uint32_t* flagbits, uint32_t* wordbase, uint32_t* n_unique,
-                             uint32_t* own_off, void* scratch, cudaStream_t stream) {
+                             uint32_t* own_off, void* scratch, int pack_pos_bits, cudaStream_t stream) {
   if (S < 1 || S > 64) return -(int)cudaErrorInvalidValue;
   if (row_ptr == nullptr && fixed_z == 0) return -(int)cudaErrorInvalidValue;
+  if (pack_pos_bits < 0 || pack_pos_bits > 32) return -(int)cudaErrorInvalidValue;
+  const u64 kmask = pack_pos_bits ? ~((1ull << pack_pos_bits) - 1) : ~0ull;
+  if (pack_pos_bits) pos_a = pos_b = nullptr;
   u32 ntiles = (n + kLocTile - 1) / kLocTile;
   u32* tile_heads = (u32*)scratch;
   if (n == 0) {
@@ -206,11 +210,11 @@ extern "C" int psb_localize2(const psb_u64* keys_a, const psb_u64* keys_b, const
     cudaMemsetAsync(seg_off, 0, sizeof(u32), stream);
     return -(int)cudaGetLastError();
   }
-  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)keys_a, (const u64*)keys_b, where, n, tile_heads);
+  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)keys_a, (const u64*)keys_b, where, n, tile_heads, kmask);
   k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique);
   k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>((const u64*)keys_a, (const u64*)keys_b, pos_a, pos_b, where, csc_row,
                                                   n, tile_heads, row_ptr, n_rows, fixed_z, vals, (u64*)ukeys, seg_off,
-                                                  csr_col, csc_val, flagbits, wordbase);
+                                                  csr_col, csc_val, flagbits, wordbase, kmask);
   k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off, own_off);
   return -(int)cudaGetLastError();
 }
@@ -232,11 +236,11 @@ extern "C" int psb_localize(const psb_u64* sorted_keys, uint32_t* sorted_pos, ui
     cudaMemsetAsync(seg_off, 0, sizeof(u32), stream);
     return -(int)cudaGetLastError();
   }
-  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, nullptr, n, tile_heads);
+  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, nullptr, n, tile_heads, ~0ull);
   k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique);
   k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, sorted_pos, nullptr, nullptr,
                                                   sorted_pos, n, tile_heads, row_ptr, n_rows, fixed_z, vals,
-                                                  (u64*)ukeys, seg_off, csr_col, csc_val, flagbits, wordbase);
+                                                  (u64*)ukeys, seg_off, csr_col, csc_val, flagbits, wordbase, ~0ull);
   k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off, own_off);
   return -(int)cudaGetLastError();
 }
@@ -297,11 +301,11 @@ extern "C" int psb_localize_static(const psb_u64* sorted_keys, uint32_t* sorted_
   const u32 ntiles = (n + kLocTile - 1) / kLocTile;
   // every tile_heads word that the scan and the emit kernel read is written by
   // k_uniq_count first, so the array needs no clearing between calls
-  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, nullptr, n, tile_heads);
+  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, nullptr, n, tile_heads, ~0ull);
   k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique);
   k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, sorted_pos, nullptr, nullptr,
                                                   sorted_pos, n, tile_heads, row_ptr, n_rows, fixed_z, vals,
-                                                  (u64*)ukeys, seg_off, csr_col, csc_val, flagbits, wordbase);
+                                                  (u64*)ukeys, seg_off, csr_col, csc_val, flagbits, wordbase, ~0ull);
   k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off,
                                         own_off);
   return -(int)cudaGetLastError();

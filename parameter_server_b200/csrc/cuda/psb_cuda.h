@@ -19,12 +19,13 @@ typedef unsigned long long psb_u64;  // 64-bit keys (same ABI as uint64_t)
 size_t psb_sort_scratch_bytes(uint32_t n, int begin_bit, int end_bit);
 int psb_sort_pairs(const void* in, int in_kind, psb_u64 seed, psb_u64* keys_a, uint32_t* vals_a,
                    int vals_given, psb_u64* keys_b, uint32_t* vals_b, uint32_t n, int begin_bit,
-                   int end_bit, void* scratch, uint32_t* status, uint32_t* where_out, cudaStream_t stream);
+                   int end_bit, void* scratch, uint32_t* status, uint32_t* where_out, int pack_pos_bits,
+                   cudaStream_t stream);
 int psb_localize2(const psb_u64* keys_a, const psb_u64* keys_b, const uint32_t* pos_a, const uint32_t* pos_b,
                   const uint32_t* where, uint32_t* csc_row, uint32_t n, const uint32_t* row_ptr, uint32_t n_rows,
                   uint32_t fixed_z, const float* vals, const psb_u64* bounds, int S, psb_u64* ukeys,
                   uint32_t* seg_off, uint32_t* csr_col, float* csc_val, uint32_t* flagbits, uint32_t* wordbase,
-                  uint32_t* n_unique, uint32_t* own_off, void* scratch, cudaStream_t stream);
+                  uint32_t* n_unique, uint32_t* own_off, void* scratch, int pack_pos_bits, cudaStream_t stream);
 size_t psb_localize_scratch_bytes(uint32_t n);
 int psb_localize(const psb_u64* sorted_keys, uint32_t* sorted_pos, uint32_t n,
                  const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z, const float* vals,

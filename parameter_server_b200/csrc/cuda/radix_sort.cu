@@ -39,9 +39,12 @@ __device__ __forceinline__ u32 digit_of(u64 k, int shift, u32 dmask) {
 
 // in_kind: 0 = uint64 keys (used as is), 1 = uint32 ids, 2 = uint64 ids; for
 // 1 and 2 the key is hash_id_to_key(id, seed) and is written to keys_out.
+// pack_bits > 0 (hashed input only): the element index is stored in the low
+// pack_bits bits of the key, which the narrow hash leaves zero, so the pairs
+// travel as single 64-bit words and need no payload array.
 __global__ void __launch_bounds__(256) k_sort_histogram(
     const void* __restrict__ in, int in_kind, u64 seed, u64* __restrict__ keys_out, u32 n,
-    int begin_bit, int end_bit, u32* __restrict__ ghist) {
+    int begin_bit, int end_bit, u32* __restrict__ ghist, int pack_bits) {
   __shared__ u32 sh[8 * kRadix];
   const int npass = (end_bit - begin_bit + kRadixBits - 1) / kRadixBits;
   for (int i = threadIdx.x; i < npass * kRadix; i += blockDim.x) sh[i] = 0;
@@ -54,6 +57,7 @@ __global__ void __launch_bounds__(256) k_sort_histogram(
     } else {
       u64 id = in_kind == 1 ? (u64)((const u32*)in)[i] : ((const u64*)in)[i];
       k = hash_id_to_key(id, seed);
+      if (pack_bits) k |= (u64)i;
       keys_out[i] = k;
     }
     for (int p = 0; p < npass; ++p) {
@@ -289,11 +293,17 @@ extern "C" size_t psb_sort_scratch_bytes(uint32_t n, int begin_bit, int end_bit)
 // vals_given = 0 means payload = element index. Passes over digit positions that
 // are constant across the batch are skipped, so which buffer holds the result is
 // only known on the device: *where_out (device word) is 0 for A, 1 for B.
+// With pack_pos_bits > 0 (see k_sort_histogram) pass null payload buffers.
 extern "C" int psb_sort_pairs(const void* in, int in_kind, psb_u64 seed, psb_u64* keys_a,
                               uint32_t* vals_a, int vals_given, psb_u64* keys_b, uint32_t* vals_b,
                               uint32_t n, int begin_bit, int end_bit, void* scratch,
-                              uint32_t* status, uint32_t* where_out, cudaStream_t stream) {
+                              uint32_t* status, uint32_t* where_out, int pack_pos_bits, cudaStream_t stream) {
   if (end_bit <= begin_bit || end_bit > 64 || begin_bit < 0) return -(int)cudaErrorInvalidValue;
+  if (pack_pos_bits) {
+    // packed mode: hashed input, index bits below the sorted range, and they must hold every index
+    if (in_kind == 0 || pack_pos_bits > begin_bit || pack_pos_bits > 32 ||
+        (pack_pos_bits < 32 && (n - 1) >> pack_pos_bits)) return -(int)cudaErrorInvalidValue;
+  }
   if (n == 0) { cudaMemsetAsync(where_out, 0, sizeof(u32), stream); return -(int)cudaGetLastError(); }
   const int npass = (end_bit - begin_bit + kRadixBits - 1) / kRadixBits;
   const u32 ntiles = (n + kSortTile - 1) / kSortTile;
@@ -303,7 +313,8 @@ extern "C" int psb_sort_pairs(const void* in, int in_kind, psb_u64 seed, psb_u64
   u32* st = plan + 32;
   cudaMemsetAsync(scratch, 0, psb_sort_scratch_bytes(n, begin_bit, end_bit), stream);
   int hb = (int)min((u32)(148 * 8), (n + 255) / 256);
-  k_sort_histogram<<<hb, 256, 0, stream>>>(in, in_kind, seed, (u64*)keys_a, n, begin_bit, end_bit, ghist);
+  k_sort_histogram<<<hb, 256, 0, stream>>>(in, in_kind, seed, (u64*)keys_a, n, begin_bit, end_bit, ghist,
+                                           pack_pos_bits);
   k_sort_plan<<<1, 256, 0, stream>>>(ghist, npass, n, plan);
   for (int p = 0; p < npass; ++p) {
     int shift = begin_bit + p * kRadixBits;
@@ -312,7 +323,7 @@ extern "C" int psb_sort_pairs(const void* in, int in_kind, psb_u64 seed, psb_u64
         (u64*)keys_a, vals_a, (u64*)keys_b, vals_b, vals_given, n, shift, (1u << bits) - 1,
         ghist + (size_t)p * kRadix, tickets + p, st + (size_t)p * ntiles * kRadix, status, plan, p);
   }
-  if (!vals_given && vals_a) k_sort_identity_payload<<<hb, 256, 0, stream>>>(plan, vals_a, n);
+  if (!vals_given && vals_a && !pack_pos_bits) k_sort_identity_payload<<<hb, 256, 0, stream>>>(plan, vals_a, n);
   cudaMemcpyAsync(where_out, plan + 16, sizeof(u32), cudaMemcpyDeviceToDevice, stream);
   return -(int)cudaGetLastError();
 }

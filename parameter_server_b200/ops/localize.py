@@ -28,7 +28,7 @@ def sort_pairs(keys: torch.Tensor, payload: Optional[torch.Tensor] = None, begin
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     where = torch.zeros(1, dtype=torch.int32, device=dev)
     check(L.psb_sort_pairs(ptr(ka), 0, 0, ptr(ka), ptr(va), int(payload is not None), ptr(kb), ptr(vb),
-                           n, begin_bit, end_bit, ptr(scratch), ptr(status), ptr(where), stream_ptr(stream)), "sort",
+                           n, begin_bit, end_bit, ptr(scratch), ptr(status), ptr(where), 0, stream_ptr(stream)), "sort",
           kernels=3 + (end_bit - begin_bit + 7) // 8)
     _lib.check_status(status, "radix sort")
     in_b = int(where.item()) == 1
@@ -80,7 +80,7 @@ class LocalBatch:
     def localize(self, ids: torch.Tensor, y: Optional[torch.Tensor], bounds: torch.Tensor, *,
                  fixed_z: int = 0, row_ptr: Optional[torch.Tensor] = None,
                  vals: Optional[torch.Tensor] = None, hash_seed: Optional[int] = None,
-                 key_bits=64, hash_bits: int = 0, stream=None):
+                 key_bits=64, hash_bits: int = 0, packed: Optional[bool] = None, stream=None):
         """Sort + unique + remap one minibatch.
 
         ``ids``: flat per-nonzero feature ids. ``int32`` (raw ids, hashed to uint64
@@ -91,6 +91,8 @@ class LocalBatch:
         of the hashed keys, which sit in the top bits; ``key_bits`` is the sorted
         bit range, an int (``[0, key_bits)``) or a ``(begin, end)`` pair. Digit
         positions that turn out constant across the batch are skipped anyway.
+        ``packed``: None = pack (key, position) into one word whenever possible,
+        False = never, True = require it.
         """
         L = _lib.lib()
         n = ids.numel()
@@ -112,9 +114,19 @@ class LocalBatch:
         else:
             in_kind, seed = (1 if ids.dtype == torch.int32 else 2), hash_seed | (hash_bits << 56)
         lo_bit, hi_bit = key_bits if isinstance(key_bits, tuple) else (0, key_bits)
-        check(L.psb_sort_pairs(ptr(ids), in_kind, seed, ptr(self.keys_a), ptr(self.pos_a), 0,
-                               ptr(self.keys_b), ptr(self.pos_b), n, lo_bit, hi_bit,
-                               ptr(self.scratch), ptr(self.status), ptr(self.where), sp), "sort",
+        # Packed mode: narrow hashed keys leave their low bits zero; when every element index fits there,
+        # (key, position) travels as one 64-bit word and the sort needs no payload array.
+        pack = 0
+        if packed is not False and hash_seed is not None and 0 < hash_bits < 64 and n > 0:
+            free = min(64 - hash_bits, 32)
+            if (n - 1) >> free == 0:
+                pack = free
+                lo_bit = max(lo_bit, 64 - hash_bits)
+        assert pack or not packed, "packed mode needs hashed keys with (64 - hash_bits) bits for the positions"
+        self.pack_bits = pack
+        check(L.psb_sort_pairs(ptr(ids), in_kind, seed, ptr(self.keys_a), 0 if pack else ptr(self.pos_a), 0,
+                               ptr(self.keys_b), 0 if pack else ptr(self.pos_b), n, lo_bit, hi_bit,
+                               ptr(self.scratch), ptr(self.status), ptr(self.where), pack, sp), "sort",
               kernels=3 + (hi_bit - lo_bit + 7) // 8)
         self.csc_val = self.csc_val_buf if vals is not None else None
         if vals is not None:
@@ -123,7 +135,7 @@ class LocalBatch:
                               ptr(self.csc_row_buf), n, ptr(row_ptr), self.n_rows, self.fixed_z, ptr(vals),
                               ptr(bounds), self.S, ptr(self.ukeys), ptr(self.seg_off), ptr(self.csr_col),
                               ptr(self.csc_val), ptr(self.flagbits), ptr(self.wordbase), ptr(self.n_unique),
-                              ptr(self.own_off), ptr(self.scratch), sp), "localize", kernels=4)
+                              ptr(self.own_off), ptr(self.scratch), pack, sp), "localize", kernels=4)
         self.csc_row = self.csc_row_buf
         return self
 

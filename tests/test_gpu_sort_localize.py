@@ -128,3 +128,28 @@ def test_sort_skips_constant_digits_and_narrow_hash(cuda_lib):
     assert b.own_off.cpu().tolist() == [0, int(np.searchsorted(u, np.uint64(1 << 63))), U]
     rows_of = np.repeat(np.arange(64), 300)
     assert np.array_equal(b.csc_row[:ids.size].cpu().numpy(), rows_of[order])
+
+
+@pytest.mark.parametrize("hash_bits,rows,z", [(40, 512, 100), (48, 300, 37), (20, 200, 64)])
+def test_packed_positions_match_pair_sort(cuda_lib, hash_bits, rows, z):
+    """Narrow hashed keys: sorting (key | position) single words gives exactly the
+    same localised batch as sorting (key, position) pairs."""
+    from parameter_server_b200.ops.localize import LocalBatch
+    rng = np.random.default_rng(31)
+    ids = (rng.zipf(1.3, rows * z) % (1 << 22)).astype(np.int32)
+    vals = rng.random(rows * z, dtype=np.float32)
+    bounds = torch.tensor([0, 1 << 62, -(1 << 63), -1], dtype=torch.int64).cuda()
+    out = []
+    for packed in (True, False):
+        b = LocalBatch(rows, ids.size, 3, "cuda", real_values=True)
+        b.localize(torch.from_numpy(ids).cuda(), None, bounds, fixed_z=z, vals=torch.from_numpy(vals).cuda(),
+                   hash_seed=3, hash_bits=hash_bits, key_bits=(64 - hash_bits, 64), packed=packed)
+        torch.cuda.synchronize()
+        assert (b.pack_bits > 0) == packed
+        U = int(b.n_unique.item())
+        out.append((U, b.ukeys[:U].cpu(), b.seg_off[:U + 1].cpu(), b.csr_col[:ids.size].cpu(),
+                    b.csc_row[:ids.size].cpu(), b.csc_val[:ids.size].cpu(), b.own_off.cpu(),
+                    b.flagbits[:(ids.size + 31) // 32].cpu(), b.wordbase[:(ids.size + 31) // 32].cpu()))
+    assert out[0][0] == out[1][0] and out[0][0] > 1
+    for x, y in zip(out[0][1:], out[1][1:]):
+        assert torch.equal(x, y)
