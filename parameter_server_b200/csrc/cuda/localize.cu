@@ -20,15 +20,26 @@ static constexpr int kLocThreads = 256;
 static constexpr int kLocItems = 16;
 static constexpr int kLocTile = kLocThreads * kLocItems;  // 4096 = 128 flag words
 
-// kmask selects the key bits (all ones, or without the packed position bits)
-__device__ __forceinline__ u32 head_ballot(const u64* __restrict__ keys, u32 n, u32 g, int lane,
-                                           u64* key_out, u64 kmask) {
-  u64 k = g < n ? keys[g] : 0;
-  u64 prev = __shfl_up_sync(0xffffffffu, k, 1);
-  if (lane == 0) prev = (g == 0 || g >= n) ? ~k : keys[g - 1];
-  bool head = g < n && (g == 0 || (k & kmask) != (prev & kmask));
-  *key_out = k;
-  return __ballot_sync(0xffffffffu, head);
+// Loads the warp's 16 x 32 consecutive keys starting at `base` (all requested
+// before the first is used) and returns, per item, the ballot of segment heads.
+// kmask selects the key bits (all ones, or without the packed position bits).
+__device__ __forceinline__ void warp_heads(const u64* __restrict__ keys, u32 n, u32 base, int lane, u64 kmask,
+                                           u64 (&k)[kLocItems], u32 (&bal)[kLocItems]) {
+#pragma unroll
+  for (int i = 0; i < kLocItems; ++i) {
+    u32 g = base + i * 32 + lane;
+    k[i] = g < n ? keys[g] : 0;
+  }
+  u64 before = (lane == 0 && base > 0 && base < n) ? keys[base - 1] : 0;   // last key before the warp's span
+#pragma unroll
+  for (int i = 0; i < kLocItems; ++i) {
+    u32 g = base + i * 32 + lane;
+    u64 prev = __shfl_up_sync(0xffffffffu, k[i], 1);
+    u64 carry = __shfl_sync(0xffffffffu, i ? k[i ? i - 1 : 0] : before, i ? 31 : 0);
+    if (lane == 0) prev = carry;
+    bool head = g < n && (g == 0 || (k[i] & kmask) != (prev & kmask));
+    bal[i] = __ballot_sync(0xffffffffu, head);
+  }
 }
 
 __global__ void __launch_bounds__(kLocThreads) k_uniq_count(const u64* __restrict__ keys_a,
@@ -39,12 +50,12 @@ __global__ void __launch_bounds__(kLocThreads) k_uniq_count(const u64* __restric
   const u64* __restrict__ keys = (where && *where) ? keys_b : keys_a;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const u32 base = blockIdx.x * (u32)kLocTile + w * (32 * kLocItems);
+  u64 k[kLocItems];
+  u32 bal[kLocItems];
+  warp_heads(keys, n, base, lane, kmask, k, bal);
   u32 cnt = 0;
 #pragma unroll
-  for (int i = 0; i < kLocItems; ++i) {
-    u64 k;
-    cnt += __popc(head_ballot(keys, n, base + i * 32 + lane, lane, &k, kmask));
-  }
+  for (int i = 0; i < kLocItems; ++i) cnt += __popc(bal[i]);
   if (lane == 0) s_w[w] = cnt;
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -116,16 +127,15 @@ __global__ void __launch_bounds__(kLocThreads) k_uniq_emit(
   const u32 base = blockIdx.x * (u32)kLocTile + w * (32 * kLocItems);
   u64 key[kLocItems];
   u32 bal[kLocItems];
+  warp_heads(keys, n, base, lane, kmask, key, bal);
   u32 cnt = 0;
 #pragma unroll
-  for (int i = 0; i < kLocItems; ++i) {
-    bal[i] = head_ballot(keys, n, base + i * 32 + lane, lane, &key[i], kmask);
-    cnt += __popc(bal[i]);
-  }
+  for (int i = 0; i < kLocItems; ++i) cnt += __popc(bal[i]);
   if (lane == 0) s_w[w] = cnt;
   __syncthreads();
   u32 run = tile_base[blockIdx.x];
   for (int i = 0; i < w; ++i) run += s_w[i];
+  const u32 zinv = fixed_z ? (u32)(0xffffffffu / fixed_z) : 0u;   // umulhi(p, zinv) <= p / fixed_z, short by at most 2
   const u32 le = 0xffffffffu >> (31 - lane);
 #pragma unroll
   for (int i = 0; i < kLocItems; ++i) {
@@ -145,7 +155,8 @@ __global__ void __launch_bounds__(kLocThreads) k_uniq_emit(
       if (csc_val) csc_val[g] = vals[p];
       u32 r;
       if (row_ptr == nullptr) {
-        r = p / fixed_z;
+        r = __umulhi(p, zinv);
+        while (p - r * fixed_z >= fixed_z) ++r;   // the estimate is at most two short
       } else {
         u32 lo = 0, hi = n_rows;  // largest r with row_ptr[r] <= p
         while (hi - lo > 1) {
