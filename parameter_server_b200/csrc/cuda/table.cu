@@ -29,6 +29,14 @@
 namespace psb {
 
 static constexpr int kThreads = 256;
+
+// Optional per-phase cycle stamps (thread 0 of every CTA, 16 slots per CTA) for tuning builds.
+#ifdef PSB_TRACE
+__device__ long long* g_trace = nullptr;
+#define PSB_TSTAMP(k) do { if (threadIdx.x == 0 && g_trace) g_trace[(size_t)blockIdx.x * 16 + (k)] = clock64(); } while (0)
+#else
+#define PSB_TSTAMP(k) do { } while (0)
+#endif
 static constexpr u32 kMaxProbe = 1u << 16;
 
 // ------------------------------------------------------------------ optimiser
@@ -246,14 +254,28 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
   __syncthreads();
   const u32 gsize = gridDim.x * blockDim.x;
   const u32 gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  PSB_TSTAMP(0);
   // ---- (a) my keys to their owners
   if (p.phases & 1) {
-  for (u32 u = gtid; u < U; u += gsize) {
-    int s = owner_of(s_off, S, u);
-    u32 j = u - s_off[s];
-    if (j < p.req_cap) p.req_keys[s][j] = p.ukeys[u];
-    if (p.grad_zero) p.grad_zero[u] = 0.f;
+  // four independent keys per thread and trip, loads first
+  for (u32 u0 = gtid; u0 < U; u0 += 4 * gsize) {
+    u64 k[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      u32 u = u0 + q * gsize;
+      k[q] = u < U ? p.ukeys[u] : 0;
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      u32 u = u0 + q * gsize;
+      if (u >= U) break;
+      int s = owner_of(s_off, S, u);
+      u32 j = u - s_off[s];
+      if (j < p.req_cap) p.req_keys[s][j] = k[q];
+      if (p.grad_zero) p.grad_zero[u] = 0.f;
+    }
   }
+  PSB_TSTAMP(1);
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) s_last = atomicAdd(&p.done[0], 1u) + 1 == gridDim.x;
@@ -270,6 +292,7 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
     if (s == 0) atomicExch(&p.done[0], 0u);
   }
   }
+  PSB_TSTAMP(2);
   // ---- (b) owner role: serve every source
   if (p.phases & 2) {
   if (threadIdx.x == 0 && p.need_applied > 0 && !wait_flag_ge_sys(p.applied, p.need_applied, iters))
@@ -291,18 +314,46 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
       s_base = base;
     }
     __syncthreads();
+    PSB_TSTAMP(3);
     const u32 n = s_n, base = s_base;
-    for (u32 j = gtid; j < n; j += gsize) {
-      u64 key = p.my_req_keys[r][j];
-      long long slot = table_find<true>(tab, sm, key, kMaxProbe);
-      float w = 0.f;
-      u32 sc = 0x7fffffffu;
-      if (slot >= 0) { w = __ldcg(&tab[slot].w); sc = (u32)slot; }
-      else set_status(p.status, kTableFull);
-      p.slot_cache[r][j] = sc;
-      p.resp_w[r][base + j] = w;
+    // Four keys per thread and trip. The first probe of each is one 16-byte load
+    // that returns key and weight, issued for all four before any is examined;
+    // only a miss on that slot (collision or new key) takes the probing path.
+    for (u32 j0 = gtid; j0 < n; j0 += 4 * gsize) {
+      u64 key[4], slot[4], k0[4], hi[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        u32 j = j0 + q * gsize;
+        key[q] = j < n ? p.my_req_keys[r][j] : 0;
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        u32 j = j0 + q * gsize;
+        slot[q] = first_slot(sm, key[q]);
+        k0[q] = kEmptyKey; hi[q] = 0;
+        if (j < n)
+          asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];"
+                       : "=l"(k0[q]), "=l"(hi[q]) : "l"(&tab[slot[q]]) : "memory");
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        u32 j = j0 + q * gsize;
+        if (j >= n) break;
+        float w = __uint_as_float((u32)hi[q]);
+        u32 sc = (u32)slot[q];
+        if (k0[q] != key[q]) {
+          long long sl = table_find<true>(tab, sm, key[q], kMaxProbe);
+          w = 0.f;
+          sc = 0x7fffffffu;
+          if (sl >= 0) { w = __ldcg(&tab[sl].w); sc = (u32)sl; }
+          else set_status(p.status, kTableFull);
+        }
+        p.slot_cache[r][j] = sc;
+        p.resp_w[r][base + j] = w;
+      }
     }
   }
+  PSB_TSTAMP(4);
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) s_last = atomicAdd(&p.done[1], 1u) + 1 == gridDim.x;
@@ -315,12 +366,14 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
   }
   if (p.n_rows == 0 || !(p.phases & 4)) return;
   // ---- (c) worker: all owners have answered -> margins
+  PSB_TSTAMP(5);
   __syncthreads();
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s)
       if (p.alive[s] && !wait_flag_ge_sys(p.my_resp_ready[s], p.ts1, iters)) set_status(p.status, kWaitTimeout);
   }
   __syncthreads();
+  PSB_TSTAMP(6);
   const int lane = threadIdx.x & 31;
   const u32 gwarp = gtid >> 5, nwarps = gsize >> 5;
   double loss_sum = 0, n_correct = 0, n_seen = 0;
@@ -329,9 +382,21 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
     if (p.row_ptr) { b = p.row_ptr[r]; e = p.row_ptr[r + 1]; }
     else { b = r * p.fixed_z; e = b + p.fixed_z; }
     float acc = 0.f;
-    for (u32 j = b + lane; j < e; j += 32) {
-      float w = __ldcg(&p.my_resp_w[__ldcs(&p.csr_col[j])]);   // column ids are streamed, the weights stay in L2
-      acc += p.csr_val ? w * __ldcs(&p.csr_val[j]) : w;
+    // eight column ids per lane are fetched before the first weight is gathered
+    for (u32 j0 = b + lane; j0 < e; j0 += 32 * 8) {
+      u32 col[8];
+      float xv[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        u32 j = j0 + q * 32;
+        col[q] = j < e ? __ldcs(&p.csr_col[j]) : 0xffffffffu;   // column ids are streamed
+        xv[q] = (p.csr_val && j < e) ? __ldcs(&p.csr_val[j]) : 1.f;
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        // Plain (L1-cached) gathers: every weight was written before the flags that this
+        // CTA has acquired, and frequent columns repeat within a few rows, so they hit L1.
+        if (col[q] != 0xffffffffu) acc += p.my_resp_w[col[q]] * xv[q];
     }
     acc = warp_sum(acc);
     if (lane == 0) {
@@ -360,7 +425,9 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
       }
     }
   }
+  PSB_TSTAMP(7);
   block_add4(loss_sum, n_correct, n_seen, 0.0, p.stats);
+  PSB_TSTAMP(8);
 }
 
 // ------------------------------------------------------------------ F1a: worker push
@@ -404,31 +471,75 @@ __global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
   const u32 gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const u32 gwarp = gtid >> 5, nwarps = gsize >> 5;
   const u32 le = 0xffffffffu >> (31 - lane);
+  PSB_TSTAMP(0);
 
   if (p.nnz > 0) {
     // phase 1: segmented reduction of gcoef[row]*x over the key-sorted nonzeros
     const u32 nwords = (p.nnz + 31) / 32;
-    for (u32 wi = gwarp; wi < nwords; wi += nwarps) {
-      u32 i = wi * 32 + lane;
-      u32 f = p.flagbits[wi];
-      u32 base = p.wordbase[wi];
-      float x = 0.f;
-      if (i < p.nnz) {
-        x = __ldg(&p.gcoef[__ldcs(&p.csc_row[i])]);
-        if (p.csc_val) x *= __ldcs(&p.csc_val[i]);
-      }
-      u32 fle = f & le;
-      int start = fle ? 31 - __clz(fle) : 0;
+    // A warp takes chunks of kChunkWords consecutive 32-element words. Inside a chunk
+    // the sum of a segment that runs over a word boundary is carried in a register
+    // and added to grad once, so a frequent key (a segment of up to millions of
+    // nonzeros) costs one atomic per chunk, not one per word: same-address atomics
+    // serialise in L2. Four words are loaded per trip (row ids, then the gathers).
+    constexpr u32 kChunkWords = 16;
+    const u32 nchunks = (nwords + kChunkWords - 1) / kChunkWords;
+    for (u32 c = gwarp; c < nchunks; c += nwarps) {
+      const u32 wend = min(nwords, (c + 1) * kChunkWords);
+      float carry = 0.f;        // sum so far of the segment that is open at the word boundary
+      u32 carry_id = 0;         // its unique-key index
+      bool open = false;
+      for (u32 w0 = c * kChunkWords; w0 < wend; w0 += 4) {
+        u32 f[4], base[4], row[4];
+        float x[4];
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        float yv = __shfl_up_sync(0xffffffffu, x, o);
-        if (lane >= start + o) x += yv;
+        for (int q = 0; q < 4; ++q) {
+          u32 wi = w0 + q, i = wi * 32 + lane;
+          bool okw = wi < wend;
+          f[q] = okw ? p.flagbits[wi] : 0u;
+          base[q] = okw ? p.wordbase[wi] : 0u;
+          row[q] = (okw && i < p.nnz) ? __ldcs(&p.csc_row[i]) : 0xffffffffu;
+          x[q] = (p.csc_val && okw && i < p.nnz) ? __ldcs(&p.csc_val[i]) : 1.f;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) x[q] = row[q] != 0xffffffffu ? x[q] * __ldg(&p.gcoef[row[q]]) : 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const u32 wi = w0 + q, i = wi * 32 + lane;
+          if (wi >= wend) break;                    // warp-uniform
+          if (open && (f[q] & 1u)) {                // the open segment ended with the previous word
+            if (lane == 0) atomicAdd(&p.grad[carry_id], carry);
+            open = false; carry = 0.f;
+          }
+          u32 fle = f[q] & le;
+          int start = fle ? 31 - __clz(fle) : 0;
+          float xs = x[q];
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            float yv = __shfl_up_sync(0xffffffffu, xs, o);
+            if (lane >= start + o) xs += yv;
+          }
+          if (fle == 0) xs += carry;                // lanes that continue the open segment (carry is 0 otherwise)
+          const bool valid = i < p.nnz;
+          const bool last_elem = i == p.nnz - 1;
+          const bool tail = valid && ((lane == 31) || ((f[q] >> (lane + 1)) & 1u) || last_elem);
+          // the word's last segment stays open unless this is the chunk's last word or the data ends here
+          const bool keep = (wi + 1 < wend) && ((wi + 1) * 32 < p.nnz);
+          const u32 id = base[q] + __popc(fle) - 1;
+          if (tail && !(keep && lane == 31)) atomicAdd(&p.grad[id], xs);
+          if (keep) {
+            carry = __shfl_sync(0xffffffffu, xs, 31);
+            carry_id = base[q] + __popc(f[q]) - 1;
+            open = true;
+          } else {
+            open = false; carry = 0.f;
+          }
+        }
       }
-      bool tail = (lane == 31) || ((f >> (lane + 1)) & 1u) || (i == p.nnz - 1);
-      if (i < p.nnz && tail) atomicAdd(&p.grad[base + __popc(fle) - 1], x);
     }
+    PSB_TSTAMP(1);
     if (!grid_barrier(p.bar, p.status)) return;
   }
+  PSB_TSTAMP(2);
 
   // phase 2: range partition + (quantise) + peer stores, 32 records per warp step
   const bool omit_keys = !p.send_keys || (p.key_hit && *p.key_hit);
@@ -463,6 +574,7 @@ __global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
   }
   // signal: all of this CTA's peer stores are ordered before its arrival, the
   // last CTA to arrive publishes counts and the release flags
+  PSB_TSTAMP(3);
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -479,6 +591,7 @@ __global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
     st_release_sys(p.ready[s], p.ts1);
     if (s == 0) atomicExch(p.done, 0u);
   }
+  PSB_TSTAMP(4);
 }
 
 // ------------------------------------------------------------------ F1b: server apply
@@ -497,6 +610,7 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
   __shared__ u32 s_last;
   const int S = p.S;
   Entry* tab = (Entry*)p.table;
+  PSB_TSTAMP(0);
   if (threadIdx.x == 0) {
     u32 acc = 0;
     const u32 iters = p.wait_iters ? p.wait_iters : kPeerWaitIters;
@@ -515,6 +629,7 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
     s_pre[S] = acc;
   }
   __syncthreads();
+  PSB_TSTAMP(1);
   const u32 total = s_pre[S];
   const u32 gsize = gridDim.x * blockDim.x;
   const u32 gtid = blockIdx.x * blockDim.x + threadIdx.x;
@@ -526,52 +641,111 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
 
   // phase A: locate the slot of every record; single source -> update in place,
   // several sources -> accumulate into gacc and elect one leader per key
-  for (u32 i = gtid; i < total; i += gsize) {
-    int r = 0;
-    while (r + 1 < S && i >= s_pre[r + 1]) ++r;
-    u32 j = i - s_pre[r];
-    float g = inbox_value(p.inbox_vals[r], p.quant, p.inbox_cap, j);
-    long long slot;
-    if (s_cached[r]) {
-      slot = p.slot_cache[r][j] & 0x7fffffffu;
-      if (slot == 0x7fffffffu) continue;
-    } else {
-      slot = table_find<true>(tab, sm, p.inbox_keys[r][j], kMaxProbe);
-      if (slot < 0) { set_status(p.status, kTableFull); if (p.slot_cache[r]) p.slot_cache[r][j] = 0x7fffffffu; continue; }
-    }
-    if (single) {
-      Entry* e = &tab[slot];
-      float w = e->w, s0 = e->s0, s1 = e->s1, w_old = w;
-      opt_step(p.opt, g, w, s0, s1);
-      e->w = w; e->s0 = s0; e->s1 = s1;
-      st.add(w, w_old);
-      if (p.slot_cache[r]) p.slot_cache[r][j] = (u32)slot;
-    } else {
-      u32 old = atomicExch(&tab[slot].epoch, p.ts1);
-      atomicAdd(&tab[slot].gacc, g);
-      p.slot_cache[r][j] = (u32)slot | (old != p.ts1 ? 0x80000000u : 0u);
-    }
-  }
-  if (!single) {
-    if (!grid_barrier(p.bar, p.status)) return;
-    // phase B: the leader of each touched key runs the optimiser on the summed gradient
-    for (u32 i = gtid; i < total; i += gsize) {
+  // four records per thread and trip: values and slots first, then the entries
+  for (u32 i0 = gtid; i0 < total; i0 += 4 * gsize) {
+    long long slot[4];
+    float g[4];
+    int rr[4];
+    u32 jj[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      u32 i = i0 + q * gsize;
+      slot[q] = -1;
+      g[q] = 0.f; rr[q] = 0; jj[q] = 0;
+      if (i >= total) continue;
       int r = 0;
       while (r + 1 < S && i >= s_pre[r + 1]) ++r;
-      u32 sc = __ldcg(&p.slot_cache[r][i - s_pre[r]]);
-      if (!(sc & 0x80000000u) ) continue;
-      u32 slot = sc & 0x7fffffffu;
-      if (slot == 0x7fffffffu) continue;
-      Entry* e = &tab[slot];
-      float g = __ldcg(&e->gacc);
-      float w = __ldcg(&e->w), s0 = __ldcg(&e->s0), s1 = __ldcg(&e->s1), w_old = w;
-      opt_step(p.opt, g, w, s0, s1);
-      e->w = w; e->s0 = s0; e->s1 = s1; e->gacc = 0.f;
-      st.add(w, w_old);
+      u32 j = i - s_pre[r];
+      rr[q] = r; jj[q] = j;
+      g[q] = inbox_value(p.inbox_vals[r], p.quant, p.inbox_cap, j);
+      if (s_cached[r]) {
+        u32 sc = p.slot_cache[r][j] & 0x7fffffffu;
+        if (sc != 0x7fffffffu) slot[q] = sc;
+      } else {
+        slot[q] = table_find<true>(tab, sm, p.inbox_keys[r][j], kMaxProbe);
+        if (slot[q] < 0) { set_status(p.status, kTableFull); if (p.slot_cache[r]) p.slot_cache[r][j] = 0x7fffffffu; }
+      }
+    }
+    if (single) {
+      float2 ws[4];
+      float s1[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        ws[q] = make_float2(0.f, 0.f); s1[q] = 0.f;
+        if (slot[q] >= 0) {
+          ws[q] = *reinterpret_cast<const float2*>(&tab[slot[q]].w);   // (w, s0): one 8-byte load
+          s1[q] = tab[slot[q]].s1;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (slot[q] < 0) continue;
+        float w = ws[q].x, s0 = ws[q].y, t1 = s1[q], w_old = w;
+        opt_step(p.opt, g[q], w, s0, t1);
+        Entry* e = &tab[slot[q]];
+        *reinterpret_cast<float2*>(&e->w) = make_float2(w, s0);
+        e->s1 = t1;
+        st.add(w, w_old);
+        if (p.slot_cache[rr[q]]) p.slot_cache[rr[q]][jj[q]] = (u32)slot[q];
+      }
+    } else {
+      u32 old[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        old[q] = 0;
+        if (slot[q] >= 0) {
+          old[q] = atomicExch(&tab[slot[q]].epoch, p.ts1);
+          atomicAdd(&tab[slot[q]].gacc, g[q]);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (slot[q] >= 0) p.slot_cache[rr[q]][jj[q]] = (u32)slot[q] | (old[q] != p.ts1 ? 0x80000000u : 0u);
     }
   }
+  PSB_TSTAMP(2);
+  if (!single) {
+    if (!grid_barrier(p.bar, p.status)) return;
+    PSB_TSTAMP(3);
+    // phase B: the leader of each touched key runs the optimiser on the summed gradient
+    for (u32 i0 = gtid; i0 < total; i0 += 4 * gsize) {
+      u32 sc[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        u32 i = i0 + q * gsize;
+        sc[q] = 0;
+        if (i >= total) continue;
+        int r = 0;
+        while (r + 1 < S && i >= s_pre[r + 1]) ++r;
+        sc[q] = __ldcg(&p.slot_cache[r][i - s_pre[r]]);
+        if ((sc[q] & 0x7fffffffu) == 0x7fffffffu) sc[q] = 0;
+      }
+      float2 ws[4], sg[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        ws[q] = sg[q] = make_float2(0.f, 0.f);
+        if (sc[q] & 0x80000000u) {
+          const Entry* e = &tab[sc[q] & 0x7fffffffu];
+          ws[q] = __ldcg(reinterpret_cast<const float2*>(&e->w));    // (w, s0)
+          sg[q] = __ldcg(reinterpret_cast<const float2*>(&e->s1));   // (s1, gacc)
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (!(sc[q] & 0x80000000u)) continue;
+        Entry* e = &tab[sc[q] & 0x7fffffffu];
+        float w = ws[q].x, s0 = ws[q].y, s1 = sg[q].x, w_old = w;
+        opt_step(p.opt, sg[q].y, w, s0, s1);
+        *reinterpret_cast<float2*>(&e->w) = make_float2(w, s0);
+        *reinterpret_cast<float2*>(&e->s1) = make_float2(s1, 0.f);
+        st.add(w, w_old);
+      }
+    }
+  }
+  PSB_TSTAMP(4);
   block_add4(st.d_nnz, st.w2, st.dw2, st.n, p.stats);
   // publish "applied" once every CTA is done
+  PSB_TSTAMP(5);
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -584,6 +758,7 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
     st_release_sys(p.applied, p.ts1);
     atomicExch(p.done, 0u);
   }
+  PSB_TSTAMP(6);
 }
 
 static int coop_grid_for(const void* fn) {
@@ -678,6 +853,12 @@ extern "C" int psb_apply(const PsbApplyParams* p, cudaStream_t stream) {
 }
 
 // sizeof of the parameter blocks, so that a binding can verify its mirror structs
+#ifdef PSB_TRACE
+extern "C" int psb_trace_set(long long* buf) {
+  return -(int)cudaMemcpyToSymbol(g_trace, &buf, sizeof(buf));
+}
+#endif
+
 extern "C" int psb_struct_size(int which) {
   switch (which) {
     case 0: return (int)sizeof(PsbPullParams);

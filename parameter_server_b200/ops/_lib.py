@@ -132,6 +132,10 @@ LAUNCHES = 0
 
 
 def lib_path() -> Path:
+    """The in-tree CUDA library; ``PSB_CUDA_LIB`` selects another build of it (e.g. one with tracing)."""
+    override = os.environ.get("PSB_CUDA_LIB")
+    if override:
+        return Path(override)
     return Path(__file__).resolve().parent.parent / "libpsb_cuda.so"
 
 
