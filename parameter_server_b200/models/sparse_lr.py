@@ -58,6 +58,8 @@ class SparseLRWorker:
         self._copy_done = [torch.cuda.Event() for _ in self.bufs]
         self._buf_free = [torch.cuda.Event() for _ in self.bufs]
         self._push_done = torch.cuda.Event()
+        # one event per ring slot, recorded after the apply of that round
+        self._applied_ev = [torch.cuda.Event() for _ in range(self.cfg.tau + 2)]
         self._staged = [None] * len(self.bufs)
 
     # ------------------------------------------------------------ pieces
@@ -132,6 +134,11 @@ class SparseLRWorker:
         self.main_stream.wait_event(self._prep_done[k])
         t = self.step_no
         need = max(0, t - self.cfg.tau)
+        if need > 0:
+            # The pull of round t needs this rank's apply of round need-1. Waiting for it on the
+            # host side of the stream (instead of spinning in the pull kernel) matters: a resident,
+            # spinning pull kernel can leave no room on the SMs for the apply kernel it waits for.
+            self.main_stream.wait_event(self._applied_ev[(need - 1) % len(self._applied_ev)])
         if self.plane.cfg.pull_cap:
             # two-sided exchange: bulk traffic only, and the push of this round is values-only
             self.plane.pull_exchange(b, t, need_applied=need, loss=self.loss_code, auc_hist=self.auc_hist,
@@ -147,6 +154,7 @@ class SparseLRWorker:
         self._push_done.record(self.main_stream)
         self.server_stream.wait_event(self._push_done)
         self.plane.apply(t, stream=self.server_stream)
+        self._applied_ev[t % len(self._applied_ev)].record(self.server_stream)
         self.step_no += 1
         return b
 

@@ -101,7 +101,12 @@ class DataPlane:
         # local scratch (zero-initialised); one word group per kernel kind
         self.sync_words = torch.zeros(64, dtype=torch.int32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.slot_cache = torch.zeros((self.S, cfg.inbox_cap), dtype=torch.int32, device=dev)
+        # Slots found per (source, record). The exchange pull of round t fills them and the
+        # apply of round t consumes them up to tau rounds later, while the pulls of the next
+        # rounds already run: one copy per ring slot, like the inboxes. Without the exchange
+        # pull only copy 0 is used (scratch of apply, and the key-caching filter's memory).
+        n_sc = cfg.ring if cfg.pull_cap else 1
+        self.slot_cache = torch.zeros((n_sc, self.S, cfg.inbox_cap), dtype=torch.int32, device=dev)
         self.push_stats = torch.zeros(4, dtype=torch.float64, device=dev)   # d_nnz, w2, dw2, n
         self.pull_stats = torch.zeros(4, dtype=torch.float64, device=dev)   # loss, correct, rows
         self.alive = [True] * self.S
@@ -121,6 +126,10 @@ class DataPlane:
                                         cfg.table_capacity, stream_ptr()), "table init")
 
     # ---------------------------------------------------------------- addresses
+    def _slot_cache_ptr(self, ts: int, source: int) -> int:
+        q = ts % self.slot_cache.shape[0]
+        return self.slot_cache.data_ptr() + (q * self.S + source) * self.cfg.inbox_cap * 4
+
     def _ctrl(self, rank: int, word: int) -> int:
         return self.fabric.ptr(rank, self.layout["ctrl"] + 4 * word)
 
@@ -214,7 +223,7 @@ class DataPlane:
             p.resp_w[s] = self.fabric.ptr(s, self.layout["resp_w"] + par * cfg.pull_cap * 4)
             p.resp_ready[s] = self._xflag(s, 1, par, self.rank)
             p.my_resp_ready[s] = self._xflag(self.rank, 1, par, s)
-            p.slot_cache[s] = self.slot_cache.data_ptr() + s * cfg.inbox_cap * 4
+            p.slot_cache[s] = self._slot_cache_ptr(ts, s)
             p.alive[s] = 1 if self.alive[s] else 0
             # header = two consecutive words {count, base} per (parity, source)
             p.req_hdr[s] = self.fabric.ptr(s, self.layout["xflags"] + 4 * (8 * self.S + (par * self.S + self.rank) * 2))
@@ -283,7 +292,7 @@ class DataPlane:
             p.mode[r] = self._mode(self.rank, q, r)
             p.alive[r] = 1 if self.alive[r] else 0
             p.cached[r] = 1 if (cached is not None and cached[r]) else 0
-            p.slot_cache[r] = self.slot_cache.data_ptr() + r * cfg.inbox_cap * 4
+            p.slot_cache[r] = self._slot_cache_ptr(ts, r)
         p.opt = self.opt.to_c()
         p.stats, p.applied = ptr(self.push_stats), self._ctrl(self.rank, 0)
         p.wait_iters = wait_iters
