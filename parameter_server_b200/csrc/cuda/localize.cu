@@ -178,7 +178,7 @@ __global__ void k_owner_offsets(const u64* __restrict__ ukeys, const u32* __rest
                                 u32* __restrict__ seg_off, u32* __restrict__ own_off) {
   const u32 U = *n_unique;
   int s = threadIdx.x;
-  if (s == 0) seg_off[U] = n;
+  if (s == 0 && seg_off) seg_off[U] = n;
   if (s > S) return;
   if (s == S) { own_off[S] = U; return; }
   u64 b = bounds[s];
@@ -193,6 +193,15 @@ __global__ void k_owner_offsets(const u64* __restrict__ ukeys, const u32* __rest
 }  // namespace psb
 
 using namespace psb;
+
+// Owner slice offsets of an already sorted unique key list (generic Push/Pull
+// path): own_off[s] = lower_bound(ukeys, bounds[s]), own_off[S] = *n_unique.
+extern "C" int psb_owner_offsets(const psb_u64* ukeys, const uint32_t* n_unique, const psb_u64* bounds, int S,
+                                 uint32_t* own_off, cudaStream_t stream) {
+  if (S < 1 || S > 64) return -(int)cudaErrorInvalidValue;
+  k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, 0, nullptr, own_off);
+  return -(int)cudaGetLastError();
+}
 
 extern "C" size_t psb_localize_scratch_bytes(uint32_t n) {
   size_t ntiles = (n + kLocTile - 1) / kLocTile;

@@ -26,6 +26,8 @@ int psb_localize2(const psb_u64* keys_a, const psb_u64* keys_b, const uint32_t* 
                   uint32_t fixed_z, const float* vals, const psb_u64* bounds, int S, psb_u64* ukeys,
                   uint32_t* seg_off, uint32_t* csr_col, float* csc_val, uint32_t* flagbits, uint32_t* wordbase,
                   uint32_t* n_unique, uint32_t* own_off, void* scratch, int pack_pos_bits, cudaStream_t stream);
+int psb_owner_offsets(const psb_u64* ukeys, const uint32_t* n_unique, const psb_u64* bounds, int S,
+                      uint32_t* own_off, cudaStream_t stream);
 size_t psb_localize_scratch_bytes(uint32_t n);
 int psb_localize(const psb_u64* sorted_keys, uint32_t* sorted_pos, uint32_t n,
                  const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z, const float* vals,

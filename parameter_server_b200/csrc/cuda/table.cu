@@ -364,8 +364,9 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
   }
   if (s_last && threadIdx.x == 0) atomicExch(&p.done[1], 0u);
   }
-  if (p.n_rows == 0 || !(p.phases & 4)) return;
-  // ---- (c) worker: all owners have answered -> margins
+  if (!(p.phases & 4)) return;
+  // ---- (c) worker: all owners have answered -> margins (none when n_rows == 0: the
+  // caller then reads the weights from the response buffer after this kernel)
   PSB_TSTAMP(5);
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -373,6 +374,7 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
       if (p.alive[s] && !wait_flag_ge_sys(p.my_resp_ready[s], p.ts1, iters)) set_status(p.status, kWaitTimeout);
   }
   __syncthreads();
+  if (p.n_rows == 0) return;
   PSB_TSTAMP(6);
   const int lane = threadIdx.x & 31;
   const u32 gwarp = gtid >> 5, nwarps = gsize >> 5;

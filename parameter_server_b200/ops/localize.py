@@ -139,17 +139,16 @@ class LocalBatch:
         self.csc_row = self.csc_row_buf
         return self
 
-    def set_keys(self, ukeys_sorted: torch.Tensor, bounds_host):
-        """Use an already sorted unique key list (generic Push/Pull API path)."""
-        import numpy as np
+    def set_keys(self, ukeys_sorted: torch.Tensor, bounds, stream=None):
+        """Use an already sorted unique key list (generic Push/Pull API path). ``bounds``
+        is the device tensor of shard boundaries; the owner offsets are computed on
+        the device, so nothing here waits for the host."""
         n = ukeys_sorted.numel()
         assert n <= self.max_nnz
         self.ukeys[:n].copy_(ukeys_sorted)
         self.n_unique.fill_(n)
-        ku = ukeys_sorted.cpu().numpy().view("uint64")
-        offs = [int(np.searchsorted(ku, np.uint64(b), side="left")) if b < (1 << 64) - 1 or True else n
-                for b in bounds_host[:-1]] + [n]
-        self.own_off.copy_(torch.tensor(offs, dtype=torch.int32))
+        check(_lib.lib().psb_owner_offsets(ptr(self.ukeys), ptr(self.n_unique), ptr(bounds), self.S,
+                                           ptr(self.own_off), stream_ptr(stream)), "owner offsets")
         self.n_rows = 0
         self.nnz = 0
         return self

@@ -176,22 +176,37 @@ def bench_wide(args):
 
 
 def bench_kv(args):
-    """Push + pull of K sorted unique keys with scalar values through the device
-    KV containers (one rank): keys/s for the pair push-then-pull."""
+    """Push + pull of K sorted unique keys per rank with scalar values through the
+    device KV containers: keys/s for the pair push-then-pull (max over ranks). Under
+    torch.distributed.run every rank is a worker and owns one key-range shard; the
+    ``nccl_a2a_ms`` column is the time of the bare all-to-all-v traffic of the same
+    exchange (keys + values out, keys out + values back), i.e. a lower bound for an
+    NCCL implementation that still had to look the keys up and apply the values."""
     import numpy as np
+    import torch.distributed as dist
     from ..parallel.dataplane import OptimizerConfig
     from ..parameter.kv import DeviceKVVector
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     out = []
     for K in args.sizes:
-        kv = DeviceKVVector.create(table_capacity=1 << max(12, int(np.ceil(np.log2(4 * K)))), max_keys=K,
-                                   opt=OptimizerConfig(algo="sum"))
-        rng = np.random.default_rng(K)
-        keys = np.unique(rng.integers(0, 1 << 40, int(K * 1.2), dtype=np.uint64))[:K]
-        kt = torch.from_numpy(keys.view(np.int64)).cuda()
-        vals = torch.randn(len(keys), device="cuda")
+        cap = 1 << max(12, int(np.ceil(np.log2(4 * K))))
+        kv = DeviceKVVector.create(None, table_capacity=cap, max_keys=K, opt=OptimizerConfig(algo="sum"),
+                                   quant=args.quant, exchange=not args.one_sided)
+        fab = kv.plane.fabric
+        rng = np.random.default_rng(K + rank)
+        keys = np.unique(rng.integers(0, 1 << 63, int(K * 1.2), dtype=np.uint64) * np.uint64(2))[:K]
+        kt = torch.from_numpy(keys.view(np.int64)).to(dev)
+        vals = torch.randn(len(keys), device=dev)
         for _ in range(3):
             kv.wait(kv.pull(kt, wait=[kv.push(kt, vals)]))
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         reps = args.iters
         e0.record()
@@ -200,8 +215,40 @@ def bench_kv(args):
         kv.wait(t)
         e1.record(); torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / reps
-        out.append({"K": len(keys), "ms_push_pull": ms, "keys_per_s": 2 * len(keys) / (ms * 1e-3)})
-    print(json.dumps({"kernel": "kv push+pull (width 1, 1 rank)", "results": out}))
+        a2a_ms = None
+        if world > 1:
+            # bare all-to-all-v of the same exchange
+            bounds = np.array(kv.plane.bounds_host[:-1], dtype=np.float64)
+            cnt = np.diff(np.append(np.searchsorted(keys.astype(np.float64), bounds), len(keys))).astype(np.int64)
+            cin = torch.zeros(world, dtype=torch.int64, device=dev)
+            dist.all_to_all_single(cin, torch.from_numpy(cnt).to(dev))
+            isz, osz = cnt.tolist(), cin.tolist()
+            rk = torch.empty(int(sum(osz)), dtype=torch.int64, device=dev)
+            rv = torch.empty(int(sum(osz)), dtype=torch.float32, device=dev)
+            back = torch.empty(len(keys), dtype=torch.float32, device=dev)
+
+            def a2a():
+                dist.all_to_all_single(rk, kt, osz, isz); dist.all_to_all_single(rv, vals, osz, isz)   # push
+                dist.all_to_all_single(rk, kt, osz, isz); dist.all_to_all_single(back, rv, isz, osz)   # pull
+            for _ in range(3):
+                a2a()
+            torch.cuda.synchronize(); dist.barrier()
+            e0.record()
+            for _ in range(reps):
+                a2a()
+            e1.record(); torch.cuda.synchronize()
+            tt = torch.tensor([ms, e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms, a2a_ms = tt.tolist()
+        out.append({"K_per_rank": len(keys), "ms_push_pull": ms, "keys_per_s": 2 * len(keys) * world / (ms * 1e-3),
+                    "nccl_a2a_ms": a2a_ms})
+        if world > 1:
+            dist.barrier()
+            fab.close()
+    if rank == 0:
+        print(json.dumps({"kernel": f"kv push+pull (width 1, {world} rank(s), quant {args.quant})", "results": out}))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def bench_darlin(args):
@@ -273,7 +320,8 @@ def main():
     s.add_argument("--log2-keys", type=int, default=24); s.add_argument("--passes", type=int, default=3)
     s.add_argument("--tau", type=int, default=2)
     s = sub.add_parser("kv"); s.add_argument("--sizes", type=int, nargs="+", default=[1000, 100000, 1000000, 16000000])
-    s.add_argument("--iters", type=int, default=5)
+    s.add_argument("--iters", type=int, default=5); s.add_argument("--quant", default="none", choices=["none", "int8", "fp16"])
+    s.add_argument("--one-sided", action="store_true", help="pull with remote probes instead of the exchange kernel")
     args = ap.parse_args()
     import sys
     sys.path.insert(0, os.fspath(Path(__file__).resolve().parents[2]))

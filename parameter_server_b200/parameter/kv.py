@@ -9,6 +9,12 @@ Every rank calls ``push`` for every round (possibly with no keys), because the
 owner aggregates one round from all live workers -- the device counterpart of
 "an empty but valid slice is still sent" (``system/message.h:136-137``).
 
+With ``exchange=True`` (the default) pulls use the two-sided exchange kernel (keys
+to the owners in bulk, weights back in bulk), which is what NVLink likes; then
+``pull`` is collective as well: every rank calls it for every round, possibly
+with no keys. ``exchange=False`` keeps the one-sided pull (remote probes), which
+any rank may call on its own.
+
 Timestamps are per object and increase by one per request unless given.
 Requests run in stream order; ``wait=[t]`` makes a request's kernels wait for
 the CUDA event of request ``t``, and ``wait(ts)`` blocks the host until request
@@ -33,6 +39,7 @@ class DeviceKVMap:
         self.dev = plane.device
         self._time = -1
         self._round = 0                       # push rounds seen by the owners
+        self._pull_round = 0                  # exchange rounds (pulls)
         self._events: Dict[int, torch.cuda.Event] = {}
         self._callbacks: Dict[int, Callable] = {}
         self._results: Dict[int, torch.Tensor] = {}
@@ -42,9 +49,20 @@ class DeviceKVMap:
 
     @classmethod
     def create(cls, fabric_or_none=None, *, table_capacity: int = 1 << 20, max_keys: int = 1 << 18,
-               opt: Optional[OptimizerConfig] = None, ring: int = 4, quant: str = "none", world: int = 1):
-        pc = PlaneConfig(table_capacity=table_capacity, inbox_cap=max_keys, ring=ring, quant=quant)
-        fab = fabric_or_none or Fabric.single(heap_layout(pc, world).total())
+               opt: Optional[OptimizerConfig] = None, ring: int = 4, quant: str = "none", world: int = 1,
+               exchange: bool = True):
+        """``fabric_or_none``: an existing fabric whose heap is large enough, or None to
+        make one: over the default process group when ``torch.distributed`` is
+        initialised with more than one rank, else a single-GPU heap."""
+        pc = PlaneConfig(table_capacity=table_capacity, inbox_cap=max_keys, ring=ring, quant=quant,
+                         pull_cap=max_keys if exchange else 0)
+        fab = fabric_or_none
+        if fab is None:
+            import torch.distributed as dist
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                fab = Fabric.from_process_group(heap_layout(pc, dist.get_world_size()).total())
+            else:
+                fab = Fabric.single(heap_layout(pc, world).total())
         return cls(DataPlane(fab, pc, opt or OptimizerConfig(algo="sum")), max_keys)
 
     def _stamp(self, ts: Optional[int]) -> int:
@@ -69,7 +87,7 @@ class DeviceKVMap:
     def _buffer(self, keys: torch.Tensor) -> LocalBatch:
         b = self._bufs[self._next_buf]
         self._next_buf = (self._next_buf + 1) % len(self._bufs)
-        b.set_keys(keys, self.plane.bounds_host)
+        b.set_keys(keys, self.plane.bounds)
         return b
 
     @staticmethod
@@ -105,8 +123,14 @@ class DeviceKVMap:
         with torch.cuda.stream(self.stream):
             b = self._buffer(k)
             # the owners must have applied every round pushed so far
-            self.plane.pull_margin(b, need_applied=self._round, with_margins=False, stream=self.stream)
-            self._results[ts] = b.w_local[:k.numel()].clone()
+            if self.plane.cfg.pull_cap:
+                rnd = self._pull_round
+                self._pull_round += 1
+                self.plane.pull_exchange(b, rnd, need_applied=self._round, with_margins=False, stream=self.stream)
+                self._results[ts] = self.plane.response_weights(rnd, k.numel()).clone()
+            else:
+                self.plane.pull_margin(b, need_applied=self._round, with_margins=False, stream=self.stream)
+                self._results[ts] = b.w_local[:k.numel()].clone()
         self._finish(ts, callback)
         return ts
 

@@ -135,7 +135,7 @@ def test_dead_source_is_skipped_and_wait_times_out_cleanly(cuda_lib):
     planes = _mk(2, opt)
     b = LocalBatch(8, 64, 2, "cuda")
     keys = np.array([5, 1 << 63, (1 << 63) + 9], dtype=np.uint64)
-    b.set_keys(torch.from_numpy(keys.view(np.int64)).cuda(), planes[0].bounds_host)
+    b.set_keys(torch.from_numpy(keys.view(np.int64)).cuda(), planes[0].bounds)
     b.grad[:3] = torch.tensor([1.0, 2.0, 3.0]).cuda()
     planes[0].push(b, 0, with_gradient=False)       # rank 1 never pushes
     planes[1].set_alive(1, False)
