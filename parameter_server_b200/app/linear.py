@@ -116,11 +116,16 @@ def run_async_sgd(conf, verbose=True):
     text = data.get("text", "LIBSVM")
     max_nnz = int(os.environ.get("PSB_MAX_NNZ_PER_ROW", "512")) * minibatch
     table_cap = 1 << int(os.environ.get("PSB_LOG2_TABLE", "22"))
+    # two-sided exchange pull unless the key-caching filter is asked for (that one belongs to the one-sided pull)
     pc = PlaneConfig(table_capacity=table_cap, inbox_cap=max_nnz, ring=tau + 2, quant=quant, key_cache=key_cache,
-                     ordered_slots=os.environ.get("PSB_ORDERED_SLOTS", "0") == "1")
+                     ordered_slots=os.environ.get("PSB_ORDERED_SLOTS", "0") == "1",
+                     pull_cap=0 if key_cache else max_nnz)
     hb = heap_layout(pc, world).total()
     fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
     plane = DataPlane(fab, pc, opt)
+    if conf.get("_checkpoint_in"):
+        from ..utils import checkpoint
+        checkpoint.load_plane(plane, conf["_checkpoint_in"])
     worker = SparseLRWorker(plane, SparseLRConfig(max_rows=minibatch, max_nnz=max_nnz, tau=tau, hash_seed=None,
                                                   pipeline=2, auc=True, real_values=text not in ("SPARSE_BINARY", "ADFEA", "TERAFEA", "CRITEO")))
     printer = ProgressPrinter()
@@ -168,6 +173,9 @@ def run_async_sgd(conf, verbose=True):
         keys, w = plane.dump_nonzero()
         os.makedirs(os.path.dirname(out) or ".", exist_ok=True)
         write_model(f"{out}_S{rank}", keys.numpy(), w.numpy())
+    if conf.get("_checkpoint_out"):
+        from ..utils import checkpoint
+        checkpoint.save_plane(plane, conf["_checkpoint_out"], meta={"minibatches": steps, "examples": printer.total})
     if dist is not None:
         dist.barrier()
         fab.close()
@@ -324,9 +332,14 @@ def main(argv: Optional[List[str]] = None):
     ap = argparse.ArgumentParser(prefix_chars="-")
     ap.add_argument("-app_file", "--app_file", default="")
     ap.add_argument("-app_conf", "--app_conf", default="")
+    ap.add_argument("-checkpoint_in", "--checkpoint_in", default="",
+                    help="async SGD: resume from the binary shard checkpoint <prefix>_S<rank>.psbckpt")
+    ap.add_argument("-checkpoint_out", "--checkpoint_out", default="",
+                    help="async SGD: write weights and optimiser state to <prefix>_S<rank>.psbckpt at the end")
     args, _ = ap.parse_known_args(argv)
     text = (open(args.app_file).read() if args.app_file else "") + args.app_conf
     conf = core.parse_text_proto(text)
+    conf["_checkpoint_in"], conf["_checkpoint_out"] = args.checkpoint_in, args.checkpoint_out
     from .. import _build
     _build.build_cuda()
     if "darlin" in conf:

@@ -259,11 +259,16 @@ void BindSystem(py::module& m) {
   app.def(py::init<Postoffice*, int>(), py::arg("po") = nullptr, py::arg("id") = 0, py::keep_alive<1, 2>());
   app.def("run", [](App& a) { a.App::Run(); }, py::call_guard<py::gil_scoped_release>());
   m.def("set_app_factory", [](py::function f) {
-    auto holder = std::make_shared<py::object>(f);
+    // The factory lives in a C++ static that is destroyed after the interpreter has
+    // gone, so it must not own a Python reference: the callable is held by a pointer
+    // that is replaced here (with the GIL held) and deliberately never freed at exit.
+    static py::object* current = nullptr;
+    delete current;
+    current = new py::object(f);
     App::external_ownership() = true;
-    App::SetFactory([holder](const std::string& conf, Postoffice* po) -> App* {
+    App::SetFactory([](const std::string& conf, Postoffice* po) -> App* {
       py::gil_scoped_acquire g;
-      py::object o = (*holder)(conf, py::cast(po, py::return_value_policy::reference));
+      py::object o = (*current)(conf, py::cast(po, py::return_value_policy::reference));
       KeepAlive().push_back(o);
       return o.cast<App*>();
     });

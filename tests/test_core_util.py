@@ -242,3 +242,28 @@ def test_options_env_workload_pool_dashboard(tmp_path, monkeypatch):
     assert "busy(ms)" in rep[0] and [l.split()[0] for l in rep[1:]] == ["H", "S0", "W1"] and " 7 " in rep[3]
     tt = core.TaskTracker(); tt.start(1); assert tt.was_started(1) and not tt.has_finished(1)
     tt.finish(1); tt.wait(1); assert tt.has_finished(1)
+
+
+def test_checkpoint_file_roundtrip(tmp_path):
+    """Binary shard checkpoint: what is written is read back bit for bit; bad files are refused."""
+    import numpy as np
+    import pytest
+    from parameter_server_b200.utils import checkpoint as ck
+    rng = np.random.default_rng(0)
+    n = 1000
+    keys = np.sort(rng.integers(0, 1 << 63, n, dtype=np.uint64))
+    w, s0, s1 = (rng.standard_normal(n).astype(np.float32) for _ in range(3))
+    p = ck.shard_path(str(tmp_path / "m"), 3)
+    ck.write_shard(p, keys, w, s0, s1, {"rank": 3, "world": 4, "key_begin": 0, "key_end": 1 << 63, "meta": {"step": 17}})
+    hdr, k2, w2, a2, b2 = ck.read_shard(p)
+    assert hdr["n"] == n and hdr["meta"]["step"] == 17 and hdr["rank"] == 3
+    assert np.array_equal(k2, keys) and np.array_equal(w2, w) and np.array_equal(a2, s0) and np.array_equal(b2, s1)
+    bad = tmp_path / "bad.psbckpt"
+    bad.write_bytes(b"not a checkpoint")
+    with pytest.raises(ValueError):
+        ck.read_shard(str(bad))
+    blob = open(p, "rb").read()
+    trunc = tmp_path / "trunc.psbckpt"
+    trunc.write_bytes(blob[:len(blob) - 100])
+    with pytest.raises(ValueError):
+        ck.read_shard(str(trunc))

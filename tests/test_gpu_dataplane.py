@@ -220,3 +220,38 @@ def test_pull_exchange_equals_one_sided_path(cuda_lib, S):
     for (k0, w0), (k1, w1) in zip(results[0][1], results[1][1]):
         assert np.array_equal(k0.numpy(), k1.numpy())
         assert np.allclose(w0.numpy(), w1.numpy(), rtol=1e-4, atol=1e-6)
+
+
+def test_checkpoint_resume_equals_uninterrupted_run(cuda_lib, tmp_path):
+    """Train 3 steps, checkpoint (weights and FTRL z/n), load into a fresh plane with a
+    different number of shards, train 3 more: same model as 6 uninterrupted steps."""
+    from parameter_server_b200.models.sparse_lr import SparseLRConfig, SparseLRWorker
+    from parameter_server_b200.parallel.dataplane import OptimizerConfig
+    from parameter_server_b200.utils import checkpoint as ck
+    opt = OptimizerConfig(algo="ftrl", alpha=0.1, beta=1.0, l1=0.01, l2=0.1)
+    rows, z = 128, 16
+    rng = np.random.default_rng(4)
+    data = [_batch(rng, rows, z, 4000)[:2] for _ in range(6)]
+
+    def worker(plane):
+        return SparseLRWorker(plane, SparseLRConfig(max_rows=rows, max_nnz=rows * z, tau=0, hash_seed=1, pipeline=1))
+
+    def run(w, batches):
+        for ids, y in batches:
+            w.step(torch.from_numpy(ids).cuda(), torch.from_numpy(y).cuda(), fixed_z=z)
+        torch.cuda.synchronize()
+
+    ref = worker(_mk(1, opt)[0])
+    run(ref, data)
+    k_ref, w_ref = ref.plane.dump_nonzero()
+
+    a = worker(_mk(1, opt)[0])
+    run(a, data[:3])
+    prefix = str(tmp_path / "ckpt")
+    ck.save_plane(a.plane, prefix, meta={"step": 3})
+    b = worker(_mk(1, opt, ordered=True)[0])
+    assert ck.load_plane(b.plane, prefix)["step"] == 3
+    run(b, data[3:])
+    k_b, w_b = b.plane.dump_nonzero()
+    assert torch.equal(k_ref, k_b)
+    assert torch.allclose(w_ref, w_b, rtol=1e-6, atol=1e-7)

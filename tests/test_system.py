@@ -207,6 +207,12 @@ def test_task_packing_more_flag_delivers_all_in_order():
         cl.stop()
 
 
+def _servers_by_range(cl):
+    """Servers ordered by the key range they own (ranges are handed out in registration
+    order, which need not be the order of the node ids)."""
+    return sorted(cl.apps("S"), key=lambda a: a.my_node().key.begin)
+
+
 def test_kv_vector_push_pull_two_channels():
     class A(core.App):
         def __init__(self, po):
@@ -231,7 +237,7 @@ def test_kv_vector_push_pull_two_channels():
         assert w1.kv.values(1).tolist() == [11, 13, 15]
         # push adds into the servers' values
         w0.kv.wait(w0.kv.push(core.request(0), k0, [np.ones(3, np.float32)]))
-        s0, s1 = cl.apps("S")
+        s0, s1 = _servers_by_range(cl)
         assert s0.kv.values(0).tolist()[:3] == [1, 1, 3] and s1.kv.values(0).tolist()[4] == 5
     finally:
         cl.stop()
@@ -252,7 +258,7 @@ def test_kv_vector_buffered_aggregation_and_dependent_pull():
         keys = np.array([2, 4, half + 1, half + 3], dtype=np.uint64)
         for w in cl.apps("W"):
             w.kv.set_channel(4, keys, np.zeros(8, np.float32))
-        for j, s in enumerate(cl.apps("S")):     # every server holds the keys of its own range
+        for j, s in enumerate(_servers_by_range(cl)):     # every server holds the keys of its own range
             s.kv.set_channel(4, keys[2 * j:2 * j + 2], np.zeros(4, np.float32))
         ts = 0
         for i, w in enumerate(cl.apps("W")):
@@ -260,7 +266,7 @@ def test_kv_vector_buffered_aggregation_and_dependent_pull():
             u = np.full(8, 10.0 * (1 + i), np.float32)
             w.kv.push(core.request(4, ts), keys, [g, u])
             w.kv.pull(core.request(4, ts + 2, [ts + 1]), keys)
-        for j, s in enumerate(cl.apps("S")):
+        for j, s in enumerate(_servers_by_range(cl)):
             s.kv.wait_received_request(ts, core.kWorkerGroup)
             buf = s.kv.buffer(ts)
             assert buf["idx_range"] == (0, 2) and buf["channel"] == 4
@@ -296,7 +302,7 @@ def test_kv_map_custom_entry_push_then_pull():
         w = ws[0]
         w.kv.wait(w.kv.pull(core.request(0), keys))
         assert w.kv.values(0).tolist() == [3, 6, 9]
-        assert [s.kv.size() for s in cl.apps("S")] == [2, 1]
+        assert [s.kv.size() for s in _servers_by_range(cl)] == [2, 1]
     finally:
         cl.stop()
 
