@@ -133,6 +133,31 @@ def build_core(force: bool = False) -> Path:
     return out
 
 
+def build_sanitized_binary(kinds: str = "address,undefined") -> Path:
+    """``bin/psb_linear_san``: the stand-alone node binary compiled with
+    ``-fsanitize=<kinds>`` (``address,undefined`` or ``thread``). The reference builds
+    with no sanitizer at all (``make/config.mk:10``); this is how the host runtime
+    (van, postoffice, executor, parameters, filters, learners) is checked for memory
+    errors, undefined behaviour and data races on CPU-only machines:
+    ``python -m parameter_server_b200._build --sanitize[=thread]`` and then run the
+    binary like ``bin/psb_linear`` (e.g. with ``system.cluster.launch_local_processes``)."""
+    core_dir = CSRC / "core"
+    cxx = os.environ.get("PSB_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
+    tag = "tsan" if "thread" in kinds else "san"
+    odir = OBJ / tag
+    odir.mkdir(parents=True, exist_ok=True)
+    flags = ["-O1", "-g", "-fno-omit-frame-pointer", f"-fsanitize={kinds}", "-std=c++17", "-Wall", "-pthread",
+             "-I", str(core_dir)]
+    sources = [s for s in sorted(core_dir.glob("*.cc")) if not s.name.startswith("bind") and s.name != "ps_main.cc"]
+    objs = [odir / (s.stem + ".o") for s in sources]
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        list(ex.map(lambda so: _run([cxx, *flags, "-c", str(so[0]), "-o", str(so[1])], None), zip(sources, objs)))
+    exe = PKG / "bin" / ("psb_linear_" + tag)
+    exe.parent.mkdir(exist_ok=True)
+    _run([cxx, f"-fsanitize={kinds}", "-pthread", "-o", str(exe), *map(str, objs), "-lz"])
+    return exe
+
+
 def build_all(force: bool = False, verbose: bool = False):
     a = build_cuda(force=force, verbose=verbose)
     b = build_core(force=force)
@@ -140,6 +165,10 @@ def build_all(force: bool = False, verbose: bool = False):
 
 
 if __name__ == "__main__":
+    san = [a for a in sys.argv if a.startswith("--sanitize")]
+    if san:
+        print(build_sanitized_binary(san[0].split("=", 1)[1] if "=" in san[0] else "address,undefined"))
+        sys.exit(0)
     paths = build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
     for p in paths:
         print(p)

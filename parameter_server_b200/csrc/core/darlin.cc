@@ -504,16 +504,22 @@ class DarlinWorker : public DarlinCompNode {
 
   void Update(Message* request) override {
     const BCDCall& call = request->task.bcd;
-    if (call.reset_kkt_filter) for (int g : fea_grp_) active_set_[g].fill(true);
+    if (call.reset_kkt_filter) { Lock l(dual_mu_); for (int g : fea_grp_) active_set_[g].fill(true); }
     int time = call.time, grp = call.feature_group_id;
     Range<Key> blk = call.key;
     auto& kv = model_[grp];
     SizeR col = kv.key.FindRange(blk);
-    busy_timer_.start();
     SArray<Real> G(col.size()), U(col.size());
     G.SetZero(); U.SetZero();
-    if (!col.empty() && X_.count(grp)) ComputeGradient(grp, col, &G, &U);
-    busy_timer_.stop();
+    {
+      // The gradient of this block and the dual update of an earlier block (which runs on
+      // the parameter's thread when its pull returns) share dual_, the weights, the active
+      // set and the trust-region deltas: one at a time, as in darlin.h:300-312,398-470.
+      Lock l(dual_mu_);
+      busy_timer_.start();
+      if (!col.empty() && X_.count(grp)) ComputeGradient(grp, col, &G, &U);
+      busy_timer_.stop();
+    }
     // push (G, U) at `time`
     Task push = Parameter::Request(grp, time, {}, filters(), blk);
     model_.Push(push, kv.key.Segment(col), {G, U});
@@ -536,6 +542,7 @@ class DarlinWorker : public DarlinCompNode {
   }
 
   void Evaluate(BCDProgress* prog) override {
+    Lock l(dual_mu_);
     double objv = 0;
     for (size_t i = 0; i < dual_.size(); ++i) objv += std::log1p(1.0 / dual_[i]);
     prog->objective = objv;
@@ -584,6 +591,7 @@ class DarlinWorker : public DarlinCompNode {
     }
   }
   void UpdateDual(int grp, SizeR col_range, const SArray<Real>& new_w) {
+    Lock l(dual_mu_);
     auto& cur_w = model_[grp].value;
     auto& active = active_set_[grp];
     auto& delta = delta_[grp];
@@ -598,7 +606,6 @@ class DarlinWorker : public DarlinCompNode {
       cur_w[j] = nw;
     }
     if (!X_.count(grp)) return;
-    Lock l(dual_mu_);
     busy_timer_.start();
     const auto& X = *X_[grp];
     const size_t* offset = X.offset().data();

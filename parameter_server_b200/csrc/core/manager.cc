@@ -8,7 +8,19 @@
 
 namespace PS {
 
+void Manager::StopCustomers() {
+  // Join every customer's executor thread before any customer is destroyed: a
+  // destructor must not run while the thread may still call into the object.
+  std::vector<Customer*> all;
+  {
+    Lock l(customer_mu_);
+    for (auto& c : customers_) all.push_back(c.second);
+  }
+  for (Customer* c : all) c->executor()->Stop();
+}
+
 Manager::~Manager() {
+  StopCustomers();
   // the app is owned here unless an external factory keeps it
   if (!App::external_ownership()) delete app_;
   app_ = nullptr;

@@ -21,6 +21,7 @@ class Manager {
   // blocks until this node is registered (and, for workers, servers are ready); then app->Run()
   void Run(bool run_app = true);
   void Stop();
+  void StopCustomers();   // joins the executor threads of all registered customers
   // handles a control message; returns false on EXIT
   bool Process(Message* msg);
 

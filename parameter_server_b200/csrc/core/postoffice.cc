@@ -7,6 +7,7 @@ namespace PS {
 Postoffice::Postoffice() : manager_(this) {}
 
 Postoffice::~Postoffice() {
+  manager_.StopCustomers();
   if (running_) {
     running_ = false;
     auto t = std::make_shared<Message>();
@@ -40,6 +41,9 @@ void Postoffice::Start(const Options& opt) {
 
 void Postoffice::Stop() {
   manager_.Stop();
+  // no customer thread may still be replying (and queueing messages) while the
+  // send thread and the queues go away
+  manager_.StopCustomers();
   if (running_) {
     running_ = false;
     auto t = std::make_shared<Message>();

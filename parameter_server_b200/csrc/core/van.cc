@@ -233,8 +233,7 @@ bool Van::Send(Message* msg, size_t* send_bytes) {
     data_size += header.size();
   }
   *send_bytes = data_size;
-  auto h = hostnames_.find(id);
-  if (h != hostnames_.end() && h->second == my_node_.hostname) sent_to_local_ += data_size;
+  if (IsLocalPeer(id)) sent_to_local_ += data_size;
   else sent_to_others_ += data_size;
   PS_VLOG(2) << "send " << msg->ShortDebugString();
   return ok;
@@ -326,8 +325,7 @@ void Van::PollLoop() {
       if (RecvTcp(fd, m.get(), &bytes)) {
         m->sender = id;
         m->recver = my_node_.id;
-        auto h = hostnames_.find(id);
-        if (h != hostnames_.end() && h->second == my_node_.hostname) received_from_local_ += bytes;
+        if (IsLocalPeer(id)) received_from_local_ += bytes;
         else received_from_others_ += bytes;
         inbox_.push(m);
       } else {

@@ -12,6 +12,7 @@
 //                 single-process GPU deployment, where the bulk data moves over
 //                 NVLink and only headers pass through the Van.
 #pragma once
+#include <atomic>
 #include <set>
 #include "message.h"
 #include "threading.h"
@@ -63,9 +64,16 @@ class Van {
   bool RecvTcp(int fd, Message* msg, size_t* bytes);
   void PollLoop();
   bool IsLocal(const Node& n) const { return n.hostname == my_node_.hostname; }
+  // whether peer `id` runs on this host (hostnames_ is guarded by mu_)
+  bool IsLocalPeer(const NodeID& id) {
+    std::lock_guard<std::mutex> l(mu_);
+    auto h = hostnames_.find(id);
+    return h != hostnames_.end() && h->second == my_node_.hostname;
+  }
 
   Node my_node_, scheduler_;
-  bool inproc_ = false, local_ipc_ = false, running_ = false;
+  bool inproc_ = false, local_ipc_ = false;
+  std::atomic<bool> running_{false};   // read by the poll thread, written by Destroy()
   int listen_fd_ = -1;
   int wake_fd_[2] = {-1, -1};
   std::mutex mu_;
