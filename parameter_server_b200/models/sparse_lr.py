@@ -36,6 +36,7 @@ class SparseLRConfig:
     real_values: bool = False
     pipeline: int = 3                  # minibatches in flight on the worker: copy | localise | pull+push
     auc: bool = False
+    nvtx: bool = False                 # NVTX ranges around the stages of submit() for timeline profilers
 
 
 class SparseLRWorker:
@@ -104,6 +105,9 @@ class SparseLRWorker:
         b = self.bufs[k]
         dev = self.plane.device
         cur = torch.cuda.current_stream(dev)
+        mark = torch.cuda.nvtx.range_push if self.cfg.nvtx else (lambda name: None)
+        done = torch.cuda.nvtx.range_pop if self.cfg.nvtx else (lambda: None)
+        mark(f"submit {self.step_no}: copy")
         # stage 1, copy stream: host -> device into this buffer's staging area (reusable once the
         # localise that last read it has finished)
         self.copy_stream.wait_stream(cur)
@@ -123,6 +127,8 @@ class SparseLRWorker:
             ids_d, y_d = to_dev(ids, "ids"), to_dev(y, "y")
             vals_d, rp_d = to_dev(vals, "vals"), to_dev(row_ptr, "row_ptr")
             self._copy_done[k].record(self.copy_stream)
+        done()
+        mark("localise")
         # stage 2, prep stream: sort + unique + remap (the buffer is free once its push has read it)
         self.prep_stream.wait_event(self._copy_done[k])
         self.prep_stream.wait_event(self._buf_free[k])
@@ -132,6 +138,8 @@ class SparseLRWorker:
                        stream=self.prep_stream)
             self._prep_done[k].record(self.prep_stream)
         self.main_stream.wait_event(self._prep_done[k])
+        done()
+        mark("pull+push+apply")
         t = self.step_no
         need = max(0, t - self.cfg.tau)
         if need > 0:
@@ -155,6 +163,7 @@ class SparseLRWorker:
         self.server_stream.wait_event(self._push_done)
         self.plane.apply(t, stream=self.server_stream)
         self._applied_ev[t % len(self._applied_ev)].record(self.server_stream)
+        done()
         self.step_no += 1
         return b
 
