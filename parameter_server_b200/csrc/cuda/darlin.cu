@@ -20,6 +20,7 @@
 //
 // The worker keeps margins m = Xw instead of dual = exp(y m): tau = 1/(1+exp(y m))
 // is evaluated where it is used, and the dual update becomes an atomic add.
+#include <cstdlib>
 #include "psb_common.cuh"
 #include "psb_cuda.h"
 
@@ -40,55 +41,82 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_grad(const PsbDarlinGrad p
   const int lane = threadIdx.x & 31;
   const u32 gwarp = gtid >> 5, nwarps = gsize >> 5;
   const u32 ncol = p.c1 - p.c0;
-  // phase 0: clear the staging area
-  for (u32 i = gtid; i < 2 * p.block_cap; i += gsize) p.stage[i] = 0.f;
-  if (!grid_barrier(p.bar, p.status)) return;
-  // phase 1: segmented reduction over the block's nonzeros
+  // The staging area is zero on entry: phase 2 of the previous call cleared what it read.
+  // phase 1: segmented reduction over the block's nonzeros. A warp takes chunks of
+  // kChunkWords consecutive 32-element words and carries the sums of a column that runs
+  // over a word boundary in registers, so that a frequent feature (a column of millions of
+  // nonzeros under a Zipf law) costs two atomics per chunk instead of two per word:
+  // same-address atomics serialise in L2.
   if (p.u1 > p.u0) {
     const u32 nz0 = p.seg_off[p.u0], nz1 = p.seg_off[p.u1];
     const u32 w0 = nz0 >> 5, w1 = (nz1 + 31) >> 5;
     const u32 le = 0xffffffffu >> (31 - lane);
-    for (u32 wi = w0 + gwarp; wi < w1; wi += nwarps) {
-      u32 i = wi * 32 + lane;
-      u32 f = p.flagbits[wi];
-      u32 fle = f & le;
-      u32 u = p.wordbase[wi] + __popc(fle) - 1;     // local unique key of this nonzero
-      bool in = i >= nz0 && i < nz1;
-      float g = 0.f, h = 0.f;
-      if (in) {
-        u32 c = p.gcol[u];
-        if (p.active[c]) {
-          u32 r = p.csc_row[i];
-          float y = p.y[r];
-          float ym = y * __ldcg(&p.margin[r]);
-          // tau = 1/(1+exp(y m)) evaluated stably
-          float en = expf(-fabsf(ym));
-          float tau = ym > 0 ? en / (1.f + en) : 1.f / (1.f + en);
-          float d = p.delta[c];
-          if (p.csc_val) {
-            float v = p.csc_val[i];
-            g = -y * tau * v;
-            h = fminf(tau * (1.f - tau) * expf(fabsf(v) * d), 0.25f) * v * v;
-          } else {
-            g = -y * tau;
-            h = fminf(tau * (1.f - tau) * expf(d), 0.25f);
+    // chunk length: up to 16 words, but no longer than what keeps every warp busy
+    const u32 kChunkWords = max(1u, min(16u, (w1 - w0 + nwarps - 1) / nwarps));
+    const u32 nchunks = (w1 - w0 + kChunkWords - 1) / kChunkWords;
+    for (u32 ch = gwarp; ch < nchunks; ch += nwarps) {
+      const u32 wb = w0 + ch * kChunkWords, we = min(w1, wb + kChunkWords);
+      float cg = 0.f, chh = 0.f;   // sums so far of the column that is open at the word boundary
+      u32 cu = 0;                  // its local unique-key index
+      bool open = false;
+      for (u32 wi = wb; wi < we; ++wi) {
+        const u32 i = wi * 32 + lane;
+        const u32 f = p.flagbits[wi];
+        const u32 fle = f & le;
+        const u32 u = p.wordbase[wi] + __popc(fle) - 1;     // local unique key of this nonzero
+        const bool in = i >= nz0 && i < nz1;
+        float g = 0.f, h = 0.f;
+        if (in) {
+          u32 c = p.gcol[u];
+          if (p.active[c]) {
+            u32 r = p.csc_row[i];
+            float y = p.y[r];
+            float ym = y * __ldcg(&p.margin[r]);
+            // tau = 1/(1+exp(y m)) evaluated stably
+            float en = expf(-fabsf(ym));
+            float tau = ym > 0 ? en / (1.f + en) : 1.f / (1.f + en);
+            float d = p.delta[c];
+            if (p.csc_val) {
+              float v = p.csc_val[i];
+              g = -y * tau * v;
+              h = fminf(tau * (1.f - tau) * expf(fabsf(v) * d), 0.25f) * v * v;
+            } else {
+              g = -y * tau;
+              h = fminf(tau * (1.f - tau) * expf(d), 0.25f);
+            }
           }
         }
-      }
-      // segmented inclusive scan inside the word; segment = column
-      int start = fle ? 31 - __clz(fle) : 0;
+        auto flush = [&](u32 uu, float gg, float hh) {
+          u32 c = p.gcol[uu] - p.c0;
+          if (c < p.block_cap && (gg != 0.f || hh != 0.f)) {
+            atomicAdd(&p.stage[c], gg);
+            atomicAdd(&p.stage[p.block_cap + c], hh);
+          }
+        };
+        if (open && (f & 1u)) {                     // the open column ended with the previous word
+          if (lane == 0) flush(cu, cg, chh);
+          open = false; cg = chh = 0.f;
+        }
+        // segmented inclusive scan inside the word; segment = column
+        int start = fle ? 31 - __clz(fle) : 0;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        float g2 = __shfl_up_sync(0xffffffffu, g, o);
-        float h2 = __shfl_up_sync(0xffffffffu, h, o);
-        if (lane >= start + o) { g += g2; h += h2; }
-      }
-      bool tail = (lane == 31) || ((f >> (lane + 1)) & 1u) || (i + 1 == nz1);
-      if (in && tail) {
-        u32 c = p.gcol[u] - p.c0;
-        if (c < p.block_cap && (g != 0.f || h != 0.f)) {
-          atomicAdd(&p.stage[c], g);
-          atomicAdd(&p.stage[p.block_cap + c], h);
+        for (int o = 1; o < 32; o <<= 1) {
+          float g2 = __shfl_up_sync(0xffffffffu, g, o);
+          float h2 = __shfl_up_sync(0xffffffffu, h, o);
+          if (lane >= start + o) { g += g2; h += h2; }
+        }
+        if (fle == 0) { g += cg; h += chh; }        // lanes that continue the open column (the carry is 0 otherwise)
+        const bool tail = (lane == 31) || ((f >> (lane + 1)) & 1u) || (i + 1 == nz1);
+        // the word's last column stays open unless this is the chunk's last word or the block's data ends here
+        const bool keep = (wi + 1 < we) && ((wi + 1) * 32 < nz1);
+        if (in && tail && !(keep && lane == 31)) flush(u, g, h);
+        if (keep) {
+          cg = __shfl_sync(0xffffffffu, g, 31);
+          chh = __shfl_sync(0xffffffffu, h, 31);
+          cu = p.wordbase[wi] + __popc(f) - 1;
+          open = true;
+        } else {
+          open = false; cg = chh = 0.f;
         }
       }
     }
@@ -99,6 +127,8 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_grad(const PsbDarlinGrad p
     int s = shard_of_col(p.shard_col, p.S, p.c0 + c);
     p.gu_inbox[s][c] = __ldcg(&p.stage[c]);
     p.gu_inbox[s][p.block_cap + c] = __ldcg(&p.stage[p.block_cap + c]);
+    p.stage[c] = 0.f;                      // leave the staging area clean for the next block
+    p.stage[p.block_cap + c] = 0.f;
   }
   __threadfence_system();
   __syncthreads();
@@ -261,7 +291,12 @@ static int darlin_grid(const void* fn) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per, fn, kDThreads, 0);
-  per = per < 1 ? 1 : (per > 4 ? 4 : per);
+  // CTAs per SM: 4 measured best (23.7 / 24.9 / 26.6 ms per pass of 256 blocks with 4 / 2 / 1);
+  // PSB_DARLIN_CTAS_PER_SM overrides (1..4).
+  int want = 4;
+  if (const char* e = getenv("PSB_DARLIN_CTAS_PER_SM")) want = atoi(e);
+  want = want < 1 ? 1 : (want > 4 ? 4 : want);
+  per = per < 1 ? 1 : (per > want ? want : per);
   return sms * per;
 }
 

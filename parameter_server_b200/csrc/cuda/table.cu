@@ -483,7 +483,8 @@ __global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
     // and added to grad once, so a frequent key (a segment of up to millions of
     // nonzeros) costs one atomic per chunk, not one per word: same-address atomics
     // serialise in L2. Four words are loaded per trip (row ids, then the gathers).
-    constexpr u32 kChunkWords = 16;
+    // chunk length: up to 16 words, but no longer than what keeps every warp busy (small batches)
+    const u32 kChunkWords = max(1u, min(16u, (nwords + nwarps - 1) / nwarps));
     const u32 nchunks = (nwords + kChunkWords - 1) / kChunkWords;
     for (u32 c = gwarp; c < nchunks; c += nwarps) {
       const u32 wend = min(nwords, (c + 1) * kChunkWords);

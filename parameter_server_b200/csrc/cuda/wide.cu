@@ -287,37 +287,105 @@ struct WidePushArgs {
   const __nv_bfloat16* ctx;                    // [N x 64] (context n in row n)
   uint32_t* done;
   uint32_t* status;
+  uint32_t* bar;                               // 2 words (grid barrier), zero on first use
+  uint32_t* n_long;                            // 1 word, zero on entry, left zero
+  uint32_t* long_list;                         // long_cap words: unique-key indices of long segments
+  float* long_acc;                             // long_cap x 64 floats, zero on entry, left zero
+  uint32_t long_cap;
 };
+
+// Segments longer than this are reduced by many warps (under a Zipf law one key can
+// own a fifth of all nonzeros; a single warp walking it would take milliseconds).
+static constexpr u32 kWideLongSeg = 1024;
+
+// G += sum over the elements [i0, i1) of gcoef[row] * C[ctx(row), 2*lane .. 2*lane+1]; the row ids,
+// coefficients and context ids of 32 elements are fetched by the lanes in parallel and then
+// broadcast one by one, the context rows come from shared memory.
+__device__ __forceinline__ void wide_seg_accumulate(const WidePushArgs& p, const __nv_bfloat162* s_ctx, u32 i0, u32 i1,
+                                                    int lane, float& g0, float& g1) {
+  for (u32 base = i0; base < i1; base += 32) {
+    const u32 i = base + lane;
+    float gc = 0.f;
+    u32 n = 0;
+    if (i < i1) {
+      const u32 r = __ldcs(&p.csc_row[i]);
+      gc = __ldg(&p.gcoef[r]);
+      n = p.row_ctx ? p.row_ctx[r] : r % (u32)p.N;
+    }
+    const int cnt = (int)min(32u, i1 - base);
+    for (int e = 0; e < cnt; ++e) {
+      const float gce = __shfl_sync(0xffffffffu, gc, e);
+      const u32 ne = __shfl_sync(0xffffffffu, n, e);
+      const __nv_bfloat162 c2 = s_ctx[ne * (kWide / 2) + lane];
+      g0 += gce * __bfloat162float(c2.x);
+      g1 += gce * __bfloat162float(c2.y);
+    }
+  }
+}
 
 __global__ void __launch_bounds__(256) k_wide_push(const WidePushArgs p) {
   __shared__ u32 s_off[PSB_MAX_SHARDS + 1];
   __shared__ u32 s_last;
+  __shared__ __nv_bfloat162 s_ctx[128 * kWide / 2];   // the context matrix, 16 KB at N = 128
   if (threadIdx.x <= p.S) s_off[threadIdx.x] = p.own_off[threadIdx.x];
+  for (int i = threadIdx.x; i < p.N * kWide / 2; i += blockDim.x) s_ctx[i] = reinterpret_cast<const __nv_bfloat162*>(p.ctx)[i];
   __syncthreads();
   const u32 U = *p.n_unique;
   const int lane = threadIdx.x & 31;
   const u32 gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
-  for (u32 u = gwarp; u < U; u += nwarps) {
-    // lane handles dimensions 2*lane, 2*lane+1
-    float g0 = 0.f, g1 = 0.f;
-    for (u32 i = p.seg_off[u]; i < p.seg_off[u + 1]; ++i) {
-      u32 r = p.csc_row[i];
-      float gc = __ldg(&p.gcoef[r]);
-      u32 n = p.row_ctx ? p.row_ctx[r] : r % (u32)p.N;
-      __nv_bfloat162 c2 = reinterpret_cast<const __nv_bfloat162*>(p.ctx + (size_t)n * kWide)[lane];
-      g0 += gc * __bfloat162float(c2.x);
-      g1 += gc * __bfloat162float(c2.y);
-    }
+  auto emit = [&](u32 u, float g0, float g1) {
     int s = owner_of(s_off, p.S, u);
     u32 j = u - s_off[s];
-    if (j >= p.inbox_cap) { if (lane == 0) set_status(p.status, kInboxOverflow); continue; }
+    if (j >= p.inbox_cap) { if (lane == 0) set_status(p.status, kInboxOverflow); return; }
     reinterpret_cast<__nv_bfloat162*>(p.inbox_vals[s] + (size_t)j * kWide)[lane] = __floats2bfloat162_rn(g0, g1);
     if (lane == 0) p.inbox_keys[s][j] = p.ukeys[u];
+  };
+  // ---- phase 1: one warp per key; long segments are only listed
+  for (u32 u = gwarp; u < U; u += nwarps) {
+    const u32 i0 = p.seg_off[u], i1 = p.seg_off[u + 1];
+    if (i1 - i0 > kWideLongSeg && p.long_cap) {
+      if (lane == 0) {
+        u32 k = atomicAdd(p.n_long, 1u);
+        if (k < p.long_cap) p.long_list[k] = u; else set_status(p.status, kInboxOverflow);
+      }
+      continue;
+    }
+    float g0 = 0.f, g1 = 0.f;   // lane handles dimensions 2*lane, 2*lane+1
+    wide_seg_accumulate(p, s_ctx, i0, i1, lane, g0, g1);
+    emit(u, g0, g1);
+  }
+  if (p.long_cap) {
+    if (!grid_barrier(p.bar, p.status)) return;
+    // ---- phase 2: the chunks of all long segments, spread over all warps
+    const u32 n_long = min(*((volatile u32*)p.n_long), p.long_cap);
+    u32 first = 0;   // index of the key's first chunk in the global chunk numbering
+    for (u32 k = 0; k < n_long; ++k) {
+      const u32 u = p.long_list[k];
+      const u32 i0 = p.seg_off[u], i1 = p.seg_off[u + 1];
+      const u32 nch = (i1 - i0 + kWideLongSeg - 1) / kWideLongSeg;
+      // chunk c of this key is taken by warp (first + c) % nwarps
+      for (u32 c = (gwarp + nwarps - first % nwarps) % nwarps; c < nch; c += nwarps) {
+        float g0 = 0.f, g1 = 0.f;
+        wide_seg_accumulate(p, s_ctx, i0 + c * kWideLongSeg, min(i1, i0 + (c + 1) * kWideLongSeg), lane, g0, g1);
+        atomicAdd(&p.long_acc[(size_t)k * kWide + 2 * lane], g0);
+        atomicAdd(&p.long_acc[(size_t)k * kWide + 2 * lane + 1], g1);
+      }
+      first += nch;
+    }
+    if (!grid_barrier(p.bar, p.status)) return;
+    // ---- phase 3: emit the long keys and leave the scratch zeroed
+    for (u32 k = gwarp; k < n_long; k += nwarps) {
+      float2* a = reinterpret_cast<float2*>(p.long_acc + (size_t)k * kWide) + lane;
+      float2 g = __ldcg(a);
+      *a = make_float2(0.f, 0.f);
+      emit(p.long_list[k], g.x, g.y);
+    }
   }
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) s_last = atomicAdd(p.done, 1u) + 1 == gridDim.x;
   __syncthreads();
+  if (s_last && threadIdx.x == 0 && p.n_long) *p.n_long = 0;
   if (s_last && threadIdx.x < p.S) {
     int s = threadIdx.x;
     __threadfence_system();
@@ -492,8 +560,17 @@ extern "C" int psb_wide_rowsum(const float* P, int N, const uint32_t* row_ptr, u
 extern "C" int psb_wide_push(const void* args, cudaStream_t stream) {
   WidePushArgs a = *reinterpret_cast<const WidePushArgs*>(args);
   if (a.S < 1 || a.S > PSB_MAX_SHARDS) return -(int)cudaErrorInvalidValue;
-  k_wide_push<<<148 * 4, 256, 0, stream>>>(a);
-  return -(int)cudaGetLastError();
+  // cooperative: the phases of the long-segment path are separated by grid barriers
+  static int grid = 0;
+  if (!grid) {
+    int dev = 0, sms = 0, per = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per, (const void*)k_wide_push, 256, 0);
+    grid = sms * (per < 1 ? 1 : (per > 4 ? 4 : per));
+  }
+  void* params[] = {&a};
+  return -(int)cudaLaunchCooperativeKernel((const void*)k_wide_push, dim3(grid), dim3(256), params, 0, stream);
 }
 extern "C" int psb_wide_apply(const void* args, cudaStream_t stream) {
   WideApplyArgs a = *reinterpret_cast<const WideApplyArgs*>(args);

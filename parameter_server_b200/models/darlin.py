@@ -129,11 +129,28 @@ class DarlinRank:
         return int(np.searchsorted(self.gcol_host, c0)), int(np.searchsorted(self.gcol_host, c1))
 
     # ---- the three kernels of a block
+    def streams(self):
+        """(gradient stream, update + dual stream) of the two-stream block pipeline."""
+        if "_streams" not in self.__dict__:
+            self._streams = (torch.cuda.Stream(device=self.dev), torch.cuda.Stream(device=self.dev))
+        return self._streams
+
+    def _cached(self, kind: str, blk: int, q: int):
+        """Parameter blocks are built once per (kernel, block, ring slot): with hundreds of
+        blocks per pass the launches are otherwise bound by the host filling these structs."""
+        cache = self.__dict__.setdefault("_param_cache", {})
+        return cache, (kind, blk, q), cache.get((kind, blk, q))
+
     def grad(self, blk: int, ts: int, stream=None):
+        q = ts % self.R
+        cache, key, p = self._cached("grad", blk, q)
+        if p is not None:
+            p.ts1 = ts + 1
+            check(_lib.lib().psb_darlin_grad(C.byref(p), stream_ptr(stream)), "darlin_grad")
+            return
         c0, c1 = self.blocks[blk]
         u0, u1 = self._block_u(c0, c1)
-        q = ts % self.R
-        p = DarlinGrad()
+        p = cache[key] = DarlinGrad()
         p.S, p.ts1, p.c0, p.c1, p.u0, p.u1, p.block_cap = self.S, ts + 1, c0, c1, u0, u1, self.cfg.block_cols
         for s in range(self.S + 1):
             p.shard_col[s] = self.shard_col[s]
@@ -148,12 +165,20 @@ class DarlinRank:
         check(_lib.lib().psb_darlin_grad(C.byref(p), stream_ptr(stream)), "darlin_grad")
 
     def update(self, blk: int, ts: int, wait_iters: int = 0, stream=None):
-        c0, c1 = self.blocks[blk]
         q = ts % self.R
-        p = DarlinUpdate()
+        cache, key, p = self._cached("update", blk, q)
+        if p is not None:
+            if p is False:
+                return
+            p.ts1, p.kkt_threshold, p.wait_iters = ts + 1, self.kkt_threshold, wait_iters
+            check(_lib.lib().psb_darlin_update(C.byref(p), stream_ptr(stream)), "darlin_update")
+            return
+        c0, c1 = self.blocks[blk]
         my0, my1 = max(c0, self.shard_col[self.rank]), min(c1, self.shard_col[self.rank + 1])
         if my1 <= my0:
+            cache[key] = False
             return                                    # no column of this block is mine
+        p = cache[key] = DarlinUpdate()
         p.S, p.ts1, p.c0, p.c1, p.my0, p.my1, p.block_cap = self.S, ts + 1, c0, c1, my0, my1, self.cfg.block_cols
         for r in range(self.S):
             p.gu_inbox[r] = self._gu(self.rank, q, r)
@@ -169,10 +194,15 @@ class DarlinRank:
         check(_lib.lib().psb_darlin_update(C.byref(p), stream_ptr(stream)), "darlin_update")
 
     def dual(self, blk: int, ts: int, wait_iters: int = 0, stream=None):
+        q = ts % self.R
+        cache, key, p = self._cached("dual", blk, q)
+        if p is not None:
+            p.ts1, p.wait_iters = ts + 1, wait_iters
+            check(_lib.lib().psb_darlin_dual(C.byref(p), stream_ptr(stream)), "darlin_dual")
+            return
         c0, c1 = self.blocks[blk]
         u0, u1 = self._block_u(c0, c1)
-        q = ts % self.R
-        p = DarlinDual()
+        p = cache[key] = DarlinDual()
         p.S, p.ts1, p.c0, p.c1, p.u0, p.u1, p.block_cap = self.S, ts + 1, c0, c1, u0, u1, self.cfg.block_cols
         for s in range(self.S + 1):
             p.shard_col[s] = self.shard_col[s]
@@ -233,16 +263,42 @@ def run_darlin(ranks: Sequence[DarlinRank], *, all_reduce=None, verbose: bool = 
             for r in ranks:
                 r.reset_kkt_filter()
         # software pipeline: gradients run `tau` blocks ahead of the weight application
-        for i in range(len(order) + tau):
-            if i < len(order):
-                for r in ranks:
-                    r.grad(order[i], ts + i)
-            j = i - tau
-            if j >= 0:
-                for r in ranks:
-                    r.update(order[j], ts + j)
-                for r in ranks:
-                    r.dual(order[j], ts + j)
+        if len(ranks) == 1 and tau > 0:
+            # One rank per process: the gradient kernels go to one stream and update + dual to
+            # another, so that the small, latency-bound kernels of different blocks overlap.
+            # Bounded delay: the gradient of block i waits for the dual update of block
+            # i - tau - 1 (an event); update(j) is enqueued after the local grad(j) has
+            # finished (an event), so its device-side waits are for other GPUs only.
+            r = ranks[0]
+            sg, su = r.streams()
+            cur = torch.cuda.current_stream(r.dev)
+            sg.wait_stream(cur); su.wait_stream(cur)
+            ev_grad = [torch.cuda.Event() for _ in order]
+            ev_dual = [torch.cuda.Event() for _ in order]
+            for i in range(len(order) + tau):
+                if i < len(order):
+                    if i - tau - 1 >= 0:
+                        sg.wait_event(ev_dual[i - tau - 1])
+                    r.grad(order[i], ts + i, stream=sg)
+                    ev_grad[i].record(sg)
+                j = i - tau
+                if j >= 0:
+                    su.wait_event(ev_grad[j])
+                    r.update(order[j], ts + j, stream=su)
+                    r.dual(order[j], ts + j, stream=su)
+                    ev_dual[j].record(su)
+            cur.wait_stream(sg); cur.wait_stream(su)
+        else:
+            for i in range(len(order) + tau):
+                if i < len(order):
+                    for r in ranks:
+                        r.grad(order[i], ts + i)
+                j = i - tau
+                if j >= 0:
+                    for r in ranks:
+                        r.update(order[j], ts + j)
+                    for r in ranks:
+                        r.dual(order[j], ts + j)
         ts += len(order)
         loss = l1 = nnz = act = vio = 0.0
         for r in ranks:

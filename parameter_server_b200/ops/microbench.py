@@ -175,6 +175,113 @@ def bench_wide(args):
                       "tflops": 2.0 * U * 64 * N / (med * 1e-3) / 1e12, "peak": tag}))
 
 
+def bench_wide_step(args):
+    """Full training step of the wide-value model on 1..N ranks: localise, pull fused with
+    the tcgen05 product against the batch's context matrix, row sums + loss, push of
+    64-wide bf16 gradients to the owners, AdaGrad apply. Per worker `rows` x `z` keys
+    (Zipf s = 1.2) over 2^log2_keys ids; examples/s of the whole job, max over ranks."""
+    import numpy as np
+    import torch.distributed as dist
+    from .localize import LocalBatch
+    from ..parallel.fabric import Fabric
+    from ..parallel.wide import WideConfig, WidePlane, wide_layout
+    from ..utils.synthetic import gen_batch
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rows, z, N = args.rows, args.z, args.n_ctx
+    n_feat = 1 << args.log2_keys
+    cap = 1
+    while cap < 2 * n_feat // world:
+        cap *= 2
+    cfg = WideConfig(table_capacity=cap, inbox_cap=rows * z, ring=args.tau + 2)
+    hb = wide_layout(cfg, world).total()
+    fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb)
+    plane = WidePlane(fab, cfg)
+    pool = [gen_batch(rows, z, n_feat, 1.2, 0, rank * 1009 + i, device=dev)[:2] for i in range(args.pool)]
+    bufs = [LocalBatch(rows, rows * z, world, dev) for _ in range(2)]
+    # every key of every rank's pool goes into its owner's table before timing
+    mine = []
+    for ids, y in pool:
+        b = bufs[0].localize(ids, y, plane.bounds, fixed_z=z, hash_seed=0, hash_bits=40)
+        torch.cuda.synchronize()
+        mine.append(b.ukeys[:int(b.n_unique.item())].cpu().numpy().view(np.uint64).copy())
+    allk = [np.unique(np.concatenate(mine))]
+    if world > 1:
+        got = [None] * world
+        dist.all_gather_object(got, allk[0])
+        allk = got
+    lo, hi = plane.bounds_host[rank], plane.bounds_host[rank + 1]
+    own = np.unique(np.concatenate([k[(k >= np.uint64(lo)) & ((k < np.uint64(hi)) if hi < (1 << 64) - 1 else True)] for k in allk]))
+    g = torch.Generator().manual_seed(rank)
+    for c0 in range(0, len(own), 1 << 20):
+        kk = own[c0:c0 + (1 << 20)]
+        plane.load(kk, torch.randn(len(kk), 64, generator=g) * 0.1)
+    ctx = (torch.randn(N, 64, generator=torch.Generator().manual_seed(7)) * 0.3).to(torch.bfloat16).to(dev)
+    P = torch.zeros(rows * z, N, device=dev)
+    step_no = [0]
+
+    def step(i):
+        ids, y = pool[i % len(pool)]
+        b = bufs[i % 2].localize(ids, y, plane.bounds, fixed_z=z, hash_seed=0, hash_bits=40)
+        plane.pull_gemm(b, ctx, P)
+        plane.rowsum(b, P, N)
+        plane.push(b, ctx, step_no[0])
+        plane.apply(step_no[0])
+        step_no[0] += 1
+
+    for i in range(4):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.iters):
+        step(i)
+    e1.record(); torch.cuda.synchronize()
+    plane.check_status("wide step")
+    # stage times (CUDA events, stages back to back on one stream), a few steps
+    names = ["localize", "pull_gemm", "rowsum", "push", "apply"]
+    acc = [0.0] * 5
+    for i in range(6):
+        ids, y = pool[i % len(pool)]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        ev[0].record()
+        b = bufs[i % 2].localize(ids, y, plane.bounds, fixed_z=z, hash_seed=0, hash_bits=40)
+        ev[1].record(); plane.pull_gemm(b, ctx, P)
+        ev[2].record(); plane.rowsum(b, P, N)
+        ev[3].record(); plane.push(b, ctx, step_no[0])
+        ev[4].record(); plane.apply(step_no[0])
+        ev[5].record(); step_no[0] += 1
+        torch.cuda.synchronize()
+        for k in range(5):
+            acc[k] += ev[k].elapsed_time(ev[k + 1]) / 6
+    if world > 1:
+        ta = torch.tensor(acc, dtype=torch.float64, device=dev)
+        dist.all_reduce(ta, op=dist.ReduceOp.MAX)
+        acc = ta.tolist()
+    stages = {n: round(v, 4) for n, v in zip(names, acc)}
+    ms = e0.elapsed_time(e1) / args.iters
+    u = float(np.mean([len(k) for k in mine]))
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    st = plane.stats.cpu().tolist()
+    if rank == 0:
+        print(json.dumps({"kernel": "wide model training step", "gpus": world, "rows_per_gpu": rows, "keys_per_row": z,
+                          "table_keys": n_feat, "contexts": N, "unique_keys_per_step_per_gpu": u, "ms_per_step": ms,
+                          "examples_per_s": world * rows / (ms * 1e-3),
+                          "value_bytes_pulled_and_pushed_per_s": world * u * 256 / (ms * 1e-3),
+                          "loss_per_example": st[0] / max(1.0, st[2]), "stage_ms_max_over_ranks": stages}))
+    if world > 1:
+        dist.barrier(); fab.close(); dist.destroy_process_group()
+
+
 def bench_kv(args):
     """Push + pull of K sorted unique keys per rank with scalar values through the
     device KV containers: keys/s for the pair push-then-pull (max over ranks). Under
@@ -316,6 +423,9 @@ def main():
     s = sub.add_parser("wide"); s.add_argument("--rows", type=int, default=32768); s.add_argument("--z", type=int, default=40)
     s.add_argument("--log2-keys", type=int, default=22); s.add_argument("--n-ctx", type=int, default=128)
     s.add_argument("--iters", type=int, default=5)
+    s = sub.add_parser("wide-step"); s.add_argument("--rows", type=int, default=32768); s.add_argument("--z", type=int, default=40)
+    s.add_argument("--log2-keys", type=int, default=25); s.add_argument("--n-ctx", type=int, default=64)
+    s.add_argument("--iters", type=int, default=20); s.add_argument("--tau", type=int, default=8); s.add_argument("--pool", type=int, default=4)
     s = sub.add_parser("darlin"); s.add_argument("--rows", type=int, default=1250000); s.add_argument("--z", type=int, default=100)
     s.add_argument("--log2-keys", type=int, default=24); s.add_argument("--passes", type=int, default=3)
     s.add_argument("--tau", type=int, default=2)
@@ -327,7 +437,8 @@ def main():
     sys.path.insert(0, os.fspath(Path(__file__).resolve().parents[2]))
     from .. import _build
     _build.build_cuda()
-    {"sort": bench_sort, "step": bench_step, "wide": bench_wide, "kv": bench_kv, "darlin": bench_darlin}[args.cmd](args)
+    {"sort": bench_sort, "step": bench_step, "wide": bench_wide, "wide-step": bench_wide_step, "kv": bench_kv,
+     "darlin": bench_darlin}[args.cmd](args)
 
 
 if __name__ == "__main__":

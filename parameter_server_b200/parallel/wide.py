@@ -34,7 +34,8 @@ class _PushArgs(C.Structure):
                 ("inbox_keys", _vp * MAX_SHARDS), ("inbox_vals", _vp * MAX_SHARDS),
                 ("ready", _vp * MAX_SHARDS), ("count", _vp * MAX_SHARDS),
                 ("ukeys", _vp), ("n_unique", _vp), ("own_off", _vp), ("seg_off", _vp), ("csc_row", _vp),
-                ("gcoef", _vp), ("row_ctx", _vp), ("ctx", _vp), ("done", _vp), ("status", _vp)]
+                ("gcoef", _vp), ("row_ctx", _vp), ("ctx", _vp), ("done", _vp), ("status", _vp),
+                ("bar", _vp), ("n_long", _vp), ("long_list", _vp), ("long_acc", _vp), ("long_cap", _u32)]
 
 
 class _ApplyArgs(C.Structure):
@@ -106,6 +107,10 @@ class WidePlane:
             m = (cfg.table_capacity << 64) // size if (cfg.ordered_slots and size > cfg.table_capacity) else 0
             self.slot_mult.append(m if m < (1 << 64) else 0)
         self.sync = torch.zeros(16, dtype=torch.int32, device=dev)
+        # scratch of the push for keys with very long segments (zeroed once, left zeroed by the kernel)
+        self.long_cap = max(64, cfg.inbox_cap // 1024 + 1)
+        self.long_list = torch.zeros(self.long_cap, dtype=torch.int32, device=dev)
+        self.long_acc = torch.zeros(self.long_cap * WIDTH, dtype=torch.float32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.stats = torch.zeros(4, dtype=torch.float64, device=dev)
         check(self.L.psb_wide_init(self._p("keys"), self._p("vals"), self._p("acc"), cfg.table_capacity, stream_ptr()), "wide_init")
@@ -163,6 +168,8 @@ class WidePlane:
         a.ukeys, a.n_unique, a.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
         a.seg_off, a.csc_row, a.gcoef, a.row_ctx, a.ctx = ptr(b.seg_off), ptr(b.csc_row), ptr(b.gcoef), ptr(row_ctx), ptr(ctx)
         a.done, a.status = self.sync.data_ptr() + 8, ptr(self.status)
+        a.bar, a.n_long = self.sync.data_ptr() + 32, self.sync.data_ptr() + 40
+        a.long_list, a.long_acc, a.long_cap = ptr(self.long_list), ptr(self.long_acc), self.long_cap
         check(self.L.psb_wide_push(C.byref(a), stream_ptr(stream)), "wide_push")
 
     def apply(self, ts: int, wait_iters: int = 0, stream=None):

@@ -49,9 +49,13 @@ def test_wide_pull_gemm_matches_fp32_matmul(cuda_lib, S, N):
     assert torch.allclose(P[:U].cpu(), ref, rtol=1e-3, atol=1e-3), float((P[:U].cpu() - ref).abs().max())
 
 
-def test_wide_training_step_matches_reference(cuda_lib):
+@pytest.mark.parametrize("n_rows", [300, 900])
+def test_wide_training_step_matches_reference(cuda_lib, n_rows):
+    """With 900 rows the most frequent key owns about 3,000 nonzeros: its gradient is
+    reduced by several warps (segments above 1,024 nonzeros are split into chunks)."""
     S, N = 2, 64
-    planes, b, ctx, table, known, all_keys, ids, y, rows, z = _setup(S, N, seed=4)
+    planes, b, ctx, table, known, all_keys, ids, y, rows, z = _setup(S, N, rows=n_rows, seed=4)
+    assert int((b.seg_off[1:int(b.n_unique.item()) + 1] - b.seg_off[:int(b.n_unique.item())]).max().item()) > (1024 if n_rows == 900 else 0)
     U = int(b.n_unique.item())
     w = planes[0]
     P = torch.zeros(b.max_nnz, N, device="cuda")
