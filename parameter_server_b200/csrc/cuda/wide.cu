@@ -145,46 +145,132 @@ struct WidePullArgs {
   uint32_t* status;
 };
 
-__global__ void __launch_bounds__(128) k_wide_pull_gemm(const __grid_constant__ CUtensorMap ctx_map, const WidePullArgs p) {
-  // operand tiles: 1024-byte aligned because of the 128-byte swizzle
-  extern __shared__ __align__(1024) unsigned char smem[];
-  unsigned char* sA = smem;                      // [128 rows x 128 B]
-  unsigned char* sB = smem + kTileM * 128;       // [N rows x 128 B]
-  __shared__ u64 s_bar[2];                       // 0: TMA, 1: MMA
-  __shared__ u32 s_tmem;
-  __shared__ u32 s_off[PSB_MAX_SHARDS + 1];
-  __shared__ u32 s_fail;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int N = p.N;
-  const u32 U = *p.n_unique;
-  if (tid <= p.S) s_off[tid] = p.own_off[tid];
+// Exchange form of the pull (see k_wide_pull_xgemm): per-owner flags and buffers.
+struct WideXArgs {
+  int S, me;
+  int N;
+  uint32_t ts1, req_cap, wait_iters, phases;
+  // my shard (owner role)
+  psb_u64* keys;
+  const __nv_bfloat16* vals;
+  psb_u64 mask, key_begin, slot_mult;
+  // requester role: where my keys go and who tells me that my rows have arrived
+  psb_u64* req_keys[PSB_MAX_SHARDS];         // owner s's request buffer for source me
+  uint32_t* req_hdr[PSB_MAX_SHARDS];         // {count, base} at owner s for source me
+  uint32_t* req_ready[PSB_MAX_SHARDS];
+  const uint32_t* my_resp_ready[PSB_MAX_SHARDS];   // set by owner s when my rows are in place
+  const __nv_bfloat16* my_resp_rows;         // [pull_cap x 64] local
+  // owner role: the sources' requests here, and their response buffers
+  const psb_u64* my_req_keys[PSB_MAX_SHARDS];
+  const uint32_t* my_req_hdr[PSB_MAX_SHARDS];
+  const uint32_t* my_req_ready[PSB_MAX_SHARDS];
+  __nv_bfloat16* resp_rows[PSB_MAX_SHARDS];  // source r's response buffer
+  uint32_t* resp_ready[PSB_MAX_SHARDS];      // source r's flag for owner me
+  uint8_t alive[PSB_MAX_SHARDS];
+  const psb_u64* ukeys;
+  const uint32_t* n_unique;
+  const uint32_t* own_off;
+  float* P;
+  uint32_t* done;                            // 2 words, zero on entry, left zero
+  uint32_t* status;
+};
+
+// Shared state of the tensor-core tile loop.
+struct WideTileCtx {
+  unsigned char* sA;
+  unsigned char* sB;
+  u64* bar;        // 2 mbarriers: 0 = TMA, 1 = MMA
+  u32 tmem_base;
+  u32 idesc;
+  u32 phase;
+  u32* s_fail;
+};
+
+// One [128 x 64] x [64 x N] tile: `row` holds this thread's 128-byte value row (zeros when
+// absent); the product goes to P[u, :].
+__device__ __forceinline__ bool wide_tile_mma_store(WideTileCtx& c, const uint4 (&row)[8], u32 u, u32 U, int N, float* P,
+                                                    u32* status) {
+  const int tid = threadIdx.x, warp = tid >> 5;
+#pragma unroll
+  for (int q = 0; q < 8; ++q)   // 16-byte chunk q of row r lands at chunk (q ^ (r & 7))
+    *reinterpret_cast<uint4*>(c.sA + tid * 128 + ((q ^ (tid & 7)) << 4)) = row[q];
+  fence_async_smem();
+  __syncthreads();
+  // ---- MMA: one thread issues K = 64 as four K = 16 steps
   if (tid == 0) {
-    s_fail = 0;
-    mbar_init(&s_bar[0], 1);
-    mbar_init(&s_bar[1], 1);
+    tc_fence_after();
+    const u64 da = make_smem_desc(smem_u32(c.sA)), db = make_smem_desc(smem_u32(c.sB));
+#pragma unroll
+    for (int k = 0; k < 4; ++k) umma_bf16(c.tmem_base, da + (u64)(2 * k), db + (u64)(2 * k), c.idesc, k > 0 ? 1u : 0u);
+    umma_commit(&c.bar[1]);
+  }
+  if (!mbar_wait(&c.bar[1], c.phase, 1u << 22)) { if (tid == 0) { *c.s_fail = 1; set_status(status, kWaitTimeout); } }
+  c.phase ^= 1;
+  tc_fence_after();
+  __syncthreads();
+  if (*c.s_fail) return false;
+  // ---- epilogue: warp w owns TMEM lanes [32w, 32w+32) = rows of the tile
+  for (int c0 = 0; c0 < N; c0 += 32) {
+    u32 r[32];
+    tmem_ld_32x32(c.tmem_base + ((u32)(warp * 32) << 16) + (u32)c0, r);
+    if (u < U) {
+      float4* dst = reinterpret_cast<float4*>(P + (size_t)u * N + c0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                             __uint_as_float(r[4 * j + 3]));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  return true;
+}
+
+// Common prologue: mbarriers, TMEM allocation, context matrix by TMA. Returns false on a time-out.
+__device__ __forceinline__ bool wide_tile_setup(WideTileCtx& c, const CUtensorMap* ctx_map, int N, u32* s_tmem, u32* status) {
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    *c.s_fail = 0;
+    mbar_init(&c.bar[0], 1);
+    mbar_init(&c.bar[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 0) tmem_alloc(&s_tmem, (u32)N);
+  if (warp == 0) tmem_alloc(s_tmem, (u32)N);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const u32 tmem_base = s_tmem;
-  // context matrix, once per CTA
+  c.tmem_base = *s_tmem;
   if (tid == 0) {
-    mbar_expect_tx(&s_bar[0], (u32)N * 128u);
-    tma_load_2d(sB, &ctx_map, 0, 0, &s_bar[0]);
+    mbar_expect_tx(&c.bar[0], (u32)N * 128u);
+    tma_load_2d(c.sB, ctx_map, 0, 0, &c.bar[0]);
   }
-  if (!mbar_wait(&s_bar[0], 0, 1u << 22)) { if (tid == 0) { s_fail = 1; set_status(p.status, kWaitTimeout); } }
+  if (!mbar_wait(&c.bar[0], 0, 1u << 22)) { if (tid == 0) { *c.s_fail = 1; set_status(status, kWaitTimeout); } }
   __syncthreads();
-  const u32 idesc = make_idesc(kTileM, N);
+  c.idesc = make_idesc(kTileM, N);
+  c.phase = 0;
+  return *c.s_fail == 0;
+}
+
+__global__ void __launch_bounds__(128) k_wide_pull_gemm(const __grid_constant__ CUtensorMap ctx_map, const WidePullArgs p) {
+  // operand tiles: 1024-byte aligned because of the 128-byte swizzle
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ u64 s_bar[2];
+  __shared__ u32 s_tmem;
+  __shared__ u32 s_off[PSB_MAX_SHARDS + 1];
+  __shared__ u32 s_fail;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int N = p.N;
+  const u32 U = *p.n_unique;
+  if (tid <= p.S) s_off[tid] = p.own_off[tid];
+  WideTileCtx c{smem, smem + kTileM * 128, s_bar, 0, 0, 0, &s_fail};
+  wide_tile_setup(c, &ctx_map, N, &s_tmem, p.status);
   const u32 ntiles = (U + kTileM - 1) / kTileM;
-  u32 phase = 0;
   for (u32 t = blockIdx.x; t < ntiles && !s_fail; t += gridDim.x) {
     // ---- gather: thread = one key = one 128-byte row
     const u32 u = t * kTileM + tid;
     uint4 row[8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) row[c] = make_uint4(0, 0, 0, 0);
+    for (int q = 0; q < 8; ++q) row[q] = make_uint4(0, 0, 0, 0);
     if (u < U) {
       int s = owner_of(s_off, p.S, u);
       const SlotMap sm{p.mask[s], p.key_begin[s], p.slot_mult[s]};
@@ -192,50 +278,135 @@ __global__ void __launch_bounds__(128) k_wide_pull_gemm(const __grid_constant__ 
       if (slot >= 0) {
         const uint4* src = reinterpret_cast<const uint4*>(p.vals[s] + (size_t)slot * kWide);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) row[c] = src[c];
+        for (int q = 0; q < 8; ++q) row[q] = src[q];
       }
       if (p.v_local) {
         uint4* dst = reinterpret_cast<uint4*>(p.v_local + (size_t)u * kWide);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) dst[c] = row[c];
+        for (int q = 0; q < 8; ++q) dst[q] = row[q];
       }
     }
-#pragma unroll
-    for (int c = 0; c < 8; ++c)   // 16-byte chunk c of row r lands at chunk (c ^ (r & 7))
-      *reinterpret_cast<uint4*>(sA + tid * 128 + ((c ^ (tid & 7)) << 4)) = row[c];
-    fence_async_smem();
-    __syncthreads();
-    // ---- MMA: one thread issues K = 64 as four K = 16 steps
-    if (tid == 0) {
-      tc_fence_after();
-      const u64 da = make_smem_desc(smem_u32(sA)), db = make_smem_desc(smem_u32(sB));
-#pragma unroll
-      for (int k = 0; k < 4; ++k) umma_bf16(tmem_base, da + (u64)(2 * k), db + (u64)(2 * k), idesc, k > 0 ? 1u : 0u);
-      umma_commit(&s_bar[1]);
-    }
-    if (!mbar_wait(&s_bar[1], phase, 1u << 22)) { if (tid == 0) { s_fail = 1; set_status(p.status, kWaitTimeout); } }
-    phase ^= 1;
-    tc_fence_after();
-    __syncthreads();
-    if (s_fail) break;
-    // ---- epilogue: warp w owns TMEM lanes [32w, 32w+32) = rows of the tile
-    for (int c0 = 0; c0 < N; c0 += 32) {
-      u32 r[32];
-      tmem_ld_32x32(tmem_base + ((u32)(warp * 32) << 16) + (u32)c0, r);
-      if (u < U) {
-        float4* dst = reinterpret_cast<float4*>(p.P + (size_t)u * N + c0);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
-                               __uint_as_float(r[4 * j + 3]));
-      }
-    }
-    tc_fence_before();
-    __syncthreads();
+    if (!wide_tile_mma_store(c, row, u, U, N, p.P, p.status)) break;
   }
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, (u32)N);
-  (void)lane;
+  if (warp == 0) tmem_dealloc(c.tmem_base, (u32)N);
+}
+
+// Exchange form of the fused pull: three roles in one cooperative kernel.
+//   (a) requester: my sorted unique keys go to their owners' request buffers in bulk;
+//   (b) owner: for every source, look its keys up in my table and store the 128-byte
+//       value rows into the source's response buffer (peer stores), then raise that
+//       source's flag;
+//   (c) requester: tile by tile, wait for the flags of the owners that cover the tile,
+//       read the rows from the local response buffer and run the tcgen05 product.
+// Only bulk stores cross NVLink (keys out, rows back); tiles of an owner that has
+// answered are multiplied while other owners are still sending. `phases` (bit 0: a,
+// bit 1: b, bit 2: c) lets ranks emulated on one GPU run the roles as separate launches.
+__global__ void __launch_bounds__(128) k_wide_pull_xgemm(const __grid_constant__ CUtensorMap ctx_map, const WideXArgs p) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ u64 s_bar[2];
+  __shared__ u32 s_tmem;
+  __shared__ u32 s_off[PSB_MAX_SHARDS + 1];
+  __shared__ u32 s_fail, s_last, s_n, s_base;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int S = p.S, N = p.N;
+  const u32 U = *p.n_unique;
+  const u32 iters = p.wait_iters ? p.wait_iters : kPeerWaitIters;
+  const u32 gsize = gridDim.x * blockDim.x, gtid = blockIdx.x * blockDim.x + tid;
+  if (tid <= S) s_off[tid] = p.own_off[tid];
+  __syncthreads();
+  // ---- (a)
+  if (p.phases & 1) {
+    for (u32 u = gtid; u < U; u += gsize) {
+      int s = owner_of(s_off, S, u);
+      u32 j = u - s_off[s];
+      if (j < p.req_cap) p.req_keys[s][j] = p.ukeys[u];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(&p.done[0], 1u) + 1 == gridDim.x;
+    __syncthreads();
+    if (s_last && tid < S) {
+      int s = tid;
+      u32 cnt = s_off[s + 1] - s_off[s];
+      if (cnt > p.req_cap) { set_status(p.status, kInboxOverflow); cnt = p.req_cap; }
+      __threadfence_system();
+      p.req_hdr[s][0] = cnt;
+      p.req_hdr[s][1] = s_off[s];
+      __threadfence_system();
+      st_release_sys(p.req_ready[s], p.ts1);
+      if (s == 0) atomicExch(&p.done[0], 0u);
+    }
+  }
+  // ---- (b)
+  if (p.phases & 2) {
+    const SlotMap sm{p.mask, p.key_begin, p.slot_mult};
+    for (int r = 0; r < S; ++r) {
+      if (!p.alive[r]) continue;
+      __syncthreads();
+      if (tid == 0) {
+        u32 n = 0, base = 0;
+        if (wait_flag_ge_sys(p.my_req_ready[r], p.ts1, iters)) {
+          n = *((volatile const u32*)&p.my_req_hdr[r][0]);
+          base = *((volatile const u32*)&p.my_req_hdr[r][1]);
+        } else {
+          set_status(p.status, kWaitTimeout);
+        }
+        s_n = min(n, p.req_cap);
+        s_base = base;
+      }
+      __syncthreads();
+      const u32 n = s_n, base = s_base;
+      // eight lanes per key: the look-up by the first of them, then one 16-byte chunk each
+      // (the trip count is the same for every lane of a warp: the shuffle needs all of them)
+      const u32 n8 = (n * 8 + 31) & ~31u;
+      for (u32 j8 = gtid; j8 < n8; j8 += gsize) {
+        const u32 j = j8 >> 3, q = j8 & 7;
+        const bool valid = j < n;
+        long long slot = -1;
+        if (valid && q == 0) slot = wide_find<false>(p.keys, sm, p.my_req_keys[r][j]);
+        slot = __shfl_sync(0xffffffffu, slot, (tid & 31) & ~7);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (slot >= 0) v = reinterpret_cast<const uint4*>(p.vals + (size_t)slot * kWide)[q];
+        if (valid) reinterpret_cast<uint4*>(p.resp_rows[r] + (size_t)(base + j) * kWide)[q] = v;
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(&p.done[1], 1u) + 1 == gridDim.x;
+    __syncthreads();
+    if (s_last && tid < S && p.alive[tid]) {
+      __threadfence_system();
+      st_release_sys(p.resp_ready[tid], p.ts1);
+    }
+    if (s_last && tid == 0) atomicExch(&p.done[1], 0u);
+  }
+  if (!(p.phases & 4)) return;
+  // ---- (c)
+  WideTileCtx c{smem, smem + kTileM * 128, s_bar, 0, 0, 0, &s_fail};
+  wide_tile_setup(c, &ctx_map, N, &s_tmem, p.status);
+  const u32 ntiles = (U + kTileM - 1) / kTileM;
+  for (u32 t = blockIdx.x; t < ntiles && !s_fail; t += gridDim.x) {
+    const u32 u0 = t * kTileM, u = u0 + tid;
+    if (tid == 0) {
+      const int sa = owner_of(s_off, S, u0), sb = owner_of(s_off, S, min(u0 + kTileM - 1, U - 1));
+      for (int s = sa; s <= sb; ++s)
+        if (p.alive[s] && !wait_flag_ge_sys(p.my_resp_ready[s], p.ts1, iters)) { s_fail = 1; set_status(p.status, kWaitTimeout); }
+    }
+    __syncthreads();
+    if (s_fail) break;
+    uint4 row[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) row[q] = make_uint4(0, 0, 0, 0);
+    if (u < U) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.my_resp_rows + (size_t)u * kWide);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) row[q] = src[q];
+    }
+    if (!wide_tile_mma_store(c, row, u, U, N, p.P, p.status)) break;
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(c.tmem_base, (u32)N);
 }
 
 // ---------------------------------------------------------------- rows: prediction, loss, gcoef
@@ -296,7 +467,7 @@ struct WidePushArgs {
 
 // Segments longer than this are reduced by many warps (under a Zipf law one key can
 // own a fifth of all nonzeros; a single warp walking it would take milliseconds).
-static constexpr u32 kWideLongSeg = 1024;
+static constexpr u32 kWideLongSeg = 256;
 
 // G += sum over the elements [i0, i1) of gcoef[row] * C[ctx(row), 2*lane .. 2*lane+1]; the row ids,
 // coefficients and context ids of 32 elements are fetched by the lanes in parallel and then
@@ -550,6 +721,40 @@ extern "C" int psb_wide_pull_gemm(const void* args, const void* ctx, uint32_t ma
   return -(int)cudaGetLastError();
 }
 
+// args: a WideXArgs block; ctx as above. Cooperative launch: the roles wait on one another.
+extern "C" int psb_wide_pull_xgemm(const void* args, const void* ctx, uint32_t max_unique, cudaStream_t stream) {
+  WideXArgs a = *reinterpret_cast<const WideXArgs*>(args);
+  if (a.N != 64 && a.N != 128) return -(int)cudaErrorInvalidValue;
+  if (a.S < 1 || a.S > PSB_MAX_SHARDS) return -(int)cudaErrorInvalidValue;
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return -(int)cudaErrorNotSupported;
+  CUtensorMap map;
+  cuuint64_t dims[2] = {(cuuint64_t)kWide, (cuuint64_t)a.N};
+  cuuint64_t strides[1] = {(cuuint64_t)kWide * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kWide, (cuuint32_t)a.N};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ctx), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -(int)cudaErrorInvalidValue;
+  size_t smem = (size_t)kTileM * 128 + (size_t)a.N * 128 + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute((const void*)k_wide_pull_xgemm, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    attr_set = true;
+  }
+  // all CTAs must be co-resident: three per SM (each holds N <= 128 of the SM's 512 TMEM columns)
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  (void)max_unique;
+  int per = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per, (const void*)k_wide_pull_xgemm, 128, smem);
+  per = per < 1 ? 1 : (per > 3 ? 3 : per);
+  void* params[] = {&map, &a};
+  return -(int)cudaLaunchCooperativeKernel((const void*)k_wide_pull_xgemm, dim3(sms * per), dim3(128), params, smem, stream);
+}
+
 extern "C" int psb_wide_rowsum(const float* P, int N, const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z,
                                const uint32_t* csr_col, const uint32_t* row_ctx, const float* y, float* gcoef,
                                float* margin, double* stats, cudaStream_t stream) {
@@ -587,5 +792,6 @@ extern "C" int psb_wide_apply(const void* args, cudaStream_t stream) {
   return -(int)cudaLaunchCooperativeKernel((const void*)k_wide_apply, dim3(grid), dim3(256), params, 0, stream);
 }
 extern "C" int psb_wide_args_size(int which) {
-  return which == 0 ? (int)sizeof(WidePullArgs) : which == 1 ? (int)sizeof(WidePushArgs) : (int)sizeof(WideApplyArgs);
+  return which == 0 ? (int)sizeof(WidePullArgs) : which == 1 ? (int)sizeof(WidePushArgs)
+       : which == 2 ? (int)sizeof(WideApplyArgs) : (int)sizeof(WideXArgs);
 }

@@ -197,7 +197,7 @@ def bench_wide_step(args):
     cap = 1
     while cap < 2 * n_feat // world:
         cap *= 2
-    cfg = WideConfig(table_capacity=cap, inbox_cap=rows * z, ring=args.tau + 2)
+    cfg = WideConfig(table_capacity=cap, inbox_cap=rows * z, ring=args.tau + 2, pull_cap=0 if args.one_sided else rows * z)
     hb = wide_layout(cfg, world).total()
     fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb)
     plane = WidePlane(fab, cfg)
@@ -227,7 +227,10 @@ def bench_wide_step(args):
     def step(i):
         ids, y = pool[i % len(pool)]
         b = bufs[i % 2].localize(ids, y, plane.bounds, fixed_z=z, hash_seed=0, hash_bits=40)
-        plane.pull_gemm(b, ctx, P)
+        if cfg.pull_cap:
+            plane.pull_xgemm(b, ctx, P, step_no[0])
+        else:
+            plane.pull_gemm(b, ctx, P)
         plane.rowsum(b, P, N)
         plane.push(b, ctx, step_no[0])
         plane.apply(step_no[0])
@@ -252,7 +255,11 @@ def bench_wide_step(args):
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
         ev[0].record()
         b = bufs[i % 2].localize(ids, y, plane.bounds, fixed_z=z, hash_seed=0, hash_bits=40)
-        ev[1].record(); plane.pull_gemm(b, ctx, P)
+        ev[1].record()
+        if cfg.pull_cap:
+            plane.pull_xgemm(b, ctx, P, step_no[0])
+        else:
+            plane.pull_gemm(b, ctx, P)
         ev[2].record(); plane.rowsum(b, P, N)
         ev[3].record(); plane.push(b, ctx, step_no[0])
         ev[4].record(); plane.apply(step_no[0])
@@ -426,6 +433,7 @@ def main():
     s = sub.add_parser("wide-step"); s.add_argument("--rows", type=int, default=32768); s.add_argument("--z", type=int, default=40)
     s.add_argument("--log2-keys", type=int, default=25); s.add_argument("--n-ctx", type=int, default=64)
     s.add_argument("--iters", type=int, default=20); s.add_argument("--tau", type=int, default=8); s.add_argument("--pool", type=int, default=4)
+    s.add_argument("--one-sided", action="store_true", help="pull by remote probes instead of the exchange kernel")
     s = sub.add_parser("darlin"); s.add_argument("--rows", type=int, default=1250000); s.add_argument("--z", type=int, default=100)
     s.add_argument("--log2-keys", type=int, default=24); s.add_argument("--passes", type=int, default=3)
     s.add_argument("--tau", type=int, default=2)

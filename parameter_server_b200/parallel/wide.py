@@ -47,6 +47,16 @@ class _ApplyArgs(C.Structure):
                 ("applied", _vp), ("bar", _vp), ("done", _vp), ("status", _vp)]
 
 
+class _XArgs(C.Structure):
+    _fields_ = [("S", _i32), ("me", _i32), ("N", _i32), ("ts1", _u32), ("req_cap", _u32), ("wait_iters", _u32), ("phases", _u32),
+                ("keys", _vp), ("vals", _vp), ("mask", _u64), ("key_begin", _u64), ("slot_mult", _u64),
+                ("req_keys", _vp * MAX_SHARDS), ("req_hdr", _vp * MAX_SHARDS), ("req_ready", _vp * MAX_SHARDS),
+                ("my_resp_ready", _vp * MAX_SHARDS), ("my_resp_rows", _vp),
+                ("my_req_keys", _vp * MAX_SHARDS), ("my_req_hdr", _vp * MAX_SHARDS), ("my_req_ready", _vp * MAX_SHARDS),
+                ("resp_rows", _vp * MAX_SHARDS), ("resp_ready", _vp * MAX_SHARDS), ("alive", C.c_uint8 * MAX_SHARDS),
+                ("ukeys", _vp), ("n_unique", _vp), ("own_off", _vp), ("P", _vp), ("done", _vp), ("status", _vp)]
+
+
 def _declare():
     L = _lib.lib()
     if getattr(L, "_wide_declared", False):
@@ -54,11 +64,12 @@ def _declare():
     L.psb_wide_init.argtypes = [_vp, _vp, _vp, _u64, _vp]
     L.psb_wide_load.argtypes = [_vp, _vp, _u64, _u64, _u64, _vp, _vp, _u32, _vp, _vp]
     L.psb_wide_pull_gemm.argtypes = [_vp, _vp, _u32, _vp]
+    L.psb_wide_pull_xgemm.argtypes = [_vp, _vp, _u32, _vp]
     L.psb_wide_rowsum.argtypes = [_vp, _i32, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]
     L.psb_wide_push.argtypes = [_vp, _vp]
     L.psb_wide_apply.argtypes = [_vp, _vp]
     L.psb_wide_args_size.argtypes = [_i32]
-    for i, st in enumerate((_PullArgs, _PushArgs, _ApplyArgs)):
+    for i, st in enumerate((_PullArgs, _PushArgs, _ApplyArgs, _XArgs)):
         if L.psb_wide_args_size(i) != C.sizeof(st):
             raise RuntimeError(f"{st.__name__}: binding is {C.sizeof(st)} bytes, library expects {L.psb_wide_args_size(i)}")
     L._wide_declared = True
@@ -74,6 +85,7 @@ class WideConfig:
     beta: float = 1.0
     key_range: Range = field(default_factory=Range.all)
     ordered_slots: bool = True
+    pull_cap: int = 0                # > 0: exchange pull (keys to the owners, rows back, in bulk); unique keys per batch
 
 
 def wide_layout(cfg: WideConfig, world: int) -> HeapLayout:
@@ -85,6 +97,10 @@ def wide_layout(cfg: WideConfig, world: int) -> HeapLayout:
     lay.add("acc", cfg.table_capacity * WIDTH * 4)
     lay.add("inbox_keys", cfg.ring * world * cfg.inbox_cap * 8)
     lay.add("inbox_vals", cfg.ring * world * cfg.inbox_cap * WIDTH * 2)
+    if cfg.pull_cap:
+        lay.add("xctrl", 4096)                                    # flags and headers of the exchange pull
+        lay.add("req_keys", 2 * world * cfg.inbox_cap * 8)        # [parity][source][key]
+        lay.add("resp_rows", 2 * cfg.pull_cap * WIDTH * 2)        # [parity][unique key][64] bf16
     return lay
 
 
@@ -108,7 +124,7 @@ class WidePlane:
             self.slot_mult.append(m if m < (1 << 64) else 0)
         self.sync = torch.zeros(16, dtype=torch.int32, device=dev)
         # scratch of the push for keys with very long segments (zeroed once, left zeroed by the kernel)
-        self.long_cap = max(64, cfg.inbox_cap // 1024 + 1)
+        self.long_cap = max(64, cfg.inbox_cap // 256 + 1)
         self.long_list = torch.zeros(self.long_cap, dtype=torch.int32, device=dev)
         self.long_acc = torch.zeros(self.long_cap * WIDTH, dtype=torch.float32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -140,6 +156,44 @@ class WidePlane:
         check(self.L.psb_wide_load(self._p("keys"), self._p("vals"), self.cfg.table_capacity - 1, self.bounds_host[self.rank],
                                    self.slot_mult[self.rank], ptr(k), ptr(v), k.numel(), ptr(self.status), stream_ptr()), "wide_load")
         torch.cuda.current_stream().synchronize()
+
+    def _xflag(self, rank, kind, par, peer):
+        """Exchange flag word: kind 0 = request ready, 1 = response ready."""
+        return self._p("xctrl", rank, 4 * ((kind * 2 + par) * self.S + peer))
+
+    def _xhdr(self, rank, par, peer):
+        return self._p("xctrl", rank, 4 * (4 * self.S + (par * self.S + peer) * 2))
+
+    def pull_xgemm(self, b, ctx: torch.Tensor, P: torch.Tensor, ts: int, *, phases: int = 7, wait_iters: int = 0,
+                   stream=None):
+        """Exchange form of :meth:`pull_gemm` for round ``ts`` (every rank calls it every round):
+        keys to the owners in bulk, value rows back in bulk, the product on the local copy."""
+        cfg = self.cfg
+        assert cfg.pull_cap >= b.max_nnz and 4 * (4 * self.S + 4 * self.S) <= 4096
+        assert ctx.dtype == torch.bfloat16 and ctx.is_contiguous() and ctx.shape[1] == WIDTH
+        par = ts & 1
+        a = _XArgs()
+        a.S, a.me, a.N, a.ts1, a.req_cap, a.wait_iters, a.phases = self.S, self.rank, ctx.shape[0], ts + 1, cfg.inbox_cap, wait_iters, phases
+        a.keys, a.vals = self._p("keys"), self._p("vals")
+        a.mask, a.key_begin, a.slot_mult = cfg.table_capacity - 1, self.bounds_host[self.rank], self.slot_mult[self.rank]
+        rb = cfg.inbox_cap * 8
+        for s in range(self.S):
+            a.req_keys[s] = self._p("req_keys", s, (par * self.S + self.rank) * rb)
+            a.req_hdr[s], a.req_ready[s] = self._xhdr(s, par, self.rank), self._xflag(s, 0, par, self.rank)
+            a.my_resp_ready[s] = self._xflag(self.rank, 1, par, s)
+            a.my_req_keys[s] = self._p("req_keys", self.rank, (par * self.S + s) * rb)
+            a.my_req_hdr[s], a.my_req_ready[s] = self._xhdr(self.rank, par, s), self._xflag(self.rank, 0, par, s)
+            a.resp_rows[s] = self._p("resp_rows", s, par * cfg.pull_cap * WIDTH * 2)
+            a.resp_ready[s] = self._xflag(s, 1, par, self.rank)
+            a.alive[s] = 1
+        a.my_resp_rows = self._p("resp_rows", self.rank, par * cfg.pull_cap * WIDTH * 2)
+        a.ukeys, a.n_unique, a.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
+        a.P, a.done, a.status = ptr(P), self.sync.data_ptr() + 48, ptr(self.status)
+        check(self.L.psb_wide_pull_xgemm(C.byref(a), ptr(ctx), b.max_nnz, stream_ptr(stream)), "wide_pull_xgemm")
+
+    def pulled_rows(self, ts: int, n: int) -> torch.Tensor:
+        """The value rows this worker received in the exchange of round ``ts`` ([n, 64] bf16)."""
+        return self.fabric.view(self.lay["resp_rows"] + (ts & 1) * self.cfg.pull_cap * WIDTH * 2, (n, WIDTH), torch.bfloat16)
 
     def pull_gemm(self, b, ctx: torch.Tensor, P: torch.Tensor, v_local: Optional[torch.Tensor] = None, stream=None):
         """``P[u, n] = <value row of unique key u, ctx[n]>`` for the batch ``b``.

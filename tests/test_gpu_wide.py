@@ -6,13 +6,13 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _setup(S, N, rows=300, z=12, n_feat=2500, seed=0):
+def _setup(S, N, rows=300, z=12, n_feat=2500, seed=0, pull_cap=0):
     from parameter_server_b200.ops.localize import LocalBatch
     from parameter_server_b200.parallel.fabric import Fabric
     from parameter_server_b200.parallel.wide import WideConfig, WidePlane, wide_layout
     from parameter_server_b200.utils.oracle import hash_id_to_key
     rng = np.random.default_rng(seed)
-    cfg = WideConfig(table_capacity=1 << 13, inbox_cap=rows * z, ring=2, alpha=0.1, beta=1.0)
+    cfg = WideConfig(table_capacity=1 << 13, inbox_cap=rows * z, ring=2, alpha=0.1, beta=1.0, pull_cap=pull_cap)
     fabs = Fabric.emulated(S, wide_layout(cfg, S).total())
     planes = [WidePlane(f, cfg) for f in fabs]
     all_ids = np.arange(n_feat)
@@ -52,10 +52,10 @@ def test_wide_pull_gemm_matches_fp32_matmul(cuda_lib, S, N):
 @pytest.mark.parametrize("n_rows", [300, 900])
 def test_wide_training_step_matches_reference(cuda_lib, n_rows):
     """With 900 rows the most frequent key owns about 3,000 nonzeros: its gradient is
-    reduced by several warps (segments above 1,024 nonzeros are split into chunks)."""
+    reduced by several warps (segments above 256 nonzeros are split into chunks)."""
     S, N = 2, 64
     planes, b, ctx, table, known, all_keys, ids, y, rows, z = _setup(S, N, rows=n_rows, seed=4)
-    assert int((b.seg_off[1:int(b.n_unique.item()) + 1] - b.seg_off[:int(b.n_unique.item())]).max().item()) > (1024 if n_rows == 900 else 0)
+    assert int((b.seg_off[1:int(b.n_unique.item()) + 1] - b.seg_off[:int(b.n_unique.item())]).max().item()) > (256 if n_rows == 900 else 0)
     U = int(b.n_unique.item())
     w = planes[0]
     P = torch.zeros(b.max_nnz, N, device="cuda")
@@ -99,3 +99,33 @@ def test_wide_training_step_matches_reference(cuda_lib, n_rows):
         got[torch.from_numpy(sel)] = p.lookup(uk[sel])
     diff = (got.float() - Wref.float()).abs()
     assert float(diff.max()) < 0.02 and float((diff > 0.004).float().mean()) < 0.02
+
+
+@pytest.mark.parametrize("S,N", [(1, 64), (2, 128), (3, 64)])
+def test_wide_exchange_pull_matches_fp32_matmul(cuda_lib, S, N):
+    """Exchange form of the pull (keys to the owners, rows back in bulk, tcgen05 product on
+    the local copy), ranks emulated on one GPU: the three roles run as separate launches."""
+    from parameter_server_b200.ops.localize import LocalBatch
+    rows, z = 300, 12
+    planes, b, ctx, table, known, all_keys, ids, y, rows, z = _setup(S, N, rows=rows, z=z, seed=5, pull_cap=rows * z)
+    U = int(b.n_unique.item())
+    batches = [b]
+    for _ in range(1, S):
+        e = LocalBatch(4, rows * z, S, "cuda")
+        e.n_unique.zero_(); e.own_off.zero_(); e.seg_off.zero_()
+        batches.append(e)
+    Ps = [torch.zeros(rows * z, N, device="cuda") for _ in range(S)]
+    for rnd in range(2):                                   # two rounds: both parities of the buffers
+        for phase in (1, 2, 4):
+            for p, bb, P in zip(planes, batches, Ps):
+                p.pull_xgemm(bb, ctx, P, rnd, phases=phase, wait_iters=1 << 12)
+        torch.cuda.synchronize()
+        for p in planes:
+            p.check_status()
+        idx = {int(k): i for i, k in enumerate(all_keys.tolist())}
+        uk = b.ukeys[:U].cpu().numpy().view(np.uint64)
+        Vref = torch.stack([table[idx[int(k)]].float() if known[idx[int(k)]] else torch.zeros(64) for k in uk.tolist()])
+        assert torch.equal(planes[0].pulled_rows(rnd, U).cpu().float(), Vref)
+        Pref = Vref @ ctx.cpu().float().T
+        assert torch.allclose(Ps[0][:U].cpu(), Pref, rtol=2e-3, atol=2e-3)
+        Ps[0].zero_()
