@@ -459,8 +459,8 @@ struct WidePushArgs {
   uint32_t* done;
   uint32_t* status;
   uint32_t* bar;                               // 2 words (grid barrier), zero on first use
-  uint32_t* n_long;                            // 1 word, zero on entry, left zero
-  uint32_t* long_list;                         // long_cap words: unique-key indices of long segments
+  unsigned long long* n_long;                  // {count (low word), chunks (high word)}, zero on entry, left zero
+  uint4* long_list;                            // long_cap entries {key index, first chunk, first element, end element}
   float* long_acc;                             // long_cap x 64 floats, zero on entry, left zero
   uint32_t long_cap;
 };
@@ -511,13 +511,18 @@ __global__ void __launch_bounds__(256) k_wide_push(const WidePushArgs p) {
     reinterpret_cast<__nv_bfloat162*>(p.inbox_vals[s] + (size_t)j * kWide)[lane] = __floats2bfloat162_rn(g0, g1);
     if (lane == 0) p.inbox_keys[s][j] = p.ukeys[u];
   };
-  // ---- phase 1: one warp per key; long segments are only listed
+  // ---- phase 1: one warp per key; long segments are only listed, with the number of their
+  // first chunk (one 64-bit atomic hands out list position and chunk numbers together, so the
+  // list is sorted by first chunk)
   for (u32 u = gwarp; u < U; u += nwarps) {
     const u32 i0 = p.seg_off[u], i1 = p.seg_off[u + 1];
     if (i1 - i0 > kWideLongSeg && p.long_cap) {
       if (lane == 0) {
-        u32 k = atomicAdd(p.n_long, 1u);
-        if (k < p.long_cap) p.long_list[k] = u; else set_status(p.status, kInboxOverflow);
+        const u32 nch = (i1 - i0 + kWideLongSeg - 1) / kWideLongSeg;
+        const unsigned long long old = atomicAdd(p.n_long, 1ull | ((unsigned long long)nch << 32));
+        const u32 k = (u32)old;
+        if (k < p.long_cap) p.long_list[k] = make_uint4(u, (u32)(old >> 32), i0, i1);
+        else set_status(p.status, kInboxOverflow);
       }
       continue;
     }
@@ -527,21 +532,25 @@ __global__ void __launch_bounds__(256) k_wide_push(const WidePushArgs p) {
   }
   if (p.long_cap) {
     if (!grid_barrier(p.bar, p.status)) return;
-    // ---- phase 2: the chunks of all long segments, spread over all warps
-    const u32 n_long = min(*((volatile u32*)p.n_long), p.long_cap);
-    u32 first = 0;   // index of the key's first chunk in the global chunk numbering
-    for (u32 k = 0; k < n_long; ++k) {
-      const u32 u = p.long_list[k];
-      const u32 i0 = p.seg_off[u], i1 = p.seg_off[u + 1];
-      const u32 nch = (i1 - i0 + kWideLongSeg - 1) / kWideLongSeg;
-      // chunk c of this key is taken by warp (first + c) % nwarps
-      for (u32 c = (gwarp + nwarps - first % nwarps) % nwarps; c < nch; c += nwarps) {
-        float g0 = 0.f, g1 = 0.f;
-        wide_seg_accumulate(p, s_ctx, i0 + c * kWideLongSeg, min(i1, i0 + (c + 1) * kWideLongSeg), lane, g0, g1);
-        atomicAdd(&p.long_acc[(size_t)k * kWide + 2 * lane], g0);
-        atomicAdd(&p.long_acc[(size_t)k * kWide + 2 * lane + 1], g1);
+    // ---- phase 2: all chunks of all long segments, one per warp and trip
+    const unsigned long long tot = *((volatile unsigned long long*)p.n_long);
+    const u32 n_long = min((u32)tot, p.long_cap);
+    const u32 n_chunks = n_long ? (u32)(tot >> 32) : 0u;
+    for (u32 c = gwarp; c < n_chunks; c += nwarps) {
+      // the entry with the largest first chunk <= c
+      u32 lo = 0, hi = n_long;
+      while (hi - lo > 1) {
+        const u32 mid = (lo + hi) >> 1;
+        if (__ldcg(&p.long_list[mid].y) <= c) lo = mid; else hi = mid;
       }
-      first += nch;
+      const uint4 e = __ldcg(&p.long_list[lo]);
+      const u32 cc = c - e.y;
+      const u32 b0 = e.z + cc * kWideLongSeg;
+      if (b0 >= e.w) continue;                       // (only if the list overflowed)
+      float g0 = 0.f, g1 = 0.f;
+      wide_seg_accumulate(p, s_ctx, b0, min(e.w, b0 + kWideLongSeg), lane, g0, g1);
+      atomicAdd(&p.long_acc[(size_t)lo * kWide + 2 * lane], g0);
+      atomicAdd(&p.long_acc[(size_t)lo * kWide + 2 * lane + 1], g1);
     }
     if (!grid_barrier(p.bar, p.status)) return;
     // ---- phase 3: emit the long keys and leave the scratch zeroed
@@ -549,14 +558,14 @@ __global__ void __launch_bounds__(256) k_wide_push(const WidePushArgs p) {
       float2* a = reinterpret_cast<float2*>(p.long_acc + (size_t)k * kWide) + lane;
       float2 g = __ldcg(a);
       *a = make_float2(0.f, 0.f);
-      emit(p.long_list[k], g.x, g.y);
+      emit(__ldcg(&p.long_list[k].x), g.x, g.y);
     }
   }
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) s_last = atomicAdd(p.done, 1u) + 1 == gridDim.x;
   __syncthreads();
-  if (s_last && threadIdx.x == 0 && p.n_long) *p.n_long = 0;
+  if (s_last && threadIdx.x == 0 && p.n_long) *p.n_long = 0ull;
   if (s_last && threadIdx.x < p.S) {
     int s = threadIdx.x;
     __threadfence_system();
@@ -741,6 +750,9 @@ extern "C" int psb_wide_pull_xgemm(const void* args, const void* ctx, uint32_t m
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute((const void*)k_wide_pull_xgemm, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    // several CTAs per SM must be resident at once: ask for the large shared-memory carve-out
+    cudaFuncSetAttribute((const void*)k_wide_pull_xgemm, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
     attr_set = true;
   }
   // all CTAs must be co-resident: three per SM (each holds N <= 128 of the SM's 512 TMEM columns)

@@ -125,7 +125,7 @@ class WidePlane:
         self.sync = torch.zeros(16, dtype=torch.int32, device=dev)
         # scratch of the push for keys with very long segments (zeroed once, left zeroed by the kernel)
         self.long_cap = max(64, cfg.inbox_cap // 256 + 1)
-        self.long_list = torch.zeros(self.long_cap, dtype=torch.int32, device=dev)
+        self.long_list = torch.zeros(self.long_cap * 4, dtype=torch.int32, device=dev)   # {key, first chunk, begin, end}
         self.long_acc = torch.zeros(self.long_cap * WIDTH, dtype=torch.float32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.stats = torch.zeros(4, dtype=torch.float64, device=dev)
