@@ -189,17 +189,20 @@ void Manager::AddNode(const Node& node) {
     Lock l(nodes_mu_);
     is_new = nodes_.find(node.id) == nodes_.end();
     nodes_[node.id] = node;
-    if (is_new) {
-      if (node.role == Node::WORKER) ++num_workers_;
-      if (node.role == Node::SERVER) ++num_servers_;
-      ++num_active_nodes_;
-    }
   }
   if (node.id == my_node().id) van_.UpdateMyNode(node);
   van_.Connect(node);
   {
     Lock l(customer_mu_);
     for (auto& c : customers_) c.second->executor()->AddNode(node);
+  }
+  if (is_new) {
+    // Counted only now: WaitServersReady / WaitWorkersReady release an app that then submits to
+    // the server or worker group, and the node must already be a member of every customer's groups.
+    Lock l(nodes_mu_);
+    if (node.role == Node::WORKER) ++num_workers_;
+    if (node.role == Node::SERVER) ++num_servers_;
+    ++num_active_nodes_;
   }
   if (IsScheduler() && node.id != my_node().id) {
     // the newcomer learns every node; everybody else learns the newcomer
