@@ -160,7 +160,7 @@ def test_node_processes_clean_under_sanitizers(data, tmp_path, kinds):
     for name, text in confs.items():
         conf = tmp_path / f"{name}.conf"
         conf.write_text(text)
-        res = launch_local_processes(2, 2, [exe, "-app_file", str(conf)], timeout=600, env=env)
+        res = launch_local_processes(2, 2, [exe, "-app_file", str(conf)], timeout=120, env=env)
         for nid, r in res.items():
             out = r.stdout or ""
             assert r.returncode == 0, (name, nid, out[-3000:])
