@@ -130,9 +130,14 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_grad(const PsbDarlinGrad p
     p.stage[c] = 0.f;                      // leave the staging area clean for the next block
     p.stage[p.block_cap + c] = 0.f;
   }
-  __threadfence_system();
+  // One system fence per CTA: the block barrier orders every thread's peer stores before
+  // thread 0's fence (fences are cumulative), and that fence precedes the arrival count.
+  // (A fence in every thread dominated these small kernels: ncu showed membar as the top stall.)
   __syncthreads();
-  if (threadIdx.x == 0) s_last = atomicAdd(p.done, 1u) + 1 == gridDim.x;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    s_last = atomicAdd(p.done, 1u) + 1 == gridDim.x;
+  }
   __syncthreads();
   if (s_last && threadIdx.x < p.S) {
     __threadfence_system();
@@ -200,10 +205,10 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_update(const PsbDarlinUpda
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) vio_max = fmaxf(vio_max, __shfl_xor_sync(0xffffffffu, vio_max, o));
   if ((threadIdx.x & 31) == 0 && vio_max > 0.f) atomicMax((int*)&s_vio, __float_as_int(vio_max));
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
     if (s_vio > 0.f && p.violation) atomicMax((int*)p.violation, __float_as_int(s_vio));
+    __threadfence_system();   // one per CTA, after the block barrier (see k_darlin_grad)
     s_last = atomicAdd(p.done, 1u) + 1 == gridDim.x;
   }
   __syncthreads();
