@@ -166,3 +166,17 @@ def test_node_processes_clean_under_sanitizers(data, tmp_path, kinds):
             assert r.returncode == 0, (name, nid, out[-3000:])
             assert "Sanitizer" not in out and "runtime error" not in out, (name, nid, out[-3000:])
     assert len(_read_model(str(tmp_path / "model_S*"))) > 10
+
+
+def test_darlin_processes_start_reliably(data, tmp_path):
+    """Twenty start-ups of 1 scheduler + 2 servers + 2 workers as OS processes: every node
+    must be a member of the groups before the scheduler's first group task goes out (a node
+    used to be counted as ready too early, and about 3 % of the start-ups hung)."""
+    from parameter_server_b200 import _build
+    exe = str(_build.PKG / "bin" / "psb_linear")
+    conf = tmp_path / "darlin.conf"
+    conf.write_text(CONF_DARLIN.format(train=data["train"], out=str(tmp_path), tau=1, tail=0))
+    for i in range(20):
+        res = launch_local_processes(2, 2, [exe, "-app_file", str(conf)], timeout=30)
+        for nid, r in res.items():
+            assert r.returncode == 0, (i, nid, (r.stdout or "")[-1500:])
