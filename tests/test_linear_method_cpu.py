@@ -180,3 +180,43 @@ def test_darlin_processes_start_reliably(data, tmp_path):
         res = launch_local_processes(2, 2, [exe, "-app_file", str(conf)], timeout=30)
         for nid, r in res.items():
             assert r.returncode == 0, (i, nid, (r.stdout or "")[-1500:])
+
+
+def test_job_control_start_ls_kill_add_stop(data, tmp_path):
+    """The job-control commands (the reference's script/ps.sh): start a job, list it, kill a
+    worker in mid-run (the scheduler re-queues its workloads and the job still finishes),
+    and stop a second job by hand."""
+    import time
+    from parameter_server_b200 import _build
+    from parameter_server_b200.system.launch import Job
+    exe = str(_build.PKG / "bin" / "psb_linear")
+    conf = tmp_path / "sgd.conf"
+    conf.write_text(CONF_SGD.format(train=data["train"], out=str(tmp_path), algo="FTRL", filters="")
+                    .replace("num_data_pass: 3", "num_data_pass: 40"))
+    job = Job(str(tmp_path / "state.json"))
+    nodes = job.start([exe, "-app_file", str(conf)], num_servers=2, num_workers=2, log_dir=str(tmp_path / "logs"))
+    assert [n["id"] for n in nodes] == ["H", "S0", "S1", "W0", "W1"]
+    # a second Job object (another invocation of the tool) finds the job through the state file
+    seen = Job(str(tmp_path / "state.json")).ls()
+    assert len(seen) == 5 and all(n["alive"] for n in seen)
+    time.sleep(0.3)
+    assert job.kill("W1")                       # a worker dies in mid-run
+    assert job.wait(120), [open(n["log"]).read()[-800:] for n in job.ls() if n["alive"]]
+    sched_log = open(nodes[0]["log"]).read()
+    assert "examples" in sched_log              # the scheduler printed its progress table
+    assert len(_read_model(str(tmp_path / "model_S*"))) > 10
+    job.stop()
+    assert not os.path.exists(str(tmp_path / "state.json"))
+    # stop: a long job is ended by hand
+    conf.write_text(conf.read_text().replace("num_data_pass: 40", "num_data_pass: 100000"))
+    job = Job(str(tmp_path / "state.json"))
+    job.start([exe, "-app_file", str(conf)], num_servers=1, num_workers=1, log_dir=str(tmp_path / "logs2"))
+    time.sleep(0.5)
+    assert all(n["alive"] for n in job.ls())
+    # add: a worker joins the running job through the scheduler's registration path
+    assert [n["id"] for n in job.add(workers=1)] == ["W1"]
+    time.sleep(0.7)
+    assert [n["id"] for n in job.ls() if n["alive"]] == ["H", "S0", "W0", "W1"]
+    assert "error" not in open(job.ls()[-1]["log"]).read().lower()
+    job.stop()
+    assert job.ls() == []
