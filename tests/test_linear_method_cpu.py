@@ -220,3 +220,22 @@ def test_job_control_start_ls_kill_add_stop(data, tmp_path):
     assert "error" not in open(job.ls()[-1]["log"]).read().lower()
     job.stop()
     assert job.ls() == []
+
+
+def test_job_control_command_line(data, tmp_path, capsys):
+    """The same commands through the module's command line (start -- bin args, ls, wait, stop)."""
+    from parameter_server_b200 import _build
+    from parameter_server_b200.system import launch
+    exe = str(_build.PKG / "bin" / "psb_linear")
+    conf = tmp_path / "sgd.conf"
+    conf.write_text(CONF_SGD.format(train=data["train"], out=str(tmp_path), algo="FTRL", filters=""))
+    st = str(tmp_path / "state.json")
+    assert launch.main(["--state", st, "start", "-ns", "1", "-nw", "2", "-log_dir", str(tmp_path / "logs"), "--",
+                        exe, "-app_file", str(conf)]) == 0
+    assert launch.main(["--state", st, "ls"]) == 0
+    out = capsys.readouterr().out
+    assert out.count("SERVER") == 2 and out.count("WORKER") == 4 and "SCHEDULER" in out   # start + ls listings
+    assert launch.main(["--state", st, "wait", "-timeout", "120"]) == 0
+    assert launch.main(["--state", st, "stop"]) == 0
+    assert not os.path.exists(st)
+    assert len(_read_model(str(tmp_path / "model_S*"))) > 10
