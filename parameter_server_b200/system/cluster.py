@@ -131,12 +131,21 @@ def launch_local_processes(num_servers: int, num_workers: int, argv: List[str], 
         procs[nid] = subprocess.Popen(cmd, env={**os.environ, **(env or {})},
                                       stdout=subprocess.PIPE if capture else None,
                                       stderr=subprocess.STDOUT if capture else None, text=True)
+    # Every node's pipe is drained by its own thread: a node that prints more than a pipe holds
+    # must not block while another node is being waited for. `timeout` bounds the whole job.
     out = {}
-    for nid, p in procs.items():
+
+    def drain(nid, p):
         try:
             so, _ = p.communicate(timeout=timeout)
         except subprocess.TimeoutExpired:
             p.kill()
             so, _ = p.communicate()
         out[nid] = subprocess.CompletedProcess(p.args, p.returncode, so, None)
-    return out
+
+    ts = [threading.Thread(target=drain, args=(nid, p), daemon=True) for nid, p in procs.items()]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    return {nid: out[nid] for nid in procs}
