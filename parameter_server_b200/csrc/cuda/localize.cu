@@ -20,6 +20,11 @@ static constexpr int kLocThreads = 256;
 static constexpr int kLocItems = 16;
 static constexpr int kLocTile = kLocThreads * kLocItems;  // 4096 = 128 flag words
 
+// Launch gate: with a non-null gate word the kernel runs only when (*gate != 0) == want.
+__device__ __forceinline__ bool gate_skips(const u32* gate, int want) {
+  return gate != nullptr && ((*gate != 0) != (want != 0));
+}
+
 // Loads the warp's 16 x 32 consecutive keys starting at `base` (all requested
 // before the first is used) and returns, per item, the ballot of segment heads.
 // kmask selects the key bits (all ones, or without the packed position bits).
@@ -45,8 +50,10 @@ __device__ __forceinline__ void warp_heads(const u64* __restrict__ keys, u32 n, 
 __global__ void __launch_bounds__(kLocThreads) k_uniq_count(const u64* __restrict__ keys_a,
                                                             const u64* __restrict__ keys_b,
                                                             const u32* __restrict__ where, u32 n,
-                                                            u32* __restrict__ tile_heads, u64 kmask) {
+                                                            u32* __restrict__ tile_heads, u64 kmask,
+                                                            const u32* __restrict__ gate) {
   __shared__ u32 s_w[8];
+  if (gate_skips(gate, 1)) return;
   const u64* __restrict__ keys = (where && *where) ? keys_b : keys_a;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const u32 base = blockIdx.x * (u32)kLocTile + w * (32 * kLocItems);
@@ -67,9 +74,10 @@ __global__ void __launch_bounds__(kLocThreads) k_uniq_count(const u64* __restric
 
 // One block: exclusive scan of tile_heads in place; writes U.
 __global__ void __launch_bounds__(1024) k_uniq_scan(u32* __restrict__ tile_heads, u32 ntiles,
-                                                    u32* __restrict__ n_unique) {
+                                                    u32* __restrict__ n_unique, const u32* __restrict__ gate) {
   __shared__ u32 s_warp[32];
   __shared__ u32 s_carry;
+  if (gate_skips(gate, 1)) return;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   if (threadIdx.x == 0) s_carry = 0;
   __syncthreads();
@@ -118,8 +126,10 @@ __global__ void __launch_bounds__(kLocThreads) k_uniq_emit(
     const u32* __restrict__ tile_base,
     const u32* __restrict__ row_ptr, u32 n_rows, u32 fixed_z, const float* __restrict__ vals,
     u64* __restrict__ ukeys, u32* __restrict__ seg_off, u32* __restrict__ csr_col,
-    float* __restrict__ csc_val, u32* __restrict__ flagbits, u32* __restrict__ wordbase, u64 kmask) {
+    float* __restrict__ csc_val, u32* __restrict__ flagbits, u32* __restrict__ wordbase, u64 kmask,
+    const u32* __restrict__ gate) {
   __shared__ u32 s_w[8];
+  if (gate_skips(gate, 1)) return;
   const bool in_b = where && *where;
   const u64* __restrict__ keys = in_b ? keys_b : keys_a;
   const u32* pos = in_b ? pos_b : pos_a;
@@ -175,7 +185,9 @@ __global__ void __launch_bounds__(kLocThreads) k_uniq_emit(
 // Also closes the CSC offsets with seg_off[U] = n.
 __global__ void k_owner_offsets(const u64* __restrict__ ukeys, const u32* __restrict__ n_unique,
                                 const u64* __restrict__ bounds, int S, u32 n,
-                                u32* __restrict__ seg_off, u32* __restrict__ own_off) {
+                                u32* __restrict__ seg_off, u32* __restrict__ own_off,
+                                const u32* __restrict__ gate, int want) {
+  if (gate_skips(gate, want)) return;
   const u32 U = *n_unique;
   int s = threadIdx.x;
   if (s == 0 && seg_off) seg_off[U] = n;
@@ -199,7 +211,7 @@ using namespace psb;
 extern "C" int psb_owner_offsets(const psb_u64* ukeys, const uint32_t* n_unique, const psb_u64* bounds, int S,
                                  uint32_t* own_off, cudaStream_t stream) {
   if (S < 1 || S > 64) return -(int)cudaErrorInvalidValue;
-  k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, 0, nullptr, own_off);
+  k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, 0, nullptr, own_off, nullptr, 0);
   return -(int)cudaGetLastError();
 }
 
@@ -210,13 +222,14 @@ extern "C" size_t psb_localize_scratch_bytes(uint32_t n) {
 
 // The sorted pairs are in (keys_a, pos_a) when *where == 0 (or where is null) and
 // in (keys_b, pos_b) otherwise. csc_row may alias the selected pos buffer.
-extern "C" int psb_localize2(const psb_u64* keys_a, const psb_u64* keys_b, const uint32_t* pos_a,
-                             const uint32_t* pos_b, const uint32_t* where, uint32_t* csc_row, uint32_t n,
-                             const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z,
-                             const float* vals, const psb_u64* bounds, int S, psb_u64* ukeys,
-                             uint32_t* seg_off, uint32_t* csr_col, float* csc_val,
-                             uint32_t* flagbits, uint32_t* wordbase, uint32_t* n_unique,
-                             uint32_t* own_off, void* scratch, int pack_pos_bits, cudaStream_t stream) {
+static int localize2_impl(const psb_u64* keys_a, const psb_u64* keys_b, const uint32_t* pos_a,
+                          const uint32_t* pos_b, const uint32_t* where, uint32_t* csc_row, uint32_t n,
+                          const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z,
+                          const float* vals, const psb_u64* bounds, int S, psb_u64* ukeys,
+                          uint32_t* seg_off, uint32_t* csr_col, float* csc_val,
+                          uint32_t* flagbits, uint32_t* wordbase, uint32_t* n_unique,
+                          uint32_t* own_off, void* scratch, int pack_pos_bits, const uint32_t* gate,
+                          cudaStream_t stream) {
   if (S < 1 || S > 64) return -(int)cudaErrorInvalidValue;
   if (row_ptr == nullptr && fixed_z == 0) return -(int)cudaErrorInvalidValue;
   if (pack_pos_bits < 0 || pack_pos_bits > 32) return -(int)cudaErrorInvalidValue;
@@ -230,12 +243,49 @@ extern "C" int psb_localize2(const psb_u64* keys_a, const psb_u64* keys_b, const
     cudaMemsetAsync(seg_off, 0, sizeof(u32), stream);
     return -(int)cudaGetLastError();
   }
-  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)keys_a, (const u64*)keys_b, where, n, tile_heads, kmask);
-  k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique);
+  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)keys_a, (const u64*)keys_b, where, n, tile_heads, kmask, gate);
+  k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique, gate);
   k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>((const u64*)keys_a, (const u64*)keys_b, pos_a, pos_b, where, csc_row,
                                                   n, tile_heads, row_ptr, n_rows, fixed_z, vals, (u64*)ukeys, seg_off,
-                                                  csr_col, csc_val, flagbits, wordbase, kmask);
-  k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off, own_off);
+                                                  csr_col, csc_val, flagbits, wordbase, kmask, gate);
+  k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off, own_off, gate, 1);
+  return -(int)cudaGetLastError();
+}
+
+extern "C" int psb_localize2(const psb_u64* keys_a, const psb_u64* keys_b, const uint32_t* pos_a,
+                             const uint32_t* pos_b, const uint32_t* where, uint32_t* csc_row, uint32_t n,
+                             const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z,
+                             const float* vals, const psb_u64* bounds, int S, psb_u64* ukeys,
+                             uint32_t* seg_off, uint32_t* csr_col, float* csc_val,
+                             uint32_t* flagbits, uint32_t* wordbase, uint32_t* n_unique,
+                             uint32_t* own_off, void* scratch, int pack_pos_bits, cudaStream_t stream) {
+  return localize2_impl(keys_a, keys_b, pos_a, pos_b, where, csc_row, n, row_ptr, n_rows, fixed_z, vals, bounds, S,
+                        ukeys, seg_off, csr_col, csc_val, flagbits, wordbase, n_unique, own_off, scratch,
+                        pack_pos_bits, nullptr, stream);
+}
+
+// Same, but every kernel of the call returns at once unless the device word *gate is non-zero.
+extern "C" int psb_localize2_gated(const psb_u64* keys_a, const psb_u64* keys_b, const uint32_t* pos_a,
+                                   const uint32_t* pos_b, const uint32_t* where, uint32_t* csc_row, uint32_t n,
+                                   const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z,
+                                   const float* vals, const psb_u64* bounds, int S, psb_u64* ukeys,
+                                   uint32_t* seg_off, uint32_t* csr_col, float* csc_val,
+                                   uint32_t* flagbits, uint32_t* wordbase, uint32_t* n_unique,
+                                   uint32_t* own_off, void* scratch, int pack_pos_bits, const uint32_t* gate,
+                                   cudaStream_t stream) {
+  return localize2_impl(keys_a, keys_b, pos_a, pos_b, where, csc_row, n, row_ptr, n_rows, fixed_z, vals, bounds, S,
+                        ukeys, seg_off, csr_col, csc_val, flagbits, wordbase, n_unique, own_off, scratch,
+                        pack_pos_bits, gate, stream);
+}
+
+// Owner offsets plus the closing CSC offset seg_off[U] = n; runs only while *skip_when_set is zero
+// (the bucket-based localisation's last step).
+extern "C" int psb_owner_offsets_n(const psb_u64* ukeys, const uint32_t* n_unique, const psb_u64* bounds, int S,
+                                   uint32_t n, uint32_t* seg_off, uint32_t* own_off,
+                                   const uint32_t* skip_when_set, cudaStream_t stream) {
+  if (S < 1 || S > 64) return -(int)cudaErrorInvalidValue;
+  k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off, own_off,
+                                        skip_when_set, 0);
   return -(int)cudaGetLastError();
 }
 
@@ -256,12 +306,12 @@ extern "C" int psb_localize(const psb_u64* sorted_keys, uint32_t* sorted_pos, ui
     cudaMemsetAsync(seg_off, 0, sizeof(u32), stream);
     return -(int)cudaGetLastError();
   }
-  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, nullptr, n, tile_heads, ~0ull);
-  k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique);
+  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, nullptr, n, tile_heads, ~0ull, nullptr);
+  k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique, nullptr);
   k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, sorted_pos, nullptr, nullptr,
                                                   sorted_pos, n, tile_heads, row_ptr, n_rows, fixed_z, vals,
-                                                  (u64*)ukeys, seg_off, csr_col, csc_val, flagbits, wordbase, ~0ull);
-  k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off, own_off);
+                                                  (u64*)ukeys, seg_off, csr_col, csc_val, flagbits, wordbase, ~0ull, nullptr);
+  k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off, own_off, nullptr, 0);
   return -(int)cudaGetLastError();
 }
 
@@ -321,12 +371,12 @@ extern "C" int psb_localize_static(const psb_u64* sorted_keys, uint32_t* sorted_
   const u32 ntiles = (n + kLocTile - 1) / kLocTile;
   // every tile_heads word that the scan and the emit kernel read is written by
   // k_uniq_count first, so the array needs no clearing between calls
-  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, nullptr, n, tile_heads, ~0ull);
-  k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique);
+  k_uniq_count<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, nullptr, n, tile_heads, ~0ull, nullptr);
+  k_uniq_scan<<<1, 1024, 0, stream>>>(tile_heads, ntiles, n_unique, nullptr);
   k_uniq_emit<<<ntiles, kLocThreads, 0, stream>>>((const u64*)sorted_keys, nullptr, sorted_pos, nullptr, nullptr,
                                                   sorted_pos, n, tile_heads, row_ptr, n_rows, fixed_z, vals,
-                                                  (u64*)ukeys, seg_off, csr_col, csc_val, flagbits, wordbase, ~0ull);
+                                                  (u64*)ukeys, seg_off, csr_col, csc_val, flagbits, wordbase, ~0ull, nullptr);
   k_owner_offsets<<<1, 96, 0, stream>>>((const u64*)ukeys, n_unique, (const u64*)bounds, S, n, seg_off,
-                                        own_off);
+                                        own_off, nullptr, 0);
   return -(int)cudaGetLastError();
 }

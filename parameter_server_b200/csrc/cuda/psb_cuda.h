@@ -28,6 +28,27 @@ int psb_localize2(const psb_u64* keys_a, const psb_u64* keys_b, const uint32_t* 
                   uint32_t* n_unique, uint32_t* own_off, void* scratch, int pack_pos_bits, cudaStream_t stream);
 int psb_owner_offsets(const psb_u64* ukeys, const uint32_t* n_unique, const psb_u64* bounds, int S,
                       uint32_t* own_off, cudaStream_t stream);
+// Gated forms: every kernel of the call returns at once unless the device word *gate is non-zero.
+int psb_sort_pairs_gated(const void* in, int in_kind, psb_u64 seed, psb_u64* keys_a, uint32_t* vals_a,
+                         int vals_given, psb_u64* keys_b, uint32_t* vals_b, uint32_t n, int begin_bit,
+                         int end_bit, void* scratch, uint32_t* status, uint32_t* where_out, int pack_pos_bits,
+                         const uint32_t* gate, cudaStream_t stream);
+int psb_localize2_gated(const psb_u64* keys_a, const psb_u64* keys_b, const uint32_t* pos_a, const uint32_t* pos_b,
+                        const uint32_t* where, uint32_t* csc_row, uint32_t n, const uint32_t* row_ptr,
+                        uint32_t n_rows, uint32_t fixed_z, const float* vals, const psb_u64* bounds, int S,
+                        psb_u64* ukeys, uint32_t* seg_off, uint32_t* csr_col, float* csc_val, uint32_t* flagbits,
+                        uint32_t* wordbase, uint32_t* n_unique, uint32_t* own_off, void* scratch,
+                        int pack_pos_bits, const uint32_t* gate, cudaStream_t stream);
+int psb_owner_offsets_n(const psb_u64* ukeys, const uint32_t* n_unique, const psb_u64* bounds, int S, uint32_t n,
+                        uint32_t* seg_off, uint32_t* own_off, const uint32_t* skip_when_set, cudaStream_t stream);
+// Bucket-based localisation (bucket_localize.cu): groups the nonzeros by key without a full sort.
+size_t psb_bucket_localize_scratch_bytes(uint32_t max_n);
+int psb_bucket_localize(const void* in, int in_kind, psb_u64 seed, uint32_t n, int low_zero_bits,
+                        const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z, const float* vals,
+                        const psb_u64* bounds, int S, psb_u64* cold_words, uint32_t* cold_pos, uint32_t* hot_pos,
+                        psb_u64* ukeys, uint32_t* seg_off, uint32_t* csr_col, uint32_t* csc_row, float* csc_val,
+                        uint32_t* flagbits, uint32_t* wordbase, uint32_t* n_unique, uint32_t* own_off,
+                        void* scratch, uint32_t* status, uint32_t* gate_out, cudaStream_t stream);
 size_t psb_localize_scratch_bytes(uint32_t n);
 int psb_localize(const psb_u64* sorted_keys, uint32_t* sorted_pos, uint32_t n,
                  const uint32_t* row_ptr, uint32_t n_rows, uint32_t fixed_z, const float* vals,

@@ -40,6 +40,10 @@ __device__ __forceinline__ u32 ld_status(const u32* p) {
   return v;
 }
 
+// Launch gate: a device word decides whether the kernels of a call run at all (the sort-based
+// localisation is enqueued behind the bucket-based one and only runs when that one gave up).
+__device__ __forceinline__ bool gate_closed(const u32* gate) { return gate != nullptr && *gate == 0; }
+
 __device__ __forceinline__ u32 digit_of(u64 k, int shift, u32 dmask) {
   return (u32)(k >> shift) & dmask;
 }
@@ -51,8 +55,9 @@ __device__ __forceinline__ u32 digit_of(u64 k, int shift, u32 dmask) {
 // travel as single 64-bit words and need no payload array.
 __global__ void __launch_bounds__(256) k_sort_histogram(
     const void* __restrict__ in, int in_kind, u64 seed, u64* __restrict__ keys_out, u32 n,
-    int begin_bit, int end_bit, u32* __restrict__ ghist, int pack_bits) {
+    int begin_bit, int end_bit, u32* __restrict__ ghist, int pack_bits, const u32* __restrict__ gate) {
   __shared__ u32 sh[8 * kRadix];
+  if (gate_closed(gate)) return;
   const int npass = (end_bit - begin_bit + kRadixBits - 1) / kRadixBits;
   for (int i = threadIdx.x; i < npass * kRadix; i += blockDim.x) sh[i] = 0;
   __syncthreads();
@@ -136,8 +141,10 @@ __global__ void __launch_bounds__(256) k_sort_histogram(
 // executed pass (payload defaults to the element index); plan[16] = buffer that
 // holds the result.
 __global__ void __launch_bounds__(kRadix) k_sort_plan(const u32* __restrict__ ghist, int npass, u32 n,
-                                                      u32* __restrict__ plan, u32* __restrict__ gpre) {
+                                                      u32* __restrict__ plan, u32* __restrict__ gpre,
+                                                      const u32* __restrict__ gate) {
   __shared__ u32 s_skip[8];
+  if (gate_closed(gate)) return;
   __shared__ u32 s_scan[kRadix];
   const int t = threadIdx.x;
   if (t < 8) s_skip[t] = 0;
@@ -171,8 +178,9 @@ __global__ void __launch_bounds__(kRadix) k_sort_plan(const u32* __restrict__ gh
 
 // When every pass is skipped (the input is already in order) and no payload was
 // given, the payload still has to become the element index.
-__global__ void k_sort_identity_payload(const u32* __restrict__ plan, u32* __restrict__ vals_a, u32 n) {
-  if (plan[17] == 0) return;
+__global__ void k_sort_identity_payload(const u32* __restrict__ plan, u32* __restrict__ vals_a, u32 n,
+                                        const u32* __restrict__ gate) {
+  if (gate_closed(gate) || plan[17] == 0) return;
   for (u32 i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) vals_a[i] = i;
 }
 
@@ -187,10 +195,10 @@ __global__ void k_sort_identity_payload(const u32* __restrict__ plan, u32* __res
 
 // One digit pass. `status` holds ntiles*256 zeroed words for this pass.
 //
-// Tile i is block i. The look-back of a tile reads the status words of lower
-// tiles only, and the hardware dispatches the blocks of a one-dimensional grid in
-// index order, so those tiles are resident or finished; should that ever not
-// hold, the bounded spin reports kLookbackTimeout instead of hanging.
+// A block takes its tile index from a per-pass ticket counter (one atomic per
+// block), so the look-back of a tile only ever waits for tiles whose blocks are
+// already running or finished, whatever order the hardware dispatches blocks in.
+// The spin is bounded all the same and reports kLookbackTimeout.
 //
 // Order of work in a tile: rank -> digit totals (published as the tile's
 // aggregate) -> keys scattered to shared memory in digit order -> look-back
@@ -199,11 +207,13 @@ __global__ void k_sort_identity_payload(const u32* __restrict__ plan, u32* __res
 __global__ void __launch_bounds__(kSortThreads, 2) k_sort_onesweep(
     u64* __restrict__ keys_a, u32* __restrict__ vals_a, u64* __restrict__ keys_b, u32* __restrict__ vals_b,
     int vals_given, u32 n, int shift, u32 dmask, const u32* __restrict__ gpre,
-    u32* __restrict__ status, u32* __restrict__ err, const u32* __restrict__ plan, int pass PSB_TRACE_PARAM) {
+    u32* __restrict__ status, u32* __restrict__ err, const u32* __restrict__ plan, int pass,
+    u32* __restrict__ ticket, const u32* __restrict__ gate PSB_TRACE_PARAM) {
 #ifdef PSB_SORT_TRACE
   long long ts[12] = {0}; int nts = 0;
 #endif
   PSB_STAMP();
+  if (gate_closed(gate)) return;
   // the plan word is the same for every tile: keep its line in L1 for the later tiles of this SM
   u32 pl;
   asm volatile("ld.global.nc.L1::evict_last.u32 %0, [%1];" : "=r"(pl) : "l"(plan + pass));
@@ -222,9 +232,12 @@ __global__ void __launch_bounds__(kSortThreads, 2) k_sort_onesweep(
   __shared__ u32 s_dstart[kRadix];             // tile-local start of each digit
   __shared__ u32 s_gbase[kRadix];              // global dst = s_gbase[d] + p
   __shared__ u32 s_warp[kRadix / 32];
+  __shared__ u32 s_tile;
 
   const int t = threadIdx.x, lane = t & 31, w = t >> 5;
-  const u32 tile = blockIdx.x;
+  if (t == 0) s_tile = atomicAdd(ticket, 1u);
+  __syncthreads();
+  const u32 tile = s_tile;
   const u32 tile_base = tile * (u32)kSortTile;
   const u32 nvalid = min((u32)kSortTile, n - tile_base);
 
@@ -419,14 +432,15 @@ extern "C" size_t psb_sort_scratch_bytes(uint32_t n, int begin_bit, int end_bit)
 // are constant across the batch are skipped, so which buffer holds the result is
 // only known on the device: *where_out (device word) is 0 for A, 1 for B.
 // With pack_pos_bits > 0 (see k_sort_histogram) pass null payload buffers.
-extern "C" int psb_sort_pairs(const void* in, int in_kind, psb_u64 seed, psb_u64* keys_a,
-                              uint32_t* vals_a, int vals_given, psb_u64* keys_b, uint32_t* vals_b,
-                              uint32_t n, int begin_bit, int end_bit, void* scratch,
-                              uint32_t* status, uint32_t* where_out, int pack_pos_bits, cudaStream_t stream
+static int sort_pairs_impl(const void* in, int in_kind, psb_u64 seed, psb_u64* keys_a,
+                           uint32_t* vals_a, int vals_given, psb_u64* keys_b, uint32_t* vals_b,
+                           uint32_t n, int begin_bit, int end_bit, void* scratch,
+                           uint32_t* status, uint32_t* where_out, int pack_pos_bits, const uint32_t* gate,
+                           cudaStream_t stream
 #ifdef PSB_SORT_TRACE
-                              , long long* trace, int trace_pass
+                           , long long* trace, int trace_pass
 #endif
-                              ) {
+                           ) {
   if (end_bit <= begin_bit || end_bit > 64 || begin_bit < 0) return -(int)cudaErrorInvalidValue;
   if (pack_pos_bits) {
     // packed mode: hashed input, index bits below the sorted range, and they must hold every index
@@ -438,25 +452,56 @@ extern "C" int psb_sort_pairs(const void* in, int in_kind, psb_u64 seed, psb_u64
   const u32 ntiles = (n + kSortTile - 1) / kSortTile;
   u32* ghist = (u32*)scratch;
   u32* gpre = ghist + (size_t)npass * kRadix;
-  u32* plan = gpre + (size_t)npass * kRadix + 16;
+  u32* tickets = gpre + (size_t)npass * kRadix;   // one zeroed word per pass (16 reserved)
+  u32* plan = tickets + 16;
   u32* st = plan + 32;
   cudaMemsetAsync(scratch, 0, psb_sort_scratch_bytes(n, begin_bit, end_bit), stream);
-  int hb = (int)min((u32)(148 * 8), (n / 8 + 255) / 256 + 1);
+  int hb = (int)min((u32)(psb_device_sm_count() * 8), (n / 8 + 255) / 256 + 1);
   k_sort_histogram<<<hb, 256, 0, stream>>>(in, in_kind, seed, (u64*)keys_a, n, begin_bit, end_bit, ghist,
-                                           pack_pos_bits);
-  k_sort_plan<<<1, kRadix, 0, stream>>>(ghist, npass, n, plan, gpre);
+                                           pack_pos_bits, gate);
+  k_sort_plan<<<1, kRadix, 0, stream>>>(ghist, npass, n, plan, gpre, gate);
   for (int p = 0; p < npass; ++p) {
     int shift = begin_bit + p * kRadixBits;
     int bits = min(kRadixBits, end_bit - shift);
     k_sort_onesweep<<<ntiles, kSortThreads, 0, stream>>>(
         (u64*)keys_a, vals_a, (u64*)keys_b, vals_b, vals_given, n, shift, (1u << bits) - 1,
-        gpre + (size_t)p * kRadix, st + (size_t)p * ntiles * kRadix, status, plan, p
+        gpre + (size_t)p * kRadix, st + (size_t)p * ntiles * kRadix, status, plan, p, tickets + p, gate
 #ifdef PSB_SORT_TRACE
         , p == trace_pass ? trace : nullptr
 #endif
         );
   }
-  if (!vals_given && vals_a && !pack_pos_bits) k_sort_identity_payload<<<hb, 256, 0, stream>>>(plan, vals_a, n);
+  if (!vals_given && vals_a && !pack_pos_bits) k_sort_identity_payload<<<hb, 256, 0, stream>>>(plan, vals_a, n, gate);
   cudaMemcpyAsync(where_out, plan + 16, sizeof(u32), cudaMemcpyDeviceToDevice, stream);
   return -(int)cudaGetLastError();
+}
+
+extern "C" int psb_sort_pairs(const void* in, int in_kind, psb_u64 seed, psb_u64* keys_a,
+                              uint32_t* vals_a, int vals_given, psb_u64* keys_b, uint32_t* vals_b,
+                              uint32_t n, int begin_bit, int end_bit, void* scratch,
+                              uint32_t* status, uint32_t* where_out, int pack_pos_bits, cudaStream_t stream
+#ifdef PSB_SORT_TRACE
+                              , long long* trace, int trace_pass
+#endif
+                              ) {
+  return sort_pairs_impl(in, in_kind, seed, keys_a, vals_a, vals_given, keys_b, vals_b, n, begin_bit, end_bit,
+                         scratch, status, where_out, pack_pos_bits, nullptr, stream
+#ifdef PSB_SORT_TRACE
+                         , trace, trace_pass
+#endif
+                         );
+}
+
+// Same, but every kernel of the call returns at once unless the device word *gate is non-zero.
+extern "C" int psb_sort_pairs_gated(const void* in, int in_kind, psb_u64 seed, psb_u64* keys_a,
+                                    uint32_t* vals_a, int vals_given, psb_u64* keys_b, uint32_t* vals_b,
+                                    uint32_t n, int begin_bit, int end_bit, void* scratch,
+                                    uint32_t* status, uint32_t* where_out, int pack_pos_bits,
+                                    const uint32_t* gate, cudaStream_t stream) {
+  return sort_pairs_impl(in, in_kind, seed, keys_a, vals_a, vals_given, keys_b, vals_b, n, begin_bit, end_bit,
+                         scratch, status, where_out, pack_pos_bits, gate, stream
+#ifdef PSB_SORT_TRACE
+                         , nullptr, -1
+#endif
+                         );
 }

@@ -151,6 +151,14 @@ def _declare(lib):
     lib.psb_localize2.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _vp, _u32, _u32, _vp, _vp, _i32, _vp, _vp, _vp, _vp,
                                   _vp, _vp, _vp, _vp, _vp, _i32, _vp]
     lib.psb_owner_offsets.argtypes = [_vp, _vp, _vp, _i32, _vp, _vp]
+    lib.psb_sort_pairs_gated.argtypes = [_vp, _i32, _u64, _vp, _vp, _i32, _vp, _vp, _u32, _i32, _i32, _vp, _vp, _vp, _i32,
+                                         _vp, _vp]
+    lib.psb_localize2_gated.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _vp, _u32, _u32, _vp, _vp, _i32, _vp, _vp, _vp,
+                                        _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp]
+    lib.psb_bucket_localize_scratch_bytes.restype = sz
+    lib.psb_bucket_localize_scratch_bytes.argtypes = [_u32]
+    lib.psb_bucket_localize.argtypes = [_vp, _i32, _u64, _u32, _i32, _vp, _u32, _u32, _vp, _vp, _i32, _vp, _vp, _vp,
+                                        _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]
     lib.psb_localize_scratch_bytes.restype = sz
     lib.psb_localize_scratch_bytes.argtypes = [_u32]
     lib.psb_localize.argtypes = [_vp, _vp, _u32, _vp, _u32, _u32, _vp, _vp, _i32, _vp, _vp, _vp, _vp,

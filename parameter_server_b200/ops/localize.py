@@ -1,7 +1,15 @@
-"""Minibatch localisation on the GPU: radix sort + unique + remap (kernel K1/K2).
+"""Minibatch localisation on the GPU: unique keys + CSC/CSR remap (kernels K1/K2).
 
 :class:`LocalBatch` owns every per-minibatch device buffer of a worker, sized
 once for the largest minibatch, so a training step allocates nothing.
+
+Two device paths produce the same outputs. ``bucket`` groups the nonzeros by
+key without a full sort (frequent keys by counting, the rest per key-range
+bucket in shared memory); it assumes keys that are spread evenly over the key
+space (hashed keys) and raises a device flag otherwise. ``sort`` is the radix
+sort + head-flag scan. ``auto`` (the default) enqueues ``bucket`` and, behind
+it, the ``sort`` kernels gated on that flag, so the result is right for any
+input and nothing waits for the host.
 """
 from __future__ import annotations
 
@@ -38,6 +46,8 @@ def sort_pairs(keys: torch.Tensor, payload: Optional[torch.Tensor] = None, begin
 class LocalBatch:
     """Device buffers of one in-flight minibatch of a worker."""
 
+    BUCKET_MIN_NNZ = 4096      # below this the sort path is as fast and has fewer launches
+
     def __init__(self, max_rows: int, max_nnz: int, n_shards: int, device, real_values: bool = False):
         dev = device
         i32, i64, f32 = torch.int32, torch.int64, torch.float32
@@ -51,6 +61,8 @@ class LocalBatch:
         self.where = torch.zeros(1, dtype=i32, device=dev)   # which ping-pong buffer holds the sorted pairs
         nb = max(L.psb_sort_scratch_bytes(max_nnz, 0, 64), L.psb_localize_scratch_bytes(max_nnz))
         self.scratch = torch.empty(nb, dtype=torch.uint8, device=dev)
+        self.bucket_scratch = torch.empty(L.psb_bucket_localize_scratch_bytes(max_nnz), dtype=torch.uint8, device=dev)
+        self.gate = torch.zeros(1, dtype=i32, device=dev)    # 1 = the bucket path gave up on this minibatch
         self.status = torch.zeros(1, dtype=i32, device=dev)
         self.ukeys = torch.empty(max_nnz, dtype=i64, device=dev)
         self.seg_off = torch.empty(max_nnz + 1, dtype=i32, device=dev)
@@ -80,7 +92,8 @@ class LocalBatch:
     def localize(self, ids: torch.Tensor, y: Optional[torch.Tensor], bounds: torch.Tensor, *,
                  fixed_z: int = 0, row_ptr: Optional[torch.Tensor] = None,
                  vals: Optional[torch.Tensor] = None, hash_seed: Optional[int] = None,
-                 key_bits=64, hash_bits: int = 0, packed: Optional[bool] = None, stream=None):
+                 key_bits=64, hash_bits: int = 0, packed: Optional[bool] = None, method: str = "auto",
+                 stream=None):
         """Sort + unique + remap one minibatch.
 
         ``ids``: flat per-nonzero feature ids. ``int32`` (raw ids, hashed to uint64
@@ -92,7 +105,10 @@ class LocalBatch:
         bit range, an int (``[0, key_bits)``) or a ``(begin, end)`` pair. Digit
         positions that turn out constant across the batch are skipped anyway.
         ``packed``: None = pack (key, position) into one word whenever possible,
-        False = never, True = require it.
+        False = never, True = require it. ``method``: ``auto`` | ``bucket`` |
+        ``sort`` (see the module docstring); inside a key's CSC segment the
+        bucket path lists the rows in no particular order, the sort path by
+        position.
         """
         L = _lib.lib()
         n = ids.numel()
@@ -124,19 +140,37 @@ class LocalBatch:
                 lo_bit = max(lo_bit, 64 - hash_bits)
         assert pack or not packed, "packed mode needs hashed keys with (64 - hash_bits) bits for the positions"
         self.pack_bits = pack
-        check(L.psb_sort_pairs(ptr(ids), in_kind, seed, ptr(self.keys_a), 0 if pack else ptr(self.pos_a), 0,
-                               ptr(self.keys_b), 0 if pack else ptr(self.pos_b), n, lo_bit, hi_bit,
-                               ptr(self.scratch), ptr(self.status), ptr(self.where), pack, sp), "sort",
-              kernels=3 + (hi_bit - lo_bit + 7) // 8)
         self.csc_val = self.csc_val_buf if vals is not None else None
         if vals is not None:
             assert self.csc_val_buf is not None
-        check(L.psb_localize2(ptr(self.keys_a), ptr(self.keys_b), ptr(self.pos_a), ptr(self.pos_b), ptr(self.where),
-                              ptr(self.csc_row_buf), n, ptr(row_ptr), self.n_rows, self.fixed_z, ptr(vals),
-                              ptr(bounds), self.S, ptr(self.ukeys), ptr(self.seg_off), ptr(self.csr_col),
-                              ptr(self.csc_val), ptr(self.flagbits), ptr(self.wordbase), ptr(self.n_unique),
-                              ptr(self.own_off), ptr(self.scratch), pack, sp), "localize", kernels=4)
         self.csc_row = self.csc_row_buf
+        assert method in ("auto", "bucket", "sort")
+        # the bucket path takes its buckets from the top key bits: only for keys sorted up to bit 64
+        use_bucket = method != "sort" and hi_bit == 64 and n >= self.BUCKET_MIN_NNZ
+        gate = 0
+        if use_bucket:
+            low_zero = (64 - hash_bits) if (hash_seed is not None and 0 < hash_bits < 64) else 0
+            check(L.psb_bucket_localize(ptr(ids), in_kind, seed, n, low_zero, ptr(row_ptr), self.n_rows, self.fixed_z,
+                                        ptr(vals), ptr(bounds), self.S, ptr(self.keys_a), ptr(self.pos_a),
+                                        ptr(self.keys_b), ptr(self.ukeys), ptr(self.seg_off), ptr(self.csr_col),
+                                        ptr(self.csc_row_buf), ptr(self.csc_val), ptr(self.flagbits),
+                                        ptr(self.wordbase), ptr(self.n_unique), ptr(self.own_off),
+                                        ptr(self.bucket_scratch), ptr(self.status), ptr(self.gate), sp),
+                  "bucket localize", kernels=10)
+            if method == "bucket":
+                return self
+            gate = ptr(self.gate)
+        # sort-based path; behind the bucket path its kernels run only if that one raised the gate
+        check(L.psb_sort_pairs_gated(ptr(ids), in_kind, seed, ptr(self.keys_a), 0 if pack else ptr(self.pos_a), 0,
+                                     ptr(self.keys_b), 0 if pack else ptr(self.pos_b), n, lo_bit, hi_bit,
+                                     ptr(self.scratch), ptr(self.status), ptr(self.where), pack, gate, sp), "sort",
+              kernels=3 + (hi_bit - lo_bit + 7) // 8)
+        check(L.psb_localize2_gated(ptr(self.keys_a), ptr(self.keys_b), ptr(self.pos_a), ptr(self.pos_b),
+                                    ptr(self.where), ptr(self.csc_row_buf), n, ptr(row_ptr), self.n_rows,
+                                    self.fixed_z, ptr(vals), ptr(bounds), self.S, ptr(self.ukeys), ptr(self.seg_off),
+                                    ptr(self.csr_col), ptr(self.csc_val), ptr(self.flagbits), ptr(self.wordbase),
+                                    ptr(self.n_unique), ptr(self.own_off), ptr(self.scratch), pack, gate, sp),
+              "localize", kernels=4)
         return self
 
     def set_keys(self, ukeys_sorted: torch.Tensor, bounds, stream=None):

@@ -64,7 +64,7 @@ def test_localize_matches_numpy(cuda_lib, S, fixed):
     bounds = torch.tensor([x if x < (1 << 63) else x - (1 << 64) for x in bounds_h], dtype=torch.int64).cuda()
     ids = torch.from_numpy(keys.view(np.int64)).cuda()
     kw = dict(fixed_z=z) if fixed else dict(row_ptr=torch.from_numpy(row_ptr.astype(np.int32)).cuda())
-    b.localize(ids, None, bounds, vals=torch.from_numpy(vals).cuda(), hash_seed=None, **kw)
+    b.localize(ids, None, bounds, vals=torch.from_numpy(vals).cuda(), hash_seed=None, method="sort", **kw)
     torch.cuda.synchronize()
     u, inv, cnt = np.unique(keys, return_inverse=True, return_counts=True)
     U = int(b.n_unique.item())
@@ -121,7 +121,7 @@ def test_sort_skips_constant_digits_and_narrow_hash(cuda_lib):
     assert torch.equal(sv2.cpu(), torch.arange(5000, dtype=torch.int32)) and torch.equal(sk2, same)
     b = LocalBatch(64, ids.size, 2, "cuda")
     bounds = torch.tensor([0, -(1 << 63), -1], dtype=torch.int64).cuda()
-    b.localize(torch.from_numpy(ids).cuda(), None, bounds, fixed_z=300, hash_seed=0, hash_bits=40)
+    b.localize(torch.from_numpy(ids).cuda(), None, bounds, fixed_z=300, hash_seed=0, hash_bits=40, method="sort")
     U = int(b.n_unique.item())
     u = np.unique(k)
     assert np.array_equal(b.ukeys[:U].cpu().numpy().view(np.uint64), u)
@@ -143,7 +143,7 @@ def test_packed_positions_match_pair_sort(cuda_lib, hash_bits, rows, z):
     for packed in (True, False):
         b = LocalBatch(rows, ids.size, 3, "cuda", real_values=True)
         b.localize(torch.from_numpy(ids).cuda(), None, bounds, fixed_z=z, vals=torch.from_numpy(vals).cuda(),
-                   hash_seed=3, hash_bits=hash_bits, key_bits=(64 - hash_bits, 64), packed=packed)
+                   hash_seed=3, hash_bits=hash_bits, key_bits=(64 - hash_bits, 64), packed=packed, method="sort")
         torch.cuda.synchronize()
         assert (b.pack_bits > 0) == packed
         U = int(b.n_unique.item())
@@ -153,3 +153,119 @@ def test_packed_positions_match_pair_sort(cuda_lib, hash_bits, rows, z):
     assert out[0][0] == out[1][0] and out[0][0] > 1
     for x, y in zip(out[0][1:], out[1][1:]):
         assert torch.equal(x, y)
+
+
+def _check_grouped(b, keys, row_ptr, vals, bounds_h, rows):
+    """Every output of a localised batch against NumPy, with the rows of a key's
+    CSC segment compared as a set (the bucket path does not order them)."""
+    nnz = keys.size
+    u, inv, cnt = np.unique(keys, return_inverse=True, return_counts=True)
+    U = int(b.n_unique.item())
+    assert U == len(u)
+    assert np.array_equal(b.ukeys[:U].cpu().numpy().view(np.uint64), u)
+    assert np.array_equal(b.csr_col[:nnz].cpu().numpy(), inv)
+    seg = b.seg_off[:U + 1].cpu().numpy().astype(np.int64)
+    assert seg[0] == 0 and seg[-1] == nnz
+    assert np.array_equal(np.diff(seg), cnt)
+    rows_of = np.repeat(np.arange(rows), np.diff(row_ptr))
+    order = np.argsort(keys, kind="stable")
+    seg_id = np.repeat(np.arange(U), cnt)
+    got_rows = b.csc_row[:nnz].cpu().numpy().astype(np.int64)
+    exp_rows = rows_of[order]
+    if vals is None:
+        assert np.array_equal(np.sort(seg_id * (rows + 1) + got_rows), np.sort(seg_id * (rows + 1) + exp_rows))
+    else:
+        # (row, value) pairs per segment, as sets
+        got_v = b.csc_val[:nnz].cpu().numpy()
+        g = np.lexsort((got_v, got_rows, seg_id))
+        e = np.lexsort((vals[order], exp_rows, seg_id))
+        assert np.array_equal(got_rows[g], exp_rows[e])
+        assert np.array_equal(got_v[g], vals[order][e])
+    own = b.own_off.cpu().numpy()
+    assert list(own) == [int(np.searchsorted(u, np.uint64(x))) for x in bounds_h[:-1]] + [U]
+    fb = b.flagbits[:(nnz + 31) // 32].cpu().numpy().view(np.uint32)
+    heads = np.zeros(nnz, dtype=bool); heads[seg[:-1]] = True
+    bits = np.unpackbits(fb.view(np.uint8), bitorder="little")[:nnz].astype(bool)
+    assert np.array_equal(bits, heads)
+    wb = b.wordbase[:(nnz + 31) // 32].cpu().numpy()
+    assert np.array_equal(wb, np.concatenate([[0], np.cumsum(heads)])[0:nnz:32])
+
+
+def _bounds(S):
+    from parameter_server_b200.utils.range import Range, shard_bounds
+    bounds_h = shard_bounds(Range.all(), S)
+    return bounds_h, torch.tensor([x if x < (1 << 63) else x - (1 << 64) for x in bounds_h], dtype=torch.int64).cuda()
+
+
+@pytest.mark.parametrize("hash_bits,rows,z,S", [(40, 2048, 100, 1), (40, 4096, 200, 8), (0, 1500, 64, 3), (52, 700, 37, 2)])
+def test_bucket_localize_hashed_ids(cuda_lib, hash_bits, rows, z, S):
+    """Bucket path on device-hashed ids with a heavy head (frequent keys go through
+    the counting path, the rest through the per-bucket tables)."""
+    from parameter_server_b200.ops.localize import LocalBatch
+    from parameter_server_b200.utils.oracle import hash_id_to_key
+    rng = np.random.default_rng(hash_bits + rows)
+    ids = (rng.zipf(1.2, rows * z) % (1 << 24)).astype(np.int32)
+    keys = hash_id_to_key(ids, 5, hash_bits or 64)
+    bounds_h, bounds = _bounds(S)
+    b = LocalBatch(rows, ids.size, S, "cuda")
+    b.localize(torch.from_numpy(ids).cuda(), None, bounds, fixed_z=z, hash_seed=5, hash_bits=hash_bits, method="bucket")
+    torch.cuda.synchronize()
+    assert int(b.gate.item()) == 0, "the bucket path gave up on evenly spread keys"
+    assert int(b.status.item()) == 0
+    _check_grouped(b, keys, np.arange(rows + 1) * z, None, bounds_h, rows)
+
+
+def test_bucket_localize_raw_keys_rows_and_values(cuda_lib):
+    """Raw 64-bit keys (no device hash, positions in their own array), CSR row
+    offsets and real values."""
+    from parameter_server_b200.ops.localize import LocalBatch
+    rng = np.random.default_rng(77)
+    rows = 3000
+    lens = rng.integers(0, 60, rows)
+    row_ptr = np.concatenate([[0], np.cumsum(lens)])
+    nnz = int(row_ptr[-1])
+    keys = _rand_keys(nnz, rng, skew=True)
+    vals = rng.random(nnz, dtype=np.float32)
+    bounds_h, bounds = _bounds(4)
+    b = LocalBatch(rows, nnz, 4, "cuda", real_values=True)
+    b.localize(torch.from_numpy(keys.view(np.int64)).cuda(), None, bounds,
+               row_ptr=torch.from_numpy(row_ptr.astype(np.int32)).cuda(), vals=torch.from_numpy(vals).cuda(),
+               hash_seed=None, method="bucket")
+    torch.cuda.synchronize()
+    assert int(b.gate.item()) == 0 and int(b.status.item()) == 0
+    _check_grouped(b, keys, row_ptr, vals, bounds_h, rows)
+
+
+def test_bucket_localize_all_distinct_and_all_equal(cuda_lib):
+    from parameter_server_b200.ops.localize import LocalBatch
+    from parameter_server_b200.utils.oracle import hash_id_to_key
+    bounds_h, bounds = _bounds(2)
+    rows, z = 1024, 64
+    for ids in (np.arange(rows * z, dtype=np.int32), np.full(rows * z, 12345, dtype=np.int32)):
+        keys = hash_id_to_key(ids, 1, 40)
+        b = LocalBatch(rows, ids.size, 2, "cuda")
+        b.localize(torch.from_numpy(ids).cuda(), None, bounds, fixed_z=z, hash_seed=1, hash_bits=40, method="bucket")
+        torch.cuda.synchronize()
+        assert int(b.gate.item()) == 0 and int(b.status.item()) == 0
+        _check_grouped(b, keys, np.arange(rows + 1) * z, None, bounds_h, rows)
+
+
+def test_auto_falls_back_to_sort_on_clustered_keys(cuda_lib):
+    """Small integer keys all fall into the first bucket: the bucket path raises its
+    flag on the device and the gated sort path produces the result."""
+    from parameter_server_b200.ops.localize import LocalBatch
+    rng = np.random.default_rng(9)
+    rows, z = 2000, 50
+    keys = rng.integers(1, 200_000, rows * z, dtype=np.int64).astype(np.uint64)
+    bounds_h, bounds = _bounds(2)
+    b = LocalBatch(rows, keys.size, 2, "cuda")
+    b.localize(torch.from_numpy(keys.view(np.int64)).cuda(), None, bounds, fixed_z=z, hash_seed=None, method="auto")
+    torch.cuda.synchronize()
+    assert int(b.gate.item()) == 1 and int(b.status.item()) == 0
+    _check_grouped(b, keys, np.arange(rows + 1) * z, None, bounds_h, rows)
+    # the same buffers, next minibatch with spread keys: the bucket path runs again
+    keys2 = _rand_keys(rows * z, rng, skew=True)
+    b.localize(torch.from_numpy(keys2.view(np.int64)).cuda(), None, bounds, fixed_z=z, hash_seed=None, method="auto")
+    torch.cuda.synchronize()
+    assert int(b.gate.item()) == 0 and int(b.status.item()) == 0
+    _check_grouped(b, keys2, np.arange(rows + 1) * z, None, bounds_h, rows)
