@@ -64,141 +64,179 @@ def write_model(path: str, keys, weights):
             out.write(f"{k}\t{format_weight(v)}\n")
 
 
-class ProgressPrinter:
-    HEADER = " sec  examples    loss      auc   accuracy   |w|_0  updt ratio"
+class GpuEngine:
+    """The device side of one rank for the node layer (``app/nodes.py``): a lock-step round is one
+    ``SparseLRWorker.submit`` from pinned host buffers; nothing here waits for the device except the
+    progress read-out and the end of the job."""
 
-    def __init__(self):
-        self.t0 = time.time()
-        self.total = 0
-        self.nnz = 0
-        self.printed = False
+    def __init__(self, worker, plane, max_rows: int, max_nnz: int, real_values: bool, depth: int = 4):
+        self.worker, self.plane = worker, plane
+        self.ring = []
+        for _ in range(depth):
+            self.ring.append({
+                "ids": torch.empty(max_nnz, dtype=torch.int64).pin_memory(),
+                "vals": torch.empty(max_nnz, dtype=torch.float32).pin_memory() if real_values else None,
+                "rp": torch.empty(max_rows + 1, dtype=torch.int32).pin_memory(),
+                "y": torch.empty(max_rows, dtype=torch.float32).pin_memory(),
+                "ev": torch.cuda.Event(),
+                "used": False,
+            })
+        self.k = 0
+        self.real_values = real_values
 
-    def line(self, p, header: bool = True) -> str:
-        self.total += int(p["n_examples"])
-        self.nnz += int(p["d_nnz"])
-        n = max(1.0, p["n_examples"])
-        ratio = (p["delta_sum"] ** 0.5) / (p["weight_sum"] ** 0.5) if p["weight_sum"] > 0 else 0.0
-        if header and not self.printed:
-            print(self.HEADER, flush=True)
-            self.printed = True
-        return (f"{int(time.time() - self.t0):4d}  {self.total:.2e}  {p['loss_sum'] / n:.3e}  {p.get('auc', 0.0):.4f}  "
-                f"{p['n_correct'] / n:.4f}  {self.nnz:.2e}  {ratio:.2e}")
+    def submit(self, batch) -> int:
+        slot = self.ring[self.k % len(self.ring)]
+        self.k += 1
+        if slot["used"]:
+            slot["ev"].synchronize()          # the copy that last read this pinned buffer is long done
+        if batch is None:
+            n, nnz = 0, 0
+            slot["rp"][0] = 0
+            vals = None
+        else:
+            yv, mats = batch
+            m = mats[0]
+            n, nnz = len(yv), m["index"].size
+            slot["ids"][:nnz].copy_(torch.from_numpy(m["index"].view(np.int64)))
+            slot["rp"][:n + 1].copy_(torch.from_numpy(m["offset"].astype(np.int32)))
+            slot["y"][:n].copy_(torch.from_numpy(np.where(yv > 0, 1.0, -1.0).astype(np.float32)))
+            vals = None
+            if self.real_values:
+                vals = slot["vals"][:nnz]
+                if m["binary"]:
+                    vals.fill_(1.0)
+                else:
+                    vals.copy_(torch.from_numpy(m["value"]))
+        self.worker.submit(slot["ids"][:nnz], slot["y"][:n], row_ptr=slot["rp"][:n + 1], vals=vals)
+        slot["ev"].record(self.worker.copy_stream)
+        slot["used"] = True
+        return n
+
+    def finish(self):
+        self.worker.wait()
+        torch.cuda.synchronize()
+        self.plane.check_status("async sgd")
+
+    def progress(self) -> dict:
+        p = self.worker.read_progress()
+        if self.worker.auc_hist is not None:
+            p["auc"] = auc_from_histogram(self.worker.auc_hist.cpu().numpy())
+            self.worker.auc_hist.zero_()
+        return p
+
+    def set_alive(self, rank: int, alive: bool):
+        self.plane.set_alive(rank, alive)
+
+    def save_model(self, path: str):
+        keys, w = self.plane.dump_nonzero()
+        write_model(path, keys.numpy(), w.numpy())
 
 
-def run_async_sgd(conf, verbose=True):
-    from ..models.sparse_lr import SparseLRConfig, SparseLRWorker
-    from ..parallel.dataplane import DataPlane, OptimizerConfig, PlaneConfig, heap_layout
-    from ..parallel.fabric import Fabric
+def _scheduler_address(dist, rank: int, world: int) -> tuple:
+    """The scheduler node's address for this job: ``PSB_SCHEDULER`` if given, else rank 0 picks a free
+    port and publishes it through the launcher's key-value store; a single process uses the
+    in-process van. Returns ``(spec, inproc)``."""
+    from . import nodes
+    from ..system import core as _core
+    if os.environ.get("PSB_SCHEDULER"):
+        return os.environ["PSB_SCHEDULER"], False
+    if dist is None or world == 1:
+        return nodes.scheduler_spec("inproc", 20000 + (os.getpid() % 20000)), True
+    store = dist.distributed_c10d._get_default_store()
+    if rank == 0:
+        spec = nodes.scheduler_spec("127.0.0.1", _core.free_port())
+        store.set("psb/scheduler", spec)
+        return spec, False
+    return store.get("psb/scheduler").decode(), False
 
-    dist, rank, world = _dist()
-    dev = torch.device("cuda", torch.cuda.current_device())
+
+def run_async_sgd(conf, verbose=True, engine: str = "gpu"):
+    """Asynchronous SGD (FTRL / AdaGrad / SGD) with every rank a server node plus a worker node of the
+    host control plane (``app/nodes.py``): files come from the scheduler's workload pool, progress
+    goes to its monitor, the model dump is its ``SAVE_MODEL`` task, lost nodes are learned from the
+    manager. ``engine="null"`` runs the same control flow without a device (tests)."""
+    from . import nodes
+
     sgd = conf["async_sgd"]
-    l1, l2 = _penalty(conf)
-    lr = conf.get("learning_rate", {})
-    algo = "ftrl" if sgd.get("algo", "FTRL") == "FTRL" else ("adagrad" if sgd.get("ada_grad", "true") == "true" else "sgd")
-    opt = OptimizerConfig(algo=algo, alpha=float(lr.get("alpha", 1)), beta=float(lr.get("beta", 1)), l1=l1, l2=l2,
-                          lr_type="constant" if lr.get("type", "DECAY") == "CONSTANT" else "decay")
     minibatch = int(sgd.get("minibatch", 1000))
     tau = int(sgd.get("max_delay", 0))
     passes = int(sgd.get("num_data_pass", 1))
-    filters = sgd.get("push_filter", [])
-    filters = filters if isinstance(filters, list) else [filters]
-    quant = "none"
-    key_cache = False
-    for f in filters:
-        if f.get("type") == "FIXING_FLOAT":
-            quant = "int8" if int(f.get("num_bytes", 3)) <= 1 else "fp16"
-        if f.get("type") == "KEY_CACHING":
-            key_cache = True
     data = conf["training_data"]
     files = _files(data)
-    my_files = files[rank::world]
     text = data.get("text", "LIBSVM")
-    max_nnz = int(os.environ.get("PSB_MAX_NNZ_PER_ROW", "512")) * minibatch
-    table_cap = 1 << int(os.environ.get("PSB_LOG2_TABLE", "22"))
-    # two-sided exchange pull unless the key-caching filter is asked for (that one belongs to the one-sided pull)
-    pc = PlaneConfig(table_capacity=table_cap, inbox_cap=max_nnz, ring=tau + 2, quant=quant, key_cache=key_cache,
-                     ordered_slots=os.environ.get("PSB_ORDERED_SLOTS", "0") == "1",
-                     pull_cap=0 if key_cache else max_nnz)
-    hb = heap_layout(pc, world).total()
-    fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
-    plane = DataPlane(fab, pc, opt)
-    if conf.get("_checkpoint_in"):
-        from ..utils import checkpoint
-        checkpoint.load_plane(plane, conf["_checkpoint_in"])
-    worker = SparseLRWorker(plane, SparseLRConfig(max_rows=minibatch, max_nnz=max_nnz, tau=tau, hash_seed=None,
-                                                  pipeline=2, auc=True, real_values=text not in ("SPARSE_BINARY", "ADFEA", "TERAFEA", "CRITEO")))
-    printer = ProgressPrinter()
-    last = time.time()
-    steps = 0
-    for _ in range(passes):
-        # every rank must submit the same number of rounds: ranks that run out of data push empty rounds
-        reader = core.StreamReader(my_files, data.get("format", "TEXT"), text, True)
-        while True:
-            got = reader.read_matrices(minibatch) if my_files else None
-            flag = torch.tensor([0 if got is None else 1], device=dev)
-            if dist is not None:
-                dist.all_reduce(flag)
-            if int(flag.item()) == 0:
-                break
-            if got is None or not got[1]:
-                ids = torch.zeros(0, dtype=torch.int64)
-                y = torch.zeros(0, dtype=torch.float32)
-                rp = torch.zeros(1, dtype=torch.int32)
-                vals = None
-            else:
-                yv, mats = got
-                m = mats[0]
-                ids = torch.from_numpy(m["index"].view(np.int64))
-                rp = torch.from_numpy(m["offset"].astype(np.int32))
-                y = torch.from_numpy(np.where(yv > 0, 1.0, -1.0).astype(np.float32))
-                vals = None if m["binary"] else torch.from_numpy(m["value"])
-            worker.submit(ids.pin_memory(), y.pin_memory(), row_ptr=rp.pin_memory(),
-                          vals=None if vals is None else vals.pin_memory())
-            steps += 1
-            if time.time() - last >= float(sgd.get("report_interval", 1)):
-                last = time.time()
-                line = printer.line(_merged_progress(worker, dist, dev), header=verbose and rank == 0)
-                if rank == 0 and verbose:
-                    print(line, flush=True)
-    worker.wait()
-    torch.cuda.synchronize()
-    plane.check_status("async sgd")
-    line = printer.line(_merged_progress(worker, dist, dev), header=verbose and rank == 0)
-    if rank == 0 and verbose:
-        print(line, flush=True)
+    fmt = data.get("format", "TEXT")
     out = conf.get("model_output", {}).get("file")
     if out:
         out = out if isinstance(out, str) else out[0]
-        keys, w = plane.dump_nonzero()
-        os.makedirs(os.path.dirname(out) or ".", exist_ok=True)
-        write_model(f"{out}_S{rank}", keys.numpy(), w.numpy())
-    if conf.get("_checkpoint_out"):
+
+    if engine == "null":
+        dist, rank, world = None, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+        eng = nodes.NullEngine(float(os.environ.get("PSB_NULL_STEP_SECONDS", "0")))
+        fab = plane = None
+    else:
+        from ..models.sparse_lr import SparseLRConfig, SparseLRWorker
+        from ..parallel.dataplane import DataPlane, OptimizerConfig, PlaneConfig, heap_layout
+        from ..parallel.fabric import Fabric
+        dist, rank, world = _dist()
+        dev = torch.device("cuda", torch.cuda.current_device())
+        l1, l2 = _penalty(conf)
+        lr = conf.get("learning_rate", {})
+        algo = "ftrl" if sgd.get("algo", "FTRL") == "FTRL" else ("adagrad" if sgd.get("ada_grad", "true") == "true" else "sgd")
+        opt = OptimizerConfig(algo=algo, alpha=float(lr.get("alpha", 1)), beta=float(lr.get("beta", 1)), l1=l1, l2=l2,
+                              lr_type="constant" if lr.get("type", "DECAY") == "CONSTANT" else "decay")
+        filters = sgd.get("push_filter", [])
+        filters = filters if isinstance(filters, list) else [filters]
+        quant = "none"
+        key_cache = False
+        for f in filters:
+            if f.get("type") == "FIXING_FLOAT":
+                quant = "int8" if int(f.get("num_bytes", 3)) <= 1 else "fp16"
+            if f.get("type") == "KEY_CACHING":
+                key_cache = True
+        max_nnz = int(os.environ.get("PSB_MAX_NNZ_PER_ROW", "512")) * minibatch
+        table_cap = 1 << int(os.environ.get("PSB_LOG2_TABLE", "22"))
+        # two-sided exchange pull unless the key-caching filter is asked for (that one belongs to the one-sided pull)
+        pc = PlaneConfig(table_capacity=table_cap, inbox_cap=max_nnz, ring=tau + 2, quant=quant, key_cache=key_cache,
+                         ordered_slots=os.environ.get("PSB_ORDERED_SLOTS", "0") == "1",
+                         pull_cap=0 if key_cache else max_nnz)
+        hb = heap_layout(pc, world).total()
+        fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
+        plane = DataPlane(fab, pc, opt)
+        if conf.get("_checkpoint_in"):
+            from ..utils import checkpoint
+            checkpoint.load_plane(plane, conf["_checkpoint_in"])
+        real_values = text not in ("SPARSE_BINARY", "ADFEA", "TERAFEA", "CRITEO")
+        worker = SparseLRWorker(plane, SparseLRConfig(max_rows=minibatch, max_nnz=max_nnz, tau=tau, hash_seed=None,
+                                                      pipeline=2, auc=True, real_values=real_values))
+        eng = GpuEngine(worker, plane, minibatch, max_nnz, real_values)
+
+    lost = []
+
+    def on_node_lost(node_id: str):
+        # REMOVE_NODE from the manager: the dead rank's rounds are not waited for any more
+        r = nodes.node_rank(node_id)
+        lost.append(node_id)
+        if r is not None and r != rank:
+            eng.set_alive(r, False)
+        if verbose:
+            print(f"[rank {rank}] node {node_id} lost", flush=True)
+
+    spec, inproc = _scheduler_address(dist, rank, world)
+    rn = nodes.start_rank_nodes(rank, world, spec, files=files, data_format=fmt, text=text, passes=passes,
+                                lease=int(os.environ.get("PSB_ROUND_LEASE", "64")),
+                                roles=os.environ.get("PSB_ROLES", "HSW"), on_node_lost=on_node_lost, inproc=inproc)
+    res = nodes.run_lockstep_worker_loop(rn, eng, minibatch=minibatch, data_format=fmt, text=text,
+                                         report_interval=float(sgd.get("report_interval", 1)), model_file=out,
+                                         announce=f"[rank {rank}]" if verbose else "")
+    if conf.get("_checkpoint_out") and plane is not None:
         from ..utils import checkpoint
-        checkpoint.save_plane(plane, conf["_checkpoint_out"], meta={"minibatches": steps, "examples": printer.total})
+        checkpoint.save_plane(plane, conf["_checkpoint_out"], meta={"minibatches": res["rounds"], "examples": res["examples"]})
+    if verbose:
+        print(f"[rank {rank}] rounds {res['rounds']} examples {res['examples']} files {res['files']} lost {lost}", flush=True)
     if dist is not None:
         dist.barrier()
         fab.close()
-    return dict(steps=steps, examples=printer.total)
-
-
-def _merged_progress(worker, dist, dev):
-    p = worker.read_progress()
-    if worker.auc_hist is not None:
-        h = worker.auc_hist.clone()
-        worker.auc_hist.zero_()
-    else:
-        h = None
-    keys = ["loss_sum", "n_correct", "n_examples", "d_nnz", "weight_sum", "delta_sum", "n_updates"]
-    t = torch.tensor([p[k] for k in keys], dtype=torch.float64, device=dev)
-    if dist is not None:
-        dist.all_reduce(t)
-        if h is not None:
-            dist.all_reduce(h)
-    out = dict(zip(keys, t.tolist()))
-    if h is not None:
-        out["auc"] = auc_from_histogram(h.cpu().numpy())
-    return out
+    return dict(steps=res["rounds"], examples=res["examples"], files=res["files"], lost=lost)
 
 
 def auc_from_histogram(h: np.ndarray) -> float:
@@ -336,10 +374,14 @@ def main(argv: Optional[List[str]] = None):
                     help="async SGD: resume from the binary shard checkpoint <prefix>_S<rank>.psbckpt")
     ap.add_argument("-checkpoint_out", "--checkpoint_out", default="",
                     help="async SGD: write weights and optimiser state to <prefix>_S<rank>.psbckpt at the end")
+    ap.add_argument("-engine", "--engine", default="gpu", choices=["gpu", "null"],
+                    help="null: run the node layer of async SGD (scheduler, workloads, leases, membership) without a device")
     args, _ = ap.parse_known_args(argv)
     text = (open(args.app_file).read() if args.app_file else "") + args.app_conf
     conf = core.parse_text_proto(text)
     conf["_checkpoint_in"], conf["_checkpoint_out"] = args.checkpoint_in, args.checkpoint_out
+    if args.engine == "null":
+        return run_async_sgd(conf, engine="null")
     from .. import _build
     _build.build_cuda()
     if "darlin" in conf:

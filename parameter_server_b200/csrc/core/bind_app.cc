@@ -80,7 +80,9 @@ void BindApp(py::module& m) {
       .def("read_matrices", [](SR& r, uint32_t n) -> py::object {
         SArray<float> y;
         std::vector<std::shared_ptr<SparseMatrix<uint64_t, float>>> mats;
-        if (!r.readMatrices(n, &y, &mats)) return py::none();
+        bool ok;
+        { py::gil_scoped_release rel; ok = r.readMatrices(n, &y, &mats); }   // parsing needs no interpreter
+        if (!ok) return py::none();
         py::list out;
         for (auto& mt : mats) {
           py::dict d;
@@ -204,6 +206,41 @@ void BindApp(py::module& m) {
       .def("restore", &WorkloadPool::restore).def("finish", &WorkloadPool::finish)
       .def("size", &WorkloadPool::size).def("num_finished", &WorkloadPool::num_finished)
       .def("wait_until_done", &WorkloadPool::waitUtilDone, py::call_guard<py::gil_scoped_release>());
+
+  // scheduler of lock-step device workers (files handed out one at a time, rounds granted in leases)
+  py::class_<LockstepSGDScheduler, App>(m, "LockstepSGDScheduler")
+      .def(py::init([](const std::vector<std::string>& files, const std::string& format, const std::string& text,
+                       int replica, bool shuffle, int lease, Postoffice* po) {
+             Workload w;
+             w.data = MakeData(files, format, text, true, -1);
+             w.replica = replica;
+             w.shuffle = shuffle;
+             return new LockstepSGDScheduler(w, lease, po);
+           }), py::arg("files"), py::arg("format") = "TEXT", py::arg("text") = "LIBSVM", py::arg("replica") = 1,
+           py::arg("shuffle") = true, py::arg("lease") = 64, py::arg("po") = nullptr, py::keep_alive<1, 8>())
+      .def("round_limit", &LockstepSGDScheduler::round_limit)
+      .def("num_workloads", [](LockstepSGDScheduler& s) { return s.pool().size(); })
+      .def("num_finished", [](LockstepSGDScheduler& s) { return s.pool().num_finished(); })
+      .def("num_examples_processed", &LockstepSGDScheduler::num_examples_processed);
+
+  // progress reports of a worker or server node to the scheduler's monitor (system/monitor.h:60-97,
+  // learner/sgd.cc:51-86)
+  typedef MonitorSlaver<SGDProgress> Reporter;
+  py::class_<Reporter, Customer>(m, "SGDReporter")
+      .def(py::init([](Postoffice* po) {
+             return new Reporter(po->manager().van().scheduler().id, kMonitorCustomerID, po);
+           }), py::arg("po"), py::keep_alive<1, 2>())
+      .def("report", [](Reporter& r, std::vector<double> objective, std::vector<double> accuracy, std::vector<double> auc,
+                        uint64_t num_examples, uint64_t nnz, double weight_sum, double delta_sum, uint64_t round) {
+        SGDProgress p;
+        p.objective = objective; p.accuracy = accuracy; p.auc = auc;
+        p.num_examples_processed = num_examples; p.nnz = nnz; p.weight_sum = weight_sum; p.delta_sum = delta_sum;
+        p.round = round;
+        r.Report(p);
+      }, py::arg("objective") = std::vector<double>(), py::arg("accuracy") = std::vector<double>(),
+         py::arg("auc") = std::vector<double>(), py::arg("num_examples") = 0, py::arg("nnz") = 0,
+         py::arg("weight_sum") = 0.0, py::arg("delta_sum") = 0.0, py::arg("round") = 0,
+         py::call_guard<py::gil_scoped_release>());
 
   py::class_<Dashboard>(m, "Dashboard")
       .def(py::init<>())

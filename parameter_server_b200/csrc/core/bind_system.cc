@@ -8,18 +8,26 @@ namespace PS {
 // keeps Python-created apps alive for the life of the process
 static std::vector<py::object>& KeepAlive() { static auto* v = new std::vector<py::object>(); return *v; }
 
+// The message handed to a Python handler shares ownership with the executor (which holds it as the
+// customer's last request / response), so a handler that defers its answer may keep the object.
+static py::object OwnedMessage(Customer* c, Message* m, bool request) {
+  std::shared_ptr<Message> held = request ? c->LastRequest() : c->LastResponse();
+  if (held && held.get() == m) return py::cast(held);
+  return py::cast(m, py::return_value_policy::reference);
+}
+
 class PyCustomer : public Customer {
  public:
   using Customer::Customer;
   void ProcessRequest(Message* m) override {
     py::gil_scoped_acquire g;
     py::function f = py::get_override(static_cast<const Customer*>(this), "process_request");
-    if (f) f(py::cast(m, py::return_value_policy::reference));
+    if (f) f(OwnedMessage(this, m, true));
   }
   void ProcessResponse(Message* m) override {
     py::gil_scoped_acquire g;
     py::function f = py::get_override(static_cast<const Customer*>(this), "process_response");
-    if (f) f(py::cast(m, py::return_value_policy::reference));
+    if (f) f(OwnedMessage(this, m, false));
   }
 };
 
@@ -29,12 +37,12 @@ class PyApp : public App {
   void ProcessRequest(Message* m) override {
     py::gil_scoped_acquire g;
     py::function f = py::get_override(static_cast<const App*>(this), "process_request");
-    if (f) f(py::cast(m, py::return_value_policy::reference));
+    if (f) f(OwnedMessage(this, m, true));
   }
   void ProcessResponse(Message* m) override {
     py::gil_scoped_acquire g;
     py::function f = py::get_override(static_cast<const App*>(this), "process_response");
-    if (f) f(py::cast(m, py::return_value_policy::reference));
+    if (f) f(OwnedMessage(this, m, false));
   }
   void Run() override {
     py::gil_scoped_acquire g;
@@ -83,6 +91,10 @@ void BindSystem(py::module& m) {
   m.attr("kOwnerGroup") = kOwnerGroup;
   m.attr("kLiveGroup") = kLiveGroup;
   m.attr("kMaxKey") = kMaxKey;
+  m.attr("SGD_REQUEST_WORKLOAD") = (int)SGDCall::REQUEST_WORKLOAD;
+  m.attr("SGD_UPDATE_MODEL") = (int)SGDCall::UPDATE_MODEL;
+  m.attr("SGD_SAVE_MODEL") = (int)SGDCall::SAVE_MODEL;
+  m.attr("SGD_ROUND_LIMIT") = (int)SGDCall::ROUND_LIMIT;
 
   py::class_<Range<Key>>(m, "KeyRange")
       .def(py::init<Key, Key>(), py::arg("begin") = 0, py::arg("end") = kMaxKey)
@@ -146,6 +158,19 @@ void BindSystem(py::module& m) {
       .def_property("msg", [](const Task& t) { return py::bytes(t.msg); },
                     [](Task& t, const std::string& s) { t.msg = s; })
       .def_readwrite("param", &Task::param).def_readwrite("has_param", &Task::has_param)
+      // the SGD call of a task (learner/proto/sgd.proto:5-26): command, workload, round lease
+      .def_readonly("has_sgd", &Task::has_sgd)
+      .def_property("sgd_cmd", [](const Task& t) { return t.has_sgd ? (int)t.sgd.cmd : 0; },
+                    [](Task& t, int c) { t.mutable_sgd()->cmd = (SGDCall::Command)c; })
+      .def_property("sgd_load_ids", [](const Task& t) { return t.sgd.load.id; },
+                    [](Task& t, const std::vector<int>& ids) { t.mutable_sgd()->load.id = ids; t.sgd.has_load = true; })
+      .def_property_readonly("sgd_load_files", [](const Task& t) { return t.sgd.load.data.file; })
+      .def_property("sgd_load_finished", [](const Task& t) { return t.sgd.load.finished; },
+                    [](Task& t, bool f) { t.mutable_sgd()->load.finished = f; })
+      .def_property("sgd_round_limit", [](const Task& t) { return t.sgd.round_limit; },
+                    [](Task& t, int64_t v) { t.mutable_sgd()->round_limit = v; })
+      .def_property("sgd_final_round", [](const Task& t) { return t.sgd.final_round; },
+                    [](Task& t, bool v) { t.mutable_sgd()->final_round = v; })
       .def("serialize", [](const Task& t) { return py::bytes(t.Serialize()); })
       .def_static("parse", [](const std::string& s) { Task t; PS_CHECK(t.Parse(s.data(), s.size())); return t; })
       .def("__repr__", &Task::ShortDebugString);
@@ -212,6 +237,7 @@ void BindSystem(py::module& m) {
       .def("start", &Postoffice::Start, py::call_guard<py::gil_scoped_release>())
       .def("stop", &Postoffice::Stop, py::call_guard<py::gil_scoped_release>())
       .def("my_node", [](Postoffice& p) { return p.manager().van().my_node(); })
+      .def("scheduler_node", [](Postoffice& p) { return p.manager().van().scheduler(); })
       .def("nodes", [](Postoffice& p) { return p.manager().nodes(); })
       .def("num_workers", [](Postoffice& p) { return p.manager().num_workers(); })
       .def("num_servers", [](Postoffice& p) { return p.manager().num_servers(); })

@@ -5,6 +5,7 @@
 // learner/proto/sgd.proto:5-26, learner/proto/bcd.proto:47-60.
 #pragma once
 #include <iomanip>
+#include <set>
 #include "data.h"
 #include "filter.h"
 #include "monitor.h"
@@ -84,18 +85,19 @@ struct SGDProgress {
   uint64_t num_examples_processed = 0;
   uint64_t nnz = 0;
   double weight_sum = 0, delta_sum = 0;
+  uint64_t round = 0;      // lock-step device workers: push/pull rounds submitted so far
   std::string Serialize() const {
     Writer w;
     auto vec = [&w](const std::vector<double>& v) { w.U64(v.size()); for (double x : v) w.F64(x); };
     vec(objective); vec(accuracy); vec(auc);
-    w.U64(num_examples_processed); w.U64(nnz); w.F64(weight_sum); w.F64(delta_sum);
+    w.U64(num_examples_processed); w.U64(nnz); w.F64(weight_sum); w.F64(delta_sum); w.U64(round);
     return w.str();
   }
   bool Parse(const std::string& s) {
     Reader r(s.data(), s.size());
     auto vec = [&r](std::vector<double>* v) { uint64_t n = r.U64(); v->clear(); for (uint64_t i = 0; i < n && r.ok(); ++i) v->push_back(r.F64()); };
     vec(&objective); vec(&accuracy); vec(&auc);
-    num_examples_processed = r.U64(); nnz = r.U64(); weight_sum = r.F64(); delta_sum = r.F64();
+    num_examples_processed = r.U64(); nnz = r.U64(); weight_sum = r.F64(); delta_sum = r.F64(); round = r.U64();
     return r.ok();
   }
 };
@@ -133,12 +135,46 @@ class ISGDScheduler : public App {
   std::string ProgressLine(double time, std::unordered_map<NodeID, SGDProgress>* progress);
   size_t num_examples_processed() const { return num_ex_processed_; }
  protected:
-  void SendWorkload(const NodeID& recver);
+  // false when the pool had nothing to hand out
+  virtual bool SendWorkload(const NodeID& recver);
   WorkloadPool* workload_pool_ = nullptr;
   MonitorMaster<SGDProgress> monitor_;
   std::atomic<size_t> num_ex_processed_{0};
   bool show_progress_ = true;
   bool printed_header_ = false;
+};
+
+// Scheduler of workers that run their push/pull rounds in lock step (one device shard and one
+// worker per GPU: round t of every worker is aggregated at the owners, so every worker has to run
+// every round, with an empty minibatch when it has no data). Files are handed out one at a time as
+// in ISGDScheduler; in addition the scheduler grants rounds in leases: a worker may run round t
+// only while t < round_limit. Workers report their round counter with their progress, the limit
+// stays `lease` rounds ahead of the largest one reported, and when the last file is finished the
+// limit that is in force becomes final: every worker stops at exactly that round, without any
+// per-round agreement between the workers.
+class LockstepSGDScheduler : public ISGDScheduler {
+ public:
+  LockstepSGDScheduler(const Workload& load, int lease, Postoffice* po = nullptr)
+      : ISGDScheduler(po), lease_(std::max(4, lease)) {
+    pool_.set(load);
+    workload_pool_ = &pool_;
+  }
+  void Run() override;
+  uint64_t round_limit() { Lock l(lease_mu_); return limit_; }
+  WorkloadPool& pool() { return pool_; }
+ protected:
+  // remembers the workers that asked when the pool was empty: the files of a lost worker go to them
+  bool SendWorkload(const NodeID& recver) override;
+ private:
+  void Grant(bool final_round);
+  void NodeLost(const NodeID& id);
+  WorkloadPool pool_;
+  std::mutex idle_mu_;
+  std::set<NodeID> idle_;
+  const int lease_;
+  std::mutex lease_mu_;
+  uint64_t max_round_ = 0, limit_ = 0;
+  bool final_sent_ = false;
 };
 
 class ISGDCompNode : public App {

@@ -220,13 +220,19 @@ struct Workload {
 };
 
 struct SGDCall {
+  // ROUND_LIMIT is not in the reference's sgd.proto: the scheduler of lock-step device workers grants
+  // push/pull rounds in leases (round_limit = first round that may not run yet; final_round closes the job).
   enum Command { NONE = 0, REQUEST_WORKLOAD = 1, UPDATE_MODEL = 2, REPORT_PROGRESS = 3, SAVE_MODEL = 4,
-                 RECOVER = 5, COMPUTE_VALIDATION_AUC = 6 };
+                 RECOVER = 5, COMPUTE_VALIDATION_AUC = 6, ROUND_LIMIT = 7 };
   Command cmd = NONE;
   bool has_load = false;
   Workload load;
-  void Save(Writer& w) const { w.U8(cmd); w.Bool(has_load); load.Save(w); }
-  void Load(Reader& r) { cmd = (Command)r.U8(); has_load = r.Bool(); load.Load(r); }
+  int64_t round_limit = -1;
+  bool final_round = false;
+  void Save(Writer& w) const { w.U8(cmd); w.Bool(has_load); load.Save(w); w.I64(round_limit); w.Bool(final_round); }
+  void Load(Reader& r) {
+    cmd = (Command)r.U8(); has_load = r.Bool(); load.Load(r); round_limit = r.I64(); final_round = r.Bool();
+  }
 };
 
 struct BCDCall {
