@@ -6,8 +6,13 @@ Nodes are OS processes running ``bin`` (by default the in-tree ``bin/psb_linear`
 ``-my_node``, ``-scheduler``, ``-num_servers`` and ``-num_workers`` appended. Without a
 host file every node runs on this machine (127.0.0.1); with one (one host per line) the
 nodes are spread round-robin over the hosts and started through ``ssh host 'cmd'``, as
-the reference does. The job's state (node ids, hosts, ports, pids, the command) is kept
-in a JSON file so that later calls (``ls``, ``add``, ``kill``, ``stop``) find the job;
+the reference does. The job's state (node ids, hosts, ports, pids with their start
+times, the command) is kept in a JSON file inside a directory that only the user can
+enter (``$XDG_RUNTIME_DIR/psb`` or ``~/.cache/psb``, mode 0700) so that later calls
+(``ls``, ``add``, ``kill``, ``stop``) find the job. A state file that is not a regular
+file owned by the caller is refused, and a process is only ever signalled when it is
+still the one that was started (same pid *and* same start time), so a stale file or a
+recycled pid cannot direct a signal at an unrelated process;
 ``add`` registers new nodes with the running scheduler and ``kill`` ends one node's
 process, which is how elasticity and node failures are exercised.
 
@@ -32,8 +37,32 @@ from typing import Dict, List, Optional
 from .cluster import node_string
 
 
+def _private_dir() -> str:
+    """A directory only this user can enter: $XDG_RUNTIME_DIR/psb, else ~/.cache/psb (created 0700)."""
+    base = os.environ.get("XDG_RUNTIME_DIR")
+    if not base or not os.path.isdir(base) or os.stat(base).st_uid != os.getuid():
+        base = os.path.join(os.path.expanduser("~"), ".cache")
+    d = os.path.join(base, "psb")
+    os.makedirs(d, mode=0o700, exist_ok=True)
+    st = os.stat(d)
+    if st.st_uid != os.getuid():
+        raise PermissionError(f"{d} belongs to another user")
+    if st.st_mode & 0o077:
+        os.chmod(d, 0o700)
+    return d
+
+
 def default_state_path() -> str:
-    return os.environ.get("PSB_STATE", os.path.join("/tmp", f"psb-state-{os.getuid()}.json"))
+    return os.environ.get("PSB_STATE") or os.path.join(_private_dir(), "job.json")
+
+
+def _start_time(pid: int) -> Optional[int]:
+    """Start time of a process in clock ticks since boot (field 22 of /proc/<pid>/stat), None if gone."""
+    try:
+        with open(f"/proc/{pid}/stat") as f:
+            return int(f.read().rsplit(")", 1)[1].split()[19])
+    except (OSError, IndexError, ValueError):
+        return None
 
 
 def _free_port() -> int:
@@ -45,7 +74,8 @@ def _free_port() -> int:
     return p
 
 
-def _alive(pid: int) -> bool:
+def _alive(pid: int, started: Optional[int] = None) -> bool:
+    """Is the process that was started as ``pid`` (at start time ``started``, if recorded) still running?"""
     try:
         os.kill(pid, 0)
     except OSError:
@@ -53,9 +83,15 @@ def _alive(pid: int) -> bool:
     # a finished child that nobody has waited for still answers signal 0
     try:
         with open(f"/proc/{pid}/stat") as f:
-            return f.read().split(")")[-1].split()[0] != "Z"
+            if f.read().split(")")[-1].split()[0] == "Z":
+                return False
     except OSError:
         return False
+    return started is None or _start_time(pid) == started
+
+
+def _node_alive(n: Dict) -> bool:
+    return _alive(n["pid"], n.get("started"))
 
 
 class Job:
@@ -64,14 +100,20 @@ class Job:
     def __init__(self, path: Optional[str] = None):
         self.path = path or default_state_path()
         self.state: Dict = {}
-        if os.path.exists(self.path):
+        if os.path.lexists(self.path):
+            # never act on a file somebody else could have planted
+            st = os.lstat(self.path)
+            import stat as _stat
+            if not _stat.S_ISREG(st.st_mode) or st.st_uid != os.getuid():
+                raise PermissionError(f"state file {self.path} is not a regular file owned by uid {os.getuid()}")
             with open(self.path) as f:
                 self.state = json.load(f)
 
     # ------------------------------------------------------------------ helpers
     def _save(self):
-        tmp = self.path + ".tmp"
-        with open(tmp, "w") as f:
+        tmp = self.path + f".{os.getpid()}.tmp"
+        fd = os.open(tmp, os.O_WRONLY | os.O_CREAT | os.O_EXCL, 0o600)
+        with os.fdopen(fd, "w") as f:
             json.dump(self.state, f, indent=1)
         os.replace(tmp, self.path)
 
@@ -87,10 +129,12 @@ class Job:
         else:
             remote = "cd " + shlex.quote(st["cwd"]) + " && exec " + " ".join(shlex.quote(c) for c in cmd)
             # -tt: the remote process is tied to this ssh session and ends with it
-            p = subprocess.Popen(["ssh", "-tt", "-o", "StrictHostKeyChecking=no", host, remote], stdout=out,
+            # host keys are checked as the user's ssh configuration says (no override here)
+            p = subprocess.Popen(["ssh", "-tt", host, remote], stdout=out,
                                  stdin=subprocess.DEVNULL, stderr=subprocess.STDOUT, start_new_session=True)
         out.close()
-        node = {"id": node_id, "role": role, "host": host, "port": port, "pid": p.pid, "log": log}
+        node = {"id": node_id, "role": role, "host": host, "port": port, "pid": p.pid, "log": log,
+                "started": _start_time(p.pid)}
         st["nodes"].append(node)
         return node
 
@@ -104,14 +148,14 @@ class Job:
     # ------------------------------------------------------------------ commands
     def start(self, argv: List[str], num_servers: int, num_workers: int, hostfile: Optional[str] = None,
               log_dir: Optional[str] = None):
-        if self.state.get("nodes") and any(_alive(n["pid"]) for n in self.state["nodes"]):
+        if self.state.get("nodes") and any(_node_alive(n) for n in self.state["nodes"]):
             raise RuntimeError(f"a job is already running (state file {self.path}); stop it first")
         hosts = None
         if hostfile:
             with open(hostfile) as f:
                 hosts = [h.strip() for h in f if h.strip() and not h.startswith("#")]
-        log_dir = log_dir or os.path.join("/tmp", f"psb-logs-{os.getuid()}-{int(time.time())}")
-        os.makedirs(log_dir, exist_ok=True)
+        log_dir = log_dir or os.path.join(_private_dir(), f"logs-{int(time.time())}")
+        os.makedirs(log_dir, mode=0o700, exist_ok=True)
         sched_host = (hosts or ["127.0.0.1"])[0]
         sched_port = _free_port()
         self.state = {"argv": argv, "num_servers": num_servers, "num_workers": num_workers, "hosts": hosts,
@@ -128,7 +172,7 @@ class Job:
         return self.state["nodes"]
 
     def ls(self) -> List[Dict]:
-        return [dict(n, alive=_alive(n["pid"])) for n in self.state.get("nodes", [])]
+        return [dict(n, alive=_node_alive(n)) for n in self.state.get("nodes", [])]
 
     def add(self, workers: int = 0, servers: int = 0) -> List[Dict]:
         """Start more nodes; they register with the running scheduler (REGISTER_NODE)."""
@@ -149,8 +193,14 @@ class Job:
         """End one node's process (a node failure, as seen by the others)."""
         for n in self.state.get("nodes", []):
             if n["id"] == node_id:
-                # the recorded pid is the node itself (local) or its ssh session (remote node)
+                # the recorded pid is the node itself (local) or its ssh session (remote node); it leads
+                # its own session (start_new_session), so the group id is the pid. Signal it only if it
+                # is still the process that was started.
+                if not _node_alive(n):
+                    return False
                 try:
+                    if os.getpgid(n["pid"]) != n["pid"]:
+                        return False
                     os.killpg(n["pid"], sig)
                 except OSError:
                     return False
@@ -160,7 +210,7 @@ class Job:
     def wait(self, timeout: Optional[float] = None) -> bool:
         """Wait until no node is alive; True if the job ended in time."""
         t0 = time.time()
-        while any(_alive(n["pid"]) for n in self.state.get("nodes", [])):
+        while any(_node_alive(n) for n in self.state.get("nodes", [])):
             for n in self.state["nodes"]:      # reap our own finished children
                 try:
                     os.waitpid(n["pid"], os.WNOHANG)
@@ -173,14 +223,14 @@ class Job:
 
     def stop(self):
         for n in self.state.get("nodes", []):
-            if _alive(n["pid"]):
+            if _node_alive(n):
                 try:
                     self.kill(n["id"], signal.SIGTERM)
                 except (OSError, KeyError):
                     pass
         self.wait(5)
         for n in self.state.get("nodes", []):
-            if _alive(n["pid"]):
+            if _node_alive(n):
                 try:
                     self.kill(n["id"], signal.SIGKILL)
                 except (OSError, KeyError):
@@ -193,7 +243,7 @@ class Job:
 
 def main(argv: Optional[List[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="python -m parameter_server_b200.system.launch")
-    ap.add_argument("--state", default=None, help="state file (default: /tmp/psb-state-<uid>.json or $PSB_STATE)")
+    ap.add_argument("--state", default=None, help="state file (default: $PSB_STATE, else job.json in a private per-user directory)")
     sub = ap.add_subparsers(dest="cmd", required=True)
     s = sub.add_parser("start")
     s.add_argument("-ns", type=int, default=1); s.add_argument("-nw", type=int, default=1)

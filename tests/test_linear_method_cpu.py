@@ -239,3 +239,38 @@ def test_job_control_command_line(data, tmp_path, capsys):
     assert launch.main(["--state", st, "stop"]) == 0
     assert not os.path.exists(st)
     assert len(_read_model(str(tmp_path / "model_S*"))) > 10
+
+
+def test_job_state_file_is_private_and_pid_reuse_is_harmless(tmp_path, monkeypatch):
+    """The job state lives in a 0700 per-user directory; a state file that is not the caller's regular
+    file is refused; a recorded pid whose start time no longer matches is never signalled."""
+    import os
+    import subprocess
+    import sys
+    from parameter_server_b200.system import launch
+    monkeypatch.setenv("XDG_RUNTIME_DIR", str(tmp_path))
+    monkeypatch.delenv("PSB_STATE", raising=False)
+    p = launch.default_state_path()
+    assert p.startswith(str(tmp_path)) and (os.stat(os.path.dirname(p)).st_mode & 0o777) == 0o700
+    # a symlink planted at the state path is refused
+    target = tmp_path / "elsewhere.json"
+    target.write_text("{}")
+    os.symlink(target, p)
+    with pytest.raises(PermissionError):
+        launch.Job()
+    os.remove(p)
+    # a live process whose recorded start time differs (a recycled pid) counts as gone and is not signalled
+    victim = subprocess.Popen([sys.executable, "-c", "import time; time.sleep(30)"], start_new_session=True)
+    try:
+        job = launch.Job()
+        job.state = {"nodes": [{"id": "W0", "pid": victim.pid, "started": (launch._start_time(victim.pid) or 0) + 12345}]}
+        assert job.ls()[0]["alive"] is False
+        assert job.kill("W0") is False
+        job.stop()
+        assert victim.poll() is None
+        job.state = {"nodes": [{"id": "W0", "pid": victim.pid, "started": launch._start_time(victim.pid)}]}
+        assert job.ls()[0]["alive"] is True and job.kill("W0") is True
+        victim.wait(10)
+    finally:
+        if victim.poll() is None:
+            victim.kill()
