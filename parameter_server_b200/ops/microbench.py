@@ -419,6 +419,129 @@ def bench_darlin(args):
         dist.barrier(); fab.close(); dist.destroy_process_group()
 
 
+def _dist_init():
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    return dist, rank, world, dev
+
+
+def _max_over_ranks(dist, world, dev, vals):
+    t = torch.tensor(vals, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def bench_fabric(args):
+    """Peer store and peer load bandwidth of this box, per direction and per GPU: every rank copies
+    `--mb` MB to (store) and from (load) the heap of rank + d, for every distance d, with the same
+    16-byte copy kernel the dense-layer path uses. The device counterpart of the reference's raw
+    transport probe (test/network_perf_ps.cc:23-47); its result is the NVLink roofline to use.
+    With one rank it measures the local copy."""
+    from ..parameter.kv_layer import fabric_copy
+    from ..parallel.fabric import Fabric
+    dist, rank, world, dev = _dist_init()
+    nbytes = args.mb << 20
+    fab = Fabric.from_process_group(nbytes + 4096) if world > 1 else Fabric.single(nbytes + 4096, dev)
+    local = torch.empty(nbytes // 4, dtype=torch.float32, device=dev).normal_()
+    sink = torch.zeros(1, device=dev)
+    res = {}
+    for d in range(0 if world == 1 else 1, world):
+        peer = (rank + d) % world
+        for name, src, dst, mode in (("store", local.data_ptr(), fab.ptr(peer, 0), 0),
+                                     ("load", fab.ptr(peer, 0), local.data_ptr(), 0),
+                                     ("load_only", fab.ptr(peer, 0), local.data_ptr(), 1)):
+            ts = []
+            for i in range(args.iters + 2):
+                if world > 1:
+                    dist.barrier()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); fabric_copy(src, dst, nbytes, mode, sink); b.record()
+                torch.cuda.synchronize()
+                if i >= 2:
+                    ts.append(a.elapsed_time(b))
+            ts.sort()
+            ms = _max_over_ranks(dist, world, dev, [ts[len(ts) // 2]])[0]
+            res[f"{name}_d{d}"] = nbytes / 1e9 / (ms * 1e-3)
+    if rank == 0:
+        kinds = ("store", "load", "load_only")
+        out = {"kernel": "fabric copy (16-byte peer accesses)", "gpus": world, "MB": args.mb,
+               "GB_per_s_per_direction_per_gpu": {k: round(v, 1) for k, v in res.items()}}
+        for k in kinds:
+            v = [x for n, x in res.items() if n.startswith(k + "_d")]
+            if v:
+                out[f"{k}_min_over_distances"] = round(min(v), 1)
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier(); fab.close(); dist.destroy_process_group()
+
+
+def bench_layer(args):
+    """Dense layers through DeviceKVLayer: for each layer of the reference's probe
+    (AlexNet, test/kv_layer_perf_ps.cc:34-70) push + apply + pull, MB/s of layer data per worker
+    as the reference prints, the achieved NVLink rate per GPU and direction, and NCCL
+    reduce-scatter + all-gather of the same tensor for comparison. Max over ranks."""
+    from ..parameter.kv_layer import DeviceKVLayer
+    from ..parallel.fabric import Fabric
+    dist, rank, world, dev = _dist_init()
+    sizes = [11 * 11 * 96, 5 * 5 * 256, 3 * 3 * 284, 3 * 3 * 256, 43264 * 4096, 4096 * 4096, 4096 * 1000]
+    if args.small:
+        sizes = [s if s < (1 << 24) else s // 16 for s in sizes]
+    layers = dict(enumerate(sizes))
+    ring = 2
+    fab = (Fabric.from_process_group(DeviceKVLayer.heap_bytes(layers, world, ring=ring)) if world > 1
+           else Fabric.single(DeviceKVLayer.heap_bytes(layers, 1, ring=ring), dev))
+    kv = DeviceKVLayer(fab, layers, updater="add", ring=ring)
+    rows = []
+    rounds = {lid: 0 for lid in layers}
+    for lid, n in layers.items():
+        data = torch.ones(n, device=dev)
+        out = torch.empty(n, device=dev)
+        ts, tn = [], []
+        for i in range(args.iters + 2):
+            if world > 1:
+                dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            kv.push(lid, data); kv.apply(lid); rounds[lid] += 1
+            kv.pull(lid, out, wait_for_round=rounds[lid])
+            b.record()
+            torch.cuda.synchronize()
+            if i >= 2:
+                ts.append(a.elapsed_time(b))
+            if world > 1 and n % world == 0:
+                shard = torch.empty(n // world, device=dev)
+                dist.barrier()
+                a.record()
+                dist.reduce_scatter_tensor(shard, data)
+                dist.all_gather_into_tensor(out, shard)
+                b.record()
+                torch.cuda.synchronize()
+                if i >= 2:
+                    tn.append(a.elapsed_time(b))
+        kv.check_status("layer bench")
+        ts.sort(); tn.sort()
+        ms = _max_over_ranks(dist, world, dev, [ts[len(ts) // 2]])[0]
+        ms_n = _max_over_ranks(dist, world, dev, [tn[len(tn) // 2]])[0] if tn else None
+        # bytes that leave (push) and enter (pull) a GPU over NVLink: the (S-1)/S part of the layer, each way
+        link = n * 4 * (world - 1) / max(1, world)
+        rows.append({"layer": lid, "elements": n, "ms_push_apply_pull": round(ms, 4),
+                     "MB_per_s_per_worker": round(n * 4 / 1e6 / (ms * 1e-3), 1),
+                     "nvlink_GB_per_s_per_gpu_per_direction": round(2 * link / 1e9 / (ms * 1e-3) / 2, 1) if world > 1 else None,
+                     "nccl_rs_ag_ms": None if ms_n is None else round(ms_n, 4)})
+    if rank == 0:
+        tot = sum(r["ms_push_apply_pull"] for r in rows)
+        print(json.dumps({"kernel": "kv layer push + apply + pull", "gpus": world, "layers": rows,
+                          "all_layers_MB_per_s_per_worker": round(sum(sizes) * 4 / 1e6 / (tot * 1e-3), 1)}))
+    if world > 1:
+        dist.barrier(); fab.close(); dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -440,13 +563,16 @@ def main():
     s = sub.add_parser("kv"); s.add_argument("--sizes", type=int, nargs="+", default=[1000, 100000, 1000000, 16000000])
     s.add_argument("--iters", type=int, default=5); s.add_argument("--quant", default="none", choices=["none", "int8", "fp16"])
     s.add_argument("--one-sided", action="store_true", help="pull with remote probes instead of the exchange kernel")
+    s = sub.add_parser("fabric"); s.add_argument("--mb", type=int, default=256); s.add_argument("--iters", type=int, default=5)
+    s = sub.add_parser("layer"); s.add_argument("--iters", type=int, default=5)
+    s.add_argument("--small", action="store_true", help="shrink the two largest layers 16x (quick runs)")
     args = ap.parse_args()
     import sys
     sys.path.insert(0, os.fspath(Path(__file__).resolve().parents[2]))
     from .. import _build
     _build.build_cuda()
     {"sort": bench_sort, "step": bench_step, "wide": bench_wide, "wide-step": bench_wide_step, "kv": bench_kv,
-     "darlin": bench_darlin}[args.cmd](args)
+     "darlin": bench_darlin, "fabric": bench_fabric, "layer": bench_layer}[args.cmd](args)
 
 
 if __name__ == "__main__":

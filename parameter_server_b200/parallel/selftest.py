@@ -100,10 +100,16 @@ def main():
         frac_keys = len(common) / max(1, len(exp))
         a = np.array([got[k] for k in common]); b = np.array([exp[k] for k in common])
         # with tau > 0 pulls may legitimately see a model that is up to tau rounds old
-        tol = 2e-3 if args.tau == 0 else 0.25
+        exact = args.tau == 0 and args.quant == "none"
+        tol = 2e-4 if exact else (2e-3 if args.tau == 0 else 0.25)
         close = float(np.isclose(a, b, rtol=tol, atol=tol * 0.1).mean()) if len(a) else 0.0
-        print(f"keys matched {frac_keys:.4f} values close {close:.4f} (n={len(exp)})")
-        ok = frac_keys > 0.9 and close > 0.9
+        print(f"keys matched {frac_keys:.4f} values close {close:.4f} (n={len(exp)}, extra keys {len(got) - len(common)})")
+        if args.tau == 0:
+            # the aggregation per round does not depend on arrival order: every key, and all but rounding
+            # (a weight that rounding puts on the other side of the L1 threshold may appear or vanish)
+            ok = frac_keys >= 0.999 and abs(len(got) - len(exp)) <= max(2, len(exp) // 1000) and close >= 0.999
+        else:
+            ok = frac_keys > 0.9 and close > 0.9
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.broadcast(flag, 0)
     dist.barrier()

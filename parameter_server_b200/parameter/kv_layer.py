@@ -21,8 +21,9 @@ _vp, _u32, _u64, _i32, _f32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int, C.c_f
 
 
 class _Push(C.Structure):
-    _fields_ = [("S", _i32), ("ts1", _u32), ("data", _vp), ("seg_begin", _u64 * (MAX_SHARDS + 1)),
-                ("inbox", _vp * MAX_SHARDS), ("ready", _vp * MAX_SHARDS), ("done", _vp)]
+    _fields_ = [("S", _i32), ("ts1", _u32), ("need_applied", _u32), ("wait_iters", _u32), ("data", _vp),
+                ("seg_begin", _u64 * (MAX_SHARDS + 1)), ("inbox", _vp * MAX_SHARDS), ("ready", _vp * MAX_SHARDS),
+                ("applied", _vp * MAX_SHARDS), ("done", _vp), ("status", _vp)]
 
 
 class _Apply(C.Structure):
@@ -43,6 +44,7 @@ def _declare():
     for name in ("psb_layer_push", "psb_layer_apply", "psb_layer_pull"):
         getattr(L, name).argtypes = [_vp, _vp]
     L.psb_layer_args_size.argtypes = [_i32]
+    L.psb_fabric_copy.argtypes = [_vp, _vp, _u64, _i32, _vp, _vp]
     for i, st in enumerate((_Push, _Apply, _Pull)):
         if L.psb_layer_args_size(i) != C.sizeof(st):
             raise RuntimeError(f"{st.__name__}: binding is {C.sizeof(st)} bytes, library expects {L.psb_layer_args_size(i)}")
@@ -53,90 +55,128 @@ def _declare():
 UPDATERS = {"assign": 0, "add": 1, "sgd": 2}
 
 
+def _up4(x: int) -> int:
+    return (x + 3) // 4 * 4
+
+
 class DeviceKVLayer:
     """All layers are declared up front (``layers``: {id: number of elements}) so
-    that every rank computes the same heap layout."""
+    that every rank computes the same heap layout.
+
+    Per layer the heap holds the owned segment, a ring of ``ring`` inbox slots per
+    source (round ``t`` uses slot ``t % ring``) and the flag words: the owner's
+    ``applied`` counter and one ``ready`` flag per (slot, source). A push of round
+    ``t`` waits on the device, bounded, until every owner has applied round
+    ``t - ring`` (the round that last used the slot), so a fast worker can run at
+    most ``ring`` rounds ahead of a slow owner and never overwrites data that is
+    still being summed. Arrival counters are per layer: layers may be pushed and
+    applied on different streams.
+
+    ``apply`` of a round waits on the device only for *other* ranks' pushes: this
+    rank's own push of the round is ordered before it by a CUDA event (two kernels
+    of one GPU never wait for one another on the device).
+    """
 
     def __init__(self, fabric: Fabric, layers: Dict[int, int], partition_thr: int = 1000, updater: str = "add",
-                 lr: float = 0.1):
+                 lr: float = 0.1, ring: int = 2):
         self.L = _declare()
         self.fabric = fabric
         self.rank, self.S = fabric.rank, fabric.world
-        self.updater, self.lr, self.thr = UPDATERS[updater], lr, partition_thr
+        self.updater, self.lr, self.thr, self.ring = UPDATERS[updater], lr, partition_thr, max(1, ring)
         self.layers = dict(layers)
         lay = HeapLayout()
         self.meta = {}
         for i, (lid, n) in enumerate(sorted(layers.items())):
             seg = self.segments(lid, n)
-            mx = max(seg[s + 1] - seg[s] for s in range(self.S))
-            self.meta[lid] = dict(idx=i, n=n, seg=seg, cap=mx,
-                                  data=lay.add(f"data{lid}", max(mx, 1) * 4),
-                                  inbox=lay.add(f"inbox{lid}", self.S * max(mx, 1) * 4),
-                                  flags=lay.add(f"flags{lid}", 4 * (self.S + 2)), ts=0)
+            cap = max(4, _up4(max(seg[s + 1] - seg[s] for s in range(self.S))))
+            self.meta[lid] = dict(idx=i, n=n, seg=seg, cap=cap,
+                                  data=lay.add(f"data{lid}", cap * 4),
+                                  inbox=lay.add(f"inbox{lid}", self.ring * self.S * cap * 4),
+                                  flags=lay.add(f"flags{lid}", 4 * (1 + self.ring * self.S)),
+                                  push_ts=0, apply_ts=0, pushed=None)
         self.lay = lay
         assert lay.total() <= fabric.heap_bytes, "heap too small"
         dev = fabric.device
-        self.sync = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.sync = torch.zeros(4 * max(1, len(layers)), dtype=torch.int32, device=dev)   # per layer: push, apply arrivals
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
 
     @staticmethod
-    def heap_bytes(layers: Dict[int, int], world: int, partition_thr: int = 1000) -> int:
+    def heap_bytes(layers: Dict[int, int], world: int, partition_thr: int = 1000, ring: int = 2) -> int:
         total = 0
         for lid, n in layers.items():
-            mx = n if n < partition_thr else (n + world - 1) // world + 1
-            total += (mx * 4 + 256) * (world + 1) + 4 * (world + 2) + 512
+            mx = _up4(n) if n < partition_thr else _up4((n + world - 1) // world) + 8
+            total += (mx * 4 + 256) * (ring * world + 1) + 4 * (ring * world + 2) + 512
         return total + 4096
 
     def segments(self, lid: int, n: int) -> List[int]:
-        """Element boundaries of the shards for layer ``lid``."""
+        """Element boundaries of the shards for layer ``lid`` (multiples of four elements, so that every
+        slice starts on a 16-byte boundary)."""
         S = self.S
         if n < self.thr:
             owner = (lid * 991) % S
             return [0 if s <= owner else n for s in range(S + 1)]
-        return [n * s // S for s in range(S)] + [n]
+        return [(n * s // S) // 4 * 4 for s in range(S)] + [n]
 
     def _p(self, rank, off):
         return self.fabric.ptr(rank, off)
 
-    def push(self, lid: int, data: torch.Tensor, stream=None) -> int:
+    def _inbox(self, m, owner: int, q: int, src: int) -> int:
+        return self._p(owner, m["inbox"] + ((q * self.S + src) * m["cap"]) * 4)
+
+    def _ready(self, m, owner: int, q: int, src: int) -> int:
+        return self._p(owner, m["flags"] + 4 * (1 + q * self.S + src))
+
+    def push(self, lid: int, data: torch.Tensor, wait_iters: int = 0, stream=None) -> int:
+        """Worker side of the layer's next round: returns its timestamp."""
         m = self.meta[lid]
         assert data.numel() == m["n"] and data.dtype == torch.float32 and data.is_contiguous()
-        ts = m["ts"]
+        ts = m["push_ts"]
+        m["push_ts"] += 1
+        q = ts % self.ring
         a = _Push()
         a.S, a.ts1, a.data = self.S, ts + 1, ptr(data)
+        a.need_applied, a.wait_iters = max(0, ts + 1 - self.ring), wait_iters
         for s in range(self.S + 1):
             a.seg_begin[s] = m["seg"][s]
         for s in range(self.S):
-            a.inbox[s] = self._p(s, m["inbox"] + self.rank * max(m["cap"], 1) * 4)
-            a.ready[s] = self._p(s, m["flags"] + 4 * (2 + self.rank))
-        a.done = self.sync.data_ptr()
+            a.inbox[s] = self._inbox(m, s, q, self.rank)
+            a.ready[s] = self._ready(m, s, q, self.rank)
+            a.applied[s] = self._p(s, m["flags"])
+        a.done, a.status = self.sync.data_ptr() + 16 * m["idx"], ptr(self.status)
         check(self.L.psb_layer_push(C.byref(a), stream_ptr(stream)), "layer_push")
+        ev = m["pushed"] = m["pushed"] or torch.cuda.Event()
+        ev.record(stream if stream is not None else torch.cuda.current_stream())
         return ts
 
     def apply(self, lid: int, alive=None, wait_iters: int = 0, stream=None):
-        """Owner side of push round ``ts`` of this layer (every rank calls it)."""
+        """Owner side of the layer's next unapplied round (every rank calls it once per round)."""
         m = self.meta[lid]
-        ts = m["ts"]
-        m["ts"] += 1
+        ts = m["apply_ts"]
+        m["apply_ts"] += 1
+        q = ts % self.ring
         n = m["seg"][self.rank + 1] - m["seg"][self.rank]
+        st = stream if stream is not None else torch.cuda.current_stream()
+        if m["pushed"] is not None:
+            st.wait_event(m["pushed"])          # this rank's own push: ordered by the stream, not by a device wait
         a = _Apply()
         a.S, a.ts1, a.updater, a.lr, a.n = self.S, ts + 1, self.updater, self.lr, n
         a.data = self._p(self.rank, m["data"])
         for r in range(self.S):
-            a.inbox[r] = self._p(self.rank, m["inbox"] + r * max(m["cap"], 1) * 4)
-            a.ready[r] = self._p(self.rank, m["flags"] + 4 * (2 + r))
+            a.inbox[r] = self._inbox(m, self.rank, q, r)
+            a.ready[r] = self._ready(m, self.rank, q, r)
             a.alive[r] = 1 if (alive is None or alive[r]) else 0
         a.wait_iters = wait_iters
-        a.applied, a.done, a.status = self._p(self.rank, m["flags"]), self.sync.data_ptr() + 8, ptr(self.status)
+        a.applied, a.done, a.status = self._p(self.rank, m["flags"]), self.sync.data_ptr() + 16 * m["idx"] + 8, ptr(self.status)
         check(self.L.psb_layer_apply(C.byref(a), stream_ptr(stream)), "layer_apply")
 
-    def pull(self, lid: int, out: torch.Tensor, wait_for_round: int = 0, stream=None):
+    def pull(self, lid: int, out: torch.Tensor, wait_for_round: int = 0, wait_iters: int = 0, stream=None):
         """Gather the layer from its owners into ``out``; waits until the owners
         have applied ``wait_for_round`` pushes."""
         m = self.meta[lid]
         assert out.numel() == m["n"] and out.dtype == torch.float32 and out.is_contiguous()
         a = _Pull()
         a.S, a.need_applied, a.out = self.S, wait_for_round, ptr(out)
+        a.wait_iters = wait_iters
         for s in range(self.S + 1):
             a.seg_begin[s] = m["seg"][s]
         for s in range(self.S):
@@ -153,3 +193,10 @@ class DeviceKVLayer:
 
     def check_status(self, what="kv layer"):
         _lib.check_status(self.status, what)
+
+
+def fabric_copy(src_ptr: int, dst_ptr: int, nbytes: int, mode: int = 0, sink=None, stream=None):
+    """16-byte copy kernel between two device addresses, either of which may be a peer's memory
+    (mode 0: copy; mode 1: read-only pass over ``src``)."""
+    L = _declare()
+    check(L.psb_fabric_copy(src_ptr, dst_ptr, nbytes, mode, ptr(sink), stream_ptr(stream)), "fabric_copy")

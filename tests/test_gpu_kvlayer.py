@@ -35,4 +35,36 @@ def test_kvlayer_push_pull(cuda_lib, S, updater):
     sizes = [len(k.segment(7)) for k in kv]
     assert sorted(sizes)[-1] == 999 and sum(sizes) == 999 and sizes[(7 * 991) % S] == 999
     big = [len(k.segment(2)) for k in kv]
-    assert sum(big) == 100_003 and max(big) - min(big) <= 1
+    assert sum(big) == 100_003 and max(big) - min(big) <= 7     # boundaries are multiples of four elements
+
+
+def test_kvlayer_ring_bounds_a_fast_worker(cuda_lib):
+    """Two emulated ranks, ring of two slots: worker 0 may push rounds 0 and 1 before anybody applies;
+    its push of round 2 would overwrite the slot of round 0, so it waits for the owner's applied
+    counter and, with a short budget and nobody applying, reports a timeout instead of overwriting."""
+    from parameter_server_b200.ops._lib import PsbCudaError
+    from parameter_server_b200.parallel.fabric import Fabric
+    from parameter_server_b200.parameter.kv_layer import DeviceKVLayer
+    layers = {0: 4096}
+    fabs = Fabric.emulated(2, DeviceKVLayer.heap_bytes(layers, 2))
+    kv = [DeviceKVLayer(f, layers, updater="add", ring=2) for f in fabs]
+    g = [torch.full((4096,), float(r + 1), device="cuda") for r in range(2)]
+    for rnd in range(2):
+        for r in range(2):
+            kv[r].push(0, g[r] * (rnd + 1))
+    torch.cuda.synchronize()
+    kv[0].check_status(); kv[1].check_status()
+    kv[0].push(0, g[0] * 100, wait_iters=2000)      # round 2: slot of round 0 is not applied yet
+    torch.cuda.synchronize()
+    with pytest.raises(PsbCudaError):
+        kv[0].check_status()
+    # the owners now apply rounds 0 and 1: each sums exactly that round's data
+    for rnd in range(2):
+        for r in range(2):
+            kv[r].apply(0)
+    out = torch.zeros(4096, device="cuda")
+    kv[1].pull(0, out, wait_for_round=2)
+    torch.cuda.synchronize()
+    kv[1].check_status()
+    # the push that timed out touched nothing: rounds 0 and 1 of both workers sum to (1 + 2) * (1 + 2)
+    assert torch.equal(out, torch.full_like(out, 9.0))

@@ -32,6 +32,23 @@ def test_two_rank_training_matches_oracle(cuda_lib, quant, pull, tau):
     assert "SELFTEST OK" in r.stdout
 
 
+@pytest.mark.parametrize("what", ["layer", "kv", "darlin", "wide"])
+def test_other_planes_over_real_peers(cuda_lib, what):
+    """KVLayer (back-to-back rounds, no host barrier), the KV containers, Darlin and the wide-value
+    exchange pull (single cooperative launch, all roles) over real peer mappings."""
+    n = min(torch.cuda.device_count(), 4)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=root)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", "29751", "-m",
+           "parameter_server_b200.parallel.selftest_peers", "--what", what]
+    r = subprocess.run(cmd, env=env, cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "SELFTEST OK" in r.stdout
+
+
 APP_CONF = """
 training_data {{ format: TEXT text: SPARSE_BINARY file: "{train}/part.*" }}
 model_output {{ format: TEXT file: "{out}/model" }}
