@@ -69,7 +69,7 @@ void BindUtil(py::module& m) {
       .def("decode", [](RemoteNode& r, Message& msg) { r.DecodeMessage(&msg); })
       .def("set_fixing_float_seed", [](RemoteNode& r, unsigned seed) {
         FilterConfig c; c.type = FilterConfig::FIXING_FLOAT;
-        static_cast<FixingFloatFilter*>(r.FindFilterOrCreate(c))->set_seed(seed);
+        static_cast<FixingFloatFilter*>(r.FilterFor(c))->set_seed(seed);
       });
   m.def("sparse_filter_mark", []() { SparseFilter f; float v = 0; f.mark(&v); return v; });
 

@@ -337,36 +337,51 @@ class DarlinServer : public DarlinCompNode {
     }
   }
  private:
+  // One coordinate of the block: g is the summed gradient, u the summed curvature bound. The
+  // objective along the coordinate is bounded by the quadratic g d + (u / (2 eta)) d^2 + lambda |w + d|,
+  // whose minimiser is a soft threshold in the variable w + d; the step is then clipped to the
+  // coordinate's trust region, which is re-sized from the step taken (darlin.h:261-304).
+  struct CoordinateStep {
+    Real step = 0, violation = 0;
+    bool frozen = false;           // KKT filter: a zero weight far inside the subdifferential
+  };
+  static CoordinateStep SolveCoordinate(Real w, Real g, Real curvature, Real lambda, Real kkt_threshold) {
+    CoordinateStep out;
+    const Real up = g + lambda, down = g - lambda;      // one-sided derivatives at w = 0 (right, left)
+    if (w == 0) {
+      if (up < 0) out.violation = -up;
+      else if (down > 0) out.violation = down;
+      else if (up > kkt_threshold && down < -kkt_threshold) { out.frozen = true; return out; }
+    }
+    const Real cw = curvature * w;
+    if (up <= cw) out.step = -up / curvature;            // the minimiser stays positive
+    else if (down >= cw) out.step = -down / curvature;   // ... stays negative
+    else out.step = -w;                                   // ... is zero
+    return out;
+  }
   void UpdateWeight(int grp, SizeR range, const SArray<Real>& G, const SArray<Real>& U) {
     const Real eta = (Real)conf_.learning_rate.alpha;
     const Real lambda = (Real)conf_.penalty.lambda[0];
-    const Real delta_max = (Real)bcd_.delta_max_value;
-    auto& value = model_[grp].value;
+    const Real widest = (Real)bcd_.delta_max_value;
+    SArray<Real>& weights = model_[grp].value;
+    SArray<Real>& radius = delta_[grp];
     auto& active = active_set_[grp];
-    auto& delta = delta_[grp];
+    const size_t first = range.begin();
     for (size_t i = 0; i < range.size(); ++i) {
-      size_t k = i + range.begin();
-      if (!active.test((uint32_t)k)) continue;
-      Real g = G[i], u = U[i] / eta + (Real)1e-10;
-      Real g_pos = g + lambda, g_neg = g - lambda;
-      Real& w = value[k];
-      Real d = -w, vio = 0;
-      if (w == 0) {
-        if (g_pos < 0) vio = -g_pos;
-        else if (g_neg > 0) vio = g_neg;
-        else if (g_pos > kkt_filter_threshold_ && g_neg < -kkt_filter_threshold_) {
-          // well inside the subdifferential: freeze this coordinate
-          active.clear((uint32_t)k);
-          kkt_filter_.mark(&w);
-          continue;
-        }
+      const uint32_t col = (uint32_t)(first + i);
+      if (!active.test(col)) continue;
+      const CoordinateStep cs = SolveCoordinate(weights[col], G[i], U[i] / eta + (Real)1e-10, lambda,
+                                                (Real)kkt_filter_threshold_);
+      if (cs.frozen) {
+        active.clear(col);
+        kkt_filter_.mark(&weights[col]);
+        continue;
       }
-      violation_ = std::max(violation_, vio);
-      if (g_pos <= u * w) d = -g_pos / u;
-      else if (g_neg >= u * w) d = -g_neg / u;
-      d = std::min(delta[k], std::max(-delta[k], d));
-      delta[k] = TrustDelta(delta_max, d);
-      w += d;
+      if (cs.violation > violation_) violation_ = cs.violation;
+      const Real r = radius[col];
+      const Real d = cs.step > r ? r : (cs.step < -r ? -r : cs.step);
+      radius[col] = TrustDelta(widest, d);
+      weights[col] += d;
     }
   }
   Real violation_ = 0;

@@ -28,57 +28,70 @@ class Filter {
   static FilterConfig* find(FilterConfig::Type type, Message* msg) { return find(type, &msg->task); }
 };
 
-// Sender: if the key list of (channel, key range) has the signature and size of
-// the one sent last time, drop the keys and send only the signature. Receiver:
-// remember the last key list per (channel, key range); re-attach on a hit.
+// Key caching. One remembered key list per (key channel, key range) of a peer.
+//   sending:   the list's signature always travels in the filter header; when the remembered list of
+//              the slot has the same signature and byte length (and is not empty) the keys themselves
+//              are left out of the message, otherwise the slot remembers the new list.
+//   receiving: a message with keys refreshes the slot; one without takes the slot's keys back in.
+// The signature is crc32c over the first kSignedBytes bytes of the list. With clear_cache_if_done
+// a slot is dropped once the exchange it served is over (a response, or a push request).
 class KeyCachingFilter : public Filter {
  public:
+  static constexpr size_t kSignedBytes = 2048;
+
   void encode(Message* msg) override {
-    auto conf = find(FilterConfig::KEY_CACHING, msg);
-    if (!conf) return;
-    if (!msg->task.has_key) { conf->has_signature = false; return; }
-    const auto& key = msg->key;
-    uint32_t sig = crc32c::Value(key.data(), std::min(key.size(), max_sig_len_));
-    conf->signature = sig;
-    conf->has_signature = true;
-    auto cache_k = std::make_pair(msg->task.key_channel, msg->task.key_range);
+    FilterConfig* hdr = find(FilterConfig::KEY_CACHING, msg);
+    if (hdr == nullptr) return;
+    hdr->has_signature = msg->task.has_key;
+    if (!msg->task.has_key) return;
+    hdr->signature = Signature(msg->key);
     Lock l(mu_);
-    auto& cache = cache_[cache_k];
-    bool hit = cache.first == sig && cache.second.size() == key.size() && !key.empty();
-    if (hit) {
-      msg->clear_key();
-    } else {
-      cache.first = sig;
-      cache.second = key;
-    }
-    if (conf->clear_cache_if_done && is_done(msg->task)) cache_.erase(cache_k);
+    const SlotId id = IdOf(msg->task);
+    Slot& slot = slots_[id];
+    if (!msg->key.empty() && slot.Matches(hdr->signature, msg->key.size())) msg->clear_key();
+    else slot.Remember(hdr->signature, msg->key);
+    Retire(*hdr, msg->task, id);
   }
+
   void decode(Message* msg) override {
-    auto conf = find(FilterConfig::KEY_CACHING, msg);
-    if (!conf || !conf->has_signature) return;
-    uint32_t sig = conf->signature;
-    auto cache_k = std::make_pair(msg->task.key_channel, msg->task.key_range);
+    FilterConfig* hdr = find(FilterConfig::KEY_CACHING, msg);
+    if (hdr == nullptr || !hdr->has_signature) return;
     Lock l(mu_);
-    auto& cache = cache_[cache_k];
+    const SlotId id = IdOf(msg->task);
+    Slot& slot = slots_[id];
     if (msg->task.has_key) {
-      PS_CHECK_EQ(crc32c::Value(msg->key.data(), std::min(msg->key.size(), max_sig_len_)), sig);
-      cache.first = sig;
-      cache.second = msg->key;
+      PS_CHECK_EQ(Signature(msg->key), hdr->signature);
+      slot.Remember(hdr->signature, msg->key);
     } else {
-      PS_CHECK_EQ(sig, cache.first) << "key cache miss on " << msg->ShortDebugString();
-      msg->key = cache.second;
+      PS_CHECK_EQ(hdr->signature, slot.signature) << "key cache miss on " << msg->ShortDebugString();
+      msg->key = slot.keys;
       msg->task.has_key = true;
     }
-    if (conf->clear_cache_if_done && is_done(msg->task)) cache_.erase(cache_k);
+    Retire(*hdr, msg->task, id);
   }
-  size_t cache_entries() const { return cache_.size(); }
+
+  size_t cache_entries() const { return slots_.size(); }
+
  private:
-  static bool is_done(const Task& t) { return !t.request || (t.has_param && t.param.push); }
-  struct KeyHash {
-    size_t operator()(const std::pair<int, Range<Key>>& k) const { return k.first * 7919u ^ k.second.Hash(); }
+  typedef std::pair<int, Range<Key>> SlotId;
+  struct Slot {
+    uint32_t signature = 0;
+    SArray<char> keys;
+    bool Matches(uint32_t sig, size_t bytes) const { return signature == sig && keys.size() == bytes; }
+    void Remember(uint32_t sig, const SArray<char>& k) { signature = sig; keys = k; }
   };
-  std::unordered_map<std::pair<int, Range<Key>>, std::pair<uint32_t, SArray<char>>, KeyHash> cache_;
-  const size_t max_sig_len_ = 2048;  // only the head of the key list is hashed
+  struct SlotIdHash {
+    size_t operator()(const SlotId& k) const { return k.first * 7919u ^ k.second.Hash(); }
+  };
+  static uint32_t Signature(const SArray<char>& keys) {
+    return crc32c::Value(keys.data(), keys.size() < kSignedBytes ? keys.size() : kSignedBytes);
+  }
+  static SlotId IdOf(const Task& t) { return SlotId(t.key_channel, t.key_range); }
+  void Retire(const FilterConfig& hdr, const Task& t, const SlotId& id) {
+    const bool exchange_over = !t.request || (t.has_param && t.param.push);
+    if (hdr.clear_cache_if_done && exchange_over) slots_.erase(id);
+  }
+  std::unordered_map<SlotId, Slot, SlotIdHash> slots_;
   std::mutex mu_;
 };
 

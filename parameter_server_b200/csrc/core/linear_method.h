@@ -186,54 +186,59 @@ struct SGDState {
   MonitorSlaver<SGDProgress>* reporter = nullptr;
 };
 
-// FTRL-proximal: per key (w, z, sqrt_n)
-template <typename V>
-struct FTRLEntry {
-  V w = 0, z = 0, sqrt_n = 0;
-  void Set(const V* data, void* state) {
-    auto* st = static_cast<SGDState<V>*>(state);
-    V w_old = w, g = *data;
-    V sqrt_n_new = std::sqrt(sqrt_n * sqrt_n + g * g);
-    V sigma = (sqrt_n_new - sqrt_n) / st->lr->alpha();
-    z += g - sigma * w;
-    sqrt_n = sqrt_n_new;
-    V eta = st->lr->eval(sqrt_n);
-    w = st->h->proximal(-z * eta, eta);
-    st->UpdateWeight(w, w_old);
-  }
-  void Get(V* data, void*) { *data = w; }
-};
+// The per-key update rules of the server. An entry is three numbers (the weight and two rule
+// specific accumulators) plus a rule; the step functions below are the same arithmetic, in the same
+// order of operations, as the device table's opt_step (csrc/cuda/table.cu), so the CPU application
+// can serve as the oracle of the GPU one.
+//   FTRL-proximal (McMahan et al.): acc0 = z, acc1 = sqrt(n);  sigma = (sqrt(n + g^2) - sqrt(n)) / alpha,
+//       z += g - sigma * w,  w = prox(-z * eta, eta) with eta = lr(sqrt(n))
+//   AdaGrad:  acc0 = sum of g^2;  w = prox(w - eta * g, eta) with eta = lr(sqrt(acc0))
+//   SGD:      acc0 = number of updates of the key;  w = prox(w - eta * g, eta) with eta = lr(sqrt(acc0))
+enum class UpdateRule { kFtrl, kAdaGrad, kSgd };
 
-// AdaGrad: per key (weight, sum of squared gradients)
 template <typename V>
-struct AdaGradEntry {
-  V weight = 0, sum_sq_grad = 0;
-  void Set(const V* data, void* state) {
-    auto* st = static_cast<SGDState<V>*>(state);
-    V g = *data;
-    sum_sq_grad += g * g;
-    V eta = st->lr->eval(std::sqrt(sum_sq_grad));
-    V w_old = weight;
-    weight = st->h->proximal(weight - eta * g, eta);
-    st->UpdateWeight(weight, w_old);
-  }
-  void Get(V* data, void*) { *data = weight; }
-};
+struct EntryCells { V w = 0, acc0 = 0, acc1 = 0; };
 
-// plain proximal SGD with eta = lr(sqrt(#updates of the key))
 template <typename V>
-struct SGDEntry {
-  V weight = 0, count = 0;
-  void Set(const V* data, void* state) {
+inline void StepFtrl(EntryCells<V>* e, V g, LearningRate<V>& lr, Penalty<V>& h) {
+  const V root_after = std::sqrt(e->acc1 * e->acc1 + g * g);
+  e->acc0 += g - (root_after - e->acc1) / lr.alpha() * e->w;
+  e->acc1 = root_after;
+  const V eta = lr.eval(root_after);
+  e->w = h.proximal(-e->acc0 * eta, eta);
+}
+template <typename V>
+inline void StepAdaGrad(EntryCells<V>* e, V g, LearningRate<V>& lr, Penalty<V>& h) {
+  e->acc0 += g * g;
+  const V eta = lr.eval(std::sqrt(e->acc0));
+  e->w = h.proximal(e->w - eta * g, eta);
+}
+template <typename V>
+inline void StepSgd(EntryCells<V>* e, V g, LearningRate<V>& lr, Penalty<V>& h) {
+  e->acc0 += 1;
+  const V eta = lr.eval(std::sqrt(e->acc0));
+  e->w = h.proximal(e->w - eta * g, eta);
+}
+
+// KVMap entry (Get / Set as parameter/kv_map.h:43-59 asks for) applying one rule.
+template <typename V, UpdateRule R>
+struct RuleEntry {
+  EntryCells<V> cells;
+  void Set(const V* grad, void* state) {
     auto* st = static_cast<SGDState<V>*>(state);
-    count += 1;
-    V eta = st->lr->eval(std::sqrt(count));
-    V w_old = weight;
-    weight = st->h->proximal(weight - eta * *data, eta);
-    st->UpdateWeight(weight, w_old);
+    const V before = cells.w;
+    switch (R) {
+      case UpdateRule::kFtrl: StepFtrl(&cells, *grad, *st->lr, *st->h); break;
+      case UpdateRule::kAdaGrad: StepAdaGrad(&cells, *grad, *st->lr, *st->h); break;
+      case UpdateRule::kSgd: StepSgd(&cells, *grad, *st->lr, *st->h); break;
+    }
+    st->UpdateWeight(cells.w, before);
   }
-  void Get(V* data, void*) { *data = weight; }
+  void Get(V* out, void*) { *out = cells.w; }
 };
+template <typename V> using FTRLEntry = RuleEntry<V, UpdateRule::kFtrl>;
+template <typename V> using AdaGradEntry = RuleEntry<V, UpdateRule::kAdaGrad>;
+template <typename V> using SGDEntry = RuleEntry<V, UpdateRule::kSgd>;
 
 static const int kModelCustomerID = 20;
 

@@ -3,61 +3,69 @@
 // peer's own filter instances (so key-cache state is per peer).
 // Counterpart of system/remote_node.h:13-65, system/remote_node.cc:7-56.
 #pragma once
+#include <memory>
 #include "filter.h"
 
 namespace PS {
 
-// Tracks which integer timestamps are finished.
+// Which integer timestamps are finished: a bit set in 64-bit words that grows on demand. A timestamp
+// that was never started counts as unfinished; negative ones (no dependency) as finished.
 class RequestTracker {
  public:
-  void Start(int ts) { Set(ts, false); }
-  void Finish(int ts) { Set(ts, true); }
-  bool IsFinished(int ts) const { return ts < 0 || ((int)data_.size() > ts && data_[ts]); }
- private:
-  void Set(int ts, bool v) {
-    PS_CHECK_GE(ts, 0);
-    PS_CHECK_LT(ts, 100000000);
-    if ((int)data_.size() <= ts) data_.resize(ts * 2 + 5, false);
-    data_[ts] = v;
+  static constexpr int kMaxTimestamp = 100000000;
+  void Start(int ts) { Word(ts) &= ~Bit(ts); }
+  void Finish(int ts) { Word(ts) |= Bit(ts); }
+  bool IsFinished(int ts) const {
+    if (ts < 0) return true;
+    const size_t w = (size_t)ts >> 6;
+    return w < words_.size() && (words_[w] & Bit(ts)) != 0;
   }
-  std::vector<bool> data_;
+ private:
+  static uint64_t Bit(int ts) { return 1ull << (ts & 63); }
+  uint64_t& Word(int ts) {
+    PS_CHECK_GE(ts, 0);
+    PS_CHECK_LT(ts, kMaxTimestamp);
+    const size_t w = (size_t)ts >> 6;
+    if (w >= words_.size()) words_.resize(w + w / 2 + 4, 0);
+    return words_[w];
+  }
+  std::vector<uint64_t> words_;
 };
 
 struct RemoteNode {
-  RemoteNode() {}
-  ~RemoteNode() { for (auto& f : filters) delete f.second; }
+  // a message passes the filters named in its header in order when it leaves, in reverse when it arrives
   void EncodeMessage(Message* msg) {
-    for (auto& conf : msg->task.filter) FindFilterOrCreate(conf)->encode(msg);
+    for (const FilterConfig& conf : msg->task.filter) FilterFor(conf)->encode(msg);
   }
   void DecodeMessage(Message* msg) {
-    // reverse order of encoding
-    for (int i = (int)msg->task.filter.size() - 1; i >= 0; --i) FindFilterOrCreate(msg->task.filter[i])->decode(msg);
+    const auto& chain = msg->task.filter;
+    for (auto it = chain.rbegin(); it != chain.rend(); ++it) FilterFor(*it)->decode(msg);
   }
-  Filter* FindFilterOrCreate(const FilterConfig& conf) {
-    auto it = filters.find((int)conf.type);
-    if (it == filters.end()) it = filters.emplace((int)conf.type, Filter::create(conf)).first;
-    return it->second;
+  // this peer's instance of a filter type, made on first use
+  Filter* FilterFor(const FilterConfig& conf) {
+    std::unique_ptr<Filter>& f = filters[(int)conf.type];
+    if (!f) f.reset(Filter::create(conf));
+    return f.get();
   }
-  // group bookkeeping; members stay ordered by key range
-  void AddGroupNode(RemoteNode* rnode) {
-    PS_CHECK(rnode != nullptr);
-    size_t pos = 0;
-    Range<Key> kr(rnode->node.key);
-    while (pos < group.size()) {
-      if (kr.InLeft(Range<Key>(group[pos]->node.key))) break;
-      ++pos;
-    }
-    group.insert(group.begin() + pos, rnode);
-    keys.insert(keys.begin() + pos, kr);
+  void ClearFilters() { filters.clear(); }
+
+  // Group bookkeeping (this entry stands for a group id): members and their key ranges, kept in key
+  // order so that a sliced message lines up with the members.
+  void AddGroupNode(RemoteNode* member) {
+    PS_CHECK(member != nullptr);
+    const Range<Key> kr(member->node.key);
+    size_t at = 0;
+    while (at < group.size() && !kr.InLeft(Range<Key>(group[at]->node.key))) ++at;
+    group.insert(group.begin() + at, member);
+    keys.insert(keys.begin() + at, kr);
   }
-  void RemoveGroupNode(RemoteNode* rnode) {
-    size_t n = group.size();
-    PS_CHECK_EQ(n, keys.size());
-    for (size_t i = 0; i < n; ++i) {
-      if (group[i] == rnode) { group.erase(group.begin() + i); keys.erase(keys.begin() + i); return; }
-    }
+  void RemoveGroupNode(RemoteNode* member) {
+    PS_CHECK_EQ(group.size(), keys.size());
+    auto it = std::find(group.begin(), group.end(), member);
+    if (it == group.end()) return;
+    keys.erase(keys.begin() + (it - group.begin()));
+    group.erase(it);
   }
-  void ClearFilters() { for (auto& f : filters) delete f.second; filters.clear(); }
 
   Node node;
   bool alive = true;
@@ -65,7 +73,7 @@ struct RemoteNode {
   RequestTracker recv_req_tracker;   // requests this node sent to me
   std::vector<RemoteNode*> group;    // members if this is a group node
   std::vector<Range<Key>> keys;      // members' key ranges, same order
-  std::unordered_map<int, Filter*> filters;
+  std::unordered_map<int, std::unique_ptr<Filter>> filters;
 };
 
 }  // namespace PS

@@ -23,40 +23,48 @@ class Sketch {
   }
 };
 
+// Count-min sketch with saturating cells. A key touches `depth` cells of ONE row of `width` cells:
+// cell j is (h + j * step) mod width with h = hash(key) and step = h rotated right by 17 bits (double
+// hashing), which is also what the device kernels k_countmin_* compute.
 template <typename K, typename V>
 class CountMin : public Sketch {
  public:
-  bool empty() const { return n_ == 0; }
-  void clear() { data_.clear(); n_ = 0; }
-  void resize(int n, int k, V v_max) {
-    n_ = std::max(n, 64);
-    data_.resize(n_);
-    data_.SetZero();
-    k_ = std::min(30, std::max(1, k));
-    v_max_ = v_max;
+  static constexpr int kMinWidth = 64, kMaxDepth = 30;
+  bool empty() const { return width_ == 0; }
+  void clear() { cells_.clear(); width_ = 0; }
+  void resize(int width, int depth, V ceiling) {
+    width_ = width < kMinWidth ? kMinWidth : width;
+    depth_ = depth < 1 ? 1 : (depth > kMaxDepth ? kMaxDepth : depth);
+    ceiling_ = ceiling;
+    cells_.resize(width_);
+    cells_.SetZero();
   }
-  // k probes h, h+d, h+2d, ... with d = rotr17(h); saturating add
   void insert(const K& key, const V& count) {
-    uint32_t h = hash(key);
-    const uint32_t delta = (h >> 17) | (h << 15);
-    for (int j = 0; j < k_; ++j) {
-      V& cell = data_[h % n_];
-      cell = count > v_max_ - cell ? v_max_ : cell + count;
-      h += delta;
+    for (Walk w(hash(key)); w.index < depth_; w.next()) {
+      V& c = cells_[w.pos % width_];
+      const V room = ceiling_ - c;
+      c = count > room ? ceiling_ : (V)(c + count);
     }
   }
   V query(const K& key) const {
-    V res = v_max_;
-    uint32_t h = hash(key);
-    const uint32_t delta = (h >> 17) | (h << 15);
-    for (int j = 0; j < k_; ++j) { res = std::min(res, data_[h % n_]); h += delta; }
-    return res;
+    V lowest = ceiling_;
+    for (Walk w(hash(key)); w.index < depth_; w.next()) {
+      const V c = cells_[w.pos % width_];
+      if (c < lowest) lowest = c;
+    }
+    return lowest;
   }
-  const SArray<V>& data() const { return data_; }
+  const SArray<V>& data() const { return cells_; }
  private:
-  SArray<V> data_;
-  int n_ = 0, k_ = 1;
-  V v_max_ = 0;
+  struct Walk {
+    explicit Walk(uint32_t h) : pos(h), step((h >> 17) | (h << 15)) {}
+    void next() { pos += step; ++index; }
+    uint32_t pos, step;
+    int index = 0;
+  };
+  SArray<V> cells_;
+  int width_ = 0, depth_ = 1;
+  V ceiling_ = 0;
 };
 
 template <typename K>

@@ -132,7 +132,6 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_grad(const PsbDarlinGrad p
   }
   // One system fence per CTA: the block barrier orders every thread's peer stores before
   // thread 0's fence (fences are cumulative), and that fence precedes the arrival count.
-  // (A fence in every thread dominated these small kernels: ncu showed membar as the top stall.)
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
@@ -296,11 +295,8 @@ static int darlin_grid(const void* fn) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per, fn, kDThreads, 0);
-  // CTAs per SM: 4 measured best (23.7 / 24.9 / 26.6 ms per pass of 256 blocks with 4 / 2 / 1);
-  // PSB_DARLIN_CTAS_PER_SM overrides (1..4).
-  int want = 4;
-  if (const char* e = getenv("PSB_DARLIN_CTAS_PER_SM")) want = atoi(e);
-  want = want < 1 ? 1 : (want > 4 ? 4 : want);
+  // at most four co-resident CTAs per SM: more only lengthen the grid barriers of these short kernels
+  const int want = 4;
   per = per < 1 ? 1 : (per > want ? want : per);
   return sms * per;
 }
@@ -332,7 +328,7 @@ extern "C" int psb_darlin_dual(const PsbDarlinDual* p, cudaStream_t stream) {
 extern "C" int psb_darlin_eval(const float* y, const float* margin, uint32_t n_rows, const float* w,
                                const unsigned char* active, uint32_t c0, uint32_t c1, float lambda, double* out,
                                cudaStream_t stream) {
-  k_darlin_eval<<<148 * 2, 256, 0, stream>>>(y, margin, n_rows, w, active, c0, c1, lambda, out);
+  k_darlin_eval<<<psb_device_sm_count() * 2, 256, 0, stream>>>(y, margin, n_rows, w, active, c0, c1, lambda, out);
   return -(int)cudaGetLastError();
 }
 extern "C" int psb_darlin_struct_size(int which) {

@@ -98,7 +98,7 @@ extern "C" int psb_gen_batch(uint32_t* ids32, psb_u64* ids64, float* vals, float
   if (n_rows == 0) return 0;
   if (zipf_s == 1.0) zipf_s = 1.0 + 1e-9;
   if (real_values && !vals) return -(int)cudaErrorInvalidValue;
-  k_gen_batch<<<148 * 8, 256, 0, stream>>>(ids32, (u64*)ids64, vals, y, n_rows, z, n_feat, zipf_s,
+  k_gen_batch<<<psb_device_sm_count() * 8, 256, 0, stream>>>(ids32, (u64*)ids64, vals, y, n_rows, z, n_feat, zipf_s,
                                            seed, batch, real_values);
   return -(int)cudaGetLastError();
 }
@@ -106,11 +106,11 @@ extern "C" int psb_gen_batch(uint32_t* ids32, psb_u64* ids64, float* vals, float
 extern "C" int psb_hash_ids(const uint32_t* ids32, const psb_u64* ids64, psb_u64* keys,
                             psb_u64 n, psb_u64 seed, cudaStream_t stream) {
   if (n == 0) return 0;
-  k_hash_ids<<<148 * 8, 256, 0, stream>>>(ids32, (const u64*)ids64, (u64*)keys, n, seed);
+  k_hash_ids<<<psb_device_sm_count() * 8, 256, 0, stream>>>(ids32, (const u64*)ids64, (u64*)keys, n, seed);
   return -(int)cudaGetLastError();
 }
 
 extern "C" int psb_flush_l2(uint32_t* buf, psb_u64 n_words, uint32_t v, cudaStream_t stream) {
-  k_flush_l2<<<148 * 8, 256, 0, stream>>>(buf, n_words, v);
+  k_flush_l2<<<psb_device_sm_count() * 8, 256, 0, stream>>>(buf, n_words, v);
   return -(int)cudaGetLastError();
 }

@@ -214,7 +214,7 @@ using namespace psb;
 // scratch: 4 zeroed u32 words {partial lo, partial hi, done, pad}; state: 4 words kept between calls
 extern "C" int psb_key_signature(const psb_u64* keys, const uint32_t* n_ptr, uint32_t max_n, uint32_t* scratch,
                                  uint32_t* state, uint32_t* hit, uint32_t* sig_out, cudaStream_t stream) {
-  int blocks = (int)min((u32)(148 * 4), max(1u, (max_n + 255) / 256));
+  int blocks = (int)min((u32)(psb_device_sm_count() * 4), max(1u, (max_n + 255) / 256));
   k_key_signature<<<blocks, 256, 0, stream>>>((const u64*)keys, n_ptr, scratch, state, hit, sig_out, scratch + 2);
   return -(int)cudaGetLastError();
 }
@@ -222,36 +222,36 @@ extern "C" int psb_fixfloat_encode(const float* x, void* code, psb_u64 n, int nb
                                    psb_u64 seed, cudaStream_t stream) {
   if (nbytes < 1 || nbytes > 7 || !(hi > lo)) return -(int)cudaErrorInvalidValue;
   if (n == 0) return 0;
-  k_fixfloat_encode<<<148 * 8, 256, 0, stream>>>(x, (unsigned char*)code, n, nbytes, lo, hi, seed);
+  k_fixfloat_encode<<<psb_device_sm_count() * 8, 256, 0, stream>>>(x, (unsigned char*)code, n, nbytes, lo, hi, seed);
   return -(int)cudaGetLastError();
 }
 extern "C" int psb_fixfloat_decode(const void* code, float* x, psb_u64 n, int nbytes, float lo, float hi,
                                    cudaStream_t stream) {
   if (nbytes < 1 || nbytes > 7 || !(hi > lo)) return -(int)cudaErrorInvalidValue;
   if (n == 0) return 0;
-  k_fixfloat_decode<<<148 * 8, 256, 0, stream>>>((const unsigned char*)code, x, n, nbytes, lo, hi);
+  k_fixfloat_decode<<<psb_device_sm_count() * 8, 256, 0, stream>>>((const unsigned char*)code, x, n, nbytes, lo, hi);
   return -(int)cudaGetLastError();
 }
 // out = {+inf, -inf} must be preset by the caller
 extern "C" int psb_minmax(const float* x, psb_u64 n, float* out, cudaStream_t stream) {
   if (n == 0) return 0;
-  k_minmax<<<148 * 4, 256, 0, stream>>>(x, n, out);
+  k_minmax<<<psb_device_sm_count() * 4, 256, 0, stream>>>(x, n, out);
   return -(int)cudaGetLastError();
 }
 extern "C" int psb_add_noise(float* x, psb_u64 n, float mean, float stdv, psb_u64 seed, cudaStream_t stream) {
   if (n == 0) return 0;
-  k_add_noise<<<148 * 8, 256, 0, stream>>>(x, n, mean, stdv, seed);
+  k_add_noise<<<psb_device_sm_count() * 8, 256, 0, stream>>>(x, n, mean, stdv, seed);
   return -(int)cudaGetLastError();
 }
 extern "C" int psb_countmin_insert(uint32_t* cells, uint32_t n_cells, int k, const psb_u64* keys,
                                    const unsigned char* counts, const uint32_t* n_ptr, uint32_t n,
                                    cudaStream_t stream) {
-  k_countmin_insert<<<148 * 4, 256, 0, stream>>>(cells, n_cells, k, (const u64*)keys, counts, n_ptr, n);
+  k_countmin_insert<<<psb_device_sm_count() * 4, 256, 0, stream>>>(cells, n_cells, k, (const u64*)keys, counts, n_ptr, n);
   return -(int)cudaGetLastError();
 }
 extern "C" int psb_countmin_query(const uint32_t* cells, uint32_t n_cells, int k, const psb_u64* keys,
                                   unsigned char* out, const uint32_t* n_ptr, uint32_t n, cudaStream_t stream) {
-  k_countmin_query<<<148 * 4, 256, 0, stream>>>(cells, n_cells, k, (const u64*)keys, out, n_ptr, n);
+  k_countmin_query<<<psb_device_sm_count() * 4, 256, 0, stream>>>(cells, n_cells, k, (const u64*)keys, out, n_ptr, n);
   return -(int)cudaGetLastError();
 }
 extern "C" int psb_ordered_match(const psb_u64* src_key, const float* src_val, uint32_t n_src,
@@ -259,7 +259,7 @@ extern "C" int psb_ordered_match(const psb_u64* src_key, const float* src_val, u
                                  unsigned long long* matched, cudaStream_t stream) {
   if (n_src == 0 || n_dst == 0) return 0;
   if (matched) cudaMemsetAsync(matched, 0, sizeof(unsigned long long), stream);
-  k_ordered_match<<<148 * 4, 256, 0, stream>>>((const u64*)src_key, src_val, n_src, (const u64*)dst_key, dst_val,
+  k_ordered_match<<<psb_device_sm_count() * 4, 256, 0, stream>>>((const u64*)src_key, src_val, n_src, (const u64*)dst_key, dst_val,
                                                n_dst, k, op, matched);
   return -(int)cudaGetLastError();
 }

@@ -798,7 +798,7 @@ extern "C" int psb_coop_grid(int which) {
 }
 
 extern "C" int psb_table_init(void* table, psb_u64 capacity, cudaStream_t stream) {
-  k_table_init<<<148 * 8, 256, 0, stream>>>((Entry*)table, capacity);
+  k_table_init<<<psb_device_sm_count() * 8, 256, 0, stream>>>((Entry*)table, capacity);
   return -(int)cudaGetLastError();
 }
 
@@ -806,7 +806,7 @@ extern "C" int psb_table_dump(const void* table, psb_u64 capacity, psb_u64* out_
                               float* out_w, psb_u64 out_cap, unsigned long long* out_n,
                               cudaStream_t stream) {
   cudaMemsetAsync(out_n, 0, sizeof(unsigned long long), stream);
-  k_table_dump<false><<<148 * 8, 256, 0, stream>>>((const Entry*)table, capacity, (u64*)out_keys,
+  k_table_dump<false><<<psb_device_sm_count() * 8, 256, 0, stream>>>((const Entry*)table, capacity, (u64*)out_keys,
                                                    nullptr, nullptr, out_w, out_cap, out_n);
   return -(int)cudaGetLastError();
 }
@@ -815,7 +815,7 @@ extern "C" int psb_table_export(const void* table, psb_u64 capacity, psb_u64* ou
                                 float* out_s0, float* out_s1, float* out_w, psb_u64 out_cap,
                                 unsigned long long* out_n, cudaStream_t stream) {
   cudaMemsetAsync(out_n, 0, sizeof(unsigned long long), stream);
-  k_table_dump<true><<<148 * 8, 256, 0, stream>>>((const Entry*)table, capacity, (u64*)out_keys,
+  k_table_dump<true><<<psb_device_sm_count() * 8, 256, 0, stream>>>((const Entry*)table, capacity, (u64*)out_keys,
                                                   out_s0, out_s1, out_w, out_cap, out_n);
   return -(int)cudaGetLastError();
 }
@@ -824,7 +824,7 @@ extern "C" int psb_table_load(void* table, psb_u64 mask, psb_u64 key_begin, psb_
                               const psb_u64* keys, const float* s0, const float* s1, const float* w,
                               psb_u64 n, uint32_t* status, cudaStream_t stream) {
   if (n == 0) return 0;
-  k_table_load<<<148 * 4, 256, 0, stream>>>((Entry*)table, SlotMap{mask, key_begin, slot_mult},
+  k_table_load<<<psb_device_sm_count() * 4, 256, 0, stream>>>((Entry*)table, SlotMap{mask, key_begin, slot_mult},
                                             (const u64*)keys, s0, s1, w, n, status);
   return -(int)cudaGetLastError();
 }

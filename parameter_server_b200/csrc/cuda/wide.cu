@@ -690,14 +690,14 @@ static EncodeTiledFn encode_tiled() {
 }
 
 extern "C" int psb_wide_init(psb_u64* keys, void* vals, float* acc, psb_u64 cap, cudaStream_t stream) {
-  k_wide_init<<<148 * 8, 256, 0, stream>>>((u64*)keys, (__nv_bfloat16*)vals, acc, cap, 0, 0.f);
+  k_wide_init<<<psb_device_sm_count() * 8, 256, 0, stream>>>((u64*)keys, (__nv_bfloat16*)vals, acc, cap, 0, 0.f);
   return -(int)cudaGetLastError();
 }
 extern "C" int psb_wide_load(psb_u64* keys, void* vals, psb_u64 mask, psb_u64 key_begin, psb_u64 slot_mult,
                              const psb_u64* in_keys, const void* in_vals, uint32_t n, uint32_t* status,
                              cudaStream_t stream) {
   if (n == 0) return 0;
-  k_wide_load<<<148 * 4, 256, 0, stream>>>((u64*)keys, (__nv_bfloat16*)vals, SlotMap{mask, key_begin, slot_mult},
+  k_wide_load<<<psb_device_sm_count() * 4, 256, 0, stream>>>((u64*)keys, (__nv_bfloat16*)vals, SlotMap{mask, key_begin, slot_mult},
                                            (const u64*)in_keys, (const __nv_bfloat16*)in_vals, n, status);
   return -(int)cudaGetLastError();
 }
@@ -725,7 +725,8 @@ extern "C" int psb_wide_pull_gemm(const void* args, const void* ctx, uint32_t ma
     attr_set = true;
   }
   int tiles = (int)((max_unique + kTileM - 1) / kTileM);
-  int grid = tiles < 1 ? 1 : (tiles > 148 * 3 ? 148 * 3 : tiles);
+  const int grid_max = psb_device_sm_count() * 3;
+  int grid = tiles < 1 ? 1 : (tiles > grid_max ? grid_max : tiles);
   k_wide_pull_gemm<<<grid, 128, smem, stream>>>(map, a);
   return -(int)cudaGetLastError();
 }
@@ -771,7 +772,7 @@ extern "C" int psb_wide_rowsum(const float* P, int N, const uint32_t* row_ptr, u
                                const uint32_t* csr_col, const uint32_t* row_ctx, const float* y, float* gcoef,
                                float* margin, double* stats, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  k_wide_rowsum<<<148 * 4, 256, 0, stream>>>(P, N, row_ptr, n_rows, fixed_z, csr_col, row_ctx, y, gcoef, margin, stats);
+  k_wide_rowsum<<<psb_device_sm_count() * 4, 256, 0, stream>>>(P, N, row_ptr, n_rows, fixed_z, csr_col, row_ctx, y, gcoef, margin, stats);
   return -(int)cudaGetLastError();
 }
 extern "C" int psb_wide_push(const void* args, cudaStream_t stream) {
