@@ -13,7 +13,12 @@ alpha 0.1, beta 1, l1 1, l2 0.1.
 Rank 0 prints one JSON line. ``value`` is timed on the device (CUDA events, max
 over ranks) with the minibatches already resident in HBM; ``e2e`` runs the same
 steps through ``SparseLRWorker.submit`` from pinned host memory and reads each
-step's loss back to the host.
+step's loss back to the host. The timed region of K steps is repeated
+``--repeats`` times (each bracketed by barrier + synchronize); ``value`` is the
+median repetition, ``ms_per_step_min/max`` the spread. With more than one GPU
+the NCCL all-to-all-v arm (same local kernels, same pipelining) is measured in
+the same invocation and reported as ``vs_nccl``; both arms report their
+logloss after the same number of examples.
 """
 from __future__ import annotations
 
@@ -92,30 +97,48 @@ class ClockSampler:
                 "samples": len(sm), "power_w_max": max(self.power) if self.power else None}
 
 
-def _bind_to_gpu_numa_node(local_rank: int):
-    """Run this rank (and allocate its pinned staging buffers) on the CPU socket next to its GPU:
-    with eight ranks copying 53 MB per step each, host buffers that all sit on one socket make the
-    end-to-end rate depend on that socket's memory and on the link between the sockets. Only the
-    process's CPU affinity changes; nothing of the GPU. Returns the node, or None if unknown."""
+def gpu_numa_cpus(local_rank: int, sysfs: str = "/sys"):
+    """(node, cpu set) of the NUMA node the GPU hangs off, or None when the machine does not say."""
+    import torch
+    pr = torch.cuda.get_device_properties(local_rank)
+    bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+    return numa_cpus_of_pci_device(bdf, sysfs)
+
+
+def numa_cpus_of_pci_device(bdf: str, sysfs: str = "/sys"):
     try:
-        pr = torch.cuda.get_device_properties(local_rank)
-        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
-        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+        with open(f"{sysfs}/bus/pci/devices/{bdf}/numa_node") as f:
             node = int(f.read())
         if node < 0:
             return None
-        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
-            cpus = set()
-            for part in f.read().strip().split(","):
-                lo, _, hi = part.partition("-")
-                cpus.update(range(int(lo), int(hi or lo) + 1))
-        allowed = cpus & os.sched_getaffinity(0)
-        if len(allowed) < 2:
-            return None
-        os.sched_setaffinity(0, allowed)
-        return node
-    except Exception:   # noqa: BLE001  (no sysfs, no such attribute, not permitted: stay where we are)
+        with open(f"{sysfs}/devices/system/node/node{node}/cpulist") as f:
+            text = f.read().strip()
+    except (OSError, ValueError):
         return None
+    cpus = set()
+    for part in text.split(","):
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return node, cpus
+
+
+def _bind_to_gpu_numa_node(local_rank: int):
+    """Run this rank (and allocate its pinned staging buffers) on the CPU socket next to its GPU:
+    with eight ranks copying tens of MB per step each, host buffers that all sit on one socket make the
+    end-to-end rate depend on that socket's memory and on the link between the sockets. Only the
+    process's CPU affinity changes; nothing of the GPU. Returns the node, or None if unknown."""
+    found = gpu_numa_cpus(local_rank)
+    if found is None:
+        return None
+    node, cpus = found
+    allowed = cpus & os.sched_getaffinity(0)
+    if len(allowed) < 2:
+        return None
+    try:
+        os.sched_setaffinity(0, allowed)
+    except OSError:
+        return None
+    return node
 
 
 def main():
@@ -131,6 +154,8 @@ def main():
     ap.add_argument("--pool", type=int, default=4, help="distinct minibatches cycled through")
     ap.add_argument("--quant", default="none")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
+    ap.add_argument("--no-nccl-arm", action="store_true", help="skip the NCCL all-to-all-v arm (measured by default on >1 GPU)")
     ap.add_argument("--breakdown", action="store_true",
                     help="also time each stage (localise / pull+margins / push / apply) with CUDA events, "
                          "stages run back to back on one stream")
@@ -204,24 +229,13 @@ def main():
             torch.cuda.synchronize()
 
     nccl = None
+    want_nccl = world > 1 and (args.impl == "nccl" or not args.no_nccl_arm)
     if args.impl == "nccl":
         assert world > 1, "--impl nccl needs at least two ranks"
-        from parameter_server_b200.parallel.nccl_baseline import NcclPushPull
-        nccl = NcclPushPull(plane, nnz)
 
     def run(pool, n, log=None):
         for i in range(n):
             ids, y = pool[i % len(pool)]
-            if nccl is not None:
-                # baseline arm: same kernels, NCCL all-to-all-v for everything that crosses GPUs
-                ids_d = ids if ids.is_cuda else ids.to(dev, non_blocking=True)
-                y_d = y if y.is_cuda else y.to(dev, non_blocking=True)
-                b = worker.prepare(ids_d, y_d, fixed_z=z)
-                nccl.step(b, worker.step_no)
-                worker.step_no += 1
-                if log is not None:
-                    log[i].copy_(plane.pull_stats, non_blocking=True)
-                continue
             worker.submit(ids, y, fixed_z=z)
             if log is not None:
                 # D2H read of this step's running loss/accuracy counters (async, pinned)
@@ -229,53 +243,145 @@ def main():
                     log[i].copy_(plane.pull_stats, non_blocking=True)
         worker.wait()
 
+    def run_nccl(pool, n, log=None):
+        """The baseline arm with the same overlap as the fused one: minibatch i+1 is copied and localised
+        (and its split sizes exchanged) on the prep stream while minibatch i goes through NCCL push/pull."""
+        prep, main_s = worker.prep_stream, worker.main_stream
+        cur = torch.cuda.current_stream()
+        prep.wait_stream(cur); main_s.wait_stream(cur)
+        evs = [torch.cuda.Event(), torch.cuda.Event()]
+        free = [torch.cuda.Event(), torch.cuda.Event()]
+        for i in range(n + 1):
+            if i < n:
+                k = i % 2
+                ids, y = pool[i % len(pool)]
+                with torch.cuda.stream(prep):
+                    if i >= 2:
+                        prep.wait_event(free[k])
+                    ids_d = ids if ids.is_cuda else ids.to(dev, non_blocking=True)
+                    y_d = y if y.is_cuda else y.to(dev, non_blocking=True)
+                    worker.bufs[k].localize(ids_d, y_d, plane.bounds, fixed_z=z, hash_seed=0,
+                                            hash_bits=args.key_bits % 64, stream=prep)
+                    nccl.exchange_counts(worker.bufs[k], k)
+                    evs[k].record(prep)
+            if i >= 1:
+                k = (i - 1) % 2
+                with torch.cuda.stream(main_s):
+                    main_s.wait_event(evs[k])
+                    nccl.step(worker.bufs[k], worker.step_no, counts_slot=k)
+                    free[k].record(main_s)
+                    worker.step_no += 1
+                    if log is not None:
+                        log[i - 1].copy_(plane.pull_stats, non_blocking=True)
+        cur.wait_stream(main_s); cur.wait_stream(prep)
+
+    def timed(fn, pool):
+        """`repeats` regions of exactly `steps` steps, each between barrier + synchronize; device time, max over ranks."""
+        out = []
+        for _ in range(max(1, args.repeats)):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            sync_all()
+            e0.record()
+            fn(pool, args.steps)
+            e1.record()
+            sync_all()
+            t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out.append(float(t.item()))
+        return sorted(out)
+
+    def timed_e2e(fn, pool_host):
+        log = torch.zeros((args.steps, 4), dtype=torch.float64).pin_memory()
+        fn(pool_host, min(args.warmup, 3))
+        out = []
+        for _ in range(max(1, min(args.repeats, 3))):
+            sync_all()
+            t0 = time.perf_counter()
+            fn(pool_host, args.steps, log)
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            sync_all()
+            tt = torch.tensor([t1 - t0], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            out.append(float(tt.item()))
+        out.sort()
+        return out[len(out) // 2], log
+
+    def examples_and_loss():
+        p = worker.read_progress()
+        t = torch.tensor([p["loss_sum"], p["n_examples"]], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t)
+        return float(t[1].item()), float(t[0].item()) / max(1.0, float(t[1].item()))
+
+    # ---------------- NCCL arm first (its own table: the two arms must not train each other's model)
+    nccl_res = None
+    if want_nccl:
+        from parameter_server_b200.parallel.nccl_baseline import NcclPushPull
+        pc_n = PlaneConfig(table_capacity=cap, inbox_cap=16, ring=args.tau + 2, quant="none",
+                           ordered_slots=not args.hashed_slots, pull_cap=0)
+        fab_n = Fabric.from_process_group(heap_layout(pc_n, world).total())
+        plane_f, worker_f = plane, worker
+        plane = DataPlane(fab_n, pc_n, opt)
+        worker = SparseLRWorker(plane, SparseLRConfig(max_rows=rows, max_nnz=nnz, tau=args.tau, hash_seed=0,
+                                                      hash_bits=args.key_bits % 64, pipeline=3))
+        nccl = NcclPushPull(plane, nnz)
+        run_nccl(pool_d, args.warmup)
+        sync_all()
+        plane.check_status("nccl warm-up")
+        worker.read_progress()
+        ts_n = timed(run_nccl, pool_d)
+        n_ex, n_loss = examples_and_loss()
+        e2e_n = None
+        if not args.no_e2e:
+            sec, _ = timed_e2e(run_nccl, pool_h)
+            e2e_n = world * rows * args.steps / sec
+        plane.check_status("nccl arm")
+        med = ts_n[len(ts_n) // 2]
+        nccl_res = {"ms_per_step": med / args.steps, "examples_per_s": world * rows * args.steps / (med * 1e-3),
+                    "e2e_examples_per_s": e2e_n, "logloss": n_loss, "after_examples": n_ex,
+                    "collectives_per_step": 4}
+        if args.impl == "nccl":
+            ts, launches = ts_n, 0
+        fab_n.close()
+        del nccl
+        nccl = None
+        plane, worker = plane_f, worker_f
+
     # ---------------- device-timed arm
-    run(pool_d, args.warmup)
-    sync_all()
-    plane.check_status("warm-up")
-    uniq = [int(b.n_unique.item()) for b in worker.bufs]
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    l0 = _lib.LAUNCHES
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    e0.record()
-    run(pool_d, args.steps)
-    e1.record()
-    sync_all()
-    launches = _lib.LAUNCHES - l0
-    ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
-    plane.check_status("timed region")
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    uniq, clocks, e2e, ours_loss = [0], None, None, None
+    if args.impl != "nccl":
+        run(pool_d, args.warmup)
+        sync_all()
+        plane.check_status("warm-up")
+        worker.read_progress()
+        uniq = [int(b.n_unique.item()) for b in worker.bufs]
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        l0 = _lib.LAUNCHES
+        ts = timed(run, pool_d)
+        launches = (_lib.LAUNCHES - l0) // max(1, args.repeats)
+        clocks = sampler.stop() if rank == 0 else None
+        plane.check_status("timed region")
+        ours_ex, ours_loss = examples_and_loss()
+        # ---------------- end-to-end arm (pinned host inputs, per-step D2H of the loss counters)
+        if not args.no_e2e:
+            sec, log = timed_e2e(run, pool_h)
+            plane.check_status("e2e region")
+            h2d = nnz * 4 + rows * 4
+            e2e = {"value": world * rows * args.steps / sec, "unit": "examples/s",
+                   "h2d_bytes_per_step": world * h2d, "d2h_bytes_per_step": world * 32,
+                   "h2d_GB_per_s_per_gpu": h2d * args.steps / sec / 1e9,
+                   "loss_per_example_last": float((log[-1, 0] - log[-2, 0]) / max(1.0, float(log[-1, 2] - log[-2, 2])))
+                   if args.steps > 1 else None}
+    ms = ts[len(ts) // 2]
     ex_per_s = world * rows * args.steps / (ms * 1e-3)
 
-    # ---------------- end-to-end arm (pinned host inputs, per-step D2H of the loss counters)
-    e2e = None
-    if not args.no_e2e:
-        log = torch.zeros((args.steps, 4), dtype=torch.float64).pin_memory()
-        run(pool_h, min(args.warmup, 3))
-        sync_all()
-        t0 = time.perf_counter()
-        run(pool_h, args.steps, log)
-        torch.cuda.synchronize()
-        t1 = time.perf_counter()
-        sync_all()
-        plane.check_status("e2e region")
-        tt = torch.tensor([t1 - t0], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        e2e = {"value": world * rows * args.steps / float(tt.item()), "unit": "examples/s",
-               "h2d_bytes_per_step": world * (nnz * 4 + rows * 4), "d2h_bytes_per_step": world * 32,
-               "loss_per_example_last": float((log[-1, 0] - log[-2, 0]) / max(1.0, float(log[-1, 2] - log[-2, 2])))
-               if args.steps > 1 else None}
-
     breakdown = None
-    if args.breakdown and nccl is None:
+    if args.breakdown and args.impl != "nccl":
         names = ["localize", "pull_margin", "push", "apply"]
         acc = {k: 0.0 for k in names}
         reps = 6
@@ -308,13 +414,13 @@ def main():
         breakdown = {k: float(v) for k, v in zip(names, tb.tolist())}
         plane.check_status("breakdown")
 
-    prog = worker.read_progress()
     if rank == 0:
         u_mean = sum(uniq) / len(uniq)
         out = {
             "metric": "FTRL sparse-LR examples/sec (whole job); push+pull keys/sec in config",
             "value": ex_per_s, "unit": "examples/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "repeats": len(ts), "ms_per_step_min": ts[0] / args.steps, "ms_per_step_max": ts[-1] / args.steps,
             "scaling": "weak", "vs_baseline": ex_per_s / PUBLISHED_FTRL_EXAMPLES_PER_S,
             "dtype": "fp32", "data": "synthetic (device generator, Zipf-like ids, random-init model)",
             "impl": args.impl,
@@ -328,7 +434,11 @@ def main():
                        "host_numa_node": numa_node, "l2_policy": f"inputs larger than L2: {args.pool} distinct minibatches of "
                                     f"{nnz * 4 / 1e6:.0f} MB ids, >=300 MB sort working set per step"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "stage_ms_max_over_ranks": breakdown,
-            "progress": {"loss_per_example": prog["loss_sum"] / max(1.0, prog["n_examples"])},
+            "logloss_after_examples": None if ours_loss is None else {"examples": ours_ex, "logloss": ours_loss},
+            "nccl_arm": nccl_res,
+            "vs_nccl": None if (nccl_res is None or args.impl == "nccl") else {
+                "device_timed": ex_per_s / nccl_res["examples_per_s"],
+                "e2e": (e2e["value"] / nccl_res["e2e_examples_per_s"]) if (e2e and nccl_res["e2e_examples_per_s"]) else None},
         }
         print(json.dumps(out))
     if world > 1:

@@ -110,6 +110,51 @@ extern "C" int psb_hash_ids(const uint32_t* ids32, const psb_u64* ids64, psb_u64
   return -(int)cudaGetLastError();
 }
 
+// ---------------------------------------------------------------- random-access probes
+// What a table walk can reach on this part: n look-ups of 32-byte entries at the given slot indices.
+// mode 0: one 16-byte load per entry (what a pull does); mode 1: read 24 bytes, write 12 (what an
+// optimiser update does). Four independent entries per thread and trip, as in the real kernels.
+namespace psb {
+__global__ void __launch_bounds__(256) k_probe_entries(Entry* __restrict__ tab, const u32* __restrict__ slots, u32 n,
+                                                       int mode, float* __restrict__ out) {
+  const u32 gsize = gridDim.x * blockDim.x, gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  for (u32 i0 = gtid; i0 < n; i0 += 4 * gsize) {
+    u32 sl[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) sl[q] = (i0 + q * gsize < n) ? slots[i0 + q * gsize] : 0u;
+    if (mode == 0) {
+      u64 k[4], hi[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(k[q]), "=l"(hi[q]) : "l"(&tab[sl[q]]) : "memory");
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (i0 + q * gsize < n) out[i0 + q * gsize] = __uint_as_float((u32)hi[q]) + (k[q] == 1 ? 1.f : 0.f);
+    } else {
+      float2 ws[4];
+      float s1[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        ws[q] = *reinterpret_cast<const float2*>(&tab[sl[q]].w);
+        s1[q] = tab[sl[q]].s1;
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (i0 + q * gsize >= n) break;
+        *reinterpret_cast<float2*>(&tab[sl[q]].w) = make_float2(ws[q].x + 1.f, ws[q].y + s1[q]);
+        tab[sl[q]].s1 = s1[q] + 1.f;
+      }
+    }
+  }
+}
+}  // namespace psb
+
+extern "C" int psb_probe_entries(void* table, const uint32_t* slots, uint32_t n, int mode, float* out,
+                                 cudaStream_t stream) {
+  psb::k_probe_entries<<<psb_device_sm_count() * 4, 256, 0, stream>>>((psb::Entry*)table, slots, n, mode, out);
+  return -(int)cudaGetLastError();
+}
+
 extern "C" int psb_flush_l2(uint32_t* buf, psb_u64 n_words, uint32_t v, cudaStream_t stream) {
   k_flush_l2<<<psb_device_sm_count() * 8, 256, 0, stream>>>(buf, n_words, v);
   return -(int)cudaGetLastError();

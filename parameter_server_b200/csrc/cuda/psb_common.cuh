@@ -74,17 +74,18 @@ __host__ __device__ __forceinline__ u64 hash_id_to_key(u64 id, u64 seed_bits) {
 //   w     : the weight that Pull returns; {key, w} sit in the first 16 bytes so
 //           a pull is a single 16-byte load
 //   s0,s1 : optimiser state (FTRL: z, sqrt_n; AdaGrad: sum_sq_grad, unused)
-//   gacc  : per-timestamp gradient accumulator used for the duplicate-key
-//           reduce across sources (zero between applies)
-//   epoch : timestamp tag of the last apply that touched the slot
+//   gacc, gcnt : per-round accumulator of the duplicate-key reduce across sources: the sum of the
+//           gradients pushed for the key in this round and how many sources pushed it. Both are
+//           updated by ONE 8-byte vector atomic per pushed record (the source that finds gcnt == 0
+//           becomes the key's leader) and both are zero between applies.
 struct __align__(32) Entry {
   u64 key;
   float w;
   float s0;
   float s1;
-  float gacc;
-  u32 epoch;
   u32 pad;
+  float gacc;     // 8-byte aligned together with gcnt
+  float gcnt;
 };
 static_assert(sizeof(Entry) == 32, "Entry must be one 32-byte sector");
 
@@ -112,6 +113,13 @@ __device__ __forceinline__ u32 ld_relaxed_gpu(const u32* p) {
 }
 __device__ __forceinline__ void st_relaxed_gpu(u32* p, u32 v) {
   asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// {a, b} += {x, y} as one 8-byte atomic on global memory (sm_90+ vector atomics); returns the old pair.
+__device__ __forceinline__ float2 atomic_add_f32x2(float* addr8, float x, float y) {
+  float2 old;
+  asm volatile("atom.global.v2.f32.add {%0, %1}, [%2], {%3, %4};"
+               : "=f"(old.x), "=f"(old.y) : "l"(addr8), "f"(x), "f"(y) : "memory");
+  return old;
 }
 __device__ __forceinline__ u64 ld_relaxed_sys_u64(const u64* p) {
   u64 v;

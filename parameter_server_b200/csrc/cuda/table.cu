@@ -692,18 +692,17 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
         if (p.slot_cache[rr[q]]) p.slot_cache[rr[q]][jj[q]] = (u32)slot[q];
       }
     } else {
-      u32 old[4];
+      // one vector atomic per record: gradient into gacc, one into gcnt; the record that finds
+      // gcnt == 0 is the key's leader in phase B
+      float seen[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        old[q] = 0;
-        if (slot[q] >= 0) {
-          old[q] = atomicExch(&tab[slot[q]].epoch, p.ts1);
-          atomicAdd(&tab[slot[q]].gacc, g[q]);
-        }
+        seen[q] = 1.f;
+        if (slot[q] >= 0) seen[q] = atomic_add_f32x2(&tab[slot[q]].gacc, g[q], 1.f).y;
       }
 #pragma unroll
       for (int q = 0; q < 4; ++q)
-        if (slot[q] >= 0) p.slot_cache[rr[q]][jj[q]] = (u32)slot[q] | (old[q] != p.ts1 ? 0x80000000u : 0u);
+        if (slot[q] >= 0) p.slot_cache[rr[q]][jj[q]] = (u32)slot[q] | (seen[q] == 0.f ? 0x80000000u : 0u);
     }
   }
   PSB_TSTAMP(2);
@@ -723,14 +722,16 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
         sc[q] = __ldcg(&p.slot_cache[r][i - s_pre[r]]);
         if ((sc[q] & 0x7fffffffu) == 0x7fffffffu) sc[q] = 0;
       }
-      float2 ws[4], sg[4];
+      float2 ws[4];
+      float4 sg[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        ws[q] = sg[q] = make_float2(0.f, 0.f);
+        ws[q] = make_float2(0.f, 0.f);
+        sg[q] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (sc[q] & 0x80000000u) {
           const Entry* e = &tab[sc[q] & 0x7fffffffu];
           ws[q] = __ldcg(reinterpret_cast<const float2*>(&e->w));    // (w, s0)
-          sg[q] = __ldcg(reinterpret_cast<const float2*>(&e->s1));   // (s1, gacc)
+          sg[q] = __ldcg(reinterpret_cast<const float4*>(&e->s1));   // (s1, pad, gacc, gcnt): the second half
         }
       }
 #pragma unroll
@@ -738,9 +739,9 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
         if (!(sc[q] & 0x80000000u)) continue;
         Entry* e = &tab[sc[q] & 0x7fffffffu];
         float w = ws[q].x, s0 = ws[q].y, s1 = sg[q].x, w_old = w;
-        opt_step(p.opt, sg[q].y, w, s0, s1);
+        opt_step(p.opt, sg[q].z, w, s0, s1);
         *reinterpret_cast<float2*>(&e->w) = make_float2(w, s0);
-        *reinterpret_cast<float2*>(&e->s1) = make_float2(s1, 0.f);
+        *reinterpret_cast<float4*>(&e->s1) = make_float4(s1, 0.f, 0.f, 0.f);   // accumulator and count back to zero
         st.add(w, w_old);
       }
     }

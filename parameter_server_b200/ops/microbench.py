@@ -11,6 +11,7 @@ repository root when present (copy bandwidth), else 6650 GB/s ("of fallback").
 from __future__ import annotations
 
 import argparse
+import ctypes as C
 import json
 import os
 from pathlib import Path
@@ -437,6 +438,36 @@ def _max_over_ranks(dist, world, dev, vals):
     return t.tolist()
 
 
+def bench_gather(args):
+    """The random-access rate of this part at the table's density: n entries of 32 bytes picked from
+    a table of 2^log2-slots entries, in address order (what a sorted key list with the order-preserving
+    slot map produces) and in random order; a 16-byte load per entry (pull) and a read-modify-write
+    (optimiser update). The roofline of the table walks of the pull and apply kernels is this rate,
+    not the copy bandwidth."""
+    from . import _lib
+    from ._lib import check, ptr, stream_ptr
+    dev = torch.device("cuda")
+    L = _lib.lib()
+    L.psb_probe_entries.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_int, C.c_void_p, C.c_void_p]
+    cap, n = 1 << args.log2_slots, args.n
+    table = torch.zeros(cap * 8, dtype=torch.float32, device=dev)
+    flush = torch.empty(64 << 20, dtype=torch.int32, device=dev)
+    out = torch.empty(n, device=dev)
+    g = torch.Generator(device=dev).manual_seed(1)
+    rnd = torch.randint(0, cap, (n,), device=dev, generator=g, dtype=torch.int64).to(torch.int32)
+    srt = torch.sort(rnd.to(torch.int64))[0].to(torch.int32)
+    peak, tag = _peak_gbs()
+    res = {"entries": n, "table_GB": cap * 32 / 1e9, "peak": tag}
+    for order, idx in (("address_order", srt), ("random_order", rnd)):
+        for mode, name, nbytes in ((0, "load16", 32), (1, "update", 64)):
+            med, best = _time(lambda: check(L.psb_probe_entries(ptr(table), ptr(idx), n, mode, ptr(out), stream_ptr())),
+                              args.iters, flush)
+            res[f"{name}_{order}"] = {"ms": round(med, 4), "G_entries_per_s": round(n / 1e9 / (med * 1e-3), 2),
+                                      "sector_GB_per_s": round(n * nbytes / 1e9 / (med * 1e-3), 1),
+                                      "frac_of_copy_bw": round(n * nbytes / 1e9 / (med * 1e-3) / peak, 3)}
+    print(json.dumps(res))
+
+
 def bench_fabric(args):
     """Peer store and peer load bandwidth of this box, per direction and per GPU: every rank copies
     `--mb` MB to (store) and from (load) the heap of rank + d, for every distance d, with the same
@@ -563,6 +594,8 @@ def main():
     s = sub.add_parser("kv"); s.add_argument("--sizes", type=int, nargs="+", default=[1000, 100000, 1000000, 16000000])
     s.add_argument("--iters", type=int, default=5); s.add_argument("--quant", default="none", choices=["none", "int8", "fp16"])
     s.add_argument("--one-sided", action="store_true", help="pull with remote probes instead of the exchange kernel")
+    s = sub.add_parser("gather"); s.add_argument("--log2-slots", type=int, default=27)
+    s.add_argument("--n", type=int, default=2680000); s.add_argument("--iters", type=int, default=5)
     s = sub.add_parser("fabric"); s.add_argument("--mb", type=int, default=256); s.add_argument("--iters", type=int, default=5)
     s = sub.add_parser("layer"); s.add_argument("--iters", type=int, default=5)
     s.add_argument("--small", action="store_true", help="shrink the two largest layers 16x (quick runs)")
@@ -572,7 +605,7 @@ def main():
     from .. import _build
     _build.build_cuda()
     {"sort": bench_sort, "step": bench_step, "wide": bench_wide, "wide-step": bench_wide_step, "kv": bench_kv,
-     "darlin": bench_darlin, "fabric": bench_fabric, "layer": bench_layer}[args.cmd](args)
+     "darlin": bench_darlin, "fabric": bench_fabric, "layer": bench_layer, "gather": bench_gather}[args.cmd](args)
 
 
 if __name__ == "__main__":

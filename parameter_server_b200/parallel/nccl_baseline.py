@@ -5,9 +5,16 @@ margins, X^T g, optimiser), but every byte that crosses GPUs goes through
 ``torch.distributed.all_to_all_single`` with split sizes, as a conventional
 implementation would do it:
 
-    counts exchange (+ host sync for the split sizes)
-    pull : keys -> owners | local table gather | values -> workers
-    push : values -> owners (keys are reused from the pull) | local apply
+    counts exchange (the split sizes have to be on the host)
+    pull : keys -> owners | local table gather (slots remembered) | values -> workers
+    push : values -> owners (keys and slots are reused from the pull) | local apply
+
+To keep the comparison fair the baseline gets what the fused path has: the split
+sizes of minibatch t+1 are exchanged and copied to the host while minibatch t
+runs (``exchange_counts`` / ``step``), so no step waits for a device-to-host
+copy of its own; the owner remembers the slots it found during the pull and the
+apply reuses them; and the driver overlaps the localisation of the next
+minibatch on another stream.
 
 This path is a baseline, not the product.
 """
@@ -46,16 +53,39 @@ class NcclPushPull:
         self.n_recv = torch.zeros(1, dtype=i32, device=dev)
         self.slot_cache = torch.zeros(cap, dtype=i32, device=dev)
         self.collectives = 0
+        # split sizes of two minibatches in flight: device tensors, pinned host copies, copy-done events
+        self._sc_dev = [torch.zeros(self.S, dtype=i64, device=dev) for _ in range(2)]
+        self._rc_dev = [torch.zeros(self.S, dtype=i64, device=dev) for _ in range(2)]
+        self._sc_host = [torch.zeros(self.S, dtype=i64).pin_memory() for _ in range(2)]
+        self._rc_host = [torch.zeros(self.S, dtype=i64).pin_memory() for _ in range(2)]
+        self._counts_ev = [torch.cuda.Event() for _ in range(2)]
 
-    def step(self, b, t: int, loss: int = 0):
-        """One minibatch (already localised into ``b``) through NCCL push/pull."""
+    def exchange_counts(self, b, k: int):
+        """Exchange the split sizes of localised batch ``b`` (slot ``k`` of two) on the current stream and
+        start their copy to the host; ``step(..., counts_slot=k)`` picks them up later."""
+        self._sc_dev[k].copy_((b.own_off[1:] - b.own_off[:-1]).to(torch.int64))
+        dist.all_to_all_single(self._rc_dev[k], self._sc_dev[k], group=self.group)
+        self._sc_host[k].copy_(self._sc_dev[k], non_blocking=True)
+        self._rc_host[k].copy_(self._rc_dev[k], non_blocking=True)
+        self._counts_ev[k].record()
+        self.collectives += 1
+
+    def step(self, b, t: int, loss: int = 0, counts_slot: int = -1):
+        """One minibatch (already localised into ``b``) through NCCL push/pull. With ``counts_slot`` the
+        split sizes come from an earlier ``exchange_counts``; otherwise they are exchanged here."""
         p, S, L = self.plane, self.S, _lib.lib()
         sp = stream_ptr()
-        # ---- split sizes (device -> host: the all-to-all-v needs them on the host)
-        self.send_counts.copy_((b.own_off[1:] - b.own_off[:-1]).to(torch.int64))
-        dist.all_to_all_single(self.recv_counts, self.send_counts, group=self.group)
-        sc = self.send_counts.tolist()
-        rc = self.recv_counts.tolist()
+        # ---- split sizes (the all-to-all-v needs them on the host)
+        if counts_slot >= 0:
+            self._counts_ev[counts_slot].synchronize()      # recorded a whole step ago: normally no wait at all
+            sc = self._sc_host[counts_slot].tolist()
+            rc = self._rc_host[counts_slot].tolist()
+            self.recv_counts.copy_(self._rc_dev[counts_slot])
+        else:
+            self.send_counts.copy_((b.own_off[1:] - b.own_off[:-1]).to(torch.int64))
+            dist.all_to_all_single(self.recv_counts, self.send_counts, group=self.group)
+            sc = self.send_counts.tolist()
+            rc = self.recv_counts.tolist()
         U, R = sum(sc), sum(rc)
         assert R <= self.cap
         # ---- pull: keys to the owners
@@ -64,7 +94,8 @@ class NcclPushPull:
         self.n_recv.fill_(R)
         self.one_off.copy_(torch.tensor([0, R], dtype=torch.int32))
         g = PullParams()
-        g.S, g.insert = 1, 0
+        g.S, g.insert = 1, 1                     # absent keys are inserted on first touch, as in the fused pull
+        g.slot_local = ptr(self.slot_cache)      # ... and the slots are remembered for the apply
         g.table[0], g.mask[0] = p.table_ptr(), p.cfg.table_capacity - 1
         g.key_begin[0], g.slot_mult[0] = p.bounds_host[self.rank], p.slot_mult[self.rank]
         g.applied[0], g.need_applied = p._ctrl(self.rank, 0), 0
@@ -115,11 +146,11 @@ class NcclPushPull:
             a.inbox_vals[r] = self.rgrad.data_ptr() + off * 4
             a.ready[r] = self.ready.data_ptr() + 4 * r
             a.count[r] = self.counts32.data_ptr() + 4 * r
-            a.alive[r], a.cached[r] = 1, 0
+            a.alive[r], a.cached[r] = 1, 1       # slots found by the gather above
             a.slot_cache[r] = self.slot_cache.data_ptr() + off * 4
             off += rc[r]
         a.opt = p.opt.to_c()
         a.stats, a.applied = ptr(p.push_stats), p._ctrl(self.rank, 0)
         a.bar, a.done, a.status = p._bar(2), p._done(2), ptr(p.status)
         check(L.psb_apply(C.byref(a), sp), "apply")
-        self.collectives += 4
+        self.collectives += 3 if counts_slot >= 0 else 4
