@@ -195,10 +195,9 @@ def run_async_sgd(conf, verbose=True, engine: str = "gpu"):
                 key_cache = True
         max_nnz = int(os.environ.get("PSB_MAX_NNZ_PER_ROW", "512")) * minibatch
         table_cap = 1 << int(os.environ.get("PSB_LOG2_TABLE", "22"))
-        # two-sided exchange pull unless the key-caching filter is asked for (that one belongs to the one-sided pull)
+        # two-sided exchange pull; the key-caching filter, when asked for, is decided inside that kernel
         pc = PlaneConfig(table_capacity=table_cap, inbox_cap=max_nnz, ring=tau + 2, quant=quant, key_cache=key_cache,
-                         ordered_slots=os.environ.get("PSB_ORDERED_SLOTS", "0") == "1",
-                         pull_cap=0 if key_cache else max_nnz)
+                         ordered_slots=os.environ.get("PSB_ORDERED_SLOTS", "0") == "1", pull_cap=max_nnz)
         hb = heap_layout(pc, world).total()
         fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
         plane = DataPlane(fab, pc, opt)

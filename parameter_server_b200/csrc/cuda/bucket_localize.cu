@@ -57,20 +57,29 @@ static constexpr u32 kHotSlots = 4096;            // hot-key lookup table (open 
 static constexpr u32 kHotMax = 2048;              // hot keys at most
 static constexpr int kWalkThreads = 1024;         // count / scatter CTAs
 static constexpr int kBucketThreads = 256;
-static constexpr int kHsBits = 12;                // home slots of a bucket's table
-static constexpr u32 kHs = 1u << kHsBits;
 static constexpr u32 kRunMax = 64;                // longest probe sequence / run of adjacent occupied slots
-static constexpr u32 kHsAll = kHs + 2 * kRunMax;  // slots including the spill area behind the last home slot
-static constexpr u32 kHsWords = kHsAll / 32;      // occupancy bitmap words
-static constexpr u32 kDistinctMax = 2048;         // distinct keys a bucket may hold
-static constexpr int kEntriesPerThread = kDistinctMax / kBucketThreads;
 static constexpr u32 kMaxBuckets = 8192;
+// A bucket's table comes in two sizes. 2^11 home slots (35 KB of shared memory, six CTAs per SM) serve
+// minibatches in which keys repeat, the usual case; 2^12 (55 KB, four per SM) those in which nearly
+// every nonzero has its own key. The sample decides (k_bl_plan), both kernels are launched and the
+// one that was not chosen returns at once.
+template <int kBits> struct BucketShape {
+  static constexpr u32 kHs = 1u << kBits;                  // home slots
+  static constexpr u32 kHsAll = kHs + 2 * kRunMax;         // plus the spill area behind the last home slot
+  static constexpr u32 kHsWords = kHsAll / 32;             // occupancy bitmap words
+  static constexpr u32 kDistinctMax = kHs / 2;             // distinct keys a bucket may hold
+  static constexpr int kEntriesPerThread = kDistinctMax / kBucketThreads;
+  static constexpr size_t smem_bytes(size_t key_bytes) {
+    return kHsAll * (key_bytes + 4 + 2) + kDistinctMax * (4 + 2) + 2 * kHsWords * 4;
+  }
+};
 static constexpr u32 kFlagAgg = 1u << 30;
 static constexpr u32 kFlagIncl = 2u << 30;
 static constexpr u32 kValMask = (1u << 30) - 1;
 
 // control words
-enum { kCtlNumHot = 0, kCtlTicket = 1, kCtlFallback = 2, kCtlHotElems = 3, kCtlWords = 16 };
+enum { kCtlNumHot = 0, kCtlTicket = 1, kCtlFallback = 2, kCtlHotElems = 3, kCtlSampleDistinct = 4, kCtlBigTables = 5,
+       kCtlWords = 16 };
 
 struct BLP {
   // input
@@ -148,8 +157,11 @@ __global__ void __launch_bounds__(256) k_bl_sample(const BLP p) {
 
 __global__ void __launch_bounds__(256) k_bl_hot(const BLP p) {
   const u32 s = blockIdx.x * blockDim.x + threadIdx.x;
-  if (s >= kSampSlots) return;
-  if (p.samp_cnt[s] < p.hot_thresh) return;
+  const u32 c = s < kSampSlots ? p.samp_cnt[s] : 0u;
+  // distinct keys of the sample (how much keys repeat decides the size of the buckets' tables)
+  const u32 occ = __ballot_sync(0xffffffffu, c > 0);
+  if ((threadIdx.x & 31) == 0 && occ) atomicAdd(&p.ctl[kCtlSampleDistinct], (u32)__popc(occ));
+  if (c < p.hot_thresh) return;
   const u64 key = p.samp_key[s];
   const u32 h = atomicAdd(&p.ctl[kCtlNumHot], 1u);
   if (h >= kHotMax) return;                                    // more candidates than places: the rest stay cold
@@ -385,6 +397,8 @@ __global__ void __launch_bounds__(1024) k_bl_plan(const BLP p) {
     p.hot_base[kHotMax] = hot_total;
     p.ctl[kCtlHotElems] = hot_total;
     if (s_max > p.cold_limit) p.ctl[kCtlFallback] = 1;   // keys are not spread evenly: use the sort
+    // more than three quarters of the sampled nonzeros have a key of their own: the big tables
+    p.ctl[kCtlBigTables] = (4ull * p.ctl[kCtlSampleDistinct] > 3ull * p.samp_m) ? 1u : 0u;
   }
 }
 
@@ -393,15 +407,15 @@ template <typename CK> struct CkT;
 template <> struct CkT<u32> { static constexpr u32 kEmpty = 0xFFFFFFFFu; };
 template <> struct CkT<u64> { static constexpr u64 kEmpty = 0xFFFFFFFFFFFFFFFFull; };
 
-// Home slot of a compact key with `rem` significant bits: its leading kHsBits bits (order preserving).
-template <typename CK>
+// Home slot of a compact key with `rem` significant bits: its leading kBits bits (order preserving).
+template <typename CK, int kBits>
 __device__ __forceinline__ u32 bucket_home(CK ck, int rem) {
-  return rem >= kHsBits ? (u32)(ck >> (rem - kHsBits)) : (u32)(ck << (kHsBits - rem));
+  return rem >= kBits ? (u32)(ck >> (rem - kBits)) : (u32)(ck << (kBits - rem));
 }
 
-template <typename CK>
+template <typename CK, int kBits>
 __device__ __forceinline__ int bucket_find(const CK* s_key, CK ck, int rem) {
-  u32 slot = bucket_home<CK>(ck, rem);
+  u32 slot = bucket_home<CK, kBits>(ck, rem);
   for (u32 probe = 0; probe < kRunMax; ++probe, ++slot) {
     const CK k = s_key[slot];
     if (k == ck) return (int)slot;
@@ -412,9 +426,9 @@ __device__ __forceinline__ int bucket_find(const CK* s_key, CK ck, int rem) {
 
 // Finds or inserts ck; returns the slot, or -1 when the probe sequence got longer than kRunMax
 // (keys that are not spread evenly inside the bucket). A new key sets its bit in the occupancy bitmap.
-template <typename CK>
+template <typename CK, int kBits>
 __device__ __forceinline__ int bucket_insert(CK* s_key, u32* s_bits, CK ck, int rem) {
-  u32 slot = bucket_home<CK>(ck, rem);
+  u32 slot = bucket_home<CK, kBits>(ck, rem);
   for (u32 probe = 0; probe < kRunMax; ++probe, ++slot) {
     CK k = s_key[slot];
     if (k == ck) return (int)slot;
@@ -446,8 +460,11 @@ __device__ __forceinline__ u32 bucket_block_scan(u32 v, u32* s_warp /* 9 words *
   return pre;
 }
 
-template <typename CK>
+template <typename CK, int kBits>
 __global__ void __launch_bounds__(kBucketThreads) k_bl_bucket(const BLP p) {
+  typedef BucketShape<kBits> Sh;
+  constexpr u32 kHsAll = Sh::kHsAll, kHsWords = Sh::kHsWords, kDistinctMax = Sh::kDistinctMax;
+  constexpr int kEntriesPerThread = Sh::kEntriesPerThread;
   extern __shared__ __align__(16) unsigned char smem[];
   CK* s_key = reinterpret_cast<CK*>(smem);                                     // table: compact keys
   u32* s_cnt = reinterpret_cast<u32*>(s_key + kHsAll);                         // per slot: count, then cursor
@@ -458,13 +475,16 @@ __global__ void __launch_bounds__(kBucketThreads) k_bl_bucket(const BLP p) {
   unsigned short* s_dense = s_rank + kHsAll;                                   // occupied slots in slot order
   __shared__ u32 s_ovf, s_b, s_ubase, s_warp[kBucketThreads / 32 + 1];
   const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+  // A CTA takes buckets by ticket until none is left (a few CTAs per SM are launched, not one per bucket).
+  for (;;) {
   if (t == 0) {
-    // one thread reads the flag for the whole CTA: other CTAs may raise it at any moment
-    s_b = ld_relaxed_gpu(&p.ctl[kCtlFallback]) ? 0xFFFFFFFFu : atomicAdd(&p.ctl[kCtlTicket], 1u);
+    // one thread reads the flags for the whole CTA: other CTAs may raise the fallback flag at any moment
+    const bool mine = (p.ctl[kCtlBigTables] != 0) == (kBits == 12);
+    s_b = (!mine || ld_relaxed_gpu(&p.ctl[kCtlFallback])) ? 0xFFFFFFFFu : atomicAdd(&p.ctl[kCtlTicket], 1u);
     s_ovf = 0;
   }
   {
-    // keys = all ones, counts = 0, bitmaps = 0, with 16-byte stores
+    // keys = all ones, counts = 0, bitmaps = 0, with 16-byte stores (while the ticket is on its way)
     uint4* k4 = reinterpret_cast<uint4*>(s_key);
     const u32 nk4 = kHsAll * sizeof(CK) / 16;
     for (u32 i = t; i < nk4; i += kBucketThreads) k4[i] = make_uint4(~0u, ~0u, ~0u, ~0u);
@@ -481,11 +501,21 @@ __global__ void __launch_bounds__(kBucketThreads) k_bl_bucket(const BLP p) {
   const int sh_l = p.nb_bits, sh_r = p.nb_bits + p.lo;
   const int rem = 64 - sh_r;                    // significant bits of a compact key
   const u64 posmask = p.packed ? ((1ull << p.lo) - 1) : 0ull;
+  // The first four nonzeros of every thread stay in registers for both passes over the bucket
+  // (a bucket of average size has no more), the rest is read again in pass 2.
+  u64 w0[4];
+  u32 p0[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const u32 j = t + q * kBucketThreads;
+    w0[q] = j < nb ? p.cold_words[cb + j] : 0;
+    p0[q] = (j < nb && !p.packed) ? p.cold_pos[cb + j] : 0;
+  }
   // hot keys of this bucket enter the table with their total count
   for (u32 i = h0 + t; i < h1; i += kBucketThreads) {
     const u32 h = p.shot_h[i];
     const CK ck = (CK)((p.shot_key[i] << sh_l) >> sh_r);
-    const int slot = bucket_insert<CK>(s_key, s_bits, ck, rem);
+    const int slot = bucket_insert<CK, kBits>(s_key, s_bits, ck, rem);
     if (slot < 0) { s_ovf = 1; continue; }
     s_cnt[slot] = p.bin_total[p.NB + h];
     s_rank[slot] = (unsigned short)h;
@@ -497,14 +527,14 @@ __global__ void __launch_bounds__(kBucketThreads) k_bl_bucket(const BLP p) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const u32 j = j0 + q * kBucketThreads;
-      wd[q] = j < nb ? p.cold_words[cb + j] : 0;
+      wd[q] = j0 == (u32)t ? w0[q] : (j < nb ? p.cold_words[cb + j] : 0);
     }
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const u32 j = j0 + q * kBucketThreads;
       if (j >= nb) break;
       const CK ck = (CK)((wd[q] << sh_l) >> sh_r);
-      const int slot = bucket_insert<CK>(s_key, s_bits, ck, rem);
+      const int slot = bucket_insert<CK, kBits>(s_key, s_bits, ck, rem);
       if (slot < 0) { s_ovf = 1; continue; }
       atomicAdd(&s_cnt[slot], 1u);
     }
@@ -644,15 +674,16 @@ __global__ void __launch_bounds__(kBucketThreads) k_bl_bucket(const BLP p) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const u32 j = j0 + q * kBucketThreads;
-      wd[q] = j < nb ? p.cold_words[cb + j] : 0;
-      ps[q] = (j < nb && !p.packed) ? p.cold_pos[cb + j] : 0;
+      const bool first = j0 == (u32)t;
+      wd[q] = first ? w0[q] : (j < nb ? p.cold_words[cb + j] : 0);
+      ps[q] = first ? p0[q] : ((j < nb && !p.packed) ? p.cold_pos[cb + j] : 0);
     }
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const u32 j = j0 + q * kBucketThreads;
       if (j >= nb) break;
       const CK ck = (CK)((wd[q] << sh_l) >> sh_r);
-      const int slot = bucket_find<CK>(s_key, ck, rem);
+      const int slot = bucket_find<CK, kBits>(s_key, ck, rem);
       if (slot < 0) continue;                     // cannot happen: the key was inserted in pass 1
       const u32 pos = p.packed ? (u32)(wd[q] & posmask) : ps[q];
       const u32 P = pb + atomicAdd(&s_cnt[slot], 1u);
@@ -661,6 +692,8 @@ __global__ void __launch_bounds__(kBucketThreads) k_bl_bucket(const BLP p) {
       p.csr_col[pos] = u;
       if (p.csc_val) p.csc_val[P] = p.vals[pos];
     }
+  }
+  __syncthreads();       // the tables are rebuilt for the next bucket
   }
 }
 
@@ -841,24 +874,30 @@ extern "C" int psb_bucket_localize(const void* in, int in_kind, psb_u64 seed, ui
   static bool attr_set = false;
   const int remaining = 64 - p.nb_bits - p.lo;      // key bits that distinguish keys inside a bucket
   const bool ck32 = remaining <= 31;
-  const size_t bucket_common = kHsAll * (4 + 2) + kDistinctMax * (4 + 2) + 2 * kHsWords * 4;
-  const size_t bucket_smem32 = kHsAll * 4 + bucket_common, bucket_smem64 = kHsAll * 8 + bucket_common;
   const size_t plan_smem = (size_t)p.NB * 12;
   if (!attr_set) {
     const size_t walk_max = kHotSlots * 10 + (size_t)(kMaxBuckets + kHotMax) * 4;
     cudaFuncSetAttribute((const void*)k_bl_plan, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kMaxBuckets * 12));
     cudaFuncSetAttribute((const void*)k_bl_walk<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)walk_max);
     cudaFuncSetAttribute((const void*)k_bl_walk<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)walk_max);
-    cudaFuncSetAttribute((const void*)k_bl_bucket<u32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bucket_smem32);
-    cudaFuncSetAttribute((const void*)k_bl_bucket<u64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bucket_smem64);
+    cudaFuncSetAttribute((const void*)k_bl_bucket<u32, 11>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BucketShape<11>::smem_bytes(4));
+    cudaFuncSetAttribute((const void*)k_bl_bucket<u32, 12>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BucketShape<12>::smem_bytes(4));
+    cudaFuncSetAttribute((const void*)k_bl_bucket<u64, 11>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BucketShape<11>::smem_bytes(8));
+    cudaFuncSetAttribute((const void*)k_bl_bucket<u64, 12>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BucketShape<12>::smem_bytes(8));
     attr_set = true;
   }
   k_bl_walk<false><<<p.G, kWalkThreads, walk_smem, stream>>>(p);
   k_bl_scan<<<(p.NBINS + 255) / 256, 256, 0, stream>>>(p);
   k_bl_plan<<<1, 1024, plan_smem, stream>>>(p);
   k_bl_walk<true><<<p.G, kWalkThreads, walk_smem, stream>>>(p);
-  if (ck32) k_bl_bucket<u32><<<p.NB, kBucketThreads, bucket_smem32, stream>>>(p);
-  else k_bl_bucket<u64><<<p.NB, kBucketThreads, bucket_smem64, stream>>>(p);
+  const u32 g11 = min(p.NB, p.G * 6), g12 = min(p.NB, p.G * 4);
+  if (ck32) {
+    k_bl_bucket<u32, 11><<<g11, kBucketThreads, BucketShape<11>::smem_bytes(4), stream>>>(p);
+    k_bl_bucket<u32, 12><<<g12, kBucketThreads, BucketShape<12>::smem_bytes(4), stream>>>(p);
+  } else {
+    k_bl_bucket<u64, 11><<<g11, kBucketThreads, BucketShape<11>::smem_bytes(8), stream>>>(p);
+    k_bl_bucket<u64, 12><<<g12, kBucketThreads, BucketShape<12>::smem_bytes(8), stream>>>(p);
+  }
   k_bl_hot_emit<<<p.G * 8, 256, 0, stream>>>(p);
   k_bl_gate<<<1, 1, 0, stream>>>(p.ctl, gate_out);
   cudaError_t e = cudaGetLastError();

@@ -58,7 +58,9 @@ int psb_localize(const psb_u64* sorted_keys, uint32_t* sorted_pos, uint32_t n,
 
 // ---------------------------------------------------------------- server shard table
 // Optimiser selection for the scalar-value table.
-enum { PSB_ALGO_FTRL = 0, PSB_ALGO_ADAGRAD = 1, PSB_ALGO_SGD = 2, PSB_ALGO_SUM = 3 };
+// PSB_ALGO_KEEP consumes a push round without touching the stored values (buffered KVVector: the
+// application reads the round out of the inboxes and decides what to do with it)
+enum { PSB_ALGO_FTRL = 0, PSB_ALGO_ADAGRAD = 1, PSB_ALGO_SGD = 2, PSB_ALGO_SUM = 3, PSB_ALGO_KEEP = 4 };
 enum { PSB_LR_CONSTANT = 0, PSB_LR_DECAY = 1 };
 enum { PSB_LOSS_LOGIT = 0, PSB_LOSS_SQUARE_HINGE = 1 };
 enum { PSB_QUANT_NONE = 0, PSB_QUANT_INT8 = 1, PSB_QUANT_FP16 = 2 };
@@ -132,6 +134,10 @@ typedef struct {
   uint32_t* bar;              // 2 words
   uint32_t* done;             // 1 word, zero on entry, left zero
   uint32_t* status;
+  // value width k (KVVector<K,V>(.., k), parameter/kv_vector.h:43-104): 0 or 1 = one value per key;
+  // k > 1: `grad` holds k values per unique key (key-major) and nnz must be 0. The inbox then holds
+  // count * k values per source, quantised in groups of 32 consecutive values.
+  int width;
 } PsbPushParams;
 
 // Server half of a push (kernel F1b): wait for the sources' flags, reduce
@@ -160,6 +166,9 @@ typedef struct {
   uint32_t* bar;
   uint32_t* done;
   uint32_t* status;
+  // value width k > 1 (sum entries only): the values live in wide_vals[slot * k + c], beside the table
+  int width;
+  float* wide_vals;
 } PsbApplyParams;
 
 // Two-sided pull fused with the margins (kernel F2, exchange form). One launch on
@@ -214,6 +223,17 @@ typedef struct {
   uint32_t* auc_hist;
   uint32_t* done;                        // 2 zeroed words
   uint32_t* status;
+  // key-caching filter (filter/key_caching.h:9-60), decided inside the kernel: when this round's key
+  // list is the previous round's (same fingerprint over every key and its position, same length),
+  // phase (a) sends no keys and the owners answer from the slot lists they remembered.
+  int key_cache;                         // 0 = off
+  psb_u64* kc_state;                     // 4 words: {fingerprint, length + 1} of even and of odd rounds
+  uint32_t* bar;                         // 2 zeroed words: grid barrier of the fingerprint pass
+  const uint32_t* slot_cache_prev[PSB_MAX_SHARDS];   // owner role: the slot lists of the round before
+  // value width k > 1: the owner answers with k values per key from wide_vals[slot * k + c]; the
+  // response buffers hold k values per unique key (no margins in that case: n_rows must be 0)
+  int width;
+  const float* wide_vals;
 } PsbPullExchangeParams;
 
 int psb_pull_exchange(const PsbPullExchangeParams* p, cudaStream_t stream);

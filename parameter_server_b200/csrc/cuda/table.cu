@@ -68,9 +68,9 @@ __device__ __forceinline__ float opt_step(const PsbOptimizer& o, float g, float&
     s0 += 1.f;    // number of updates of this key
     float eta = lr_eval(o, sqrtf(s0));
     w = prox(o, w - eta * g, eta);
-  } else {        // PSB_ALGO_SUM: plain accumulate (KVVector PLUS / custom "+=" entries)
+  } else if (o.algo == PSB_ALGO_SUM) {   // plain accumulate (KVVector PLUS / custom "+=" entries)
     w += g;
-  }
+  }                                       // PSB_ALGO_KEEP: the stored value stays
   return w;
 }
 
@@ -257,6 +257,22 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
   PSB_TSTAMP(0);
   // ---- (a) my keys to their owners
   if (p.phases & 1) {
+  bool key_hit = false;
+  if (p.key_cache) {
+    // Key caching: fingerprint of the whole list (every key mixed with its position), summed over the
+    // grid; all CTAs then take the same decision. The two accumulators alternate by round parity.
+    const u32 par = (p.ts1 - 1) & 1u;
+    unsigned long long fp = 0;
+    for (u32 u = gtid; u < U; u += gsize) fp += fmix64(p.ukeys[u] ^ ((u64)u * 0x9E3779B97F4A7C15ull));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) fp += __shfl_xor_sync(0xffffffffu, fp, o);
+    if ((threadIdx.x & 31) == 0 && fp) atomicAdd(&p.kc_state[2 * par], fp);
+    if (gtid == 0) p.kc_state[2 * par + 1] = (u64)U + 1;
+    __threadfence();
+    if (!grid_barrier(p.bar, p.status)) return;
+    const u64 cur = __ldcg(&p.kc_state[2 * par]), prev = __ldcg(&p.kc_state[2 * (par ^ 1)]);
+    key_hit = p.ts1 > 1 && cur == prev && __ldcg(&p.kc_state[2 * (par ^ 1) + 1]) == (u64)U + 1;
+  }
   // four independent keys per thread and trip, loads first
   for (u32 u0 = gtid; u0 < U; u0 += 4 * gsize) {
     u64 k[4];
@@ -271,7 +287,7 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
       if (u >= U) break;
       int s = owner_of(s_off, S, u);
       u32 j = u - s_off[s];
-      if (j < p.req_cap) p.req_keys[s][j] = k[q];
+      if (j < p.req_cap && !key_hit) p.req_keys[s][j] = k[q];
       if (p.grad_zero) p.grad_zero[u] = 0.f;
     }
   }
@@ -285,11 +301,15 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
     u32 c = s_off[s + 1] - s_off[s];
     if (c > p.req_cap) { set_status(p.status, kInboxOverflow); c = p.req_cap; }
     __threadfence_system();
-    p.req_hdr[s][0] = c;
+    p.req_hdr[s][0] = c | (key_hit ? 0x80000000u : 0u);     // top bit: no keys, answer from the remembered slots
     p.req_hdr[s][1] = s_off[s];
     __threadfence_system();
     st_release_sys(p.req_ready[s], p.ts1);
-    if (s == 0) atomicExch(&p.done[0], 0u);
+    if (s == 0) {
+      atomicExch(&p.done[0], 0u);
+      // every CTA has read the other parity's fingerprint by now: clear it for the next round
+      if (p.key_cache) p.kc_state[2 * (((p.ts1 - 1) & 1u) ^ 1)] = 0;
+    }
   }
   }
   PSB_TSTAMP(2);
@@ -310,12 +330,29 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
       } else {
         set_status(p.status, kWaitTimeout);
       }
-      s_n = min(n, p.req_cap);
+      s_n = min(n & 0x7fffffffu, p.req_cap) | (n & 0x80000000u);
       s_base = base;
     }
     __syncthreads();
     PSB_TSTAMP(3);
-    const u32 n = s_n, base = s_base;
+    const u32 n = s_n & 0x7fffffffu, base = s_base;
+    const int kw = p.width > 1 ? p.width : 1;
+    if (s_n & 0x80000000u) {
+      // key-cache hit at the source: same keys as in the round before, so the same slots
+      for (u32 j = gtid; j < n; j += gsize) {
+        const u32 sc = p.slot_cache_prev[r][j] & 0x7fffffffu;
+        p.slot_cache[r][j] = sc;
+        if (kw == 1) {
+          float w = 0.f;
+          if (sc != 0x7fffffffu) w = __ldcg(&tab[sc].w);
+          p.resp_w[r][base + j] = w;
+        } else {
+          for (int c = 0; c < kw; ++c)
+            p.resp_w[r][(size_t)(base + j) * kw + c] = sc != 0x7fffffffu ? __ldcg(&p.wide_vals[(size_t)sc * kw + c]) : 0.f;
+        }
+      }
+      continue;
+    }
     // Four keys per thread and trip. The first probe of each is one 16-byte load
     // that returns key and weight, issued for all four before any is examined;
     // only a miss on that slot (collision or new key) takes the probing path.
@@ -349,7 +386,12 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
           else set_status(p.status, kTableFull);
         }
         p.slot_cache[r][j] = sc;
-        p.resp_w[r][base + j] = w;
+        if (kw == 1) {
+          p.resp_w[r][base + j] = w;
+        } else {
+          for (int c = 0; c < kw; ++c)
+            p.resp_w[r][(size_t)(base + j) * kw + c] = sc != 0x7fffffffu ? __ldcg(&p.wide_vals[(size_t)sc * kw + c]) : 0.f;
+        }
       }
     }
   }
@@ -544,18 +586,40 @@ __global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
   }
   PSB_TSTAMP(2);
 
-  // phase 2: range partition + (quantise) + peer stores, 32 records per warp step
+  // phase 2: range partition + (quantise) + peer stores, 32 values per warp step. With value width k
+  // an owner's slice is cnt keys and cnt * k values (key-major); the group prefix counts value groups.
   const bool omit_keys = !p.send_keys || (p.key_hit && *p.key_hit);
+  const u32 kw = p.width > 1 ? (u32)p.width : 1u;
+  if (kw > 1) {
+    // group prefix over values instead of keys (recomputed by every CTA's thread 0)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      u32 acc = 0;
+      for (int s = 0; s < S; ++s) {
+        s_gp[s] = acc;
+        acc += (min(s_off[s + 1] - s_off[s], p.inbox_cap) * kw + 31) / 32;
+      }
+      s_gp[S] = acc;
+    }
+    __syncthreads();
+    if (!omit_keys)
+      for (u32 u = gtid; u < s_off[S]; u += gsize) {
+        const int s = owner_of(s_off, S, u);
+        const u32 j = u - s_off[s];
+        if (j < p.inbox_cap) p.inbox_keys[s][j] = p.ukeys[u];
+      }
+  }
   const u32 G = s_gp[S];
   for (u32 g = gwarp; g < G; g += nwarps) {
     int s = 0;
     while (s + 1 < S && g >= s_gp[s + 1]) ++s;
-    u32 cnt = min(s_off[s + 1] - s_off[s], p.inbox_cap);
+    u32 cnt = min(s_off[s + 1] - s_off[s], p.inbox_cap) * kw;       // values of this owner's slice
     u32 j0 = (g - s_gp[s]) * 32, j = j0 + lane;
     bool valid = j < cnt;
-    u32 u = s_off[s] + j;
+    size_t u = (size_t)s_off[s] * kw + j;
     float v = valid ? __ldcg(&p.grad[u]) : 0.f;
-    if (!omit_keys && valid) p.inbox_keys[s][j] = p.ukeys[u];
+    if (kw == 1 && !omit_keys && valid) p.inbox_keys[s][j] = p.ukeys[u];
+    const u32 vcap = p.inbox_cap * kw;
     if (p.quant == PSB_QUANT_NONE) {
       if (valid) ((float*)p.inbox_vals[s])[j] = v;
     } else {
@@ -564,12 +628,12 @@ __global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
       if (p.quant == PSB_QUANT_INT8) {
         float scale = amax / 127.f;
         int code = amax > 0.f ? __float2int_rn(v / scale) : 0;
-        signed char* codes = (signed char*)(scales + scale_words(p.inbox_cap));
+        signed char* codes = (signed char*)(scales + scale_words(vcap));
         if (valid) codes[j] = (signed char)max(-127, min(127, code));
         if (lane == 0) scales[j0 >> 5] = scale;
       } else {
         float scale = amax > 0.f ? amax : 1.f;
-        __half* codes = (__half*)(scales + scale_words(p.inbox_cap));
+        __half* codes = (__half*)(scales + scale_words(vcap));
         if (valid) codes[j] = __float2half_rn(v / scale);
         if (lane == 0) scales[j0 >> 5] = scale;
       }
@@ -642,6 +706,32 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
   const SlotMap sm{p.mask, p.key_begin, p.slot_mult};
   StatAcc st;
 
+  if (p.width > 1) {
+    // k values per key, sum entries: every record adds its k values to wide_vals[slot * k ..]. One
+    // source: plain read-modify-write (a slot belongs to one record); several: atomic adds.
+    const u32 kw = (u32)p.width, vcap = p.inbox_cap * kw;
+    for (u32 i = gtid; i < total; i += gsize) {
+      int r = 0;
+      while (r + 1 < S && i >= s_pre[r + 1]) ++r;
+      const u32 j = i - s_pre[r];
+      long long slot;
+      if (s_cached[r]) {
+        const u32 sc = p.slot_cache[r][j] & 0x7fffffffu;
+        slot = sc != 0x7fffffffu ? (long long)sc : -1;
+      } else {
+        slot = table_find<true>(tab, sm, p.inbox_keys[r][j], kMaxProbe);
+        if (slot < 0) set_status(p.status, kTableFull);
+      }
+      if (slot < 0) continue;
+      float* dst = p.wide_vals + (size_t)slot * kw;
+      if (p.opt.algo != PSB_ALGO_KEEP)
+        for (u32 c = 0; c < kw; ++c) {
+          const float g = inbox_value(p.inbox_vals[r], p.quant, vcap, j * kw + c);
+          if (single) dst[c] += g; else atomicAdd(&dst[c], g);
+        }
+      st.n += 1;
+    }
+  } else {
   // phase A: locate the slot of every record; single source -> update in place,
   // several sources -> accumulate into gacc and elect one leader per key
   // four records per thread and trip: values and slots first, then the entries
@@ -745,6 +835,7 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
         st.add(w, w_old);
       }
     }
+  }
   }
   PSB_TSTAMP(4);
   block_add4(st.d_nnz, st.w2, st.dw2, st.n, p.stats);

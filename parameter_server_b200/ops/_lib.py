@@ -17,7 +17,7 @@ from pathlib import Path
 import torch
 
 MAX_SHARDS = 16
-ALGO_FTRL, ALGO_ADAGRAD, ALGO_SGD, ALGO_SUM = 0, 1, 2, 3
+ALGO_FTRL, ALGO_ADAGRAD, ALGO_SGD, ALGO_SUM, ALGO_KEEP = 0, 1, 2, 3, 4
 LR_CONSTANT, LR_DECAY = 0, 1
 LOSS_LOGIT, LOSS_SQUARE_HINGE = 0, 1
 QUANT_NONE, QUANT_INT8, QUANT_FP16 = 0, 1, 2
@@ -64,6 +64,8 @@ class PullExchangeParams(C.Structure):
         ("row_ptr", _vp), ("n_rows", _u32), ("fixed_z", _u32), ("csr_col", _vp), ("csr_val", _vp), ("y", _vp),
         ("loss", _i32), ("gcoef", _vp), ("margin", _vp), ("stats", _vp), ("auc_hist", _vp),
         ("done", _vp), ("status", _vp),
+        ("key_cache", _i32), ("kc_state", _vp), ("bar", _vp), ("slot_cache_prev", _vp * MAX_SHARDS),
+        ("width", _i32), ("wide_vals", _vp),
     ]
 
 
@@ -77,6 +79,7 @@ class PushParams(C.Structure):
         ("ukeys", _vp), ("n_unique", _vp), ("own_off", _vp),
         ("nnz", _u32), ("csc_row", _vp), ("csc_val", _vp), ("flagbits", _vp), ("wordbase", _vp),
         ("gcoef", _vp), ("grad", _vp), ("bar", _vp), ("done", _vp), ("status", _vp),
+        ("width", _i32),
     ]
 
 
@@ -91,6 +94,7 @@ class ApplyParams(C.Structure):
         ("slot_cache", _vp * MAX_SHARDS),
         ("opt", Optimizer), ("stats", _vp), ("applied", _vp), ("wait_iters", _u32),
         ("bar", _vp), ("done", _vp), ("status", _vp),
+        ("width", _i32), ("wide_vals", _vp),
     ]
 
 

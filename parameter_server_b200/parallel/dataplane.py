@@ -38,7 +38,7 @@ CTRL_WORDS = 1024
 
 @dataclass
 class OptimizerConfig:
-    algo: str = "ftrl"            # ftrl | adagrad | sgd | sum
+    algo: str = "ftrl"            # ftrl | adagrad | sgd | sum | keep (consume a round, leave the values)
     alpha: float = 0.1
     beta: float = 1.0
     l1: float = 1.0
@@ -47,7 +47,7 @@ class OptimizerConfig:
 
     def to_c(self) -> Optimizer:
         algo = {"ftrl": _lib.ALGO_FTRL, "adagrad": _lib.ALGO_ADAGRAD, "sgd": _lib.ALGO_SGD,
-                "sum": _lib.ALGO_SUM}[self.algo]
+                "sum": _lib.ALGO_SUM, "keep": _lib.ALGO_KEEP}[self.algo]
         lr = _lib.LR_CONSTANT if self.lr_type == "constant" else _lib.LR_DECAY
         return Optimizer(algo, lr, self.alpha, self.beta, self.l1, self.l2)
 
@@ -62,6 +62,8 @@ class PlaneConfig:
     ordered_slots: bool = False             # keys are uniformly hashed: order-preserving slot map
     key_cache: bool = False                 # key-caching filter: skip keys (push) and probes (pull) on a repeated key list
     pull_cap: int = 0                       # unique keys per worker minibatch for the two-sided pull (0: off)
+    width: int = 1                          # values per key (k of KVVector<K,V>(.., k)); k > 1: sum entries, exchange pull
+    channels: int = 1                       # independent key/value sets (the KVVector channels), one table each
 
     def quant_code(self) -> int:
         return {"none": _lib.QUANT_NONE, "int8": _lib.QUANT_INT8, "fp16": _lib.QUANT_FP16}[self.quant]
@@ -72,15 +74,18 @@ def heap_layout(cfg: PlaneConfig, world: int) -> HeapLayout:
     assert cfg.table_capacity < (1 << 31)
     assert 8 + 3 * cfg.ring * world <= CTRL_WORDS
     lay = HeapLayout()
+    k = max(1, cfg.width)
     lay.add("ctrl", CTRL_WORDS * 4)
-    lay.add("table", cfg.table_capacity * 32)
+    lay.add("table", cfg.channels * cfg.table_capacity * 32)
+    if k > 1:
+        lay.add("wide_vals", cfg.channels * cfg.table_capacity * k * 4)
     lay.add("inbox_keys", cfg.ring * world * cfg.inbox_cap * 8)
-    lay.add("inbox_vals", cfg.ring * world * cfg.inbox_cap * 4 + 256)
+    lay.add("inbox_vals", cfg.ring * world * cfg.inbox_cap * k * 4 + 256)
     if cfg.pull_cap:
         # two-sided pull: request areas per (parity, source), response buffer per parity, flags
         lay.add("xflags", 4 * (16 * world + 16))
         lay.add("req_keys", 2 * world * cfg.inbox_cap * 8)
-        lay.add("resp_w", 2 * cfg.pull_cap * 4)
+        lay.add("resp_w", 2 * cfg.pull_cap * k * 4)
     return lay
 
 
@@ -113,6 +118,7 @@ class DataPlane:
         # key-caching filter state: signature of the previous key list, and the slots found for it
         self.sig_state = torch.zeros(4, dtype=torch.int32, device=dev)
         self.sig_scratch = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.kc_state = torch.zeros(4, dtype=torch.int64, device=dev)       # exchange pull: fingerprints by round parity
         self.pull_slot_cache = None
         # order-preserving slot multiplier per shard: floor(capacity * 2^64 / range_size)
         self.slot_mult = []
@@ -122,8 +128,13 @@ class DataPlane:
             self.slot_mult.append(m if m < (1 << 64) else 0)
         self.applied_ts1 = 0
         self.ctrl = fabric.view(self.layout["ctrl"], (CTRL_WORDS,), torch.int32)
+        self.width = max(1, cfg.width)
+        assert self.width == 1 or (cfg.pull_cap and opt.algo in ("sum", "keep")), \
+            "values of width k > 1 are sum entries (KVVector) and use the exchange pull"
         check(_lib.lib().psb_table_init(fabric.ptr(self.rank, self.layout["table"]),
-                                        cfg.table_capacity, stream_ptr()), "table init")
+                                        cfg.channels * cfg.table_capacity, stream_ptr()), "table init")
+        if self.width > 1:
+            fabric.view(self.layout["wide_vals"], (cfg.channels * cfg.table_capacity * self.width,), torch.float32).zero_()
 
     # ---------------------------------------------------------------- addresses
     def _slot_cache_ptr(self, ts: int, source: int) -> int:
@@ -146,7 +157,7 @@ class DataPlane:
         return self.fabric.ptr(owner, self.layout["inbox_keys"] + ((q * self.S + src) * self.cfg.inbox_cap) * 8)
 
     def _inbox_vals(self, owner: int, q: int, src: int) -> int:
-        return self.fabric.ptr(owner, self.layout["inbox_vals"] + ((q * self.S + src) * self.cfg.inbox_cap) * 4)
+        return self.fabric.ptr(owner, self.layout["inbox_vals"] + ((q * self.S + src) * self.cfg.inbox_cap) * 4 * self.width)
 
     def _bar(self, kind: int) -> int:
         return self.sync_words.data_ptr() + 16 * kind
@@ -154,8 +165,15 @@ class DataPlane:
     def _done(self, kind: int) -> int:
         return self.sync_words.data_ptr() + 16 * kind + 8
 
-    def table_ptr(self, rank: Optional[int] = None) -> int:
-        return self.fabric.ptr(self.rank if rank is None else rank, self.layout["table"])
+    def table_ptr(self, rank: Optional[int] = None, channel: int = 0) -> int:
+        assert 0 <= channel < self.cfg.channels
+        return self.fabric.ptr(self.rank if rank is None else rank,
+                               self.layout["table"] + channel * self.cfg.table_capacity * 32)
+
+    def wide_vals_ptr(self, channel: int = 0) -> int:
+        if self.width == 1:
+            return 0
+        return self.fabric.ptr(self.rank, self.layout["wide_vals"] + channel * self.cfg.table_capacity * self.width * 4)
 
     # ---------------------------------------------------------------- key-caching filter
     def key_signature(self, b, stream=None):
@@ -202,7 +220,8 @@ class DataPlane:
         return self.fabric.ptr(rank, self.layout["xflags"] + 4 * (((kind * 2) + par) * self.S + idx))
 
     def pull_exchange(self, b, ts: int, *, need_applied: int = 0, with_margins: bool = True, loss: int = 0,
-                      auc_hist: Optional[torch.Tensor] = None, phases: int = 7, wait_iters: int = 0, stream=None):
+                      auc_hist: Optional[torch.Tensor] = None, phases: int = 7, wait_iters: int = 0, channel: int = 0,
+                      stream=None):
         """Exchange form of F2 for round ``ts``: keys go to the owners in bulk, the
         owners look them up (inserting absent keys), remember the slots for the push
         of the same round and store the weights into this worker's response buffer.
@@ -220,7 +239,7 @@ class DataPlane:
             p.req_ready[s] = self._xflag(s, 0, par, self.rank)
             p.my_req_keys[s] = self.fabric.ptr(self.rank, self.layout["req_keys"] + (par * self.S + s) * req_bytes)
             p.my_req_ready[s] = self._xflag(self.rank, 0, par, s)
-            p.resp_w[s] = self.fabric.ptr(s, self.layout["resp_w"] + par * cfg.pull_cap * 4)
+            p.resp_w[s] = self.fabric.ptr(s, self.layout["resp_w"] + par * cfg.pull_cap * 4 * self.width)
             p.resp_ready[s] = self._xflag(s, 1, par, self.rank)
             p.my_resp_ready[s] = self._xflag(self.rank, 1, par, s)
             p.slot_cache[s] = self._slot_cache_ptr(ts, s)
@@ -228,10 +247,12 @@ class DataPlane:
             # header = two consecutive words {count, base} per (parity, source)
             p.req_hdr[s] = self.fabric.ptr(s, self.layout["xflags"] + 4 * (8 * self.S + (par * self.S + self.rank) * 2))
             p.my_req_hdr[s] = self.fabric.ptr(self.rank, self.layout["xflags"] + 4 * (8 * self.S + (par * self.S + s) * 2))
-        p.table, p.mask = self.table_ptr(), cfg.table_capacity - 1
+        p.table, p.mask = self.table_ptr(channel=channel), cfg.table_capacity - 1
         p.key_begin, p.slot_mult = self.bounds_host[self.rank], self.slot_mult[self.rank]
         p.applied = self._ctrl(self.rank, 0)
-        p.my_resp_w = self.fabric.ptr(self.rank, self.layout["resp_w"] + par * cfg.pull_cap * 4)
+        p.width, p.wide_vals = self.width, self.wide_vals_ptr(channel)
+        assert self.width == 1 or not with_margins, "margins need scalar values"
+        p.my_resp_w = self.fabric.ptr(self.rank, self.layout["resp_w"] + par * cfg.pull_cap * 4 * self.width)
         p.ukeys, p.n_unique, p.own_off, p.grad_zero = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off), ptr(b.grad)
         if with_margins:
             p.row_ptr, p.n_rows, p.fixed_z = ptr(b.row_ptr), b.n_rows, b.fixed_z
@@ -239,11 +260,19 @@ class DataPlane:
             p.gcoef, p.margin = ptr(b.gcoef), ptr(b.margin)
         p.loss, p.stats, p.auc_hist = loss, ptr(self.pull_stats), ptr(auc_hist)
         p.done, p.status = self.sync_words.data_ptr() + 48, ptr(self.status)
+        if cfg.key_cache and phases == 7:
+            # the key-caching filter is decided inside the kernel (needs all three roles in one launch:
+            # the fingerprint pass ends with a grid barrier)
+            p.key_cache, p.kc_state, p.bar = 1, ptr(self.kc_state), self.sync_words.data_ptr() + 64
+            for s in range(self.S):
+                p.slot_cache_prev[s] = self._slot_cache_ptr(ts - 1, s) if ts > 0 else self._slot_cache_ptr(ts, s)
         check(_lib.lib().psb_pull_exchange(C.byref(p), stream_ptr(stream)), "pull_exchange")
 
     def response_weights(self, ts: int, n: int) -> torch.Tensor:
         """The weights this worker received in the exchange of round ``ts``."""
-        return self.fabric.view(self.layout["resp_w"] + (ts & 1) * self.cfg.pull_cap * 4, (n,), torch.float32)
+        k = self.width
+        v = self.fabric.view(self.layout["resp_w"] + (ts & 1) * self.cfg.pull_cap * 4 * k, (n * k,), torch.float32)
+        return v if k == 1 else v.view(n, k)
 
     # ---------------------------------------------------------------- worker: push
     def push(self, b, ts: int, *, with_gradient: bool = True, send_keys: bool = True, stream=None):
@@ -272,17 +301,21 @@ class DataPlane:
         else:
             p.nnz = 0
         p.grad = ptr(b.grad)
+        p.width = self.width
+        assert self.width == 1 or not with_gradient
         p.bar, p.done, p.status = self._bar(1), self._done(1), ptr(self.status)
         check(_lib.lib().psb_push(C.byref(p), stream_ptr(stream)), "push")
 
     # ---------------------------------------------------------------- server: apply
-    def apply(self, ts: int, *, cached=None, wait_iters: int = 0, stream=None):
-        """F1b: apply push round ``ts`` from every alive source."""
+    def apply(self, ts: int, *, cached=None, wait_iters: int = 0, channel: int = 0, opt: Optional[OptimizerConfig] = None,
+              stream=None):
+        """F1b: apply push round ``ts`` from every alive source (into the table of ``channel``)."""
         cfg = self.cfg
         q = ts % cfg.ring
         p = ApplyParams()
         p.S, p.ts1, p.inbox_cap, p.quant = self.S, ts + 1, cfg.inbox_cap, cfg.quant_code()
-        p.table, p.mask = self.table_ptr(), cfg.table_capacity - 1
+        p.table, p.mask = self.table_ptr(channel=channel), cfg.table_capacity - 1
+        p.width, p.wide_vals = self.width, self.wide_vals_ptr(channel)
         p.key_begin, p.slot_mult = self.bounds_host[self.rank], self.slot_mult[self.rank]
         for r in range(self.S):
             p.inbox_keys[r] = self._inbox_keys(self.rank, q, r)
@@ -293,7 +326,7 @@ class DataPlane:
             p.alive[r] = 1 if self.alive[r] else 0
             p.cached[r] = 1 if (cached is not None and cached[r]) else 0
             p.slot_cache[r] = self._slot_cache_ptr(ts, r)
-        p.opt = self.opt.to_c()
+        p.opt = (opt or self.opt).to_c()
         p.stats, p.applied = ptr(self.push_stats), self._ctrl(self.rank, 0)
         p.wait_iters = wait_iters
         p.bar, p.done, p.status = self._bar(2), self._done(2), ptr(self.status)
