@@ -299,8 +299,15 @@ def run_evaluation(conf, verbose=True):
 
 
 def run_darlin(conf, verbose=True):
+    """Darlin (block coordinate descent, L1 logistic regression) on the GPUs. Preprocessing runs on the
+    device (``models/darlin_prep.py``): tail-feature filter through the count-min kernels, the global
+    column space as a device union of the ranks' key sets, feature groups cut into
+    ``ceil(nnz per row * feature_block_ratio)`` blocks, prior groups first; ``save_model_every_n_iter``
+    writes intermediate models."""
     from ..models.darlin import DarlinConfig, DarlinRank, darlin_heap_bytes, run_darlin as drive
+    from ..models.darlin_prep import build_columns, plan_blocks
     from ..parallel.fabric import Fabric
+    from ..utils.range import Range
 
     dist, rank, world = _dist()
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -308,8 +315,10 @@ def run_darlin(conf, verbose=True):
     l1, _ = _penalty(conf)
     data = conf["training_data"]
     files = _files(data)[rank::world]
-    reader = core.StreamReader(files, data.get("format", "TEXT"), data.get("text", "LIBSVM"), True)
-    idx, off, ys, vs, binary = [], [np.zeros(1, np.int64)], [], [], True
+    by_group = str(data.get("ignore_feature_group", "false")) != "true"
+    reader = core.StreamReader(files, data.get("format", "TEXT"), data.get("text", "LIBSVM"), not by_group)
+    groups = {}          # group id -> lists of chunks
+    ys, n_rows = [], 0
     while True:
         got = reader.read_matrices(100000) if files else None
         if got is None:
@@ -317,48 +326,83 @@ def run_darlin(conf, verbose=True):
         yv, mats = got
         if not mats:
             continue
-        m = mats[0]
-        idx.append(m["index"]); off.append(m["offset"][1:].astype(np.int64) + off[-1][-1]); ys.append(yv)
-        if not m["binary"]:
-            binary = False; vs.append(m["value"])
-    keys = np.concatenate(idx) if idx else np.zeros(0, np.uint64)
-    row_ptr = np.concatenate(off).astype(np.int32)
+        for m in mats:
+            g = groups.setdefault(int(m["id"]), dict(id=int(m["id"]), index=[], offset=[np.zeros(1, np.int64)], value=[],
+                                                     binary=True, rows=0))
+            # a group may be absent from earlier chunks: its rows there are empty
+            if g["rows"] < n_rows:
+                g["offset"].append(np.full(n_rows - g["rows"], g["offset"][-1][-1], np.int64))
+            g["index"].append(m["index"])
+            g["offset"].append(m["offset"][1:].astype(np.int64) + g["offset"][-1][-1])
+            if not m["binary"]:
+                g["binary"] = False
+                g["value"].append(m["value"])
+            elif not g["binary"]:
+                g["value"].append(np.ones(len(m["index"]), np.float32))
+            g["rows"] = n_rows + len(yv)
+        ys.append(yv)
+        n_rows += len(yv)
+    glist = []
+    for g in groups.values():
+        if g["rows"] < n_rows:
+            g["offset"].append(np.full(n_rows - g["rows"], g["offset"][-1][-1], np.int64))
+        glist.append(dict(id=g["id"], index=np.concatenate(g["index"]) if g["index"] else np.zeros(0, np.uint64),
+                          offset=np.concatenate(g["offset"]), binary=g["binary"],
+                          value=np.concatenate(g["value"]) if g["value"] else np.zeros(0, np.float32)))
+    if not glist:
+        glist = [dict(id=0, index=np.zeros(0, np.uint64), offset=np.zeros(n_rows + 1, np.int64), binary=True,
+                      value=np.zeros(0, np.float32))]
     y = np.where(np.concatenate(ys) > 0, 1.0, -1.0).astype(np.float32) if ys else np.zeros(0, np.float32)
+    tail = int(d.get("tail_feature_freq", 0))
+    nnz_local = sum(len(g["index"]) for g in glist)
+    cells = int(min(1 << 28, max(1 << 16, float(d.get("countmin_n_ratio", 2.0)) * max(1, nnz_local) * world)))
+    col, row_ptr, vals, space = build_columns(glist, n_rows, dev, dist=dist, tail_freq=tail, countmin_cells=cells,
+                                              countmin_k=int(d.get("countmin_k", 2)))
+    prior = d.get("prior_fea_group", [])
+    prior = [int(x) for x in (prior if isinstance(prior, list) else [prior])]
+    plan = plan_blocks(space, feature_block_ratio=float(d.get("feature_block_ratio", 4)),
+                       max_block_cols=int(os.environ.get("PSB_DARLIN_BLOCK", str(1 << 16))), prior_groups=prior,
+                       prior_iters=int(d.get("num_iter_for_prior_fea_group", 5)))
     cfg = DarlinConfig(lambda_l1=l1, eta=float(conf.get("learning_rate", {}).get("alpha", 1.0)),
                        delta_init=float(d.get("delta_init_value", 1)), delta_max=float(d.get("delta_max_value", 5)),
                        kkt_ratio=float(d.get("kkt_filter_threshold_ratio", 10)), max_pass=int(d.get("max_pass_of_data", 10)),
                        epsilon=float(d.get("epsilon", 1e-4)), tau=int(d.get("max_block_delay", 0)),
-                       block_cols=int(os.environ.get("PSB_DARLIN_BLOCK", str(1 << 16))),
-                       random_block_order=d.get("random_feature_block_order", "true") == "true")
+                       block_cols=max(1, plan.block_cols),
+                       random_block_order=d.get("random_feature_block_order", "true") == "true",
+                       key_range=Range(0, max(1, space.n_cols)))
     hb = darlin_heap_bytes(cfg, world)
     fab = Fabric.from_process_group(hb) if world > 1 else Fabric.single(hb, dev)
-    uniq = np.unique(keys)
-    if dist is not None:
-        gathered = [None] * world
-        dist.all_gather_object(gathered, uniq)
-        uniq = np.unique(np.concatenate(gathered))
-    r = DarlinRank(fab, cfg, torch.from_numpy(keys.view(np.int64)).to(dev), torch.from_numpy(y).to(dev),
-                   row_ptr=torch.from_numpy(row_ptr).to(dev),
-                   vals=None if binary else torch.from_numpy(np.concatenate(vs)).to(dev),
-                   global_keys=torch.from_numpy(uniq.view(np.int64)).to(dev))
+    # the block kernels see column indices as keys; the column space is their identity list
+    r = DarlinRank(fab, cfg, col.to(torch.int64), torch.from_numpy(y).to(dev), row_ptr=row_ptr, vals=vals,
+                   global_keys=torch.arange(space.n_cols, dtype=torch.int64, device=dev))
+    r.set_blocks(plan.blocks, plan.prior)
 
-    def all_reduce(vals, op):
+    def all_reduce(vals_, op):
         if dist is None:
-            return vals
-        t = torch.tensor(vals, dtype=torch.float64, device=dev)
+            return vals_
+        t = torch.tensor(vals_, dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.SUM if op == "sum" else dist.ReduceOp.MAX)
         return t.tolist()
 
+    out = conf.get("model_output", {}).get("file")
+    out = (out if isinstance(out, str) else out[0]) if out else None
+
+    def save(suffix=""):
+        if not out:
+            return
+        cols_, w = r.my_model()
+        keys = space.col_key[torch.from_numpy(cols_.astype(np.int64)).to(dev)].cpu().numpy().view(np.uint64)
+        os.makedirs(os.path.dirname(out) or ".", exist_ok=True)
+        write_model(f"{out}{suffix}_S{rank}", keys, w)
+
     n_ex = int(all_reduce([float(len(y))], "sum")[0])
     if rank == 0 and verbose:
+        print(f"  {n_ex} examples, {space.n_cols} features in {len(space.groups)} group(s), {len(plan.blocks)} blocks"
+              + (f", tail filter dropped {space.dropped_nnz} local nonzeros" if tail else ""))
         print("  iter |  objective    relative   |w|_0   | violation  active set")
-    hist = drive([r], all_reduce=all_reduce if dist is not None else None, verbose=verbose and rank == 0, num_examples=n_ex)
-    out = conf.get("model_output", {}).get("file")
-    if out:
-        out = out if isinstance(out, str) else out[0]
-        k, w = r.my_model()
-        os.makedirs(os.path.dirname(out) or ".", exist_ok=True)
-        write_model(f"{out}_S{rank}", k, w)
+    hist = drive([r], all_reduce=all_reduce if dist is not None else None, verbose=verbose and rank == 0, num_examples=n_ex,
+                 save_every=int(d.get("save_model_every_n_iter", 0)), save_fn=lambda it: save(f"_iter_{it}"))
+    save()
     if dist is not None:
         dist.barrier()
         fab.close()

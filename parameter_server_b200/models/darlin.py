@@ -94,15 +94,19 @@ class DarlinRank:
         self.step = 0
 
     def set_global_keys(self, global_keys: torch.Tensor):
+        """``global_keys``: the sorted global key list (uint64 as int64, on the device). The local keys'
+        columns and the shards' column ranges are found on the device (binary searches over the list)."""
         cfg, dev = self.cfg, self.dev
         self.global_keys = global_keys
         self.n_cols = global_keys.numel()
-        gk = global_keys.cpu().numpy().view(np.uint64)
-        lk = self.local_keys.cpu().numpy().view(np.uint64)
-        self.gcol = torch.from_numpy(np.searchsorted(gk, lk).astype(np.int32)).to(dev)
-        self.gcol_host = np.searchsorted(gk, lk)
+        sign = -(1 << 63)                                 # signed order of (k ^ sign) = unsigned order of k
+        gk = global_keys ^ sign
+        gcol = torch.searchsorted(gk, self.local_keys ^ sign)
+        self.gcol = gcol.to(torch.int32)
+        self.gcol_host = gcol.cpu().numpy()               # block -> local key range look-ups on the host
         bh = shard_bounds(cfg.key_range, self.S)
-        self.shard_col = [int(np.searchsorted(gk, np.uint64(min(b, (1 << 64) - 1)))) for b in bh[:-1]] + [self.n_cols]
+        edges = torch.from_numpy(np.array([min(b, (1 << 64) - 1) for b in bh[:-1]], dtype=np.uint64).view(np.int64)).to(dev) ^ sign
+        self.shard_col = torch.searchsorted(gk, edges).tolist() + [self.n_cols]
         f32 = torch.float32
         n = max(1, self.n_cols)
         # owner state (only my column range is touched) and worker copies
@@ -114,6 +118,15 @@ class DarlinRank:
         self.active_w = torch.ones(n, dtype=torch.uint8, device=dev)
         nb = (self.n_cols + cfg.block_cols - 1) // cfg.block_cols
         self.blocks = [(i * cfg.block_cols, min(self.n_cols, (i + 1) * cfg.block_cols)) for i in range(nb)]
+        self.prior_blocks: List[int] = []
+
+    def set_blocks(self, blocks: List[tuple], prior: Optional[List[int]] = None):
+        """Use the given column ranges as feature blocks (none wider than ``cfg.block_cols``); ``prior``
+        lists block indices that open the first pass, one after another (no delay)."""
+        assert all(0 <= c0 < c1 <= self.n_cols and c1 - c0 <= self.cfg.block_cols for c0, c1 in blocks)
+        self.blocks = list(blocks)
+        self.prior_blocks = list(prior or [])
+        self.__dict__.pop("_param_cache", None)
 
     # ---- addresses in a rank's heap
     def _flag(self, rank: int, kind: int, q: int, idx: int) -> int:
@@ -243,11 +256,15 @@ class DarlinRank:
         _lib.check_status(self.status, what)
 
 
-def run_darlin(ranks: Sequence[DarlinRank], *, all_reduce=None, verbose: bool = False, num_examples: Optional[int] = None):
+def run_darlin(ranks: Sequence[DarlinRank], *, all_reduce=None, verbose: bool = False, num_examples: Optional[int] = None,
+               save_every: int = 0, save_fn=None):
     """Drive passes over the blocks. ``ranks``: every rank of an emulated fabric
     (kernels of the ranks run one after another), or the single local rank of a
     multi-process run, with ``all_reduce(values, op)`` combining the per-pass
-    scalars across processes."""
+    scalars across processes. The first pass opens with the ranks' ``prior_blocks``
+    (one after another, no delay; ``app/linear_method/darlin.h:76-82``). With
+    ``save_every = n`` and ``save_fn(iteration)`` the model is written after every
+    n-th pass (``save_model_every_n_iter``, ``darlin.h:97-100``)."""
     cfg = ranks[0].cfg
     tau = cfg.tau if len(ranks) == 1 or all_reduce is not None else 0   # emulated ranks share a stream: no delay
     nb = len(ranks[0].blocks)
@@ -262,6 +279,16 @@ def run_darlin(ranks: Sequence[DarlinRank], *, all_reduce=None, verbose: bool = 
         if reset_kkt:
             for r in ranks:
                 r.reset_kkt_filter()
+        if it == 0 and ranks[0].prior_blocks:
+            # the prior groups' blocks first, strictly one after another
+            for blk in ranks[0].prior_blocks:
+                for r in ranks:
+                    r.grad(blk, ts)
+                for r in ranks:
+                    r.update(blk, ts)
+                for r in ranks:
+                    r.dual(blk, ts)
+                ts += 1
         # software pipeline: gradients run `tau` blocks ahead of the weight application
         if len(ranks) == 1 and tau > 0:
             # One rank per process: the gradient kernels go to one stream and update + dual to
@@ -316,6 +343,8 @@ def run_darlin(ranks: Sequence[DarlinRank], *, all_reduce=None, verbose: bool = 
         thr = vio / max(1, n_ex) * cfg.kkt_ratio
         for r in ranks:
             r.kkt_threshold = thr
+        if save_every > 0 and save_fn is not None and (it + 1) % save_every == 0:
+            save_fn(it)
         if 0 < rel <= cfg.epsilon:
             if reset_kkt:
                 break

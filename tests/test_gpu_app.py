@@ -20,7 +20,8 @@ training_data {{ format: TEXT text: SPARSE_BINARY file: "{train}/part.*" }}
 model_output {{ format: TEXT file: "{out}/darlin" }}
 penalty {{ type: L1 lambda: 2 }}
 learning_rate {{ type: CONSTANT alpha: 0.5 }}
-darlin {{ max_pass_of_data: 8 epsilon: 1e-5 max_block_delay: 0 }}
+darlin {{ max_pass_of_data: 8 epsilon: 1e-5 max_block_delay: 0 tail_feature_freq: 2 feature_block_ratio: 1
+  save_model_every_n_iter: 3 }}
 """
 CONF_EVAL = """
 validation_data {{ format: TEXT text: SPARSE_BINARY file: "{train}/part.*" }}
@@ -44,5 +45,6 @@ def test_async_sgd_darlin_and_evaluation_apps(cuda_lib, tmp_path, monkeypatch):
     assert ev["auc"] > 0.68 and ev["logloss"] < 0.67
     hist = linear.run_darlin(core.parse_text_proto(CONF_DARLIN.format(train=tmp_path / "train", out=tmp_path)), verbose=False)
     assert hist[-1]["objective"] < 0.95 * 4500 * np.log(2)
+    assert glob.glob(str(tmp_path / "darlin_iter_2_S0")), "no intermediate model after the third pass"
     ev2 = linear.run_evaluation(core.parse_text_proto(CONF_EVAL.format(train=tmp_path / "train", out=tmp_path, name="darlin")), verbose=False)
     assert ev2["auc"] > 0.68

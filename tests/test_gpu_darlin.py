@@ -69,3 +69,50 @@ def test_darlin_bounded_delay_single_rank_converges(cuda_lib):
         assert hist[-1]["objective"] < 0.95 * 4000 * np.log(2)       # well below the zero model
         assert hist[-1]["objective"] <= hist[0]["objective"]
     assert abs(objs[0] - objs[2]) / objs[0] < 0.05
+
+
+def test_device_preprocessing_tail_filter_groups_and_blocks(cuda_lib):
+    """Column space, tail filter and block division on the device against NumPy: two feature groups,
+    keys below the frequency threshold dropped, columns group-major with keys ascending inside a
+    group, blocks per group from nnz per row, prior group first."""
+    from parameter_server_b200.models.darlin_prep import build_columns, plan_blocks
+    rng = np.random.default_rng(0)
+    rows = 500
+    groups = []
+    for gid, (n_feat, z) in enumerate([(40, 3), (3000, 6)]):
+        lens = rng.integers(1, 2 * z, rows)
+        off = np.concatenate([[0], np.cumsum(lens)])
+        ids = np.minimum((rng.pareto(1.0, off[-1]) * 3).astype(np.int64), n_feat - 1)
+        keys = (ids.astype(np.uint64) * np.uint64(0x9E3779B97F4A7C15)) ^ np.uint64(gid << 60)
+        groups.append(dict(id=gid, offset=off, index=keys, value=np.zeros(0, np.float32), binary=True))
+    col, row_ptr, vals, space = build_columns(groups, rows, "cuda", tail_freq=4, countmin_cells=1 << 20, countmin_k=2)
+    assert vals is None and len(space.groups) == 2
+    base = 0
+    exp_rows = [[] for _ in range(rows)]
+    for g in groups:
+        u, cnt = np.unique(g["index"], return_counts=True)
+        kept = u[cnt >= 4]                                   # the sketch is large: estimates are exact here
+        gid, c0, c1 = space.groups[g["id"]]
+        assert (c0, c1) == (base, base + len(kept))
+        assert np.array_equal(space.col_key[c0:c1].cpu().numpy().view(np.uint64), kept)
+        for r in range(rows):
+            ks = g["index"][g["offset"][r]:g["offset"][r + 1]]
+            exp_rows[r] += [base + int(np.searchsorted(kept, k)) for k in ks if k in set(kept.tolist())]
+        base += len(kept)
+    rp = row_ptr.cpu().numpy()
+    c = col.cpu().numpy()
+    for r in range(0, rows, 7):
+        assert sorted(c[rp[r]:rp[r + 1]].tolist()) == sorted(exp_rows[r]), r
+    assert space.dropped_nnz == sum(len(g["index"]) for g in groups) - len(c) > 0
+    plan = plan_blocks(space, feature_block_ratio=2.0, max_block_cols=64, prior_groups=[0], prior_iters=3)
+    assert all(b1 - b0 <= 64 for b0, b1 in plan.blocks) and plan.block_cols <= 64
+    assert [b for b, g in zip(plan.blocks, plan.group_of) if g == 0][0][0] == 0
+    n0 = sum(1 for g in plan.group_of if g == 0)
+    assert plan.prior == list(range(n0)) * 3
+    # every column is in exactly one block, blocks never straddle a group
+    covered = np.zeros(space.n_cols, int)
+    for (b0, b1), g in zip(plan.blocks, plan.group_of):
+        covered[b0:b1] += 1
+        gid, c0, c1 = space.groups[g]
+        assert c0 <= b0 and b1 <= c1
+    assert (covered == 1).all()
