@@ -1,6 +1,7 @@
 // Python bindings of utilities: hashes, sketches, filters (stand-alone
 // encode/decode), ordered match.
 #include "bind_common.h"
+#include "data.h"
 #include "filter.h"
 #include "ordered_match.h"
 #include "remote_node.h"
@@ -24,6 +25,15 @@ void BindUtil(py::module& m) {
     return py::make_tuple(out[0], out[1]);
   });
   m.def("sketch_hash", [](uint64_t k) { return Sketch::hash(k); });
+  m.def("read_file", [](const std::string& name) -> py::object {
+    std::string out;
+    bool ok;
+    { py::gil_scoped_release r; ok = readFileToString(name, &out); }
+    if (!ok) return py::none();
+    return py::bytes(out);
+  }, "whole contents of a plain, .gz or s3:// file (None if it cannot be opened)");
+  m.def("s3_file_url", &s3FileUrl);
+  m.def("s3_directory_url", &s3DirectoryUrl);
 
   typedef CountMin<uint64_t, uint8_t> CM8;
   py::class_<CM8>(m, "CountMin")

@@ -277,9 +277,34 @@ MatrixInfo readMatrixInfo(const ExampleInfo& info, int slot_idx, int sizeof_idx,
 }
 
 // ================================================================ files
+bool s3file(const std::string& name) { return name.compare(0, 5, "s3://") == 0 && name.size() > 5; }
+static std::string s3Bucket(const std::string& name) {
+  const size_t slash = name.find('/', 5);
+  return name.substr(5, slash == std::string::npos ? std::string::npos : slash - 5);
+}
+static std::string s3Object(const std::string& name) {
+  const size_t slash = name.find('/', 5);
+  return slash == std::string::npos ? "" : name.substr(slash + 1);
+}
+std::string s3FileUrl(const std::string& name) { return "http://" + s3Bucket(name) + ".s3.amazonaws.com/" + s3Object(name); }
+std::string s3DirectoryUrl(const std::string& name) {
+  return "http://" + s3Bucket(name) + ".s3.amazonaws.com/?prefix=" + s3Object(name);
+}
+// only characters that need no quoting may reach the shell
+static bool shellSafe(const std::string& s) {
+  for (char c : s)
+    if (!(isalnum((unsigned char)c) || strchr("._-/:?=%+~,@", c))) return false;
+  return true;
+}
+
 File* File::open(const std::string& name, const char* flag) {
   if (name == "stdin") return new File(stdin, nullptr, name, true);
   if (name == "stdout") return new File(stdout, nullptr, name, true);
+  if (s3file(name)) {
+    if (flag[0] != 'r' || !shellSafe(name)) return nullptr;   // objects are read only
+    FILE* pipe = popen(("curl -s -f -X GET " + s3FileUrl(name)).c_str(), "r");
+    return pipe ? new File(pipe, nullptr, name, false, true) : nullptr;
+  }
   bool gz = name.size() > 3 && name.compare(name.size() - 3, 3, ".gz") == 0;
   if (gz) {
     gzFile g = gzopen(name.c_str(), flag);
@@ -316,7 +341,7 @@ bool File::flush() { return gz_ ? gzflush(gz_, Z_FINISH) == Z_OK : fflush(f_) ==
 bool File::close() {
   bool ok = true;
   if (gz_) { ok = gzclose(gz_) == Z_OK; gz_ = nullptr; }
-  if (f_) { if (!std_) ok = fclose(f_) == 0; f_ = nullptr; }
+  if (f_) { if (pipe_) ok = pclose(f_) == 0; else if (!std_) ok = fclose(f_) == 0; f_ = nullptr; }
   return ok;
 }
 bool readFileToString(const std::string& name, std::string* out) {
@@ -381,6 +406,31 @@ DataConfig searchFiles(const DataConfig& config) {
   out.file.clear();
   for (const std::string& pat : config.file) {
     if (File::exists(pat)) { out.file.push_back(pat); continue; }
+    if (s3file(pat)) {
+      // the bucket's listing for the directory part, objects whose file name matches the pattern
+      const std::string dir_name = getPath(pat);
+      std::regex re;
+      try { re = std::regex(getFilename(pat)); } catch (const std::regex_error&) { continue; }
+      std::string listing;
+      if (shellSafe(dir_name)) {
+        if (FILE* pipe = popen(("curl -s -f -X GET " + s3DirectoryUrl(dir_name + "/")).c_str(), "r")) {
+          char buf[4096];
+          size_t n;
+          while ((n = fread(buf, 1, sizeof(buf), pipe)) > 0) listing.append(buf, n);
+          pclose(pipe);
+        }
+      }
+      size_t at = 0, found = 0;
+      while ((at = listing.find("<Key>", at)) != std::string::npos) {
+        const size_t end = listing.find("</Key>", at);
+        if (end == std::string::npos) break;
+        const std::string object = listing.substr(at + 5, end - at - 5);
+        if (std::regex_match(getFilename(object), re)) { out.file.push_back("s3://" + s3Bucket(pat) + "/" + object); ++found; }
+        at = end;
+      }
+      if (!found) out.file.push_back(pat);      // no listing (or nothing matched): take the name as an object
+      continue;
+    }
     std::string dir = getPath(pat);
     std::regex re;
     try { re = std::regex(getFilename(pat)); } catch (const std::regex_error&) { continue; }

@@ -143,7 +143,8 @@ class InfoParser {
 };
 
 // ---------------------------------------------------------------- files
-// Plain, gzip (by ".gz" suffix) or stdin/stdout ("stdin"/"stdout") file.
+// Plain, gzip (by ".gz" suffix) or stdin/stdout ("stdin"/"stdout") file; "s3://bucket/object" is read
+// through a pipe from `curl` (read-only, as util/file.cc:23-61 does when built with USE_S3).
 class File {
  public:
   static File* open(const std::string& name, const char* flag);
@@ -166,12 +167,17 @@ class File {
   bool close();
   const std::string& filename() const { return name_; }
  private:
-  File(FILE* f, gzFile gz, const std::string& name, bool std_stream) : f_(f), gz_(gz), name_(name), std_(std_stream) {}
+  File(FILE* f, gzFile gz, const std::string& name, bool std_stream, bool pipe = false)
+      : f_(f), gz_(gz), name_(name), std_(std_stream), pipe_(pipe) {}
   FILE* f_ = nullptr;
   gzFile gz_ = nullptr;
   std::string name_;
   bool std_ = false;
+  bool pipe_ = false;      // f_ came from popen
 };
+bool s3file(const std::string& name);                        // "s3://..."
+std::string s3FileUrl(const std::string& name);             // http://<bucket>.s3.amazonaws.com/<object>
+std::string s3DirectoryUrl(const std::string& name);        // bucket listing restricted to the prefix
 bool readFileToString(const std::string& name, std::string* out);
 bool writeStringToFile(const std::string& data, const std::string& name);
 std::vector<std::string> readFilenamesInDirectory(const std::string& dir);

@@ -267,3 +267,33 @@ def test_checkpoint_file_roundtrip(tmp_path):
     trunc.write_bytes(blob[:len(blob) - 100])
     with pytest.raises(ValueError):
         ck.read_shard(str(trunc))
+
+
+def test_s3_files_are_read_through_curl(tmp_path, monkeypatch):
+    """s3://bucket/object is read from a `curl` pipe (a stand-in curl here: no network), bucket
+    listings expand a file-name pattern, and nothing but plain characters reaches the shell."""
+    import os
+    import stat
+    from parameter_server_b200.system import core
+    store = tmp_path / "bucket"
+    (store / "data").mkdir(parents=True)
+    (store / "data" / "part-0").write_text("1 3:1 7:1\n")
+    (store / "data" / "part-1").write_text("-1 2:1\n")
+    fake = tmp_path / "bin" / "curl"
+    fake.parent.mkdir()
+    fake.write_text(f"""#!/bin/sh
+url="$5"
+case "$url" in
+  *'?prefix='*) echo '<ListBucketResult><Contents><Key>data/part-0</Key></Contents><Contents><Key>data/part-1</Key></Contents><Contents><Key>data/other</Key></Contents></ListBucketResult>' ;;
+  *) path="${{url#http://mybucket.s3.amazonaws.com/}}"; [ -f "{store}/$path" ] || exit 22; cat "{store}/$path" ;;
+esac
+""")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", f"{fake.parent}:{os.environ['PATH']}")
+    assert core.s3_file_url("s3://mybucket/data/part-0") == "http://mybucket.s3.amazonaws.com/data/part-0"
+    assert core.read_file("s3://mybucket/data/part-0") == b"1 3:1 7:1\n"
+    assert core.search_files(["s3://mybucket/data/part-.*"]) == ["s3://mybucket/data/part-0", "s3://mybucket/data/part-1"]
+    r = core.StreamReader(["s3://mybucket/data/part-1"], "TEXT", "LIBSVM", True)
+    y, mats = r.read_matrices(10)
+    assert list(y) == [-1.0] and list(mats[0]["index"]) == [2]
+    assert core.read_file("s3://mybucket/data/x;rm -rf y") is None      # refused before any shell sees it
