@@ -35,85 +35,106 @@ __device__ __forceinline__ int shard_of_col(const u32* shard_col, int S, u32 c) 
   return s;
 }
 
-__global__ void __launch_bounds__(kDThreads) k_darlin_grad(const PsbDarlinGrad p) {
-  __shared__ u32 s_last;
+// Phase 1 of the gradient step: segmented reduction over the block's nonzeros into the staging area
+// (zero on entry: phase 2 of the previous use of this area cleared what it read). A warp takes chunks of
+// consecutive 32-element words and carries the sums of a column that runs over a word boundary in
+// registers, so that a frequent feature (a column of millions of nonzeros under a Zipf law) costs two
+// atomics per chunk instead of two per word: same-address atomics serialise in L2. The loads of
+// kGradGroup words are issued together before the (sequential) scans, because every word costs a chain
+// of three dependent gathers (word base -> column -> column state; row -> label, margin).
+static constexpr int kGradGroup = 4;
+
+// The CTAs that share a column pass: all of the grid, or a part of it when several passes run side
+// by side (k_darlin_pass). index: this CTA's place among them.
+struct Part { u32 index, count; };
+__device__ __forceinline__ Part whole_grid() { return Part{blockIdx.x, gridDim.x}; }
+__device__ void darlin_grad_p1(const PsbDarlinGrad& p) {
+  if (p.u1 <= p.u0) return;
   const u32 gsize = gridDim.x * blockDim.x, gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = threadIdx.x & 31;
   const u32 gwarp = gtid >> 5, nwarps = gsize >> 5;
-  const u32 ncol = p.c1 - p.c0;
-  // The staging area is zero on entry: phase 2 of the previous call cleared what it read.
-  // phase 1: segmented reduction over the block's nonzeros. A warp takes chunks of
-  // kChunkWords consecutive 32-element words and carries the sums of a column that runs
-  // over a word boundary in registers, so that a frequent feature (a column of millions of
-  // nonzeros under a Zipf law) costs two atomics per chunk instead of two per word:
-  // same-address atomics serialise in L2.
-  if (p.u1 > p.u0) {
-    const u32 nz0 = p.seg_off[p.u0], nz1 = p.seg_off[p.u1];
-    const u32 w0 = nz0 >> 5, w1 = (nz1 + 31) >> 5;
-    const u32 le = 0xffffffffu >> (31 - lane);
-    // chunk length: up to 16 words, but no longer than what keeps every warp busy
-    const u32 kChunkWords = max(1u, min(16u, (w1 - w0 + nwarps - 1) / nwarps));
-    const u32 nchunks = (w1 - w0 + kChunkWords - 1) / kChunkWords;
-    for (u32 ch = gwarp; ch < nchunks; ch += nwarps) {
-      const u32 wb = w0 + ch * kChunkWords, we = min(w1, wb + kChunkWords);
-      float cg = 0.f, chh = 0.f;   // sums so far of the column that is open at the word boundary
-      u32 cu = 0;                  // its local unique-key index
-      bool open = false;
-      for (u32 wi = wb; wi < we; ++wi) {
+  const u32 nz0 = p.seg_off[p.u0], nz1 = p.seg_off[p.u1];
+  const u32 w0 = nz0 >> 5, w1 = (nz1 + 31) >> 5;
+  const u32 le = 0xffffffffu >> (31 - lane);
+  // chunk length: up to 16 words, but no longer than what keeps every warp busy
+  const u32 kChunkWords = max(1u, min(16u, (w1 - w0 + nwarps - 1) / nwarps));
+  const u32 nchunks = (w1 - w0 + kChunkWords - 1) / kChunkWords;
+  auto flush = [&](u32 col, float gg, float hh) {
+    const u32 c = col - p.c0;
+    if (c < p.block_cap && (gg != 0.f || hh != 0.f)) {
+      atomicAdd(&p.stage[c], gg);
+      atomicAdd(&p.stage[p.block_cap + c], hh);
+    }
+  };
+  for (u32 ch = gwarp; ch < nchunks; ch += nwarps) {
+    const u32 wb = w0 + ch * kChunkWords, we = min(w1, wb + kChunkWords);
+    float cg = 0.f, chh = 0.f;   // sums so far of the column that is open at the word boundary
+    u32 ccol = 0;                // that column
+    bool open = false;
+    for (u32 gb = wb; gb < we; gb += kGradGroup) {
+      u32 f[kGradGroup], col[kGradGroup], row[kGradGroup];
+      float g[kGradGroup], h[kGradGroup], val[kGradGroup];
+      bool in[kGradGroup];
+#pragma unroll
+      for (int k = 0; k < kGradGroup; ++k) {
+        const u32 wi = gb + k;
+        const bool valid = wi < we;
+        f[k] = valid ? p.flagbits[wi] : 0u;
+        const u32 base = valid ? p.wordbase[wi] : 0u;
         const u32 i = wi * 32 + lane;
-        const u32 f = p.flagbits[wi];
-        const u32 fle = f & le;
-        const u32 u = p.wordbase[wi] + __popc(fle) - 1;     // local unique key of this nonzero
-        const bool in = i >= nz0 && i < nz1;
-        float g = 0.f, h = 0.f;
-        if (in) {
-          u32 c = p.gcol[u];
-          if (p.active[c]) {
-            u32 r = p.csc_row[i];
-            float y = p.y[r];
-            float ym = y * __ldcg(&p.margin[r]);
-            // tau = 1/(1+exp(y m)) evaluated stably
-            float en = expf(-fabsf(ym));
-            float tau = ym > 0 ? en / (1.f + en) : 1.f / (1.f + en);
-            float d = p.delta[c];
-            if (p.csc_val) {
-              float v = p.csc_val[i];
-              g = -y * tau * v;
-              h = fminf(tau * (1.f - tau) * expf(fabsf(v) * d), 0.25f) * v * v;
-            } else {
-              g = -y * tau;
-              h = fminf(tau * (1.f - tau) * expf(d), 0.25f);
-            }
-          }
+        in[k] = valid && i >= nz0 && i < nz1;
+        col[k] = in[k] ? p.gcol[base + __popc(f[k] & le) - 1] : 0u;   // local unique key -> global column
+        row[k] = in[k] ? p.csc_row[i] : 0u;
+        val[k] = (in[k] && p.csc_val) ? p.csc_val[i] : 1.f;
+      }
+#pragma unroll
+      for (int k = 0; k < kGradGroup; ++k) {
+        g[k] = h[k] = 0.f;
+        // every gather of this level is issued before the active flag is known
+        const unsigned char act = in[k] ? p.active[col[k]] : (unsigned char)0;
+        const float y = in[k] ? p.y[row[k]] : 0.f;
+        const float mg = in[k] ? __ldcg(&p.margin[row[k]]) : 0.f;
+        const float d = in[k] ? p.delta[col[k]] : 0.f;
+        if (act) {
+          const float ym = y * mg;
+          // tau = 1/(1+exp(y m)) evaluated stably; the fast exponential and reciprocal are good to a few
+          // ulp, far inside what the sums over a column carry
+          const float en = __expf(-fabsf(ym));
+          const float rc = __fdividef(1.f, 1.f + en);
+          const float tau = ym > 0 ? en * rc : rc;
+          const float v = val[k];
+          g[k] = -y * tau * v;
+          h[k] = fminf(tau * (1.f - tau) * __expf(fabsf(v) * d), 0.25f) * v * v;
         }
-        auto flush = [&](u32 uu, float gg, float hh) {
-          u32 c = p.gcol[uu] - p.c0;
-          if (c < p.block_cap && (gg != 0.f || hh != 0.f)) {
-            atomicAdd(&p.stage[c], gg);
-            atomicAdd(&p.stage[p.block_cap + c], hh);
-          }
-        };
-        if (open && (f & 1u)) {                     // the open column ended with the previous word
-          if (lane == 0) flush(cu, cg, chh);
+      }
+#pragma unroll
+      for (int k = 0; k < kGradGroup; ++k) {
+        const u32 wi = gb + k;
+        if (wi >= we) break;
+        const u32 i = wi * 32 + lane;
+        const u32 fw = f[k], fle = fw & le;
+        float gg = g[k], hh = h[k];
+        if (open && (fw & 1u)) {                     // the open column ended with the previous word
+          if (lane == 0) flush(ccol, cg, chh);
           open = false; cg = chh = 0.f;
         }
         // segmented inclusive scan inside the word; segment = column
-        int start = fle ? 31 - __clz(fle) : 0;
+        const int start = fle ? 31 - __clz(fle) : 0;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-          float g2 = __shfl_up_sync(0xffffffffu, g, o);
-          float h2 = __shfl_up_sync(0xffffffffu, h, o);
-          if (lane >= start + o) { g += g2; h += h2; }
+          const float g2 = __shfl_up_sync(0xffffffffu, gg, o);
+          const float h2 = __shfl_up_sync(0xffffffffu, hh, o);
+          if (lane >= start + o) { gg += g2; hh += h2; }
         }
-        if (fle == 0) { g += cg; h += chh; }        // lanes that continue the open column (the carry is 0 otherwise)
-        const bool tail = (lane == 31) || ((f >> (lane + 1)) & 1u) || (i + 1 == nz1);
+        if (fle == 0) { gg += cg; hh += chh; }       // lanes that continue the open column (the carry is 0 otherwise)
+        const bool tail = (lane == 31) || ((fw >> (lane + 1)) & 1u) || (i + 1 == nz1);
         // the word's last column stays open unless this is the chunk's last word or the block's data ends here
         const bool keep = (wi + 1 < we) && ((wi + 1) * 32 < nz1);
-        if (in && tail && !(keep && lane == 31)) flush(u, g, h);
+        if (in[k] && tail && !(keep && lane == 31)) flush(col[k], gg, hh);
         if (keep) {
-          cg = __shfl_sync(0xffffffffu, g, 31);
-          chh = __shfl_sync(0xffffffffu, h, 31);
-          cu = p.wordbase[wi] + __popc(f) - 1;
+          cg = __shfl_sync(0xffffffffu, gg, 31);
+          chh = __shfl_sync(0xffffffffu, hh, 31);
+          ccol = __shfl_sync(0xffffffffu, col[k], 31);
           open = true;
         } else {
           open = false; cg = chh = 0.f;
@@ -121,13 +142,19 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_grad(const PsbDarlinGrad p
       }
     }
   }
-  if (!grid_barrier(p.bar, p.status)) return;
-  // phase 2: dense slices to the owners
+}
+
+// Phase 2 of the gradient step (after a grid barrier): the dense (G, U) slices go to the owners; the
+// last CTA to finish raises this source's flag at every owner.
+__device__ void darlin_grad_p2(const PsbDarlinGrad& p, const Part part) {
+  __shared__ u32 s_last;
+  const u32 gsize = part.count * blockDim.x, gtid = part.index * blockDim.x + threadIdx.x;
+  const u32 ncol = p.c1 - p.c0;
   for (u32 c = gtid; c < ncol; c += gsize) {
     int s = shard_of_col(p.shard_col, p.S, p.c0 + c);
     p.gu_inbox[s][c] = __ldcg(&p.stage[c]);
     p.gu_inbox[s][p.block_cap + c] = __ldcg(&p.stage[p.block_cap + c]);
-    p.stage[c] = 0.f;                      // leave the staging area clean for the next block
+    p.stage[c] = 0.f;                      // leave the staging area clean for its next block
     p.stage[p.block_cap + c] = 0.f;
   }
   // One system fence per CTA: the block barrier orders every thread's peer stores before
@@ -135,7 +162,7 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_grad(const PsbDarlinGrad p
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
-    s_last = atomicAdd(p.done, 1u) + 1 == gridDim.x;
+    s_last = atomicAdd(p.done, 1u) + 1 == part.count;
   }
   __syncthreads();
   if (s_last && threadIdx.x < p.S) {
@@ -145,7 +172,15 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_grad(const PsbDarlinGrad p
   }
 }
 
-__global__ void __launch_bounds__(kDThreads) k_darlin_update(const PsbDarlinUpdate p) {
+__device__ bool darlin_grad_body(const PsbDarlinGrad& p) {
+  darlin_grad_p1(p);
+  if (!grid_barrier(p.bar, p.status)) return false;
+  darlin_grad_p2(p, whole_grid());
+  return true;
+}
+__global__ void __launch_bounds__(kDThreads) k_darlin_grad(const PsbDarlinGrad p) { darlin_grad_body(p); }
+
+__device__ void darlin_update_body(const PsbDarlinUpdate& p, const Part part) {
   __shared__ u32 s_last;
   __shared__ float s_vio;
   const int S = p.S;
@@ -158,7 +193,7 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_update(const PsbDarlinUpda
     }
   }
   __syncthreads();
-  const u32 gsize = gridDim.x * blockDim.x, gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const u32 gsize = part.count * blockDim.x, gtid = part.index * blockDim.x + threadIdx.x;
   float vio_max = 0.f;
   const float nan = __int_as_float(0x7fffffff);
   for (u32 c = p.my0 + gtid; c < p.my1; c += gsize) {
@@ -207,8 +242,8 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_update(const PsbDarlinUpda
   __syncthreads();
   if (threadIdx.x == 0) {
     if (s_vio > 0.f && p.violation) atomicMax((int*)p.violation, __float_as_int(s_vio));
-    __threadfence_system();   // one per CTA, after the block barrier (see k_darlin_grad)
-    s_last = atomicAdd(p.done, 1u) + 1 == gridDim.x;
+    __threadfence_system();   // one per CTA, after the block barrier (see darlin_grad_p2)
+    s_last = atomicAdd(p.done, 1u) + 1 == part.count;
   }
   __syncthreads();
   if (s_last && threadIdx.x < S && p.alive[threadIdx.x]) {
@@ -217,12 +252,14 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_update(const PsbDarlinUpda
   }
   if (s_last && threadIdx.x == 0) atomicExch(p.done, 0u);
 }
+__global__ void __launch_bounds__(kDThreads) k_darlin_update(const PsbDarlinUpdate p) { darlin_update_body(p, whole_grid()); }
 
-__global__ void __launch_bounds__(kDThreads) k_darlin_dual(const PsbDarlinDual p) {
-  const int S = p.S;
+// The margin step in three parts: bounded wait for the owners' slices; m_i += dw_j x_ij over the
+// block's nonzeros; after a grid barrier the per-column state of the whole block.
+__device__ void darlin_dual_wait(const PsbDarlinDual& p) {
   if (threadIdx.x == 0) {
     const u32 iters = p.wait_iters ? p.wait_iters : kPeerWaitIters;
-    for (int s = 0; s < S; ++s) {
+    for (int s = 0; s < p.S; ++s) {
       // only owners that hold a part of this block publish a slice
       u32 lo = max(p.c0, p.shard_col[s]), hi = min(p.c1, p.shard_col[s + 1]);
       if (lo >= hi || !p.alive[s]) continue;
@@ -230,30 +267,56 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_dual(const PsbDarlinDual p
     }
   }
   __syncthreads();
+}
+// The same wait by one warp for itself: lane s polls owner s's flag, so the flags are polled side by side.
+__device__ void darlin_dual_wait_warp(const PsbDarlinDual& p) {
+  const int s = threadIdx.x & 31;
+  if (s < p.S) {
+    const u32 lo = max(p.c0, p.shard_col[s]), hi = min(p.c1, p.shard_col[s + 1]);
+    if (lo < hi && p.alive[s]) {
+      const u32 iters = p.wait_iters ? p.wait_iters : kPeerWaitIters;
+      if (!wait_flag_ge_sys(p.wnew_ready[s], p.ts1, iters)) set_status(p.status, kWaitTimeout);
+    }
+  }
+  __syncwarp();
+}
+__device__ void darlin_dual_p1(const PsbDarlinDual& p) {
+  if (p.u1 <= p.u0) return;
   const u32 gsize = gridDim.x * blockDim.x, gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = threadIdx.x & 31;
   const u32 gwarp = gtid >> 5, nwarps = gsize >> 5;
-  // phase 1: m_i += dw_j x_ij over the block's nonzeros
-  if (p.u1 > p.u0) {
-    const u32 nz0 = p.seg_off[p.u0], nz1 = p.seg_off[p.u1];
-    const u32 w0 = nz0 >> 5, w1 = (nz1 + 31) >> 5;
-    const u32 le = 0xffffffffu >> (31 - lane);
-    for (u32 wi = w0 + gwarp; wi < w1; wi += nwarps) {
-      u32 i = wi * 32 + lane;
-      if (i < nz0 || i >= nz1) continue;
-      u32 u = p.wordbase[wi] + __popc(p.flagbits[wi] & le) - 1;
-      u32 c = p.gcol[u];
-      if (!p.active[c]) continue;
-      float nw = p.wnew[c - p.c0];
-      if (nw != nw) continue;                       // deactivated by the owner
-      float dw = nw - p.w_cur[c];
-      if (dw == 0.f) continue;
-      float x = p.csc_val ? p.csc_val[i] : 1.f;
-      atomicAdd(&p.margin[p.csc_row[i]], dw * x);
+  const u32 nz0 = p.seg_off[p.u0], nz1 = p.seg_off[p.u1];
+  const u32 w0 = nz0 >> 5, w1 = (nz1 + 31) >> 5;
+  const u32 le = 0xffffffffu >> (31 - lane);
+  constexpr int kGroup = 4;                 // words whose gathers are in flight together
+  for (u32 wa = w0 + gwarp; wa < w1; wa += nwarps * kGroup) {
+    u32 col[kGroup], row[kGroup];
+    float x[kGroup];
+    bool in[kGroup];
+#pragma unroll
+    for (int k = 0; k < kGroup; ++k) {
+      const u32 wi = wa + k * nwarps;
+      const u32 i = wi * 32 + lane;
+      in[k] = wi < w1 && i >= nz0 && i < nz1;
+      col[k] = in[k] ? p.gcol[p.wordbase[wi] + __popc(p.flagbits[wi] & le) - 1] : 0u;
+      row[k] = in[k] ? p.csc_row[i] : 0u;
+      x[k] = (in[k] && p.csc_val) ? p.csc_val[i] : 1.f;
+    }
+#pragma unroll
+    for (int k = 0; k < kGroup; ++k) {
+      if (!in[k]) continue;
+      // the three gathers are independent of each other: issue them together
+      const unsigned char act = p.active[col[k]];
+      const float nw = p.wnew[col[k] - p.c0];
+      const float wc = p.w_cur[col[k]];
+      const float dw = nw - wc;                     // NaN (deactivated by the owner) fails the test below
+      if (act && dw == dw && dw != 0.f) atomicAdd(&p.margin[row[k]], dw * x[k]);
     }
   }
-  if (!grid_barrier(p.bar, p.status)) return;
-  // phase 2: per-column state of the whole block (also columns without local data)
+}
+__device__ void darlin_dual_p2(const PsbDarlinDual& p, const Part part) {
+  const u32 gsize = part.count * blockDim.x, gtid = part.index * blockDim.x + threadIdx.x;
+  // per-column state of the whole block (also columns without local data)
   for (u32 c = p.c0 + gtid; c < p.c1; c += gsize) {
     if (!p.active[c]) continue;
     float nw = p.wnew[c - p.c0];
@@ -261,6 +324,141 @@ __global__ void __launch_bounds__(kDThreads) k_darlin_dual(const PsbDarlinDual p
     float dw = nw - p.w_cur[c];
     p.delta[c] = fminf(p.delta_max, 2.f * fabsf(dw) + 0.1f);
     p.w_cur[c] = nw;
+  }
+}
+__device__ bool darlin_dual_body(const PsbDarlinDual& p) {
+  darlin_dual_wait(p);
+  darlin_dual_p1(p);
+  if (!grid_barrier(p.bar, p.status)) return false;
+  darlin_dual_p2(p, whole_grid());
+  return true;
+}
+__global__ void __launch_bounds__(kDThreads) k_darlin_dual(const PsbDarlinDual p) { darlin_dual_body(p); }
+
+// ---------------------------------------------------------------- a whole pass in one launch
+// The block schedule of a pass (darlin.h:56-85,157-164) as one persistent cooperative kernel. The
+// per-block parameter blocks (one per block and ring slot) are prepared by the host once and read from
+// device memory here; only the stamp and the KKT threshold change from pass to pass. Between GPUs the
+// same release/acquire flags as in the single-block kernels are used.
+//
+// Without delay (tau = 0) a block's gradient, owner update and margin step run one after another with
+// a grid barrier between the phases. With delay tau >= 1 the scheduler's wait_time window lets the
+// gradient of block i run on margins that miss the weight changes of the last tau blocks, so step i is
+// two phases with ONE grid barrier between them, and nothing in it waits for work of the same step
+// unless tau == 1:
+//
+//   phase A   nonzero passes: gradient sums of block i into staging area i % ring; margin update of
+//             block i - tau (its new weights were published during step i - 1)
+//   ---- grid barrier
+//   phase B   column passes: gradient slices of block i to the owners (+ flags); column state of block
+//             i - tau; owner update of block i - tau + 1 (+ flags), whose slices arrived a step ago
+//             when tau >= 2
+//
+// There is no barrier between phase B of step i and phase A of step i + 1: the two touch different
+// staging areas, different blocks' column state, and the margins only by atomic adds and loads that
+// the window allows to be stale; a CTA that runs ahead stops at the barrier of step i + 1.
+template <typename P>
+__device__ __forceinline__ void load_params(P* dst, const P* src) {
+  static_assert(sizeof(P) % 4 == 0, "parameter blocks are copied word by word");
+  const u32* s = reinterpret_cast<const u32*>(src);
+  u32* d = reinterpret_cast<u32*>(dst);
+  for (u32 i = threadIdx.x; i < sizeof(P) / 4; i += blockDim.x) d[i] = s[i];
+}
+
+static constexpr int kPassThreads = 1024;
+
+__device__ __forceinline__ u64 globaltimer_ns() {
+  u64 t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__global__ void __launch_bounds__(kPassThreads, 1) k_darlin_pass(const PsbDarlinPass q) {
+  __shared__ PsbDarlinGrad s_g;
+  __shared__ PsbDarlinUpdate s_u;
+  __shared__ PsbDarlinDual s_d;
+  const int R = q.ring;
+  const u32 n = q.n_steps, tau = (u32)q.tau;
+  if (tau == 0) {
+    for (u32 i = 0; i < n; ++i) {
+      const u32 ts = q.ts_base + i;
+      const size_t at = (size_t)q.order[i] * R + ts % R;
+      __syncthreads();                             // nobody still reads the previous step's blocks
+      load_params(&s_g, &q.grad[at]);
+      load_params(&s_u, &q.update[at]);
+      load_params(&s_d, &q.dual[at]);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        s_g.ts1 = s_u.ts1 = s_d.ts1 = ts + 1;
+        s_u.kkt_threshold = q.kkt_threshold;
+        s_u.wait_iters = s_d.wait_iters = q.wait_iters;
+      }
+      __syncthreads();
+      darlin_grad_p1(s_g);
+      if (!grid_barrier(q.bar, q.status)) return;
+      darlin_grad_p2(s_g, whole_grid());
+      if (s_u.S > 0) darlin_update_body(s_u, whole_grid());      // S == 0: none of the block's columns is mine
+      darlin_dual_wait(s_d);
+      darlin_dual_p1(s_d);
+      if (!grid_barrier(q.bar, q.status)) return;
+      darlin_dual_p2(s_d, whole_grid());
+      // the next gradient reads trust regions and the active set that the column pass wrote
+      if (!grid_barrier(q.bar, q.status)) return;
+    }
+    return;
+  }
+  // shares of the column passes: the owner update is the longest of the three, the column state the
+  // shortest; with fewer than six CTAs (never on a real device) every CTA would need all three
+  const u32 n_upd = gridDim.x / 2, n_out = gridDim.x / 3;
+  for (u32 i = 0; i < n + tau; ++i) {
+    const bool has_g = i < n, has_d = i >= tau, has_u = i + 1 >= tau && i + 1 - tau < n;
+    // With q.phase_ns, CTA 0 adds up where its time goes: {loading the parameter blocks, the two nonzero
+    // passes, barrier, its column pass (the owner update)} in nanoseconds (the CTA is held together at
+    // every mark).
+    u64 t[5];
+    auto mark = [&](int k) {
+      if (q.phase_ns == nullptr || blockIdx.x != 0) return;
+      __syncthreads();
+      if (threadIdx.x == 0) t[k] = globaltimer_ns();
+    };
+    mark(0);
+    __syncthreads();                               // nobody still reads the previous step's blocks
+    if (has_g) { const u32 ts = q.ts_base + i; load_params(&s_g, &q.grad[(size_t)q.order[i] * R + ts % R]); }
+    if (has_d) { const u32 ts = q.ts_base + i - tau; load_params(&s_d, &q.dual[(size_t)q.order[i - tau] * R + ts % R]); }
+    if (has_u) { const u32 ts = q.ts_base + i + 1 - tau; load_params(&s_u, &q.update[(size_t)q.order[i + 1 - tau] * R + ts % R]); }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      s_g.ts1 = q.ts_base + i + 1;
+      s_d.ts1 = q.ts_base + i - tau + 1;
+      s_u.ts1 = q.ts_base + i + 1 - tau + 1;
+      s_u.kkt_threshold = q.kkt_threshold;
+      s_u.wait_iters = s_d.wait_iters = q.wait_iters;
+    }
+    __syncthreads();
+    // phase A. Both nonzero passes are a burst of gathers followed by arithmetic; odd warps take them in
+    // the other order so that one half's arithmetic runs under the other half's memory latency.
+    mark(1);
+    if ((threadIdx.x >> 5) & 1) {
+      if (has_d) { darlin_dual_wait_warp(s_d); darlin_dual_p1(s_d); }
+      if (has_g) darlin_grad_p1(s_g);
+    } else {
+      if (has_g) darlin_grad_p1(s_g);
+      if (has_d) { darlin_dual_wait_warp(s_d); darlin_dual_p1(s_d); }
+    }
+    mark(2);
+    if (!grid_barrier(q.bar, q.status)) return;
+    mark(3);
+    // phase B: the three column passes side by side, each on its share of the CTAs
+    if (blockIdx.x < n_upd) {
+      if (has_u && s_u.S > 0) darlin_update_body(s_u, Part{blockIdx.x, n_upd});
+    } else if (blockIdx.x < n_upd + n_out) {
+      if (has_g) darlin_grad_p2(s_g, Part{blockIdx.x - n_upd, n_out});
+    } else {
+      if (has_d) darlin_dual_p2(s_d, Part{blockIdx.x - n_upd - n_out, gridDim.x - n_upd - n_out});
+    }
+    mark(4);
+    if (q.phase_ns != nullptr && blockIdx.x == 0 && threadIdx.x == 0)
+      for (int k = 0; k < 4; ++k) q.phase_ns[k] += t[k + 1] - t[k];
   }
 }
 
@@ -325,6 +523,16 @@ extern "C" int psb_darlin_dual(const PsbDarlinDual* p, cudaStream_t stream) {
   if (p->S < 1 || p->S > PSB_MAX_SHARDS || p->c1 - p->c0 > p->block_cap) return -(int)cudaErrorInvalidValue;
   return launch_darlin((const void*)k_darlin_dual, p, stream);
 }
+extern "C" int psb_darlin_pass(const PsbDarlinPass* p, cudaStream_t stream) {
+  if (p->ring < 1 || p->tau < 0 || p->tau + 1 > p->ring) return -(int)cudaErrorInvalidValue;
+  if (psb_device_sm_count() < 6) return -(int)cudaErrorInvalidValue;   // the column passes share the CTAs 3 : 2 : 1
+  // one CTA of 1024 threads per SM: the grid barrier gets shorter with fewer arrivals, and the gathers
+  // of the nonzero passes want every warp slot the register file allows
+  PsbDarlinPass local = *p;
+  void* args[] = {&local};
+  return -(int)cudaLaunchCooperativeKernel((const void*)k_darlin_pass, dim3(psb_device_sm_count()), dim3(kPassThreads), args,
+                                           0, stream);
+}
 extern "C" int psb_darlin_eval(const float* y, const float* margin, uint32_t n_rows, const float* w,
                                const unsigned char* active, uint32_t c0, uint32_t c1, float lambda, double* out,
                                cudaStream_t stream) {
@@ -332,5 +540,6 @@ extern "C" int psb_darlin_eval(const float* y, const float* margin, uint32_t n_r
   return -(int)cudaGetLastError();
 }
 extern "C" int psb_darlin_struct_size(int which) {
-  return which == 0 ? (int)sizeof(PsbDarlinGrad) : which == 1 ? (int)sizeof(PsbDarlinUpdate) : (int)sizeof(PsbDarlinDual);
+  return which == 0 ? (int)sizeof(PsbDarlinGrad) : which == 1 ? (int)sizeof(PsbDarlinUpdate)
+       : which == 2 ? (int)sizeof(PsbDarlinDual) : (int)sizeof(PsbDarlinPass);
 }

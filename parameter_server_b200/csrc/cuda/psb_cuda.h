@@ -346,6 +346,26 @@ typedef struct {
   uint32_t* bar; uint32_t* status;
 } PsbDarlinDual;
 
+// A pass over n_steps feature blocks in one cooperative launch (see k_darlin_pass). grad / update /
+// dual: device arrays of parameter blocks indexed [block * ring + stamp % ring], filled by the host
+// (an update block with S == 0 means "no column of that block is mine"); order: device array of
+// block indices; stamps ts_base .. ts_base + n_steps - 1.
+typedef struct {
+  const PsbDarlinGrad* grad;
+  const PsbDarlinUpdate* update;
+  const PsbDarlinDual* dual;
+  const uint32_t* order;
+  uint32_t n_steps;
+  uint32_t ts_base;
+  int tau;
+  int ring;
+  float kkt_threshold;
+  uint32_t wait_iters;
+  uint32_t* bar;
+  uint32_t* status;
+  psb_u64* phase_ns;            // optional: 4 accumulators of CTA 0's time per phase (see k_darlin_pass)
+} PsbDarlinPass;
+int psb_darlin_pass(const PsbDarlinPass* p, cudaStream_t stream);
 int psb_darlin_grad(const PsbDarlinGrad* p, cudaStream_t stream);
 int psb_darlin_update(const PsbDarlinUpdate* p, cudaStream_t stream);
 int psb_darlin_dual(const PsbDarlinDual* p, cudaStream_t stream);

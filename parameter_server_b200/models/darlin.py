@@ -24,7 +24,7 @@ import numpy as np
 import torch
 
 from ..ops import _lib
-from ..ops._lib import DarlinDual, DarlinGrad, DarlinUpdate, check, ptr, stream_ptr
+from ..ops._lib import DarlinDual, DarlinGrad, DarlinPass, DarlinUpdate, check, ptr, stream_ptr
 from ..ops.localize import LocalBatch
 from ..parallel.fabric import Fabric, HeapLayout
 from ..utils.range import Range, shard_bounds
@@ -89,9 +89,10 @@ class DarlinRank:
         self.sync = torch.zeros(16, dtype=torch.int32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.violation = torch.zeros(1, dtype=torch.float32, device=dev)
-        self.stage = torch.zeros(2 * cfg.block_cols, dtype=torch.float32, device=dev)
+        self.stage = torch.zeros(self.R * 2 * cfg.block_cols, dtype=torch.float32, device=dev)   # one area per ring slot
         self.kkt_threshold = 1e20
         self.step = 0
+        self.phase_ns: Optional[torch.Tensor] = None   # int64[4]: set to have run_pass add up its phase times
 
     def set_global_keys(self, global_keys: torch.Tensor):
         """``global_keys``: the sorted global key list (uint64 as int64, on the device). The local keys'
@@ -127,6 +128,7 @@ class DarlinRank:
         self.blocks = list(blocks)
         self.prior_blocks = list(prior or [])
         self.__dict__.pop("_param_cache", None)
+        self.__dict__.pop("_pass_dev", None)
 
     # ---- addresses in a rank's heap
     def _flag(self, rank: int, kind: int, q: int, idx: int) -> int:
@@ -154,45 +156,38 @@ class DarlinRank:
         cache = self.__dict__.setdefault("_param_cache", {})
         return cache, (kind, blk, q), cache.get((kind, blk, q))
 
-    def grad(self, blk: int, ts: int, stream=None):
-        q = ts % self.R
+    def _grad_params(self, blk: int, q: int) -> DarlinGrad:
         cache, key, p = self._cached("grad", blk, q)
         if p is not None:
-            p.ts1 = ts + 1
-            check(_lib.lib().psb_darlin_grad(C.byref(p), stream_ptr(stream)), "darlin_grad")
-            return
+            return p
         c0, c1 = self.blocks[blk]
         u0, u1 = self._block_u(c0, c1)
         p = cache[key] = DarlinGrad()
-        p.S, p.ts1, p.c0, p.c1, p.u0, p.u1, p.block_cap = self.S, ts + 1, c0, c1, u0, u1, self.cfg.block_cols
+        p.S, p.c0, p.c1, p.u0, p.u1, p.block_cap = self.S, c0, c1, u0, u1, self.cfg.block_cols
         for s in range(self.S + 1):
             p.shard_col[s] = self.shard_col[s]
         b = self.b
         p.seg_off, p.csc_row, p.csc_val = ptr(b.seg_off), ptr(b.csc_row), ptr(b.csc_val)
         p.flagbits, p.wordbase, p.gcol = ptr(b.flagbits), ptr(b.wordbase), ptr(self.gcol)
-        p.y, p.margin, p.active, p.delta, p.stage = ptr(self.y), ptr(self.margin), ptr(self.active_w), ptr(self.delta_w), ptr(self.stage)
+        p.y, p.margin, p.active, p.delta, p.stage = ptr(self.y), ptr(self.margin), ptr(self.active_w), ptr(self.delta_w), self.stage.data_ptr() + q * 2 * self.cfg.block_cols * 4
         for s in range(self.S):
             p.gu_inbox[s] = self._gu(s, q, self.rank)
             p.ready[s] = self._flag(s, 0, q, self.rank)
         p.bar, p.done, p.status = self.sync.data_ptr(), self.sync.data_ptr() + 8, ptr(self.status)
-        check(_lib.lib().psb_darlin_grad(C.byref(p), stream_ptr(stream)), "darlin_grad")
+        return p
 
-    def update(self, blk: int, ts: int, wait_iters: int = 0, stream=None):
-        q = ts % self.R
+    def _update_params(self, blk: int, q: int):
+        """The owner's parameter block, or False when none of the block's columns is mine."""
         cache, key, p = self._cached("update", blk, q)
         if p is not None:
-            if p is False:
-                return
-            p.ts1, p.kkt_threshold, p.wait_iters = ts + 1, self.kkt_threshold, wait_iters
-            check(_lib.lib().psb_darlin_update(C.byref(p), stream_ptr(stream)), "darlin_update")
-            return
+            return p
         c0, c1 = self.blocks[blk]
         my0, my1 = max(c0, self.shard_col[self.rank]), min(c1, self.shard_col[self.rank + 1])
         if my1 <= my0:
             cache[key] = False
-            return                                    # no column of this block is mine
+            return False
         p = cache[key] = DarlinUpdate()
-        p.S, p.ts1, p.c0, p.c1, p.my0, p.my1, p.block_cap = self.S, ts + 1, c0, c1, my0, my1, self.cfg.block_cols
+        p.S, p.c0, p.c1, p.my0, p.my1, p.block_cap = self.S, c0, c1, my0, my1, self.cfg.block_cols
         for r in range(self.S):
             p.gu_inbox[r] = self._gu(self.rank, q, r)
             p.ready[r] = self._flag(self.rank, 0, q, r)
@@ -201,22 +196,19 @@ class DarlinRank:
             p.wnew_ready[r] = self._flag(r, 1, q, self.rank)
         p.w, p.delta, p.active = ptr(self.w_own), ptr(self.delta_own), ptr(self.active_own)
         cfg = self.cfg
-        p.eta, p.lam, p.delta_max, p.kkt_threshold = cfg.eta, cfg.lambda_l1, cfg.delta_max, self.kkt_threshold
-        p.violation, p.wait_iters = ptr(self.violation), wait_iters
+        p.eta, p.lam, p.delta_max = cfg.eta, cfg.lambda_l1, cfg.delta_max
+        p.violation = ptr(self.violation)
         p.done, p.status = self.sync.data_ptr() + 24, ptr(self.status)
-        check(_lib.lib().psb_darlin_update(C.byref(p), stream_ptr(stream)), "darlin_update")
+        return p
 
-    def dual(self, blk: int, ts: int, wait_iters: int = 0, stream=None):
-        q = ts % self.R
+    def _dual_params(self, blk: int, q: int) -> DarlinDual:
         cache, key, p = self._cached("dual", blk, q)
         if p is not None:
-            p.ts1, p.wait_iters = ts + 1, wait_iters
-            check(_lib.lib().psb_darlin_dual(C.byref(p), stream_ptr(stream)), "darlin_dual")
-            return
+            return p
         c0, c1 = self.blocks[blk]
         u0, u1 = self._block_u(c0, c1)
         p = cache[key] = DarlinDual()
-        p.S, p.ts1, p.c0, p.c1, p.u0, p.u1, p.block_cap = self.S, ts + 1, c0, c1, u0, u1, self.cfg.block_cols
+        p.S, p.c0, p.c1, p.u0, p.u1, p.block_cap = self.S, c0, c1, u0, u1, self.cfg.block_cols
         for s in range(self.S + 1):
             p.shard_col[s] = self.shard_col[s]
         b = self.b
@@ -227,9 +219,62 @@ class DarlinRank:
         for s in range(self.S):
             p.wnew_ready[s] = self._flag(self.rank, 1, q, s)
             p.alive[s] = 1
-        p.wait_iters = wait_iters
         p.bar, p.status = self.sync.data_ptr() + 32, ptr(self.status)
+        return p
+
+    def grad(self, blk: int, ts: int, stream=None):
+        p = self._grad_params(blk, ts % self.R)
+        p.ts1 = ts + 1
+        check(_lib.lib().psb_darlin_grad(C.byref(p), stream_ptr(stream)), "darlin_grad")
+
+    def update(self, blk: int, ts: int, wait_iters: int = 0, stream=None):
+        p = self._update_params(blk, ts % self.R)
+        if p is False:
+            return                                    # no column of this block is mine
+        p.ts1, p.kkt_threshold, p.wait_iters = ts + 1, self.kkt_threshold, wait_iters
+        check(_lib.lib().psb_darlin_update(C.byref(p), stream_ptr(stream)), "darlin_update")
+
+    def dual(self, blk: int, ts: int, wait_iters: int = 0, stream=None):
+        p = self._dual_params(blk, ts % self.R)
+        p.ts1, p.wait_iters = ts + 1, wait_iters
         check(_lib.lib().psb_darlin_dual(C.byref(p), stream_ptr(stream)), "darlin_dual")
+
+    # ---- a whole pass in one launch
+    def _pass_arrays(self):
+        """Device copies of every block's parameter blocks, [block * R + ring slot] (built once)."""
+        arr = self.__dict__.get("_pass_dev")
+        if arr is not None:
+            return arr
+        nb, R = len(self.blocks), self.R
+        G, U, D = (DarlinGrad * (nb * R))(), (DarlinUpdate * (nb * R))(), (DarlinDual * (nb * R))()
+        for blk in range(nb):
+            for q in range(R):
+                C.memmove(C.byref(G, (blk * R + q) * C.sizeof(DarlinGrad)), C.byref(self._grad_params(blk, q)), C.sizeof(DarlinGrad))
+                u = self._update_params(blk, q)
+                if u is not False:
+                    C.memmove(C.byref(U, (blk * R + q) * C.sizeof(DarlinUpdate)), C.byref(u), C.sizeof(DarlinUpdate))
+                C.memmove(C.byref(D, (blk * R + q) * C.sizeof(DarlinDual)), C.byref(self._dual_params(blk, q)), C.sizeof(DarlinDual))
+
+        def to_dev(a):
+            return torch.frombuffer(bytearray(bytes(a)), dtype=torch.uint8).to(self.dev)
+        arr = self._pass_dev = (to_dev(G), to_dev(U), to_dev(D))
+        self._pass_bar = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        return arr
+
+    def run_pass(self, order: Sequence[int], ts_base: int, tau: int, wait_iters: int = 0, stream=None):
+        """All blocks of ``order`` with stamps ``ts_base ..`` in ONE cooperative launch: gradients run
+        ``tau`` blocks ahead of the weight application (``k_darlin_pass``). Only for one rank per GPU:
+        ranks that share a GPU would wait for each other's launches."""
+        G, U, D = self._pass_arrays()
+        p = DarlinPass()
+        od = torch.tensor(list(order), dtype=torch.int32, device=self.dev)
+        p.grad, p.update, p.dual, p.order = ptr(G), ptr(U), ptr(D), ptr(od)
+        p.n_steps, p.ts_base, p.tau, p.ring = len(order), ts_base, tau, self.R
+        p.kkt_threshold, p.wait_iters = self.kkt_threshold, wait_iters
+        p.bar, p.status = ptr(self._pass_bar), ptr(self.status)
+        p.phase_ns = ptr(self.phase_ns) if self.phase_ns is not None else None
+        check(_lib.lib().psb_darlin_pass(C.byref(p), stream_ptr(stream)), "darlin_pass")
+        self._pass_order = od          # keep the schedule alive until the launch has run
 
     def reset_kkt_filter(self):
         self.active_own.fill_(1)
@@ -272,6 +317,8 @@ def run_darlin(ranks: Sequence[DarlinRank], *, all_reduce=None, verbose: bool = 
     ts = 0
     reset_kkt = False
     n_ex = num_examples or sum(r.n_rows for r in ranks)
+    if len(ranks) == 1:
+        ranks[0]._pass_arrays()                    # host work that is not part of a pass
     for it in range(cfg.max_pass):
         order = list(range(nb))
         if cfg.random_block_order:
@@ -279,43 +326,27 @@ def run_darlin(ranks: Sequence[DarlinRank], *, all_reduce=None, verbose: bool = 
         if reset_kkt:
             for r in ranks:
                 r.reset_kkt_filter()
-        if it == 0 and ranks[0].prior_blocks:
-            # the prior groups' blocks first, strictly one after another
-            for blk in ranks[0].prior_blocks:
-                for r in ranks:
-                    r.grad(blk, ts)
-                for r in ranks:
-                    r.update(blk, ts)
-                for r in ranks:
-                    r.dual(blk, ts)
-                ts += 1
-        # software pipeline: gradients run `tau` blocks ahead of the weight application
-        if len(ranks) == 1 and tau > 0:
-            # One rank per process: the gradient kernels go to one stream and update + dual to
-            # another, so that the small, latency-bound kernels of different blocks overlap.
-            # Bounded delay: the gradient of block i waits for the dual update of block
-            # i - tau - 1 (an event); update(j) is enqueued after the local grad(j) has
-            # finished (an event), so its device-side waits are for other GPUs only.
+        ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        ev[0].record()
+        if len(ranks) == 1:
+            # one rank per GPU: the whole pass is one persistent kernel (the prior blocks, one after
+            # another, form a pass of their own with no delay)
             r = ranks[0]
-            sg, su = r.streams()
-            cur = torch.cuda.current_stream(r.dev)
-            sg.wait_stream(cur); su.wait_stream(cur)
-            ev_grad = [torch.cuda.Event() for _ in order]
-            ev_dual = [torch.cuda.Event() for _ in order]
-            for i in range(len(order) + tau):
-                if i < len(order):
-                    if i - tau - 1 >= 0:
-                        sg.wait_event(ev_dual[i - tau - 1])
-                    r.grad(order[i], ts + i, stream=sg)
-                    ev_grad[i].record(sg)
-                j = i - tau
-                if j >= 0:
-                    su.wait_event(ev_grad[j])
-                    r.update(order[j], ts + j, stream=su)
-                    r.dual(order[j], ts + j, stream=su)
-                    ev_dual[j].record(su)
-            cur.wait_stream(sg); cur.wait_stream(su)
+            if it == 0 and r.prior_blocks:
+                r.run_pass(r.prior_blocks, ts, 0)
+                ts += len(r.prior_blocks)
+            r.run_pass(order, ts, tau)
         else:
+            # ranks emulated on one GPU: their kernels run one after another, block by block
+            if it == 0 and ranks[0].prior_blocks:
+                for blk in ranks[0].prior_blocks:
+                    for r in ranks:
+                        r.grad(blk, ts)
+                    for r in ranks:
+                        r.update(blk, ts)
+                    for r in ranks:
+                        r.dual(blk, ts)
+                    ts += 1
             for i in range(len(order) + tau):
                 if i < len(order):
                     for r in ranks:
@@ -327,6 +358,7 @@ def run_darlin(ranks: Sequence[DarlinRank], *, all_reduce=None, verbose: bool = 
                     for r in ranks:
                         r.dual(order[j], ts + j)
         ts += len(order)
+        ev[1].record()
         loss = l1 = nnz = act = vio = 0.0
         for r in ranks:
             a = r.evaluate()
@@ -337,7 +369,8 @@ def run_darlin(ranks: Sequence[DarlinRank], *, all_reduce=None, verbose: bool = 
             vio = all_reduce([vio], "max")[0]
         obj = loss + l1
         rel = (history[-1]["objective"] - obj) / history[-1]["objective"] if history else 1.0
-        history.append(dict(iter=it, objective=obj, relative=rel, nnz_w=int(nnz), violation=vio, active=int(act)))
+        history.append(dict(iter=it, objective=obj, relative=rel, nnz_w=int(nnz), violation=vio, active=int(act),
+                            device_ms=ev[0].elapsed_time(ev[1])))      # the pass on the device (evaluate() has synchronised)
         if verbose:
             print(f" {it:5d} | {obj:.5e}  {rel:.3e}  {int(nnz):8d} | {vio:.3e}  {int(act):9d}")
         thr = vio / max(1, n_ex) * cfg.kkt_ratio

@@ -131,6 +131,15 @@ class DarlinDual(C.Structure):
     ]
 
 
+class DarlinPass(C.Structure):
+    _fields_ = [
+        ("grad", _vp), ("update", _vp), ("dual", _vp), ("order", _vp),
+        ("n_steps", _u32), ("ts_base", _u32), ("tau", _i32), ("ring", _i32),
+        ("kkt_threshold", _f32), ("wait_iters", _u32), ("bar", _vp), ("status", _vp),
+        ("phase_ns", _vp),
+    ]
+
+
 _LIB = None
 LAUNCHES = 0
 
@@ -179,6 +188,7 @@ def _declare(lib):
     lib.psb_darlin_grad.argtypes = [C.POINTER(DarlinGrad), _vp]
     lib.psb_darlin_update.argtypes = [C.POINTER(DarlinUpdate), _vp]
     lib.psb_darlin_dual.argtypes = [C.POINTER(DarlinDual), _vp]
+    lib.psb_darlin_pass.argtypes = [C.POINTER(DarlinPass), _vp]
     lib.psb_darlin_eval.argtypes = [_vp, _vp, _u32, _vp, _vp, _u32, _u32, _f32, _vp, _vp]
     lib.psb_darlin_struct_size.argtypes = [_i32]
     lib.psb_key_signature.argtypes = [_vp, _vp, _u32, _vp, _vp, _vp, _vp, _vp]
@@ -234,7 +244,7 @@ def lib():
             if _LIB.psb_struct_size(which) != C.sizeof(st):
                 raise RuntimeError(f"{st.__name__}: binding struct is {C.sizeof(st)} bytes, "
                                    f"library expects {_LIB.psb_struct_size(which)}")
-        for which, st in enumerate((DarlinGrad, DarlinUpdate, DarlinDual)):
+        for which, st in enumerate((DarlinGrad, DarlinUpdate, DarlinDual, DarlinPass)):
             if _LIB.psb_darlin_struct_size(which) != C.sizeof(st):
                 raise RuntimeError(f"{st.__name__}: binding struct is {C.sizeof(st)} bytes, "
                                    f"library expects {_LIB.psb_darlin_struct_size(which)}")

@@ -408,13 +408,25 @@ def bench_darlin(args):
         dist.barrier()
     torch.cuda.synchronize()
     t0 = time.time()
+    if args.phases:
+        r.phase_ns = torch.zeros(4, dtype=torch.int64, device=dev)
     hist = run_darlin([r], all_reduce=all_reduce if world > 1 else None, num_examples=rows * world)
     torch.cuda.synchronize()
     dt = time.time() - t0
+    dev_ms = [h["device_ms"] for h in hist]
+    if world > 1:
+        t = torch.tensor(dev_ms, dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms = t.tolist()
     if rank == 0:
         print(json.dumps({"kernel": "darlin", "gpus": world, "rows_per_gpu": rows, "nnz_per_row": z, "features": nf,
                           "blocks_per_pass": len(r.blocks), "tau": args.tau, "preprocess_s": prep,
                           "s_per_pass": dt / len(hist), "examples_per_s_per_pass": rows * world * len(hist) / dt,
+                          "device_ms_per_pass_max_over_ranks": [round(v, 3) for v in dev_ms],
+                          "examples_per_s_device": rows * world / (min(dev_ms) * 1e-3),
+                          "phase_ms_per_pass_cta0": None if r.phase_ns is None else dict(zip(
+                              ["load_parameter_blocks", "nonzero_passes", "barrier", "owner_update"],
+                              [round(v / 1e6 / len(hist), 3) for v in r.phase_ns.tolist()])),
                           "objective": [h["objective"] for h in hist], "nnz_w": hist[-1]["nnz_w"]}))
     if world > 1:
         dist.barrier(); fab.close(); dist.destroy_process_group()
@@ -588,7 +600,7 @@ def main():
     s.add_argument("--log2-keys", type=int, default=25); s.add_argument("--n-ctx", type=int, default=64)
     s.add_argument("--iters", type=int, default=20); s.add_argument("--tau", type=int, default=8); s.add_argument("--pool", type=int, default=4)
     s.add_argument("--one-sided", action="store_true", help="pull by remote probes instead of the exchange kernel")
-    s = sub.add_parser("darlin"); s.add_argument("--rows", type=int, default=1250000); s.add_argument("--z", type=int, default=100)
+    s = sub.add_parser("darlin"); s.add_argument("--phases", action="store_true"); s.add_argument("--rows", type=int, default=1250000); s.add_argument("--z", type=int, default=100)
     s.add_argument("--log2-keys", type=int, default=24); s.add_argument("--passes", type=int, default=3)
     s.add_argument("--tau", type=int, default=2)
     s = sub.add_parser("kv"); s.add_argument("--sizes", type=int, nargs="+", default=[1000, 100000, 1000000, 16000000])

@@ -145,6 +145,32 @@ def test_darlin(rank, world, dev):
             bool(np.allclose(got, np.where(np.isnan(w_ref), 0, w_ref), rtol=2e-3, atol=2e-4))
         if not ok:
             print("darlin objective", [h["objective"] for h in hist], "oracle", h_ref)
+    # With a block delay the pass kernel overlaps the blocks' steps across the GPUs: every wait must be
+    # met (status 0) and the objectives must follow the delayed restatement. (Not to the last digit: on
+    # the device the gradient of block i runs beside the margin update of block i - tau, so it sees
+    # some of it.) A small step and many blocks, since a delay of tau blocks out of five diverges.
+    import dataclasses
+    for tau in (1, 2):
+        cfg_t = dataclasses.replace(cfg, tau=tau, eta=0.3, block_cols=16, max_pass=5)
+        fab_t = Fabric.from_process_group(darlin_heap_bytes(cfg_t, world))
+        rt = DarlinRank(fab_t, cfg_t, torch.from_numpy(keys.view(np.int64)).to(dev), torch.from_numpy(y).to(dev), fixed_z=z,
+                        global_keys=torch.from_numpy(gk.view(np.int64)).to(dev))
+        ht = run_darlin([rt], all_reduce=all_reduce, num_examples=rows * world)
+        torch.cuda.synchronize()
+        rt.check_status(f"rank {rank} tau {tau}")
+        if rank == 0:
+            orders = []
+            for it in range(cfg_t.max_pass):
+                o = list(range(len(rt.blocks))); np.random.default_rng(1000 + it).shuffle(o)
+                orders.append([rt.blocks[i] for i in o])
+            _, h_ref = oracle.darlin_oracle([(k, row_ptr, yy, None) for k, yy in parts], gk, cfg_t.lambda_l1, cfg_t.eta,
+                                            cfg_t.delta_init, cfg_t.delta_max, orders, cfg_t.max_pass, cfg_t.kkt_ratio, tau=tau)
+            got = [h["objective"] for h in ht]
+            if not (np.allclose(got, h_ref, rtol=5e-3) and got[-1] < got[0]):
+                ok = False
+                print(f"darlin with delay {tau}: objective", got, "delayed restatement", h_ref)
+        dist.barrier()
+        fab_t.close()
     return ok, fab
 
 

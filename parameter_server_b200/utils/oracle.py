@@ -185,10 +185,11 @@ def auc(y, score):
     return float(a)
 
 
-def darlin_oracle(parts, global_keys, lam, eta, delta_init, delta_max, blocks_per_pass, n_pass, kkt_ratio=10.0):
-    """NumPy restatement of Darlin with BSP blocks (no delay). ``parts``: list of
-    (keys_flat uint64, row_ptr, y, vals or None) per worker; ``blocks_per_pass``:
-    list (per pass) of lists of (c0, c1) column ranges in processing order.
+def darlin_oracle(parts, global_keys, lam, eta, delta_init, delta_max, blocks_per_pass, n_pass, kkt_ratio=10.0, tau=0):
+    """NumPy restatement of Darlin. ``parts``: list of (keys_flat uint64, row_ptr, y, vals or None) per
+    worker; ``blocks_per_pass``: list (per pass) of lists of (c0, c1) column ranges in processing order.
+    ``tau``: block delay: the gradient of the i-th block of a pass is taken before the weights of the
+    blocks i - tau .. i - 1 reach the margins (0: every block sees all earlier ones).
     Returns (w per global column, history of objectives)."""
     ncol = len(global_keys)
     w = np.zeros(ncol, f32); delta = np.full(ncol, delta_init, f32); active = np.ones(ncol, bool)
@@ -201,45 +202,59 @@ def darlin_oracle(parts, global_keys, lam, eta, delta_init, delta_max, blocks_pe
     n_ex = sum(len(d["y"]) for d in data)
     thr = 1e20
     hist = []
+
+    def gradient(c0, c1):
+        G = np.zeros(c1 - c0, np.float64); U = np.zeros(c1 - c0, np.float64)
+        for d in data:
+            sel = (d["col"] >= c0) & (d["col"] < c1) & active[d["col"]]
+            c, r, x = d["col"][sel], d["rows"][sel], d["x"][sel]
+            ym = d["y"][r] * d["m"][r]
+            en = np.exp(-np.abs(ym)); t = np.where(ym > 0, en / (1 + en), 1 / (1 + en))
+            dl = delta[c]
+            if d["binary"]:
+                g = -d["y"][r] * t; h = np.minimum(t * (1 - t) * np.exp(dl), 0.25)
+            else:
+                g = -d["y"][r] * t * x; h = np.minimum(t * (1 - t) * np.exp(np.abs(x) * dl), 0.25) * x * x
+            np.add.at(G, c - c0, g); np.add.at(U, c - c0, h)
+        return G, U
+
+    def apply(c0, c1, G, U, thr):
+        vio_max = 0.0
+        new_w = w[c0:c1].copy()
+        for j in range(c1 - c0):
+            k = c0 + j
+            if not active[k]:
+                continue
+            g, u = f32(G[j]), f32(U[j]) / f32(eta) + f32(1e-10)
+            gp, gn = g + f32(lam), g - f32(lam)
+            wk = w[k]; dd = -wk; vio = 0.0
+            if wk == 0:
+                if gp < 0: vio = -gp
+                elif gn > 0: vio = gn
+                elif gp > thr and gn < -thr:
+                    active[k] = False; continue
+            vio_max = max(vio_max, float(vio))
+            if gp <= u * wk: dd = -gp / u
+            elif gn >= u * wk: dd = -gn / u
+            dd = min(delta[k], max(-delta[k], dd))
+            delta[k] = min(delta_max, 2 * abs(dd) + 0.1)
+            new_w[j] = wk + dd
+        dw = new_w - w[c0:c1]
+        for d in data:
+            sel = (d["col"] >= c0) & (d["col"] < c1) & active[d["col"]]
+            np.add.at(d["m"], d["rows"][sel], dw[d["col"][sel] - c0] * d["x"][sel])
+        w[c0:c1] = new_w
+        return vio_max
+
     for it in range(n_pass):
         vio_max = 0.0
-        for (c0, c1) in blocks_per_pass[it]:
-            G = np.zeros(c1 - c0, np.float64); U = np.zeros(c1 - c0, np.float64)
-            for d in data:
-                sel = (d["col"] >= c0) & (d["col"] < c1) & active[d["col"]]
-                c, r, x = d["col"][sel], d["rows"][sel], d["x"][sel]
-                ym = d["y"][r] * d["m"][r]
-                en = np.exp(-np.abs(ym)); tau = np.where(ym > 0, en / (1 + en), 1 / (1 + en))
-                dl = delta[c]
-                if d["binary"]:
-                    g = -d["y"][r] * tau; h = np.minimum(tau * (1 - tau) * np.exp(dl), 0.25)
-                else:
-                    g = -d["y"][r] * tau * x; h = np.minimum(tau * (1 - tau) * np.exp(np.abs(x) * dl), 0.25) * x * x
-                np.add.at(G, c - c0, g); np.add.at(U, c - c0, h)
-            new_w = w[c0:c1].copy()
-            for j in range(c1 - c0):
-                k = c0 + j
-                if not active[k]:
-                    continue
-                g, u = f32(G[j]), f32(U[j]) / f32(eta) + f32(1e-10)
-                gp, gn = g + f32(lam), g - f32(lam)
-                wk = w[k]; dd = -wk; vio = 0.0
-                if wk == 0:
-                    if gp < 0: vio = -gp
-                    elif gn > 0: vio = gn
-                    elif gp > thr and gn < -thr:
-                        active[k] = False; continue
-                vio_max = max(vio_max, float(vio))
-                if gp <= u * wk: dd = -gp / u
-                elif gn >= u * wk: dd = -gn / u
-                dd = min(delta[k], max(-delta[k], dd))
-                delta[k] = min(delta_max, 2 * abs(dd) + 0.1)
-                new_w[j] = wk + dd
-            dw = new_w - w[c0:c1]
-            for d in data:
-                sel = (d["col"] >= c0) & (d["col"] < c1) & active[d["col"]]
-                np.add.at(d["m"], d["rows"][sel], dw[d["col"][sel] - c0] * d["x"][sel])
-            w[c0:c1] = new_w
+        blocks = blocks_per_pass[it]
+        waiting = {}
+        for i in range(len(blocks) + tau):
+            if i < len(blocks):
+                waiting[i] = gradient(*blocks[i])
+            if i >= tau:
+                vio_max = max(vio_max, apply(*blocks[i - tau], *waiting.pop(i - tau), thr))
         loss = sum(float(np.sum(np.log1p(np.exp(-np.abs(d["y"] * d["m"]))) + np.maximum(-d["y"] * d["m"], 0))) for d in data)
         hist.append(loss + lam * float(np.abs(w).sum()))
         thr = vio_max / n_ex * kkt_ratio
