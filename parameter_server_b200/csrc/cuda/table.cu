@@ -247,6 +247,7 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
   __shared__ u32 s_off[PSB_MAX_SHARDS + 1];
   __shared__ u32 s_last;
   __shared__ u32 s_n, s_base;
+  __shared__ u32 s_wslot[kThreads];                // slots of a tile of the k-wide owner path
   const int S = p.S;
   const u32 U = *p.n_unique;
   const u32 iters = p.wait_iters ? p.wait_iters : kPeerWaitIters;
@@ -337,19 +338,55 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
     PSB_TSTAMP(3);
     const u32 n = s_n & 0x7fffffffu, base = s_base;
     const int kw = p.width > 1 ? p.width : 1;
+    if (kw > 1) {
+      // k values per key. A CTA takes tiles of blockDim.x keys: one thread per key finds the slot
+      // (remembered slots on a key-cache hit at the source), then the whole CTA copies the tile's
+      // k-wide rows with consecutive threads on consecutive values (16 bytes each when k % 4 == 0),
+      // so that the peer stores of a warp form whole lines.
+      const bool hit = (s_n & 0x80000000u) != 0;
+      for (u32 t0 = blockIdx.x * blockDim.x; t0 < n; t0 += gridDim.x * blockDim.x) {
+        const u32 j = t0 + threadIdx.x;
+        if (j < n) {
+          u32 sc;
+          if (hit) {
+            sc = p.slot_cache_prev[r][j] & 0x7fffffffu;
+          } else {
+            const long long sl = table_find<true>(tab, sm, p.my_req_keys[r][j], kMaxProbe);
+            sc = sl >= 0 ? (u32)sl : 0x7fffffffu;
+            if (sl < 0) set_status(p.status, kTableFull);
+          }
+          p.slot_cache[r][j] = sc;
+          s_wslot[threadIdx.x] = sc;
+        }
+        __syncthreads();
+        const u32 cnt = min((u32)blockDim.x, n - t0);
+        float* dst = p.resp_w[r] + (size_t)(base + t0) * kw;
+        if ((kw & 3) == 0) {
+          const u32 q4 = (u32)kw >> 2;
+          for (u32 idx = threadIdx.x; idx < cnt * q4; idx += blockDim.x) {
+            const u32 jj = idx / q4, c4 = idx - jj * q4, sc = s_wslot[jj];
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (sc != 0x7fffffffu) v = __ldcg(reinterpret_cast<const float4*>(p.wide_vals + (size_t)sc * kw) + c4);
+            reinterpret_cast<float4*>(dst)[idx] = v;
+          }
+        } else {
+          for (u32 idx = threadIdx.x; idx < cnt * (u32)kw; idx += blockDim.x) {
+            const u32 jj = idx / (u32)kw, c = idx - jj * (u32)kw, sc = s_wslot[jj];
+            dst[idx] = sc != 0x7fffffffu ? __ldcg(&p.wide_vals[(size_t)sc * kw + c]) : 0.f;
+          }
+        }
+        __syncthreads();
+      }
+      continue;
+    }
     if (s_n & 0x80000000u) {
       // key-cache hit at the source: same keys as in the round before, so the same slots
       for (u32 j = gtid; j < n; j += gsize) {
         const u32 sc = p.slot_cache_prev[r][j] & 0x7fffffffu;
         p.slot_cache[r][j] = sc;
-        if (kw == 1) {
-          float w = 0.f;
-          if (sc != 0x7fffffffu) w = __ldcg(&tab[sc].w);
-          p.resp_w[r][base + j] = w;
-        } else {
-          for (int c = 0; c < kw; ++c)
-            p.resp_w[r][(size_t)(base + j) * kw + c] = sc != 0x7fffffffu ? __ldcg(&p.wide_vals[(size_t)sc * kw + c]) : 0.f;
-        }
+        float w = 0.f;
+        if (sc != 0x7fffffffu) w = __ldcg(&tab[sc].w);
+        p.resp_w[r][base + j] = w;
       }
       continue;
     }
@@ -386,12 +423,7 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
           else set_status(p.status, kTableFull);
         }
         p.slot_cache[r][j] = sc;
-        if (kw == 1) {
-          p.resp_w[r][base + j] = w;
-        } else {
-          for (int c = 0; c < kw; ++c)
-            p.resp_w[r][(size_t)(base + j) * kw + c] = sc != 0x7fffffffu ? __ldcg(&p.wide_vals[(size_t)sc * kw + c]) : 0.f;
-        }
+        p.resp_w[r][base + j] = w;
       }
     }
   }
@@ -672,6 +704,7 @@ __device__ __forceinline__ float inbox_value(const void* vals, int quant, u32 ca
 }
 
 __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
+  __shared__ u32 s_wslot[kThreads], s_wsrc[kThreads], s_wrec[kThreads];   // a tile of the k-wide path
   __shared__ u32 s_pre[PSB_MAX_SHARDS + 1];
   __shared__ u32 s_cached[PSB_MAX_SHARDS];
   __shared__ u32 s_last;
@@ -707,29 +740,60 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
   StatAcc st;
 
   if (p.width > 1) {
-    // k values per key, sum entries: every record adds its k values to wide_vals[slot * k ..]. One
-    // source: plain read-modify-write (a slot belongs to one record); several: atomic adds.
+    // k values per key, sum entries: every record adds its k values to wide_vals[slot * k ..]. A CTA
+    // takes tiles of blockDim.x records: one thread per record finds the slot, then the CTA adds the
+    // tile's values with consecutive threads on consecutive values (coalesced inbox reads; 16 bytes
+    // per thread where the inbox holds plain floats and k % 4 == 0). One source: plain
+    // read-modify-write (a slot belongs to one record); several: atomic adds.
     const u32 kw = (u32)p.width, vcap = p.inbox_cap * kw;
-    for (u32 i = gtid; i < total; i += gsize) {
-      int r = 0;
-      while (r + 1 < S && i >= s_pre[r + 1]) ++r;
-      const u32 j = i - s_pre[r];
-      long long slot;
-      if (s_cached[r]) {
-        const u32 sc = p.slot_cache[r][j] & 0x7fffffffu;
-        slot = sc != 0x7fffffffu ? (long long)sc : -1;
-      } else {
-        slot = table_find<true>(tab, sm, p.inbox_keys[r][j], kMaxProbe);
-        if (slot < 0) set_status(p.status, kTableFull);
-      }
-      if (slot < 0) continue;
-      float* dst = p.wide_vals + (size_t)slot * kw;
-      if (p.opt.algo != PSB_ALGO_KEEP)
-        for (u32 c = 0; c < kw; ++c) {
-          const float g = inbox_value(p.inbox_vals[r], p.quant, vcap, j * kw + c);
-          if (single) dst[c] += g; else atomicAdd(&dst[c], g);
+    for (u32 t0 = blockIdx.x * blockDim.x; t0 < total; t0 += gridDim.x * blockDim.x) {
+      const u32 i = t0 + threadIdx.x;
+      if (i < total) {
+        int r = 0;
+        while (r + 1 < S && i >= s_pre[r + 1]) ++r;
+        const u32 j = i - s_pre[r];
+        u32 sc;
+        if (s_cached[r]) {
+          sc = p.slot_cache[r][j] & 0x7fffffffu;
+        } else {
+          const long long sl = table_find<true>(tab, sm, p.inbox_keys[r][j], kMaxProbe);
+          sc = sl >= 0 ? (u32)sl : 0x7fffffffu;
+          if (sl < 0) set_status(p.status, kTableFull);
         }
-      st.n += 1;
+        s_wslot[threadIdx.x] = sc;
+        s_wsrc[threadIdx.x] = (u32)r;
+        s_wrec[threadIdx.x] = j;
+        if (sc != 0x7fffffffu) st.n += 1;
+      }
+      __syncthreads();
+      const u32 cnt = min((u32)blockDim.x, total - t0);
+      if (p.opt.algo != PSB_ALGO_KEEP) {
+        if ((kw & 3) == 0 && p.quant == PSB_QUANT_NONE) {
+          const u32 q4 = kw >> 2;
+          for (u32 idx = threadIdx.x; idx < cnt * q4; idx += blockDim.x) {
+            const u32 jj = idx / q4, c4 = idx - jj * q4, sc = s_wslot[jj];
+            if (sc == 0x7fffffffu) continue;
+            const float4 g = reinterpret_cast<const float4*>((const float*)p.inbox_vals[s_wsrc[jj]] + (size_t)s_wrec[jj] * kw)[c4];
+            float4* dst = reinterpret_cast<float4*>(p.wide_vals + (size_t)sc * kw) + c4;
+            if (single) {
+              float4 o = *dst;
+              o.x += g.x; o.y += g.y; o.z += g.z; o.w += g.w;
+              *dst = o;
+            } else {
+              atomicAdd(dst, g);
+            }
+          }
+        } else {
+          for (u32 idx = threadIdx.x; idx < cnt * kw; idx += blockDim.x) {
+            const u32 jj = idx / kw, c = idx - jj * kw, sc = s_wslot[jj];
+            if (sc == 0x7fffffffu) continue;
+            const float g = inbox_value(p.inbox_vals[s_wsrc[jj]], p.quant, vcap, s_wrec[jj] * kw + c);
+            float* dst = p.wide_vals + (size_t)sc * kw + c;
+            if (single) *dst += g; else atomicAdd(dst, g);
+          }
+        }
+      }
+      __syncthreads();
     }
   } else {
   // phase A: locate the slot of every record; single source -> update in place,

@@ -291,15 +291,19 @@ def bench_wide_step(args):
 
 
 def bench_kv(args):
-    """Push + pull of K sorted unique keys per rank with scalar values through the
-    device KV containers: keys/s for the pair push-then-pull (max over ranks). Under
-    torch.distributed.run every rank is a worker and owns one key-range shard; the
-    ``nccl_a2a_ms`` column is the time of the bare all-to-all-v traffic of the same
-    exchange (keys + values out, keys out + values back), i.e. a lower bound for an
-    NCCL implementation that still had to look the keys up and apply the values."""
+    """Push + pull of K sorted unique keys per rank through the device KV containers, for value widths
+    ``--widths`` and filters ``--modes`` (``none``; ``key_caching``: the key list repeats, so after the
+    first round no keys travel; ``int8``: block-scaled 8-bit values on the wire): milliseconds for the
+    pair push-then-pull (max over ranks) and keys/s over all ranks. Under torch.distributed.run every
+    rank is a worker and owns one key-range shard. ``nccl_ms`` is the same pair done the conventional
+    way on the same table (all-to-all-v of keys and values through NCCL, then look-up and merge by the
+    owner with the library's kernels, ``parallel/nccl_baseline.py`` ``NcclKV``); its split sizes are
+    computed once outside the timed region. ``max_err`` compares what the last pull returned with the
+    sum of everything pushed. The reference's probe: ``test/kv_map_perf_ps.cc:27-60``."""
     import numpy as np
     import torch.distributed as dist
     from ..parallel.dataplane import OptimizerConfig
+    from ..parallel.nccl_baseline import NcclKV
     from ..parameter.kv import DeviceKVVector
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -307,61 +311,84 @@ def bench_kv(args):
     dev = torch.device("cuda", torch.cuda.current_device())
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    modes = [args.quant] if args.quant != "none" and args.modes == ["none"] else args.modes
     out = []
-    for K in args.sizes:
-        cap = 1 << max(12, int(np.ceil(np.log2(4 * K))))
-        kv = DeviceKVVector.create(None, table_capacity=cap, max_keys=K, opt=OptimizerConfig(algo="sum"),
-                                   quant=args.quant, exchange=not args.one_sided)
-        fab = kv.plane.fabric
-        rng = np.random.default_rng(K + rank)
-        keys = np.unique(rng.integers(0, 1 << 63, int(K * 1.2), dtype=np.uint64) * np.uint64(2))[:K]
-        kt = torch.from_numpy(keys.view(np.int64)).to(dev)
-        vals = torch.randn(len(keys), device=dev)
+
+    def timed(fn, reps, finish=lambda: None):
         for _ in range(3):
-            kv.wait(kv.pull(kt, wait=[kv.push(kt, vals)]))
+            fn()
+        finish()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = args.iters
         e0.record()
         for _ in range(reps):
-            t = kv.pull(kt, wait=[kv.push(kt, vals)])
-        kv.wait(t)
+            fn()
+        finish()                                   # the containers work on a stream of their own
         e1.record(); torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / reps
-        a2a_ms = None
         if world > 1:
-            # bare all-to-all-v of the same exchange
-            bounds = np.array(kv.plane.bounds_host[:-1], dtype=np.float64)
-            cnt = np.diff(np.append(np.searchsorted(keys.astype(np.float64), bounds), len(keys))).astype(np.int64)
-            cin = torch.zeros(world, dtype=torch.int64, device=dev)
-            dist.all_to_all_single(cin, torch.from_numpy(cnt).to(dev))
-            isz, osz = cnt.tolist(), cin.tolist()
-            rk = torch.empty(int(sum(osz)), dtype=torch.int64, device=dev)
-            rv = torch.empty(int(sum(osz)), dtype=torch.float32, device=dev)
-            back = torch.empty(len(keys), dtype=torch.float32, device=dev)
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
 
-            def a2a():
-                dist.all_to_all_single(rk, kt, osz, isz); dist.all_to_all_single(rv, vals, osz, isz)   # push
-                dist.all_to_all_single(rk, kt, osz, isz); dist.all_to_all_single(back, rv, isz, osz)   # pull
-            for _ in range(3):
-                a2a()
-            torch.cuda.synchronize(); dist.barrier()
-            e0.record()
-            for _ in range(reps):
-                a2a()
-            e1.record(); torch.cuda.synchronize()
-            tt = torch.tensor([ms, e0.elapsed_time(e1) / reps], dtype=torch.float64, device=dev)
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            ms, a2a_ms = tt.tolist()
-        out.append({"K_per_rank": len(keys), "ms_push_pull": ms, "keys_per_s": 2 * len(keys) * world / (ms * 1e-3),
-                    "nccl_a2a_ms": a2a_ms})
-        if world > 1:
-            dist.barrier()
-            fab.close()
+    for K in args.sizes:
+        rng = np.random.default_rng(K + rank)
+        keys = np.unique(rng.integers(0, 1 << 63, int(K * 1.2), dtype=np.uint64) * np.uint64(2))[:K]
+        kt = torch.from_numpy(keys.view(np.int64)).to(dev)
+        for width in args.widths:
+            if K * width > args.max_values:
+                continue                                      # the inbox ring would not fit
+            vals = torch.randn(len(keys), width, device=dev)
+            for mode in modes:
+                cap = 1 << max(12, int(np.ceil(np.log2(4 * K))))
+                kv = DeviceKVVector.create(None, table_capacity=cap, max_keys=K, opt=OptimizerConfig(algo="sum"),
+                                           quant=mode if mode in ("int8", "fp16") else "none", k=width,
+                                           key_cache=mode == "key_caching", exchange=not args.one_sided)
+                fab = kv.plane.fabric
+                pushes = [0]
+                last = [None]
+
+                def pair():
+                    pushes[0] += 1
+                    if last[0] is not None:
+                        kv.discard(last[0])
+                    last[0] = kv.pull(kt, wait=[kv.push(kt, vals)])
+
+                ms = timed(pair, args.iters, lambda: kv.stream.synchronize())
+                kv.wait(last[0])
+                got = kv.result(last[0]).view(len(keys), width)
+                err = float((got - pushes[0] * vals).abs().max().item() / pushes[0])
+                row = {"K_per_rank": len(keys), "width": width, "mode": mode, "ms_push_pull": round(ms, 4),
+                       "keys_per_s": 2 * len(keys) * world / (ms * 1e-3),
+                       "value_GB_per_s": 2 * len(keys) * width * 4 * world / (ms * 1e-3) / 1e9,
+                       "max_err": err, "nccl_ms": None}
+                if args.nccl and mode == "none" and not args.one_sided:
+                    nk = NcclKV(kv.plane, K)
+                    nk.set_keys(keys)
+                    back = torch.empty(len(keys), width, device=dev)
+
+                    def nccl_pair():
+                        nk.push(kt, vals)
+                        nk.pull(kt, back)
+                    before = pushes[0]
+                    row["nccl_ms"] = round(timed(nccl_pair, args.iters), 4)
+                    torch.cuda.synchronize()
+                    n_all = before + 3 + args.iters
+                    row["nccl_max_err"] = float((back - n_all * vals).abs().max().item() / n_all)
+                    row["speedup_vs_nccl"] = round(row["nccl_ms"] / ms, 3)
+                    kv.plane.check_status("nccl arm")
+                out.append(row)
+                if world > 1:
+                    dist.barrier()
+                if fab is not None:
+                    fab.close()
+                del kv
+                torch.cuda.empty_cache()
     if rank == 0:
-        print(json.dumps({"kernel": f"kv push+pull (width 1, {world} rank(s), quant {args.quant})", "results": out}))
+        print(json.dumps({"kernel": f"kv push+pull ({world} rank(s))", "results": out}))
     if world > 1:
         dist.destroy_process_group()
 
@@ -606,6 +633,9 @@ def main():
     s = sub.add_parser("kv"); s.add_argument("--sizes", type=int, nargs="+", default=[1000, 100000, 1000000, 16000000])
     s.add_argument("--iters", type=int, default=5); s.add_argument("--quant", default="none", choices=["none", "int8", "fp16"])
     s.add_argument("--one-sided", action="store_true", help="pull with remote probes instead of the exchange kernel")
+    s.add_argument("--widths", type=int, nargs="+", default=[1]); s.add_argument("--nccl", action="store_true")
+    s.add_argument("--modes", nargs="+", default=["none"], choices=["none", "key_caching", "int8", "fp16"])
+    s.add_argument("--max-values", type=int, default=1 << 26, help="skip K x width above this (memory of the inbox ring)")
     s = sub.add_parser("gather"); s.add_argument("--log2-slots", type=int, default=27)
     s.add_argument("--n", type=int, default=2680000); s.add_argument("--iters", type=int, default=5)
     s = sub.add_parser("fabric"); s.add_argument("--mb", type=int, default=256); s.add_argument("--iters", type=int, default=5)

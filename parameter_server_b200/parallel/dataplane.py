@@ -230,42 +230,47 @@ class DataPlane:
         cfg = self.cfg
         assert cfg.pull_cap >= b.max_nnz, "pull_cap must cover the largest minibatch's unique keys"
         par = ts & 1
-        p = PullExchangeParams()
-        p.S, p.me, p.ts1, p.need_applied, p.req_cap, p.wait_iters, p.phases = \
-            self.S, self.rank, ts + 1, need_applied, cfg.inbox_cap, wait_iters, phases
-        req_bytes = cfg.inbox_cap * 8
-        for s in range(self.S):
-            p.req_keys[s] = self.fabric.ptr(s, self.layout["req_keys"] + (par * self.S + self.rank) * req_bytes)
-            p.req_ready[s] = self._xflag(s, 0, par, self.rank)
-            p.my_req_keys[s] = self.fabric.ptr(self.rank, self.layout["req_keys"] + (par * self.S + s) * req_bytes)
-            p.my_req_ready[s] = self._xflag(self.rank, 0, par, s)
-            p.resp_w[s] = self.fabric.ptr(s, self.layout["resp_w"] + par * cfg.pull_cap * 4 * self.width)
-            p.resp_ready[s] = self._xflag(s, 1, par, self.rank)
-            p.my_resp_ready[s] = self._xflag(self.rank, 1, par, s)
-            p.slot_cache[s] = self._slot_cache_ptr(ts, s)
-            p.alive[s] = 1 if self.alive[s] else 0
-            # header = two consecutive words {count, base} per (parity, source)
-            p.req_hdr[s] = self.fabric.ptr(s, self.layout["xflags"] + 4 * (8 * self.S + (par * self.S + self.rank) * 2))
-            p.my_req_hdr[s] = self.fabric.ptr(self.rank, self.layout["xflags"] + 4 * (8 * self.S + (par * self.S + s) * 2))
-        p.table, p.mask = self.table_ptr(channel=channel), cfg.table_capacity - 1
-        p.key_begin, p.slot_mult = self.bounds_host[self.rank], self.slot_mult[self.rank]
-        p.applied = self._ctrl(self.rank, 0)
-        p.width, p.wide_vals = self.width, self.wide_vals_ptr(channel)
+
+        def build():
+            p = PullExchangeParams()
+            p.S, p.me, p.req_cap = self.S, self.rank, cfg.inbox_cap
+            req_bytes = cfg.inbox_cap * 8
+            for s in range(self.S):
+                p.req_keys[s] = self.fabric.ptr(s, self.layout["req_keys"] + (par * self.S + self.rank) * req_bytes)
+                p.req_ready[s] = self._xflag(s, 0, par, self.rank)
+                p.my_req_keys[s] = self.fabric.ptr(self.rank, self.layout["req_keys"] + (par * self.S + s) * req_bytes)
+                p.my_req_ready[s] = self._xflag(self.rank, 0, par, s)
+                p.resp_w[s] = self.fabric.ptr(s, self.layout["resp_w"] + par * cfg.pull_cap * 4 * self.width)
+                p.resp_ready[s] = self._xflag(s, 1, par, self.rank)
+                p.my_resp_ready[s] = self._xflag(self.rank, 1, par, s)
+                p.slot_cache[s] = self._slot_cache_ptr(ts, s)
+                p.alive[s] = 1 if self.alive[s] else 0
+                # header = two consecutive words {count, base} per (parity, source)
+                p.req_hdr[s] = self.fabric.ptr(s, self.layout["xflags"] + 4 * (8 * self.S + (par * self.S + self.rank) * 2))
+                p.my_req_hdr[s] = self.fabric.ptr(self.rank, self.layout["xflags"] + 4 * (8 * self.S + (par * self.S + s) * 2))
+                p.slot_cache_prev[s] = self._slot_cache_ptr(ts - 1, s) if ts > 0 else self._slot_cache_ptr(ts, s)
+            p.table, p.mask = self.table_ptr(channel=channel), cfg.table_capacity - 1
+            p.key_begin, p.slot_mult = self.bounds_host[self.rank], self.slot_mult[self.rank]
+            p.applied = self._ctrl(self.rank, 0)
+            p.width, p.wide_vals = self.width, self.wide_vals_ptr(channel)
+            p.my_resp_w = self.fabric.ptr(self.rank, self.layout["resp_w"] + par * cfg.pull_cap * 4 * self.width)
+            p.stats = ptr(self.pull_stats)
+            p.done, p.status = self.sync_words.data_ptr() + 48, ptr(self.status)
+            return p
+        # everything that depends on the round only through its ring slot and parity is filled once
+        p = self._params("pull_exchange", (ts % (2 * cfg.ring) if ts > 0 else -1, channel), build)
+        p.ts1, p.need_applied, p.wait_iters, p.phases = ts + 1, need_applied, wait_iters, phases
         assert self.width == 1 or not with_margins, "margins need scalar values"
-        p.my_resp_w = self.fabric.ptr(self.rank, self.layout["resp_w"] + par * cfg.pull_cap * 4 * self.width)
         p.ukeys, p.n_unique, p.own_off, p.grad_zero = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off), ptr(b.grad)
         if with_margins:
             p.row_ptr, p.n_rows, p.fixed_z = ptr(b.row_ptr), b.n_rows, b.fixed_z
             p.csr_col, p.csr_val, p.y = ptr(b.csr_col), ptr(b.csr_val), ptr(b.y)
             p.gcoef, p.margin = ptr(b.gcoef), ptr(b.margin)
-        p.loss, p.stats, p.auc_hist = loss, ptr(self.pull_stats), ptr(auc_hist)
-        p.done, p.status = self.sync_words.data_ptr() + 48, ptr(self.status)
+        p.loss, p.auc_hist = loss, ptr(auc_hist)
         if cfg.key_cache and phases == 7:
             # the key-caching filter is decided inside the kernel (needs all three roles in one launch:
             # the fingerprint pass ends with a grid barrier)
             p.key_cache, p.kc_state, p.bar = 1, ptr(self.kc_state), self.sync_words.data_ptr() + 64
-            for s in range(self.S):
-                p.slot_cache_prev[s] = self._slot_cache_ptr(ts - 1, s) if ts > 0 else self._slot_cache_ptr(ts, s)
         check(_lib.lib().psb_pull_exchange(C.byref(p), stream_ptr(stream)), "pull_exchange")
 
     def response_weights(self, ts: int, n: int) -> torch.Tensor:
@@ -280,16 +285,21 @@ class DataPlane:
         are X^T gcoef computed in the kernel; otherwise ``b.grad`` is sent as is."""
         cfg = self.cfg
         q = ts % cfg.ring
-        p = PushParams()
-        p.S, p.ts1, p.inbox_cap = self.S, ts + 1, cfg.inbox_cap
-        p.quant, p.send_keys = cfg.quant_code(), int(send_keys)
-        for s in range(self.S):
-            p.inbox_keys[s] = self._inbox_keys(s, q, self.rank)
-            p.inbox_vals[s] = self._inbox_vals(s, q, self.rank)
-            p.ready[s] = self._ready(s, q, self.rank)
-            p.count[s] = self._count(s, q, self.rank)
-            p.mode[s] = self._mode(s, q, self.rank)
-            p.applied[s] = self._ctrl(s, 0)
+
+        def build():
+            p = PushParams()
+            p.S, p.inbox_cap, p.quant, p.width = self.S, cfg.inbox_cap, cfg.quant_code(), self.width
+            for s in range(self.S):
+                p.inbox_keys[s] = self._inbox_keys(s, q, self.rank)
+                p.inbox_vals[s] = self._inbox_vals(s, q, self.rank)
+                p.ready[s] = self._ready(s, q, self.rank)
+                p.count[s] = self._count(s, q, self.rank)
+                p.mode[s] = self._mode(s, q, self.rank)
+                p.applied[s] = self._ctrl(s, 0)
+            p.bar, p.done, p.status = self._bar(1), self._done(1), ptr(self.status)
+            return p
+        p = self._params("push", q, build)
+        p.ts1, p.send_keys = ts + 1, int(send_keys)
         if cfg.key_cache:
             p.key_hit = ptr(b.key_hit)
         p.need_applied = max(0, ts + 1 - cfg.ring)
@@ -301,9 +311,7 @@ class DataPlane:
         else:
             p.nnz = 0
         p.grad = ptr(b.grad)
-        p.width = self.width
         assert self.width == 1 or not with_gradient
-        p.bar, p.done, p.status = self._bar(1), self._done(1), ptr(self.status)
         check(_lib.lib().psb_push(C.byref(p), stream_ptr(stream)), "push")
 
     # ---------------------------------------------------------------- server: apply
@@ -312,33 +320,49 @@ class DataPlane:
         """F1b: apply push round ``ts`` from every alive source (into the table of ``channel``)."""
         cfg = self.cfg
         q = ts % cfg.ring
-        p = ApplyParams()
-        p.S, p.ts1, p.inbox_cap, p.quant = self.S, ts + 1, cfg.inbox_cap, cfg.quant_code()
-        p.table, p.mask = self.table_ptr(channel=channel), cfg.table_capacity - 1
-        p.width, p.wide_vals = self.width, self.wide_vals_ptr(channel)
-        p.key_begin, p.slot_mult = self.bounds_host[self.rank], self.slot_mult[self.rank]
+
+        def build():
+            p = ApplyParams()
+            p.S, p.inbox_cap, p.quant = self.S, cfg.inbox_cap, cfg.quant_code()
+            p.table, p.mask = self.table_ptr(channel=channel), cfg.table_capacity - 1
+            p.width, p.wide_vals = self.width, self.wide_vals_ptr(channel)
+            p.key_begin, p.slot_mult = self.bounds_host[self.rank], self.slot_mult[self.rank]
+            for r in range(self.S):
+                p.inbox_keys[r] = self._inbox_keys(self.rank, q, r)
+                p.inbox_vals[r] = self._inbox_vals(self.rank, q, r)
+                p.ready[r] = self._ready(self.rank, q, r)
+                p.count[r] = self._count(self.rank, q, r)
+                p.mode[r] = self._mode(self.rank, q, r)
+                p.alive[r] = 1 if self.alive[r] else 0
+                p.slot_cache[r] = self._slot_cache_ptr(ts, r)
+            p.stats, p.applied = ptr(self.push_stats), self._ctrl(self.rank, 0)
+            p.bar, p.done, p.status = self._bar(2), self._done(2), ptr(self.status)
+            return p
+        p = self._params("apply", (q, channel), build)
+        p.ts1, p.wait_iters = ts + 1, wait_iters
         for r in range(self.S):
-            p.inbox_keys[r] = self._inbox_keys(self.rank, q, r)
-            p.inbox_vals[r] = self._inbox_vals(self.rank, q, r)
-            p.ready[r] = self._ready(self.rank, q, r)
-            p.count[r] = self._count(self.rank, q, r)
-            p.mode[r] = self._mode(self.rank, q, r)
-            p.alive[r] = 1 if self.alive[r] else 0
             p.cached[r] = 1 if (cached is not None and cached[r]) else 0
-            p.slot_cache[r] = self._slot_cache_ptr(ts, r)
         p.opt = (opt or self.opt).to_c()
-        p.stats, p.applied = ptr(self.push_stats), self._ctrl(self.rank, 0)
-        p.wait_iters = wait_iters
-        p.bar, p.done, p.status = self._bar(2), self._done(2), ptr(self.status)
         check(_lib.lib().psb_apply(C.byref(p), stream_ptr(stream)), "apply")
         self.applied_ts1 = ts + 1
 
     # ---------------------------------------------------------------- membership
+    def _params(self, kind: str, key, build):
+        """A fresh copy of the parameter block of ``kind`` whose round-independent part (peer
+        addresses by ring slot, table, flags) ``build`` fills once per ``key``: with small requests the
+        host would otherwise spend longer filling these blocks than the device spends on the kernels."""
+        cache = self.__dict__.setdefault("_param_cache", {})
+        tmpl = cache.get((kind, key))
+        if tmpl is None:
+            tmpl = cache[(kind, key)] = build()
+        return type(tmpl).from_buffer_copy(tmpl)
+
     def set_alive(self, rank: int, alive: bool):
         """Host-side membership: a dead source is skipped by ``apply`` (its wait
         completes immediately), as with ``alive=false`` in the reference's
         ``Executor::RemoveNode`` (``system/executor.cc:303-313``)."""
         self.alive[rank] = alive
+        self.__dict__.pop("_param_cache", None)        # the cached parameter blocks carry the membership
 
     def check_status(self, what: str = "data plane"):
         _lib.check_status(self.status, what)

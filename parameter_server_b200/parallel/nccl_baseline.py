@@ -154,3 +154,102 @@ class NcclPushPull:
         a.bar, a.done, a.status = p._bar(2), p._done(2), ptr(p.status)
         check(L.psb_apply(C.byref(a), sp), "apply")
         self.collectives += 3 if counts_slot >= 0 else 4
+
+
+class NcclKV:
+    """Push and pull of sorted unique keys with ``k``-wide values the conventional way, for the KV
+    microbenchmark: all-to-all-v of keys and values through NCCL, then the owner's look-up and merge
+    with the library's own table kernels (``k_apply`` over the received segments; ``k_pull_margin`` as a
+    local gather that remembers the slots). It works on the local shard of ``plane`` (table, key range
+    and slot map are the plane's), so both arms of the benchmark hit the same table.
+
+    The split sizes are computed once per key list on the host (``set_keys``): the benchmark repeats
+    its key list, and a real implementation would have to exchange them every round."""
+
+    def __init__(self, plane: DataPlane, max_keys: int, group=None):
+        self.plane, self.group = plane, group
+        self.S, self.rank, self.k = plane.S, plane.rank, plane.width
+        dev = self.dev = plane.device
+        cap = self.cap = max_keys * 2 + 1024
+        i32, i64, f32 = torch.int32, torch.int64, torch.float32
+        self.rkeys = torch.empty(cap, dtype=i64, device=dev)
+        self.rvals = torch.empty(cap * self.k, dtype=f32, device=dev)
+        self.rw = torch.empty(cap, dtype=f32, device=dev)
+        self.slot_cache = torch.zeros(cap, dtype=i32, device=dev)
+        self.counts32 = torch.zeros(self.S, dtype=i32, device=dev)
+        self.ready = torch.full((self.S,), 0x7FFFFFF0, dtype=i32, device=dev)
+        self.dummy = torch.zeros(64, dtype=i32, device=dev)
+        self.one_off = torch.zeros(2, dtype=i32, device=dev)
+        self.n_recv = torch.zeros(1, dtype=i32, device=dev)
+        self.t = 0
+
+    def set_keys(self, keys_u64):
+        """Split sizes of a sorted unique uint64 key list (NumPy) by the plane's key ranges."""
+        import numpy as np
+        inner = np.array(self.plane.bounds_host[1:-1], dtype=np.uint64)
+        cuts = np.concatenate([[0], np.searchsorted(keys_u64, inner), [len(keys_u64)]])
+        self.sc = np.diff(cuts).astype(np.int64).tolist()
+        cin = torch.zeros(self.S, dtype=torch.int64, device=self.dev)
+        if self.S > 1:
+            dist.all_to_all_single(cin, torch.tensor(self.sc, dtype=torch.int64, device=self.dev), group=self.group)
+        else:
+            cin[0] = self.sc[0]
+        self.rc = cin.tolist()
+        self.R = sum(self.rc)
+        assert self.R <= self.cap
+        self.counts32.copy_(cin.to(torch.int32))
+        self.n_recv.fill_(self.R)
+        self.one_off.copy_(torch.tensor([0, self.R], dtype=torch.int32))
+
+    def _a2a(self, out, inp, osz, isz, width=1):
+        out, inp = out.reshape(-1), inp.reshape(-1)
+        if self.S == 1:
+            out.copy_(inp)
+        else:
+            dist.all_to_all_single(out, inp, [n * width for n in osz], [n * width for n in isz], group=self.group)
+
+    def push(self, keys: torch.Tensor, vals: torch.Tensor):
+        p, S, k, L = self.plane, self.S, self.k, _lib.lib()
+        R = self.R
+        self._a2a(self.rkeys[:R], keys, self.rc, self.sc)
+        self._a2a(self.rvals[:R * k], vals.reshape(-1), self.rc, self.sc, k)
+        a = ApplyParams()
+        a.S, a.ts1, a.inbox_cap, a.quant = S, self.t + 1, self.cap, 0
+        a.table, a.mask = p.table_ptr(), p.cfg.table_capacity - 1
+        a.key_begin, a.slot_mult = p.bounds_host[self.rank], p.slot_mult[self.rank]
+        off = 0
+        for r in range(S):
+            a.inbox_keys[r] = self.rkeys.data_ptr() + off * 8
+            a.inbox_vals[r] = self.rvals.data_ptr() + off * k * 4
+            a.ready[r] = self.ready.data_ptr() + 4 * r
+            a.count[r] = self.counts32.data_ptr() + 4 * r
+            a.alive[r], a.cached[r] = 1, 0
+            a.slot_cache[r] = self.slot_cache.data_ptr() + off * 4
+            off += self.rc[r]
+        a.opt = p.opt.to_c()
+        a.stats, a.applied = ptr(p.push_stats), self.dummy.data_ptr() + 128
+        a.bar, a.done, a.status = p._bar(2), p._done(2), ptr(p.status)
+        a.width, a.wide_vals = k, p.wide_vals_ptr(0)
+        check(L.psb_apply(C.byref(a), stream_ptr()), "apply")
+        self.t += 1
+
+    def pull(self, keys: torch.Tensor, out: torch.Tensor):
+        p, k, L = self.plane, self.k, _lib.lib()
+        R = self.R
+        self._a2a(self.rkeys[:R], keys, self.rc, self.sc)
+        g = PullParams()
+        g.S, g.insert = 1, 1
+        g.slot_local = ptr(self.slot_cache)
+        g.table[0], g.mask[0] = p.table_ptr(), p.cfg.table_capacity - 1
+        g.key_begin[0], g.slot_mult[0] = p.bounds_host[self.rank], p.slot_mult[self.rank]
+        g.applied[0], g.need_applied = self.dummy.data_ptr() + 128, 0
+        g.ukeys, g.n_unique, g.own_off = ptr(self.rkeys), ptr(self.n_recv), ptr(self.one_off)
+        g.w_local, g.n_rows = ptr(self.rw), 0
+        g.stats, g.bar, g.status = ptr(p.pull_stats), p._bar(0), ptr(p.status)
+        check(L.psb_pull_margin(C.byref(g), stream_ptr()), "gather")
+        if k == 1:
+            self._a2a(out, self.rw[:R], self.sc, self.rc)
+        else:
+            wide = p.fabric.view(p.layout["wide_vals"], (p.cfg.table_capacity, k), torch.float32)
+            torch.index_select(wide, 0, self.slot_cache[:R].long(), out=self.rvals[:R * k].view(R, k))
+            self._a2a(out.reshape(-1), self.rvals[:R * k], self.sc, self.rc, k)

@@ -199,6 +199,12 @@ class DeviceKVMap:
     def result(self, ts: int) -> torch.Tensor:
         return self._results.pop(ts)
 
+    def discard(self, ts: int):
+        """Forget request ``ts`` (its event, callback and pulled values) without waiting for it."""
+        self._events.pop(ts, None)
+        self._callbacks.pop(ts, None)
+        self._results.pop(ts, None)
+
     def write_to_file(self, path: str):
         """``key<TAB>value`` per non-zero entry of this shard."""
         from ..app.linear import write_model
