@@ -169,6 +169,14 @@ typedef struct {
   // value width k > 1 (sum entries only): the values live in wide_vals[slot * k + c], beside the table
   int width;
   float* wide_vals;
+  // Several sources, every one with remembered slots: tile_off[r * (tiles + 1) + k] is the first record of
+  // source r whose key lies in the k-th of `tiles` equal parts of this shard's key range (written by the
+  // exchange pull of the same round). Records of one part from all sources are merged in shared memory
+  // and every key gets one optimiser step and one entry write. Null: every record goes through the
+  // accumulate-then-lead protocol. slow: one word, set while a part did not fit shared memory.
+  const uint32_t* tile_off;
+  int tiles;
+  uint32_t* slow;
 } PsbApplyParams;
 
 // Two-sided pull fused with the margins (kernel F2, exchange form). One launch on
@@ -234,6 +242,13 @@ typedef struct {
   // response buffers hold k values per unique key (no margins in that case: n_rows must be 0)
   int width;
   const float* wide_vals;
+  // nullable: where the owner notes, per source r, the first request of each of `tiles` (a power of two)
+  // equal parts of its key range [key_begin, key_end) (key_end 0 = 2^64): tile_off[r * (tiles + 1) + k].
+  // On a key-cache hit the previous round's notes (tile_off_prev) are copied.
+  uint32_t* tile_off;
+  const uint32_t* tile_off_prev;
+  int tiles;
+  psb_u64 key_end;
 } PsbPullExchangeParams;
 
 int psb_pull_exchange(const PsbPullExchangeParams* p, cudaStream_t stream);

@@ -29,6 +29,8 @@
 namespace psb {
 
 static constexpr int kThreads = 256;
+static constexpr int kMergeHashBits = 11;               // k_apply's per-part merge table: 2048 slots, half full at most
+static constexpr int kMergeHash = 1 << kMergeHashBits;
 
 // Optional per-phase cycle stamps (thread 0 of every CTA, 16 slots per CTA) for tuning builds.
 #ifdef PSB_TRACE
@@ -338,6 +340,30 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
     PSB_TSTAMP(3);
     const u32 n = s_n & 0x7fffffffu, base = s_base;
     const int kw = p.width > 1 ? p.width : 1;
+    if (p.tile_off != nullptr && S > 1) {
+      // for the merge in k_apply: where each equal part of my key range starts in this source's list
+      const u32 T = (u32)p.tiles;
+      u32* to = p.tile_off + (size_t)r * (T + 1);
+      if (s_n & 0x80000000u) {
+        const u32* tp = p.tile_off_prev + (size_t)r * (T + 1);
+        for (u32 k = gtid; k <= T; k += gsize) to[k] = tp[k];
+      } else {
+        const u64 range = p.key_end - p.key_begin;          // key_end 0 stands for 2^64
+        const int sh = 64 - (31 - __clz(T));
+        for (u32 k = gtid; k <= T; k += gsize) {
+          u32 lo = 0, hi = n;
+          if (k == T) lo = n;
+          else if (k > 0) {
+            const u64 bound = p.key_begin + __umul64hi(range, (u64)k << sh);
+            while (lo < hi) {
+              const u32 mid = (lo + hi) >> 1;
+              if (p.my_req_keys[r][mid] < bound) lo = mid + 1; else hi = mid;
+            }
+          }
+          to[k] = lo;
+        }
+      }
+    }
     if (kw > 1) {
       // k values per key. A CTA takes tiles of blockDim.x keys: one thread per key finds the slot
       // (remembered slots on a key-cache hit at the source), then the whole CTA copies the tile's
@@ -734,8 +760,13 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
   const u32 gsize = gridDim.x * blockDim.x;
   const u32 gtid = blockIdx.x * blockDim.x + threadIdx.x;
   int n_src = 0;
-  for (int r = 0; r < S; ++r) n_src += p.alive[r] ? 1 : 0;
+  bool all_cached = true;
+  for (int r = 0; r < S; ++r) {
+    n_src += p.alive[r] ? 1 : 0;
+    if (p.alive[r] && !s_cached[r]) all_cached = false;
+  }
   const bool single = n_src <= 1;
+  const bool merge = !single && p.tile_off != nullptr && all_cached && p.width <= 1;
   const SlotMap sm{p.mask, p.key_begin, p.slot_mult};
   StatAcc st;
 
@@ -791,6 +822,79 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
             float* dst = p.wide_vals + (size_t)sc * kw + c;
             if (single) *dst += g; else atomicAdd(dst, g);
           }
+        }
+      }
+      __syncthreads();
+    }
+  } else if (merge) {
+    // Several sources whose slots are all remembered: one key-range part at a time, the records of all
+    // sources are summed per slot in a shared-memory hash table, then every slot gets one optimiser
+    // step and one entry write. A part with more records than the table takes goes through the
+    // accumulate-then-lead protocol below (phase B then runs for those records only).
+    const u32 T = (u32)p.tiles;
+    __shared__ u32 s_hslot[kMergeHash];
+    __shared__ float s_hacc[kMergeHash];
+    __shared__ u32 s_tlo[PSB_MAX_SHARDS], s_tpre[PSB_MAX_SHARDS + 1];
+    // The notes divide the key range into T parts; neighbouring parts are taken together so that a
+    // step covers about 400 records of this round (a third of what the merge table takes).
+    u32 group = 1;
+    while (group < T && (u64)total * group < (u64)400 * T) group <<= 1;
+    const u32 n_tiles = T / group;
+    for (u32 tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      if (threadIdx.x < 32) {
+        const int r = threadIdx.x;
+        u32 lo = 0, len = 0;
+        if (r < S) {
+          const u32 nr = s_pre[r + 1] - s_pre[r];               // 0: dead or empty source
+          lo = min(p.tile_off[(size_t)r * (T + 1) + (size_t)tile * group], nr);
+          const u32 hi = min(p.tile_off[(size_t)r * (T + 1) + (size_t)(tile + 1) * group], nr);
+          len = hi > lo ? hi - lo : 0;
+        }
+        u32 inc = len;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const u32 v = __shfl_up_sync(0xffffffffu, inc, o);
+          if (r >= o) inc += v;
+        }
+        if (r < S) { s_tlo[r] = lo; s_tpre[r] = inc - len; }
+        if (r == S - 1) s_tpre[S] = inc;
+      }
+      for (u32 h = threadIdx.x; h < kMergeHash; h += blockDim.x) { s_hslot[h] = 0xffffffffu; s_hacc[h] = 0.f; }
+      __syncthreads();
+      const u32 cnt = s_tpre[S];
+      const bool fits = cnt <= kMergeHash / 2;
+      if (!fits && threadIdx.x == 0) atomicExch(p.slow, 1u);
+      for (u32 i = threadIdx.x; i < cnt; i += blockDim.x) {
+        int r = 0;
+        while (r + 1 < S && i >= s_tpre[r + 1]) ++r;
+        const u32 j = s_tlo[r] + (i - s_tpre[r]);
+        const u32 sc = p.slot_cache[r][j] & 0x7fffffffu;
+        if (sc == 0x7fffffffu) continue;
+        const float g = inbox_value(p.inbox_vals[r], p.quant, p.inbox_cap, j);
+        if (fits) {
+          u32 h = (sc * 2654435761u) >> (32 - kMergeHashBits);
+          for (;;) {
+            const u32 old = atomicCAS(&s_hslot[h], 0xffffffffu, sc);
+            if (old == 0xffffffffu || old == sc) { atomicAdd(&s_hacc[h], g); break; }
+            h = (h + 1) & (kMergeHash - 1);
+          }
+        } else {
+          const float seen = atomic_add_f32x2(&tab[sc].gacc, g, 1.f).y;
+          p.slot_cache[r][j] = sc | (seen == 0.f ? 0x80000000u : 0u);
+        }
+      }
+      __syncthreads();
+      if (fits) {
+        for (u32 h = threadIdx.x; h < kMergeHash; h += blockDim.x) {
+          const u32 sc = s_hslot[h];
+          if (sc == 0xffffffffu) continue;
+          Entry* e = &tab[sc];
+          const float2 ws = *reinterpret_cast<const float2*>(&e->w);
+          float w = ws.x, s0 = ws.y, t1 = e->s1, w_old = w;
+          opt_step(p.opt, s_hacc[h], w, s0, t1);
+          *reinterpret_cast<float2*>(&e->w) = make_float2(w, s0);
+          e->s1 = t1;
+          st.add(w, w_old);
         }
       }
       __syncthreads();
@@ -859,9 +963,16 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
         if (slot[q] >= 0) p.slot_cache[rr[q]][jj[q]] = (u32)slot[q] | (seen[q] == 0.f ? 0x80000000u : 0u);
     }
   }
+  }
   PSB_TSTAMP(2);
-  if (!single) {
+  bool phase_b = !single && p.width <= 1;
+  if (merge) {
     if (!grid_barrier(p.bar, p.status)) return;
+    phase_b = __ldcg(p.slow) != 0;                 // only if a part went through the accumulators
+  } else if (phase_b) {
+    if (!grid_barrier(p.bar, p.status)) return;
+  }
+  if (phase_b) {
     PSB_TSTAMP(3);
     // phase B: the leader of each touched key runs the optimiser on the summed gradient
     for (u32 i0 = gtid; i0 < total; i0 += 4 * gsize) {
@@ -900,7 +1011,6 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
       }
     }
   }
-  }
   PSB_TSTAMP(4);
   block_add4(st.d_nnz, st.w2, st.dw2, st.n, p.stats);
   // publish "applied" once every CTA is done
@@ -913,6 +1023,7 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
   }
   __syncthreads();
   if (s_last && threadIdx.x == 0) {
+    if (p.slow) atomicExch(p.slow, 0u);
     __threadfence_system();
     st_release_sys(p.applied, p.ts1);
     atomicExch(p.done, 0u);

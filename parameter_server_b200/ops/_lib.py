@@ -66,6 +66,7 @@ class PullExchangeParams(C.Structure):
         ("done", _vp), ("status", _vp),
         ("key_cache", _i32), ("kc_state", _vp), ("bar", _vp), ("slot_cache_prev", _vp * MAX_SHARDS),
         ("width", _i32), ("wide_vals", _vp),
+        ("tile_off", _vp), ("tile_off_prev", _vp), ("tiles", _i32), ("key_end", _u64),
     ]
 
 
@@ -95,6 +96,7 @@ class ApplyParams(C.Structure):
         ("opt", Optimizer), ("stats", _vp), ("applied", _vp), ("wait_iters", _u32),
         ("bar", _vp), ("done", _vp), ("status", _vp),
         ("width", _i32), ("wide_vals", _vp),
+        ("tile_off", _vp), ("tiles", _i32), ("slow", _vp),
     ]
 
 

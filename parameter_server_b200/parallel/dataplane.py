@@ -112,6 +112,14 @@ class DataPlane:
         # pull only copy 0 is used (scratch of apply, and the key-caching filter's memory).
         n_sc = cfg.ring if cfg.pull_cap else 1
         self.slot_cache = torch.zeros((n_sc, self.S, cfg.inbox_cap), dtype=torch.int32, device=dev)
+        # For the merge of several sources in apply: the exchange pull notes where each of `tiles` equal
+        # parts of this shard's key range starts in every source's list (about 400 records per part
+        # when the lists are full), one set of notes per ring slot like the slots.
+        self.tiles = 0
+        self.tile_off = None
+        if cfg.pull_cap and self.S > 1 and max(1, cfg.width) == 1:
+            self.tiles = min(1 << 16, max(64, 1 << max(0, (cfg.inbox_cap // 400)).bit_length()))
+            self.tile_off = torch.zeros((n_sc, self.S, self.tiles + 1), dtype=torch.int32, device=dev)
         self.push_stats = torch.zeros(4, dtype=torch.float64, device=dev)   # d_nnz, w2, dw2, n
         self.pull_stats = torch.zeros(4, dtype=torch.float64, device=dev)   # loss, correct, rows
         self.alive = [True] * self.S
@@ -256,6 +264,12 @@ class DataPlane:
             p.my_resp_w = self.fabric.ptr(self.rank, self.layout["resp_w"] + par * cfg.pull_cap * 4 * self.width)
             p.stats = ptr(self.pull_stats)
             p.done, p.status = self.sync_words.data_ptr() + 48, ptr(self.status)
+            if self.tile_off is not None:
+                n_sc = self.tile_off.shape[0]
+                p.tile_off = self.tile_off[ts % n_sc].data_ptr()
+                p.tile_off_prev = self.tile_off[(ts - 1) % n_sc].data_ptr()
+                p.tiles = self.tiles
+                p.key_end = self.bounds_host[self.rank + 1] & ((1 << 64) - 1)      # 2^64 is passed as 0
             return p
         # everything that depends on the round only through its ring slot and parity is filled once
         p = self._params("pull_exchange", (ts % (2 * cfg.ring) if ts > 0 else -1, channel), build)
@@ -337,6 +351,9 @@ class DataPlane:
                 p.slot_cache[r] = self._slot_cache_ptr(ts, r)
             p.stats, p.applied = ptr(self.push_stats), self._ctrl(self.rank, 0)
             p.bar, p.done, p.status = self._bar(2), self._done(2), ptr(self.status)
+            if self.tile_off is not None:
+                p.tile_off = self.tile_off[ts % self.tile_off.shape[0]].data_ptr()
+                p.tiles, p.slow = self.tiles, self.sync_words.data_ptr() + 96
             return p
         p = self._params("apply", (q, channel), build)
         p.ts1, p.wait_iters = ts + 1, wait_iters
