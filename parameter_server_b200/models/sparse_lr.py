@@ -37,6 +37,7 @@ class SparseLRConfig:
     pipeline: int = 3                  # minibatches in flight on the worker: copy | localise | pull+push
     auc: bool = False
     nvtx: bool = False                 # NVTX ranges around the stages of submit() for timeline profilers
+    graph_localize: bool = True        # replay the localisation of a repeated call from a CUDA graph
 
 
 class SparseLRWorker:
@@ -132,10 +133,11 @@ class SparseLRWorker:
         # stage 2, prep stream: sort + unique + remap (the buffer is free once its push has read it)
         self.prep_stream.wait_event(self._copy_done[k])
         self.prep_stream.wait_event(self._buf_free[k])
+        loc = b.localize_replayed if self.cfg.graph_localize else b.localize
         with torch.cuda.stream(self.prep_stream):
-            b.localize(ids_d, y_d, self.plane.bounds, fixed_z=fixed_z, row_ptr=rp_d, vals=vals_d,
-                       hash_seed=self.cfg.hash_seed, key_bits=self.cfg.key_bits, hash_bits=self.cfg.hash_bits,
-                       stream=self.prep_stream)
+            loc(ids_d, y_d, self.plane.bounds, fixed_z=fixed_z, row_ptr=rp_d, vals=vals_d,
+                hash_seed=self.cfg.hash_seed, key_bits=self.cfg.key_bits, hash_bits=self.cfg.hash_bits,
+                stream=self.prep_stream)
             self._prep_done[k].record(self.prep_stream)
         self.main_stream.wait_event(self._prep_done[k])
         done()

@@ -459,6 +459,44 @@ def bench_darlin(args):
         dist.barrier(); fab.close(); dist.destroy_process_group()
 
 
+def bench_h2d(args):
+    """Host-to-device copy ceiling of this box: every rank copies ``--mb`` MB from pinned host memory to
+    its GPU ``--iters`` times in a row (two host buffers in turn, one stream), all ranks at the same
+    time. GB/s per GPU from the slowest rank's CUDA-event time, and the sum over ranks: what an
+    end-to-end training step that ships its minibatch from the host can reach at best."""
+    dist, rank, world, dev = _dist_init()
+    n = int(args.mb * 1000 * 1000)
+    host = [torch.empty(n, dtype=torch.uint8).pin_memory() for _ in range(2)]
+    for h in host:
+        h.random_(0, 255)
+    dst = [torch.empty(n, dtype=torch.uint8, device=dev) for _ in range(2)]
+    st = torch.cuda.Stream(device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(st):
+        for i in range(3):
+            dst[i % 2].copy_(host[i % 2], non_blocking=True)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    with torch.cuda.stream(st):
+        e0.record()
+        for i in range(args.iters):
+            dst[i % 2].copy_(host[i % 2], non_blocking=True)
+        e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.iters
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        print(json.dumps({"kernel": "pinned host -> device copy", "gpus": world, "MB_per_copy": args.mb,
+                          "ms_per_copy_max_over_ranks": round(ms, 4), "GB_per_s_per_gpu": n / (ms * 1e-3) / 1e9,
+                          "GB_per_s_all_gpus": world * n / (ms * 1e-3) / 1e9}))
+    if world > 1:
+        dist.barrier(); dist.destroy_process_group()
+
+
 def _dist_init():
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -638,6 +676,7 @@ def main():
     s.add_argument("--max-values", type=int, default=1 << 26, help="skip K x width above this (memory of the inbox ring)")
     s = sub.add_parser("gather"); s.add_argument("--log2-slots", type=int, default=27)
     s.add_argument("--n", type=int, default=2680000); s.add_argument("--iters", type=int, default=5)
+    s = sub.add_parser("h2d"); s.add_argument("--mb", type=float, default=52.7); s.add_argument("--iters", type=int, default=50)
     s = sub.add_parser("fabric"); s.add_argument("--mb", type=int, default=256); s.add_argument("--iters", type=int, default=5)
     s = sub.add_parser("layer"); s.add_argument("--iters", type=int, default=5)
     s.add_argument("--small", action="store_true", help="shrink the two largest layers 16x (quick runs)")
@@ -647,7 +686,7 @@ def main():
     from .. import _build
     _build.build_cuda()
     {"sort": bench_sort, "step": bench_step, "wide": bench_wide, "wide-step": bench_wide_step, "kv": bench_kv,
-     "darlin": bench_darlin, "fabric": bench_fabric, "layer": bench_layer, "gather": bench_gather}[args.cmd](args)
+     "darlin": bench_darlin, "h2d": bench_h2d, "fabric": bench_fabric, "layer": bench_layer, "gather": bench_gather}[args.cmd](args)
 
 
 if __name__ == "__main__":
