@@ -138,7 +138,12 @@ __device__ __forceinline__ bool wait_flag_ge_sys(const u32* flag, u32 want, u32 
   return false;
 }
 
-// Default budgets: ~2 s of polling for cross-GPU waits, ~0.5 s in-grid.
+// Default budgets, in polls. A cross-GPU poll is a 100 ns sleep plus a system-scope load (about 1.2 us
+// in all), so 2^24 polls give a peer roughly 20 s (a rank may be held up by its data loader; a wait for
+// S sources polls them one after another, so the worst case is S times that). An in-grid poll is a
+// 40 ns sleep plus a load from L2 (under 1 us): 2^22 polls end a barrier that cannot complete after
+// about 3 s. A wait that runs out sets the status word and the kernel carries on or returns; the host
+// then clears the barrier and arrival words (check_status of the owning object) before the next launch.
 static constexpr u32 kPeerWaitIters = 1u << 24;
 static constexpr u32 kGridWaitIters = 1u << 22;
 

@@ -18,7 +18,10 @@
 //     holds it until the process exits;
 //   * the first call on a device looks up the array's device address (no
 //     allocation, but a runtime query), so make that first call before starting
-//     any stream capture;
+//     any stream capture. The address is remembered per device for the life of
+//     the process: after a cudaDeviceReset in the same process the remembered
+//     address is stale, so do not call this function again in a process that
+//     has reset the device;
 //   * all calls on one device share the array and it keeps the previous call's
 //     contents. Nothing in it has to start at zero (every word that is read is
 //     written earlier in the same call), but two calls that overlap on the GPU

@@ -298,7 +298,7 @@ class DarlinRank:
         return self.global_keys[c0:c1][nz].cpu().numpy().view(np.uint64), w[nz].cpu().numpy()
 
     def check_status(self, what="darlin"):
-        _lib.check_status(self.status, what)
+        _lib.check_status(self.status, what, reset=(self.sync, self.__dict__.get("_pass_bar")))
 
 
 def run_darlin(ranks: Sequence[DarlinRank], *, all_reduce=None, verbose: bool = False, num_examples: Optional[int] = None,

@@ -280,9 +280,17 @@ def stream_ptr(stream=None) -> int:
     return stream.cuda_stream
 
 
-def check_status(status: torch.Tensor, what: str = ""):
-    """Host check of a device status word (synchronises)."""
+def check_status(status: torch.Tensor, what: str = "", reset=()):
+    """Host check of a device status word (synchronises). On an error the status word and the
+    tensors in ``reset`` are zeroed before the exception is raised: a kernel that gave up at a grid
+    barrier leaves its barrier and arrival counters half counted, and with them every later launch
+    would fail the same way; zeroed, the object that owns them can be used again."""
     code = int(status.item())
     if code != 0:
+        if status.is_cuda:
+            torch.cuda.synchronize(status.device)      # every stream: nothing may still count on those words
         status.zero_()
+        for t in reset:
+            if t is not None:
+                t.zero_()
         raise PsbCudaError(f"{what or 'kernel'} reported status {code}: {STATUS_NAMES.get(code, '?')}")

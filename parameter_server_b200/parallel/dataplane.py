@@ -382,7 +382,10 @@ class DataPlane:
         self.__dict__.pop("_param_cache", None)        # the cached parameter blocks carry the membership
 
     def check_status(self, what: str = "data plane"):
-        _lib.check_status(self.status, what)
+        """Raise if a kernel of this plane reported an error; the plane's barrier and arrival words are
+        cleared then, so that the next round can run (the stamps in the peers' flags are monotone and
+        need no repair)."""
+        _lib.check_status(self.status, what, reset=(self.sync_words,))
 
     # ---------------------------------------------------------------- model io
     def dump_nonzero(self):

@@ -253,4 +253,4 @@ class WidePlane:
         return out
 
     def check_status(self, what="wide plane"):
-        _lib.check_status(self.status, what)
+        _lib.check_status(self.status, what, reset=(self.sync,))

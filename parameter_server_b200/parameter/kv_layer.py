@@ -192,7 +192,7 @@ class DeviceKVLayer:
         return self.fabric.view(m["data"], (n,), torch.float32)
 
     def check_status(self, what="kv layer"):
-        _lib.check_status(self.status, what)
+        _lib.check_status(self.status, what, reset=(self.sync,))
 
 
 def fabric_copy(src_ptr: int, dst_ptr: int, nbytes: int, mode: int = 0, sink=None, stream=None):

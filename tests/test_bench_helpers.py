@@ -31,3 +31,17 @@ def test_reference_arm_prints_unavailable(capsys):
     import json
     line = json.loads(capsys.readouterr().out)
     assert line["impl"] == "reference" and "unavailable" in line
+
+
+def test_check_status_clears_the_words_it_is_given():
+    """An error status is raised once; the status word and the barrier / arrival words passed along
+    are zero afterwards, so the object that owns them can run again."""
+    import pytest
+    import torch
+    from parameter_server_b200.ops import _lib
+    status = torch.tensor([3], dtype=torch.int32)
+    sync = torch.tensor([5, 1, 7, 0], dtype=torch.int32)
+    with pytest.raises(_lib.PsbCudaError, match="timed out"):
+        _lib.check_status(status, "probe", reset=(sync, None))
+    assert int(status.item()) == 0 and sync.tolist() == [0, 0, 0, 0]
+    _lib.check_status(status, "probe", reset=(sync,))        # clean: no exception
