@@ -8,11 +8,19 @@
 //                     the tensor core expects, then multiply the [128 x 64] tile
 //                     by the batch's [64 x N] context matrix with tcgen05.mma
 //                     (accumulator in TMEM), read the result back with tcgen05.ld
-//                     and store P[U x N]. The context matrix is brought in once
+//                     and either store P[U x N] or, fused, add each product that a
+//                     row needs straight into that row's margin: the tile's
+//                     products are staged in shared memory and the CTA walks the
+//                     CSC segments of the tile's keys (margin[row] += P[key,
+//                     context(row)]), so the U x N matrix never reaches memory.
+//                     The context matrix is brought in once
 //                     per CTA by a TMA tiled load (cp.async.bulk.tensor.2d, no
 //                     multicast) with the same swizzle.
 //   k_wide_rowsum     worker: prediction per row = sum over its keys of
-//                     P[key, context(row)], logistic loss and d loss / d margin.
+//                     P[key, context(row)], logistic loss and d loss / d margin
+//                     (the unfused form, from a stored P).
+//   k_wide_rowloss    worker: logistic loss and d loss / d margin from margins that
+//                     the fused pull has accumulated.
 //   k_wide_push       worker: gradient of every unique key,
 //                     G[u,:] = sum_{rows containing u} gcoef[row] * C[:, ctx(row)],
 //                     one warp per key over the CSC segment, written as bf16
@@ -33,6 +41,7 @@ namespace psb {
 static constexpr int kWide = 64;                 // values per key
 static constexpr int kTileM = 128;               // keys per MMA tile
 static constexpr u32 kWideProbe = 1u << 16;
+static constexpr u32 kPullLongSeg = 512;         // fused margins: longer segments go to k_wide_long_margins
 
 // ---------------------------------------------------------------- small PTX wrappers
 __device__ __forceinline__ u32 smem_u32(const void* p) { return (u32)__cvta_generic_to_shared(p); }
@@ -143,6 +152,16 @@ struct WidePullArgs {
   float* P;                               // [U x N] fp32
   __nv_bfloat16* v_local;                 // nullable: gathered rows [U x 64]
   uint32_t* status;
+  // fused margins (margin non-null; P may then be null): CSC of the batch and the rows' contexts
+  const uint32_t* seg_off;
+  const uint32_t* csc_row;
+  const uint32_t* row_ctx;                // nullable -> row % N
+  float* margin;                          // [n_rows], zero on entry
+  // keys with long segments are only listed here (with their row of products); k_wide_long_margins adds them
+  unsigned long long* plong_n;            // {count (low word), chunks (high word)}, zero on entry
+  uint4* plong_list;                      // {unused, first chunk, first element, end element}
+  float* plong_rows;                      // [plong_cap x N]
+  uint32_t plong_cap;
 };
 
 // Exchange form of the pull (see k_wide_pull_xgemm): per-owner flags and buffers.
@@ -173,6 +192,15 @@ struct WideXArgs {
   float* P;
   uint32_t* done;                            // 2 words, zero on entry, left zero
   uint32_t* status;
+  // fused margins, as in WidePullArgs
+  const uint32_t* seg_off;
+  const uint32_t* csc_row;
+  const uint32_t* row_ctx;
+  float* margin;
+  unsigned long long* plong_n;
+  uint4* plong_list;
+  float* plong_rows;
+  uint32_t plong_cap;
 };
 
 // Shared state of the tensor-core tile loop.
@@ -184,6 +212,19 @@ struct WideTileCtx {
   u32 idesc;
   u32 phase;
   u32* s_fail;
+  // fused margins: staging of the tile's products [128 x (N + 1)] fp32 and of its 129 segment offsets
+  float* sP;
+  u32* s_seg;      // [129] segment offsets of the tile's keys
+  u32* s_pre;      // [129] prefix of the short keys' lengths
+  u32* s_wsum;     // [4]
+  const u32* seg_off;
+  const u32* csc_row;
+  const u32* row_ctx;
+  float* margin;
+  unsigned long long* plong_n;
+  uint4* plong_list;
+  float* plong_rows;
+  u32 plong_cap;
 };
 
 // One [128 x 64] x [64 x N] tile: `row` holds this thread's 128-byte value row (zeros when
@@ -210,18 +251,72 @@ __device__ __forceinline__ bool wide_tile_mma_store(WideTileCtx& c, const uint4 
   __syncthreads();
   if (*c.s_fail) return false;
   // ---- epilogue: warp w owns TMEM lanes [32w, 32w+32) = rows of the tile
+  const int ldp = N + 1;                          // padded: thread = row, so a column is a bank stride apart
   for (int c0 = 0; c0 < N; c0 += 32) {
     u32 r[32];
     tmem_ld_32x32(c.tmem_base + ((u32)(warp * 32) << 16) + (u32)c0, r);
-    if (u < U) {
+    if (P != nullptr && u < U) {
       float4* dst = reinterpret_cast<float4*>(P + (size_t)u * N + c0);
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
                              __uint_as_float(r[4 * j + 3]));
     }
+    if (c.margin != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) c.sP[tid * ldp + c0 + j] = __uint_as_float(r[j]);
+    }
   }
   tc_fence_before();
+  if (c.margin != nullptr) {
+    // The tile's keys own the contiguous nonzeros [seg_off[u0], seg_off[u0 + 128)): every nonzero adds the
+    // product of its key and its row's context to the row's margin. A key with a long segment (under a
+    // Zipf law one key can own a fifth of all nonzeros) is only listed, with its row of products, and
+    // k_wide_long_margins spreads it over the whole grid; the others are walked here, all 128 threads
+    // over the short keys' nonzeros laid end to end.
+    const u32 u0 = u - (u32)tid;
+    c.s_seg[tid] = c.seg_off[min(u0 + (u32)tid, U)];
+    if (tid == 0) c.s_seg[kTileM] = c.seg_off[min(u0 + (u32)kTileM, U)];
+    __syncthreads();
+    const u32 i0 = c.s_seg[tid], len = c.s_seg[tid + 1] - i0;
+    bool is_long = false;
+    if (len > kPullLongSeg && c.plong_cap) {
+      const u32 nch = (len + kPullLongSeg - 1) / kPullLongSeg;
+      const unsigned long long old = atomicAdd(c.plong_n, 1ull | ((unsigned long long)nch << 32));
+      const u32 k = (u32)old;
+      if (k < c.plong_cap) {
+        is_long = true;
+        c.plong_list[k] = make_uint4(u, (u32)(old >> 32), i0, i0 + len);
+        for (int j = 0; j < N; ++j) c.plong_rows[(size_t)k * N + j] = c.sP[tid * ldp + j];
+      }                                            // a full list: the key is walked here after all
+    }
+    // exclusive prefix of the short keys' lengths (warp scans, then the four warp totals)
+    const u32 mine = is_long ? 0u : len;
+    u32 inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const u32 v = __shfl_up_sync(0xffffffffu, inc, o);
+      if ((tid & 31) >= o) inc += v;
+    }
+    if ((tid & 31) == 31) c.s_wsum[warp] = inc;
+    __syncthreads();
+    u32 base = 0;
+    for (int w = 0; w < warp; ++w) base += c.s_wsum[w];
+    c.s_pre[tid] = base + inc - mine;
+    if (tid == kTileM - 1) c.s_pre[kTileM] = base + inc;
+    __syncthreads();
+    const u32 total = c.s_pre[kTileM];
+    for (u32 t = tid; t < total; t += kTileM) {
+      int lo = 0, hi = kTileM - 1;                 // the last key whose share starts at or before t
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (c.s_pre[mid] <= t) lo = mid; else hi = mid - 1;
+      }
+      const u32 row = c.csc_row[c.s_seg[lo] + (t - c.s_pre[lo])];
+      const u32 cx = c.row_ctx ? c.row_ctx[row] : row % (u32)N;
+      atomicAdd(&c.margin[row], c.sP[lo * ldp + (int)cx]);
+    }
+  }
   __syncthreads();
   return true;
 }
@@ -262,7 +357,10 @@ __global__ void __launch_bounds__(128) k_wide_pull_gemm(const __grid_constant__ 
   const int N = p.N;
   const u32 U = *p.n_unique;
   if (tid <= p.S) s_off[tid] = p.own_off[tid];
-  WideTileCtx c{smem, smem + kTileM * 128, s_bar, 0, 0, 0, &s_fail};
+  __shared__ u32 s_seg[kTileM + 1], s_pre[kTileM + 1], s_wsum[4];
+  WideTileCtx c{smem, smem + kTileM * 128, s_bar, 0, 0, 0, &s_fail,
+                reinterpret_cast<float*>(smem + kTileM * 128 + N * 128), s_seg, s_pre, s_wsum,
+                p.seg_off, p.csc_row, p.row_ctx, p.margin, p.plong_n, p.plong_list, p.plong_rows, p.plong_cap};
   wide_tile_setup(c, &ctx_map, N, &s_tmem, p.status);
   const u32 ntiles = (U + kTileM - 1) / kTileM;
   for (u32 t = blockIdx.x; t < ntiles && !s_fail; t += gridDim.x) {
@@ -357,18 +455,44 @@ __global__ void __launch_bounds__(128) k_wide_pull_xgemm(const __grid_constant__
       }
       __syncthreads();
       const u32 n = s_n, base = s_base;
-      // eight lanes per key: the look-up by the first of them, then one 16-byte chunk each
-      // (the trip count is the same for every lane of a warp: the shuffle needs all of them)
+      // Eight lanes per key: the look-up by the first of them, then one 16-byte chunk each. Four keys
+      // per lane group and trip, every stage issued for all four before the next stage starts (key,
+      // first probe, row chunk are a chain of dependent loads). The trip count is the same for every
+      // lane of a warp: the shuffle needs all of them.
       const u32 n8 = (n * 8 + 31) & ~31u;
-      for (u32 j8 = gtid; j8 < n8; j8 += gsize) {
-        const u32 j = j8 >> 3, q = j8 & 7;
-        const bool valid = j < n;
-        long long slot = -1;
-        if (valid && q == 0) slot = wide_find<false>(p.keys, sm, p.my_req_keys[r][j]);
-        slot = __shfl_sync(0xffffffffu, slot, (tid & 31) & ~7);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (slot >= 0) v = reinterpret_cast<const uint4*>(p.vals + (size_t)slot * kWide)[q];
-        if (valid) reinterpret_cast<uint4*>(p.resp_rows[r] + (size_t)(base + j) * kWide)[q] = v;
+      for (u32 j8 = gtid; j8 < n8; j8 += 4 * gsize) {
+        u64 key[4], k0[4], sl0[4];
+        long long slot[4];
+        bool act[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const u32 x = j8 + q * gsize;
+          act[q] = x < n8;                          // the same for a whole warp
+          key[q] = (act[q] && (x >> 3) < n && (x & 7) == 0) ? p.my_req_keys[r][x >> 3] : kEmptyKey;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          sl0[q] = first_slot(sm, key[q]);
+          k0[q] = key[q] != kEmptyKey ? ld_relaxed_sys_u64(&p.keys[sl0[q]]) : kEmptyKey;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          slot[q] = -1;
+          if (key[q] != kEmptyKey) slot[q] = k0[q] == key[q] ? (long long)sl0[q] : wide_find<false>(p.keys, sm, key[q]);
+          if (act[q]) slot[q] = __shfl_sync(0xffffffffu, slot[q], (tid & 31) & ~7);
+        }
+        uint4 v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const u32 x = j8 + q * gsize;
+          v[q] = make_uint4(0, 0, 0, 0);
+          if (act[q] && slot[q] >= 0) v[q] = reinterpret_cast<const uint4*>(p.vals + (size_t)slot[q] * kWide)[x & 7];
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const u32 x = j8 + q * gsize;
+          if (act[q] && (x >> 3) < n) reinterpret_cast<uint4*>(p.resp_rows[r] + (size_t)(base + (x >> 3)) * kWide)[x & 7] = v[q];
+        }
       }
     }
     __threadfence_system();
@@ -383,7 +507,10 @@ __global__ void __launch_bounds__(128) k_wide_pull_xgemm(const __grid_constant__
   }
   if (!(p.phases & 4)) return;
   // ---- (c)
-  WideTileCtx c{smem, smem + kTileM * 128, s_bar, 0, 0, 0, &s_fail};
+  __shared__ u32 s_seg[kTileM + 1], s_pre[kTileM + 1], s_wsum[4];
+  WideTileCtx c{smem, smem + kTileM * 128, s_bar, 0, 0, 0, &s_fail,
+                reinterpret_cast<float*>(smem + kTileM * 128 + N * 128), s_seg, s_pre, s_wsum,
+                p.seg_off, p.csc_row, p.row_ctx, p.margin, p.plong_n, p.plong_list, p.plong_rows, p.plong_cap};
   wide_tile_setup(c, &ctx_map, N, &s_tmem, p.status);
   const u32 ntiles = (U + kTileM - 1) / kTileM;
   for (u32 t = blockIdx.x; t < ntiles && !s_fail; t += gridDim.x) {
@@ -434,6 +561,55 @@ __global__ void __launch_bounds__(256) k_wide_rowsum(const float* __restrict__ P
       correct += ym > 0 ? 1 : 0;
       seen += 1;
     }
+  }
+  loss = warp_sum_d(loss); correct = warp_sum_d(correct); seen = warp_sum_d(seen);
+  if (lane == 0 && stats && seen > 0) { atomicAdd(&stats[0], loss); atomicAdd(&stats[1], correct); atomicAdd(&stats[2], seen); }
+}
+
+// The long segments that the fused pull listed: chunks of kPullLongSeg nonzeros, one per warp and trip
+// (the list is sorted by first chunk: one 64-bit atomic handed out position and chunk numbers together).
+__global__ void __launch_bounds__(256) k_wide_long_margins(const unsigned long long* __restrict__ plong_n,
+                                                           const uint4* __restrict__ list, const float* __restrict__ rows,
+                                                           u32 cap, int N, const u32* __restrict__ csc_row,
+                                                           const u32* __restrict__ row_ctx, float* __restrict__ margin) {
+  const int lane = threadIdx.x & 31;
+  const u32 gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+  const unsigned long long tot = *plong_n;
+  const u32 n_long = min((u32)tot, cap);
+  const u32 n_chunks = n_long ? (u32)(tot >> 32) : 0u;
+  for (u32 c = gwarp; c < n_chunks; c += nwarps) {
+    u32 lo = 0, hi = n_long;                       // the entry with the largest first chunk <= c
+    while (hi - lo > 1) {
+      const u32 mid = (lo + hi) >> 1;
+      if (list[mid].y <= c) lo = mid; else hi = mid;
+    }
+    const uint4 e = list[lo];
+    const u32 b0 = e.z + (c - e.y) * kPullLongSeg;
+    if (b0 >= e.w) continue;                       // (a chunk number of a key that did not fit the list)
+    const u32 b1 = min(e.w, b0 + kPullLongSeg);
+    for (u32 i = b0 + lane; i < b1; i += 32) {
+      const u32 row = csc_row[i];
+      const u32 cx = row_ctx ? row_ctx[row] : row % (u32)N;
+      atomicAdd(&margin[row], rows[(size_t)lo * N + cx]);
+    }
+  }
+}
+
+// margins are complete (the fused pull added every product): loss, accuracy and d loss / d margin per row
+__global__ void __launch_bounds__(256) k_wide_rowloss(const float* __restrict__ margin, const float* __restrict__ y,
+                                                      u32 n_rows, float* __restrict__ gcoef, double* __restrict__ stats,
+                                                      unsigned long long* plong_n) {
+  const int lane = threadIdx.x & 31;
+  if (plong_n != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *plong_n = 0ull;   // the list is used up
+  double loss = 0, correct = 0, seen = 0;
+  for (u32 r = blockIdx.x * blockDim.x + threadIdx.x; r < n_rows; r += gridDim.x * blockDim.x) {
+    const float yy = y[r], ym = yy * margin[r];
+    const float en = expf(-fabsf(ym));
+    const float tau = ym > 0 ? en / (1.f + en) : 1.f / (1.f + en);
+    gcoef[r] = -yy * tau;
+    loss += log1pf(en) + fmaxf(-ym, 0.f);
+    correct += ym > 0 ? 1 : 0;
+    seen += 1;
   }
   loss = warp_sum_d(loss); correct = warp_sum_d(correct); seen = warp_sum_d(seen);
   if (lane == 0 && stats && seen > 0) { atomicAdd(&stats[0], loss); atomicAdd(&stats[1], correct); atomicAdd(&stats[2], seen); }
@@ -718,10 +894,11 @@ extern "C" int psb_wide_pull_gemm(const void* args, const void* ctx, uint32_t ma
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return -(int)cudaErrorInvalidValue;
-  size_t smem = (size_t)kTileM * 128 + (size_t)a.N * 128 + 1024;
+  if (a.margin == nullptr && a.P == nullptr) return -(int)cudaErrorInvalidValue;
+  size_t smem = (size_t)kTileM * 128 + (size_t)a.N * 128 + 1024 + (a.margin ? (size_t)kTileM * (a.N + 1) * 4 : 0);
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute((const void*)k_wide_pull_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    cudaFuncSetAttribute((const void*)k_wide_pull_gemm, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
     attr_set = true;
   }
   int tiles = (int)((max_unique + kTileM - 1) / kTileM);
@@ -747,10 +924,11 @@ extern "C" int psb_wide_pull_xgemm(const void* args, const void* ctx, uint32_t m
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return -(int)cudaErrorInvalidValue;
-  size_t smem = (size_t)kTileM * 128 + (size_t)a.N * 128 + 1024;
+  if ((a.phases & 4) && a.margin == nullptr && a.P == nullptr) return -(int)cudaErrorInvalidValue;
+  size_t smem = (size_t)kTileM * 128 + (size_t)a.N * 128 + 1024 + (a.margin ? (size_t)kTileM * (a.N + 1) * 4 : 0);
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute((const void*)k_wide_pull_xgemm, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    cudaFuncSetAttribute((const void*)k_wide_pull_xgemm, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
     // several CTAs per SM must be resident at once: ask for the large shared-memory carve-out
     cudaFuncSetAttribute((const void*)k_wide_pull_xgemm, cudaFuncAttributePreferredSharedMemoryCarveout,
                          cudaSharedmemCarveoutMaxShared);
@@ -773,6 +951,18 @@ extern "C" int psb_wide_rowsum(const float* P, int N, const uint32_t* row_ptr, u
                                float* margin, double* stats, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   k_wide_rowsum<<<psb_device_sm_count() * 4, 256, 0, stream>>>(P, N, row_ptr, n_rows, fixed_z, csr_col, row_ctx, y, gcoef, margin, stats);
+  return -(int)cudaGetLastError();
+}
+// After a fused pull: add the listed long segments into the margins, then loss and d loss / d margin per row.
+extern "C" int psb_wide_rowloss(float* margin, const float* y, uint32_t n_rows, float* gcoef, double* stats,
+                                unsigned long long* plong_n, const void* plong_list, const float* plong_rows,
+                                uint32_t plong_cap, int N, const uint32_t* csc_row, const uint32_t* row_ctx,
+                                cudaStream_t stream) {
+  if (plong_n != nullptr && plong_cap > 0)
+    k_wide_long_margins<<<psb_device_sm_count() * 4, 256, 0, stream>>>(plong_n, (const uint4*)plong_list, plong_rows, plong_cap,
+                                                                       N, csc_row, row_ctx, margin);
+  const int blocks = (int)((n_rows + 255) / 256);
+  k_wide_rowloss<<<blocks < 1 ? 1 : (blocks > 1024 ? 1024 : blocks), 256, 0, stream>>>(margin, y, n_rows, gcoef, stats, plong_n);
   return -(int)cudaGetLastError();
 }
 extern "C" int psb_wide_push(const void* args, cudaStream_t stream) {

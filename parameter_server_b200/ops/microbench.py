@@ -225,14 +225,25 @@ def bench_wide_step(args):
     P = torch.zeros(rows * z, N, device=dev)
     step_no = [0]
 
+    def pull_and_rows(b, mark=lambda: None):
+        """Default: the pull kernel stores the product matrix P[U x N] and a second kernel gathers per row.
+        --fused: the pull kernel adds the products into the rows' margins itself and nothing of P reaches
+        memory (less traffic; at this size the extra work per tile costs more than the traffic it saves)."""
+        fused = args.fused
+        if cfg.pull_cap:
+            plane.pull_xgemm(b, ctx, None if fused else P, step_no[0], fuse_margins=fused)
+        else:
+            plane.pull_gemm(b, ctx, None if fused else P, fuse_margins=fused)
+        mark()
+        if fused:
+            plane.rowloss(b)
+        else:
+            plane.rowsum(b, P, N)
+
     def step(i):
         ids, y = pool[i % len(pool)]
         b = bufs[i % 2].localize(ids, y, plane.bounds, fixed_z=z, hash_seed=0, hash_bits=40)
-        if cfg.pull_cap:
-            plane.pull_xgemm(b, ctx, P, step_no[0])
-        else:
-            plane.pull_gemm(b, ctx, P)
-        plane.rowsum(b, P, N)
+        pull_and_rows(b)
         plane.push(b, ctx, step_no[0])
         plane.apply(step_no[0])
         step_no[0] += 1
@@ -257,11 +268,7 @@ def bench_wide_step(args):
         ev[0].record()
         b = bufs[i % 2].localize(ids, y, plane.bounds, fixed_z=z, hash_seed=0, hash_bits=40)
         ev[1].record()
-        if cfg.pull_cap:
-            plane.pull_xgemm(b, ctx, P, step_no[0])
-        else:
-            plane.pull_gemm(b, ctx, P)
-        ev[2].record(); plane.rowsum(b, P, N)
+        pull_and_rows(b, ev[2].record)
         ev[3].record(); plane.push(b, ctx, step_no[0])
         ev[4].record(); plane.apply(step_no[0])
         ev[5].record(); step_no[0] += 1
@@ -665,6 +672,7 @@ def main():
     s.add_argument("--log2-keys", type=int, default=25); s.add_argument("--n-ctx", type=int, default=64)
     s.add_argument("--iters", type=int, default=20); s.add_argument("--tau", type=int, default=8); s.add_argument("--pool", type=int, default=4)
     s.add_argument("--one-sided", action="store_true", help="pull by remote probes instead of the exchange kernel")
+    s.add_argument("--fused", action="store_true", help="add the products into the margins inside the pull kernel instead of storing P[U x N]")
     s = sub.add_parser("darlin"); s.add_argument("--phases", action="store_true"); s.add_argument("--rows", type=int, default=1250000); s.add_argument("--z", type=int, default=100)
     s.add_argument("--log2-keys", type=int, default=24); s.add_argument("--passes", type=int, default=3)
     s.add_argument("--tau", type=int, default=2)

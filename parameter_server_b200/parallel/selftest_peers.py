@@ -202,7 +202,9 @@ def test_wide(rank, world, dev):
     ok = True
     for rnd in range(3):                       # both parities of the exchange buffers, and one reuse
         P.zero_()
-        plane.pull_xgemm(b, ctx, P, rnd)       # one cooperative launch: requester, owner and product roles
+        # one cooperative launch: requester, owner and product roles; the last round also adds the
+        # products into the rows' margins (the fused form the training step uses)
+        plane.pull_xgemm(b, ctx, P, rnd, fuse_margins=rnd == 2)
         torch.cuda.synchronize()
         plane.check_status(f"rank {rank} round {rnd}")
         U = int(b.n_unique.item())
@@ -218,6 +220,12 @@ def test_wide(rank, world, dev):
         if not torch.allclose(P[:U].cpu(), Pref, rtol=2e-3, atol=2e-3):
             print(f"rank {rank} round {rnd}: product max err {float((P[:U].cpu() - Pref).abs().max())}")
             ok = False
+        if rnd == 2:
+            col = b.csr_col[:rows * z].cpu().numpy().reshape(rows, z)
+            mref = Pref[torch.from_numpy(col), torch.from_numpy(np.arange(rows) % N)[:, None]].sum(1)
+            if not torch.allclose(b.margin[:rows].cpu(), mref, rtol=2e-3, atol=2e-3):
+                print(f"rank {rank}: fused margins max err {float((b.margin[:rows].cpu() - mref).abs().max())}")
+                ok = False
         dist.barrier()
     return ok, fab
 

@@ -23,10 +23,20 @@ _vp, _u32, _u64, _i32, _f32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int, C.c_f
 WIDTH = 64
 
 
+class _nullctx:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
 class _PullArgs(C.Structure):
     _fields_ = [("S", _i32), ("N", _i32), ("keys", _vp * MAX_SHARDS), ("vals", _vp * MAX_SHARDS),
                 ("mask", _u64 * MAX_SHARDS), ("key_begin", _u64 * MAX_SHARDS), ("slot_mult", _u64 * MAX_SHARDS),
-                ("ukeys", _vp), ("n_unique", _vp), ("own_off", _vp), ("P", _vp), ("v_local", _vp), ("status", _vp)]
+                ("ukeys", _vp), ("n_unique", _vp), ("own_off", _vp), ("P", _vp), ("v_local", _vp), ("status", _vp),
+                ("seg_off", _vp), ("csc_row", _vp), ("row_ctx", _vp), ("margin", _vp),
+                ("plong_n", _vp), ("plong_list", _vp), ("plong_rows", _vp), ("plong_cap", _u32)]
 
 
 class _PushArgs(C.Structure):
@@ -54,7 +64,9 @@ class _XArgs(C.Structure):
                 ("my_resp_ready", _vp * MAX_SHARDS), ("my_resp_rows", _vp),
                 ("my_req_keys", _vp * MAX_SHARDS), ("my_req_hdr", _vp * MAX_SHARDS), ("my_req_ready", _vp * MAX_SHARDS),
                 ("resp_rows", _vp * MAX_SHARDS), ("resp_ready", _vp * MAX_SHARDS), ("alive", C.c_uint8 * MAX_SHARDS),
-                ("ukeys", _vp), ("n_unique", _vp), ("own_off", _vp), ("P", _vp), ("done", _vp), ("status", _vp)]
+                ("ukeys", _vp), ("n_unique", _vp), ("own_off", _vp), ("P", _vp), ("done", _vp), ("status", _vp),
+                ("seg_off", _vp), ("csc_row", _vp), ("row_ctx", _vp), ("margin", _vp),
+                ("plong_n", _vp), ("plong_list", _vp), ("plong_rows", _vp), ("plong_cap", _u32)]
 
 
 def _declare():
@@ -66,6 +78,7 @@ def _declare():
     L.psb_wide_pull_gemm.argtypes = [_vp, _vp, _u32, _vp]
     L.psb_wide_pull_xgemm.argtypes = [_vp, _vp, _u32, _vp]
     L.psb_wide_rowsum.argtypes = [_vp, _i32, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]
+    L.psb_wide_rowloss.argtypes = [_vp, _vp, _u32, _vp, _vp, _vp, _vp, _vp, _u32, _i32, _vp, _vp, _vp]
     L.psb_wide_push.argtypes = [_vp, _vp]
     L.psb_wide_apply.argtypes = [_vp, _vp]
     L.psb_wide_args_size.argtypes = [_i32]
@@ -127,6 +140,11 @@ class WidePlane:
         self.long_cap = max(64, cfg.inbox_cap // 256 + 1)
         self.long_list = torch.zeros(self.long_cap * 4, dtype=torch.int32, device=dev)   # {key, first chunk, begin, end}
         self.long_acc = torch.zeros(self.long_cap * WIDTH, dtype=torch.float32, device=dev)
+        # the fused pull's list of keys with long segments: {count, chunks}, entries, their rows of products
+        self.plong_cap = max(64, cfg.inbox_cap // 512 + 1)
+        self.plong_n = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.plong_list = torch.zeros(self.plong_cap * 4, dtype=torch.int32, device=dev)
+        self.plong_rows = torch.zeros(self.plong_cap * 128, dtype=torch.float32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.stats = torch.zeros(4, dtype=torch.float64, device=dev)
         check(self.L.psb_wide_init(self._p("keys"), self._p("vals"), self._p("acc"), cfg.table_capacity, stream_ptr()), "wide_init")
@@ -164,8 +182,22 @@ class WidePlane:
     def _xhdr(self, rank, par, peer):
         return self._p("xctrl", rank, 4 * (4 * self.S + (par * self.S + peer) * 2))
 
-    def pull_xgemm(self, b, ctx: torch.Tensor, P: torch.Tensor, ts: int, *, phases: int = 7, wait_iters: int = 0,
-                   stream=None):
+    def _fused(self, a, b, P, fuse_margins: bool, row_ctx, stream):
+        """``fuse_margins``: the kernel adds every product a row needs into ``b.margin`` (zeroed here) and
+        ``P`` may be None; :meth:`rowloss` then finishes the rows."""
+        a.P = ptr(P)
+        if fuse_margins:
+            with torch.cuda.stream(stream) if stream is not None else _nullctx():
+                b.margin[:max(1, b.n_rows)].zero_()
+            a.seg_off, a.csc_row, a.row_ctx, a.margin = ptr(b.seg_off), ptr(b.csc_row), ptr(row_ctx), ptr(b.margin)
+            a.plong_n, a.plong_list, a.plong_rows = ptr(self.plong_n), ptr(self.plong_list), ptr(self.plong_rows)
+            a.plong_cap = self.plong_cap
+            self._fused_call = (a.N, row_ctx)
+        else:
+            assert P is not None
+
+    def pull_xgemm(self, b, ctx: torch.Tensor, P: Optional[torch.Tensor], ts: int, *, phases: int = 7, wait_iters: int = 0,
+                   fuse_margins: bool = False, row_ctx: Optional[torch.Tensor] = None, stream=None):
         """Exchange form of :meth:`pull_gemm` for round ``ts`` (every rank calls it every round):
         keys to the owners in bulk, value rows back in bulk, the product on the local copy."""
         cfg = self.cfg
@@ -188,14 +220,16 @@ class WidePlane:
             a.alive[s] = 1
         a.my_resp_rows = self._p("resp_rows", self.rank, par * cfg.pull_cap * WIDTH * 2)
         a.ukeys, a.n_unique, a.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
-        a.P, a.done, a.status = ptr(P), self.sync.data_ptr() + 48, ptr(self.status)
+        a.done, a.status = self.sync.data_ptr() + 48, ptr(self.status)
+        self._fused(a, b, P, fuse_margins and bool(phases & 4), row_ctx, stream)
         check(self.L.psb_wide_pull_xgemm(C.byref(a), ptr(ctx), b.max_nnz, stream_ptr(stream)), "wide_pull_xgemm")
 
     def pulled_rows(self, ts: int, n: int) -> torch.Tensor:
         """The value rows this worker received in the exchange of round ``ts`` ([n, 64] bf16)."""
         return self.fabric.view(self.lay["resp_rows"] + (ts & 1) * self.cfg.pull_cap * WIDTH * 2, (n, WIDTH), torch.bfloat16)
 
-    def pull_gemm(self, b, ctx: torch.Tensor, P: torch.Tensor, v_local: Optional[torch.Tensor] = None, stream=None):
+    def pull_gemm(self, b, ctx: torch.Tensor, P: Optional[torch.Tensor], v_local: Optional[torch.Tensor] = None,
+                  fuse_margins: bool = False, row_ctx: Optional[torch.Tensor] = None, stream=None):
         """``P[u, n] = <value row of unique key u, ctx[n]>`` for the batch ``b``.
         ``ctx``: [N, 64] bf16 with N in (64, 128)."""
         a = _PullArgs()
@@ -204,13 +238,21 @@ class WidePlane:
             a.keys[s], a.vals[s] = self._p("keys", s), self._p("vals", s)
             a.mask[s], a.key_begin[s], a.slot_mult[s] = self.cfg.table_capacity - 1, self.bounds_host[s], self.slot_mult[s]
         a.ukeys, a.n_unique, a.own_off = ptr(b.ukeys), ptr(b.n_unique), ptr(b.own_off)
-        a.P, a.v_local, a.status = ptr(P), ptr(v_local), ptr(self.status)
+        a.v_local, a.status = ptr(v_local), ptr(self.status)
+        self._fused(a, b, P, fuse_margins, row_ctx, stream)
         assert ctx.dtype == torch.bfloat16 and ctx.is_contiguous() and ctx.shape[1] == WIDTH
         check(self.L.psb_wide_pull_gemm(C.byref(a), ptr(ctx), b.max_nnz, stream_ptr(stream)), "wide_pull_gemm")
 
     def rowsum(self, b, P: torch.Tensor, N: int, row_ctx: Optional[torch.Tensor] = None, stream=None):
         check(self.L.psb_wide_rowsum(ptr(P), N, ptr(b.row_ptr), b.n_rows, b.fixed_z, ptr(b.csr_col), ptr(row_ctx), ptr(b.y),
                                      ptr(b.gcoef), ptr(b.margin), ptr(self.stats), stream_ptr(stream)), "wide_rowsum")
+
+    def rowloss(self, b, stream=None):
+        """Loss, accuracy counters and ``gcoef`` from the margins that a fused pull accumulated."""
+        N, row_ctx = self._fused_call
+        check(self.L.psb_wide_rowloss(ptr(b.margin), ptr(b.y), b.n_rows, ptr(b.gcoef), ptr(self.stats), ptr(self.plong_n),
+                                      ptr(self.plong_list), ptr(self.plong_rows), self.plong_cap, N, ptr(b.csc_row),
+                                      ptr(row_ctx), stream_ptr(stream)), "wide_rowloss", kernels=2)
 
     def push(self, b, ctx: torch.Tensor, ts: int, row_ctx: Optional[torch.Tensor] = None, stream=None):
         q = ts % self.cfg.ring

@@ -49,18 +49,24 @@ def test_wide_pull_gemm_matches_fp32_matmul(cuda_lib, S, N):
     assert torch.allclose(P[:U].cpu(), ref, rtol=1e-3, atol=1e-3), float((P[:U].cpu() - ref).abs().max())
 
 
-@pytest.mark.parametrize("n_rows", [300, 900])
-def test_wide_training_step_matches_reference(cuda_lib, n_rows):
+@pytest.mark.parametrize("n_rows,fused", [(300, False), (900, False), (900, True)])
+def test_wide_training_step_matches_reference(cuda_lib, n_rows, fused):
     """With 900 rows the most frequent key owns about 3,000 nonzeros: its gradient is
-    reduced by several warps (segments above 256 nonzeros are split into chunks)."""
+    reduced by several warps (segments above 256 nonzeros are split into chunks).
+    ``fused``: the pull kernel adds the products into the rows' margins itself and no
+    product matrix is stored."""
     S, N = 2, 64
     planes, b, ctx, table, known, all_keys, ids, y, rows, z = _setup(S, N, rows=n_rows, seed=4)
     assert int((b.seg_off[1:int(b.n_unique.item()) + 1] - b.seg_off[:int(b.n_unique.item())]).max().item()) > (256 if n_rows == 900 else 0)
     U = int(b.n_unique.item())
     w = planes[0]
     P = torch.zeros(b.max_nnz, N, device="cuda")
-    w.pull_gemm(b, ctx, P)
-    w.rowsum(b, P, N)
+    if fused:
+        w.pull_gemm(b, ctx, None, fuse_margins=True)
+        w.rowloss(b)
+    else:
+        w.pull_gemm(b, ctx, P)
+        w.rowsum(b, P, N)
     w.push(b, ctx, 0)
     # the other (virtual) worker pushes nothing: publish an empty round for it
     from parameter_server_b200.ops.localize import LocalBatch
@@ -118,7 +124,8 @@ def test_wide_exchange_pull_matches_fp32_matmul(cuda_lib, S, N):
     for rnd in range(2):                                   # two rounds: both parities of the buffers
         for phase in (1, 2, 4):
             for p, bb, P in zip(planes, batches, Ps):
-                p.pull_xgemm(bb, ctx, P, rnd, phases=phase, wait_iters=1 << 12)
+                # the second round also adds the products into the rows' margins (fused form)
+                p.pull_xgemm(bb, ctx, P, rnd, phases=phase, wait_iters=1 << 12, fuse_margins=rnd == 1)
         torch.cuda.synchronize()
         for p in planes:
             p.check_status()
@@ -128,4 +135,9 @@ def test_wide_exchange_pull_matches_fp32_matmul(cuda_lib, S, N):
         assert torch.equal(planes[0].pulled_rows(rnd, U).cpu().float(), Vref)
         Pref = Vref @ ctx.cpu().float().T
         assert torch.allclose(Ps[0][:U].cpu(), Pref, rtol=2e-3, atol=2e-3)
+        if rnd == 1:
+            col = b.csr_col[:rows * z].cpu().numpy().reshape(rows, z)
+            n_of_row = np.arange(rows) % N
+            margin = Pref[torch.from_numpy(col), torch.from_numpy(n_of_row)[:, None]].sum(1)
+            assert torch.allclose(b.margin[:rows].cpu(), margin, rtol=2e-3, atol=2e-3)
         Ps[0].zero_()
