@@ -64,6 +64,42 @@ def bench_sort(args):
                       "frac_of_copy_bw_if_all_sort": bytes_sort / 1e9 / (med * 1e-3) / peak, "peak": tag}))
 
 
+def bench_localize(args):
+    """The localisation of one minibatch alone (unique keys + CSC/CSR remap + owner offsets) on
+    ``--rows`` x ``--z`` ids hashed to ``--key-bits`` significant bits: milliseconds per call by CUDA
+    events over distinct minibatches (inputs larger than L2), for ``--method`` bucket, sort or auto, and
+    with ``--graph`` replayed from a CUDA graph. Small ``--iters`` / ``--warmup`` make it a profiler target."""
+    from ..ops.localize import LocalBatch
+    from ..utils.synthetic import gen_batch
+    dev = torch.device("cuda")
+    rows, z = args.rows, args.z
+    nnz = rows * z
+    pool = [gen_batch(rows, z, 1 << args.log2_keys, 1.05, 0, i, device=dev)[:2] for i in range(4)]
+    b = LocalBatch(rows, nnz, 1, dev)
+    bounds = torch.tensor([0, -1], dtype=torch.int64, device=dev)
+    kw = dict(fixed_z=z, hash_seed=0, hash_bits=args.key_bits % 64, method=args.method)
+    st = torch.cuda.current_stream()
+
+    def run(i):
+        ids, y = pool[i % len(pool)]
+        if args.graph:
+            b.localize_replayed(ids, y, bounds, stream=st, **kw)
+        else:
+            b.localize(ids, y, bounds, **kw)
+    for i in range(args.warmup):
+        run(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.iters):
+        run(i)
+    e1.record(); torch.cuda.synchronize()
+    _lib_check = int(b.status.item())
+    print(json.dumps({"kernel": "localize", "rows": rows, "z": z, "nnz": nnz, "key_bits": args.key_bits, "method": args.method,
+                      "graph": bool(args.graph), "unique": int(b.n_unique.item()), "fell_back_to_sort": int(b.gate.item()),
+                      "status": _lib_check, "ms": round(e0.elapsed_time(e1) / max(1, args.iters), 4)}))
+
+
 def bench_step(args):
     from . import _lib
     from ..models.sparse_lr import SparseLRConfig, make_single_gpu
@@ -662,6 +698,10 @@ def main():
     sub = ap.add_subparsers(dest="cmd", required=True)
     s = sub.add_parser("sort"); s.add_argument("--n", type=int, default=65536 * 200)
     s.add_argument("--bits", type=int, default=64); s.add_argument("--iters", type=int, default=5)
+    s = sub.add_parser("localize"); s.add_argument("--rows", type=int, default=65536); s.add_argument("--z", type=int, default=200)
+    s.add_argument("--log2-keys", type=int, default=26); s.add_argument("--key-bits", type=int, default=40)
+    s.add_argument("--method", default="auto", choices=["auto", "bucket", "sort"]); s.add_argument("--graph", action="store_true")
+    s.add_argument("--iters", type=int, default=20); s.add_argument("--warmup", type=int, default=8)
     s = sub.add_parser("step"); s.add_argument("--rows", type=int, default=65536); s.add_argument("--z", type=int, default=200)
     s.add_argument("--log2-keys", type=int, default=26); s.add_argument("--iters", type=int, default=5)
     s.add_argument("--hashed-slots", action="store_true")
@@ -694,7 +734,7 @@ def main():
     from .. import _build
     _build.build_cuda()
     {"sort": bench_sort, "step": bench_step, "wide": bench_wide, "wide-step": bench_wide_step, "kv": bench_kv,
-     "darlin": bench_darlin, "h2d": bench_h2d, "fabric": bench_fabric, "layer": bench_layer, "gather": bench_gather}[args.cmd](args)
+     "darlin": bench_darlin, "h2d": bench_h2d, "localize": bench_localize, "fabric": bench_fabric, "layer": bench_layer, "gather": bench_gather}[args.cmd](args)
 
 
 if __name__ == "__main__":
