@@ -199,7 +199,8 @@ class LocalBatch:
         if ent == "seen":
             g = torch.cuda.CUDAGraph()
             before = _lib.LAUNCHES
-            with torch.cuda.graph(g, stream=stream):
+            # thread_local: other threads of the process (loaders, node threads) may call the runtime meanwhile
+            with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
                 self.localize(ids, y, bounds, row_ptr=row_ptr, vals=vals, stream=torch.cuda.current_stream(), **kw)
             state = {a: getattr(self, a) for a in ("nnz", "n_rows", "fixed_z", "row_ptr", "csr_val", "y", "pack_bits",
                                                    "csc_val", "csc_row")}

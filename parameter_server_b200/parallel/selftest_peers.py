@@ -205,6 +205,8 @@ def test_wide(rank, world, dev):
         # one cooperative launch: requester, owner and product roles; the last round also adds the
         # products into the rows' margins (the fused form the training step uses)
         plane.pull_xgemm(b, ctx, P, rnd, fuse_margins=rnd == 2)
+        if rnd == 2:
+            plane.rowloss(b)                   # adds the keys with long segments, then loss and gcoef
         torch.cuda.synchronize()
         plane.check_status(f"rank {rank} round {rnd}")
         U = int(b.n_unique.item())

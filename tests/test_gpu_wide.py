@@ -126,6 +126,8 @@ def test_wide_exchange_pull_matches_fp32_matmul(cuda_lib, S, N):
             for p, bb, P in zip(planes, batches, Ps):
                 # the second round also adds the products into the rows' margins (fused form)
                 p.pull_xgemm(bb, ctx, P, rnd, phases=phase, wait_iters=1 << 12, fuse_margins=rnd == 1)
+        if rnd == 1:
+            planes[0].rowloss(b)               # the fused margins are complete after the long segments are added
         torch.cuda.synchronize()
         for p in planes:
             p.check_status()
