@@ -257,14 +257,14 @@ class DarlinServer : public DarlinCompNode {
     fea_grp_ = call.fea_grp;
     int time = 0;
     const bool tail = call.tail_feature_freq > 0;
-    // round 1 per group: workers push (key, count); release their filtered-key pulls
+    // first exchange per group: workers push (key, count); release their filtered-key pulls
     for (int grp : fea_grp_) {
       (void)grp;
       if (tail) model_.WaitReceivedRequest(time, kWorkerGroup);
       model_.FinishReceivedRequest(time + 1, kWorkerGroup);
       time += kTimeRatio;
     }
-    // round 2 per group: workers push their keys; allocate weights; release the initial pulls
+    // second exchange per group: workers push their keys; allocate weights; release the initial pulls
     for (int grp : fea_grp_) {
       model_.WaitReceivedRequest(time, kWorkerGroup);
       auto& kv = model_[grp];
@@ -449,7 +449,7 @@ class DarlinWorker : public DarlinCompNode {
     int time = 0;
     std::unordered_map<int, Localizer<Key, Real>> localizer;
     std::unordered_map<int, SArray<Key>> uniq;
-    // round 1: tail-feature filter
+    // first exchange: tail-feature filter
     for (int grp : fea_grp_) {
       auto it = raw_.find(grp);
       SArray<Key> keys;
@@ -484,7 +484,7 @@ class DarlinWorker : public DarlinCompNode {
       }
       time += kTimeRatio;
     }
-    // round 2: publish my keys, fetch initial weights, build column-major X and the dual
+    // second exchange: publish my keys, fetch initial weights, build column-major X and the dual
     dual_.resize(y_.size());
     dual_.SetValue(1);
     for (int grp : fea_grp_) {
