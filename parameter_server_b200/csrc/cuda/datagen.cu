@@ -155,6 +155,26 @@ extern "C" int psb_probe_entries(void* table, const uint32_t* slots, uint32_t n,
   return -(int)cudaGetLastError();
 }
 
+// Ids that arrive as a bit stream (`bits` per id, id i at bit offset i * bits of little-endian 32-bit
+// words; the stream has a spare word after the last id) become 32-bit ids: two word loads, a funnel
+// shift and a mask per id, neighbouring threads on neighbouring ids.
+__global__ void __launch_bounds__(256) k_unpack_ids(const uint32_t* __restrict__ words, int bits, uint32_t n,
+                                                    uint32_t* __restrict__ out) {
+  const uint32_t mask = bits >= 32 ? 0xffffffffu : ((1u << bits) - 1u);
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const unsigned long long off = (unsigned long long)i * (unsigned)bits;
+    const uint32_t w = (uint32_t)(off >> 5), sh = (uint32_t)(off & 31);
+    out[i] = __funnelshift_r(words[w], words[w + 1], sh) & mask;
+  }
+}
+extern "C" int psb_unpack_ids(const uint32_t* words, int bits, uint32_t n, uint32_t* out, cudaStream_t stream) {
+  if (bits < 1 || bits > 32) return -(int)cudaErrorInvalidValue;
+  if (n == 0) return 0;
+  const uint32_t blocks = (n + 255) / 256, mx = (uint32_t)psb_device_sm_count() * 8;
+  k_unpack_ids<<<blocks > mx ? mx : blocks, 256, 0, stream>>>(words, bits, n, out);
+  return -(int)cudaGetLastError();
+}
+
 extern "C" int psb_flush_l2(uint32_t* buf, psb_u64 n_words, uint32_t v, cudaStream_t stream) {
   k_flush_l2<<<psb_device_sm_count() * 8, 256, 0, stream>>>(buf, n_words, v);
   return -(int)cudaGetLastError();

@@ -395,6 +395,8 @@ int psb_gen_batch(uint32_t* ids32, psb_u64* ids64, float* vals, float* y, uint32
 int psb_hash_ids(const uint32_t* ids32, const psb_u64* ids64, psb_u64* keys, psb_u64 n,
                  psb_u64 seed, cudaStream_t stream);
 int psb_flush_l2(uint32_t* buf, psb_u64 n_words, uint32_t v, cudaStream_t stream);
+// out[i] = bits [i * bits, (i + 1) * bits) of the little-endian word stream (which has a spare word at its end)
+int psb_unpack_ids(const uint32_t* words, int bits, uint32_t n, uint32_t* out, cudaStream_t stream);
 int psb_device_sm_count(void);
 
 // ---------------------------------------------------------------- symmetric heap (CUDA IPC)

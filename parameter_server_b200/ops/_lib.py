@@ -204,6 +204,7 @@ def _declare(lib):
     lib.psb_gen_batch.argtypes = [_vp, _vp, _vp, _vp, _u32, _u32, _u64, _f64, _u64, _u64, _i32, _vp]
     lib.psb_hash_ids.argtypes = [_vp, _vp, _vp, _u64, _u64, _vp]
     lib.psb_flush_l2.argtypes = [_vp, _u64, _u32, _vp]
+    lib.psb_unpack_ids.argtypes = [_vp, _i32, _u32, _vp, _vp]
     lib.psb_heap_alloc.argtypes = [C.POINTER(_vp), sz]
     lib.psb_heap_free.argtypes = [_vp]
     lib.psb_ipc_export.argtypes = [_vp, _vp]

@@ -19,6 +19,7 @@ import torch
 
 from . import _lib
 from ._lib import check, ptr, stream_ptr
+from ..utils.idpack import PackedIds
 
 
 def sort_pairs(keys: torch.Tensor, payload: Optional[torch.Tensor] = None, begin_bit: int = 0,
@@ -111,6 +112,15 @@ class LocalBatch:
         position.
         """
         L = _lib.lib()
+        if isinstance(ids, PackedIds):
+            # a bit stream from the loader: unpack to 32-bit ids first (part of the same launch sequence,
+            # so a replayed graph contains it)
+            n = ids.n
+            assert n <= self.max_nnz and ids.words.is_cuda and hash_seed is not None
+            if self.__dict__.get("_ids32") is None:
+                self._ids32 = torch.empty(self.max_nnz, dtype=torch.int32, device=self.device)
+            check(L.psb_unpack_ids(ptr(ids.words), ids.bits, n, ptr(self._ids32), stream_ptr(stream)), "unpack ids")
+            ids = self._ids32[:n]
         n = ids.numel()
         assert n <= self.max_nnz
         self.nnz = n
@@ -184,8 +194,10 @@ class LocalBatch:
         launch commands of plain kernels are fetched over the same link and queue behind the copies.
         Calls that never repeat (minibatches of varying size) run as plain launches."""
         def addr(t):
+            if isinstance(t, PackedIds):
+                return (t.words.data_ptr(), t.n, t.bits)
             return (0, 0) if t is None else (t.data_ptr(), t.numel())
-        key = (addr(ids), ids.dtype, addr(y), addr(bounds), addr(row_ptr), addr(vals),
+        key = (addr(ids), None if isinstance(ids, PackedIds) else ids.dtype, addr(y), addr(bounds), addr(row_ptr), addr(vals),
                tuple(sorted((k, v) for k, v in kw.items())))
         graphs = self.__dict__.setdefault("_graphs", {})
         ent = graphs.get(key)
