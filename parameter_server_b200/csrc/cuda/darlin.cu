@@ -80,10 +80,14 @@ __device__ void darlin_grad_p1(const PsbDarlinGrad& p) {
         const u32 wi = gb + k;
         const bool valid = wi < we;
         f[k] = valid ? p.flagbits[wi] : 0u;
-        const u32 base = valid ? p.wordbase[wi] : 0u;
         const u32 i = wi * 32 + lane;
         in[k] = valid && i >= nz0 && i < nz1;
-        col[k] = in[k] ? p.gcol[base + __popc(f[k] & le) - 1] : 0u;   // local unique key -> global column
+        if (p.csc_col != nullptr) {
+          col[k] = in[k] ? p.csc_col[i] : 0u;                         // the column of every nonzero is at hand
+        } else {
+          const u32 base = valid ? p.wordbase[wi] : 0u;
+          col[k] = in[k] ? p.gcol[base + __popc(f[k] & le) - 1] : 0u;   // local unique key -> global column
+        }
         row[k] = in[k] ? p.csc_row[i] : 0u;
         val[k] = (in[k] && p.csc_val) ? p.csc_val[i] : 1.f;
       }
@@ -298,7 +302,8 @@ __device__ void darlin_dual_p1(const PsbDarlinDual& p) {
       const u32 wi = wa + k * nwarps;
       const u32 i = wi * 32 + lane;
       in[k] = wi < w1 && i >= nz0 && i < nz1;
-      col[k] = in[k] ? p.gcol[p.wordbase[wi] + __popc(p.flagbits[wi] & le) - 1] : 0u;
+      if (p.csc_col != nullptr) col[k] = in[k] ? p.csc_col[i] : 0u;
+      else col[k] = in[k] ? p.gcol[p.wordbase[wi] + __popc(p.flagbits[wi] & le) - 1] : 0u;
       row[k] = in[k] ? p.csc_row[i] : 0u;
       x[k] = (in[k] && p.csc_val) ? p.csc_val[i] : 1.f;
     }

@@ -315,6 +315,7 @@ typedef struct {
   float* gu_inbox[PSB_MAX_SHARDS];   // owner s: [2][block_cap] area of this source
   uint32_t* ready[PSB_MAX_SHARDS];   // owner s: flag of this source
   uint32_t* bar; uint32_t* done; uint32_t* status;
+  const uint32_t* csc_col;           // nullable: global column of every nonzero (saves two dependent gathers per nonzero)
 } PsbDarlinGrad;
 
 typedef struct {
@@ -359,6 +360,7 @@ typedef struct {
   uint8_t alive[PSB_MAX_SHARDS];
   uint32_t wait_iters;
   uint32_t* bar; uint32_t* status;
+  const uint32_t* csc_col;           // nullable, as in PsbDarlinGrad
 } PsbDarlinDual;
 
 // A pass over n_steps feature blocks in one cooperative launch (see k_darlin_pass). grad / update /

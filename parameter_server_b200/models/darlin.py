@@ -105,6 +105,11 @@ class DarlinRank:
         gcol = torch.searchsorted(gk, self.local_keys ^ sign)
         self.gcol = gcol.to(torch.int32)
         self.gcol_host = gcol.cpu().numpy()               # block -> local key range look-ups on the host
+        # the global column of every nonzero (CSC order): 4 bytes per nonzero that save the block kernels
+        # two dependent gathers per nonzero (word base -> local key -> column)
+        U = self.local_keys.numel()
+        seg = self.b.seg_off[:U + 1].long()
+        self.csc_col = torch.repeat_interleave(self.gcol, seg[1:] - seg[:-1]) if U else torch.zeros(0, dtype=torch.int32, device=dev)
         bh = shard_bounds(cfg.key_range, self.S)
         edges = torch.from_numpy(np.array([min(b, (1 << 64) - 1) for b in bh[:-1]], dtype=np.uint64).view(np.int64)).to(dev) ^ sign
         self.shard_col = torch.searchsorted(gk, edges).tolist() + [self.n_cols]
@@ -174,6 +179,7 @@ class DarlinRank:
             p.gu_inbox[s] = self._gu(s, q, self.rank)
             p.ready[s] = self._flag(s, 0, q, self.rank)
         p.bar, p.done, p.status = self.sync.data_ptr(), self.sync.data_ptr() + 8, ptr(self.status)
+        p.csc_col = ptr(self.csc_col) if self.csc_col.numel() else None
         return p
 
     def _update_params(self, blk: int, q: int):
@@ -220,6 +226,7 @@ class DarlinRank:
             p.wnew_ready[s] = self._flag(self.rank, 1, q, s)
             p.alive[s] = 1
         p.bar, p.status = self.sync.data_ptr() + 32, ptr(self.status)
+        p.csc_col = ptr(self.csc_col) if self.csc_col.numel() else None
         return p
 
     def grad(self, blk: int, ts: int, stream=None):
