@@ -176,12 +176,18 @@ def test_pipelined_submit_matches_synchronous(cuda_lib):
     assert np.allclose(outs[0][1].numpy(), outs[1][1].numpy(), rtol=1e-5, atol=1e-7)
 
 
-@pytest.mark.parametrize("S", [1, 3])
-def test_pull_exchange_equals_one_sided_path(cuda_lib, S):
+@pytest.mark.parametrize("S,hashed", [(1, True), (3, True), (8, True), (2, False)])
+def test_pull_exchange_equals_one_sided_path(cuda_lib, S, hashed):
     """Two-sided pull (keys to owners, weights back, slots reused by a values-only
     push) gives the same margins and the same model as the one-sided path. The
     three phases run as separate launches here because the emulated ranks share
-    one GPU and one stream."""
+    one GPU and one stream. With several sources the exchange path merges the
+    sources' records per key-range part in shared memory, the one-sided path
+    accumulates in the table and lets one record per key lead: both must agree,
+    with eight sources too. ``hashed=False``: small consecutive keys, which all
+    fall into the first part of the first owner, more than the merge table takes,
+    so that part goes through the accumulate-then-lead protocol inside the
+    exchange path."""
     from parameter_server_b200.ops.localize import LocalBatch
     from parameter_server_b200.parallel.dataplane import OptimizerConfig
     opt = OptimizerConfig(algo="ftrl", alpha=0.1, beta=1.0, l1=0.01, l2=0.1)
@@ -190,13 +196,17 @@ def test_pull_exchange_equals_one_sided_path(cuda_lib, S):
     rounds = [[_batch(rng, rows, z, 2000) for _ in range(S)] for _ in range(4)]
     results = []
     for mode in ("one_sided", "exchange"):
-        planes = _mk(S, opt, pull_cap=rows * z if mode == "exchange" else 0, ordered=True, inbox=rows * z)
+        planes = _mk(S, opt, pull_cap=rows * z if mode == "exchange" else 0, ordered=hashed, inbox=rows * z)
         bufs = [LocalBatch(rows, rows * z, S, "cuda") for _ in range(S)]
         margins = []
         for t, data in enumerate(rounds):
             for r in range(S):
                 ids, y, _ = data[r]
-                bufs[r].localize(torch.from_numpy(ids).cuda(), torch.from_numpy(y).cuda(), planes[r].bounds, fixed_z=z, hash_seed=1)
+                if hashed:
+                    bufs[r].localize(torch.from_numpy(ids).cuda(), torch.from_numpy(y).cuda(), planes[r].bounds, fixed_z=z, hash_seed=1)
+                else:
+                    bufs[r].localize(torch.from_numpy(ids.astype(np.int64) + 1).cuda(), torch.from_numpy(y).cuda(),
+                                     planes[r].bounds, fixed_z=z, hash_seed=None)
             if mode == "one_sided":
                 for r in range(S):
                     planes[r].pull_margin(bufs[r], need_applied=t)
