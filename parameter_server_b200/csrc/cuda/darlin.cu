@@ -53,7 +53,7 @@ __device__ void darlin_grad_p1(const PsbDarlinGrad& p) {
   const u32 gsize = gridDim.x * blockDim.x, gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = threadIdx.x & 31;
   const u32 gwarp = gtid >> 5, nwarps = gsize >> 5;
-  const u32 nz0 = p.seg_off[p.u0], nz1 = p.seg_off[p.u1];
+  const u32 nz0 = p.nz0, nz1 = p.nz1;
   const u32 w0 = nz0 >> 5, w1 = (nz1 + 31) >> 5;
   const u32 le = 0xffffffffu >> (31 - lane);
   // chunk length: up to 16 words, but no longer than what keeps every warp busy
@@ -289,7 +289,7 @@ __device__ void darlin_dual_p1(const PsbDarlinDual& p) {
   const u32 gsize = gridDim.x * blockDim.x, gtid = blockIdx.x * blockDim.x + threadIdx.x;
   const int lane = threadIdx.x & 31;
   const u32 gwarp = gtid >> 5, nwarps = gsize >> 5;
-  const u32 nz0 = p.seg_off[p.u0], nz1 = p.seg_off[p.u1];
+  const u32 nz0 = p.nz0, nz1 = p.nz1;
   const u32 w0 = nz0 >> 5, w1 = (nz1 + 31) >> 5;
   const u32 le = 0xffffffffu >> (31 - lane);
   constexpr int kGroup = 4;                 // words whose gathers are in flight together
@@ -415,6 +415,30 @@ __global__ void __launch_bounds__(kPassThreads, 1) k_darlin_pass(const PsbDarlin
   // shares of the column passes: the owner update is the longest of the three, the column state the
   // shortest; with fewer than six CTAs (never on a real device) every CTA would need all three
   const u32 n_upd = gridDim.x / 2, n_out = gridDim.x / 3;
+  // The parameter blocks of step i + 1 are fetched (one word per thread, into a register) right after the
+  // barrier of step i, so that their global-memory latency runs under the column passes.
+  constexpr u32 WG = sizeof(PsbDarlinGrad) / 4, WU = sizeof(PsbDarlinUpdate) / 4, WD = sizeof(PsbDarlinDual) / 4;
+  static_assert(WG + WU + WD <= kPassThreads, "one word of the three parameter blocks per thread");
+  auto fetch = [&](u32 i, u32& word) -> bool {
+    const u32 t = threadIdx.x;
+    if (t < WG) {
+      if (i >= n) return false;
+      word = reinterpret_cast<const u32*>(&q.grad[(size_t)q.order[i] * R + (q.ts_base + i) % R])[t];
+    } else if (t < WG + WU) {
+      if (i + 1 < tau || i + 1 - tau >= n) return false;
+      const u32 k = i + 1 - tau;
+      word = reinterpret_cast<const u32*>(&q.update[(size_t)q.order[k] * R + (q.ts_base + k) % R])[t - WG];
+    } else if (t < WG + WU + WD) {
+      if (i < tau || i - tau >= n) return false;
+      const u32 j = i - tau;
+      word = reinterpret_cast<const u32*>(&q.dual[(size_t)q.order[j] * R + (q.ts_base + j) % R])[t - WG - WU];
+    } else {
+      return false;
+    }
+    return true;
+  };
+  u32 pre = 0;
+  bool pre_ok = fetch(0, pre);
   for (u32 i = 0; i < n + tau; ++i) {
     const bool has_g = i < n, has_d = i >= tau, has_u = i + 1 >= tau && i + 1 - tau < n;
     // With q.phase_ns, CTA 0 adds up where its time goes: {loading the parameter blocks, the two nonzero
@@ -428,9 +452,12 @@ __global__ void __launch_bounds__(kPassThreads, 1) k_darlin_pass(const PsbDarlin
     };
     mark(0);
     __syncthreads();                               // nobody still reads the previous step's blocks
-    if (has_g) { const u32 ts = q.ts_base + i; load_params(&s_g, &q.grad[(size_t)q.order[i] * R + ts % R]); }
-    if (has_d) { const u32 ts = q.ts_base + i - tau; load_params(&s_d, &q.dual[(size_t)q.order[i - tau] * R + ts % R]); }
-    if (has_u) { const u32 ts = q.ts_base + i + 1 - tau; load_params(&s_u, &q.update[(size_t)q.order[i + 1 - tau] * R + ts % R]); }
+    if (pre_ok) {
+      const u32 tt = threadIdx.x;
+      if (tt < WG) reinterpret_cast<u32*>(&s_g)[tt] = pre;
+      else if (tt < WG + WU) reinterpret_cast<u32*>(&s_u)[tt - WG] = pre;
+      else reinterpret_cast<u32*>(&s_d)[tt - WG - WU] = pre;
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
       s_g.ts1 = q.ts_base + i + 1;
@@ -453,6 +480,7 @@ __global__ void __launch_bounds__(kPassThreads, 1) k_darlin_pass(const PsbDarlin
     mark(2);
     if (!grid_barrier(q.bar, q.status)) return;
     mark(3);
+    pre_ok = fetch(i + 1, pre);
     // phase B: the three column passes side by side, each on its share of the CTAs
     if (blockIdx.x < n_upd) {
       if (has_u && s_u.S > 0) darlin_update_body(s_u, Part{blockIdx.x, n_upd});

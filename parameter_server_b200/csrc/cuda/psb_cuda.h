@@ -316,6 +316,7 @@ typedef struct {
   uint32_t* ready[PSB_MAX_SHARDS];   // owner s: flag of this source
   uint32_t* bar; uint32_t* done; uint32_t* status;
   const uint32_t* csc_col;           // nullable: global column of every nonzero (saves two dependent gathers per nonzero)
+  uint32_t nz0, nz1;                 // = seg_off[u0], seg_off[u1]: the block's nonzeros (filled by the host: one load level less)
 } PsbDarlinGrad;
 
 typedef struct {
@@ -361,6 +362,7 @@ typedef struct {
   uint32_t wait_iters;
   uint32_t* bar; uint32_t* status;
   const uint32_t* csc_col;           // nullable, as in PsbDarlinGrad
+  uint32_t nz0, nz1;                 // as in PsbDarlinGrad
 } PsbDarlinDual;
 
 // A pass over n_steps feature blocks in one cooperative launch (see k_darlin_pass). grad / update /

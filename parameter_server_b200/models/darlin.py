@@ -110,6 +110,7 @@ class DarlinRank:
         U = self.local_keys.numel()
         seg = self.b.seg_off[:U + 1].long()
         self.csc_col = torch.repeat_interleave(self.gcol, seg[1:] - seg[:-1]) if U else torch.zeros(0, dtype=torch.int32, device=dev)
+        self.seg_host = seg.cpu().numpy() if U else np.zeros(1, dtype=np.int64)      # the blocks' nonzero ranges go into their parameter blocks
         bh = shard_bounds(cfg.key_range, self.S)
         edges = torch.from_numpy(np.array([min(b, (1 << 64) - 1) for b in bh[:-1]], dtype=np.uint64).view(np.int64)).to(dev) ^ sign
         self.shard_col = torch.searchsorted(gk, edges).tolist() + [self.n_cols]
@@ -180,6 +181,7 @@ class DarlinRank:
             p.ready[s] = self._flag(s, 0, q, self.rank)
         p.bar, p.done, p.status = self.sync.data_ptr(), self.sync.data_ptr() + 8, ptr(self.status)
         p.csc_col = ptr(self.csc_col) if self.csc_col.numel() else None
+        p.nz0, p.nz1 = int(self.seg_host[u0]), int(self.seg_host[u1])
         return p
 
     def _update_params(self, blk: int, q: int):
@@ -227,6 +229,7 @@ class DarlinRank:
             p.alive[s] = 1
         p.bar, p.status = self.sync.data_ptr() + 32, ptr(self.status)
         p.csc_col = ptr(self.csc_col) if self.csc_col.numel() else None
+        p.nz0, p.nz1 = int(self.seg_host[u0]), int(self.seg_host[u1])
         return p
 
     def grad(self, blk: int, ts: int, stream=None):

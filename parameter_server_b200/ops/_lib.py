@@ -107,7 +107,7 @@ class DarlinGrad(C.Structure):
         ("seg_off", _vp), ("csc_row", _vp), ("csc_val", _vp), ("flagbits", _vp), ("wordbase", _vp), ("gcol", _vp),
         ("y", _vp), ("margin", _vp), ("active", _vp), ("delta", _vp), ("stage", _vp),
         ("gu_inbox", _vp * MAX_SHARDS), ("ready", _vp * MAX_SHARDS),
-        ("bar", _vp), ("done", _vp), ("status", _vp), ("csc_col", _vp),
+        ("bar", _vp), ("done", _vp), ("status", _vp), ("csc_col", _vp), ("nz0", _u32), ("nz1", _u32),
     ]
 
 
@@ -129,7 +129,7 @@ class DarlinDual(C.Structure):
         ("seg_off", _vp), ("csc_row", _vp), ("csc_val", _vp), ("flagbits", _vp), ("wordbase", _vp), ("gcol", _vp),
         ("margin", _vp), ("w_cur", _vp), ("delta", _vp), ("active", _vp), ("delta_max", _f32),
         ("wnew", _vp), ("wnew_ready", _vp * MAX_SHARDS), ("alive", C.c_uint8 * MAX_SHARDS),
-        ("wait_iters", _u32), ("bar", _vp), ("status", _vp), ("csc_col", _vp),
+        ("wait_iters", _u32), ("bar", _vp), ("status", _vp), ("csc_col", _vp), ("nz0", _u32), ("nz1", _u32),
     ]
 
 
