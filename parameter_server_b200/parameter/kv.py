@@ -103,9 +103,15 @@ class DeviceKVMap:
             self._callbacks[ts] = callback
 
     def _buffer(self, keys: torch.Tensor) -> LocalBatch:
+        # A request with the very key tensor of the request before it (the usual push-then-pull pair; same
+        # object, not written to since) reuses that request's key buffer and owner offsets: three launches less.
+        tag = (id(keys), keys._version, keys.data_ptr(), keys.numel())
+        if tag == self.__dict__.get("_last_keys_tag"):
+            return self._last_buf
         b = self._bufs[self._next_buf]
         self._next_buf = (self._next_buf + 1) % len(self._bufs)
         b.set_keys(keys, self.plane.bounds)
+        self._last_keys_tag, self._last_buf, self._last_keys = tag, b, keys      # (keeps the tensor, and so its id, alive)
         return b
 
     @staticmethod
