@@ -70,7 +70,11 @@ __global__ void __launch_bounds__(256) k_layer_push(const LayerPushArgs p) {
   }
   __syncthreads();
   const u64 gsize = (u64)gridDim.x * blockDim.x, gtid = blockIdx.x * (u64)blockDim.x + threadIdx.x;
-  for (int s = 0; s < p.S; ++s) {
+  // Every CTA takes the owners in its own order (CTA b starts with owner b mod S): at any moment the grid's
+  // stores are spread over all owners. With every CTA on owner 0 first, all GPUs would write into the same
+  // GPU at the same time and the other links would sit idle.
+  for (int k = 0; k < p.S; ++k) {
+    const int s = (int)((blockIdx.x + (u32)k) % (u32)p.S);
     if (!s_ok[s]) continue;
     const u64 b = p.seg_begin[s], n = p.seg_begin[s + 1] - b;
     const float* src = p.data + b;
@@ -179,7 +183,8 @@ __global__ void __launch_bounds__(256) k_layer_pull(const LayerPullArgs p) {
   }
   __syncthreads();
   const u64 gsize = (u64)gridDim.x * blockDim.x, gtid = blockIdx.x * (u64)blockDim.x + threadIdx.x;
-  for (int s = 0; s < p.S; ++s) {
+  for (int k = 0; k < p.S; ++k) {
+    const int s = (int)((blockIdx.x + (u32)k) % (u32)p.S);   // owners in a per-CTA order, as in k_layer_push
     const u64 b = p.seg_begin[s], n = p.seg_begin[s + 1] - b;
     const float* src = p.data[s];
     float* dst = p.out + b;

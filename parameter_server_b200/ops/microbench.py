@@ -679,11 +679,12 @@ def bench_layer(args):
         ts.sort(); tn.sort()
         ms = _max_over_ranks(dist, world, dev, [ts[len(ts) // 2]])[0]
         ms_n = _max_over_ranks(dist, world, dev, [tn[len(tn) // 2]])[0] if tn else None
-        # bytes that leave (push) and enter (pull) a GPU over NVLink: the (S-1)/S part of the layer, each way
+        # Per direction and GPU: my push sends the (S-1)/S part of the layer out and the peers' pulls of my
+        # shard send as much out again; the same two amounts come in (the peers' pushes, my pull).
         link = n * 4 * (world - 1) / max(1, world)
         rows.append({"layer": lid, "elements": n, "ms_push_apply_pull": round(ms, 4),
                      "MB_per_s_per_worker": round(n * 4 / 1e6 / (ms * 1e-3), 1),
-                     "nvlink_GB_per_s_per_gpu_per_direction": round(2 * link / 1e9 / (ms * 1e-3) / 2, 1) if world > 1 else None,
+                     "nvlink_GB_per_s_per_gpu_per_direction": round(2 * link / 1e9 / (ms * 1e-3), 1) if world > 1 else None,
                      "nccl_rs_ag_ms": None if ms_n is None else round(ms_n, 4)})
     if rank == 0:
         tot = sum(r["ms_push_apply_pull"] for r in rows)
