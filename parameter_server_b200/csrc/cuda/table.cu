@@ -277,21 +277,26 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
     key_hit = p.ts1 > 1 && cur == prev && __ldcg(&p.kc_state[2 * (par ^ 1) + 1]) == (u64)U + 1;
   }
   // four independent keys per thread and trip, loads first
-  for (u32 u0 = gtid; u0 < U; u0 += 4 * gsize) {
-    u64 k[4];
+  // Every CTA takes the owners in its own order (CTA b starts with owner b mod S), each owner's part of the
+  // key list divided over the whole grid: at any moment the grid's peer stores are spread over all owners
+  // instead of all GPUs writing into the same one.
+  for (int kk = 0; kk < S; ++kk) {
+    const int s = (int)((blockIdx.x + (u32)kk) % (u32)S);
+    const u32 b0 = s_off[s], cnt = s_off[s + 1] - b0;
+    for (u32 j0 = gtid; j0 < cnt; j0 += 4 * gsize) {
+      u64 k[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      u32 u = u0 + q * gsize;
-      k[q] = u < U ? p.ukeys[u] : 0;
-    }
+      for (int q = 0; q < 4; ++q) {
+        const u32 j = j0 + q * gsize;
+        k[q] = j < cnt ? p.ukeys[b0 + j] : 0;
+      }
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      u32 u = u0 + q * gsize;
-      if (u >= U) break;
-      int s = owner_of(s_off, S, u);
-      u32 j = u - s_off[s];
-      if (j < p.req_cap && !key_hit) p.req_keys[s][j] = k[q];
-      if (p.grad_zero) p.grad_zero[u] = 0.f;
+      for (int q = 0; q < 4; ++q) {
+        const u32 j = j0 + q * gsize;
+        if (j >= cnt) break;
+        if (j < p.req_cap && !key_hit) p.req_keys[s][j] = k[q];
+        if (p.grad_zero) p.grad_zero[b0 + j] = 0.f;
+      }
     }
   }
   PSB_TSTAMP(1);
@@ -322,7 +327,8 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
     set_status(p.status, kWaitTimeout);
   Entry* tab = (Entry*)p.table;
   const SlotMap sm{p.mask, p.key_begin, p.slot_mult};
-  for (int r = 0; r < S; ++r) {
+  for (int kk = 0; kk < S; ++kk) {
+    const int r = (int)((blockIdx.x + (u32)kk) % (u32)S);   // sources in a per-CTA order: no source gets all answers at once
     if (!p.alive[r]) continue;
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -667,10 +673,12 @@ __global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
         if (j < p.inbox_cap) p.inbox_keys[s][j] = p.ukeys[u];
       }
   }
-  const u32 G = s_gp[S];
-  for (u32 g = gwarp; g < G; g += nwarps) {
-    int s = 0;
-    while (s + 1 < S && g >= s_gp[s + 1]) ++s;
+  // owners in a per-CTA order, each owner's groups divided over the whole grid (see k_pull_exchange)
+  for (int kk = 0; kk < S; ++kk) {
+  const int s = (int)((blockIdx.x + (u32)kk) % (u32)S);
+  const u32 ng = s_gp[s + 1] - s_gp[s];
+  for (u32 gi = gwarp; gi < ng; gi += nwarps) {
+    const u32 g = s_gp[s] + gi;
     u32 cnt = min(s_off[s + 1] - s_off[s], p.inbox_cap) * kw;       // values of this owner's slice
     u32 j0 = (g - s_gp[s]) * 32, j = j0 + lane;
     bool valid = j < cnt;
@@ -696,6 +704,7 @@ __global__ void __launch_bounds__(kThreads) k_push(const PsbPushParams p) {
         if (lane == 0) scales[j0 >> 5] = scale;
       }
     }
+  }
   }
   // signal: all of this CTA's peer stores are ordered before its arrival, the
   // last CTA to arrive publishes counts and the release flags
