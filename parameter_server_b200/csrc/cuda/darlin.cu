@@ -188,13 +188,10 @@ __device__ void darlin_update_body(const PsbDarlinUpdate& p, const Part part) {
   __shared__ u32 s_last;
   __shared__ float s_vio;
   const int S = p.S;
-  if (threadIdx.x == 0) {
-    s_vio = 0.f;
+  if (threadIdx.x == 0) s_vio = 0.f;
+  if (threadIdx.x < S && p.alive[threadIdx.x]) {   // one lane per source: the polls run side by side
     const u32 iters = p.wait_iters ? p.wait_iters : kPeerWaitIters;
-    for (int r = 0; r < S; ++r) {
-      if (!p.alive[r]) continue;
-      if (!wait_flag_ge_sys(p.ready[r], p.ts1, iters)) set_status(p.status, kWaitTimeout);
-    }
+    if (!wait_flag_ge_sys(p.ready[threadIdx.x], p.ts1, iters)) set_status(p.status, kWaitTimeout);
   }
   __syncthreads();
   const u32 gsize = part.count * blockDim.x, gtid = part.index * blockDim.x + threadIdx.x;

@@ -475,9 +475,9 @@ __global__ void __launch_bounds__(kThreads) k_pull_exchange(const PsbPullExchang
   // caller then reads the weights from the response buffer after this kernel)
   PSB_TSTAMP(5);
   __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s)
-      if (p.alive[s] && !wait_flag_ge_sys(p.my_resp_ready[s], p.ts1, iters)) set_status(p.status, kWaitTimeout);
+  if (threadIdx.x < S) {                           // one lane per owner: the polls run side by side
+    const int s = threadIdx.x;
+    if (p.alive[s] && !wait_flag_ge_sys(p.my_resp_ready[s], p.ts1, iters)) set_status(p.status, kWaitTimeout);
   }
   __syncthreads();
   if (p.n_rows == 0) return;
@@ -746,22 +746,32 @@ __global__ void __launch_bounds__(kThreads) k_apply(const PsbApplyParams p) {
   const int S = p.S;
   Entry* tab = (Entry*)p.table;
   PSB_TSTAMP(0);
-  if (threadIdx.x == 0) {
-    u32 acc = 0;
-    const u32 iters = p.wait_iters ? p.wait_iters : kPeerWaitIters;
-    for (int r = 0; r < S; ++r) {
-      s_pre[r] = acc;
+  // the sources' flags are polled side by side (lane r of warp 0 waits for source r): a system-scope
+  // poll costs about a microsecond even when the flag is already set, and eight in a row add up
+  if (threadIdx.x < 32) {
+    const int r = threadIdx.x;
+    u32 mine = 0;
+    if (r < S) {
       s_cached[r] = p.cached[r];
-      if (!p.alive[r]) continue;
-      if (!wait_flag_ge_sys(p.ready[r], p.ts1, iters)) {
-        set_status(p.status, kWaitTimeout);
-        continue;
+      if (p.alive[r]) {
+        const u32 iters = p.wait_iters ? p.wait_iters : kPeerWaitIters;
+        if (wait_flag_ge_sys(p.ready[r], p.ts1, iters)) {
+          const u32 c = *((volatile const u32*)p.count[r]);
+          if (p.mode[r] && *((volatile const u32*)p.mode[r])) s_cached[r] = 1;
+          mine = min(c, p.inbox_cap);
+        } else {
+          set_status(p.status, kWaitTimeout);
+        }
       }
-      u32 c = *((volatile const u32*)p.count[r]);
-      if (p.mode[r] && *((volatile const u32*)p.mode[r])) s_cached[r] = 1;
-      acc += min(c, p.inbox_cap);
     }
-    s_pre[S] = acc;
+    u32 inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const u32 v = __shfl_up_sync(0xffffffffu, inc, o);
+      if (r >= o) inc += v;
+    }
+    if (r < S) s_pre[r] = inc - mine;
+    if (r == S - 1) s_pre[S] = inc;
   }
   __syncthreads();
   PSB_TSTAMP(1);
