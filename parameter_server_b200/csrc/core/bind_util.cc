@@ -2,6 +2,7 @@
 // encode/decode), ordered match.
 #include "bind_common.h"
 #include "data.h"
+#include "evaluation.h"
 #include "filter.h"
 #include "ordered_match.h"
 #include "remote_node.h"
@@ -25,6 +26,8 @@ void BindUtil(py::module& m) {
     return py::make_tuple(out[0], out[1]);
   });
   m.def("sketch_hash", [](uint64_t k) { return Sketch::hash(k); });
+  m.def("hwtic", []() { return hwtic(); }, "time-stamp counter now");
+  m.def("hwtoc", [](uint64_t start) { return hwtoc(start); }, "cycles since hwtic()");
   m.def("read_file", [](const std::string& name) -> py::object {
     std::string out;
     bool ok;

@@ -107,6 +107,23 @@ inline std::chrono::steady_clock::time_point tic() { return std::chrono::steady_
 inline double toc(std::chrono::steady_clock::time_point start) {
   return std::chrono::duration<double>(std::chrono::steady_clock::now() - start).count();
 }
+// Cycle-counter pair for very short sections (the reference's hwtic / hwtoc, util/resource_usage.h:33-50):
+// hwtic() reads the time-stamp counter, hwtoc(start) the cycles since (0 where the target has no such counter).
+inline uint64_t hwtic() {
+#if defined(__x86_64__) || defined(__i386__)
+  uint32_t lo, hi;
+  __asm__ __volatile__("rdtsc" : "=a"(lo), "=d"(hi));
+  return ((uint64_t)hi << 32) | lo;
+#elif defined(__aarch64__)
+  uint64_t v;
+  __asm__ __volatile__("mrs %0, cntvct_el0" : "=r"(v));
+  return v;
+#else
+  return 0;
+#endif
+}
+inline uint64_t hwtoc(uint64_t start) { return hwtic() - start; }
+
 class Timer {
  public:
   void start() { tp_ = tic(); }

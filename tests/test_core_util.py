@@ -297,3 +297,11 @@ esac
     y, mats = r.read_matrices(10)
     assert list(y) == [-1.0] and list(mats[0]["index"]) == [2]
     assert core.read_file("s3://mybucket/data/x;rm -rf y") is None      # refused before any shell sees it
+
+
+def test_cycle_counter_timer_pair_moves_forward():
+    """hwtic / hwtoc (the reference's cycle-counter timers, util/resource_usage.h): monotone and non-zero."""
+    from parameter_server_b200.system import core
+    t0 = core.hwtic()
+    x = sum(range(20000))
+    assert x > 0 and core.hwtoc(t0) > 0 and core.hwtic() >= t0
