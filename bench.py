@@ -34,6 +34,8 @@ PUBLISHED_FTRL_EXAMPLES_PER_S = 4.0e4   # online FTRL progress log of the refere
 
 
 def reference_arm():
+    if int(os.environ.get("RANK", "0")) != 0:          # under torch.distributed.run: one line, from rank 0
+        return 0
     print(json.dumps({
         "impl": "reference",
         "unavailable": "reference is a Makefile C++ project (no setup.py/pyproject; pip install fails) and its "
