@@ -90,7 +90,7 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
                     print(out)
     out = cuda_lib_path()
     if force or jobs or _newer(objs, out):
-        _run([nvcc, "-shared", "-o", str(out), *map(str, objs), "-lcuda"])
+        _link([nvcc, "-shared"], out, [*map(str, objs), "-lcuda"])
     return out
 
 
@@ -123,14 +123,26 @@ def build_core(force: bool = False) -> Path:
     out = core_lib_path()
     lib_objs = [o for o in objs if not o.name.endswith("_main.o")]
     if force or jobs or _newer(lib_objs, out):
-        _run([cxx, "-shared", "-pthread", "-o", str(out), *map(str, lib_objs), "-lz"])
+        _link([cxx, "-shared", "-pthread"], out, [*map(str, lib_objs), "-lz"])
     # the stand-alone linear-method binary (every node of a CPU deployment runs it)
     exe = PKG / "bin" / "psb_linear"
     exe.parent.mkdir(exist_ok=True)
     exe_objs = [o for o in objs if not o.name.startswith("core_bind") and o.name != "core_ps_main.o"]
     if force or jobs or _newer(exe_objs, exe):
-        _run([cxx, "-pthread", "-o", str(exe), *map(str, exe_objs), "-lz"])
+        _link([cxx, "-pthread"], exe, [*map(str, exe_objs), "-lz"])
     return out
+
+
+def _link(cmd: list, out: Path, inputs: list):
+    """Link into a temporary name and rename: a process that loads or executes ``out`` at the same
+    moment (two test runs side by side) sees the old file or the new one, never a half-written one."""
+    tmp = out.with_name(f"{out.name}.tmp.{os.getpid()}")
+    try:
+        _run([*cmd, "-o", str(tmp), *inputs])
+        os.replace(tmp, out)
+    finally:
+        if tmp.exists():
+            tmp.unlink()
 
 
 def build_sanitized_binary(kinds: str = "address,undefined") -> Path:
@@ -154,7 +166,7 @@ def build_sanitized_binary(kinds: str = "address,undefined") -> Path:
         list(ex.map(lambda so: _run([cxx, *flags, "-c", str(so[0]), "-o", str(so[1])], None), zip(sources, objs)))
     exe = PKG / "bin" / ("psb_linear_" + tag)
     exe.parent.mkdir(exist_ok=True)
-    _run([cxx, f"-fsanitize={kinds}", "-pthread", "-o", str(exe), *map(str, objs), "-lz"])
+    _link([cxx, f"-fsanitize={kinds}", "-pthread"], exe, [*map(str, objs), "-lz"])
     return exe
 
 
