@@ -9,11 +9,14 @@ Two shared objects are produced next to this file:
   DAG engine, van, postoffice, manager, CPU containers/filters/parsers) as a
   pybind11 module.
 
-Objects are rebuilt only when a source or header is newer than the output.
+A library is rebuilt when the contents of its sources, headers or compiler flags differ from those it
+was built from (a digest kept beside it in ``<library>.stamp``; file times do not survive a copy to
+another machine); single objects are recompiled when their source or a header is newer.
 ``nvcc`` cross-compiles without a GPU, so this also runs on CPU-only boxes.
 """
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -49,6 +52,24 @@ def _newer(src_list, out: Path) -> bool:
     return any(Path(s).stat().st_mtime > t for s in src_list)
 
 
+def _digest(files, extra: str = "") -> str:
+    h = hashlib.sha256(extra.encode())
+    for f in sorted(map(Path, files)):
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    return h.hexdigest()
+
+
+def _stale(files, out: Path, extra: str = "") -> bool:
+    """True if ``out`` is missing or was built from other contents than ``files`` (and ``extra``) now have."""
+    stamp = out.with_name(out.name + ".stamp")
+    return not out.exists() or not stamp.exists() or stamp.read_text().strip() != _digest(files, extra)
+
+
+def _mark(files, out: Path, extra: str = ""):
+    out.with_name(out.name + ".stamp").write_text(_digest(files, extra) + "\n")
+
+
 def _run(cmd, log: Path | None = None):
     p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if log is not None:
@@ -73,8 +94,8 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     headers = sorted(cu_dir.glob("*.cuh")) + sorted(cu_dir.glob("*.h"))
     sources = sorted(cu_dir.glob("*.cu"))
     out = cuda_lib_path()
-    if not force and not _newer(sources + headers, out):
-        return out  # the shipped library is current (e.g. on a box that received only the .so)
+    if not force and not _stale(sources + headers, out, " ".join(NVCC_FLAGS)):
+        return out  # the shipped library is current (e.g. on a box that received only the .so and its stamp)
     nvcc = _nvcc()
     objs, jobs = [], []
     for src in sources:
@@ -89,8 +110,9 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
                 if verbose:
                     print(out)
     out = cuda_lib_path()
-    if force or jobs or _newer(objs, out):
+    if force or jobs or _newer(objs, out) or not out.exists():
         _link([nvcc, "-shared"], out, [*map(str, objs), "-lcuda"])
+    _mark(sources + headers, out, " ".join(NVCC_FLAGS))
     return out
 
 
@@ -106,7 +128,7 @@ def build_core(force: bool = False) -> Path:
     # statically would put a second C++ runtime next to the one NumPy/PyTorch load.
     out = core_lib_path()
     exe = PKG / "bin" / "psb_linear"
-    if not force and not _newer(sources + headers, out) and exe.exists() and not _newer(sources + headers, exe):
+    if not force and not _stale(sources + headers, out) and exe.exists() and not _stale(sources + headers, exe):
         return out
     cxx = os.environ.get("PSB_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
     inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", str(core_dir)]
@@ -130,6 +152,8 @@ def build_core(force: bool = False) -> Path:
     exe_objs = [o for o in objs if not o.name.startswith("core_bind") and o.name != "core_ps_main.o"]
     if force or jobs or _newer(exe_objs, exe):
         _link([cxx, "-pthread"], exe, [*map(str, exe_objs), "-lz"])
+    _mark(sources + headers, out)
+    _mark(sources + headers, exe)
     return out
 
 
