@@ -185,7 +185,7 @@ void BindSystem(py::module& m) {
       .def_property("callback", [](Message& msg) { return msg.callback; },
                     [](Message& msg, py::object f) {
                       if (f.is_none()) { msg.callback = nullptr; return; }
-                      auto holder = std::make_shared<py::object>(f);
+                      auto holder = HoldPython(f);
                       msg.callback = [holder]() { py::gil_scoped_acquire g; (*holder)(); };
                     })
       .def("set_key", [](Message& msg, py::array_t<uint64_t, py::array::c_style | py::array::forcecast> k) {
@@ -249,7 +249,7 @@ void BindSystem(py::module& m) {
       .def("received_bytes", [](Postoffice& p) { return p.manager().van().received_bytes(); })
       .def("statistic", [](Postoffice& p) { return p.manager().van().Statistic(); })
       .def("add_node_failure_handler", [](Postoffice& p, py::function f) {
-        auto holder = std::make_shared<py::object>(f);
+        auto holder = HoldPython(f);
         p.manager().AddNodeFailureHandler([holder](const NodeID& id) { py::gil_scoped_acquire g; (*holder)(id); });
       })
       .def("node_disconnected", [](Postoffice& p, const NodeID& id) { p.manager().NodeDisconnected(id); },
@@ -319,14 +319,14 @@ void BindSystem(py::module& m) {
         std::vector<SArray<float>> vals;
         for (auto& v : values) vals.push_back(FromNumpy<float>(v));
         std::function<void()> f;
-        if (!cb.is_none()) { auto h = std::make_shared<py::object>(cb); f = [h]() { py::gil_scoped_acquire g; (*h)(); }; }
+        if (!cb.is_none()) { auto h = HoldPython(cb); f = [h]() { py::gil_scoped_acquire g; (*h)(); }; }
         py::gil_scoped_release r;
         return kv.Push(t, k, vals, f);
       }, py::arg("task"), py::arg("keys"), py::arg("values") = std::vector<py::array_t<float>>(), py::arg("callback") = py::none())
       .def("pull", [](KVVectorF& kv, const Task& t, py::array_t<uint64_t, py::array::c_style | py::array::forcecast> keys, py::object cb) {
         SArray<uint64_t> k = FromNumpy<uint64_t>(keys);
         std::function<void()> f;
-        if (!cb.is_none()) { auto h = std::make_shared<py::object>(cb); f = [h]() { py::gil_scoped_acquire g; (*h)(); }; }
+        if (!cb.is_none()) { auto h = HoldPython(cb); f = [h]() { py::gil_scoped_acquire g; (*h)(); }; }
         py::gil_scoped_release r;
         return kv.Pull(t, k, f);
       }, py::arg("task"), py::arg("keys"), py::arg("callback") = py::none())
@@ -372,7 +372,7 @@ void BindSystem(py::module& m) {
       })
       .def("pull", [](KVLayerSum& l, const Task& t, py::array_t<float, py::array::c_style> out, py::object cb) {
         std::function<void()> f;
-        if (!cb.is_none()) { auto h = std::make_shared<py::object>(cb); f = [h]() { py::gil_scoped_acquire g; (*h)(); }; }
+        if (!cb.is_none()) { auto h = HoldPython(cb); f = [h]() { py::gil_scoped_acquire g; (*h)(); }; }
         float* p = out.mutable_data();
         size_t n = out.size();
         py::gil_scoped_release r;

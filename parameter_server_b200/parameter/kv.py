@@ -125,10 +125,21 @@ class DeviceKVMap:
     def push(self, keys, values, ts: Optional[int] = None, wait: Optional[List[int]] = None, callback=None,
              channel: int = 0) -> int:
         """Push sorted unique uint64 keys with one value (``k`` values: an ``(n, k)`` array) each into
-        ``channel``; returns the timestamp."""
+        ``channel``; returns the timestamp. Both halves of the round are enqueued here: the worker half
+        (values into the owners' inboxes) and this rank's owner half (merge of the round)."""
         ts = self._stamp(ts)
-        k = self._as_keys(keys, self.dev)
         self._begin(wait)
+        rnd = self.push_only(keys, values)
+        self._push_round_of[ts] = rnd
+        self.apply_round(rnd, channel=channel)
+        self._finish(ts, callback)
+        return ts
+
+    def push_only(self, keys, values) -> int:
+        """The worker half of a push round: the values go into the owners' inboxes. Returns the round.
+        The owner half is :meth:`apply_round`; :meth:`push` does both, the node-level customers
+        (``parameter/kv_nodes.py``) let the server node decide when the round is merged."""
+        k = self._as_keys(keys, self.dev)
         with torch.cuda.stream(self.stream):
             b = self._buffer(k)
             n = k.numel()
@@ -138,13 +149,15 @@ class DeviceKVMap:
                 b.grad[:n * self.k].copy_(v)
             rnd = self._round
             self._round += 1
-            self._push_round_of[ts] = rnd
             self.plane.push(b, rnd, with_gradient=False, stream=self.stream)
-            # buffered: the round is consumed (its ring slot becomes reusable later) but not merged
+        return rnd
+
+    def apply_round(self, rnd: int, channel: int = 0):
+        """The owner half of push round ``rnd``: merge what every live worker sent (a buffered container
+        only consumes the round: its ring slot becomes reusable later, the values stay unmerged)."""
+        with torch.cuda.stream(self.stream):
             self.plane.apply(rnd, channel=channel, stream=self.stream,
                              opt=OptimizerConfig(algo="keep") if self.buffer_value else None)
-        self._finish(ts, callback)
-        return ts
 
     def buffer(self, ts: int):
         """What this rank, as an owner, received in the push with timestamp ``ts``: one
