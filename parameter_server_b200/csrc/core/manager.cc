@@ -241,6 +241,16 @@ void Manager::RemoveNode(const NodeID& node_id) {
     for (auto& c : customers_) c.second->executor()->RemoveNode(node);
   }
   if (node_assigner_) node_assigner_->remove(node);
+  if (!IsScheduler()) {
+    // A node that did not see the connection drop itself learns of the loss from the scheduler's
+    // REMOVE_NODE: its failure handlers run once per lost node, whichever way the news came.
+    std::vector<NodeFailureHandler> hs;
+    {
+      Lock l(nodes_mu_);
+      if (failure_notified_.insert(node_id).second) hs = node_failure_handlers_;
+    }
+    for (auto& h : hs) h(node_id);
+  }
   if (IsScheduler()) {
     Task task = NewControlTask(Control::REMOVE_NODE);
     task.ctrl.node.push_back(node);
@@ -256,7 +266,7 @@ void Manager::NodeDisconnected(const NodeID& node_id) {
   {
     Lock l(nodes_mu_);
     if (nodes_.find(node_id) == nodes_.end() && node_id != van_.scheduler().id) return;
-    hs = node_failure_handlers_;
+    if (failure_notified_.insert(node_id).second) hs = node_failure_handlers_;
   }
   PS_LOG(WARN) << my_node().id << ": node " << node_id << " is disconnected";
   for (auto& h : hs) h(node_id);

@@ -3,6 +3,7 @@
 // orderly shutdown (READY_TO_EXIT / EXIT) and node-failure handling
 // (REMOVE_NODE). Counterpart of system/manager.h:13-93, system/manager.cc:26-333.
 #pragma once
+#include <set>
 #include "assigner.h"
 #include "env.h"
 #include "van.h"
@@ -78,6 +79,7 @@ class Manager {
   std::atomic<bool> done_{false};
   bool in_exit_ = false;
   std::vector<NodeFailureHandler> node_failure_handlers_;
+  std::set<NodeID> failure_notified_;   // lost nodes whose handlers have run (guarded by nodes_mu_)
 
   std::mutex customer_mu_;
   std::condition_variable customer_cv_;

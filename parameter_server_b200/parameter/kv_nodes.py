@@ -64,6 +64,13 @@ class KVServerCustomer(core.Customer):
         self._held: Dict[int, list] = {}              # round -> push requests not yet finished
         self.applied_rounds = 0
         self.log: List[tuple] = []                    # (kind, sender, time) in processing order
+        # the manager tells every node when a node has left (system/manager.cc:250-270): a lost worker's
+        # rounds are not waited for any more, and the data plane skips it as a source
+        po.add_node_failure_handler(self._node_lost)
+
+    def _node_lost(self, node_id: str):
+        if node_id in self._pushed:
+            self.worker_lost(node_id, rank=int(node_id[1:]) if node_id[1:].isdigit() else None)
 
     def process_request(self, m):
         kind = bytes(m.task.msg)[:4]

@@ -90,8 +90,7 @@ def test_callback_fires_once_all_servers_answered_and_lost_worker_is_not_waited_
         tp = w0.push([5], [1.0], callback=lambda: fired.append("pushed"))
         time.sleep(0.3)
         assert fired == []                            # W1's push of the round is missing
-        for s in cl.apps("S"):
-            s.kv.worker_lost("W1", rank=1)            # what the node-lost event of the manager drives
+        cl.nodes["H"].node_disconnected("W1")         # the scheduler learns that W1 is gone and tells every node
         w0.wait(tp)
         assert fired == ["pushed"]
         assert sorted(e for e in events if e[0] == "apply") == [("apply", "S0", 0), ("apply", "S1", 0)]
