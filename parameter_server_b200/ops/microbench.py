@@ -78,22 +78,25 @@ def bench_localize(args):
     b = LocalBatch(rows, nnz, 1, dev)
     bounds = torch.tensor([0, -1], dtype=torch.int64, device=dev)
     kw = dict(fixed_z=z, hash_seed=0, hash_bits=args.key_bits % 64, method=args.method)
-    st = torch.cuda.current_stream()
+    st = torch.cuda.Stream(device=dev)          # a graph cannot be captured on the default stream
 
     def run(i):
         ids, y = pool[i % len(pool)]
         if args.graph:
             b.localize_replayed(ids, y, bounds, stream=st, **kw)
         else:
-            b.localize(ids, y, bounds, **kw)
-    for i in range(args.warmup):
-        run(i)
+            b.localize(ids, y, bounds, stream=st, **kw)
+    with torch.cuda.stream(st):
+        for i in range(max(args.warmup, 2 * len(pool) if args.graph else 0)):   # every minibatch through its capture
+            run(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.iters):
-        run(i)
-    e1.record(); torch.cuda.synchronize()
+    with torch.cuda.stream(st):
+        e0.record(st)
+        for i in range(args.iters):
+            run(i)
+        e1.record(st)
+    torch.cuda.synchronize()
     _lib_check = int(b.status.item())
     print(json.dumps({"kernel": "localize", "rows": rows, "z": z, "nnz": nnz, "key_bits": args.key_bits, "method": args.method,
                       "graph": bool(args.graph), "unique": int(b.n_unique.item()), "fell_back_to_sort": int(b.gate.item()),
