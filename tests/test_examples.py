@@ -1,0 +1,38 @@
+"""The tutorial under examples/linear runs as written: data generator, online and batch training and the
+two evaluations with the shipped configuration files, CPU nodes as local processes."""
+import glob
+import os
+import re
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CONF = os.path.join(ROOT, "examples", "linear", "ctr")
+
+
+def _run(conf, ns, nw):
+    from parameter_server_b200 import _build
+    from parameter_server_b200.system.cluster import launch_local_processes
+    _build.build_core()
+    exe = os.path.join(ROOT, "parameter_server_b200", "bin", "psb_linear")
+    out = launch_local_processes(ns, nw, [exe, "-app_file", os.path.join(CONF, conf)], timeout=240)
+    assert all(p.returncode == 0 for p in out.values()), {k: (p.returncode, p.stdout[-400:]) for k, p in out.items()}
+    return out["H"].stdout
+
+
+def test_tutorial_configs_train_and_evaluate(tmp_path, monkeypatch):
+    monkeypatch.chdir(tmp_path)
+    os.makedirs("model")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "linear", "make_data.py"), "--files", "2",
+                        "--rows", "2500", "--nnz", "16", "--features", "2000"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert len(glob.glob("data/ctr/train/part-*")) == 2 and len(glob.glob("data/ctr/test/part-*")) == 1
+    _run("online_l1lr.conf", 2, 2)
+    assert len(glob.glob("model/ctr_online_S*")) == 2
+    ev = _run("eval_online.conf", 1, 1)
+    auc = float(re.search(r"auc[:= ]+([0-9.]+)", ev, re.I).group(1))
+    assert auc > 0.6, ev[-500:]
+    _run("batch_l1lr.conf", 2, 2)
+    assert len(glob.glob("model/ctr_batch_S*")) == 2
+    ev = _run("eval_batch.conf", 1, 1)
+    assert float(re.search(r"auc[:= ]+([0-9.]+)", ev, re.I).group(1)) > 0.6, ev[-500:]
