@@ -36,3 +36,28 @@ def test_tutorial_configs_train_and_evaluate(tmp_path, monkeypatch):
     assert len(glob.glob("model/ctr_batch_S*")) == 2
     ev = _run("eval_batch.conf", 1, 1)
     assert float(re.search(r"auc[:= ]+([0-9.]+)", ev, re.I).group(1)) > 0.6, ev[-500:]
+
+
+def test_libsvm_and_criteo_examples(tmp_path, monkeypatch):
+    """The rcv1-style (LIBSVM, real values) and criteo-style (click-log lines, one feature group per field)
+    configurations train and evaluate on generated data of their formats."""
+    global CONF
+    monkeypatch.chdir(tmp_path)
+    os.makedirs("model")
+    gen = os.path.join(ROOT, "examples", "linear", "make_data.py")
+    for fmt, out in (("libsvm", "data/rcv1"), ("criteo", "data/criteo")):
+        r = subprocess.run([sys.executable, gen, "--format", fmt, "--out", out, "--files", "2", "--rows", "2000", "--nnz", "16",
+                            "--features", "2000"], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+    keep = CONF
+    try:
+        CONF = os.path.join(ROOT, "examples", "linear", "rcv1")
+        _run("online_l1lr.conf", 2, 2)
+        assert float(re.search(r"auc[:= ]+([0-9.]+)", _run("eval_online.conf", 1, 1), re.I).group(1)) > 0.6
+        _run("batch_l1lr.conf", 2, 2)
+        assert float(re.search(r"auc[:= ]+([0-9.]+)", _run("eval_batch.conf", 1, 1), re.I).group(1)) > 0.6
+        CONF = os.path.join(ROOT, "examples", "linear", "criteo")
+        _run("batch_l1lr.conf", 2, 2)
+        assert float(re.search(r"auc[:= ]+([0-9.]+)", _run("eval_batch.conf", 1, 1), re.I).group(1)) > 0.6
+    finally:
+        CONF = keep
