@@ -61,3 +61,17 @@ def test_libsvm_and_criteo_examples(tmp_path, monkeypatch):
         assert float(re.search(r"auc[:= ]+([0-9.]+)", _run("eval_batch.conf", 1, 1), re.I).group(1)) > 0.6
     finally:
         CONF = keep
+
+
+def test_kv_api_examples():
+    """The two small programs under examples/kv run as a user would run them."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "examples", "kv", "hello.py")],
+                         capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.count("hello world") == 3 and "every server has answered" in out.stdout
+    assert "last response came from S1" in out.stdout
+    out = subprocess.run([sys.executable, os.path.join(root, "examples", "kv", "kv_vector.py")],
+                         capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    assert "pulled [3.0, 6.0, 9.0]" in out.stdout
