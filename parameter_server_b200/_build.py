@@ -157,6 +157,39 @@ def build_core(force: bool = False) -> Path:
     return out
 
 
+def build_static(force: bool = False):
+    """``lib/libpsb.a`` (the host runtime: util, data, system, filter, learner, parameter and the linear
+    methods) and ``lib/libpsbmain.a`` (the ``main`` of a program that defines only ``PS::CreateServerNode``
+    and ``PS::WorkerNodeMain``), for C++ programs that link the runtime the way the reference's users link
+    ``build/libps.a`` and ``build/libpsmain.a`` (``Makefile:28-47``). Headers are ``csrc/core/*.h``."""
+    build_core(force=force)
+    core_dir = CSRC / "core"
+    libdir = PKG / "lib"
+    libdir.mkdir(exist_ok=True)
+    objs = [OBJ / ("core_" + s.stem + ".o") for s in sorted(core_dir.glob("*.cc"))
+            if not s.name.startswith("bind") and not s.stem.endswith("_main")]
+    lib, main_lib = libdir / "libpsb.a", libdir / "libpsbmain.a"
+    if force or _newer(objs, lib):
+        _archive(lib, objs)
+    main_obj = OBJ / "simple_main.o"
+    if force or _newer([core_dir / "ps_main.cc", *core_dir.glob("*.h")], main_obj) or _newer([main_obj], main_lib):
+        cxx = os.environ.get("PSB_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
+        _run([cxx, "-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread", "-DPSB_SIMPLE_MAIN", "-I", str(core_dir),
+              "-c", str(core_dir / "ps_main.cc"), "-o", str(main_obj)])
+        _archive(main_lib, [main_obj])
+    return lib, main_lib
+
+
+def _archive(out: Path, objs: list):
+    tmp = out.with_name(f"{out.name}.tmp.{os.getpid()}")
+    try:
+        _run(["ar", "crs", str(tmp), *map(str, objs)])
+        os.replace(tmp, out)
+    finally:
+        if tmp.exists():
+            tmp.unlink()
+
+
 def _link(cmd: list, out: Path, inputs: list):
     """Link into a temporary name and rename: a process that loads or executes ``out`` at the same
     moment (two test runs side by side) sees the old file or the new one, never a half-written one."""
@@ -204,6 +237,13 @@ if __name__ == "__main__":
     san = [a for a in sys.argv if a.startswith("--sanitize")]
     if san:
         print(build_sanitized_binary(san[0].split("=", 1)[1] if "=" in san[0] else "address,undefined"))
+        sys.exit(0)
+    if "--static" in sys.argv:
+        for p in build_static(force="--force" in sys.argv):
+            print(p)
+        sys.exit(0)
+    if "--core" in sys.argv:
+        print(build_core(force="--force" in sys.argv))
         sys.exit(0)
     paths = build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
     for p in paths:

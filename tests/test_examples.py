@@ -75,3 +75,21 @@ def test_kv_api_examples():
                          capture_output=True, text=True, timeout=120)
     assert out.returncode == 0, out.stderr
     assert "pulled [3.0, 6.0, 9.0]" in out.stdout
+
+
+def test_cpp_program_links_static_runtime(tmp_path):
+    """A C++ program that defines only CreateServerNode / WorkerNodeMain links against lib/libpsb.a and
+    lib/libpsbmain.a and runs as scheduler + 2 servers + 2 workers over TCP."""
+    from parameter_server_b200 import _build
+    from parameter_server_b200.system.cluster import launch_local_processes
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib, main_lib = _build.build_static()
+    exe = tmp_path / "kv_sum"
+    cxx = os.environ.get("PSB_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
+    subprocess.run([cxx, "-O1", "-std=c++17", "-pthread", "-I", os.path.join(root, "parameter_server_b200", "csrc", "core"),
+                    os.path.join(root, "examples", "cpp", "kv_sum.cc"), str(main_lib), str(lib), "-lz", "-o", str(exe)],
+                   check=True, timeout=600)
+    out = launch_local_processes(2, 2, [str(exe)], timeout=120)
+    assert all(p.returncode == 0 for p in out.values()), {k: (p.returncode, p.stdout[-300:]) for k, p in out.items()}
+    for w in ("W0", "W1"):
+        assert f"{w} pulled 3 6 9" in out[w].stdout
