@@ -19,7 +19,7 @@ examples: lib $(EXAMPLES)   ## the C++ programs under examples/cpp, linked again
 
 build/%: examples/cpp/%.cc $(LIBDIR)/libpsb.a $(LIBDIR)/libpsbmain.a
 	@mkdir -p build
-	$(CXX) -O2 -std=c++17 -Wall -pthread -I$(CORE) $< $(LIBDIR)/libpsbmain.a $(LIBDIR)/libpsb.a -lz -o $@
+	$(CXX) -O2 -std=c++17 -Wall -pthread -I$(CORE) $< $(if $(shell grep -l "^int main" $<),,$(LIBDIR)/libpsbmain.a) $(LIBDIR)/libpsb.a -lz -o $@
 
 test:                 ## everything that needs no GPU
 	$(PY) -m pytest tests -q -m "not gpu"

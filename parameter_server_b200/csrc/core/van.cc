@@ -17,6 +17,7 @@ std::mutex Van::hub_mu_;
 std::map<std::string, std::shared_ptr<Van::InProcEndpoint>> Van::hub_;
 
 static const uint32_t kFrameMagic = 0x50534231;  // "PSB1"
+static const int kSocketBufferBytes = 4 << 20;    // asked of the kernel, which caps it at its own limit
 
 static bool WriteAll(int fd, const void* p, size_t n) {
   const char* c = (const char*)p;
@@ -105,6 +106,10 @@ void Van::Init(const Node& my_node, const Node& scheduler, bool local_ipc) {
       listen_fd_ = socket(AF_INET, SOCK_STREAM, 0);
       int one = 1;
       setsockopt(listen_fd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+      // accepted streams inherit this: room for a few whole messages, so that a sender's write returns
+      // while the poll thread is still busy with another peer
+      int rcv = kSocketBufferBytes;
+      setsockopt(listen_fd_, SOL_SOCKET, SO_RCVBUF, &rcv, sizeof(rcv));
       sockaddr_in addr; memset(&addr, 0, sizeof(addr));
       addr.sin_family = AF_INET;
       addr.sin_addr.s_addr = htonl(INADDR_ANY);
@@ -168,6 +173,8 @@ bool Van::Connect(const Node& node) {
       if (connect(fd, (sockaddr*)&addr, sizeof(addr)) == 0) break;
     } else {
       fd = socket(AF_INET, SOCK_STREAM, 0);
+      int snd = kSocketBufferBytes;
+      setsockopt(fd, SOL_SOCKET, SO_SNDBUF, &snd, sizeof(snd));
       sockaddr_in addr; memset(&addr, 0, sizeof(addr));
       addr.sin_family = AF_INET;
       addr.sin_port = htons((uint16_t)node.port);

@@ -77,19 +77,28 @@ def test_kv_api_examples():
     assert "pulled [3.0, 6.0, 9.0]" in out.stdout
 
 
-def test_cpp_program_links_static_runtime(tmp_path):
-    """A C++ program that defines only CreateServerNode / WorkerNodeMain links against lib/libpsb.a and
-    lib/libpsbmain.a and runs as scheduler + 2 servers + 2 workers over TCP."""
+def test_cpp_programs_link_static_runtime(tmp_path):
+    """C++ programs link against lib/libpsb.a (and lib/libpsbmain.a when they define only CreateServerNode /
+    WorkerNodeMain) and run as scheduler + 2 servers + 2 workers over TCP."""
     from parameter_server_b200 import _build
     from parameter_server_b200.system.cluster import launch_local_processes
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     lib, main_lib = _build.build_static()
-    exe = tmp_path / "kv_sum"
     cxx = os.environ.get("PSB_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
-    subprocess.run([cxx, "-O1", "-std=c++17", "-pthread", "-I", os.path.join(root, "parameter_server_b200", "csrc", "core"),
-                    os.path.join(root, "examples", "cpp", "kv_sum.cc"), str(main_lib), str(lib), "-lz", "-o", str(exe)],
-                   check=True, timeout=600)
-    out = launch_local_processes(2, 2, [str(exe)], timeout=120)
+
+    def compile_(name, libs):
+        exe = tmp_path / name
+        subprocess.run([cxx, "-O1", "-std=c++17", "-pthread", "-I", os.path.join(root, "parameter_server_b200", "csrc", "core"),
+                        os.path.join(root, "examples", "cpp", name + ".cc"), *map(str, libs), "-lz", "-o", str(exe)],
+                       check=True, timeout=600)
+        return str(exe)
+
+    out = launch_local_processes(2, 2, [compile_("kv_sum", [main_lib, lib])], timeout=120)
     assert all(p.returncode == 0 for p in out.values()), {k: (p.returncode, p.stdout[-300:]) for k, p in out.items()}
     for w in ("W0", "W1"):
         assert f"{w} pulled 3 6 9" in out[w].stdout
+    out = launch_local_processes(2, 2, [compile_("network_perf", [lib]), "-n=20", "-data_size=200"], timeout=120)
+    assert all(p.returncode == 0 for p in out.values()), {k: (p.returncode, p.stdout[-300:]) for k, p in out.items()}
+    for w in ("W0", "W1"):
+        m = re.search(r"packet size 200 KB to 2 servers, 20 rounds, throughput ([0-9.]+) MB/s", out[w].stdout)
+        assert m and float(m.group(1)) > 1.0, out[w].stdout
