@@ -230,6 +230,7 @@ def build_sanitized_binary(kinds: str = "address,undefined") -> Path:
 def build_all(force: bool = False, verbose: bool = False):
     a = build_cuda(force=force, verbose=verbose)
     b = build_core(force=force)
+    build_static()
     return a, b
 
 
