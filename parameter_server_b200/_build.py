@@ -162,21 +162,25 @@ def build_static(force: bool = False):
     methods) and ``lib/libpsbmain.a`` (the ``main`` of a program that defines only ``PS::CreateServerNode``
     and ``PS::WorkerNodeMain``), for C++ programs that link the runtime the way the reference's users link
     ``build/libps.a`` and ``build/libpsmain.a`` (``Makefile:28-47``). Headers are ``csrc/core/*.h``."""
-    build_core(force=force)
     core_dir = CSRC / "core"
     libdir = PKG / "lib"
+    lib, main_lib = libdir / "libpsb.a", libdir / "libpsbmain.a"
+    inputs = sorted(core_dir.glob("*.cc")) + sorted(core_dir.glob("*.h"))
+    # staleness by the digest of the sources, as for the shared objects: a copy of the tree that carries the
+    # archives but not the object files (they are intermediate) must find the archives up to date
+    if not force and lib.exists() and main_lib.exists() and not _stale(inputs, lib):
+        return lib, main_lib
     libdir.mkdir(exist_ok=True)
     objs = [OBJ / ("core_" + s.stem + ".o") for s in sorted(core_dir.glob("*.cc"))
             if not s.name.startswith("bind") and not s.stem.endswith("_main")]
-    lib, main_lib = libdir / "libpsb.a", libdir / "libpsbmain.a"
-    if force or _newer(objs, lib):
-        _archive(lib, objs)
+    build_core(force=force or not all(o.exists() for o in objs))
+    _archive(lib, objs)
     main_obj = OBJ / "simple_main.o"
-    if force or _newer([core_dir / "ps_main.cc", *core_dir.glob("*.h")], main_obj) or _newer([main_obj], main_lib):
-        cxx = os.environ.get("PSB_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
-        _run([cxx, "-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread", "-DPSB_SIMPLE_MAIN", "-I", str(core_dir),
-              "-c", str(core_dir / "ps_main.cc"), "-o", str(main_obj)])
-        _archive(main_lib, [main_obj])
+    cxx = os.environ.get("PSB_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
+    _run([cxx, "-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread", "-DPSB_SIMPLE_MAIN", "-I", str(core_dir),
+          "-c", str(core_dir / "ps_main.cc"), "-o", str(main_obj)])
+    _archive(main_lib, [main_obj])
+    _mark(inputs, lib)
     return lib, main_lib
 
 
