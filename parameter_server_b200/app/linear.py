@@ -30,7 +30,8 @@ from ..system import core
 def _files(conf_data) -> List[str]:
     pats = conf_data.get("file", [])
     pats = pats if isinstance(pats, list) else [pats]
-    return list(core.search_files(pats))
+    hdfs = conf_data.get("hdfs")          # data { hdfs { home ugi namenode } }: the files are read through `hadoop fs`
+    return list(core.search_files(pats, hdfs if isinstance(hdfs, dict) else None))
 
 
 def _penalty(conf):

@@ -123,9 +123,19 @@ void BindApp(py::module& m) {
   m.def("text_to_records", [](const std::vector<std::string>& files, const std::string& text, const std::string& out) {
     return textToRecords(MakeData(files, "TEXT", text, false, -1), out);
   });
-  m.def("search_files", [](const std::vector<std::string>& patterns) {
-    DataConfig d; d.file = patterns; return searchFiles(d).file;
-  });
+  m.def("search_files", [](const std::vector<std::string>& patterns, py::object hdfs) {
+    DataConfig d; d.file = patterns;
+    if (!hdfs.is_none()) {
+      py::dict h = hdfs.cast<py::dict>();
+      auto get = [&](const char* k) { return h.contains(k) ? py::str(h[k]).cast<std::string>() : std::string(); };
+      d.has_hdfs = true; d.hdfs.home = get("home"); d.hdfs.ugi = get("ugi"); d.hdfs.namenode = get("namenode");
+    }
+    return searchFiles(d).file;
+  }, py::arg("patterns"), py::arg("hdfs") = py::none(),
+     "files matching the patterns (regular expression in the file part); with hdfs={home, ugi, namenode} the "
+     "patterns name HDFS files, the names returned start with hdfs:// and every reader of this process opens "
+     "such names through `hadoop fs -cat`");
+  m.def("hadoop_fs", []() { return currentHadoopFS(); }, "the command prefix used for hdfs:// files");
 
   m.def("localize", [](py::array_t<uint64_t, py::array::c_style | py::array::forcecast> offset,
                        py::array_t<uint64_t, py::array::c_style | py::array::forcecast> index, int threads) {

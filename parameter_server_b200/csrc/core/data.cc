@@ -297,6 +297,13 @@ static bool shellSafe(const std::string& s) {
   return true;
 }
 
+// the same for a whole command line: blanks separate its words
+static bool shellSafeCommand(const std::string& s) {
+  for (char c : s)
+    if (!(c == ' ' || isalnum((unsigned char)c) || strchr("._-/:?=%+~,@", c))) return false;
+  return true;
+}
+
 File* File::open(const std::string& name, const char* flag) {
   if (name == "stdin") return new File(stdin, nullptr, name, true);
   if (name == "stdout") return new File(stdout, nullptr, name, true);
@@ -306,6 +313,13 @@ File* File::open(const std::string& name, const char* flag) {
     return pipe ? new File(pipe, nullptr, name, false, true) : nullptr;
   }
   bool gz = name.size() > 3 && name.compare(name.size() - 3, 3, ".gz") == 0;
+  if (hdfsfile(name)) {
+    std::string cmd = currentHadoopFS() + " -cat " + name;
+    if (flag[0] != 'r' || !shellSafeCommand(cmd)) return nullptr;   // read only, like the reference
+    if (gz) cmd += " | gunzip";
+    FILE* pipe = popen(cmd.c_str(), "r");
+    return pipe ? new File(pipe, nullptr, name, false, true) : nullptr;
+  }
   if (gz) {
     gzFile g = gzopen(name.c_str(), flag);
     return g ? new File(nullptr, g, name, false) : nullptr;
@@ -383,8 +397,46 @@ std::string removeExtension(const std::string& file) {
   size_t p = file.find_last_of('.');
   return p == std::string::npos ? file : file.substr(0, p);
 }
-std::string hadoopFS(const std::string& namenode) {
-  return namenode.empty() ? "hadoop fs" : "hadoop fs -D fs.default.name=" + namenode;
+bool hdfsfile(const std::string& name) { return name.compare(0, 7, "hdfs://") == 0 && name.size() > 7; }
+std::string hadoopFS(const HDFSConfig& conf) {
+  std::string home = conf.home;
+  if (home.empty()) if (const char* env = getenv("HADOOP_HOME")) home = env;
+  std::string cmd = home.empty() ? "hadoop fs" : home + "/bin/hadoop fs";
+  if (!conf.namenode.empty()) cmd += " -D fs.default.name=" + conf.namenode;
+  if (!conf.ugi.empty()) cmd += " -D hadoop.job.ugi=" + conf.ugi;
+  return cmd;
+}
+namespace {
+std::mutex hadoop_mu;
+std::string hadoop_cmd;   // empty: not set, the default prefix is used
+}  // namespace
+void setHadoopFS(const HDFSConfig& conf) {
+  std::lock_guard<std::mutex> l(hadoop_mu);
+  hadoop_cmd = hadoopFS(conf);
+}
+std::string currentHadoopFS() {
+  std::lock_guard<std::mutex> l(hadoop_mu);
+  return hadoop_cmd.empty() ? hadoopFS(HDFSConfig()) : hadoop_cmd;
+}
+std::vector<std::string> readFilenamesInHdfsDirectory(const std::string& dir) {
+  std::vector<std::string> out;
+  const std::string cmd = currentHadoopFS() + " -ls " + dir;
+  if (!shellSafeCommand(cmd)) return out;
+  FILE* pipe = popen(cmd.c_str(), "r");
+  if (!pipe) return out;
+  // permissions, replication, owner, group, size, date, time, name: anything else (the "Found n items"
+  // line) is skipped, and so are directories
+  char line[10000];
+  while (fgets(line, sizeof(line), pipe)) {
+    std::vector<std::string> col;
+    std::istringstream in(line);
+    for (std::string w; in >> w;) col.push_back(w);
+    if (col.size() != 8 || col[0][0] == 'd') continue;
+    out.push_back(col.back());
+  }
+  pclose(pipe);
+  std::sort(out.begin(), out.end());
+  return out;
 }
 
 void FileLineReader::Reload() {
@@ -404,7 +456,24 @@ void FileLineReader::Reload() {
 DataConfig searchFiles(const DataConfig& config) {
   DataConfig out = config;
   out.file.clear();
-  for (const std::string& pat : config.file) {
+  if (config.has_hdfs) setHadoopFS(config.hdfs);
+  for (const std::string& given : config.file) {
+    // with an `hdfs` block plain paths name HDFS files: "/a/b" becomes "hdfs:///a/b", a URI that hadoop takes
+    const std::string pat = config.has_hdfs && !hdfsfile(given) ? "hdfs://" + given : given;
+    if (hdfsfile(pat)) {
+      const std::string dir = getPath(pat);
+      std::regex re;
+      try { re = std::regex(getFilename(pat)); } catch (const std::regex_error&) { continue; }
+      size_t found = 0;
+      for (const std::string& f : readFilenamesInHdfsDirectory(dir)) {
+        if (!std::regex_match(getFilename(f), re)) continue;
+        // `-ls` prints full paths, with or without the scheme
+        out.file.push_back(hdfsfile(f) ? f : "hdfs://" + f);
+        ++found;
+      }
+      if (!found) out.file.push_back(pat);      // no listing: take the name as a file
+      continue;
+    }
     if (File::exists(pat)) { out.file.push_back(pat); continue; }
     if (s3file(pat)) {
       // the bucket's listing for the directory part, objects whose file name matches the pattern

@@ -186,7 +186,17 @@ bool createDir(const std::string& dir);
 std::string getPath(const std::string& full);      // directory part
 std::string getFilename(const std::string& full);  // file part
 std::string removeExtension(const std::string& file);
-std::string hadoopFS(const std::string& hdfs_namenode);  // "hadoop fs -D fs.default.name=..." command prefix
+// Files in HDFS are named "hdfs://[namenode]/path" and are read through a pipe from `hadoop fs -cat`
+// (util/file.cc:91-112); directories are listed with `hadoop fs -ls` (util/file.cc:350-373).
+bool hdfsfile(const std::string& name);
+// The command prefix "<home>/bin/hadoop fs [-D fs.default.name=..] [-D hadoop.job.ugi=..]"; an empty home
+// means $HADOOP_HOME, else `hadoop` from the PATH (util/file.cc:296-302).
+std::string hadoopFS(const HDFSConfig& conf);
+// The prefix that File::open and the directory listing use for hdfs:// names; searchFiles sets it from a
+// DataConfig that has an `hdfs` block. One setting per process, as the job has one file system.
+void setHadoopFS(const HDFSConfig& conf);
+std::string currentHadoopFS();
+std::vector<std::string> readFilenamesInHdfsDirectory(const std::string& dir);   // full names, files only
 
 class FileLineReader {
  public:

@@ -79,6 +79,10 @@ inline DataConfig ParseData(const TextNode& n) {
   d.max_num_lines_per_file = (int)n.integer("max_num_lines_per_file", -1);
   d.shuffle = n.boolean("shuffle", false);
   d.replica = (int)n.integer("replica", 1);
+  if (const TextNode* h = n.child("hdfs")) {
+    d.has_hdfs = true;
+    d.hdfs.home = h->str("home", ""); d.hdfs.ugi = h->str("ugi", ""); d.hdfs.namenode = h->str("namenode", "");
+  }
   if (const TextNode* r = n.child("range")) { d.has_range = true; d.range = Range<Key>(r->integer("begin"), r->integer("end")); }
   return d;
 }

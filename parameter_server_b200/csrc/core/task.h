@@ -175,6 +175,13 @@ struct ParamCall {
 };
 
 // ---------------------------------------------------------------- data / workload
+// Where the hadoop command is and how to reach the file system (data/proto/data.proto:46-50).
+struct HDFSConfig {
+  std::string home;      // HADOOP_HOME
+  std::string ugi;       // hadoop.job.ugi, "user,passwd"
+  std::string namenode;  // fs.default.name
+};
+
 struct DataConfig {
   enum DataFormat { BIN = 1, PROTO = 2, TEXT = 3 };
   enum TextFormat { DENSE = 1, SPARSE = 2, SPARSE_BINARY = 3, ADFEA = 4, LIBSVM = 5, TERAFEA = 6, VW = 7, CRITEO = 8 };
@@ -187,10 +194,12 @@ struct DataConfig {
   bool shuffle = false;
   bool has_range = false; Range<Key> range;
   int replica = 1;
+  bool has_hdfs = false; HDFSConfig hdfs;   // the files are in HDFS and are read through `hadoop fs`
   void Save(Writer& w) const {
     w.U8(format); w.U8(text); w.U64(file.size()); for (auto& f : file) w.Str(f);
     w.Bool(ignore_feature_group); w.I64(max_num_files_per_worker); w.I64(max_num_lines_per_file);
     w.Bool(shuffle); w.Bool(has_range); SaveRange(w, range); w.I64(replica);
+    w.Bool(has_hdfs); w.Str(hdfs.home); w.Str(hdfs.ugi); w.Str(hdfs.namenode);
   }
   void Load(Reader& r) {
     format = (DataFormat)r.U8(); text = (TextFormat)r.U8(); uint64_t n = r.U64(); file.clear();
@@ -198,6 +207,7 @@ struct DataConfig {
     ignore_feature_group = r.Bool(); max_num_files_per_worker = (int)r.I64();
     max_num_lines_per_file = (int)r.I64(); shuffle = r.Bool(); has_range = r.Bool();
     range = LoadRange(r); replica = (int)r.I64();
+    has_hdfs = r.Bool(); hdfs.home = r.Str(); hdfs.ugi = r.Str(); hdfs.namenode = r.Str();
   }
 };
 

@@ -299,6 +299,63 @@ esac
     assert core.read_file("s3://mybucket/data/x;rm -rf y") is None      # refused before any shell sees it
 
 
+def _fake_hadoop(home, log):
+    """<home>/bin/hadoop: `fs [-D k=v]... -cat URI` prints the local file behind hdfs://<path>, `-ls URI`
+    prints a listing in the 8 columns of `hadoop fs -ls` (with a directory and a header line)."""
+    import stat
+    exe = home / "bin" / "hadoop"
+    exe.parent.mkdir(parents=True)
+    exe.write_text(f"""#!/bin/sh
+echo "$@" >> {log}
+[ "$1" = fs ] || exit 2
+shift
+while [ "$1" = -D ]; do shift; shift; done
+op="$1"; path="${{2#hdfs://}}"
+case "$op" in
+  -cat) [ -f "$path" ] || exit 1; cat "$path" ;;
+  -ls) echo "Found some items"
+       echo "drwxr-xr-x   - u g          0 2015-03-18 16:34 $path/sub"
+       for f in "$path"/*; do [ -f "$f" ] && echo "-rw-r--r--   3 u g       1234 2015-03-18 16:34 $f"; done ;;
+  *) exit 2 ;;
+esac
+""")
+    exe.chmod(exe.stat().st_mode | stat.S_IEXEC)
+
+
+def test_hdfs_files_are_read_through_hadoop_fs(tmp_path):
+    """A data block with `hdfs {{ home ugi namenode }}` names HDFS files: directories are listed with
+    `hadoop fs -ls`, files are read from a `hadoop fs -cat` pipe (gunzip behind it for .gz), the -D options
+    carry the name node and the user (a stand-in hadoop command here)."""
+    import gzip
+    from parameter_server_b200.system import core
+    store = tmp_path / "store" / "train"
+    (store / "sub").mkdir(parents=True)
+    (store / "part-0").write_text("1 3:1 7:1\n")
+    (store / "part-1").write_text("-1 2:1\n")
+    with gzip.open(store / "zipped-0.gz", "wt") as f:
+        f.write("1 5:1\n-1 6:1\n")
+    (store / "other").write_text("x\n")
+    log = tmp_path / "hadoop.log"
+    _fake_hadoop(tmp_path / "hadoop", log)
+    hdfs = {"home": str(tmp_path / "hadoop"), "ugi": "me,secret", "namenode": "nn:9000"}
+    files = core.search_files([f"{store}/part-.*"], hdfs)
+    assert files == [f"hdfs://{store}/part-0", f"hdfs://{store}/part-1"]
+    assert core.hadoop_fs() == f"{tmp_path}/hadoop/bin/hadoop fs -D fs.default.name=nn:9000 -D hadoop.job.ugi=me,secret"
+    assert core.read_file(files[0]) == b"1 3:1 7:1\n"
+    y, mats = core.StreamReader([files[1]], "TEXT", "LIBSVM", True).read_matrices(10)
+    assert list(y) == [-1.0] and list(mats[0]["index"]) == [2]
+    y, mats = core.StreamReader([f"hdfs://{store}/zipped-0.gz"], "TEXT", "LIBSVM", True).read_matrices(10)
+    assert list(y) == [1.0, -1.0] and list(mats[0]["index"]) == [5, 6]
+    calls = log.read_text().splitlines()
+    assert calls[0] == f"fs -D fs.default.name=nn:9000 -D hadoop.job.ugi=me,secret -ls hdfs://{store}"
+    assert f"fs -D fs.default.name=nn:9000 -D hadoop.job.ugi=me,secret -cat hdfs://{store}/part-0" in calls
+    assert core.read_file(f"hdfs://{store}/x;rm -rf y") is None      # refused before any shell sees it
+    # the GPU application resolves a configuration's data block the same way
+    from parameter_server_b200.app.linear import _files
+    conf = core.parse_text_proto(f'training_data {{ hdfs {{ home: "{tmp_path}/hadoop" }} file: "{store}/part-.*" }}')
+    assert _files(conf["training_data"]) == files
+
+
 def test_cycle_counter_timer_pair_moves_forward():
     """hwtic / hwtoc (the reference's cycle-counter timers, util/resource_usage.h): monotone and non-zero."""
     from parameter_server_b200.system import core

@@ -168,6 +168,31 @@ def test_node_processes_clean_under_sanitizers(data, tmp_path, kinds):
     assert len(_read_model(str(tmp_path / "model_S*"))) > 10
 
 
+def test_training_data_in_hdfs(data, tmp_path):
+    """training_data with an `hdfs` block: scheduler and workers (OS processes) list and read the files through
+    `<home>/bin/hadoop fs` (a stand-in command that serves local files), for the online and the batch solver."""
+    from test_core_util import _fake_hadoop
+    from parameter_server_b200 import _build
+    log = tmp_path / "hadoop.log"
+    _fake_hadoop(tmp_path / "hadoop", log)
+    exe = str(_build.PKG / "bin" / "psb_linear")
+    hdfs = f'hdfs {{ home: "{tmp_path}/hadoop" namenode: "nn:9000" }} file:'
+    for name, text in (("sgd", CONF_SGD.format(train=data["train"], out=str(tmp_path), algo="FTRL", filters="")),
+                       ("darlin", CONF_DARLIN.format(train=data["train"], out=str(tmp_path), tau=1, tail=0))):
+        conf = tmp_path / f"{name}.conf"
+        conf.write_text(text.replace("file:", hdfs, 1))
+        assert "hdfs {" in conf.read_text().splitlines()[1]
+        res = launch_local_processes(2, 2, [exe, "-app_file", str(conf)], timeout=180)
+        for nid, r in res.items():
+            assert r.returncode == 0, (name, nid, r.stdout[-2000:])
+    calls = log.read_text()
+    assert f"-ls hdfs://{data['train']}" in calls and f"-cat hdfs://{data['train']}/part-" in calls
+    w = _read_model(str(tmp_path / "model_S*"))
+    y, m = _score(data["train_files"], w)
+    assert core.evaluate(y, m)["auc"] > 0.68
+    assert len(_read_model(str(tmp_path / "darlin_S*"))) > 10
+
+
 def test_darlin_processes_start_reliably(data, tmp_path):
     """Twenty start-ups of 1 scheduler + 2 servers + 2 workers as OS processes: every node
     must be a member of the groups before the scheduler's first group task goes out (a node
