@@ -313,6 +313,12 @@ def run_darlin(conf, verbose=True):
     dist, rank, world = _dist()
     dev = torch.device("cuda", torch.cuda.current_device())
     d = conf["darlin"]
+    init_w = d.get("init_w", {})
+    if isinstance(init_w, dict) and init_w.get("type", "ZERO") != "ZERO":
+        # the device solver starts every weight at zero (dual = 1 needs no pass over the data); other starts
+        # are served by the CPU nodes (bin/psb_linear), which take the same configuration file
+        raise SystemExit("darlin.init_w other than ZERO is not supported by the GPU application: "
+                         "run this configuration on the CPU nodes (bin/psb_linear)")
     l1, _ = _penalty(conf)
     data = conf["training_data"]
     files = _files(data)[rank::world]

@@ -269,7 +269,7 @@ class DarlinServer : public DarlinCompNode {
       model_.WaitReceivedRequest(time, kWorkerGroup);
       auto& kv = model_[grp];
       kv.value.resize(kv.key.size());
-      kv.value.SetZero();
+      kv.value.SetValue(bcd_.init_w);      // the workers pull these and start from dual = exp(y . Xw)
       active_set_[grp].resize((uint32_t)kv.key.size(), true);
       delta_[grp].resize(kv.key.size());
       delta_[grp].SetValue((Real)bcd_.delta_init_value);

@@ -45,6 +45,7 @@ struct BCDConfig {
   std::vector<FilterConfig> comm_filter;
   int save_model_every_n_iter = 0;
   bool load_local_data = false;
+  ParamInit init_w;            // initial weights on the servers (learner/proto/bcd.proto:40); ZERO by default
   // linear-method extensions
   double delta_init_value = 1;
   double delta_max_value = 5;
@@ -163,6 +164,18 @@ inline Config ParseConfig(const std::string& text) {
     for (auto* f : n->children_of("comm_filter")) b.comm_filter.push_back(ParseFilter(*f));
     b.save_model_every_n_iter = (int)n->integer("save_model_every_n_iter", 0);
     b.load_local_data = n->boolean("load_local_data", false);
+    if (const TextNode* w = n->child("init_w")) {
+      static const std::map<std::string, ParamInit::Type> types = {
+          {"ZERO", ParamInit::ZERO}, {"CONSTANT", ParamInit::CONSTANT}, {"GAUSSIAN", ParamInit::GAUSSIAN},
+          {"FILE", ParamInit::FILE}, {"CLONE", ParamInit::CLONE}};
+      auto it = types.find(w->str("type", "ZERO"));
+      PS_CHECK(it != types.end()) << "unknown init_w type " << w->str("type");
+      b.init_w.type = it->second;
+      b.init_w.constant = w->num("constant", 1);
+      b.init_w.mean = w->num("mean", 0);
+      b.init_w.std = w->num("std", 1);
+      b.init_w.file_name = w->str("file_name", "");
+    }
     b.delta_init_value = n->num("delta_init_value", 1);
     b.delta_max_value = n->num("delta_max_value", 5);
     b.kkt_filter_threshold_ratio = n->num("kkt_filter_threshold_ratio", 10);

@@ -131,6 +131,28 @@ def test_darlin_in_process(data, tmp_path, tau, tail):
     assert obj < (0.93 if tau == 0 else 0.99) * len(y) * np.log(2)
 
 
+def test_darlin_starts_from_given_weights(data, tmp_path):
+    """darlin { init_w { type: CONSTANT constant: c } }: the servers allocate the weights with that value and the
+    workers start from dual = exp(y . Xw). After one pass the model differs from the zero start's; after twelve
+    it has reached the same neighbourhood of the optimum of this convex problem."""
+    const = "init_w { type: CONSTANT constant: 0.05 }"
+    objs = {}
+    for name, init, passes in (("zero", "", 12), ("const", const, 12), ("zero1", "", 1), ("const1", const, 1)):
+        out = tmp_path / name
+        out.mkdir()
+        conf = CONF_DARLIN.format(train=data["train"], out=str(out), tau=0, tail=0).replace(
+            "max_pass_of_data: 12", f"max_pass_of_data: {passes} random_feature_block_order: false {init}")
+        cl = LocalCluster(2, 2, None, conf=conf, run=True)
+        cl.join(timeout=180)
+        cl.stop()
+        w = _read_model(str(out / "darlin_S*"))
+        y, m = _score(data["train_files"], w)
+        objs[name] = (np.log1p(np.exp(-y * m)).sum() + 2 * sum(abs(v) for v in w.values()), w)
+    assert objs["const1"][1] != objs["zero1"][1]
+    assert objs["const"][0] < 0.93 * len(y) * np.log(2)
+    assert abs(objs["const"][0] - objs["zero"][0]) < 0.1 * objs["zero"][0], (objs["const"][0], objs["zero"][0])
+
+
 def test_async_sgd_multi_process_tcp(data, tmp_path):
     """1 scheduler + 2 servers + 2 workers as OS processes on 127.0.0.1."""
     from parameter_server_b200 import _build
