@@ -31,7 +31,7 @@ class Tokens {
 void ExampleParser::Init(TextFormat format, bool ignore_fea_slot, bool shuffle_fea_id) {
   format_ = format;
   ignore_fea_slot_ = ignore_fea_slot;
-  shuffle_fea_id_ = shuffle_fea_id;
+  shuffle_fea_id_ = shuffle_fea_id || ReaderFlags::get().shuffle_fea_id;
   PS_CHECK(format != DataConfig::VW) << "the vw text format is not supported";
 }
 
@@ -544,6 +544,9 @@ DataConfig appendFiles(const DataConfig& conf, const std::string& suffix) {
 template <typename V>
 void StreamReader<V>::init(const DataConfig& data) {
   data_ = searchFiles(data);
+  // the process-wide -line_limit applies to text files whose configuration sets no limit of its own
+  if (data_.max_num_lines_per_file < 0 && ReaderFlags::get().line_limit > 0 && data_.format == DataConfig::TEXT)
+    data_.max_num_lines_per_file = ReaderFlags::get().line_limit;
   next_file_ = 0;
   file_.reset();
   record_.reset();

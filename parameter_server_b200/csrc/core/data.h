@@ -114,6 +114,15 @@ ExampleInfo mergeExampleInfo(const ExampleInfo& a, const ExampleInfo& b);
 MatrixInfo readMatrixInfo(const ExampleInfo& info, int slot_idx, int sizeof_idx, int sizeof_val);
 
 // ---------------------------------------------------------------- parsers
+// Reader settings that a node takes from its command line (-hash_kernel, -shuffle_fea_id, -line_limit):
+// defaults of every StreamReader, ExampleParser and FileLineReader made afterwards in this process.
+struct ReaderFlags {
+  uint64_t hash_kernel = 0;
+  bool shuffle_fea_id = false;
+  int line_limit = 0;
+  static ReaderFlags& get() { static ReaderFlags f; return f; }
+};
+
 class ExampleParser {
  public:
   typedef DataConfig::TextFormat TextFormat;
@@ -200,7 +209,8 @@ std::vector<std::string> readFilenamesInHdfsDirectory(const std::string& dir);  
 
 class FileLineReader {
  public:
-  explicit FileLineReader(const std::string& file, int line_limit = 0) : file_(file), line_limit_(line_limit) {}
+  explicit FileLineReader(const std::string& file, int line_limit = 0)
+      : file_(file), line_limit_(line_limit > 0 ? line_limit : ReaderFlags::get().line_limit) {}
   void set_line_callback(std::function<void(char*)> cb) { cb_ = std::move(cb); }
   // calls the callback once per line
   void Reload();
@@ -277,7 +287,7 @@ class StreamReader {
   std::unique_ptr<RecordReader> record_;
   ExampleParser parser_;
   std::vector<char> line_;
-  uint64_t hash_kernel_ = 0;
+  uint64_t hash_kernel_ = ReaderFlags::get().hash_kernel;
 };
 
 // ---------------------------------------------------------------- slot reader

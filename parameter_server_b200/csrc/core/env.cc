@@ -39,6 +39,9 @@ Options Options::Parse(const std::vector<std::string>& args) {
     else if (name == "bind_to") o.bind_to = atoi(next().c_str());
     else if (name == "report_interval") o.report_interval = atoi(next().c_str());
     else if (name == "log_dir") o.log_dir = next();
+    else if (name == "hash_kernel") o.hash_kernel = strtoull(next().c_str(), nullptr, 10);
+    else if (name == "line_limit") o.line_limit = atoi(next().c_str());
+    else if (name == "shuffle_fea_id") o.shuffle_fea_id = has_val ? as_bool(val) : true;
     else if (name == "local") o.local = has_val ? as_bool(val) : true;
     else if (name == "logtostderr" || name == "v") { if (!has_val && i + 1 < args.size() && args[i + 1][0] != '-') ++i; }
     else { o.rest.push_back(a); }

@@ -28,6 +28,11 @@ struct Options {
   int report_interval = 0;    // seconds between heartbeat reports, 0 = off
   std::string log_dir;
   bool exit_on_scheduler_loss = true;
+  // process-wide settings of the readers (data/stream_reader.h:104, data/text_parser.cc:163,
+  // util/filelinereader.cc:29 in the reference, where they are global flags too)
+  uint64_t hash_kernel = 0;   // >0: every feature id is taken modulo this
+  bool shuffle_fea_id = false;  // TERAFEA ids are mixed by a hash
+  int line_limit = 0;         // >0: at most this many lines are read from a text file
   std::vector<std::string> rest;  // unparsed arguments
 
   // "-name value", "-name=value", "--name value"; bool flags may omit the value

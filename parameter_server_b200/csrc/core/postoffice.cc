@@ -1,6 +1,7 @@
 #include "postoffice.h"
 
 #include "customer.h"
+#include "data.h"
 
 namespace PS {
 
@@ -20,6 +21,10 @@ Postoffice::~Postoffice() {
 }
 
 void Postoffice::StartThreads() {
+  ReaderFlags& rf = ReaderFlags::get();
+  if (opt_.hash_kernel) rf.hash_kernel = opt_.hash_kernel;
+  if (opt_.shuffle_fea_id) rf.shuffle_fea_id = true;
+  if (opt_.line_limit > 0) rf.line_limit = opt_.line_limit;
   running_ = true;
   recv_thread_ = std::thread([this] { Recv(); });
   send_thread_ = std::thread([this] { Send(); });

@@ -356,6 +356,25 @@ def test_hdfs_files_are_read_through_hadoop_fs(tmp_path):
     assert _files(conf["training_data"]) == files
 
 
+def test_data_tool_show_and_convert(tmp_path, capsys):
+    """utils/datatool: `show` prints parsed examples, `convert` writes a record file that the stream reader
+    reads back with format PROTO, and the per-slot statistics beside it."""
+    import json
+    from parameter_server_b200.system import core
+    from parameter_server_b200.utils import datatool
+    (tmp_path / "part-0").write_text("1 3:1 7:0.5\n-1 2:1\n")
+    (tmp_path / "part-1").write_text("1 9:2\n")
+    assert datatool.main(["show", "-input", str(tmp_path / "part-0"), "-format", "libsvm", "-n", "1"]) == 0
+    first = json.loads(capsys.readouterr().out.strip())
+    assert first["0"]["val"] == [1.0] and first["1"]["key"] == [3, 7] and first["1"]["val"] == [1.0, 0.5]
+    assert datatool.main(["convert", "-input", str(tmp_path / "part-.*"), "-output", str(tmp_path / "all")]) == 0
+    assert "3 examples from 2 file(s)" in capsys.readouterr().out
+    info = json.load(open(tmp_path / "all.info"))
+    assert info["num_ex"] == 3 and info["slot"][1]["nnz_ele"] == 4
+    y, mats = core.StreamReader([str(tmp_path / "all.recordio")], "PROTO", "LIBSVM").read_matrices(10)
+    assert list(y) == [1.0, -1.0, 1.0] and list(mats[0]["index"]) == [3, 7, 2, 9]
+
+
 def test_cycle_counter_timer_pair_moves_forward():
     """hwtic / hwtoc (the reference's cycle-counter timers, util/resource_usage.h): monotone and non-zero."""
     from parameter_server_b200.system import core

@@ -215,6 +215,27 @@ def test_training_data_in_hdfs(data, tmp_path):
     assert len(_read_model(str(tmp_path / "darlin_S*"))) > 10
 
 
+def test_reader_flags_on_the_command_line(data, tmp_path):
+    """-hash_kernel N folds every feature id into [0, N) in the stream reader; -line_limit caps the lines read
+    per text file (the reference's global flags of the same names)."""
+    from parameter_server_b200 import _build
+    exe = str(_build.PKG / "bin" / "psb_linear")
+    conf = tmp_path / "sgd.conf"
+    conf.write_text(CONF_SGD.format(train=data["train"], out=str(tmp_path), algo="FTRL", filters="")
+                    .replace("lambda: 0.5", "lambda: 0.01"))
+    res = launch_local_processes(1, 2, [exe, "-app_file", str(conf), "-hash_kernel", "50", "-line_limit=200"], timeout=180)
+    for nid, r in res.items():
+        assert r.returncode == 0, (nid, r.stdout[-2000:])
+    w = _read_model(str(tmp_path / "model_S*"))
+    assert 5 < len(w) <= 50 and max(w) < 50
+    # the batch solver reads its files line by line: 4 files x 200 lines, not the 1500 lines per file that are there
+    conf.write_text(CONF_DARLIN.format(train=data["train"], out=str(tmp_path), tau=0, tail=0))
+    res = launch_local_processes(1, 2, [exe, "-app_file", str(conf), "-line_limit=200"], timeout=180)
+    for nid, r in res.items():
+        assert r.returncode == 0, (nid, r.stdout[-2000:])
+    assert "loaded 800 examples" in res["H"].stdout, res["H"].stdout[:600]
+
+
 def test_darlin_processes_start_reliably(data, tmp_path):
     """Twenty start-ups of 1 scheduler + 2 servers + 2 workers as OS processes: every node
     must be a member of the groups before the scheduler's first group task goes out (a node
