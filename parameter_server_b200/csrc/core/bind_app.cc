@@ -173,6 +173,20 @@ void BindApp(py::module& m) {
     return ToNumpy(y);
   }, py::arg("offset"), py::arg("index"), py::arg("value"), py::arg("x"), py::arg("cols"), py::arg("trans") = false,
      py::arg("threads") = 2);
+  m.def("sparse_debug_string", [](py::array_t<uint64_t, py::array::c_style | py::array::forcecast> offset,
+                                  py::array_t<uint32_t, py::array::c_style | py::array::forcecast> index, py::object value,
+                                  size_t cols) {
+    MatrixInfo info;
+    info.row = SizeR(0, offset.size() - 1);
+    info.col = SizeR(0, cols);
+    info.nnz = index.size();
+    SArray<size_t> off(offset.size());
+    for (py::ssize_t i = 0; i < offset.size(); ++i) off[i] = offset.data()[i];
+    SArray<float> val;
+    if (!value.is_none()) val = FromNumpy<float>(value.cast<py::array_t<float, py::array::c_style | py::array::forcecast>>());
+    info.type = val.empty() ? MatrixInfo::SPARSE_BINARY : MatrixInfo::SPARSE;
+    return SparseMatrix<uint32_t, float>(info, off, FromNumpy<uint32_t>(index), val).debugString();
+  }, py::arg("offset"), py::arg("index"), py::arg("value"), py::arg("cols"), "header and first entries of a CSR matrix");
 
   m.def("transpose_csr", [](py::array_t<uint64_t, py::array::c_style | py::array::forcecast> offset,
                             py::array_t<uint32_t, py::array::c_style | py::array::forcecast> index, size_t cols) {

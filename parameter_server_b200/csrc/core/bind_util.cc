@@ -26,6 +26,12 @@ void BindUtil(py::module& m) {
     return py::make_tuple(out[0], out[1]);
   });
   m.def("sketch_hash", [](uint64_t k) { return Sketch::hash(k); });
+  m.def("res_usage", []() {
+    py::dict d;
+    d["my_phy_mem_mb"] = ResUsage::myPhyMem(); d["my_vir_mem_mb"] = ResUsage::myVirMem();
+    d["host_total_mem_mb"] = ResUsage::hostTotalMem(); d["host_in_use_mem_mb"] = ResUsage::hostInUseMem();
+    return d;
+  }, "memory of this process and of the machine, in MB");
   m.def("hwtic", []() { return hwtic(); }, "time-stamp counter now");
   m.def("hwtoc", [](uint64_t start) { return hwtoc(start); }, "cycles since hwtic()");
   m.def("read_file", [](const std::string& name) -> py::object {

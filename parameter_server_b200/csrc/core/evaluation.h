@@ -159,7 +159,22 @@ class ResUsage {
  public:
   static double myPhyMem() { return Field(1) * 4096.0 / (1 << 20); }
   static double myVirMem() { return Field(0) * 4096.0 / (1 << 20); }
+  // the machine's memory in MB: total, and in use (total - free - buffers - page cache)
+  static double hostTotalMem() { return MemInfo("MemTotal:") / 1024.0; }
+  static double hostInUseMem() {
+    return (MemInfo("MemTotal:") - MemInfo("MemFree:") - MemInfo("Buffers:") - MemInfo("Cached:")) / 1024.0;
+  }
  private:
+  static double MemInfo(const char* name) {   // the kB figure of one /proc/meminfo line
+    std::ifstream f("/proc/meminfo");
+    std::string key;
+    double kb = 0;
+    while (f >> key) {
+      if (key == name) { f >> kb; return kb; }
+      f.ignore(256, '\n');
+    }
+    return 0;
+  }
   static double Field(int i) {
     std::ifstream f("/proc/self/statm");
     double v[2] = {0, 0};

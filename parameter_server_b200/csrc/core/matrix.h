@@ -20,6 +20,12 @@ struct MatrixInfo {
   size_t nnz = 0;
   uint32_t sizeof_index = 0, sizeof_value = 0;
   double nnz_per_row = 0, nnz_per_col = 0;
+  std::string DebugString() const {
+    std::ostringstream ss;
+    ss << (type == DENSE ? "DENSE" : type == SPARSE ? "SPARSE" : "SPARSE_BINARY") << (row_major ? " row-major" : " col-major")
+       << " id " << id << " rows " << row.ToString() << " cols " << col.ToString() << " nnz " << nnz;
+    return ss.str();
+  }
 };
 
 template <typename V>
@@ -37,6 +43,8 @@ class Matrix {
   bool empty() const { return nnz() == 0; }
   size_t innerSize() const { return rowMajor() ? cols() : rows(); }
   size_t outerSize() const { return rowMajor() ? rows() : cols(); }
+  // header and the first entries, for logs (util/matrix.h:121, util/sparse_matrix.h:365-371)
+  virtual std::string debugString() const { return info_.DebugString(); }
   // y = A x and y = A' x
   virtual void times(const V* x, V* y, int num_threads = 2) const = 0;
   virtual void transTimes(const V* x, V* y, int num_threads = 2) const = 0;
@@ -74,6 +82,11 @@ class DenseMatrix : public Matrix<V> {
   SArray<V>& value() { return value_; }
   const SArray<V>& value() const { return value_; }
   V& at(size_t r, size_t c) { return this->rowMajor() ? value_[r * this->cols() + c] : value_[c * this->rows() + r]; }
+  std::string debugString() const override {
+    std::ostringstream ss;
+    ss << this->info_.DebugString() << "\nvalue: " << value_;
+    return ss.str();
+  }
   void times(const V* x, V* y, int = 2) const override {
     size_t R = this->rows(), C = this->cols();
     for (size_t r = 0; r < R; ++r) {
@@ -105,6 +118,13 @@ class SparseMatrix : public Matrix<V> {
   const SArray<size_t>& offset() const { return offset_; }
   const SArray<I>& index() const { return index_; }
   const SArray<V>& value() const { return value_; }
+
+  std::string debugString() const override {
+    std::ostringstream ss;
+    ss << this->info_.DebugString() << "\noffset: " << offset_ << "\nindex: " << index_;
+    if (!this->binary()) ss << "\nvalue: " << value_;
+    return ss.str();
+  }
 
   using Matrix<V>::times;
   using Matrix<V>::transTimes;

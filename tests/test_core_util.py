@@ -375,6 +375,18 @@ def test_data_tool_show_and_convert(tmp_path, capsys):
     assert list(y) == [1.0, -1.0, 1.0] and list(mats[0]["index"]) == [3, 7, 2, 9]
 
 
+def test_resource_usage_and_matrix_debug_string():
+    from parameter_server_b200.system import core
+    r = core.res_usage()
+    assert 1 < r["my_phy_mem_mb"] <= r["my_vir_mem_mb"]
+    assert 0 < r["host_in_use_mem_mb"] < r["host_total_mem_mb"] and r["my_phy_mem_mb"] < r["host_total_mem_mb"]
+    s = core.sparse_debug_string(np.array([0, 2, 3], np.uint64), np.array([1, 4, 2], np.uint32), None, 5)
+    assert "SPARSE_BINARY row-major" in s and "nnz 3" in s and "index: [3]{1,4,2}" in s and "value" not in s
+    s = core.sparse_debug_string(np.array([0, 2, 3], np.uint64), np.array([1, 4, 2], np.uint32),
+                                 np.array([.5, 1, 2], np.float32), 5)
+    assert "value: [3]{0.5,1,2}" in s
+
+
 def test_cycle_counter_timer_pair_moves_forward():
     """hwtic / hwtoc (the reference's cycle-counter timers, util/resource_usage.h): monotone and non-zero."""
     from parameter_server_b200.system import core
