@@ -4,14 +4,15 @@ reference's ``docker/local.sh`` (and ``docker/build.sh``, ``docker/rm_local.sh``
     python -m parameter_server_b200.system.docker build  [-image NAME]
     python -m parameter_server_b200.system.docker local  NUM_SERVERS NUM_WORKERS APP_CONF DATA_DIR MODEL_DIR [args...]
     python -m parameter_server_b200.system.docker rm     NUM_SERVERS NUM_WORKERS
+    python -m parameter_server_b200.system.docker upload LOCAL_FILE s3://bucket/key
 
 ``local`` mounts the configuration at ``/app.conf``, the data at ``/data`` and the model directory at
 ``/model`` in every container and starts the scheduler on the docker bridge's address, port 8000, the
 servers and workers on the ports after it, as the reference does. ``--dry-run`` prints the ``docker``
 commands instead of running them. The image is built from ``docker/Dockerfile`` at the repository
 root (CPU nodes: the C++ host runtime and ``bin/psb_linear``). The reference's EC2 / docker-machine
-swarm scripts (``cloud.sh``, ``fire_amazonec2.sh``, ``shut.sh``, ``upload_s3.sh``) drive a tool that is
-no longer distributed and are not rebuilt.
+swarm scripts (``cloud.sh``, ``fire_amazonec2.sh``, ``shut.sh``) drive a tool that is no longer distributed
+and are not rebuilt; ``upload`` is ``upload_s3.sh`` (one ``curl --upload-file`` to a public-read object).
 """
 from __future__ import annotations
 
@@ -57,6 +58,17 @@ def local_commands(num_servers: int, num_workers: int, app: str, data: str, mode
     return cmds
 
 
+def upload_command(local_file: str, s3_path: str) -> List[str]:
+    """`curl --upload-file` of one file to a public-read S3 object, the job of ``docker/upload_s3.sh:1-24``
+    (data or a configuration that the containers then read as ``s3://bucket/key``)."""
+    if not s3_path.startswith("s3://") or "/" not in s3_path[5:]:
+        raise SystemExit("upload: the target must be s3://bucket/key")
+    bucket, key = s3_path[5:].split("/", 1)
+    size = os.path.getsize(local_file)
+    return ["curl", f"http://{bucket}.s3.amazonaws.com/{key}?Content-Length={size}&x-amz-acl=public-read",
+            "--upload-file", local_file]
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     dry = "--dry-run" in argv
@@ -76,6 +88,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         cmds = local_commands(int(argv[1]), int(argv[2]), argv[3], argv[4], argv[5], argv[6:], bridge_ip(), image)
     elif argv[0] == "rm" and len(argv) >= 3:
         cmds = [["docker", "rm", "-f"] + [f"n{i}" for i in range(int(argv[1]) + int(argv[2]) + 1)]]
+    elif argv[0] == "upload" and len(argv) == 3:
+        cmds = [upload_command(argv[1], argv[2])]
     else:
         print(__doc__)
         return 2

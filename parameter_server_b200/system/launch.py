@@ -254,7 +254,15 @@ def main(argv: Optional[List[str]] = None) -> int:
     s = sub.add_parser("kill"); s.add_argument("id")
     sub.add_parser("stop")
     s = sub.add_parser("wait"); s.add_argument("-timeout", type=float, default=None)
+    s = sub.add_parser("root-node", help="print the -scheduler string for this machine (script/get_root_node.sh)")
+    s.add_argument("interface", help="network interface whose address the scheduler binds, e.g. eth0; '' = first one")
+    s.add_argument("port", type=int)
     a = ap.parse_args(argv)
+    if a.cmd == "root-node":
+        from . import core
+        from .cluster import node_string
+        print(node_string("SCHEDULER", core.local_ip(a.interface), a.port, "H"))
+        return 0
     job = Job(a.state)
     if a.cmd == "start":
         cmd = [c for c in a.argv if c != "--"]

@@ -43,6 +43,21 @@ def test_docker_local_commands(tmp_path, capsys):
     assert capsys.readouterr().out.strip() == "docker rm -f n0 n1 n2 n3"
 
 
+def test_root_node_string_and_s3_upload_command(tmp_path, capsys):
+    """`launch root-node IFACE PORT` prints the -scheduler string of this machine; `docker upload` is one curl
+    call with the object's size and a public-read ACL."""
+    from parameter_server_b200.system import docker, launch
+    assert launch.main(["root-node", "lo", "8000"]) == 0
+    assert capsys.readouterr().out.strip() == "role:SCHEDULER,hostname:'127.0.0.1',port:8000,id:'H'"
+    f = tmp_path / "app.conf"
+    f.write_text("x" * 37)
+    assert docker.main(["--dry-run", "upload", str(f), "s3://mybucket/jobs/app.conf"]) == 0
+    out = capsys.readouterr().out.strip()
+    assert out == f"curl 'http://mybucket.s3.amazonaws.com/jobs/app.conf?Content-Length=37&x-amz-acl=public-read' --upload-file {f}"
+    with pytest.raises(SystemExit):
+        docker.main(["--dry-run", "upload", str(f), "/not/s3"])
+
+
 def test_binary_matrix_files_round_trip(tmp_path):
     from parameter_server_b200.utils import binfmt
     rng = np.random.default_rng(0)
