@@ -314,10 +314,9 @@ def run_darlin(conf, verbose=True):
     dev = torch.device("cuda", torch.cuda.current_device())
     d = conf["darlin"]
     init_w = d.get("init_w", {})
-    if isinstance(init_w, dict) and init_w.get("type", "ZERO") != "ZERO":
-        # the device solver starts every weight at zero (dual = 1 needs no pass over the data); other starts
-        # are served by the CPU nodes (bin/psb_linear), which take the same configuration file
-        raise SystemExit("darlin.init_w other than ZERO is not supported by the GPU application: "
+    init_type = init_w.get("type", "ZERO") if isinstance(init_w, dict) else "ZERO"
+    if init_type not in ("ZERO", "CONSTANT", "GAUSSIAN"):
+        raise SystemExit(f"darlin.init_w type {init_type} is not supported by the GPU application: "
                          "run this configuration on the CPU nodes (bin/psb_linear)")
     l1, _ = _penalty(conf)
     data = conf["training_data"]
@@ -383,6 +382,14 @@ def run_darlin(conf, verbose=True):
     r = DarlinRank(fab, cfg, col.to(torch.int64), torch.from_numpy(y).to(dev), row_ptr=row_ptr, vals=vals,
                    global_keys=torch.arange(space.n_cols, dtype=torch.int64, device=dev))
     r.set_blocks(plan.blocks, plan.prior)
+    if init_type != "ZERO":
+        # the same vector on every rank: a constant, or draws of one seeded generator over the column space
+        if init_type == "CONSTANT":
+            w0 = np.full(space.n_cols, float(init_w.get("constant", 1)), np.float32)
+        else:
+            w0 = np.random.RandomState(20141010).normal(float(init_w.get("mean", 0)), float(init_w.get("std", 1)),
+                                                        space.n_cols).astype(np.float32)
+        r.set_initial_weights(torch.from_numpy(w0))
 
     def all_reduce(vals_, op):
         if dist is None:

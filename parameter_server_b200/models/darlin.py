@@ -127,6 +127,25 @@ class DarlinRank:
         self.blocks = [(i * cfg.block_cols, min(self.n_cols, (i + 1) * cfg.block_cols)) for i in range(nb)]
         self.prior_blocks: List[int] = []
 
+    def set_initial_weights(self, w0: torch.Tensor):
+        """Start from ``w0`` (float32 per global column, the same vector on every rank) instead of zero: the
+        owners' weights and the workers' copies take it, and the margins become X w0 over this rank's rows
+        (the reference's ``init_w``: servers allocate with it, ``learner/bcd.h:199``, workers compute
+        ``X w`` from the first pull, ``learner/bcd.h:414-416``). Call before the first pass."""
+        n = self.n_cols
+        w0 = w0.to(self.dev, torch.float32).flatten()
+        assert w0.numel() == n
+        self.w_own[:n].copy_(w0)
+        self.w_cur[:n].copy_(w0)
+        self.margin.zero_()
+        nnz = self.csc_col.numel()
+        if nnz:
+            contrib = w0[self.csc_col.long()]
+            if self.b.csc_val is not None:
+                contrib = contrib * self.b.csc_val[:nnz]
+            self.margin.index_add_(0, self.b.csc_row[:nnz].long(), contrib)
+        torch.cuda.current_stream(self.dev).synchronize()      # the passes run on streams of their own
+
     def set_blocks(self, blocks: List[tuple], prior: Optional[List[int]] = None):
         """Use the given column ranges as feature blocks (none wider than ``cfg.block_cols``); ``prior``
         lists block indices that open the first pass, one after another (no delay)."""

@@ -185,20 +185,25 @@ def auc(y, score):
     return float(a)
 
 
-def darlin_oracle(parts, global_keys, lam, eta, delta_init, delta_max, blocks_per_pass, n_pass, kkt_ratio=10.0, tau=0):
+def darlin_oracle(parts, global_keys, lam, eta, delta_init, delta_max, blocks_per_pass, n_pass, kkt_ratio=10.0, tau=0, w0=None):
     """NumPy restatement of Darlin. ``parts``: list of (keys_flat uint64, row_ptr, y, vals or None) per
     worker; ``blocks_per_pass``: list (per pass) of lists of (c0, c1) column ranges in processing order.
     ``tau``: block delay: the gradient of the i-th block of a pass is taken before the weights of the
     blocks i - tau .. i - 1 reach the margins (0: every block sees all earlier ones).
+    ``w0``: initial weight per global column (zero when None); the margins start at X w0.
     Returns (w per global column, history of objectives)."""
     ncol = len(global_keys)
-    w = np.zeros(ncol, f32); delta = np.full(ncol, delta_init, f32); active = np.ones(ncol, bool)
+    w = np.zeros(ncol, f32) if w0 is None else np.asarray(w0, f32).copy()
+    delta = np.full(ncol, delta_init, f32); active = np.ones(ncol, bool)
     data = []
     for keys, row_ptr, y, vals in parts:
         col = np.searchsorted(global_keys, keys)
         rows = np.repeat(np.arange(len(y)), np.diff(row_ptr))
         x = np.ones(len(keys), f32) if vals is None else vals.astype(f32)
-        data.append(dict(col=col, rows=rows, x=x, y=y.astype(f32), m=np.zeros(len(y), f32), binary=vals is None))
+        m = np.zeros(len(y), f32)
+        if w0 is not None:
+            np.add.at(m, rows, w[col] * x)
+        data.append(dict(col=col, rows=rows, x=x, y=y.astype(f32), m=m, binary=vals is None))
     n_ex = sum(len(d["y"]) for d in data)
     thr = 1e20
     hist = []

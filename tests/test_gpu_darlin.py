@@ -54,6 +54,49 @@ def test_darlin_matches_oracle(cuda_lib, S, real):
     assert 0 < hist[-1]["nnz_w"] < len(gk)
 
 
+@pytest.mark.parametrize("S,real", [(1, False), (2, True)])
+def test_darlin_warm_start_matches_oracle(cuda_lib, S, real):
+    """set_initial_weights (the reference's init_w): margins start at X w0, and the passes that follow match
+    the NumPy restatement started from the same weights."""
+    from parameter_server_b200.models.darlin import DarlinConfig, DarlinRank, darlin_heap_bytes, run_darlin
+    from parameter_server_b200.parallel.fabric import Fabric
+    from parameter_server_b200.utils import oracle
+    rng = np.random.default_rng(40 + S)
+    rows, z, n_feat = 500, 8, 250
+    cfg = DarlinConfig(lambda_l1=1.0, eta=0.3, block_cols=64, max_pass=3, epsilon=0.0, random_block_order=True, kkt_ratio=10.0)
+    fabs = Fabric.emulated(S, darlin_heap_bytes(cfg, S))
+    parts = [_data(rng, rows, z, n_feat, real) for _ in range(S)]
+    gk = np.unique(np.concatenate([p[0] for p in parts]))
+    gkt = torch.from_numpy(gk.view(np.int64)).cuda()
+    w0 = (np.full(len(gk), 0.05, np.float32) if S == 1 else
+          np.random.RandomState(7).normal(0, 0.1, len(gk)).astype(np.float32))
+    ranks = []
+    for f, (keys, y, vals) in zip(fabs, parts):
+        r = DarlinRank(f, cfg, torch.from_numpy(keys.view(np.int64)).cuda(), torch.from_numpy(y).cuda(), fixed_z=z,
+                       vals=None if vals is None else torch.from_numpy(vals).cuda(), global_keys=gkt)
+        r.set_initial_weights(torch.from_numpy(w0))
+        x = np.ones(rows * z, np.float32) if vals is None else vals
+        want = (w0[np.searchsorted(gk, keys)] * x).reshape(rows, z).sum(1)
+        assert np.allclose(r.margin.cpu().numpy(), want, rtol=1e-4, atol=1e-5)
+        ranks.append(r)
+    hist = run_darlin(ranks)
+    torch.cuda.synchronize()
+    blocks = ranks[0].blocks
+    orders = []
+    for it in range(cfg.max_pass):
+        o = list(range(len(blocks))); np.random.default_rng(1000 + it).shuffle(o)
+        orders.append([blocks[i] for i in o])
+    row_ptr = np.arange(rows + 1) * z
+    w_ref, h_ref = oracle.darlin_oracle([(k, row_ptr, y, v) for k, y, v in parts], gk, cfg.lambda_l1, cfg.eta,
+                                        cfg.delta_init, cfg.delta_max, orders, cfg.max_pass, cfg.kkt_ratio, w0=w0)
+    assert np.allclose([h["objective"] for h in hist], h_ref, rtol=2e-4)
+    got = np.zeros(len(gk), np.float32)
+    for r in ranks:
+        k, w = r.my_model()
+        got[np.searchsorted(gk, k)] = w
+    assert np.allclose(got, np.where(np.isnan(w_ref), 0, w_ref), rtol=2e-3, atol=2e-4)
+
+
 def test_darlin_bounded_delay_single_rank_converges(cuda_lib):
     from parameter_server_b200.models.darlin import DarlinConfig, DarlinRank, darlin_heap_bytes, run_darlin
     from parameter_server_b200.parallel.fabric import Fabric
