@@ -433,7 +433,12 @@ def main(argv: Optional[List[str]] = None):
                     help="async SGD: write weights and optimiser state to <prefix>_S<rank>.psbckpt at the end")
     ap.add_argument("-engine", "--engine", default="gpu", choices=["gpu", "null"],
                     help="null: run the node layer of async SGD (scheduler, workloads, leases, membership) without a device")
+    ap.add_argument("-hash_kernel", "--hash_kernel", type=int, default=0, help=">0: feature ids are taken modulo this")
+    ap.add_argument("-shuffle_fea_id", "--shuffle_fea_id", action="store_true", help="TERAFEA ids are mixed by a hash")
+    ap.add_argument("-line_limit", "--line_limit", type=int, default=0, help=">0: lines read per text file")
     args, _ = ap.parse_known_args(argv)
+    if args.hash_kernel or args.shuffle_fea_id or args.line_limit:
+        core.set_reader_flags(args.hash_kernel, args.shuffle_fea_id, args.line_limit)
     text = (open(args.app_file).read() if args.app_file else "") + args.app_conf
     conf = core.parse_text_proto(text)
     conf["_checkpoint_in"], conf["_checkpoint_out"] = args.checkpoint_in, args.checkpoint_out

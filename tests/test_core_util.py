@@ -387,6 +387,21 @@ def test_resource_usage_and_matrix_debug_string():
     assert "value: [3]{0.5,1,2}" in s
 
 
+def test_reader_flags_in_process(tmp_path):
+    """set_reader_flags: what -hash_kernel and -line_limit do to a stream reader made afterwards."""
+    from parameter_server_b200.system import core
+    f = tmp_path / "part-0"
+    f.write_text("".join(f"1 {100 + i}:1 {200 + i}:1\n" for i in range(20)))
+    try:
+        core.set_reader_flags(hash_kernel=7, line_limit=5)
+        y, mats = core.StreamReader([str(f)], "TEXT", "LIBSVM", True).read_matrices(100)
+        assert len(y) == 5 and max(mats[0]["index"]) < 7
+    finally:
+        core.set_reader_flags()
+    y, mats = core.StreamReader([str(f)], "TEXT", "LIBSVM", True).read_matrices(100)
+    assert len(y) == 20 and max(mats[0]["index"]) == 219
+
+
 def test_cycle_counter_timer_pair_moves_forward():
     """hwtic / hwtoc (the reference's cycle-counter timers, util/resource_usage.h): monotone and non-zero."""
     from parameter_server_b200.system import core
