@@ -108,10 +108,17 @@ class GpuEngine:
                     vals.fill_(1.0)
                 else:
                     vals.copy_(torch.from_numpy(m["value"]))
+        rows = n
+        if nnz == 0 and n > 0:
+            # every nonzero of the minibatch was filtered out (tail features): the round runs empty, as when
+            # there is no minibatch; the rows still count as read
+            n = 0
+            slot["rp"][0] = 0
+            vals = None
         self.worker.submit(slot["ids"][:nnz], slot["y"][:n], row_ptr=slot["rp"][:n + 1], vals=vals)
         slot["ev"].record(self.worker.copy_stream)
         slot["used"] = True
-        return n
+        return rows
 
     def finish(self):
         self.worker.wait()
@@ -227,7 +234,11 @@ def run_async_sgd(conf, verbose=True, engine: str = "gpu"):
                                 roles=os.environ.get("PSB_ROLES", "HSW"), on_node_lost=on_node_lost, inproc=inproc)
     res = nodes.run_lockstep_worker_loop(rn, eng, minibatch=minibatch, data_format=fmt, text=text,
                                          report_interval=float(sgd.get("report_interval", 1)), model_file=out,
-                                         announce=f"[rank {rank}]" if verbose else "")
+                                         announce=f"[rank {rank}]" if verbose else "",
+                                         tail_filter=nodes.TailFeatureFilter(int(sgd["tail_feature_freq"]),
+                                                                             float(sgd.get("countmin_n", 1e8)),
+                                                                             int(sgd.get("countmin_k", 2)))
+                                         if int(sgd.get("tail_feature_freq", 0)) > 0 else None)
     if conf.get("_checkpoint_out") and plane is not None:
         from ..utils import checkpoint
         checkpoint.save_plane(plane, conf["_checkpoint_out"], meta={"minibatches": res["rounds"], "examples": res["examples"]})

@@ -35,6 +35,8 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional
 
+import numpy as np
+
 from ..system import core
 from ..system.cluster import node_string
 
@@ -92,6 +94,44 @@ class NullEngine(Engine):
         self.saved.append(path)
         with open(path, "w") as f:
             f.write("")
+
+
+class TailFeatureFilter:
+    """Drops rare features from the minibatches before they reach the device: the loader-side count-min
+    filter of the reference's ``MinibatchReader`` (``learner/sgd.h:88-91,123-134``). Every minibatch adds the
+    counts of its unique keys to the sketch (saturating 8-bit cells); a nonzero stays when its key's estimated
+    count so far is greater than ``freq``. ``countmin_n`` cells, ``countmin_k`` hash functions
+    (``async_sgd { tail_feature_freq countmin_n countmin_k }``)."""
+
+    def __init__(self, freq: int, countmin_n: float = 1e8, countmin_k: int = 2):
+        self.freq = int(freq)
+        self.filter = core.FreqencyFilter()
+        self.filter.resize(int(min(max(countmin_n, 1024), 1 << 30)), int(countmin_k))
+        self.dropped = 0
+
+    def apply(self, batch):
+        """``batch``: ``(labels, [csr dict per slot])`` from the stream reader; returns the same with the
+        filtered nonzeros taken out (rows keep their places, some may become empty)."""
+        y, mats = batch
+        out = []
+        for m in mats:
+            keys = np.ascontiguousarray(m["index"], dtype=np.uint64)
+            uniq, cnt = np.unique(keys, return_counts=True)
+            self.filter.insert_keys(uniq, np.minimum(cnt, 255).astype(np.uint8))
+            kept = self.filter.query_keys(uniq, self.freq)
+            mask = np.isin(keys, kept, assume_unique=False)
+            if mask.all():
+                out.append(m)
+                continue
+            self.dropped += int(len(keys) - mask.sum())
+            off = np.asarray(m["offset"], dtype=np.int64)
+            new_off = np.concatenate([[0], np.cumsum(mask, dtype=np.int64)])[off].astype(np.uint64)
+            f = dict(m)
+            f["offset"], f["index"] = new_off, keys[mask]
+            if not m["binary"] and len(m["value"]):
+                f["value"] = np.asarray(m["value"])[mask]
+            out.append(f)
+        return y, out
 
 
 @dataclass
@@ -285,7 +325,8 @@ def node_rank(node_id: str) -> Optional[int]:
 def run_lockstep_worker_loop(nodes: RankNodes, engine: Engine, *, minibatch: int, data_format: str = "TEXT",
                              text: str = "LIBSVM", report_interval: float = 1.0, model_file: Optional[str] = None,
                              idle_wait: float = 0.0005, start_timeout: float = 120.0, save_timeout: float = 600.0,
-                             after_round: Optional[Callable[[int], None]] = None, announce: str = "") -> dict:
+                             after_round: Optional[Callable[[int], None]] = None, announce: str = "",
+                             tail_filter: Optional["TailFeatureFilter"] = None) -> dict:
     """The rank's main loop: rounds ``0, 1, ...`` while the scheduler's lease allows, a minibatch of
     the current workload per round (an empty round when there is none), progress reports, and at
     the end the commands of the rank's server node (model dump). Returns counters."""
@@ -340,7 +381,7 @@ def run_lockstep_worker_loop(nodes: RankNodes, engine: Engine, *, minibatch: int
                 files_done += 1
                 continue
             if len(got[0]) and got[1]:
-                batch = got
+                batch = got if tail_filter is None else tail_filter.apply(got)
                 break
         examples += engine.submit(batch)
         t += 1

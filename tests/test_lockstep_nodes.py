@@ -119,3 +119,38 @@ def test_worker_killed_between_steps_files_requeued(tmp_path):
     assert sum(r[2] for r in res) >= len(sizes) - 2 and sum(r[1] for r in res) >= sum(sizes) - 2 * 300
     for o in outs:
         assert "node W2 lost" in o, o
+
+
+def test_tail_feature_filter_of_the_loader():
+    """async_sgd.tail_feature_freq in the GPU application: a feature's nonzeros pass once the count-min
+    estimate of its count so far exceeds the threshold; rows keep their places."""
+    import numpy as np
+    from parameter_server_b200.app.nodes import TailFeatureFilter
+    f = TailFeatureFilter(freq=2, countmin_n=1 << 16, countmin_k=2)
+
+    def batch(rows):
+        off = np.cumsum([0] + [len(r) for r in rows]).astype(np.uint64)
+        idx = np.array([k for r in rows for k in r], dtype=np.uint64)
+        return np.ones(len(rows), np.float32), [dict(id=1, offset=off, index=idx, value=np.arange(len(idx), dtype=np.float32), binary=False)]
+
+    # key 5 appears three times in the first minibatch (kept at once), key 9 twice, key 11 once
+    y, (m,) = f.apply(batch([[5, 9], [5, 11], [5, 9]]))
+    assert list(m["offset"]) == [0, 1, 2, 3] and list(m["index"]) == [5, 5, 5] and list(m["value"]) == [0, 2, 4]
+    # second minibatch: 9 has now been seen three times, 11 twice
+    y, (m,) = f.apply(batch([[9], [11], []]))
+    assert list(m["offset"]) == [0, 1, 1, 1] and list(m["index"]) == [9]
+    y, (m,) = f.apply(batch([[11, 5]]))
+    assert list(m["index"]) == [11, 5] and f.dropped == 4
+
+
+def test_application_reads_tail_filter_from_the_configuration(tmp_path):
+    """The application (node layer only, counting engine) runs a job whose async_sgd block sets the filter."""
+    d = str(tmp_path)
+    _write_files(d, [120, 130])
+    conf = _conf(d, minibatch=50)
+    text = open(conf).read().replace("report_interval: 0.05", "report_interval: 0.05 tail_feature_freq: 2 countmin_n: 65536")
+    open(conf, "w").write(text)
+    procs = _launch(d, conf, 1, ["HSW"], 1, 1)
+    out = procs[0].communicate(timeout=120)[0]
+    assert procs[0].returncode == 0, out[-2000:]
+    assert _summary(out)[1:] == (250, 2)
