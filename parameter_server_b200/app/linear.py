@@ -192,15 +192,23 @@ def run_async_sgd(conf, verbose=True, engine: str = "gpu"):
         algo = "ftrl" if sgd.get("algo", "FTRL") == "FTRL" else ("adagrad" if sgd.get("ada_grad", "true") == "true" else "sgd")
         opt = OptimizerConfig(algo=algo, alpha=float(lr.get("alpha", 1)), beta=float(lr.get("beta", 1)), l1=l1, l2=l2,
                               lr_type="constant" if lr.get("type", "DECAY") == "CONSTANT" else "decay")
-        filters = sgd.get("push_filter", [])
-        filters = filters if isinstance(filters, list) else [filters]
+        def _filter_list(name):
+            v = sgd.get(name, [])
+            return v if isinstance(v, list) else [v]
+
         quant = "none"
         key_cache = False
-        for f in filters:
-            if f.get("type") == "FIXING_FLOAT":
-                quant = "int8" if int(f.get("num_bytes", 3)) <= 1 else "fp16"
-            if f.get("type") == "KEY_CACHING":
-                key_cache = True
+        for name in ("push_filter", "pull_filter"):
+            for f in _filter_list(name):
+                kind = f.get("type")
+                if kind == "FIXING_FLOAT" and name == "push_filter":
+                    quant = "int8" if int(f.get("num_bytes", 3)) <= 1 else "fp16"
+                elif kind == "KEY_CACHING":
+                    key_cache = True          # one switch: repeated key lists skip the keys (push) and the probes (pull)
+                elif rank == 0 and verbose:
+                    # pulled weights travel as fp32, nothing is compressed on NVLink, and the gradient never
+                    # leaves the fused kernel between its computation and the push: these have no place here
+                    print(f"note: {name} {kind} is not applied by the GPU application", flush=True)
         max_nnz = int(os.environ.get("PSB_MAX_NNZ_PER_ROW", "512")) * minibatch
         table_cap = 1 << int(os.environ.get("PSB_LOG2_TABLE", "22"))
         # two-sided exchange pull; the key-caching filter, when asked for, is decided inside that kernel
