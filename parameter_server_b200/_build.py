@@ -22,6 +22,7 @@ import shutil
 import subprocess
 import sys
 import sysconfig
+import time
 from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
@@ -232,10 +233,24 @@ def build_sanitized_binary(kinds: str = "address,undefined") -> Path:
 
 
 def build_all(force: bool = False, verbose: bool = False):
+    """Everything, and one line per artefact on stdout: whether it was compiled by this call or found
+    current (same source digest), so that a build log shows what the call did."""
+    t0 = time.time()
+    before = {p: (p.stat().st_mtime_ns if p.exists() else None) for p in _artefacts()}
     a = build_cuda(force=force, verbose=verbose)
     b = build_core(force=force)
     build_static()
+    for p in _artefacts():
+        now = p.stat().st_mtime_ns if p.exists() else None
+        what = "missing" if now is None else ("built" if now != before[p] else "up to date")
+        print(f"[build] {p.relative_to(PKG.parent)}: {what}" + (f", {p.stat().st_size} bytes" if now else ""))
+    n_cu = len(list((CSRC / "cuda").glob("*.cu")))
+    print(f"[build] {n_cu} CUDA sources for sm_100a ({' '.join(NVCC_FLAGS[:4])} ...), {time.time() - t0:.1f} s")
     return a, b
+
+
+def _artefacts():
+    return [cuda_lib_path(), core_lib_path(), PKG / "bin" / "psb_linear", PKG / "lib" / "libpsb.a", PKG / "lib" / "libpsbmain.a"]
 
 
 if __name__ == "__main__":
