@@ -31,7 +31,8 @@ def _files(conf_data) -> List[str]:
     pats = conf_data.get("file", [])
     pats = pats if isinstance(pats, list) else [pats]
     hdfs = conf_data.get("hdfs")          # data { hdfs { home ugi namenode } }: the files are read through `hadoop fs`
-    return list(core.search_files(pats, hdfs if isinstance(hdfs, dict) else None))
+    # format BIN: a matrix x is a handful of files (x.index, x.offset, x.label, x.info, ...); the search returns x
+    return list(core.search_files(pats, hdfs if isinstance(hdfs, dict) else None, conf_data.get("format", "TEXT")))
 
 
 def _penalty(conf):

@@ -96,6 +96,15 @@ class NullEngine(Engine):
             f.write("")
 
 
+def make_reader(files: List[str], data_format: str, text: str):
+    """The minibatch source of a workload: mapped binary matrices for ``format: BIN`` (no parsing), the C++
+    stream reader for text and record files. Both give ``read_matrices(n) -> (labels, [csr dict]) | None``."""
+    if data_format == "BIN":
+        from ..utils.binfmt import BinReader
+        return BinReader(files)
+    return core.StreamReader(files, data_format, text, True)
+
+
 class TailFeatureFilter:
     """Drops rare features from the minibatches before they reach the device: the loader-side count-min
     filter of the reference's ``MinibatchReader`` (``learner/sgd.h:88-91,123-134``). Every minibatch adds the
@@ -371,7 +380,7 @@ def run_lockstep_worker_loop(nodes: RankNodes, engine: Engine, *, minibatch: int
                     cur = state.workloads.get(timeout=idle_wait) if idle_wait else state.workloads.get_nowait()
                 except queue.Empty:
                     break
-                reader = core.StreamReader(cur.files, data_format, text, True)
+                reader = make_reader(cur.files, data_format, text)
                 if announce and files_done == 0:
                     print(f"{announce} first workload {cur.files[0]}", flush=True)
             got = reader.read_matrices(minibatch)

@@ -123,15 +123,16 @@ void BindApp(py::module& m) {
   m.def("text_to_records", [](const std::vector<std::string>& files, const std::string& text, const std::string& out) {
     return textToRecords(MakeData(files, "TEXT", text, false, -1), out);
   });
-  m.def("search_files", [](const std::vector<std::string>& patterns, py::object hdfs) {
+  m.def("search_files", [](const std::vector<std::string>& patterns, py::object hdfs, const std::string& format) {
     DataConfig d; d.file = patterns;
+    if (format == "BIN") d.format = DataConfig::BIN;
     if (!hdfs.is_none()) {
       py::dict h = hdfs.cast<py::dict>();
       auto get = [&](const char* k) { return h.contains(k) ? py::str(h[k]).cast<std::string>() : std::string(); };
       d.has_hdfs = true; d.hdfs.home = get("home"); d.hdfs.ugi = get("ugi"); d.hdfs.namenode = get("namenode");
     }
     return searchFiles(d).file;
-  }, py::arg("patterns"), py::arg("hdfs") = py::none(),
+  }, py::arg("patterns"), py::arg("hdfs") = py::none(), py::arg("format") = "TEXT",
      "files matching the patterns (regular expression in the file part); with hdfs={home, ugi, namenode} the "
      "patterns name HDFS files, the names returned start with hdfs:// and every reader of this process opens "
      "such names through `hadoop fs -cat`");

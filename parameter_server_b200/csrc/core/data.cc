@@ -475,6 +475,24 @@ DataConfig searchFiles(const DataConfig& config) {
       continue;
     }
     if (File::exists(pat)) { out.file.push_back(pat); continue; }
+    if (config.format == DataConfig::BIN) {
+      // a binary matrix x is the files x.index, x.offset, x.label, x.info (and x.value): the pattern names x
+      static const char* kSuffix[] = {".index", ".offset", ".value", ".label", ".info"};
+      if (File::exists(pat + ".info")) { out.file.push_back(pat); continue; }
+      const std::string dir = getPath(pat);
+      std::regex re;
+      try { re = std::regex(getFilename(pat)); } catch (const std::regex_error&) { continue; }
+      for (std::string f : readFilenamesInDirectory(dir)) {
+        for (const char* suf : kSuffix) {
+          const size_t n = strlen(suf);
+          if (f.size() > n && f.compare(f.size() - n, n, suf) == 0) { f.resize(f.size() - n); break; }
+        }
+        const std::string full = dir + "/" + f;
+        if (std::regex_match(f, re) && std::find(out.file.begin(), out.file.end(), full) == out.file.end())
+          out.file.push_back(full);
+      }
+      continue;
+    }
     if (s3file(pat)) {
       // the bucket's listing for the directory part, objects whose file name matches the pattern
       const std::string dir_name = getPath(pat);
@@ -550,6 +568,7 @@ void StreamReader<V>::init(const DataConfig& data) {
   next_file_ = 0;
   file_.reset();
   record_.reset();
+  bin_.reset();
   line_.resize(60 * 1024);
   if (data_.format == DataConfig::TEXT) parser_.Init(data_.text, data_.ignore_feature_group);
 }
@@ -569,7 +588,85 @@ bool StreamReader<V>::openNextFile() {
 }
 
 template <typename V>
+bool StreamReader<V>::openNextBin() {
+  while (next_file_ < (int)data_.file.size()) {
+    const std::string name = data_.file[next_file_++];
+    lines_in_file_ = 0;
+    std::string info;
+    auto b = std::make_unique<BinFiles>();
+    if (readFileToString(name + ".info", &info)) {
+      bool binary = false;
+      for (const std::string& line : split(info, '\n', true)) {
+        const size_t colon = line.find(':');
+        if (colon == std::string::npos) continue;
+        std::istringstream k(line.substr(0, colon)), v(line.substr(colon + 1));
+        std::string key, val;
+        k >> key; v >> val;
+        if (key == "sizeof_index") b->sizeof_index = atoi(val.c_str());
+        else if (key == "sizeof_value") b->sizeof_value = atoi(val.c_str());
+        else if (key == "bool_value") binary = val == "true";
+      }
+      b->offset.reset(File::open(name + ".offset", "r"));
+      b->index.reset(File::open(name + ".index", "r"));
+      b->label.reset(File::open(name + ".label", "r"));
+      if (!binary) b->value.reset(File::open(name + ".value", "r"));
+      uint64_t first = 0;
+      const bool sizes_ok = (b->sizeof_index == 4 || b->sizeof_index == 8) && (b->sizeof_value == 4 || b->sizeof_value == 8);
+      if (sizes_ok && b->offset && b->index && b->label && (binary || b->value) && b->offset->read(&first, 8) == 8) {
+        b->prev_offset = first;
+        bin_ = std::move(b);
+        return true;
+      }
+    }
+    PS_LOG(WARN) << "cannot open the binary matrix " << name;
+  }
+  return false;
+}
+
+template <typename V>
+bool StreamReader<V>::nextBinExample(Example* ex) {
+  while (true) {
+    if (!bin_ && !openNextBin()) return false;
+    uint64_t next = 0;
+    const bool limit = data_.max_num_lines_per_file >= 0 && (int)lines_in_file_ >= data_.max_num_lines_per_file;
+    if (!limit && bin_->offset->read(&next, 8) == 8 && next >= bin_->prev_offset) {
+      const size_t k = next - bin_->prev_offset;
+      bin_->prev_offset = next;
+      ++lines_in_file_;
+      double lab = 0;
+      if (bin_->label->read(&lab, 8) != 8) lab = 0;
+      ex->Clear();
+      ex->add_slot(0)->val.push_back((float)lab);
+      Slot* fea = ex->add_slot(1);
+      fea->key.resize(k);
+      bool ok = true;
+      if (bin_->sizeof_index == 8) {
+        ok = bin_->index->read(fea->key.data(), 8 * k) == 8 * k;
+      } else {
+        std::vector<uint32_t> narrow(k);
+        ok = bin_->index->read(narrow.data(), 4 * k) == 4 * k;
+        for (size_t i = 0; i < k; ++i) fea->key[i] = narrow[i];
+      }
+      if (ok && bin_->value) {
+        fea->val.resize(k);
+        if (bin_->sizeof_value == 4) {
+          ok = bin_->value->read(fea->val.data(), 4 * k) == 4 * k;
+        } else {
+          std::vector<double> wide(k);
+          ok = bin_->value->read(wide.data(), 8 * k) == 8 * k;
+          for (size_t i = 0; i < k; ++i) fea->val[i] = (float)wide[i];
+        }
+      }
+      if (ok) return true;
+      PS_LOG(WARN) << "the binary matrix " << data_.file[next_file_ - 1] << " ends inside a row";
+    }
+    bin_.reset();  // end of this matrix
+  }
+}
+
+template <typename V>
 bool StreamReader<V>::nextExample(Example* ex) {
+  if (data_.format == DataConfig::BIN) return nextBinExample(ex);
   while (true) {
     if (!file_ && !openNextFile()) return false;
     bool limit = data_.max_num_lines_per_file >= 0 && (int)lines_in_file_ >= data_.max_num_lines_per_file;
@@ -586,8 +683,6 @@ bool StreamReader<V>::nextExample(Example* ex) {
       } else if (data_.format == DataConfig::PROTO) {
         ++lines_in_file_;
         if (record_->ReadProtocolMessage(ex)) return true;
-      } else {
-        PS_CHECK(false) << "binary matrix files are read with SArray::ReadFromFile";
       }
     }
     file_.reset();  // end of this file

@@ -285,6 +285,17 @@ class StreamReader {
   size_t lines_in_file_ = 0;
   std::unique_ptr<File> file_;
   std::unique_ptr<RecordReader> record_;
+  // format BIN: a matrix x is x.offset (uint64 row offsets), x.index (uint32 or uint64 columns), x.label
+  // (float64), x.value (float32 or float64, absent for binary matrices) and the text x.info; rows are read
+  // one after another from the four streams
+  struct BinFiles {
+    std::unique_ptr<File> offset, index, label, value;
+    int sizeof_index = 4, sizeof_value = 8;
+    uint64_t prev_offset = 0;
+  };
+  std::unique_ptr<BinFiles> bin_;
+  bool openNextBin();
+  bool nextBinExample(Example* ex);
   ExampleParser parser_;
   std::vector<char> line_;
   uint64_t hash_kernel_ = ReaderFlags::get().hash_kernel;

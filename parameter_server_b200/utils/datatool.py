@@ -4,7 +4,9 @@
                ``data/show_example.h:8-18``;
 * ``convert``  text files -> one record file of serialised examples plus ``<output>.info`` with the per-slot
                statistics (what ``data/text2proto.h:4-39`` sketches): ``<output>.recordio`` can then be named in a
-               configuration with ``format: PROTO``.
+               configuration with ``format: PROTO``. ``-to bin`` writes a binary matrix instead
+               (``<output>.index .offset .label [.value] .info``, 64-bit ids): name ``<output>`` with ``format: BIN``
+               and the GPU application maps it and reads minibatches without parsing.
 
     python -m parameter_server_b200.utils.datatool show -input part-0 -format libsvm -n 3
     python -m parameter_server_b200.utils.datatool convert -input 'data/part-.*' -output data/all -format criteo
@@ -24,10 +26,13 @@ def _args(argv):
     ap.add_argument("-format", "--format", default="libsvm",
                     help="libsvm, adfea, terafea, criteo, vw, dense, sparse, sparse_binary")
     ap.add_argument("-n", "--n", type=int, default=3, help="show: how many examples")
+    ap.add_argument("-to", "--to", default="recordio", choices=["recordio", "bin"],
+                    help="convert: record file of examples, or a binary matrix (format: BIN, read without parsing)")
     return ap.parse_args(argv)
 
 
-def show(args, out=sys.stdout) -> int:
+def show(args, out=None) -> int:
+    out = out or sys.stdout
     from ..system import core
     fmt = args.format.upper()
     lines = sys.stdin if args.input == "stdin" else open(args.input)
@@ -43,12 +48,26 @@ def show(args, out=sys.stdout) -> int:
     return shown
 
 
-def convert(args, out=sys.stdout) -> int:
+def convert(args, out=None) -> int:
+    out = out or sys.stdout
     from ..system import core
     if not args.output:
         raise SystemExit("convert needs -output")
     fmt = args.format.upper()
     files = list(core.search_files([args.input]))
+    if args.to == "bin":
+        from .binfmt import BinWriter
+        w = BinWriter(args.output)
+        reader = core.StreamReader(files, "TEXT", fmt, True)
+        while True:
+            got = reader.read_matrices(65536)
+            if got is None:
+                break
+            if len(got[0]) and got[1]:
+                w.add(got)
+        w.close()
+        print(f"{w.rows} examples, {w.nnz} nonzeros from {len(files)} file(s) -> {args.output}.{{index,offset,label,info}}", file=out)
+        return w.rows
     n = core.text_to_records(files, fmt, args.output + ".recordio")
     info = core.SlotReader(files, fmt, "").read()
     with open(args.output + ".info", "w") as f:

@@ -83,3 +83,48 @@ def test_binary_matrix_files_round_trip(tmp_path):
     ex = core.parse_example(first, "SPARSE")
     got = np.concatenate([ex[g]["key"] for g in sorted(k for k in ex if isinstance(k, int))]) if ex else []
     assert sorted(int(k) for k in got) == sorted(X[0].indices.tolist())
+
+
+def test_bin_reader_and_writer(tmp_path, capsys):
+    """Minibatches from mapped binary matrices: the reference's MATLAB layout (32-bit ids, float64 values) and
+    the converter's (64-bit ids, float32 values); rows, offsets and values match the matrix; a minibatch stays
+    valid while the next one is read."""
+    from parameter_server_b200.utils import binfmt, datatool
+    rng = np.random.default_rng(0)
+    X = sp.random(300, 5000, density=0.01, random_state=1, format="csr", dtype=np.float64)
+    X.data = np.round(X.data * 8 + 1) / 4
+    y = np.where(rng.random(300) < 0.5, 1.0, -1.0)
+    binfmt.mat2bin(str(tmp_path / "a"), y, X)
+    r = binfmt.BinReader([str(tmp_path / "a.index"), str(tmp_path / "a.offset"), str(tmp_path / "a.info")])
+    assert r.names == [str(tmp_path / "a")]
+    first = r.read_matrices(128)
+    second = r.read_matrices(128)
+    Xs = X.copy(); Xs.sort_indices()
+    for k, (yy, (m,)) in enumerate([first, second]):        # `first` was not overwritten by reading `second`
+        r0, r1 = k * 128, (k + 1) * 128
+        assert np.array_equal(yy, y[r0:r1].astype(np.float32))
+        assert np.array_equal(m["offset"], (Xs.indptr[r0:r1 + 1] - Xs.indptr[r0]).astype(np.uint64))
+        assert np.array_equal(m["index"], Xs.indices[Xs.indptr[r0]:Xs.indptr[r1]].astype(np.uint64))
+        assert np.allclose(m["value"], Xs.data[Xs.indptr[r0]:Xs.indptr[r1]]) and not m["binary"]
+    third = r.read_matrices(128)
+    assert len(third[0]) == 300 - 256 and r.read_matrices(128) is None
+    # text -> binary matrix with 64-bit ids, and back
+    big = (1 << 40) + 5
+    (tmp_path / "part-0").write_text(f"1 3:1 {big}:1\n-1 2:1\n")
+    (tmp_path / "part-1").write_text("1 9:1\n")
+    assert datatool.main(["convert", "-input", str(tmp_path / "part-.*"), "-output", str(tmp_path / "all"), "-to", "bin"]) == 0
+    assert "3 examples, 4 nonzeros" in capsys.readouterr().out
+    yy, (m,) = binfmt.BinReader([str(tmp_path / "all")]).read_matrices(10)
+    assert list(yy) == [1, -1, 1] and list(m["index"]) == [3, big, 2, 9] and list(m["offset"]) == [0, 2, 3, 4]
+    # the C++ stream reader (what the CPU nodes use) reads both layouts row by row
+    from parameter_server_b200.system import core
+    y2, mats = core.StreamReader([str(tmp_path / "all")], "BIN", "LIBSVM", True).read_matrices(10)
+    assert list(y2) == [1, -1, 1] and list(mats[0]["index"]) == [3, big, 2, 9] and list(mats[0]["offset"]) == [0, 2, 3, 4]
+    assert core.search_files([str(tmp_path / "a.*")], None, "BIN") == [str(tmp_path / "a"), str(tmp_path / "all")]
+    rd = core.StreamReader([str(tmp_path / "a")], "BIN", "LIBSVM", True)
+    y3, mats = rd.read_matrices(200)
+    assert np.array_equal(y3, y[:200].astype(np.float32))
+    assert np.array_equal(mats[0]["index"], Xs.indices[:Xs.indptr[200]].astype(np.uint64))
+    assert np.allclose(mats[0]["value"], Xs.data[:Xs.indptr[200]])
+    y4, _ = rd.read_matrices(200)
+    assert len(y4) == 100 and rd.read_matrices(200) is None

@@ -236,6 +236,26 @@ def test_reader_flags_on_the_command_line(data, tmp_path):
     assert "loaded 800 examples" in res["H"].stdout, res["H"].stdout[:600]
 
 
+def test_training_data_as_binary_matrices(data, tmp_path):
+    """format: BIN: the text files converted to binary matrices train the same model family (CPU nodes as OS
+    processes); one workload per matrix."""
+    from parameter_server_b200 import _build
+    from parameter_server_b200.utils import datatool
+    bindir = tmp_path / "bin"
+    bindir.mkdir()
+    for i, f in enumerate(data["train_files"]):
+        assert datatool.main(["convert", "-input", f, "-output", str(bindir / f"part-{i}"), "-format", "sparse_binary", "-to", "bin"]) == 0
+    conf = tmp_path / "sgd.conf"
+    conf.write_text(CONF_SGD.format(train=str(bindir), out=str(tmp_path), algo="FTRL", filters="")
+                    .replace("format: TEXT text: SPARSE_BINARY", "format: BIN", 1))
+    res = launch_local_processes(2, 2, [str(_build.PKG / "bin" / "psb_linear"), "-app_file", str(conf)], timeout=180)
+    for nid, r in res.items():
+        assert r.returncode == 0, (nid, r.stdout[-2000:])
+    w = _read_model(str(tmp_path / "model_S*"))
+    y, m = _score(data["train_files"], w)
+    assert core.evaluate(y, m)["auc"] > 0.68
+
+
 def test_darlin_processes_start_reliably(data, tmp_path):
     """Twenty start-ups of 1 scheduler + 2 servers + 2 workers as OS processes: every node
     must be a member of the groups before the scheduler's first group task goes out (a node

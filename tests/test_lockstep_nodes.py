@@ -154,3 +154,21 @@ def test_application_reads_tail_filter_from_the_configuration(tmp_path):
     out = procs[0].communicate(timeout=120)[0]
     assert procs[0].returncode == 0, out[-2000:]
     assert _summary(out)[1:] == (250, 2)
+
+
+def test_application_reads_binary_matrices(tmp_path):
+    """format: BIN in the data section: one workload per matrix (not per companion file), minibatches are slices
+    of the mapped files (node layer with the counting engine)."""
+    from parameter_server_b200.utils import datatool
+    d = str(tmp_path)
+    _write_files(d, [120, 130])
+    for i in range(2):
+        assert datatool.main(["convert", "-input", f"{d}/part-0{i}", "-output", f"{d}/bin-{i}", "-to", "bin"]) == 0
+    conf = _conf(d, minibatch=50)
+    text = open(conf).read().replace('format: TEXT text: LIBSVM file: "%s/part-.*"' % d, 'format: BIN file: "%s/bin-.*"' % d)
+    assert "format: BIN" in text
+    open(conf, "w").write(text)
+    procs = _launch(d, conf, 1, ["HSW"], 1, 1)
+    out = procs[0].communicate(timeout=120)[0]
+    assert procs[0].returncode == 0, out[-2000:]
+    assert _summary(out)[1:] == (250, 2)
