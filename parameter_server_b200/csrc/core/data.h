@@ -34,6 +34,26 @@ inline std::string join(const std::vector<std::string>& v, const std::string& de
 // strict numeric conversions: the whole token must parse
 inline bool strtofloat(const char* s, float* v) {
   if (!s || !*s) return false;
+  // plain decimals ("1", "-1", "0.25", up to 9 digits in all) are most of every data file: they need no
+  // locale-aware parser; anything else (exponents, inf, long mantissas) goes to strtof
+  {
+    const char* p = s;
+    bool neg = false;
+    if (*p == '-') { neg = true; ++p; } else if (*p == '+') { ++p; }
+    uint32_t mant = 0;
+    int digits = 0, frac = 0;
+    while (*p >= '0' && *p <= '9' && digits < 9) { mant = mant * 10 + (uint32_t)(*p - '0'); ++p; ++digits; }
+    if (*p == '.') {
+      ++p;
+      while (*p >= '0' && *p <= '9' && digits < 9) { mant = mant * 10 + (uint32_t)(*p - '0'); ++p; ++digits; ++frac; }
+    }
+    if (*p == '\0' && digits > 0) {
+      static const double kPow10[10] = {1, 1e1, 1e2, 1e3, 1e4, 1e5, 1e6, 1e7, 1e8, 1e9};
+      const double x = (double)mant / kPow10[frac];     // exact operands; the double quotient then rounds to float
+      *v = (float)(neg ? -x : x);
+      return true;
+    }
+  }
   char* end; *v = strtof(s, &end); return *end == '\0';
 }
 inline bool strtoi32(const char* s, int32_t* v) {
@@ -42,6 +62,11 @@ inline bool strtoi32(const char* s, int32_t* v) {
 }
 inline bool strtou64(const char* s, uint64_t* v) {
   if (!s || !*s) return false;
+  // up to 19 digits cannot overflow 64 bits
+  uint64_t x = 0;
+  const char* p = s;
+  while (*p >= '0' && *p <= '9' && p - s < 19) { x = x * 10 + (uint64_t)(*p - '0'); ++p; }
+  if (*p == '\0') { *v = x; return true; }
   char* end; *v = strtoull(s, &end, 10); return *end == '\0';
 }
 
