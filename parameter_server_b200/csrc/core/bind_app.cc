@@ -77,6 +77,7 @@ void BindApp(py::module& m) {
            }), py::arg("files"), py::arg("format") = "TEXT", py::arg("text") = "LIBSVM",
            py::arg("ignore_feature_group") = false, py::arg("max_num_lines_per_file") = -1)
       .def("set_hash_kernel", &SR::set_hash_kernel)
+      .def("set_parse_threads", &SR::set_parse_threads)
       .def("read_matrices", [](SR& r, uint32_t n) -> py::object {
         SArray<float> y;
         std::vector<std::shared_ptr<SparseMatrix<uint64_t, float>>> mats;

@@ -569,6 +569,8 @@ void StreamReader<V>::init(const DataConfig& data) {
   file_.reset();
   record_.reset();
   bin_.reset();
+  parsed_.clear();
+  parsed_pos_ = 0;
   line_.resize(60 * 1024);
   if (data_.format == DataConfig::TEXT) parser_.Init(data_.text, data_.ignore_feature_group);
 }
@@ -664,8 +666,44 @@ bool StreamReader<V>::nextBinExample(Example* ex) {
   }
 }
 
+// Reads the lines of up to `num_examples` examples (one thread: the file is a stream) and parses them on
+// parse_threads_ threads, each taking a contiguous share of the lines; parsed_ keeps their order.
+template <typename V>
+void StreamReader<V>::parseAhead(uint32_t num_examples) {
+  parsed_.clear();
+  parsed_pos_ = 0;
+  std::vector<std::string> lines;
+  lines.reserve(num_examples);
+  while (lines.size() < num_examples) {
+    if (!file_ && !openNextFile()) break;
+    const bool limit = data_.max_num_lines_per_file >= 0 && (int)lines_in_file_ >= data_.max_num_lines_per_file;
+    if (!limit && file_->readLine(line_.data(), (int)line_.size())) {
+      ++lines_in_file_;
+      lines.emplace_back(line_.data());
+      continue;
+    }
+    file_.reset();  // end of this file
+  }
+  if (lines.empty()) return;
+  const int T = (int)std::min<size_t>(parse_threads_, (lines.size() + 255) / 256);
+  std::vector<std::vector<Example>> part(T);
+  auto work = [&](int t) {
+    const size_t b = lines.size() * t / T, e = lines.size() * (t + 1) / T;
+    part[t].reserve(e - b);
+    Example ex;
+    for (size_t i = b; i < e; ++i)
+      if (parser_.ToProto(&lines[i][0], &ex)) part[t].push_back(std::move(ex));
+  };
+  std::vector<std::thread> threads;
+  for (int t = 1; t < T; ++t) threads.emplace_back(work, t);
+  work(0);
+  for (auto& th : threads) th.join();
+  for (auto& p : part) for (auto& ex : p) parsed_.push_back(std::move(ex));
+}
+
 template <typename V>
 bool StreamReader<V>::nextExample(Example* ex) {
+  if (parsed_pos_ < parsed_.size()) { *ex = std::move(parsed_[parsed_pos_++]); return true; }
   if (data_.format == DataConfig::BIN) return nextBinExample(ex);
   while (true) {
     if (!file_ && !openNextFile()) return false;
@@ -700,6 +738,8 @@ bool StreamReader<V>::readMatrices(uint32_t num_examples, SArray<V>* label,
   if (examples) examples->clear();
   uint32_t n = 0;
   Example ex;
+  if (data_.format == DataConfig::TEXT && parse_threads_ > 1 && num_examples >= 256 && parsed_pos_ >= parsed_.size())
+    parseAhead(num_examples);
   while (n < num_examples && nextExample(&ex)) {
     if (examples) examples->push_back(ex);
     bool has_label = false;

@@ -145,6 +145,7 @@ struct ReaderFlags {
   uint64_t hash_kernel = 0;
   bool shuffle_fea_id = false;
   int line_limit = 0;
+  int parse_threads = 2;       // -num_threads: threads that parse the lines of a text minibatch
   static ReaderFlags& get() { static ReaderFlags f; return f; }
 };
 
@@ -296,6 +297,8 @@ class StreamReader {
   explicit StreamReader(const DataConfig& data) { init(data); }
   void init(const DataConfig& data);
   void set_hash_kernel(uint64_t modulo) { hash_kernel_ = modulo; }
+  // Text files: the lines of a minibatch are parsed by this many threads (the order of the examples is kept).
+  void set_parse_threads(int n) { parse_threads_ = std::max(1, n); }
   // reads up to num_examples; returns false when no example was read
   bool readMatrices(uint32_t num_examples, SArray<V>* label, std::vector<std::shared_ptr<SparseMatrix<uint64_t, V>>>* mats,
                     std::vector<Example>* examples = nullptr);
@@ -324,6 +327,11 @@ class StreamReader {
   ExampleParser parser_;
   std::vector<char> line_;
   uint64_t hash_kernel_ = ReaderFlags::get().hash_kernel;
+  int parse_threads_ = ReaderFlags::get().parse_threads;
+  // examples parsed ahead by parseAhead(), handed out by nextExample() before it reads on
+  std::vector<Example> parsed_;
+  size_t parsed_pos_ = 0;
+  void parseAhead(uint32_t num_examples);
 };
 
 // ---------------------------------------------------------------- slot reader

@@ -25,6 +25,7 @@ void Postoffice::StartThreads() {
   if (opt_.hash_kernel) rf.hash_kernel = opt_.hash_kernel;
   if (opt_.shuffle_fea_id) rf.shuffle_fea_id = true;
   if (opt_.line_limit > 0) rf.line_limit = opt_.line_limit;
+  if (opt_.num_threads > 0) rf.parse_threads = opt_.num_threads;
   running_ = true;
   recv_thread_ = std::thread([this] { Recv(); });
   send_thread_ = std::thread([this] { Send(); });

@@ -280,7 +280,7 @@ def test_job_control_start_ls_kill_add_stop(data, tmp_path):
     exe = str(_build.PKG / "bin" / "psb_linear")
     conf = tmp_path / "sgd.conf"
     conf.write_text(CONF_SGD.format(train=data["train"], out=str(tmp_path), algo="FTRL", filters="")
-                    .replace("num_data_pass: 3", "num_data_pass: 40"))
+                    .replace("num_data_pass: 3", "num_data_pass: 200"))
     job = Job(str(tmp_path / "state.json"))
     nodes = job.start([exe, "-app_file", str(conf)], num_servers=2, num_workers=2, log_dir=str(tmp_path / "logs"))
     assert [n["id"] for n in nodes] == ["H", "S0", "S1", "W0", "W1"]
@@ -296,7 +296,7 @@ def test_job_control_start_ls_kill_add_stop(data, tmp_path):
     job.stop()
     assert not os.path.exists(str(tmp_path / "state.json"))
     # stop: a long job is ended by hand
-    conf.write_text(conf.read_text().replace("num_data_pass: 40", "num_data_pass: 100000"))
+    conf.write_text(conf.read_text().replace("num_data_pass: 200", "num_data_pass: 100000"))
     job = Job(str(tmp_path / "state.json"))
     job.start([exe, "-app_file", str(conf)], num_servers=1, num_workers=1, log_dir=str(tmp_path / "logs2"))
     time.sleep(0.5)
