@@ -456,9 +456,10 @@ def main(argv: Optional[List[str]] = None):
     ap.add_argument("-hash_kernel", "--hash_kernel", type=int, default=0, help=">0: feature ids are taken modulo this")
     ap.add_argument("-shuffle_fea_id", "--shuffle_fea_id", action="store_true", help="TERAFEA ids are mixed by a hash")
     ap.add_argument("-line_limit", "--line_limit", type=int, default=0, help=">0: lines read per text file")
+    ap.add_argument("-num_threads", "--num_threads", type=int, default=0, help="threads that parse a text minibatch (default 2)")
     args, _ = ap.parse_known_args(argv)
-    if args.hash_kernel or args.shuffle_fea_id or args.line_limit:
-        core.set_reader_flags(args.hash_kernel, args.shuffle_fea_id, args.line_limit)
+    if args.hash_kernel or args.shuffle_fea_id or args.line_limit or args.num_threads:
+        core.set_reader_flags(args.hash_kernel, args.shuffle_fea_id, args.line_limit, args.num_threads)
     text = (open(args.app_file).read() if args.app_file else "") + args.app_conf
     conf = core.parse_text_proto(text)
     conf["_checkpoint_in"], conf["_checkpoint_out"] = args.checkpoint_in, args.checkpoint_out

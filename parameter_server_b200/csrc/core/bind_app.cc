@@ -138,11 +138,12 @@ void BindApp(py::module& m) {
      "patterns name HDFS files, the names returned start with hdfs:// and every reader of this process opens "
      "such names through `hadoop fs -cat`");
   m.def("hadoop_fs", []() { return currentHadoopFS(); }, "the command prefix used for hdfs:// files");
-  m.def("set_reader_flags", [](uint64_t hash_kernel, bool shuffle_fea_id, int line_limit) {
+  m.def("set_reader_flags", [](uint64_t hash_kernel, bool shuffle_fea_id, int line_limit, int parse_threads) {
     ReaderFlags& f = ReaderFlags::get();
     f.hash_kernel = hash_kernel; f.shuffle_fea_id = shuffle_fea_id; f.line_limit = line_limit;
-  }, py::arg("hash_kernel") = 0, py::arg("shuffle_fea_id") = false, py::arg("line_limit") = 0,
-     "process-wide defaults of the readers made afterwards: the node flags -hash_kernel, -shuffle_fea_id, -line_limit");
+    if (parse_threads > 0) f.parse_threads = parse_threads;
+  }, py::arg("hash_kernel") = 0, py::arg("shuffle_fea_id") = false, py::arg("line_limit") = 0, py::arg("parse_threads") = 0,
+     "process-wide defaults of the readers made afterwards: the node flags -hash_kernel, -shuffle_fea_id, -line_limit, -num_threads (0 keeps the current number)");
 
   m.def("localize", [](py::array_t<uint64_t, py::array::c_style | py::array::forcecast> offset,
                        py::array_t<uint64_t, py::array::c_style | py::array::forcecast> index, int threads) {
