@@ -191,6 +191,9 @@ class BinWriter:
 
     def __init__(self, name: str):
         self.name = name
+        import os
+        if os.path.dirname(name):
+            os.makedirs(os.path.dirname(name), exist_ok=True)
         self.f = {k: open(name + "." + k, "wb") for k in ("index", "offset", "value", "label")}
         np.zeros(1, np.uint64).tofile(self.f["offset"])
         self.rows, self.nnz, self.binary, self.max_col = 0, 0, True, 0

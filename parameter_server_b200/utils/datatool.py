@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 
 
@@ -55,6 +56,8 @@ def convert(args, out=None) -> int:
         raise SystemExit("convert needs -output")
     fmt = args.format.upper()
     files = list(core.search_files([args.input]))
+    if os.path.dirname(args.output):
+        os.makedirs(os.path.dirname(args.output), exist_ok=True)
     if args.to == "bin":
         from .binfmt import BinWriter
         w = BinWriter(args.output)
