@@ -5,6 +5,7 @@
 //  * MurmurHash3 x86_32, x86_128 and x64_128 (public-domain algorithm by Austin
 //    Appleby, util/murmurhash3.h:29-33), written from the published algorithm.
 #pragma once
+#include <algorithm>
 #include <cstddef>
 #include <cstdint>
 #include <cstring>
@@ -49,119 +50,84 @@ inline uint32_t Unmask(uint32_t masked) { uint32_t r = masked - kMaskDelta; retu
 }  // namespace crc32c
 
 // ---------------------------------------------------------------- MurmurHash3
+// The three variants share one shape: the input is cut into stripes of L lanes (L = 1, 4 words of 32 bits, or
+// 2 words of 64 bits); lane j of a stripe is scrambled with its constants and folded into state word j, which
+// is then rotated, chained to its neighbour and stepped; a last, partial stripe is zero-padded and only
+// scrambled; the length is mixed in and the state words are cross-added around a finalising mix.
 namespace murmur {
-inline uint32_t rotl32(uint32_t x, int8_t r) { return (x << r) | (x >> (32 - r)); }
-inline uint64_t rotl64(uint64_t x, int8_t r) { return (x << r) | (x >> (64 - r)); }
-inline uint32_t fmix32(uint32_t h) { h ^= h >> 16; h *= 0x85ebca6b; h ^= h >> 13; h *= 0xc2b2ae35; h ^= h >> 16; return h; }
-inline uint64_t fmix64(uint64_t k) { k ^= k >> 33; k *= 0xff51afd7ed558ccdULL; k ^= k >> 33; k *= 0xc4ceb9fe1a85ec53ULL; k ^= k >> 33; return k; }
-inline uint32_t blk32(const uint8_t* p, int i) { uint32_t v; memcpy(&v, p + 4 * i, 4); return v; }
-inline uint64_t blk64(const uint8_t* p, int i) { uint64_t v; memcpy(&v, p + 8 * i, 8); return v; }
+template <typename W> inline W rotl(W x, int r) { return (W)((x << r) | (x >> (int(sizeof(W)) * 8 - r))); }
+inline uint32_t fmix(uint32_t h) { h ^= h >> 16; h *= 0x85ebca6b; h ^= h >> 13; h *= 0xc2b2ae35; h ^= h >> 16; return h; }
+inline uint64_t fmix(uint64_t k) { k ^= k >> 33; k *= 0xff51afd7ed558ccdULL; k ^= k >> 33; k *= 0xc4ceb9fe1a85ec53ULL; k ^= k >> 33; return k; }
+
+// little-endian word from `n` <= sizeof(W) bytes, the missing high bytes zero
+template <typename W> inline W load_le(const uint8_t* p, size_t n) {
+  W v = 0;
+  for (size_t i = 0; i < n; ++i) v |= (W)p[i] << (8 * i);
+  return v;
+}
+// a whole word (little-endian hosts)
+template <typename W> inline W load_word(const uint8_t* p) { W v; memcpy(&v, p, sizeof(W)); return v; }
+
+// W: state word; L: lanes. mul[j], mul[(j+1)%L] scramble lane j around a rotation by kr[j]; the state word is
+// then rotated by hr[j] and stepped to h * 5 + add[j].
+template <typename W, int L>
+struct Variant {
+  W mul[L];
+  int kr[L], hr[L];
+  uint32_t add[L];
+  W scramble(W k, int j) const { return (W)(rotl<W>((W)(k * mul[j]), kr[j]) * mul[(j + 1) % L]); }
+  void run(const void* key, int len, uint32_t seed, W* h) const {
+    const uint8_t* p = (const uint8_t*)key;
+    const size_t word = sizeof(W), stripe = word * L;
+    for (int j = 0; j < L; ++j) h[j] = seed;
+    size_t left = (size_t)len;
+    for (; left >= stripe; left -= stripe, p += stripe) {
+      for (int j = 0; j < L; ++j) {
+        h[j] ^= scramble(load_word<W>(p + word * j), j);
+        h[j] = rotl<W>(h[j], hr[j]);
+        if (L > 1) h[j] += h[(j + 1) % L];
+        h[j] = (W)(h[j] * 5 + add[j]);
+      }
+    }
+    // the ragged end: highest lane first, as the state words are not chained here the order does not matter
+    for (int j = L - 1; j >= 0; --j) {
+      if (left <= word * j) continue;
+      const size_t n = std::min(word, left - word * j);
+      h[j] ^= scramble(load_le<W>(p + word * j, n), j);
+    }
+    for (int j = 0; j < L; ++j) h[j] ^= (W)len;
+    for (int pass = 0; pass < 2; ++pass) {
+      for (int j = 1; j < L; ++j) h[0] += h[j];
+      for (int j = 1; j < L; ++j) h[j] += h[0];
+      if (pass == 0) for (int j = 0; j < L; ++j) h[j] = fmix(h[j]);
+    }
+  }
+};
 }  // namespace murmur
 
 inline void MurmurHash3_x86_32(const void* key, int len, uint32_t seed, void* out) {
   using namespace murmur;
-  const uint8_t* data = (const uint8_t*)key;
-  const int nblocks = len / 4;
-  uint32_t h1 = seed;
   const uint32_t c1 = 0xcc9e2d51, c2 = 0x1b873593;
-  for (int i = 0; i < nblocks; ++i) {
-    uint32_t k1 = blk32(data, i);
-    k1 *= c1; k1 = rotl32(k1, 15); k1 *= c2;
-    h1 ^= k1; h1 = rotl32(h1, 13); h1 = h1 * 5 + 0xe6546b64;
-  }
-  const uint8_t* tail = data + nblocks * 4;
-  uint32_t k1 = 0;
-  switch (len & 3) {
-    case 3: k1 ^= tail[2] << 16;  // fallthrough
-    case 2: k1 ^= tail[1] << 8;   // fallthrough
-    case 1: k1 ^= tail[0]; k1 *= c1; k1 = rotl32(k1, 15); k1 *= c2; h1 ^= k1;
-  }
-  h1 ^= len;
-  h1 = fmix32(h1);
-  *(uint32_t*)out = h1;
+  auto scramble = [&](uint32_t k) { return (uint32_t)(rotl<uint32_t>(k * c1, 15) * c2); };
+  const uint8_t* p = (const uint8_t*)key;
+  uint32_t h = seed;
+  size_t left = (size_t)len;
+  for (; left >= 4; left -= 4, p += 4) h = rotl<uint32_t>(h ^ scramble(load_word<uint32_t>(p)), 13) * 5 + 0xe6546b64;
+  if (left) h ^= scramble(load_le<uint32_t>(p, left));
+  *(uint32_t*)out = fmix(h ^ (uint32_t)len);
 }
 
 inline void MurmurHash3_x86_128(const void* key, const int len, uint32_t seed, void* out) {
-  using namespace murmur;
-  const uint8_t* data = (const uint8_t*)key;
-  const int nblocks = len / 16;
-  uint32_t h1 = seed, h2 = seed, h3 = seed, h4 = seed;
-  const uint32_t c1 = 0x239b961b, c2 = 0xab0e9789, c3 = 0x38b34ae5, c4 = 0xa1e38b93;
-  for (int i = 0; i < nblocks; ++i) {
-    uint32_t k1 = blk32(data, i * 4 + 0), k2 = blk32(data, i * 4 + 1);
-    uint32_t k3 = blk32(data, i * 4 + 2), k4 = blk32(data, i * 4 + 3);
-    k1 *= c1; k1 = rotl32(k1, 15); k1 *= c2; h1 ^= k1;
-    h1 = rotl32(h1, 19); h1 += h2; h1 = h1 * 5 + 0x561ccd1b;
-    k2 *= c2; k2 = rotl32(k2, 16); k2 *= c3; h2 ^= k2;
-    h2 = rotl32(h2, 17); h2 += h3; h2 = h2 * 5 + 0x0bcaa747;
-    k3 *= c3; k3 = rotl32(k3, 17); k3 *= c4; h3 ^= k3;
-    h3 = rotl32(h3, 15); h3 += h4; h3 = h3 * 5 + 0x96cd1c35;
-    k4 *= c4; k4 = rotl32(k4, 18); k4 *= c1; h4 ^= k4;
-    h4 = rotl32(h4, 13); h4 += h1; h4 = h4 * 5 + 0x32ac3b17;
-  }
-  const uint8_t* tail = data + nblocks * 16;
-  uint32_t k1 = 0, k2 = 0, k3 = 0, k4 = 0;
-  switch (len & 15) {
-    case 15: k4 ^= tail[14] << 16;  // fallthrough
-    case 14: k4 ^= tail[13] << 8;   // fallthrough
-    case 13: k4 ^= tail[12] << 0; k4 *= c4; k4 = rotl32(k4, 18); k4 *= c1; h4 ^= k4;  // fallthrough
-    case 12: k3 ^= tail[11] << 24;  // fallthrough
-    case 11: k3 ^= tail[10] << 16;  // fallthrough
-    case 10: k3 ^= tail[9] << 8;    // fallthrough
-    case 9: k3 ^= tail[8] << 0; k3 *= c3; k3 = rotl32(k3, 17); k3 *= c4; h3 ^= k3;    // fallthrough
-    case 8: k2 ^= tail[7] << 24;    // fallthrough
-    case 7: k2 ^= tail[6] << 16;    // fallthrough
-    case 6: k2 ^= tail[5] << 8;     // fallthrough
-    case 5: k2 ^= tail[4] << 0; k2 *= c2; k2 = rotl32(k2, 16); k2 *= c3; h2 ^= k2;    // fallthrough
-    case 4: k1 ^= tail[3] << 24;    // fallthrough
-    case 3: k1 ^= tail[2] << 16;    // fallthrough
-    case 2: k1 ^= tail[1] << 8;     // fallthrough
-    case 1: k1 ^= tail[0] << 0; k1 *= c1; k1 = rotl32(k1, 15); k1 *= c2; h1 ^= k1;
-  }
-  h1 ^= len; h2 ^= len; h3 ^= len; h4 ^= len;
-  h1 += h2; h1 += h3; h1 += h4; h2 += h1; h3 += h1; h4 += h1;
-  h1 = fmix32(h1); h2 = fmix32(h2); h3 = fmix32(h3); h4 = fmix32(h4);
-  h1 += h2; h1 += h3; h1 += h4; h2 += h1; h3 += h1; h4 += h1;
-  ((uint32_t*)out)[0] = h1; ((uint32_t*)out)[1] = h2; ((uint32_t*)out)[2] = h3; ((uint32_t*)out)[3] = h4;
+  static const murmur::Variant<uint32_t, 4> v = {{0x239b961b, 0xab0e9789, 0x38b34ae5, 0xa1e38b93},
+                                                 {15, 16, 17, 18}, {19, 17, 15, 13},
+                                                 {0x561ccd1b, 0x0bcaa747, 0x96cd1c35, 0x32ac3b17}};
+  v.run(key, len, seed, (uint32_t*)out);
 }
 
 inline void MurmurHash3_x64_128(const void* key, const int len, const uint32_t seed, void* out) {
-  using namespace murmur;
-  const uint8_t* data = (const uint8_t*)key;
-  const int nblocks = len / 16;
-  uint64_t h1 = seed, h2 = seed;
-  const uint64_t c1 = 0x87c37b91114253d5ULL, c2 = 0x4cf5ad432745937fULL;
-  for (int i = 0; i < nblocks; ++i) {
-    uint64_t k1 = blk64(data, i * 2 + 0), k2 = blk64(data, i * 2 + 1);
-    k1 *= c1; k1 = rotl64(k1, 31); k1 *= c2; h1 ^= k1;
-    h1 = rotl64(h1, 27); h1 += h2; h1 = h1 * 5 + 0x52dce729;
-    k2 *= c2; k2 = rotl64(k2, 33); k2 *= c1; h2 ^= k2;
-    h2 = rotl64(h2, 31); h2 += h1; h2 = h2 * 5 + 0x38495ab5;
-  }
-  const uint8_t* tail = data + nblocks * 16;
-  uint64_t k1 = 0, k2 = 0;
-  switch (len & 15) {
-    case 15: k2 ^= ((uint64_t)tail[14]) << 48;  // fallthrough
-    case 14: k2 ^= ((uint64_t)tail[13]) << 40;  // fallthrough
-    case 13: k2 ^= ((uint64_t)tail[12]) << 32;  // fallthrough
-    case 12: k2 ^= ((uint64_t)tail[11]) << 24;  // fallthrough
-    case 11: k2 ^= ((uint64_t)tail[10]) << 16;  // fallthrough
-    case 10: k2 ^= ((uint64_t)tail[9]) << 8;    // fallthrough
-    case 9: k2 ^= ((uint64_t)tail[8]) << 0; k2 *= c2; k2 = rotl64(k2, 33); k2 *= c1; h2 ^= k2;  // fallthrough
-    case 8: k1 ^= ((uint64_t)tail[7]) << 56;    // fallthrough
-    case 7: k1 ^= ((uint64_t)tail[6]) << 48;    // fallthrough
-    case 6: k1 ^= ((uint64_t)tail[5]) << 40;    // fallthrough
-    case 5: k1 ^= ((uint64_t)tail[4]) << 32;    // fallthrough
-    case 4: k1 ^= ((uint64_t)tail[3]) << 24;    // fallthrough
-    case 3: k1 ^= ((uint64_t)tail[2]) << 16;    // fallthrough
-    case 2: k1 ^= ((uint64_t)tail[1]) << 8;     // fallthrough
-    case 1: k1 ^= ((uint64_t)tail[0]) << 0; k1 *= c1; k1 = rotl64(k1, 31); k1 *= c2; h1 ^= k1;
-  }
-  h1 ^= len; h2 ^= len;
-  h1 += h2; h2 += h1;
-  h1 = fmix64(h1); h2 = fmix64(h2);
-  h1 += h2; h2 += h1;
-  ((uint64_t*)out)[0] = h1; ((uint64_t*)out)[1] = h2;
+  static const murmur::Variant<uint64_t, 2> v = {{0x87c37b91114253d5ULL, 0x4cf5ad432745937fULL}, {31, 33}, {27, 31},
+                                                 {0x52dce729, 0x38495ab5}};
+  v.run(key, len, seed, (uint64_t*)out);
 }
 
 }  // namespace PS
