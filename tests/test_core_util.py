@@ -19,6 +19,16 @@ def test_crc32c_and_murmur_known_vectors():
     assert core.murmurhash3_x86_32(b"hello, world", 0) == 0x149BBB7F
     assert core.murmurhash3_x64_128(b"", 0) == (0, 0)
     assert core.murmurhash3_x64_128(b"hello", 0) == (0xCBD8A7B341BD9B02, 0x5B1E906A48AE1D19)
+    # every tail length of the three variants (0..49 bytes, three seeds), against a digest taken from an
+    # implementation that had been checked against the published vectors above
+    import hashlib
+    data = bytes((i * 37 + 11) % 256 for i in range(80))
+    h = hashlib.sha256()
+    for n in range(50):
+        for seed in (0, 1, 512927377):
+            h.update(repr((core.murmurhash3_x86_32(data[:n], seed), core.murmurhash3_x86_128(data[:n], seed),
+                           core.murmurhash3_x64_128(data[:n], seed))).encode())
+    assert h.hexdigest() == "7675e6d440d3154dc82809d766e11cf38f3cf6a8e114f448534946f3f1745231"
     a, b = core.murmurhash3_x64_128(b"abcdefghijklmnopqrstuvwxyz", 512927377)
     assert (a, b) != core.murmurhash3_x64_128(b"abcdefghijklmnopqrstuvwxyy", 512927377)
 
