@@ -7,6 +7,9 @@
 #include <sys/socket.h>
 #include <unistd.h>
 
+#include <random>
+#include <set>
+
 namespace PS {
 
 Options Options::Parse(const std::vector<std::string>& args) {
@@ -80,6 +83,33 @@ void Options::InitFromEnv() {
 }
 
 int Env::FreePort() {
+  // A port that is free now and stays free until the caller binds it: taken from below the range that the
+  // kernel uses for the source ports of outgoing connections (a port from that range, found by binding port 0,
+  // can be grabbed by any connect() on the machine before the node that was promised it starts to listen).
+  static std::mutex mu;
+  static std::set<int> handed_out;
+  static std::mt19937 rng((unsigned)std::chrono::steady_clock::now().time_since_epoch().count() ^ (unsigned)getpid());
+  int low = 32768;
+  if (FILE* f = fopen("/proc/sys/net/ipv4/ip_local_port_range", "r")) {
+    int a = 0, b = 0;
+    if (fscanf(f, "%d %d", &a, &b) == 2 && a > 0) low = a;
+    fclose(f);
+  }
+  std::lock_guard<std::mutex> l(mu);
+  const int first = 10000;
+  for (int attempt = 0; low > first + 1000 && attempt < 200; ++attempt) {
+    const int port = first + (int)(rng() % (unsigned)(low - first));
+    if (handed_out.count(port)) continue;
+    int fd = socket(AF_INET, SOCK_STREAM, 0);
+    sockaddr_in addr; memset(&addr, 0, sizeof(addr));
+    addr.sin_family = AF_INET;
+    addr.sin_addr.s_addr = htonl(INADDR_ANY);
+    addr.sin_port = htons((uint16_t)port);
+    const bool ok = bind(fd, (sockaddr*)&addr, sizeof(addr)) == 0;
+    close(fd);
+    if (ok) { handed_out.insert(port); return port; }
+  }
+  // no room below the range: whatever the kernel gives
   int fd = socket(AF_INET, SOCK_STREAM, 0);
   sockaddr_in addr; memset(&addr, 0, sizeof(addr));
   addr.sin_family = AF_INET;

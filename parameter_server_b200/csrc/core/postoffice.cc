@@ -5,6 +5,12 @@
 
 namespace PS {
 
+namespace {
+// set on a thread that must not write to sockets itself: the van's poll thread while it runs the sink (if it
+// blocked on a peer whose poll thread is blocked on this node, neither would read again)
+thread_local bool tl_queue_only = false;
+}  // namespace
+
 Postoffice::Postoffice() : manager_(this) {}
 
 Postoffice::~Postoffice() {
@@ -20,6 +26,18 @@ Postoffice::~Postoffice() {
   if (recv_thread_.joinable()) recv_thread_.join();
 }
 
+void Postoffice::InstallSink() {
+  // over sockets the van's poll thread runs the receive path itself; the receive thread then only waits for
+  // the end (in-process nodes have no poll thread: their receive thread takes messages from the peer's push)
+  manager_.van().set_sink([this](const MessagePtr& m) {
+    if (!sink_open_) return;
+    tl_queue_only = true;
+    auto* copy = new Message(*m);
+    copy->recver = manager_.van().my_node().id;
+    if (!Incoming(copy)) sink_open_ = false;
+  });
+}
+
 void Postoffice::StartThreads() {
   ReaderFlags& rf = ReaderFlags::get();
   if (opt_.hash_kernel) rf.hash_kernel = opt_.hash_kernel;
@@ -27,12 +45,14 @@ void Postoffice::StartThreads() {
   if (opt_.line_limit > 0) rf.line_limit = opt_.line_limit;
   if (opt_.num_threads > 0) rf.parse_threads = opt_.num_threads;
   running_ = true;
+  manager_.van().enable_sink();
   recv_thread_ = std::thread([this] { Recv(); });
   send_thread_ = std::thread([this] { Send(); });
 }
 
 void Postoffice::Run(const Options& opt) {
   opt_ = opt;
+  InstallSink();
   manager_.Init(opt);
   StartThreads();
   manager_.Run(true);
@@ -40,6 +60,7 @@ void Postoffice::Run(const Options& opt) {
 
 void Postoffice::Start(const Options& opt) {
   opt_ = opt;
+  InstallSink();
   manager_.Init(opt);
   StartThreads();
   manager_.Run(false);
@@ -63,15 +84,39 @@ void Postoffice::Stop() {
   manager_.van().Destroy();
 }
 
+void Postoffice::SendNow(Message* msg) {
+  size_t bytes = 0;
+  manager_.van().Send(msg, &bytes);
+  if (msg->task.request) manager_.AddRequest(msg);
+}
+
 void Postoffice::Send() {
   while (true) {
     MessagePtr msg;
     sending_queue_.wait_and_pop(msg);
     if (msg->terminate) break;
-    size_t bytes = 0;
-    manager_.van().Send(msg.get(), &bytes);
-    if (msg->task.request) manager_.AddRequest(msg.get());
+    {
+      Lock l(send_mu_);
+      SendNow(msg.get());
+    }
+    --pending_sends_;
   }
+}
+
+void Postoffice::Dispatch(const MessagePtr& msg) {
+  // Nothing queued and nobody sending: this thread writes the message itself. A message that another
+  // thread queues in the meantime is not ordered against this one anyway; this thread's own earlier
+  // messages have left (they were sent here) or are still pending (then this one queues up behind them).
+  if (running_ && !tl_queue_only && pending_sends_.load() == 0 && send_mu_.try_lock()) {
+    if (pending_sends_.load() == 0) {
+      SendNow(msg.get());
+      send_mu_.unlock();
+      return;
+    }
+    send_mu_.unlock();
+  }
+  ++pending_sends_;
+  sending_queue_.push(msg);
 }
 
 void Postoffice::Queue(Message* raw) {
@@ -101,11 +146,11 @@ void Postoffice::Queue(Message* raw) {
       MessagePtr holder = it->second;
       pack_.erase(it);
       holder->task.task.push_back(t);
-      sending_queue_.push(holder);
+      Dispatch(holder);
       return;
     }
   }
-  sending_queue_.push(msg);
+  Dispatch(msg);
 }
 
 void Postoffice::Recv() {
@@ -113,20 +158,24 @@ void Postoffice::Recv() {
     auto msg = new Message();
     size_t bytes = 0;
     if (!manager_.van().Recv(msg, &bytes)) { delete msg; break; }
-    if (!msg->task.control && msg->task.request && !msg->task.task.empty() && msg->task.more) {
-      // unpack
-      std::vector<Task> tasks = msg->task.task;
-      for (auto& t : tasks) {
-        auto unpacked = new Message(t);
-        unpacked->sender = msg->sender;
-        unpacked->recver = msg->recver;
-        if (!Process(unpacked)) { delete msg; return; }
-      }
-      delete msg;
-      continue;
-    }
-    if (!Process(msg)) break;
+    if (!Incoming(msg)) break;
   }
+}
+
+bool Postoffice::Incoming(Message* msg) {
+  if (!msg->task.control && msg->task.request && !msg->task.task.empty() && msg->task.more) {
+    // unpack
+    std::vector<Task> tasks = msg->task.task;
+    for (auto& t : tasks) {
+      auto unpacked = new Message(t);
+      unpacked->sender = msg->sender;
+      unpacked->recver = msg->recver;
+      if (!Process(unpacked)) { delete msg; return false; }
+    }
+    delete msg;
+    return true;
+  }
+  return Process(msg);
 }
 
 bool Postoffice::Process(Message* msg) {

@@ -334,7 +334,7 @@ void Van::PollLoop() {
         m->recver = my_node_.id;
         if (IsLocalPeer(id)) received_from_local_ += bytes;
         else received_from_others_ += bytes;
-        inbox_.push(m);
+        Deliver(m);
       } else {
         // EOF or a broken stream: the peer is gone
         close(fd);
@@ -347,10 +347,29 @@ void Van::PollLoop() {
   for (int fd : fds) close(fd);
 }
 
+void Van::Deliver(const MessagePtr& m) {
+  ULock l(deliver_mu_);
+  if (sink_ && direct_ok_ && inbox_.empty() && !recv_busy_) {
+    PS_VLOG(2) << "recv " << m->ShortDebugString();
+    sink_(m);        // under the lock: Recv() cannot take a later message meanwhile
+    return;
+  }
+  inbox_.push_back(m);
+  deliver_cv_.notify_one();
+}
+
 bool Van::Recv(Message* msg, size_t* recv_bytes) {
   MessagePtr m;
-  if (inproc_) my_endpoint_->queue.wait_and_pop(m);
-  else inbox_.wait_and_pop(m);
+  if (inproc_) {
+    my_endpoint_->queue.wait_and_pop(m);
+  } else {
+    ULock l(deliver_mu_);
+    recv_busy_ = false;              // the caller is done with the message before
+    deliver_cv_.wait(l, [this] { return !inbox_.empty(); });
+    m = inbox_.front();
+    inbox_.pop_front();
+    recv_busy_ = !m->terminate;
+  }
   *msg = *m;
   msg->recver = my_node_.id;
   size_t n = msg->key.size() + 64;
@@ -365,8 +384,10 @@ void Van::WakeUp() {
   auto m = std::make_shared<Message>();
   m->terminate = true;
   m->sender = my_node_.id;
-  if (inproc_) my_endpoint_->queue.push(m);
-  else inbox_.push(m);
+  if (inproc_) { my_endpoint_->queue.push(m); return; }
+  Lock l(deliver_mu_);
+  inbox_.push_back(m);
+  deliver_cv_.notify_one();
 }
 
 std::string Van::Statistic() const {

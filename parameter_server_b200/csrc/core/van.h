@@ -44,6 +44,14 @@ class Van {
   void UpdateMyNode(const Node& n) { my_node_.rank = n.rank; my_node_.key = n.key; }
   const Node& scheduler() const { return scheduler_; }
   void set_disconnect_handler(DisconnectHandler h) { on_disconnect_ = std::move(h); }
+  // tcp: with a sink, and once enable_sink() has been called, the poll thread hands a complete message to the
+  // sink as it arrives instead of queueing it for Recv(): one thread hand-over less per message. It does so
+  // only while nothing is queued and the thread that calls Recv() is back in Recv(), so messages are handled
+  // in their order of arrival and never two at a time. The sink runs on the poll thread and must not block on
+  // a peer (it may queue messages, not write them to sockets). Set before Init().
+  typedef std::function<void(const MessagePtr&)> Sink;
+  void set_sink(Sink s) { sink_ = std::move(s); }
+  void enable_sink() { direct_ok_ = true; }
   // "sent x MB (y local), received ..." summary, as printed at exit
   std::string Statistic() const;
   size_t sent_bytes() const { return sent_to_local_ + sent_to_others_; }
@@ -82,9 +90,16 @@ class Van {
   std::map<NodeID, std::string> hostnames_;
   std::shared_ptr<InProcEndpoint> my_endpoint_;
   std::thread poll_thread_;
-  ThreadsafeQueue<MessagePtr> inbox_;     // tcp: complete messages from PollLoop
+  // tcp: complete messages from PollLoop that wait for Recv()
+  std::mutex deliver_mu_;
+  std::condition_variable deliver_cv_;
+  std::deque<MessagePtr> inbox_;
+  bool recv_busy_ = false;                // the Recv() caller is handling the message it took last
+  std::atomic<bool> direct_ok_{false};
+  void Deliver(const MessagePtr& m);
   std::map<int, NodeID> fd_to_id_;
   DisconnectHandler on_disconnect_;
+  Sink sink_;
   std::atomic<size_t> sent_to_local_{0}, sent_to_others_{0}, received_from_local_{0}, received_from_others_{0};
 };
 
