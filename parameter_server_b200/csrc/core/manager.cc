@@ -80,6 +80,12 @@ void Manager::Stop() {
     // wait until every other node is ready to exit, then release them
     {
       ULock l(nodes_mu_);
+      // A job that only the scheduler works on (model evaluation) can be over before the other nodes have
+      // joined: they must still find the scheduler, register and be sent away properly, or they would
+      // report a lost scheduler. Nodes that were lost on the way are not waited for.
+      nodes_cv_.wait_for(l, std::chrono::seconds(30), [this] {
+        return (num_servers_ >= opt_.num_servers && num_workers_ >= opt_.num_workers) || !failure_notified_.empty();
+      });
       in_exit_ = true;
       nodes_cv_.wait_for(l, std::chrono::seconds(120), [this] { return num_active_nodes_ <= 1; });
     }
