@@ -169,12 +169,14 @@ def build_static(force: bool = False):
     inputs = sorted(core_dir.glob("*.cc")) + sorted(core_dir.glob("*.h"))
     # staleness by the digest of the sources, as for the shared objects: a copy of the tree that carries the
     # archives but not the object files (they are intermediate) must find the archives up to date
+    build_core(force=force)          # the module and the node binary have stamps of their own
     if not force and lib.exists() and main_lib.exists() and not _stale(inputs, lib):
         return lib, main_lib
     libdir.mkdir(exist_ok=True)
     objs = [OBJ / ("core_" + s.stem + ".o") for s in sorted(core_dir.glob("*.cc"))
             if not s.name.startswith("bind") and not s.stem.endswith("_main")]
-    build_core(force=force or not all(o.exists() for o in objs))
+    if not all(o.exists() for o in objs):
+        build_core(force=True)
     _archive(lib, objs)
     main_obj = OBJ / "simple_main.o"
     cxx = os.environ.get("PSB_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
