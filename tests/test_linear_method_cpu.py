@@ -256,6 +256,33 @@ def test_training_data_as_binary_matrices(data, tmp_path):
     assert core.evaluate(y, m)["auc"] > 0.68
 
 
+def test_scheduler_only_job_waits_for_late_nodes(data, tmp_path):
+    """Model evaluation is done by the scheduler alone and takes milliseconds here; a server and a worker that
+    start a second later must still find the scheduler, register, and be released by the exit handshake."""
+    import subprocess
+    import time
+    from parameter_server_b200 import _build
+    from parameter_server_b200.system.cluster import node_string
+    exe = str(_build.PKG / "bin" / "psb_linear")
+    train = tmp_path / "sgd.conf"
+    train.write_text(CONF_SGD.format(train=data["train"], out=str(tmp_path), algo="FTRL", filters=""))
+    res = launch_local_processes(1, 1, [exe, "-app_file", str(train)], timeout=180)
+    assert all(r.returncode == 0 for r in res.values())
+    conf = tmp_path / "eval.conf"
+    conf.write_text(CONF_EVAL.format(val=data["val"], out=str(tmp_path)))
+    sched = node_string("SCHEDULER", "127.0.0.1", core.free_port(), "H")
+    procs = {}
+    for nid, role, delay in (("H", "SCHEDULER", 0.0), ("S0", "SERVER", 1.0), ("W0", "WORKER", 0.0)):
+        time.sleep(delay)
+        spec = sched if nid == "H" else node_string(role, "127.0.0.1", core.free_port(), nid)
+        procs[nid] = subprocess.Popen([exe, "-app_file", str(conf), "-my_node", spec, "-scheduler", sched,
+                                       "-num_servers", "1", "-num_workers", "1"],
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    outs = {nid: p.communicate(timeout=120)[0] for nid, p in procs.items()}
+    assert all(p.returncode == 0 for p in procs.values()), {k: (procs[k].returncode, v[-400:]) for k, v in outs.items()}
+    assert "auc" in outs["H"].lower()
+
+
 def test_darlin_processes_start_reliably(data, tmp_path):
     """Twenty start-ups of 1 scheduler + 2 servers + 2 workers as OS processes: every node
     must be a member of the groups before the scheduler's first group task goes out (a node
