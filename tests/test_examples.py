@@ -75,6 +75,10 @@ def test_kv_api_examples():
                          capture_output=True, text=True, timeout=120)
     assert out.returncode == 0, out.stderr
     assert "pulled [3.0, 6.0, 9.0]" in out.stdout
+    out = subprocess.run([sys.executable, os.path.join(root, "examples", "kv", "kv_layer.py")],
+                         capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    assert "layer 2: 1000 values, every one 3" in out.stdout and "held as [500, 500]" in out.stdout
 
 
 def test_cpp_programs_link_static_runtime(tmp_path):
