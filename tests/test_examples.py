@@ -101,6 +101,9 @@ def test_cpp_programs_link_static_runtime(tmp_path):
     assert all(p.returncode == 0 for p in out.values()), {k: (p.returncode, p.stdout[-300:]) for k, p in out.items()}
     for w in ("W0", "W1"):
         assert f"{w} pulled 3 6 9" in out[w].stdout
+    out = launch_local_processes(1, 2, [compile_("aggregation", [lib])], timeout=120)
+    assert all(p.returncode == 0 for p in out.values()), {k: (p.returncode, p.stdout[-300:]) for k, p in out.items()}
+    assert "W0 pulled 8 12 8 12 8 12 4 6" in out["W0"].stdout and "W1 pulled 8 12 4 6 8 12 8 12" in out["W1"].stdout
     out = launch_local_processes(2, 2, [compile_("network_perf", [lib]), "-n=20", "-data_size=200"], timeout=120)
     assert all(p.returncode == 0 for p in out.values()), {k: (p.returncode, p.stdout[-300:]) for k, p in out.items()}
     for w in ("W0", "W1"):
