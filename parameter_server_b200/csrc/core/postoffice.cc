@@ -107,8 +107,13 @@ void Postoffice::Dispatch(const MessagePtr& msg) {
   // Nothing queued and nobody sending: this thread writes the message itself. A message that another
   // thread queues in the meantime is not ordered against this one anyway; this thread's own earlier
   // messages have left (they were sent here) or are still pending (then this one queues up behind them).
+  // Only what cannot make this thread wait for the peer: submitting threads hold their executor's lock, and a
+  // thread that held it while blocked in a write would stall the node's whole receive path (two nodes doing so
+  // to each other would never read again). Large payloads go through the send thread, which holds no such lock.
+  size_t payload = msg->key.size() + 512;
+  for (auto& v : msg->value) payload += v.size();
   if (running_ && !tl_queue_only && pending_sends_.load() == 0 && send_mu_.try_lock()) {
-    if (pending_sends_.load() == 0) {
+    if (pending_sends_.load() == 0 && manager_.van().WritableNow(msg->recver, payload)) {
       SendNow(msg.get());
       send_mu_.unlock();
       return;

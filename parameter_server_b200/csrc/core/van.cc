@@ -1,5 +1,7 @@
 #include "van.h"
 
+#include <sys/ioctl.h>
+
 #include <arpa/inet.h>
 #include <fcntl.h>
 #include <netdb.h>
@@ -18,6 +20,7 @@ std::map<std::string, std::shared_ptr<Van::InProcEndpoint>> Van::hub_;
 
 static const uint32_t kFrameMagic = 0x50534231;  // "PSB1"
 static const int kSocketBufferBytes = 4 << 20;    // asked of the kernel, which caps it at its own limit
+static const size_t kDirectSendBytes = 64 << 10;  // what a submitting thread may write itself (see WritableNow)
 
 static bool WriteAll(int fd, const void* p, size_t n) {
   const char* c = (const char*)p;
@@ -146,7 +149,7 @@ void Van::Destroy() {
 bool Van::Connect(const Node& node) {
   PS_CHECK(!node.id.empty());
   Lock l(mu_);
-  hostnames_[node.id] = node.hostname;
+  { Lock n(names_mu_); hostnames_[node.id] = node.hostname; }
   if (inproc_) {
     if (in_senders_.count(node.id)) return true;
     // the peer may not have bound yet: wait briefly
@@ -246,6 +249,17 @@ bool Van::Send(Message* msg, size_t* send_bytes) {
   return ok;
 }
 
+bool Van::WritableNow(const NodeID& id, size_t bytes) {
+  if (inproc_) return true;
+  if (bytes > kDirectSendBytes) return false;
+  std::unique_lock<std::mutex> l(mu_, std::try_to_lock);
+  if (!l.owns_lock()) return false;           // somebody is writing: do not wait for it
+  auto it = senders_.find(id);
+  if (it == senders_.end()) return false;
+  int unsent = 0;
+  return ioctl(it->second, TIOCOUTQ, &unsent) == 0 && unsent == 0;
+}
+
 bool Van::SendTcp(int fd, const std::string& header, Message* msg) {
   // [magic][nframes][len...] then the frames: header, (key), values...
   std::vector<uint64_t> lens;
@@ -317,7 +331,7 @@ void Van::PollLoop() {
         std::string id;
         if (ReadAll(fd, hello, sizeof(hello)) && hello[0] == kFrameMagic && hello[1] < 256) {
           id.resize(hello[1]);
-          if (ReadAll(fd, &id[0], hello[1])) { fds.push_back(fd); Lock l(mu_); fd_to_id_[fd] = id; }
+          if (ReadAll(fd, &id[0], hello[1])) { fds.push_back(fd); fd_to_id_[fd] = id; }
           else close(fd);
         } else close(fd);
       }
@@ -328,7 +342,10 @@ void Van::PollLoop() {
       auto m = std::make_shared<Message>();
       size_t bytes = 0;
       NodeID id;
-      { Lock l(mu_); id = fd_to_id_[fd]; }
+      // (no lock: only this thread uses the map, and the lock of the senders must not be waited for here:
+      // a send thread blocked in a write holds it until the peer reads, and the peer reads only while its
+      // own poll thread runs)
+      id = fd_to_id_[fd];
       if (RecvTcp(fd, m.get(), &bytes)) {
         m->sender = id;
         m->recver = my_node_.id;
@@ -339,7 +356,7 @@ void Van::PollLoop() {
         // EOF or a broken stream: the peer is gone
         close(fd);
         fds.erase(std::find(fds.begin(), fds.end(), fd));
-        { Lock l(mu_); fd_to_id_.erase(fd); }
+        fd_to_id_.erase(fd);
         if (running_ && on_disconnect_ && !id.empty()) on_disconnect_(id);
       }
     }

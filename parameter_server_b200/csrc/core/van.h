@@ -49,6 +49,9 @@ class Van {
   // only while nothing is queued and the thread that calls Recv() is back in Recv(), so messages are handled
   // in their order of arrival and never two at a time. The sink runs on the poll thread and must not block on
   // a peer (it may queue messages, not write them to sockets). Set before Init().
+  // true if `bytes` more can be written to the channel to `id` at once without waiting for the peer (nothing
+  // of what was written before is still unsent and the message is far smaller than the socket buffer)
+  bool WritableNow(const NodeID& id, size_t bytes);
   typedef std::function<void(const MessagePtr&)> Sink;
   void set_sink(Sink s) { sink_ = std::move(s); }
   void enable_sink() { direct_ok_ = true; }
@@ -72,9 +75,10 @@ class Van {
   bool RecvTcp(int fd, Message* msg, size_t* bytes);
   void PollLoop();
   bool IsLocal(const Node& n) const { return n.hostname == my_node_.hostname; }
-  // whether peer `id` runs on this host (hostnames_ is guarded by mu_)
+  // whether peer `id` runs on this host. hostnames_ has a lock of its own that is never held across a write:
+  // the poll thread asks this for every message and must not wait for a sender that is blocked on the peer
   bool IsLocalPeer(const NodeID& id) {
-    std::lock_guard<std::mutex> l(mu_);
+    std::lock_guard<std::mutex> l(names_mu_);
     auto h = hostnames_.find(id);
     return h != hostnames_.end() && h->second == my_node_.hostname;
   }
@@ -87,6 +91,7 @@ class Van {
   std::mutex mu_;
   std::map<NodeID, int> senders_;                                 // tcp: peer id -> fd
   std::map<NodeID, std::shared_ptr<InProcEndpoint>> in_senders_;  // inproc peers
+  std::mutex names_mu_;
   std::map<NodeID, std::string> hostnames_;
   std::shared_ptr<InProcEndpoint> my_endpoint_;
   std::thread poll_thread_;

@@ -45,7 +45,7 @@ training_data {{ format: TEXT text: SPARSE_BINARY file: "{train}/part.*" }}
 model_output {{ format: TEXT file: "{out}/darlin" }}
 loss {{ type: LOGIT }}
 penalty {{ type: L1 lambda: 2 }}
-learning_rate {{ type: CONSTANT alpha: 0.9 }}
+learning_rate {{ type: CONSTANT alpha: 0.5 }}
 darlin {{
   max_pass_of_data: 12
   epsilon: 1e-4
@@ -149,7 +149,7 @@ def test_darlin_starts_from_given_weights(data, tmp_path):
         y, m = _score(data["train_files"], w)
         objs[name] = (np.log1p(np.exp(-y * m)).sum() + 2 * sum(abs(v) for v in w.values()), w)
     assert objs["const1"][1] != objs["zero1"][1]
-    assert objs["const"][0] < 0.93 * len(y) * np.log(2)
+    assert objs["const"][0] < 0.95 * len(y) * np.log(2)          # well below the zero model
     assert abs(objs["const"][0] - objs["zero"][0]) < 0.1 * objs["zero"][0], (objs["const"][0], objs["zero"][0])
 
 
